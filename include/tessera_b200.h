@@ -1,0 +1,154 @@
+/*
+ * tessera_b200 -- C ABI of the sm_100a CUDA backend for Tessera's quantized
+ * projection path.
+ *
+ * The entry points mirror, one for one, what an implementation of the
+ * reference's `tessera::Backend` (include/tessera/backend.hpp:847-1037) has
+ * to provide: device set-up, buffers, copies, synchronisation and a
+ * name-keyed kernel launch.  The host-side `CudaBackend` class
+ * (tessera_b200/backend/cuda_backend.cpp) is a thin C++23 wrapper over these
+ * calls; any other host language can bind them directly.
+ *
+ * Conventions: plain pointers and sizes only; every call returns 0 on
+ * success or a positive code equal to the reference's `tessera::StatusCode`
+ * (include/tessera/types.hpp:38-48).  All device work of one context is
+ * issued on that context's stream, in call order.  Nothing here falls back
+ * to the CPU: without a CUDA device every call fails with TSR_DEVICE_ERROR.
+ */
+#ifndef TESSERA_B200_H_
+#define TESSERA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum tsr_status {
+  TSR_OK = 0,
+  TSR_INVALID_ARGUMENT = 1,
+  TSR_UNSUPPORTED_FEATURE = 4,
+  TSR_OUT_OF_MEMORY = 5,
+  TSR_DEVICE_ERROR = 6
+};
+
+/* MemoryKind, include/tessera/backend.hpp:22-25 */
+enum tsr_memory_kind { TSR_MEM_DEVICE = 0, TSR_MEM_HOST_VISIBLE = 1 };
+
+typedef struct tsr_context tsr_context;
+
+/* ---- devices: ListGpuNames(), backend.hpp:1066-1071 -------------------- */
+int tsr_device_count(int* count);
+int tsr_device_name(int device, char* out, size_t capacity);
+
+/* ---- context: Backend::SetDeviceIndex + Init, backend.hpp:871-894 -------
+ * tsr_create owns a non-blocking stream.  tsr_create_on_stream borrows a
+ * caller-owned cudaStream_t (for hosts that already run a stream). */
+int tsr_create(int device_index, tsr_context** out);
+int tsr_create_on_stream(int device_index, void* cuda_stream, tsr_context** out);
+void tsr_destroy(tsr_context* ctx);
+int tsr_context_device(const tsr_context* ctx);
+void* tsr_context_stream(const tsr_context* ctx);
+/* Backend::DeviceName / MemoryInfo, backend.hpp:853-860 */
+int tsr_memory_info(tsr_context* ctx, uint64_t* total_bytes, uint64_t* free_bytes);
+/* Text of the last failure on this context (never NULL). */
+const char* tsr_last_error(const tsr_context* ctx);
+
+/* ---- buffers: AllocateBuffer / FreeBuffer, backend.hpp:896-912 ----------
+ * bytes == 0 is TSR_INVALID_ARGUMENT.  Device allocations are served from a
+ * per-context pool so that a mid-step allocation (scratch growth in
+ * src/models/qwen3_5/project.cpp:127-138) does not synchronise the device.
+ * host_map receives the host address for TSR_MEM_HOST_VISIBLE, else NULL. */
+int tsr_alloc(tsr_context* ctx, size_t bytes, int kind, void** handle, void** host_map);
+int tsr_free(tsr_context* ctx, int kind, void* handle);
+
+/* ---- copies: CopyH2DAt / CopyD2HAt / CopyD2D / CopyPeerFrom,
+ * backend.hpp:918-1003.  h2d returns once `src` is reusable and is ordered
+ * before later launches; d2h blocks until the bytes are in `dst`; d2d is
+ * stream-ordered and does not block.  Bounds are the caller's (the C++
+ * wrapper checks them against Buffer::Size()). */
+int tsr_copy_h2d(tsr_context* ctx, void* dst, size_t dst_offset, const void* src, size_t bytes);
+int tsr_copy_d2h(tsr_context* ctx, const void* src, size_t src_offset, void* dst, size_t bytes);
+int tsr_copy_d2d(tsr_context* ctx, const void* src, size_t src_offset, void* dst, size_t dst_offset,
+                 size_t bytes);
+/* dst lives on ctx's device, src on src_device (peer access is enabled on
+ * first use; the copy is complete on return). */
+int tsr_copy_peer(tsr_context* ctx, void* dst, int src_device, const void* src, size_t bytes);
+/* Backend::Synchronize, backend.hpp:1026 */
+int tsr_synchronize(tsr_context* ctx);
+
+/* ---- kernels by name: LoadKernel / LaunchKernel, backend.hpp:1005-1023 --
+ * tsr_kernel_lookup returns the id (>= 0) of a built-in or -1 when this
+ * backend does not implement the name (the C++ wrapper maps that to
+ * UnsupportedFeature, which the reference's callers treat as "fall back",
+ * src/core/decode_internal.hpp:1297-1323).
+ *
+ * tsr_launch binds buffers first, then 64-bit scalars, in the parameter order
+ * of the reference's per-kernel contracts (backend.hpp:150-390 and the kernel
+ * sources cited beside each id in tessera_b200/csrc/dispatch.cu).  The grid
+ * and block of the reference's KernelLaunch are accepted and validated
+ * (non-zero) but, like the Vulkan backend with block_*, the launch shape is
+ * chosen here from the scalars; only grid_y of the split-K families is
+ * meaningful and it must equal the `split` scalar.  buffer_bytes[i] is the
+ * size of buffer i; every launch checks it against the bytes the scalars
+ * imply and fails with TSR_INVALID_ARGUMENT instead of reading out of range. */
+int tsr_kernel_count(void);
+const char* tsr_kernel_name(int kernel);
+int tsr_kernel_lookup(const char* name);
+int tsr_launch(tsr_context* ctx, int kernel, const uint32_t grid[3], const uint32_t block[3],
+               const void* const* buffers, const size_t* buffer_bytes, int n_buffers,
+               const uint64_t* scalars, int n_scalars);
+
+/* ---- typed launchers (what tsr_launch dispatches to) ---------------------
+ * `stream` is a cudaStream_t.  Shapes follow C[m,n] = A[m,k] . dq(W[n,k])^T.
+ * All pointers are device pointers; A, C and scale vectors need 16-byte
+ * alignment, weights 16-byte (Q6_K: 2-byte) alignment. */
+
+/* gemm_q4k_vec, gemm_q4k_rows{2..5}: src/backends/vulkan/kernels/gemm_q4k_vec.comp:66-104,
+ * gemm_q4k_rows2.comp:63-109; oracle GemmQ4KRef src/core/numerics/gemm.cpp:62-73.
+ * split > 1 writes chunk y of the k range to region y of c (c holds split*m*n floats). */
+int tsr_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                 uint64_t split, void* stream);
+/* gemm_q6k_vec, gemm_q6k_rows{2..5}: gemm_q6k_vec.comp:49-106; GemmQ6KRef gemm.cpp:88-99 */
+int tsr_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                 uint64_t split, void* stream);
+/* gemm_vec_reduce: gemm_vec_reduce.comp:20-32 (also gemm_mxfp4_wmma_reduce,
+ * src/backends/rocm/rocm_kernels_basic.cpp:1497-1510) */
+int tsr_gemm_vec_reduce(const float* part, float* c, uint64_t total, uint64_t split, void* stream);
+/* gemm_mxfp4, gemm_mxfp4_rows, gemm_mxfp4_batched: gemm_mxfp4.comp:51-87; GemmMxFp4Ref
+ * gemm.cpp:311-344.  w = n*k/2 nibble bytes followed by n*k/32 E8M0 bytes. */
+int tsr_gemm_mxfp4(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                   void* stream);
+/* gemm_fp8: gemm_fp8.comp:52-68; GemmFp8Ref gemm.cpp:253-277 */
+int tsr_gemm_fp8(const float* a, const void* w, const float* s, float* c, uint64_t m, uint64_t n,
+                 uint64_t k, void* stream);
+/* gemm_mxfp4_wmma (W4A8): gemm_mxfp4_wmma.comp:78-117; a = m*k E4M3 bytes, as = m fp32
+ * token scales, wref = n E8M0 bytes, c = split regions of m*n. */
+int tsr_gemm_mxfp4_w4a8(const void* a_fp8, const void* w, const float* as, const void* wref,
+                        float* c, uint64_t m, uint64_t n, uint64_t k, uint64_t split,
+                        void* stream);
+/* mxfp4_row_ref: mxfp4_row_ref.comp:26-40 */
+int tsr_mxfp4_row_ref(const void* w, void* wref, uint64_t n, uint64_t k, void* stream);
+/* quantize_fp8: quantize_fp8.comp:74-105; QuantizeFp8Ref src/core/numerics/quant.cpp:180-205 */
+int tsr_quantize_fp8(float* data, float* scale, uint64_t rows, uint64_t cols, void* stream);
+/* quantize_fp8_pack, quantize_fp8_pack_rows: quantize_fp8_pack_rows.comp:60-95;
+ * QuantizeFp8PackRef quant.cpp:207-229 */
+int tsr_quantize_fp8_pack(const float* in, void* out, float* scale, uint64_t rows, uint64_t cols,
+                          void* stream);
+/* round_bf16: round_bf16.comp:14-24; RoundBf16Ref quant.cpp:231-243 */
+int tsr_round_bf16(float* x, uint64_t n, void* stream);
+/* add, fill: backend.hpp:150-152,258-260 */
+int tsr_add(const float* a, const float* b, float* o, uint64_t n, void* stream);
+int tsr_fill(int32_t* data, int32_t value, uint64_t n, void* stream);
+/* Dequantise whole blocks to fp32 with the reference's rounding sequence
+ * (bit-exact check of the codecs).  fmt: 0 Q4_K (quant.cpp:656-675), 1 Q6_K
+ * (quant.cpp:421-449), 2 MXFP4 packed n x k (quant.cpp:279-297), 3 FP8 E4M3
+ * bytes with per-row scale (gemm.cpp:266-270). */
+int tsr_dequantize(int fmt, const void* w, const float* row_scale, float* out, uint64_t n,
+                   uint64_t k, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,214 @@
+"""ctypes front-end of the CPU oracle.  TEST INFRASTRUCTURE ONLY.
+
+``Oracle()`` loads ``oracle/liboracle.so`` (the plain-C restatement);
+``Oracle(reference=True)`` loads ``oracle/_ref/libtessera_ref.so`` (the
+reference's own host functions) when it was built.  Both expose the same
+numpy-level calls, so either can check a CUDA result or be timed as the CPU
+baseline.  Only tests, the smoke check and the benchmark's CPU-baseline leg
+import this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "liboracle.so")
+REF_SO = os.path.join(_HERE, "_ref", "libtessera_ref.so")
+
+_sz = C.c_size_t
+_p = C.c_void_p
+
+
+def build(reference_root: str = "/root/reference") -> None:
+    subprocess.run(["make", "-C", _HERE, f"REFERENCE={reference_root}"], check=True,
+                   stdout=subprocess.DEVNULL)
+
+
+def reference_available() -> bool:
+    return os.path.exists(REF_SO)
+
+
+def _ptr(a: np.ndarray):
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(_p)
+
+
+class Oracle:
+    def __init__(self, reference: bool = False):
+        self.reference = reference
+        path = REF_SO if reference else ORACLE_SO
+        if not os.path.exists(path):
+            if reference:
+                raise FileNotFoundError(path)
+            build()
+        self.lib = C.CDLL(path)
+        self.pre = "ref_" if reference else "orc_"
+
+    def _fn(self, name, restype, argtypes):
+        fn = getattr(self.lib, self.pre + name)
+        fn.restype, fn.argtypes = restype, argtypes
+        return fn
+
+    # ---- scalar codecs (vectorised by looping in Python: small inputs only)
+    def _map(self, name, restype, argtype, values, out_dtype):
+        fn = self._fn(name, restype, [argtype])
+        return np.array([fn(v) for v in values], dtype=out_dtype)
+
+    def fp16_to_float(self, h):
+        return self._map("fp16_to_float", C.c_float, C.c_uint16, [int(x) for x in h], np.float32)
+
+    def fp8e4m3_to_float(self, b):
+        return self._map("fp8e4m3_to_float", C.c_float, C.c_uint8, [int(x) for x in b], np.float32)
+
+    def e8m0_to_float(self, b):
+        return self._map("e8m0_to_float", C.c_float, C.c_uint8, [int(x) for x in b], np.float32)
+
+    def f4e2m1_to_float(self, b):
+        return self._map("f4e2m1_to_float", C.c_float, C.c_uint8, [int(x) for x in b], np.float32)
+
+    def fp32_to_fp8e4m3(self, v):
+        return self._map("fp32_to_fp8e4m3", C.c_uint8, C.c_float, [float(x) for x in v], np.uint8)
+
+    def fp32_to_f4e2m1(self, v):
+        return self._map("fp32_to_f4e2m1", C.c_uint8, C.c_float, [float(x) for x in v], np.uint8)
+
+    # ---- blocks
+    def dequant_blocks(self, fmt: int, w: np.ndarray) -> np.ndarray:
+        bb = 144 if fmt == 0 else 210
+        nb = w.size // bb
+        out = np.empty(nb * 256, dtype=np.float32)
+        fn = self._fn("dequant_blocks", C.c_int, [C.c_int, _p, _sz, _p])
+        assert fn(fmt, _ptr(w), nb, _ptr(out)) == 0
+        return out
+
+    # ---- GEMMs
+    def _gemm3(self, name, a, w, m, n, k, threads=0):
+        c = np.empty((m, n), dtype=np.float32)
+        if threads and not self.reference:
+            fn = self._fn(name + "_mt", C.c_int, [_p, _p, _p, _sz, _sz, _sz, C.c_int])
+            rc = fn(_ptr(a), _ptr(w), _ptr(c), m, n, k, threads)
+        else:
+            fn = self._fn(name, C.c_int, [_p, _p, _p, _sz, _sz, _sz])
+            rc = fn(_ptr(a), _ptr(w), _ptr(c), m, n, k)
+        assert rc == 0, rc
+        return c
+
+    def gemm_q4k(self, a, w, m, n, k, threads=0):
+        return self._gemm3("gemm_q4k", a, w, m, n, k, threads)
+
+    def gemm_q6k(self, a, w, m, n, k, threads=0):
+        return self._gemm3("gemm_q6k", a, w, m, n, k, threads)
+
+    def gemm_mxfp4(self, a, w_packed, m, n, k, threads=0):
+        """w_packed is the device layout blob||scales."""
+        blob = np.ascontiguousarray(w_packed[: n * k // 2])
+        sc = np.ascontiguousarray(w_packed[n * k // 2:])
+        c = np.empty((m, n), dtype=np.float32)
+        if threads and not self.reference:
+            fn = self._fn("gemm_mxfp4_mt", C.c_int, [_p, _p, _p, _p, _sz, _sz, _sz, C.c_int])
+            rc = fn(_ptr(a), _ptr(blob), _ptr(sc), _ptr(c), m, n, k, threads)
+        else:
+            fn = self._fn("gemm_mxfp4", C.c_int, [_p, _p, _p, _p, _sz, _sz, _sz])
+            rc = fn(_ptr(a), _ptr(blob), _ptr(sc), _ptr(c), m, n, k)
+        assert rc == 0, rc
+        return c
+
+    def gemm_fp8(self, a, w, s, m, n, k, threads=0):
+        c = np.empty((m, n), dtype=np.float32)
+        if threads and not self.reference:
+            fn = self._fn("gemm_fp8_mt", C.c_int, [_p, _p, _p, _p, _sz, _sz, _sz, C.c_int])
+            rc = fn(_ptr(a), _ptr(w), _ptr(s), _ptr(c), m, n, k, threads)
+        else:
+            fn = self._fn("gemm_fp8", C.c_int, [_p, _p, _p, _p, _sz, _sz, _sz])
+            rc = fn(_ptr(a), _ptr(w), _ptr(s), _ptr(c), m, n, k)
+        assert rc == 0, rc
+        return c
+
+    # ---- activation quantisation
+    def quantize_fp8(self, data: np.ndarray):
+        rows, cols = data.shape
+        out = np.ascontiguousarray(data, dtype=np.float32).copy()
+        scale = np.empty(rows, dtype=np.float32)
+        fn = self._fn("quantize_fp8", C.c_int, [_p, _p, _sz, _sz])
+        assert fn(_ptr(out), _ptr(scale), rows, cols) == 0
+        return out, scale
+
+    def quantize_fp8_pack(self, data: np.ndarray):
+        rows, cols = data.shape
+        codes = np.empty((rows, cols), dtype=np.uint8)
+        scale = np.empty(rows, dtype=np.float32)
+        fn = self._fn("quantize_fp8_pack", C.c_int, [_p, _p, _p, _sz, _sz])
+        assert fn(_ptr(np.ascontiguousarray(data, dtype=np.float32)), _ptr(codes), _ptr(scale), rows, cols) == 0
+        return codes, scale
+
+    def round_bf16(self, x: np.ndarray) -> np.ndarray:
+        out = np.ascontiguousarray(x, dtype=np.float32).copy()
+        fn = self._fn("round_bf16", C.c_int, [_p, _sz])
+        assert fn(_ptr(out), out.size) == 0
+        return out
+
+    # ---- W4A8
+    def fold_mxfp4_to_fp8(self, w_packed, rows, cols):
+        blob = np.ascontiguousarray(w_packed[: rows * cols // 2])
+        sc = np.ascontiguousarray(w_packed[rows * cols // 2:])
+        out = np.empty((rows, cols), dtype=np.uint8)
+        wref = np.empty(rows, dtype=np.uint8)
+        fn = self._fn("fold_mxfp4_to_fp8", C.c_int, [_p, _p, _p, _p, _sz, _sz])
+        assert fn(_ptr(blob), _ptr(sc), _ptr(out), _ptr(wref), rows, cols) == 0
+        return out, wref
+
+    def gemm_mxfp4_fp8(self, a8, as_, w8, wref, m, n, k):
+        c = np.empty((m, n), dtype=np.float32)
+        fn = self._fn("gemm_mxfp4_fp8", C.c_int, [_p, _p, _p, _p, _p, _sz, _sz, _sz])
+        assert fn(_ptr(a8), _ptr(as_), _ptr(w8), _ptr(wref), _ptr(c), m, n, k) == 0
+        return c
+
+    # ---- restatement-only entry points (device contracts with no host ref)
+    def gemm_vec_split(self, fmt, a, w, m, n, k, split):
+        assert not self.reference
+        part = np.empty((split, m, n), dtype=np.float32)
+        fn = self._fn("gemm_vec_split", C.c_int, [C.c_int, _p, _p, _p, _sz, _sz, _sz, _sz])
+        assert fn(fmt, _ptr(a), _ptr(w), _ptr(part), m, n, k, split) == 0
+        return part
+
+    def gemm_vec_reduce(self, part):
+        assert not self.reference
+        split = part.shape[0]
+        total = part.size // split
+        c = np.empty(total, dtype=np.float32)
+        fn = self._fn("gemm_vec_reduce", C.c_int, [_p, _p, _sz, _sz])
+        assert fn(_ptr(part), _ptr(c), total, split) == 0
+        return c
+
+    def gemm_vec_split_rule(self, outputs, k, target=2048):
+        fn = self._fn("gemm_vec_split_rule", _sz, [_sz, _sz, _sz])
+        return fn(outputs, k, target)
+
+    def mxfp4_row_ref(self, w_packed, rows, cols):
+        assert not self.reference
+        sc = np.ascontiguousarray(w_packed[rows * cols // 2:])
+        wref = np.empty(rows, dtype=np.uint8)
+        fn = self._fn("mxfp4_row_ref", C.c_int, [_p, _p, _sz, _sz])
+        assert fn(_ptr(sc), _ptr(wref), rows, cols) == 0
+        return wref
+
+    def gemm_mxfp4_wmma(self, a8, w_packed, as_, wref, m, n, k, split):
+        assert not self.reference
+        c = np.empty((split, m, n), dtype=np.float32)
+        fn = self._fn("gemm_mxfp4_wmma", C.c_int, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _sz])
+        assert fn(_ptr(a8), _ptr(w_packed), _ptr(as_), _ptr(wref), _ptr(c), m, n, k, split) == 0
+        return c
+
+    def tp_reduce(self, partials):
+        assert not self.reference
+        world = len(partials)
+        count = partials[0].size
+        arr = (C.c_void_p * world)(*[p.ctypes.data for p in partials])
+        out = np.empty(count, dtype=np.float32)
+        fn = self._fn("tp_reduce", C.c_int, [_p, _sz, _sz, _p])
+        assert fn(arr, world, count, _ptr(out)) == 0
+        return out.reshape(partials[0].shape)

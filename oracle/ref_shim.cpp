@@ -1,0 +1,105 @@
+// C-ABI shim over the reference's own host reference functions
+// (tessera::core::*Ref).  TEST INFRASTRUCTURE ONLY.  It is compiled together
+// with the reference's src/core/numerics/{quant,gemm}.cpp, taken from where
+// the reference checkout lies, into oracle/_ref/libtessera_ref.so by
+// oracle/Makefile.  It pins the C restatement in oracle.c and can serve as
+// the timed CPU baseline.  No reference source is copied: this file only
+// calls the reference's public functions.
+#include <cstddef>
+#include <cstdint>
+#include <span>
+
+#include "core/numerics/gemm.hpp"
+#include "core/numerics/quant.hpp"
+
+namespace tc = tessera::core;
+
+namespace {
+template <typename T>
+std::span<const std::byte> Bytes(const T* p, std::size_t n) {
+  return {reinterpret_cast<const std::byte*>(p), n};
+}
+template <typename T>
+std::span<std::byte> MutBytes(T* p, std::size_t n) {
+  return {reinterpret_cast<std::byte*>(p), n};
+}
+template <typename E>
+int Code(const E& result) {
+  return result ? 0 : -static_cast<int>(result.error());
+}
+}  // namespace
+
+extern "C" {
+
+float ref_fp16_to_float(std::uint16_t h) { return tc::Fp16ToFloat(h); }
+float ref_bf16_to_float(std::uint16_t b) { return tc::Bf16ToFloat(b); }
+float ref_fp8e4m3_to_float(std::uint8_t b) { return tc::Fp8E4M3ToFloat(b); }
+float ref_e8m0_to_float(std::uint8_t s) { return tc::E8M0ToFloat(s); }
+float ref_f4e2m1_to_float(std::uint8_t n) { return tc::F4E2M1ToFloat(n); }
+std::uint8_t ref_fp32_to_fp8e4m3(float v) { return tc::Fp32ToFp8E4M3Bits(v); }
+std::uint8_t ref_fp32_to_f4e2m1(float v) { return tc::Fp32ToF4E2M1Nibble(v); }
+std::uint16_t ref_fp16_from_float(float v) { return tc::Fp16FromFloat(v); }
+
+int ref_dequant_blocks(int fmt, const std::uint8_t* bytes, std::size_t nblocks, float* out) {
+  const std::size_t bb = fmt == 0 ? 144 : 210;
+  for (std::size_t b = 0; b < nblocks; ++b) {
+    auto in = Bytes(bytes + b * bb, bb);
+    std::span<float> o(out + b * 256, 256);
+    if (fmt == 0) {
+      tc::DequantizeQ4K(in, o);
+    } else if (fmt == 1) {
+      tc::DequantizeQ6K(in, o);
+    } else {
+      return -1;
+    }
+  }
+  return 0;
+}
+
+int ref_quantize_q4k(const float* values, std::size_t nblocks, std::uint8_t* out) {
+  for (std::size_t b = 0; b < nblocks; ++b) {
+    tc::QuantizeQ4K(std::span<const float>(values + b * 256, 256),
+                    reinterpret_cast<std::byte*>(out + b * 144));
+  }
+  return 0;
+}
+
+int ref_gemm_q4k(const float* a, const std::uint8_t* w, float* c, std::size_t m, std::size_t n,
+                 std::size_t k) {
+  return Code(tc::GemmQ4KRef({a, m * k}, Bytes(w, n * (k / 256) * 144), {c, m * n}, m, n, k));
+}
+int ref_gemm_q6k(const float* a, const std::uint8_t* w, float* c, std::size_t m, std::size_t n,
+                 std::size_t k) {
+  return Code(tc::GemmQ6KRef({a, m * k}, Bytes(w, n * (k / 256) * 210), {c, m * n}, m, n, k));
+}
+int ref_gemm_mxfp4(const float* a, const std::uint8_t* w, const std::uint8_t* s, float* c,
+                   std::size_t m, std::size_t n, std::size_t k) {
+  return Code(tc::GemmMxFp4Ref({a, m * k}, Bytes(w, n * (k / 2)), Bytes(s, n * (k / 32)),
+                               {c, m * n}, m, n, k));
+}
+int ref_gemm_fp8(const float* a, const std::uint8_t* w, const float* s, float* c, std::size_t m,
+                 std::size_t n, std::size_t k) {
+  return Code(tc::GemmFp8Ref({a, m * k}, Bytes(w, n * k), {s, n}, {c, m * n}, m, n, k));
+}
+int ref_quantize_fp8(float* data, float* scale, std::size_t rows, std::size_t cols) {
+  return Code(tc::QuantizeFp8Ref({data, rows * cols}, {scale, rows}, rows, cols));
+}
+int ref_quantize_fp8_pack(const float* in, std::uint8_t* out, float* scale, std::size_t rows,
+                          std::size_t cols) {
+  return Code(tc::QuantizeFp8PackRef({in, rows * cols}, MutBytes(out, rows * cols), {scale, rows},
+                                     rows, cols));
+}
+int ref_round_bf16(float* x, std::size_t n) { return Code(tc::RoundBf16Ref({x, n})); }
+int ref_fold_mxfp4_to_fp8(const std::uint8_t* w, const std::uint8_t* scales, std::uint8_t* out,
+                          std::uint8_t* wref, std::size_t rows, std::size_t cols) {
+  return Code(tc::FoldMxFp4ToFp8(Bytes(w, rows * cols / 2), Bytes(scales, rows * (cols / 32)),
+                                 MutBytes(out, rows * cols), MutBytes(wref, rows), rows, cols));
+}
+int ref_gemm_mxfp4_fp8(const std::uint8_t* a_fp8, const float* as, const std::uint8_t* w_fp8,
+                       const std::uint8_t* wref, float* c, std::size_t m, std::size_t n,
+                       std::size_t k) {
+  return Code(tc::GemmMxFp4Fp8Ref(Bytes(a_fp8, m * k), {as, m}, Bytes(w_fp8, n * k),
+                                  Bytes(wref, n), {c, m * n}, m, n, k));
+}
+
+}  // extern "C"

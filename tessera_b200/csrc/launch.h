@@ -1,0 +1,37 @@
+// Internal launcher prototypes shared by the .cu files of the library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tsr {
+
+// Status values equal tessera::StatusCode (include/tessera/types.hpp:38-48).
+constexpr int kOk = 0;
+constexpr int kInvalidArgument = 1;
+constexpr int kUnsupportedFeature = 4;
+constexpr int kOutOfMemory = 5;
+constexpr int kDeviceError = 6;
+
+// Maps the pending launch error (cudaGetLastError) to a status.
+inline int check_launch() {
+  const cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return kOk;
+  if (e == cudaErrorMemoryAllocation) return kOutOfMemory;
+  if (e == cudaErrorInvalidValue || e == cudaErrorInvalidConfiguration) return kInvalidArgument;
+  return kDeviceError;
+}
+
+// General warp-per-row family (gemv_rows.cu).
+int rows_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                  uint64_t split, cudaStream_t st);
+int rows_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                  uint64_t split, cudaStream_t st);
+int rows_gemm_mxfp4(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                    cudaStream_t st);
+int rows_gemm_fp8(const float* a, const void* w, const float* s, float* c, uint64_t m, uint64_t n,
+                  uint64_t k, cudaStream_t st);
+int rows_gemm_w4a8(const void* a8, const void* w, const float* as, const void* wref, float* c,
+                   uint64_t m, uint64_t n, uint64_t k, uint64_t split, cudaStream_t st);
+
+}  // namespace tsr
