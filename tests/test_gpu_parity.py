@@ -1,0 +1,311 @@
+"""CUDA kernels against the CPU oracle and the golden fixtures, driven through
+the C ABI the way the reference's projection code drives its backend."""
+import numpy as np
+import pytest
+
+from tessera_b200 import synth
+from tessera_b200.backend import KernelLaunch
+from tessera_b200.capi import StatusCode, StatusError
+from tessera_b200.project import F4E2M1, Q4K, Q6K, GemmVecSplit, Projector
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3  # max |y - ref| / max |ref| for fp32-accumulated projection outputs
+
+
+def run_named(backend, name, buffers, scalars, grid_y=1):
+    k = backend.LoadKernel(name)
+    backend.LaunchKernel(k, KernelLaunch(grid_y=grid_y, buffers=buffers, scalars=scalars))
+
+
+# ------------------------------------------------------------ codecs, exact
+
+@pytest.mark.parametrize("fmt,name", [(0, "q4k"), (1, "q6k")])
+def test_dequantised_blocks_are_bit_exact(backend, golden, fmt, name):
+    import ctypes as C
+    w = golden[f"{name}_w"]
+    n, k = 16, 512
+    wb = backend.upload(w)
+    out = backend.AllocateBuffer(n * k * 4)
+    rc = backend._lib.tsr_dequantize(fmt, wb.Handle(), None, out.Handle(), n, k, backend.stream())
+    assert rc == 0
+    got = backend.download(out, np.float32, n * k)
+    assert np.array_equal(got, golden[f"{name}_dequant"])
+
+
+def test_dequantised_mxfp4_and_fp8_are_bit_exact(backend, oracle, golden):
+    n, k = 16, 512
+    wm = golden["mxfp4_w"]
+    wb = backend.upload(wm)
+    out = backend.AllocateBuffer(n * k * 4)
+    assert backend._lib.tsr_dequantize(2, wb.Handle(), None, out.Handle(), n, k, backend.stream()) == 0
+    got = backend.download(out, np.float32, n * k).reshape(n, k)
+    blob, sc = wm[: n * k // 2].reshape(n, k // 2), wm[n * k // 2:].reshape(n, k // 32)
+    nib = np.stack([blob & 15, blob >> 4], axis=-1).reshape(n, k)
+    exp = golden["e2m1_decode"][nib] * np.repeat(golden["e8m0_decode"][sc], 32, axis=1)
+    assert np.array_equal(got, exp.astype(np.float32))
+    kf = 200
+    wf, sf = golden["fp8_w"], golden["fp8_s"]
+    out2 = backend.AllocateBuffer(n * kf * 4)
+    sb = backend.upload(sf)
+    assert backend._lib.tsr_dequantize(3, backend.upload(wf).Handle(), sb.Handle(), out2.Handle(), n, kf,
+                                       backend.stream()) == 0
+    got2 = backend.download(out2, np.float32, n * kf).reshape(n, kf)
+    exp2 = (sf[:, None] * golden["e4m3_decode"][wf.reshape(n, kf)]).astype(np.float32)
+    assert np.array_equal(got2, exp2)
+
+
+def test_quantize_fp8_matches_golden_bit_exact(backend, golden):
+    x = golden["quant_in"]
+    rows, cols = x.shape
+    data = backend.upload(x)
+    scale = backend.AllocateBuffer(rows * 4)
+    run_named(backend, "quantize_fp8", [data, scale], [rows, cols])
+    got = backend.download(data, np.float32, rows * cols).reshape(rows, cols)
+    assert np.array_equal(backend.download(scale, np.float32, rows), golden["quant_scale"])
+    assert np.array_equal(got.view(np.uint32), golden["quant_qdq"].view(np.uint32)) or \
+        np.array_equal(got, golden["quant_qdq"], equal_nan=True)
+
+
+@pytest.mark.parametrize("name", ["quantize_fp8_pack", "quantize_fp8_pack_rows"])
+def test_quantize_fp8_pack_matches_golden_bit_exact(backend, golden, name):
+    x = golden["quant_in"]
+    rows, cols = x.shape
+    src = backend.upload(x)
+    codes = backend.AllocateBuffer(rows * cols)
+    scale = backend.AllocateBuffer(rows * 4)
+    run_named(backend, name, [src, codes, scale], [rows, cols])
+    assert np.array_equal(backend.download(codes, np.uint8, rows * cols).reshape(rows, cols), golden["quant_codes"])
+    assert np.array_equal(backend.download(scale, np.float32, rows), golden["quant_scale"])
+
+
+def test_quantize_fp8_random_rows_bit_exact(backend, oracle):
+    x = synth.activations(16, 5120, seed=21)
+    x[3] *= 1e-3
+    x[7] *= 300.0
+    codes_ref, scale_ref = oracle.quantize_fp8_pack(x)
+    qdq_ref, _ = oracle.quantize_fp8(x)
+    src = backend.upload(x)
+    codes = backend.AllocateBuffer(x.size)
+    scale = backend.AllocateBuffer(16 * 4)
+    run_named(backend, "quantize_fp8_pack_rows", [src, codes, scale], [16, 5120])
+    assert np.array_equal(backend.download(codes, np.uint8, x.size).reshape(16, 5120), codes_ref)
+    assert np.array_equal(backend.download(scale, np.float32, 16), scale_ref)
+    run_named(backend, "quantize_fp8", [src, scale], [16, 5120])
+    assert np.array_equal(backend.download(src, np.float32, x.size).reshape(16, 5120), qdq_ref)
+
+
+def test_round_bf16_add_fill_row_ref_exact(backend, oracle, golden):
+    x = golden["encode_in"]
+    x = x[np.isfinite(x)]
+    buf = backend.upload(x)
+    run_named(backend, "round_bf16", [buf], [x.size])
+    assert np.array_equal(backend.download(buf, np.float32, x.size), golden["round_bf16"])
+    a = synth.activations(1, 1000, seed=1).reshape(-1)
+    b = synth.activations(1, 1000, seed=2).reshape(-1)
+    o = backend.AllocateBuffer(4000)
+    run_named(backend, "add", [backend.upload(a), backend.upload(b), o], [1000])
+    assert np.array_equal(backend.download(o, np.float32, 1000), a + b)
+    run_named(backend, "fill", [o], [0xFFFFFFFF & -7, 1000])
+    assert (backend.download(o, np.int32, 1000) == -7).all()
+    wm = golden["mxfp4_w"]
+    wref = backend.AllocateBuffer(16)
+    run_named(backend, "mxfp4_row_ref", [backend.upload(wm), wref], [16, 512])
+    assert np.array_equal(backend.download(wref, np.uint8, 16), golden["w4a8_wref"])
+
+
+# ------------------------------------------------ projections vs golden
+
+def test_projections_match_golden(backend, golden):
+    a = backend.upload(golden["a"])
+    m, n, k = 3, 16, 512
+    out = backend.AllocateBuffer(m * n * 4)
+    for name, ids in (("q4k", ["gemm_q4k", "gemm_q4k_vec", "gemm_q4k_rows3", "gemm_q4k_batched", "gemm_q4k_wmma"]),
+                      ("q6k", ["gemm_q6k", "gemm_q6k_vec", "gemm_q6k_rows3", "gemm_q6k_batched", "gemm_q6k_wmma"]),
+                      ("mxfp4", ["gemm_mxfp4", "gemm_mxfp4_rows", "gemm_mxfp4_batched"])):
+        w = backend.upload(golden[f"{name}_w"])
+        for kid in ids:
+            run_named(backend, "fill", [out], [0, m * n])
+            sc = [m, n, k, 1] if ("_vec" in kid or "_rows3" in kid) else [m, n, k]
+            run_named(backend, kid, [a, w, out], sc)
+            got = backend.download(out, np.float32, m * n).reshape(m, n)
+            assert rel_err(got, golden[f"{name}_gemm"]) < 1e-5, kid
+    af = backend.upload(golden["fp8_a"])
+    outf = backend.AllocateBuffer(2 * 16 * 4)
+    run_named(backend, "gemm_fp8", [af, backend.upload(golden["fp8_w"]), backend.upload(golden["fp8_s"]), outf],
+              [2, 16, 200])
+    assert rel_err(backend.download(outf, np.float32, 32).reshape(2, 16), golden["fp8_gemm"]) < 1e-5
+
+
+def test_w4a8_matches_golden(backend, golden):
+    m, n, k = 3, 16, 512
+    a8, as_ = backend.upload(golden["w4a8_a8"]), backend.upload(golden["w4a8_as"])
+    w, wref = backend.upload(golden["mxfp4_w"]), backend.upload(golden["w4a8_wref"])
+    for split in (1, 2, 4):
+        c = backend.AllocateBuffer(split * m * n * 4)
+        run_named(backend, "gemm_mxfp4_wmma", [a8, w, as_, wref, c], [m, n, k, split, 0], grid_y=split)
+        out = backend.AllocateBuffer(m * n * 4)
+        if split > 1:
+            run_named(backend, "gemm_mxfp4_wmma_reduce", [c, out], [m * n, split])
+        else:
+            out = c
+        got = backend.download(out, np.float32, m * n).reshape(m, n)
+        assert rel_err(got, golden["w4a8_gemm"]) < 1e-5, split
+
+
+# ------------------------------------- projections vs oracle, seeded shapes
+
+SHAPES = [
+    # (m, n, k): ragged n (not a multiple of 8), split remainders, m = 1..17
+    (1, 64, 256), (1, 13, 768), (2, 100, 1024), (3, 40, 512), (4, 24, 2048), (5, 9, 256),
+    (7, 33, 1280), (16, 48, 1024), (17, 31, 512),
+]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+@pytest.mark.parametrize("dtype", [Q4K, Q6K, F4E2M1])
+def test_project_batch_matches_oracle(backend, oracle, dtype, m, n, k):
+    """ProjectBatch picks the kernel id exactly as the reference does."""
+    a = synth.activations(m, k, seed=m * 131 + n)
+    if dtype == Q4K:
+        w, ref = synth.q4k_weights(n, k, seed=n), None
+        ref = oracle.gemm_q4k(a, w, m, n, k)
+    elif dtype == Q6K:
+        w = synth.q6k_weights(n, k, seed=n)
+        ref = oracle.gemm_q6k(a, w, m, n, k)
+    else:
+        w = synth.mxfp4_weights(n, k, seed=n)
+        ref = oracle.gemm_mxfp4(a, w, m, n, k)
+    p = Projector(backend)
+    out = backend.AllocateBuffer(m * n * 4)
+    p.ProjectBatch(dtype, backend.upload(a), backend.upload(w), out, m, n, k)
+    got = backend.download(out, np.float32, m * n).reshape(m, n)
+    assert rel_err(got, ref) < TOL, p.last_kernel
+    assert rel_err(got, ref) < 2e-5, p.last_kernel  # fp32 path: only the summation order differs
+
+
+@pytest.mark.parametrize("fmt,dtype", [(0, Q4K), (1, Q6K)])
+@pytest.mark.parametrize("split", [1, 2, 4, 8])
+def test_vec_split_partial_regions(backend, oracle, fmt, dtype, split):
+    """split > 1: chunk y of the k range lands in region y of C, then gemm_vec_reduce."""
+    m, n, k = 2, 19, 2048
+    a = synth.activations(m, k, seed=3)
+    w = synth.q4k_weights(n, k, seed=4) if fmt == 0 else synth.q6k_weights(n, k, seed=4)
+    part_ref = oracle.gemm_vec_split(fmt, a, w, m, n, k, split)
+    part = backend.AllocateBuffer(split * m * n * 4)
+    run_named(backend, f"gemm_{dtype}_vec", [backend.upload(a), backend.upload(w), part], [m, n, k, split],
+              grid_y=split)
+    got = backend.download(part, np.float32, split * m * n).reshape(split, m, n)
+    assert rel_err(got, part_ref) < 2e-5
+    out = backend.AllocateBuffer(m * n * 4)
+    run_named(backend, "gemm_vec_reduce", [part, out], [m * n, split])
+    red = backend.download(out, np.float32, m * n)
+    # the reduce itself is an ordered sum: bit-exact given the partials
+    assert np.array_equal(red, oracle.gemm_vec_reduce(got))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 40, 200), (3, 17, 1024), (16, 64, 4096), (2, 8, 24)])
+def test_fp8_projection_matches_oracle(backend, oracle, m, n, k):
+    a = synth.activations(m, k, seed=5)
+    w, s = synth.fp8_weights(n, k, seed=6)
+    ref = oracle.gemm_fp8(a, w, s, m, n, k)
+    out = backend.AllocateBuffer(m * n * 4)
+    run_named(backend, "gemm_fp8", [backend.upload(a), backend.upload(w), backend.upload(s), out], [m, n, k])
+    assert rel_err(backend.download(out, np.float32, m * n).reshape(m, n), ref) < 2e-5
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_w4a8_qdq_then_projection(backend, oracle, m):
+    """The W4A8 variant of the measurement configs: per-token FP8
+    quantise-dequantise of the activation, then the exact MXFP4 projection
+    (src/models/qwen3_5/project.cpp:269-272)."""
+    n, k = 96, 1024
+    a = synth.activations(m, k, seed=31, bf16=True)
+    w = synth.mxfp4_weights(n, k, seed=32)
+    qdq, _ = oracle.quantize_fp8(a)
+    ref = oracle.gemm_mxfp4(qdq, w, m, n, k)
+    ab = backend.upload(a)
+    scale = backend.AllocateBuffer(m * 4)
+    run_named(backend, "quantize_fp8", [ab, scale], [m, k])
+    out = backend.AllocateBuffer(m * n * 4)
+    Projector(backend).ProjectBatch(F4E2M1, ab, backend.upload(w), out, m, n, k)
+    assert rel_err(backend.download(out, np.float32, m * n).reshape(m, n), ref) < 2e-5
+
+
+def test_w4a8_tensor_contract_vs_oracle(backend, oracle):
+    """quantize_fp8_pack_rows + mxfp4_row_ref + gemm_mxfp4_wmma (+reduce), the
+    launch sequence of ProjectWmma (src/models/qwen3_5/project.cpp:92-231)."""
+    m, n, k = 7, 200, 2048
+    a = synth.activations(m, k, seed=41)
+    w = synth.mxfp4_weights(n, k, seed=42, exp_lo=-14, exp_hi=2)
+    a8_ref, as_ref = oracle.quantize_fp8_pack(a)
+    fold, wref_ref = oracle.fold_mxfp4_to_fp8(w, n, k)
+    ref = oracle.gemm_mxfp4_fp8(a8_ref, as_ref, fold, wref_ref, m, n, k)
+    ab, wb = backend.upload(a), backend.upload(w)
+    a8, as_, wref = backend.AllocateBuffer(m * k), backend.AllocateBuffer(m * 4), backend.AllocateBuffer(n)
+    run_named(backend, "mxfp4_row_ref", [wb, wref], [n, k])
+    run_named(backend, "quantize_fp8_pack_rows", [ab, a8, as_], [m, k])
+    split = 4
+    part = backend.AllocateBuffer(split * m * n * 4)
+    run_named(backend, "gemm_mxfp4_wmma", [a8, wb, as_, wref, part], [m, n, k, split, 0], grid_y=split)
+    part_host = backend.download(part, np.float32, split * m * n).reshape(split, m, n)
+    assert rel_err(part_host, oracle.gemm_mxfp4_wmma(a8_ref, w, as_ref, wref_ref, m, n, k, split)) < 2e-5
+    out = backend.AllocateBuffer(m * n * 4)
+    run_named(backend, "gemm_mxfp4_wmma_reduce", [part, out], [m * n, split])
+    assert rel_err(backend.download(out, np.float32, m * n).reshape(m, n), ref) < 2e-5
+
+
+# ----------------------------------------------------- contract errors
+
+def test_launch_contract_errors(backend):
+    a = backend.AllocateBuffer(256 * 4)
+    w = backend.AllocateBuffer(8 * 144)
+    c = backend.AllocateBuffer(8 * 4)
+    with pytest.raises(StatusError) as e:
+        backend.LoadKernel("attention")
+    assert e.value.code == StatusCode.UnsupportedFeature
+    with pytest.raises(StatusError) as e:
+        backend.LoadKernel("gemm_q4k_vec", b"\x01")
+    assert e.value.code == StatusCode.UnsupportedFeature
+    with pytest.raises(StatusError) as e:
+        backend.AllocateBuffer(0)
+    assert e.value.code == StatusCode.InvalidArgument
+    bad = [
+        ("gemm_q4k_vec", [a, w, c], [1, 8, 256]),          # missing split scalar
+        ("gemm_q4k_vec", [a, w, c], [1, 8, 250, 1]),       # k not a block multiple
+        ("gemm_q4k_vec", [a, w, c], [1, 8, 256, 2]),       # split does not divide k/256
+        ("gemm_q4k_vec", [a, w, c], [1, 16, 256, 1]),      # weight and output buffers too small
+        ("gemm_q4k_vec", [a, w, c], [0, 8, 256, 1]),       # m = 0
+        ("gemm_q4k_rows2", [a, w, c], [1, 8, 256, 1]),     # rows kernel with the wrong m
+        ("gemm_mxfp4", [a, w, c], [1, 8, 250]),            # k not a multiple of 32
+        ("round_bf16", [c], [9]),                          # buffer too small
+        ("add", [a, a], [4]),                              # buffer count
+        ("quantize_fp8_pack", [a, w, c], [1, 6]),          # cols not a multiple of 4
+    ]
+    for name, bufs, scal in bad:
+        with pytest.raises(StatusError) as e:
+            run_named(backend, name, bufs, scal)
+        assert e.value.code == StatusCode.InvalidArgument, name
+    kern = backend.LoadKernel("add")
+    from tessera_b200.backend import KernelLaunch as KL
+    with pytest.raises(StatusError):
+        backend.LaunchKernel(kern, KL(grid_x=0, buffers=[a, a, a], scalars=[4]))
+    # out-of-range host copies are refused before touching the device
+    with pytest.raises(StatusError):
+        backend.CopyH2DAt(c, 16, np.zeros(8, np.float32))
+    backend.Synchronize()
+
+
+def test_copies_round_trip(backend):
+    g = np.random.default_rng(0)
+    big = g.integers(0, 256, size=9 * (4 << 20) + 12345, dtype=np.uint8)  # spans the staging ring twice
+    buf = backend.upload(big)
+    assert np.array_equal(backend.download(buf, np.uint8, big.size), big)
+    dst = backend.AllocateBuffer(big.size)
+    backend.CopyD2D(buf, 100, dst, 7, 5000)
+    assert np.array_equal(backend.download(dst, np.uint8, 5000, offset=7), big[100:5100])
+    total, free = backend.MemoryInfo()
+    assert total > free > 0
+    assert "B200" in backend.DeviceName() or backend.DeviceName()
