@@ -1,0 +1,384 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized projection path on B200.
+
+One step = every quantized projection of one decoded token of the synthetic
+27B-class hybrid model (tessera_b200/workload.py: 497 projections, Q4_K/Q6_K
+mix, about 14.6 GB of weights streamed per token at one GPU), driven through
+the backend interface exactly as the reference's ProjectBatch drives its
+backend.  Attention, the delta-rule scan, norms and sampling are not part of
+the path and are not run.  Under `--gpus N` (torchrun) the projections are
+tensor-parallel: column-parallel ones take n/N rows, row-parallel ones k/N
+columns followed by an all-reduce of the 5120 partial sums.
+
+Prints one JSON line (rank 0).  `--impl reference` times the reference's own
+CPU functions for the same path instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from tessera_b200 import synth, workload  # noqa: E402
+
+METRIC = "decode_projection_tok_s"
+UNIT = "tok/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_q4k_vec launch on the
+# 17408 x 5120 Q4_K weight (profiles/gemv_q4k_staged_17408x5120.md)
+TRAFFIC_Q4K_17408x5120 = 50196736 + 14592
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0}, "fallback"
+
+
+def config_dict(world: int):
+    return {
+        "workload": "27B-class decode step, quantized projections only (configs[3] shapes: hidden 5120, "
+                    "64 layers, FFN 17408, vocab 151936, Q4_K/Q6_K mix), m=1",
+        "projections_per_step": len(workload.decode_projections()),
+        "parameters": workload.total_parameters(),
+        "weight_bytes_per_rank": workload.total_weight_bytes(0, world),
+        "parallelism": f"tp{world}",
+        "cache": "weights streamed per step exceed L2 a hundredfold; no flush needed",
+    }
+
+
+# --------------------------------------------------------------------------
+# clocks
+class ClockSampler:
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": []}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------
+# CPU arms
+def cpu_sample_shapes():
+    """One projection of each distinct (dtype, n, k) with its multiplicity."""
+    shapes = {}
+    for p in workload.decode_projections():
+        shapes.setdefault((p.dtype, p.n, p.k), 0)
+        shapes[(p.dtype, p.n, p.k)] += 1
+    return shapes
+
+
+_CPU_INPUTS = {}
+CPU_SAMPLE_ROWS = 4096
+
+
+def run_cpu_sample(oracle, threads: int, budget_s: float, pool=None):
+    """Times the CPU implementation on up to CPU_SAMPLE_ROWS rows of one
+    projection per distinct shape, repeats the pass until `budget_s` of CPU
+    work is spent, and scales by rows and multiplicity to a whole step.
+    Returns (tok/s, description)."""
+    shapes = cpu_sample_shapes()
+    if not _CPU_INPUTS:
+        for (dtype, n, k) in shapes:
+            rows = min(n, CPU_SAMPLE_ROWS)
+            w = synth.q4k_weights(rows, k, seed=1) if dtype == "q4k" else synth.q6k_weights(rows, k, seed=1)
+            _CPU_INPUTS[(dtype, n, k)] = (rows, w, synth.activations(1, k, seed=2))
+    spent, passes, est = 0.0, 0, []
+    while spent < budget_s or passes == 0:
+        step_s = 0.0
+        for (dtype, n, k), count in shapes.items():
+            rows, w, a = _CPU_INPUTS[(dtype, n, k)]
+            fn = oracle.gemm_q4k if dtype == "q4k" else oracle.gemm_q6k
+            t0 = time.perf_counter()
+            if pool is None:
+                fn(a, w, 1, rows, k, threads=threads)
+            else:
+                rb = (k // 256) * (144 if dtype == "q4k" else 210)
+                chunk = (rows + threads - 1) // threads
+                jobs = [(r0, min(rows, r0 + chunk)) for r0 in range(0, rows, chunk)]
+                list(pool.map(lambda j: fn(a, w[j[0] * rb:j[1] * rb], 1, j[1] - j[0], k), jobs))
+            dt = time.perf_counter() - t0
+            spent += dt
+            step_s += dt * (n / rows) * count
+        est.append(step_s)
+        passes += 1
+    return 1.0 / float(np.median(est)), (
+        f"up to {CPU_SAMPLE_ROWS} rows of one projection of each of the {len(shapes)} distinct shapes, "
+        f"{passes} passes, {spent:.1f} s of CPU work on {threads} threads, scaled by rows and multiplicity to a full step")
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle.oracle import Oracle, reference_available
+    threads = os.cpu_count() or 1
+    if reference_available():
+        oracle, kind = Oracle(reference=True), "reference"
+        pool = ThreadPoolExecutor(threads)
+    else:
+        oracle, kind, pool = Oracle(), "port", None
+    for _ in range(max(args.warmup, 0)):
+        run_cpu_sample(oracle, threads, 1.0, pool)
+    values, sample = [], ""
+    t0 = time.perf_counter()
+    for _ in range(max(args.steps, 1)):
+        v, sample = run_cpu_sample(oracle, threads, min(20.0, max(1.0, 90.0 / max(args.steps, 1))), pool)
+        values.append(v)
+    total = time.perf_counter() - t0
+    value = float(np.mean(values))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / value, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(1),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": total,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------
+# GPU arm
+class CudaArrayView:
+    """Exposes a backend buffer to torch (for the NCCL all-reduce) without a copy."""
+
+    def __init__(self, ptr: int, count: int):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+
+def gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from tessera_b200.backend import CreateBackend
+    from tessera_b200.project import Projector
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    stream = torch.cuda.Stream()
+    backend = CreateBackend(stream=stream.cuda_stream)
+    backend.SetDeviceIndex(local)
+    backend.Init()
+    proj = Projector(backend)
+    launches = [0]
+    raw_launch = backend.LaunchKernel
+
+    def counted(kernel, launch):
+        launches[0] += 1
+        raw_launch(kernel, launch)
+    backend.LaunchKernel = counted
+
+    plan = workload.decode_projections()
+    # ---- weights: one seeded host tensor per distinct local shape, a private
+    # device copy per projection (distinct addresses, so nothing stays in L2)
+    templates = {}
+    weights = []
+    for p in plan:
+        n, k = workload.shard(p, rank, world)
+        key = (p.dtype, n, k)
+        if key not in templates:
+            host = synth.q4k_weights(n, k, seed=3) if p.dtype == "q4k" else synth.q6k_weights(n, k, seed=3)
+            templates[key] = backend.upload(host)
+        buf = backend.AllocateBuffer(templates[key].Size())
+        backend.CopyD2D(templates[key], 0, buf, 0, buf.Size())
+        weights.append((p, n, k, buf))
+    backend.Synchronize()
+    for t in templates.values():
+        t.release()
+    templates.clear()
+
+    # ---- activations (host, pinned by the backend's staging ring) and outputs
+    act_len = {"x": workload.HIDDEN}
+    for p, n, k, _ in weights:
+        act_len[p.act] = max(act_len.get(p.act, 0), k)
+    host_act = {name: synth.activations(1, ln, seed=5, index=i).reshape(-1) for i, (name, ln) in enumerate(act_len.items())}
+    dev_act = {name: backend.upload(h) for name, h in host_act.items()}
+    max_n = max(n for _, n, _, _ in weights)
+    out_buf = backend.AllocateBuffer(max_n * 4)
+    logits_n = weights[-1][1]
+    logits_buf = backend.AllocateBuffer(logits_n * 4)
+    logits_host = np.empty(logits_n, dtype=np.float32)
+    reduce_view = torch.as_tensor(CudaArrayView(out_buf.Handle(), workload.HIDDEN), device=f"cuda:{local}") if world > 1 else None
+
+    def run_step(only=None):
+        for p, n, k, w in weights:
+            if only is not None and p.name not in only:
+                continue
+            dst = logits_buf if p.name == "output" else out_buf
+            proj.ProjectBatch(p.dtype, dev_act[p.act], w, dst, 1, n, k)
+            if world > 1 and p.kind == workload.ROW:
+                dist.all_reduce(reduce_view)
+
+    h2d_bytes = host_act["x"].nbytes
+    d2h_bytes = logits_host.nbytes
+
+    def e2e_step(graph):
+        backend.CopyH2D(dev_act["x"], host_act["x"])
+        graph.replay()
+        backend.CopyD2H(logits_buf, logits_host)
+
+    with torch.cuda.stream(stream):
+        run_step()  # allocates the split-K scratch and warms the kernel cache before capture
+        backend.Synchronize()
+        launches[0] = 0
+        run_step()
+        launches_per_step = launches[0]
+        backend.Synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            run_step()
+        dominant = ("ffn_gate", "ffn_up")
+        launches[0] = 0
+        dom_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(dom_graph, stream=stream):
+            run_step(only=dominant)
+        dom_launches = launches[0]
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        def timed(fn, steps):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            barrier()
+            ms = e0.elapsed_time(e1)
+            if world > 1:
+                t = torch.tensor([ms], device=f"cuda:{local}")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms
+
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        with ClockSampler(local) as clocks:
+            ms_total = timed(graph.replay, args.steps)
+            for _ in range(2):
+                e2e_step(graph)
+            ms_e2e = timed(lambda: e2e_step(graph), args.steps)
+            for _ in range(2):
+                dom_graph.replay()
+            ms_dom = timed(dom_graph.replay, args.steps)
+
+    value = args.steps / (ms_total * 1e-3)
+    e2e_value = args.steps / (ms_e2e * 1e-3)
+    # ---- roofline of the dominant kernel (gemm_q4k_vec on the ffn_gate/ffn_up shape)
+    peaks, peak_kind = measured_peaks()
+    gate = next(x for x in weights if x[0].name == "ffn_gate")
+    n_g, k_g = gate[1], gate[2]
+    alg_bytes = workload.weight_bytes("q4k", n_g, k_g) + k_g * 4 + n_g * 4
+    n_dom_kernels = sum(1 for p, _, _, _ in weights if p.name in dominant)
+    t_launch_s = ms_dom * 1e-3 / (args.steps * n_dom_kernels)
+    achieved = alg_bytes / t_launch_s / 1e9
+    roofline = {
+        "bound": "hbm", "kernel": "gemv_q4k_staged_kernel (gemm_q4k_vec)", "shape": [1, n_g, k_g],
+        "achieved": achieved, "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
+        "frac": achieved / peaks["hbm_gbs"], "us_per_launch": t_launch_s * 1e6,
+        "algorithmic_bytes": alg_bytes,
+        "traffic": TRAFFIC_Q4K_17408x5120 if (n_g, k_g) == (17408, 5120) else None,
+        "launches_timed": args.steps * n_dom_kernels, "kernel_launches_per_replay": dom_launches,
+    }
+    step_bytes = workload.total_weight_bytes(rank, world)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32 accumulate over Q4_K/Q6_K (int8 digits on the staged path)",
+        "data": "synthetic", "config": config_dict(world),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
+        "gpu_launches": launches_per_step * args.steps,
+        "launches_per_step": launches_per_step,
+        "step_hbm_gbs_per_gpu": step_bytes / (ms_total * 1e-3 / args.steps) / 1e9,
+        "roofline": roofline, "clocks": clocks.summary(),
+    }
+    if rank == 0 and world == 1:
+        from oracle.oracle import Oracle
+        threads = os.cpu_count() or 1
+        v, sample = run_cpu_sample(Oracle(), threads, 12.0)
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+    if rank == 0:
+        print(json.dumps(line))
+    backend.Synchronize()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -41,6 +41,7 @@ struct tsr_context {
   bool stage_busy[kStageWindows] = {};
   int stage_next = 0;
   bool peer_enabled[64] = {};
+  unsigned int seen_timeouts = 0;
   std::mutex mutex;
 
   int fail(cudaError_t e, const char* what) {
@@ -301,7 +302,15 @@ int tsr_synchronize(tsr_context* ctx) {
   if (!ctx) return tsr::kInvalidArgument;
   if (int s = ctx->select()) return s;
   const cudaError_t e = cudaStreamSynchronize(ctx->stream);
-  return e == cudaSuccess ? tsr::kOk : ctx->fail(e, "cudaStreamSynchronize");
+  if (e != cudaSuccess) return ctx->fail(e, "cudaStreamSynchronize");
+  // A staged kernel whose bounded wait ran out has left wrong results behind.
+  unsigned int timeouts = 0;
+  if (tsr::staged_wait_timeouts(&timeouts) == tsr::kOk && timeouts != ctx->seen_timeouts) {
+    ctx->seen_timeouts = timeouts;
+    ctx->error = "a staged kernel gave up waiting for a TMA copy";
+    return tsr::kDeviceError;
+  }
+  return tsr::kOk;
 }
 
 }  // extern "C"

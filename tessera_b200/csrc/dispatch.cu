@@ -32,6 +32,8 @@ int tsr_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n
       split == 0 || (k / 256) % split != 0 || split > 65535)
     return kInvalidArgument;
   if (!aligned16(a) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
+  const int rc = staged_gemm_q4k(a, w, c, m, n, k, split, static_cast<cudaStream_t>(stream));
+  if (rc != kUnsupportedFeature) return rc;
   return rows_gemm_q4k(a, w, c, m, n, k, split, static_cast<cudaStream_t>(stream));
 }
 

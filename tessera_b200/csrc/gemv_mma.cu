@@ -1,0 +1,521 @@
+// Staged tensor-pipe GEMV for Q4_K weights (m = 1..8 activation rows).
+//
+// Data path, per CTA (one 64-row tile of W, one split chunk of k):
+//   HBM --TMA 3-D boxes (64 rows x 2 blocks x 144 B, two per stage)--> shared
+//   memory ring --LDS.64 per thread--> packed nibbles --one LOP3 per four
+//   weights--> u8 A fragments --mma.sync m16n8k32 (s32 accumulate)--> registers
+//   --per-sub-block integer scale, per-block fp32 scale--> C.
+//
+// Weights are the A operand (16 weight rows per warp), activations the B
+// operand.  Each fp32 activation row is expanded, once per CTA, into int8
+// "digit" columns a ~= s*(q1 + q2/254 + q3/254^2) (three digits for m <= 2,
+// two above), so the dot products are exact integer arithmetic and the only
+// rounding is the <= 6e-8 (three digits) or <= 1.6e-5 (two digits) relative
+// quantisation of the activation against its row maximum.  One MMA covers
+// exactly one 32-element Q4_K sub-block, whose 6-bit scale multiplies the
+// integer partial sum; the fp16 super-block scale d is applied in fp32 once
+// per block.  The -dmin*mn*sum(a) term of the format
+// (src/core/numerics/quant.cpp:656-675 of the reference: w = d*sc*q - dmin*mn)
+// is two more MMAs per block against per-sub-block activation digit sums.
+//
+// Shared-memory reads are conflict free: the box row pitch (2 * 144 = 288 B)
+// is 32 mod 128, so the sixteen lanes of an LDS.64 phase (four rows x four
+// 8-byte pieces) cover all 32 banks once.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+#include <mutex>
+#include <unordered_map>
+
+#include "codec.cuh"
+#include "launch.h"
+#include "pipeline.cuh"
+
+namespace tsr {
+
+__device__ unsigned int g_wait_timeouts = 0;
+
+namespace {
+
+constexpr int kTileRows = 64;   // rows of W per CTA
+constexpr int kBoxBlocks = 2;   // Q4_K blocks per box row (pitch 288 B)
+constexpr int kBoxesPerStage = 2;
+constexpr int kChunkBlocks = kBoxBlocks * kBoxesPerStage;
+constexpr int kRowPitch = kBoxBlocks * kQ4KBlockBytes;
+constexpr int kBoxBytes = kTileRows * kRowPitch;        // 18432
+constexpr int kStageBytes = kBoxesPerStage * kBoxBytes;  // 36864
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kMaxSmem = 227 * 1024;
+constexpr int kMaxCols = 16;
+
+struct StagedParams {
+  const float* a;
+  float* c;
+  int m, n, k;
+  int per;     // blocks per split chunk
+  int stages;  // ring depth
+  int terms;   // int8 digits per activation row
+  int ncols;   // m * terms
+  int debug;   // experiment switches: 1 skips activation staging, 2 skips the block math
+  unsigned long long region_stride;
+};
+
+__device__ __forceinline__ uint4 lds128(const unsigned char* p) {
+  return *reinterpret_cast<const uint4*>(p);
+}
+__device__ __forceinline__ uint2 lds64(const unsigned char* p) {
+  return *reinterpret_cast<const uint2*>(p);
+}
+
+// D(16x8, s32) = A(16x32, u8, row) * B(32x8, s8, col), zero accumulate input
+__device__ __forceinline__ void mma_u8s8_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// Quantise four activations to int8 digits; digit t of the four values comes
+// back packed in w[t], with the digit sums in sum[t].
+__device__ __forceinline__ void quantise4(float4 x, float inv_s, float s, uint32_t (&w)[3],
+                                          int (&sum)[3]) {
+  const float v[4] = {x.x, x.y, x.z, x.w};
+  w[0] = w[1] = w[2] = 0;
+  sum[0] = sum[1] = sum[2] = 0;
+  const float s2 = s * (1.0f / 254.0f);
+  const float inv2 = inv_s * 254.0f, inv3 = inv2 * 254.0f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float q1 = fminf(fmaxf(rintf(v[e] * inv_s), -127.f), 127.f);
+    float r = fmaf(-q1, s, v[e]);
+    const float q2 = fminf(fmaxf(rintf(r * inv2), -127.f), 127.f);
+    r = fmaf(-q2, s2, r);
+    const float q3 = fminf(fmaxf(rintf(r * inv3), -127.f), 127.f);
+    const int i1 = static_cast<int>(q1), i2 = static_cast<int>(q2), i3 = static_cast<int>(q3);
+    w[0] |= (static_cast<uint32_t>(i1) & 0xFFu) << (8 * e);
+    w[1] |= (static_cast<uint32_t>(i2) & 0xFFu) << (8 * e);
+    w[2] |= (static_cast<uint32_t>(i3) & 0xFFu) << (8 * e);
+    sum[0] += i1;
+    sum[1] += i2;
+    sum[2] += i3;
+  }
+}
+
+// Activation staging.  Layout in shared memory:
+//   act : [block][sub-block 0..7][column][32 bytes]   int8 digits in k order
+//   sums: [block][digit plane 0..1][column][8 bytes]  per-sub-block digit sums
+//         S = D0 + 128*D1 with D0 in [-64,63]
+//   cscale[column] = s_row * 254^-digit
+__device__ __forceinline__ void stage_store(const StagedParams& p, int i, int k, float4 x, float inv_s,
+                                            float s, unsigned char* act, unsigned char* sums,
+                                            int lane) {
+  uint32_t w[3];
+  int sum[3];
+  quantise4(x, inv_s, s, w, sum);
+  const int bl = k >> 8, sb = (k >> 5) & 7;
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {
+    if (t < p.terms) {
+      const int col = i * p.terms + t;
+      *reinterpret_cast<uint32_t*>(act + ((bl * 8 + sb) * p.ncols + col) * 32 + (k & 31)) = w[t];
+      int sacc = sum[t];
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) sacc += __shfl_xor_sync(0xFFFFFFFFu, sacc, o);
+      if ((lane & 7) == 0) {
+        const int d1 = (sacc + 64) >> 7;
+        const int d0 = sacc - 128 * d1;
+        sums[((bl * 2 + 0) * p.ncols + col) * 8 + sb] = static_cast<unsigned char>(d0);
+        sums[((bl * 2 + 1) * p.ncols + col) * 8 + sb] = static_cast<unsigned char>(d1);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float4 load_quad(const StagedParams& p, const float* arow, int k0, int q) {
+  if (k0 + q * 4 < p.k) return __ldg(reinterpret_cast<const float4*>(arow + q * 4));
+  return make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+__device__ __forceinline__ float abs_max4(float m, float4 x) {
+  return fmaxf(m, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
+}
+
+__device__ void stage_activations(const StagedParams& p, int k0, unsigned char* act,
+                                  unsigned char* sums, float* cscale, float* red) {
+  const int quads = p.per * 64;  // float4 groups per row (a multiple of 64)
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int kBatch = 8;
+  constexpr int kWarps = kThreads / 32;
+  const bool small = quads <= kThreads * kBatch;  // the whole row fits in registers
+  for (int i = 0; i < p.m; ++i) {
+    const float* arow = p.a + static_cast<size_t>(i) * p.k + k0;
+    float4 x[kBatch];
+    float amax = 0.0f;
+    if (small) {
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        const int q = threadIdx.x + b * kThreads;
+        x[b] = q < quads ? load_quad(p, arow, k0, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) amax = abs_max4(amax, x[b]);
+    } else {
+      for (int q0 = threadIdx.x; q0 < quads; q0 += kThreads * kBatch) {
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+          const int q = q0 + b * kThreads;
+          x[b] = q < quads ? load_quad(p, arow, k0, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) amax = abs_max4(amax, x[b]);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    if (lane == 0) red[warp] = amax;
+    __syncthreads();
+    float row_max = red[0];
+#pragma unroll
+    for (int wv = 1; wv < kWarps; ++wv) row_max = fmaxf(row_max, red[wv]);
+    __syncthreads();
+    // Finite, non-zero scale; an all-zero row quantises to zeros with s = 1.
+    row_max = fminf(row_max, 3.0e38f);
+    const float s = row_max > 0.0f ? row_max * (1.0f / 127.0f) : 1.0f;
+    const float inv_s = 1.0f / s;
+    if (static_cast<int>(threadIdx.x) < p.terms) {
+      float cs = s;
+      for (int t = 0; t < static_cast<int>(threadIdx.x); ++t) cs *= (1.0f / 254.0f);
+      cscale[i * p.terms + threadIdx.x] = cs;
+    }
+    if (small) {
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        const int q = threadIdx.x + b * kThreads;
+        // q - lane is a multiple of 32 and quads a multiple of 64: warp-uniform branch
+        if (q < quads) stage_store(p, i, q * 4, x[b], inv_s, s, act, sums, lane);
+      }
+    } else {
+      for (int q0 = threadIdx.x; q0 < quads; q0 += kThreads * kBatch) {
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+          const int q = q0 + b * kThreads;
+          x[b] = q < quads ? load_quad(p, arow, k0, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+          const int q = q0 + b * kThreads;
+          if (q < quads) stage_store(p, i, q * 4, x[b], inv_s, s, act, sums, lane);
+        }
+      }
+    }
+  }
+}
+
+template <int NCG>
+__global__ void __launch_bounds__(kThreads)
+gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nchunks = (p.per + kChunkBlocks - 1) / kChunkBlocks;
+  const int nblk_pad = nchunks * kChunkBlocks;
+  unsigned char* act = smem + static_cast<size_t>(p.stages) * kStageBytes;
+  unsigned char* sums = act + static_cast<size_t>(nblk_pad) * p.ncols * 256;
+  float* cscale = reinterpret_cast<float*>(sums + static_cast<size_t>(nblk_pad) * p.ncols * 16);
+  float* red = cscale + kMaxCols;           // 16 floats
+  float* xchg = red + 16;                   // [4 row groups][32 lanes][NCG*4]
+  float* outbuf = xchg + 4 * 32 * NCG * 4;  // [64 rows][NCG*8]
+  uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
+  uint64_t* empty = full + p.stages;
+  const int row0 = blockIdx.x * kTileRows;
+  const int b0 = blockIdx.y * p.per;
+  const bool producer = (tid == kConsumerThreads);
+
+  if (producer) {
+    tma_prefetch_descriptor(&tmap);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kConsumerWarps);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (producer) {
+    const int first = nchunks < p.stages ? nchunks : p.stages;
+    for (int c = 0; c < first; ++c) {
+      unsigned char* dst = smem + static_cast<size_t>(c) * kStageBytes;
+      mbar_expect_tx(&full[c], kStageBytes);
+      tma_load_3d(dst, &tmap, 0, b0 + c * kChunkBlocks, row0, &full[c]);
+      tma_load_3d(dst + kBoxBytes, &tmap, 0, b0 + c * kChunkBlocks + kBoxBlocks, row0, &full[c]);
+    }
+  }
+  if (!(p.debug & 1)) stage_activations(p, b0 * kBlockElems, act, sums, cscale, red);
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      for (int c = p.stages; c < nchunks; ++c) {
+        const int s = c % p.stages, r = c / p.stages;
+        if (!mbar_wait(&empty[s], (r & 1) ^ 1, &g_wait_timeouts)) break;
+        unsigned char* dst = smem + static_cast<size_t>(s) * kStageBytes;
+        mbar_expect_tx(&full[s], kStageBytes);
+        tma_load_3d(dst, &tmap, 0, b0 + c * kChunkBlocks, row0, &full[s]);
+        tma_load_3d(dst + kBoxBytes, &tmap, 0, b0 + c * kChunkBlocks + kBoxBlocks, row0, &full[s]);
+      }
+    }
+    return;
+  }
+
+  const int gid = lane >> 2, tig = lane & 3;
+  const int rg = warp & 3, bx = warp >> 2;  // row group, box of the stage
+  const int rowA = rg * 16 + gid;
+  constexpr uint32_t kNib = 0x0F0F0F0Fu;
+
+  float o[NCG][4];
+#pragma unroll
+  for (int g = 0; g < NCG; ++g)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
+
+  for (int c = 0; c < nchunks; ++c) {
+    const int s = c % p.stages, r = c / p.stages;
+    if (!mbar_wait(&full[s], r & 1, &g_wait_timeouts)) break;
+    const unsigned char* st = smem + static_cast<size_t>(s) * kStageBytes + bx * kBoxBytes;
+#pragma unroll 1
+    for (int bi = 0; bi < kBoxBlocks; ++bi) {
+      const int bl = c * kChunkBlocks + bx * kBoxBlocks + bi;
+      if (bl >= p.per || (p.debug & 2)) break;
+      const unsigned char* pa = st + rowA * kRowPitch + bi * kQ4KBlockBytes;
+      const unsigned char* pb = pa + 8 * kRowPitch;
+      const uint4 ha = lds128(pa), hb = lds128(pb);
+      // 6-bit scales and mins of the 8 sub-blocks as bytes (quant.cpp:58-70)
+      const uint32_t scA[2] = {ha.y & 0x3F3F3F3Fu, (ha.w & kNib) | ((ha.y >> 2) & 0x30303030u)};
+      const uint32_t mnA[2] = {ha.z & 0x3F3F3F3Fu, ((ha.w >> 4) & kNib) | ((ha.z >> 2) & 0x30303030u)};
+      const uint32_t scB[2] = {hb.y & 0x3F3F3F3Fu, (hb.w & kNib) | ((hb.y >> 2) & 0x30303030u)};
+      const uint32_t mnB[2] = {hb.z & 0x3F3F3F3Fu, ((hb.w >> 4) & kNib) | ((hb.z >> 2) & 0x30303030u)};
+
+      int t1[NCG][4];
+#pragma unroll
+      for (int g = 0; g < NCG; ++g)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) t1[g][e] = 0;
+
+      const unsigned char* actb = act + static_cast<size_t>(bl) * 8 * p.ncols * 32 + tig * 8;
+#pragma unroll
+      for (int grp = 0; grp < 4; ++grp) {
+        const uint2 qa = lds64(pa + 16 + 32 * grp + 8 * tig);
+        const uint2 qb = lds64(pb + 16 + 32 * grp + 8 * tig);
+        const int sclA = (scA[grp >> 1] >> (16 * (grp & 1))) & 0xFF;
+        const int schA = (scA[grp >> 1] >> (16 * (grp & 1) + 8)) & 0xFF;
+        const int sclB = (scB[grp >> 1] >> (16 * (grp & 1))) & 0xFF;
+        const int schB = (scB[grp >> 1] >> (16 * (grp & 1) + 8)) & 0xFF;
+#pragma unroll
+        for (int g = 0; g < NCG; ++g) {
+          const int col = g * 8 + gid;
+          uint2 fl = make_uint2(0, 0), fh = make_uint2(0, 0);
+          if (col < p.ncols) {
+            fl = lds64(actb + ((2 * grp) * p.ncols + col) * 32);
+            fh = lds64(actb + ((2 * grp + 1) * p.ncols + col) * 32);
+          }
+          int pl[4], ph[4];
+          mma_u8s8_zero(pl, qa.x & kNib, qb.x & kNib, qa.y & kNib, qb.y & kNib, fl.x, fl.y);
+          mma_u8s8_zero(ph, (qa.x >> 4) & kNib, (qb.x >> 4) & kNib, (qa.y >> 4) & kNib,
+                        (qb.y >> 4) & kNib, fh.x, fh.y);
+          t1[g][0] += sclA * pl[0] + schA * ph[0];
+          t1[g][1] += sclA * pl[1] + schA * ph[1];
+          t1[g][2] += sclB * pl[2] + schB * ph[2];
+          t1[g][3] += sclB * pl[3] + schB * ph[3];
+        }
+      }
+      // min term: k slots 0..7 are the sub-blocks; lanes tig 0/1 hold mins 0..3 / 4..7
+      const uint32_t am = tig == 0 ? mnA[0] : (tig == 1 ? mnA[1] : 0u);
+      const uint32_t bm = tig == 0 ? mnB[0] : (tig == 1 ? mnB[1] : 0u);
+      const float dA = fp16_bits_to_float(ha.x & 0xFFFFu), mA = fp16_bits_to_float(ha.x >> 16);
+      const float dB = fp16_bits_to_float(hb.x & 0xFFFFu), mB = fp16_bits_to_float(hb.x >> 16);
+#pragma unroll
+      for (int g = 0; g < NCG; ++g) {
+        const int col = g * 8 + gid;
+        uint32_t s0 = 0, s1 = 0;
+        if (col < p.ncols && tig < 2) {
+          s0 = *reinterpret_cast<const uint32_t*>(sums + ((bl * 2 + 0) * p.ncols + col) * 8 + tig * 4);
+          s1 = *reinterpret_cast<const uint32_t*>(sums + ((bl * 2 + 1) * p.ncols + col) * 8 + tig * 4);
+        }
+        int r0[4], r1[4];
+        mma_u8s8_zero(r0, am, bm, 0u, 0u, s0, 0u);
+        mma_u8s8_zero(r1, am, bm, 0u, 0u, s1, 0u);
+        o[g][0] += dA * static_cast<float>(t1[g][0]) - mA * static_cast<float>(r0[0] + 128 * r1[0]);
+        o[g][1] += dA * static_cast<float>(t1[g][1]) - mA * static_cast<float>(r0[1] + 128 * r1[1]);
+        o[g][2] += dB * static_cast<float>(t1[g][2]) - mB * static_cast<float>(r0[2] + 128 * r1[2]);
+        o[g][3] += dB * static_cast<float>(t1[g][3]) - mB * static_cast<float>(r0[3] + 128 * r1[3]);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);
+  }
+
+  // The two warps of a row group (one per box) add their partial sums; the
+  // digit columns of each activation row are then combined through shared memory.
+  if (bx == 1) {
+#pragma unroll
+    for (int g = 0; g < NCG; ++g)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) xchg[((rg * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  if (bx == 0) {
+#pragma unroll
+    for (int g = 0; g < NCG; ++g) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = g * 8 + 2 * tig + (e & 1);
+        const int rr = rowA + (e >> 1) * 8;
+        const float v = o[g][e] + xchg[((rg * 32 + lane) * NCG + g) * 4 + e];
+        if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v * cscale[col];
+      }
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  float* cout = p.c + blockIdx.y * p.region_stride;
+  for (int idx = tid; idx < p.m * kTileRows; idx += kConsumerThreads) {
+    const int i = idx / kTileRows, rr = idx - i * kTileRows;
+    if (row0 + rr < p.n) {
+      float v = 0.0f;
+      for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
+      cout[static_cast<size_t>(i) * p.n + row0 + rr] = v;
+    }
+  }
+}
+
+// ---- tensor-map cache: a map depends only on (base, rows, blocks per row)
+struct MapKey {
+  const void* base;
+  uint64_t n, nb;
+  bool operator==(const MapKey& o) const { return base == o.base && n == o.n && nb == o.nb; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.base) ^ (k.n * 0x9E3779B97F4A7C15ull) ^ (k.nb << 40);
+  }
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+int q4k_tensor_map(const void* w, uint64_t n, uint64_t nb, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  const MapKey key{w, n, nb};
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return kOk;
+  }
+  // (18 x u64 = one 144-byte block, blocks of a row, rows)
+  const uint64_t dims[3] = {18, nb, n};
+  const uint64_t strides[2] = {kQ4KBlockBytes, nb * kQ4KBlockBytes};
+  const uint32_t box[3] = {18, kBoxBlocks, kTileRows};
+  CUtensorMap map;
+  const int rc = encode_tensor_map(&map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, w, dims, strides, box);
+  if (rc != kOk) return rc;
+  if (g_maps.size() > 65536) g_maps.clear();
+  g_maps.emplace(key, map);
+  *out = map;
+  return kOk;
+}
+
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  return v ? std::atoi(v) : fallback;
+}
+
+template <int NCG>
+size_t fixed_smem(uint64_t nblk_pad, int ncols) {
+  return nblk_pad * ncols * (256 + 16) + (kMaxCols + 16) * 4 + 4 * 32 * NCG * 4 * 4 +
+         kTileRows * NCG * 8 * 4 + 2 * 8 * 16 + 128;
+}
+
+template <int NCG>
+int launch_staged(const CUtensorMap& map, StagedParams p, uint64_t n, uint64_t split, uint64_t nchunks,
+                  cudaStream_t st) {
+  const size_t fixed = fixed_smem<NCG>(nchunks * kChunkBlocks, p.ncols);
+  if (fixed + 2 * kStageBytes > static_cast<size_t>(kMaxSmem)) return kUnsupportedFeature;
+  // Ring depth: two CTAs per SM when two stages each still fit in half of
+  // shared memory, otherwise one CTA with as many stages as fit.
+  const size_t half = kMaxSmem / 2 - 1024;
+  const int fit_half = fixed < half ? static_cast<int>((half - fixed) / kStageBytes) : 0;
+  const int fit_full = static_cast<int>((kMaxSmem - fixed) / kStageBytes);
+  int want = static_cast<int>(nchunks < 6 ? nchunks : 6);
+  if (want < 2) want = 2;
+  int depth = fit_half >= 2 ? (want < fit_half ? want : fit_half) : (want < fit_full ? want : fit_full);
+  const int forced = env_int("TSR_STAGES", 0);
+  if (forced >= 2 && forced <= fit_full && forced <= 16) depth = forced;
+  p.stages = depth;
+  const size_t smem = static_cast<size_t>(depth) * kStageBytes + fixed;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(gemv_q4k_staged_kernel<NCG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         kMaxSmem);
+    attr = true;
+  }
+  const dim3 grid(static_cast<unsigned>((n + kTileRows - 1) / kTileRows), static_cast<unsigned>(split));
+  gemv_q4k_staged_kernel<NCG><<<grid, kThreads, smem, st>>>(map, p);
+  return check_launch();
+}
+
+}  // namespace
+
+int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType type, uint32_t rank, const void* base,
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
+  using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      encode = reinterpret_cast<EncodeFn>(fn);
+  });
+  if (!encode) return kDeviceError;
+  cuuint64_t d[5], s[5];
+  cuuint32_t b[5], e[5];
+  for (uint32_t i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    e[i] = 1;
+    if (i + 1 < rank) s[i] = strides_bytes[i];
+  }
+  const CUresult r = encode(map, type, rank, const_cast<void*>(base), d, s, b, e,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? kOk : kInvalidArgument;
+}
+
+// Returns kUnsupportedFeature when the shape is outside what the staged
+// kernel covers; the caller then uses the general warp-per-row family.
+int staged_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                    uint64_t split, cudaStream_t st) {
+  if (m > 8 || env_int("TSR_DISABLE_STAGED", 0)) return kUnsupportedFeature;
+  const uint64_t nb = k / kBlockElems, per = nb / split;
+  const uint64_t nchunks = (per + kChunkBlocks - 1) / kChunkBlocks;
+  const int terms = m <= 2 ? 3 : 2;
+  const int ncols = static_cast<int>(m) * terms;
+  CUtensorMap map;
+  if (int rc = q4k_tensor_map(w, n, nb, &map)) return rc;
+  StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
+                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0),
+                 static_cast<unsigned long long>(m * n)};
+  if (ncols <= 8) return launch_staged<1>(map, p, n, split, nchunks, st);
+  return launch_staged<2>(map, p, n, split, nchunks, st);
+}
+
+int staged_wait_timeouts(unsigned int* count) {
+  return cudaMemcpyFromSymbol(count, g_wait_timeouts, sizeof(unsigned int)) == cudaSuccess ? kOk : kDeviceError;
+}
+
+}  // namespace tsr

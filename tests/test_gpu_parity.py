@@ -12,7 +12,12 @@ from conftest import rel_err
 
 pytestmark = pytest.mark.gpu
 
-TOL = 2e-3  # max |y - ref| / max |ref| for fp32-accumulated projection outputs
+TOL = 2e-3  # contract: max |y - ref| / max |ref| for fp32-accumulated projection outputs
+# What the kernels actually deliver.  fp32 paths differ from the oracle only in
+# summation order (~1e-6); the staged Q4_K kernel expands each activation row
+# into int8 digits against its row maximum: three digits (<= 6e-8) for m <= 2,
+# two digits (<= 1.6e-5 per element) for m = 3..8.
+TIGHT = 1e-4
 
 
 def run_named(backend, name, buffers, scalars, grid_y=1):
@@ -131,7 +136,7 @@ def test_projections_match_golden(backend, golden):
             sc = [m, n, k, 1] if ("_vec" in kid or "_rows3" in kid) else [m, n, k]
             run_named(backend, kid, [a, w, out], sc)
             got = backend.download(out, np.float32, m * n).reshape(m, n)
-            assert rel_err(got, golden[f"{name}_gemm"]) < 1e-5, kid
+            assert rel_err(got, golden[f"{name}_gemm"]) < TIGHT, kid
     af = backend.upload(golden["fp8_a"])
     outf = backend.AllocateBuffer(2 * 16 * 4)
     run_named(backend, "gemm_fp8", [af, backend.upload(golden["fp8_w"]), backend.upload(golden["fp8_s"]), outf],
@@ -183,7 +188,7 @@ def test_project_batch_matches_oracle(backend, oracle, dtype, m, n, k):
     p.ProjectBatch(dtype, backend.upload(a), backend.upload(w), out, m, n, k)
     got = backend.download(out, np.float32, m * n).reshape(m, n)
     assert rel_err(got, ref) < TOL, p.last_kernel
-    assert rel_err(got, ref) < 2e-5, p.last_kernel  # fp32 path: only the summation order differs
+    assert rel_err(got, ref) < (2e-5 if m <= 2 or m > 8 else TIGHT), p.last_kernel
 
 
 @pytest.mark.parametrize("fmt,dtype", [(0, Q4K), (1, Q6K)])
@@ -198,7 +203,7 @@ def test_vec_split_partial_regions(backend, oracle, fmt, dtype, split):
     run_named(backend, f"gemm_{dtype}_vec", [backend.upload(a), backend.upload(w), part], [m, n, k, split],
               grid_y=split)
     got = backend.download(part, np.float32, split * m * n).reshape(split, m, n)
-    assert rel_err(got, part_ref) < 2e-5
+    assert rel_err(got, part_ref) < 2e-5  # m = 2: three-digit activations
     out = backend.AllocateBuffer(m * n * 4)
     run_named(backend, "gemm_vec_reduce", [part, out], [m * n, split])
     red = backend.download(out, np.float32, m * n)
