@@ -1,7 +1,7 @@
 // Staged tensor-pipe GEMV for Q4_K weights (m = 1..8 activation rows).
 //
 // Data path, per CTA (one 64-row tile of W, one split chunk of k):
-//   HBM --TMA 3-D boxes (64 rows x 2 blocks x 144 B, two per stage)--> shared
+//   HBM --TMA 3-D box (64 rows x 2 blocks x 144 B per stage)--> shared
 //   memory ring --LDS.64 per thread--> packed nibbles --one LOP3 per four
 //   weights--> u8 A fragments --mma.sync m16n8k32 (s32 accumulate)--> registers
 //   --per-sub-block integer scale, per-block fp32 scale--> C.
@@ -40,11 +40,11 @@ namespace {
 
 constexpr int kTileRows = 64;   // rows of W per CTA
 constexpr int kBoxBlocks = 2;   // Q4_K blocks per box row (pitch 288 B)
-constexpr int kBoxesPerStage = 2;
+constexpr int kBoxesPerStage = 1;  // stages alternate between the two consumer warp sets
 constexpr int kChunkBlocks = kBoxBlocks * kBoxesPerStage;
 constexpr int kRowPitch = kBoxBlocks * kQ4KBlockBytes;
 constexpr int kBoxBytes = kTileRows * kRowPitch;        // 18432
-constexpr int kStageBytes = kBoxesPerStage * kBoxBytes;  // 36864
+constexpr int kStageBytes = kBoxesPerStage * kBoxBytes;  // 18432
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
@@ -61,8 +61,14 @@ struct StagedParams {
   int ncols;   // m * terms
   int debug;   // experiment switches: 1 skips activation staging, 2 skips the block math
   unsigned long long region_stride;
+  unsigned long long* trace;  // optional per-CTA timeline (experiments only)
 };
 
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ uint4 lds128(const unsigned char* p) {
   return *reinterpret_cast<const uint4*>(p);
 }
@@ -81,29 +87,32 @@ __device__ __forceinline__ void mma_u8s8_zero(int (&d)[4], uint32_t a0, uint32_t
 }
 
 // Quantise four activations to int8 digits; digit t of the four values comes
-// back packed in w[t], with the digit sums in sum[t].
-__device__ __forceinline__ void quantise4(float4 x, float inv_s, float s, uint32_t (&w)[3],
-                                          int (&sum)[3]) {
+// back packed in w[t] (two's complement bytes), with the digit sums in sum[t].
+// Rounding uses the 1.5*2^23 magic constant: after t = x*inv + magic the low
+// mantissa byte of t is the two's-complement integer rint(x*inv), which stays
+// within [-127,127] because the scale is the row maximum / 127, so neither a
+// conversion instruction nor a clamp is needed.
+__device__ __forceinline__ void quantise4(float4 x, float inv_s, float s, uint32_t (&w)[3]) {
   const float v[4] = {x.x, x.y, x.z, x.w};
-  w[0] = w[1] = w[2] = 0;
-  sum[0] = sum[1] = sum[2] = 0;
+  constexpr float kMagic = 12582912.0f;
   const float s2 = s * (1.0f / 254.0f);
   const float inv2 = inv_s * 254.0f, inv3 = inv2 * 254.0f;
+  uint32_t t1[4], t2[4], t3[4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
-    const float q1 = fminf(fmaxf(rintf(v[e] * inv_s), -127.f), 127.f);
-    float r = fmaf(-q1, s, v[e]);
-    const float q2 = fminf(fmaxf(rintf(r * inv2), -127.f), 127.f);
-    r = fmaf(-q2, s2, r);
-    const float q3 = fminf(fmaxf(rintf(r * inv3), -127.f), 127.f);
-    const int i1 = static_cast<int>(q1), i2 = static_cast<int>(q2), i3 = static_cast<int>(q3);
-    w[0] |= (static_cast<uint32_t>(i1) & 0xFFu) << (8 * e);
-    w[1] |= (static_cast<uint32_t>(i2) & 0xFFu) << (8 * e);
-    w[2] |= (static_cast<uint32_t>(i3) & 0xFFu) << (8 * e);
-    sum[0] += i1;
-    sum[1] += i2;
-    sum[2] += i3;
+    const float a1 = fmaf(v[e], inv_s, kMagic);
+    float r = fmaf(-(a1 - kMagic), s, v[e]);
+    const float a2 = fmaf(r, inv2, kMagic);
+    r = fmaf(-(a2 - kMagic), s2, r);
+    const float a3 = fmaf(r, inv3, kMagic);
+    t1[e] = __float_as_uint(a1);
+    t2[e] = __float_as_uint(a2);
+    t3[e] = __float_as_uint(a3);
   }
+  // gather the low bytes of four words into one
+  w[0] = __byte_perm(__byte_perm(t1[0], t1[1], 0x0040), __byte_perm(t1[2], t1[3], 0x0040), 0x5410);
+  w[1] = __byte_perm(__byte_perm(t2[0], t2[1], 0x0040), __byte_perm(t2[2], t2[3], 0x0040), 0x5410);
+  w[2] = __byte_perm(__byte_perm(t3[0], t3[1], 0x0040), __byte_perm(t3[2], t3[3], 0x0040), 0x5410);
 }
 
 // Activation staging.  Layout in shared memory:
@@ -112,26 +121,41 @@ __device__ __forceinline__ void quantise4(float4 x, float inv_s, float s, uint32
 //         S = D0 + 128*D1 with D0 in [-64,63]
 //   cscale[column] = s_row * 254^-digit
 __device__ __forceinline__ void stage_store(const StagedParams& p, int i, int k, float4 x, float inv_s,
-                                            float s, unsigned char* act, unsigned char* sums,
-                                            int lane) {
+                                            float s, unsigned char* act) {
   uint32_t w[3];
-  int sum[3];
-  quantise4(x, inv_s, s, w, sum);
-  const int bl = k >> 8, sb = (k >> 5) & 7;
-#pragma unroll
-  for (int t = 0; t < 3; ++t) {
-    if (t < p.terms) {
-      const int col = i * p.terms + t;
-      *reinterpret_cast<uint32_t*>(act + ((bl * 8 + sb) * p.ncols + col) * 32 + (k & 31)) = w[t];
-      int sacc = sum[t];
-#pragma unroll
-      for (int o = 1; o < 8; o <<= 1) sacc += __shfl_xor_sync(0xFFFFFFFFu, sacc, o);
-      if ((lane & 7) == 0) {
-        const int d1 = (sacc + 64) >> 7;
-        const int d0 = sacc - 128 * d1;
-        sums[((bl * 2 + 0) * p.ncols + col) * 8 + sb] = static_cast<unsigned char>(d0);
-        sums[((bl * 2 + 1) * p.ncols + col) * 8 + sb] = static_cast<unsigned char>(d1);
-      }
+  quantise4(x, inv_s, s, w);
+  // (block*8 + sub-block) = k / 32
+  unsigned char* dst = act + ((k >> 5) * p.ncols + i * p.terms) * 32 + (k & 31);
+  *reinterpret_cast<uint32_t*>(dst) = w[0];
+  *reinterpret_cast<uint32_t*>(dst + 32) = w[1];
+  if (p.terms > 2) *reinterpret_cast<uint32_t*>(dst + 64) = w[2];
+}
+
+// Digit sums of every (sub-block, column) from the staged bytes: one thread
+// per sub-block walks its columns.
+__device__ __forceinline__ void stage_sums(const StagedParams& p, const unsigned char* act,
+                                           unsigned char* sums) {
+  const int items = p.per * 8;  // block*8 + sub-block
+  for (int bs = threadIdx.x; bs < items; bs += kThreads) {
+    const int bl = bs >> 3, sb = bs & 7;
+    const unsigned char* src = act + static_cast<size_t>(bs) * p.ncols * 32;
+    unsigned char* d0p = sums + (bl * 2 * p.ncols) * 8 + sb;
+    unsigned char* d1p = d0p + p.ncols * 8;
+    for (int col = 0; col < p.ncols; ++col) {
+      const uint4 u0 = *reinterpret_cast<const uint4*>(src + col * 32);
+      const uint4 u1 = *reinterpret_cast<const uint4*>(src + col * 32 + 16);
+      int s0 = __dp4a(static_cast<int>(u0.x), 0x01010101, 0);
+      int s1 = __dp4a(static_cast<int>(u0.y), 0x01010101, 0);
+      int s2 = __dp4a(static_cast<int>(u0.z), 0x01010101, 0);
+      int s3 = __dp4a(static_cast<int>(u0.w), 0x01010101, 0);
+      s0 = __dp4a(static_cast<int>(u1.x), 0x01010101, s0);
+      s1 = __dp4a(static_cast<int>(u1.y), 0x01010101, s1);
+      s2 = __dp4a(static_cast<int>(u1.z), 0x01010101, s2);
+      s3 = __dp4a(static_cast<int>(u1.w), 0x01010101, s3);
+      const int sacc = (s0 + s1) + (s2 + s3);
+      const int d1 = (sacc + 64) >> 7;
+      d0p[col * 8] = static_cast<unsigned char>(sacc - 128 * d1);
+      d1p[col * 8] = static_cast<unsigned char>(d1);
     }
   }
 }
@@ -145,8 +169,10 @@ __device__ __forceinline__ float abs_max4(float m, float4 x) {
   return fmaxf(m, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
 }
 
-__device__ void stage_activations(const StagedParams& p, int k0, unsigned char* act,
-                                  unsigned char* sums, float* cscale, float* red) {
+template <typename AfterFirstLoads>
+__device__ __forceinline__ void stage_activations(const StagedParams& p, int k0, unsigned char* act,
+                                                  unsigned char* sums, float* cscale, float* red,
+                                                  unsigned long long* tr, AfterFirstLoads after_first_loads) {
   const int quads = p.per * 64;  // float4 groups per row (a multiple of 64)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int kBatch = 8;
@@ -162,9 +188,12 @@ __device__ void stage_activations(const StagedParams& p, int k0, unsigned char* 
         const int q = threadIdx.x + b * kThreads;
         x[b] = q < quads ? load_quad(p, arow, k0, q) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
+      // the activation loads are in flight: now queue the weight prefetch behind them
+      if (i == 0) after_first_loads();
 #pragma unroll
       for (int b = 0; b < kBatch; ++b) amax = abs_max4(amax, x[b]);
     } else {
+      if (i == 0) after_first_loads();
       for (int q0 = threadIdx.x; q0 < quads; q0 += kThreads * kBatch) {
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
@@ -175,6 +204,7 @@ __device__ void stage_activations(const StagedParams& p, int k0, unsigned char* 
         for (int b = 0; b < kBatch; ++b) amax = abs_max4(amax, x[b]);
       }
     }
+    if (tr && threadIdx.x == 0) tr[40] = gtime();
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
     if (lane == 0) red[warp] = amax;
@@ -183,6 +213,7 @@ __device__ void stage_activations(const StagedParams& p, int k0, unsigned char* 
 #pragma unroll
     for (int wv = 1; wv < kWarps; ++wv) row_max = fmaxf(row_max, red[wv]);
     __syncthreads();
+    if (tr && threadIdx.x == 0) tr[41] = gtime();
     // Finite, non-zero scale; an all-zero row quantises to zeros with s = 1.
     row_max = fminf(row_max, 3.0e38f);
     const float s = row_max > 0.0f ? row_max * (1.0f / 127.0f) : 1.0f;
@@ -197,7 +228,7 @@ __device__ void stage_activations(const StagedParams& p, int k0, unsigned char* 
       for (int b = 0; b < kBatch; ++b) {
         const int q = threadIdx.x + b * kThreads;
         // q - lane is a multiple of 32 and quads a multiple of 64: warp-uniform branch
-        if (q < quads) stage_store(p, i, q * 4, x[b], inv_s, s, act, sums, lane);
+        if (q < quads) stage_store(p, i, q * 4, x[b], inv_s, s, act);
       }
     } else {
       for (int q0 = threadIdx.x; q0 < quads; q0 += kThreads * kBatch) {
@@ -209,11 +240,16 @@ __device__ void stage_activations(const StagedParams& p, int k0, unsigned char* 
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
           const int q = q0 + b * kThreads;
-          if (q < quads) stage_store(p, i, q * 4, x[b], inv_s, s, act, sums, lane);
+          if (q < quads) stage_store(p, i, q * 4, x[b], inv_s, s, act);
         }
       }
     }
   }
+  if (tr && threadIdx.x == 0) tr[42] = gtime();
+  __syncthreads();
+  if (tr && threadIdx.x == 0) tr[43] = gtime();
+  stage_sums(p, act, sums);
+  if (tr && threadIdx.x == 0) tr[44] = gtime();
 }
 
 template <int NCG>
@@ -231,30 +267,41 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   float* outbuf = xchg + 4 * 32 * NCG * 4;  // [64 rows][NCG*8]
   uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
   uint64_t* empty = full + p.stages;
+  const unsigned char* zero_page = reinterpret_cast<const unsigned char*>(empty + p.stages);  // 16 zero bytes
   const int row0 = blockIdx.x * kTileRows;
   const int b0 = blockIdx.y * p.per;
   const bool producer = (tid == kConsumerThreads);
+  unsigned long long* tr = p.trace ? p.trace + (blockIdx.y * gridDim.x + blockIdx.x) * 64 : nullptr;
+  if (tr && tid == 0) tr[0] = gtime();
 
+  if (tid < 4) reinterpret_cast<uint32_t*>(empty + p.stages)[tid] = 0u;
   if (producer) {
     tma_prefetch_descriptor(&tmap);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], kConsumerWarps);
+      mbar_init(&empty[s], kConsumerWarps / 2);
     }
     mbar_fence_init();
   }
   __syncthreads();
-  if (producer) {
-    const int first = nchunks < p.stages ? nchunks : p.stages;
-    for (int c = 0; c < first; ++c) {
-      unsigned char* dst = smem + static_cast<size_t>(c) * kStageBytes;
-      mbar_expect_tx(&full[c], kStageBytes);
-      tma_load_3d(dst, &tmap, 0, b0 + c * kChunkBlocks, row0, &full[c]);
-      tma_load_3d(dst + kBoxBytes, &tmap, 0, b0 + c * kChunkBlocks + kBoxBlocks, row0, &full[c]);
+  auto prologue = [&]() {
+    if (producer) {
+      const int first = nchunks < p.stages ? nchunks : p.stages;
+      for (int c = 0; c < first; ++c) {
+        unsigned char* dst = smem + static_cast<size_t>(c) * kStageBytes;
+        mbar_expect_tx(&full[c], kStageBytes);
+        tma_load_3d(dst, &tmap, 0, b0 + c * kChunkBlocks, row0, &full[c]);
+      }
     }
+  };
+  if (tr && tid == 0) tr[1] = gtime();
+  if (!(p.debug & 1)) {
+    stage_activations(p, b0 * kBlockElems, act, sums, cscale, red, tr, prologue);
+  } else {
+    prologue();
   }
-  if (!(p.debug & 1)) stage_activations(p, b0 * kBlockElems, act, sums, cscale, red);
   __syncthreads();
+  if (tr && tid == 0) tr[2] = gtime();
 
   if (warp == kConsumerWarps) {
     if (lane == 0) {
@@ -264,16 +311,35 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
         unsigned char* dst = smem + static_cast<size_t>(s) * kStageBytes;
         mbar_expect_tx(&full[s], kStageBytes);
         tma_load_3d(dst, &tmap, 0, b0 + c * kChunkBlocks, row0, &full[s]);
-        tma_load_3d(dst + kBoxBytes, &tmap, 0, b0 + c * kChunkBlocks + kBoxBlocks, row0, &full[s]);
       }
     }
     return;
   }
 
   const int gid = lane >> 2, tig = lane & 3;
-  const int rg = warp & 3, bx = warp >> 2;  // row group, box of the stage
+  const int rg = warp & 3, bx = warp >> 2;  // row group; warp set bx takes chunks c = bx (mod 2)
   const int rowA = rg * 16 + gid;
   constexpr uint32_t kNib = 0x0F0F0F0Fu;
+
+  // Per-thread fragment addresses.  A lane whose column does not exist reads
+  // the zero page with zero strides, so the loop needs no predicates.
+  const unsigned char* act_t[NCG];
+  const unsigned char* sum_t[NCG];
+  uint32_t act_sb[NCG], act_blk[NCG], sum_plane[NCG], sum_blk[NCG];
+#pragma unroll
+  for (int g = 0; g < NCG; ++g) {
+    const int col = g * 8 + gid;
+    const bool valid = col < p.ncols;
+    act_t[g] = valid ? act + col * 32 + tig * 8 : zero_page;
+    act_sb[g] = valid ? p.ncols * 32 : 0;
+    act_blk[g] = act_sb[g] * 8;
+    const bool sv = valid && tig < 2;
+    sum_t[g] = sv ? sums + col * 8 + tig * 4 : zero_page;
+    sum_plane[g] = sv ? p.ncols * 8 : 0;
+    sum_blk[g] = sum_plane[g] * 2;
+  }
+  const uint32_t mask0 = tig == 0 ? 0xFFFFFFFFu : 0u, mask1 = tig == 1 ? 0xFFFFFFFFu : 0u;
+  const uint32_t row_off = rowA * kRowPitch;
 
   float o[NCG][4];
 #pragma unroll
@@ -281,83 +347,86 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
 
-  for (int c = 0; c < nchunks; ++c) {
-    const int s = c % p.stages, r = c / p.stages;
-    if (!mbar_wait(&full[s], r & 1, &g_wait_timeouts)) break;
-    const unsigned char* st = smem + static_cast<size_t>(s) * kStageBytes + bx * kBoxBytes;
-#pragma unroll 1
+  int slot = bx % p.stages, round = bx / p.stages;
+  for (int c = bx; c < nchunks; c += 2) {
+    if (tr && tid == 0 && c < 24) tr[8 + 2 * c] = gtime();
+    if (!mbar_wait(&full[slot], round & 1, &g_wait_timeouts)) break;
+    if (tr && tid == 0 && c < 24) tr[9 + 2 * c] = gtime();
+    const unsigned char* st = smem + static_cast<size_t>(slot) * kStageBytes + row_off;
+    const int blocks_here = (p.debug & 2) ? 0 : min(kBoxBlocks, p.per - c * kChunkBlocks);
+#pragma unroll
     for (int bi = 0; bi < kBoxBlocks; ++bi) {
-      const int bl = c * kChunkBlocks + bx * kBoxBlocks + bi;
-      if (bl >= p.per || (p.debug & 2)) break;
-      const unsigned char* pa = st + rowA * kRowPitch + bi * kQ4KBlockBytes;
-      const unsigned char* pb = pa + 8 * kRowPitch;
-      const uint4 ha = lds128(pa), hb = lds128(pb);
-      // 6-bit scales and mins of the 8 sub-blocks as bytes (quant.cpp:58-70)
-      const uint32_t scA[2] = {ha.y & 0x3F3F3F3Fu, (ha.w & kNib) | ((ha.y >> 2) & 0x30303030u)};
-      const uint32_t mnA[2] = {ha.z & 0x3F3F3F3Fu, ((ha.w >> 4) & kNib) | ((ha.z >> 2) & 0x30303030u)};
-      const uint32_t scB[2] = {hb.y & 0x3F3F3F3Fu, (hb.w & kNib) | ((hb.y >> 2) & 0x30303030u)};
-      const uint32_t mnB[2] = {hb.z & 0x3F3F3F3Fu, ((hb.w >> 4) & kNib) | ((hb.z >> 2) & 0x30303030u)};
+      if (bi < blocks_here) {
+        const int bl = c * kChunkBlocks + bi;
+        const unsigned char* pa = st + bi * kQ4KBlockBytes;
+        const unsigned char* pb = pa + 8 * kRowPitch;
+        const uint4 ha = lds128(pa), hb = lds128(pb);
+        // 6-bit scales and mins of the 8 sub-blocks as bytes (quant.cpp:58-70)
+        const uint32_t scA[2] = {ha.y & 0x3F3F3F3Fu, (ha.w & kNib) | ((ha.y >> 2) & 0x30303030u)};
+        const uint32_t mnA[2] = {ha.z & 0x3F3F3F3Fu, ((ha.w >> 4) & kNib) | ((ha.z >> 2) & 0x30303030u)};
+        const uint32_t scB[2] = {hb.y & 0x3F3F3F3Fu, (hb.w & kNib) | ((hb.y >> 2) & 0x30303030u)};
+        const uint32_t mnB[2] = {hb.z & 0x3F3F3F3Fu, ((hb.w >> 4) & kNib) | ((hb.z >> 2) & 0x30303030u)};
 
-      int t1[NCG][4];
+        int t1[NCG][4];
 #pragma unroll
-      for (int g = 0; g < NCG; ++g)
+        for (int g = 0; g < NCG; ++g)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) t1[g][e] = 0;
+          for (int e = 0; e < 4; ++e) t1[g][e] = 0;
 
-      const unsigned char* actb = act + static_cast<size_t>(bl) * 8 * p.ncols * 32 + tig * 8;
 #pragma unroll
-      for (int grp = 0; grp < 4; ++grp) {
-        const uint2 qa = lds64(pa + 16 + 32 * grp + 8 * tig);
-        const uint2 qb = lds64(pb + 16 + 32 * grp + 8 * tig);
-        const int sclA = (scA[grp >> 1] >> (16 * (grp & 1))) & 0xFF;
-        const int schA = (scA[grp >> 1] >> (16 * (grp & 1) + 8)) & 0xFF;
-        const int sclB = (scB[grp >> 1] >> (16 * (grp & 1))) & 0xFF;
-        const int schB = (scB[grp >> 1] >> (16 * (grp & 1) + 8)) & 0xFF;
+        for (int grp = 0; grp < 4; ++grp) {
+          const uint2 qa = lds64(pa + 16 + 32 * grp + 8 * tig);
+          const uint2 qb = lds64(pb + 16 + 32 * grp + 8 * tig);
+          const int sclA = __byte_perm(scA[grp >> 1], 0, 0x4440 + 2 * (grp & 1));
+          const int schA = __byte_perm(scA[grp >> 1], 0, 0x4441 + 2 * (grp & 1));
+          const int sclB = __byte_perm(scB[grp >> 1], 0, 0x4440 + 2 * (grp & 1));
+          const int schB = __byte_perm(scB[grp >> 1], 0, 0x4441 + 2 * (grp & 1));
+#pragma unroll
+          for (int g = 0; g < NCG; ++g) {
+            const unsigned char* ab = act_t[g] + bl * act_blk[g];
+            const uint2 fl = lds64(ab + (2 * grp) * act_sb[g]);
+            const uint2 fh = lds64(ab + (2 * grp + 1) * act_sb[g]);
+            int pl[4], ph[4];
+            mma_u8s8_zero(pl, qa.x & kNib, qb.x & kNib, qa.y & kNib, qb.y & kNib, fl.x, fl.y);
+            mma_u8s8_zero(ph, (qa.x >> 4) & kNib, (qb.x >> 4) & kNib, (qa.y >> 4) & kNib,
+                          (qb.y >> 4) & kNib, fh.x, fh.y);
+            t1[g][0] += sclA * pl[0] + schA * ph[0];
+            t1[g][1] += sclA * pl[1] + schA * ph[1];
+            t1[g][2] += sclB * pl[2] + schB * ph[2];
+            t1[g][3] += sclB * pl[3] + schB * ph[3];
+          }
+        }
+        // min term: k slots 0..7 are the sub-blocks; lanes tig 0/1 hold mins 0..3 / 4..7
+        const uint32_t am = (mnA[0] & mask0) | (mnA[1] & mask1);
+        const uint32_t bm = (mnB[0] & mask0) | (mnB[1] & mask1);
+        const float dA = fp16_bits_to_float(ha.x & 0xFFFFu), mA = fp16_bits_to_float(ha.x >> 16);
+        const float dB = fp16_bits_to_float(hb.x & 0xFFFFu), mB = fp16_bits_to_float(hb.x >> 16);
 #pragma unroll
         for (int g = 0; g < NCG; ++g) {
-          const int col = g * 8 + gid;
-          uint2 fl = make_uint2(0, 0), fh = make_uint2(0, 0);
-          if (col < p.ncols) {
-            fl = lds64(actb + ((2 * grp) * p.ncols + col) * 32);
-            fh = lds64(actb + ((2 * grp + 1) * p.ncols + col) * 32);
-          }
-          int pl[4], ph[4];
-          mma_u8s8_zero(pl, qa.x & kNib, qb.x & kNib, qa.y & kNib, qb.y & kNib, fl.x, fl.y);
-          mma_u8s8_zero(ph, (qa.x >> 4) & kNib, (qb.x >> 4) & kNib, (qa.y >> 4) & kNib,
-                        (qb.y >> 4) & kNib, fh.x, fh.y);
-          t1[g][0] += sclA * pl[0] + schA * ph[0];
-          t1[g][1] += sclA * pl[1] + schA * ph[1];
-          t1[g][2] += sclB * pl[2] + schB * ph[2];
-          t1[g][3] += sclB * pl[3] + schB * ph[3];
+          const unsigned char* sp = sum_t[g] + bl * sum_blk[g];
+          const uint32_t s0 = *reinterpret_cast<const uint32_t*>(sp);
+          const uint32_t s1 = *reinterpret_cast<const uint32_t*>(sp + sum_plane[g]);
+          int r0[4], r1[4];
+          mma_u8s8_zero(r0, am, bm, 0u, 0u, s0, 0u);
+          mma_u8s8_zero(r1, am, bm, 0u, 0u, s1, 0u);
+          o[g][0] = fmaf(dA, static_cast<float>(t1[g][0]), fmaf(-mA, static_cast<float>(r0[0] + 128 * r1[0]), o[g][0]));
+          o[g][1] = fmaf(dA, static_cast<float>(t1[g][1]), fmaf(-mA, static_cast<float>(r0[1] + 128 * r1[1]), o[g][1]));
+          o[g][2] = fmaf(dB, static_cast<float>(t1[g][2]), fmaf(-mB, static_cast<float>(r0[2] + 128 * r1[2]), o[g][2]));
+          o[g][3] = fmaf(dB, static_cast<float>(t1[g][3]), fmaf(-mB, static_cast<float>(r0[3] + 128 * r1[3]), o[g][3]));
         }
-      }
-      // min term: k slots 0..7 are the sub-blocks; lanes tig 0/1 hold mins 0..3 / 4..7
-      const uint32_t am = tig == 0 ? mnA[0] : (tig == 1 ? mnA[1] : 0u);
-      const uint32_t bm = tig == 0 ? mnB[0] : (tig == 1 ? mnB[1] : 0u);
-      const float dA = fp16_bits_to_float(ha.x & 0xFFFFu), mA = fp16_bits_to_float(ha.x >> 16);
-      const float dB = fp16_bits_to_float(hb.x & 0xFFFFu), mB = fp16_bits_to_float(hb.x >> 16);
-#pragma unroll
-      for (int g = 0; g < NCG; ++g) {
-        const int col = g * 8 + gid;
-        uint32_t s0 = 0, s1 = 0;
-        if (col < p.ncols && tig < 2) {
-          s0 = *reinterpret_cast<const uint32_t*>(sums + ((bl * 2 + 0) * p.ncols + col) * 8 + tig * 4);
-          s1 = *reinterpret_cast<const uint32_t*>(sums + ((bl * 2 + 1) * p.ncols + col) * 8 + tig * 4);
-        }
-        int r0[4], r1[4];
-        mma_u8s8_zero(r0, am, bm, 0u, 0u, s0, 0u);
-        mma_u8s8_zero(r1, am, bm, 0u, 0u, s1, 0u);
-        o[g][0] += dA * static_cast<float>(t1[g][0]) - mA * static_cast<float>(r0[0] + 128 * r1[0]);
-        o[g][1] += dA * static_cast<float>(t1[g][1]) - mA * static_cast<float>(r0[1] + 128 * r1[1]);
-        o[g][2] += dB * static_cast<float>(t1[g][2]) - mB * static_cast<float>(r0[2] + 128 * r1[2]);
-        o[g][3] += dB * static_cast<float>(t1[g][3]) - mB * static_cast<float>(r0[3] + 128 * r1[3]);
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[s]);
+    if (lane == 0) mbar_arrive(&empty[slot]);
+    slot += 2;
+    if (slot >= p.stages) {
+      slot -= p.stages;
+      ++round;
+    }
   }
 
-  // The two warps of a row group (one per box) add their partial sums; the
+  if (tr && tid == 0) tr[3] = gtime();
+  // The two warps of a row group (even and odd chunks) add their partial sums; the
   // digit columns of each activation row are then combined through shared memory.
   if (bx == 1) {
 #pragma unroll
@@ -388,6 +457,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
       cout[static_cast<size_t>(i) * p.n + row0 + rr] = v;
     }
   }
+  if (tr && tid == 0) tr[4] = gtime();
 }
 
 // ---- tensor-map cache: a map depends only on (base, rows, blocks per row)
@@ -446,7 +516,7 @@ int launch_staged(const CUtensorMap& map, StagedParams p, uint64_t n, uint64_t s
   const size_t half = kMaxSmem / 2 - 1024;
   const int fit_half = fixed < half ? static_cast<int>((half - fixed) / kStageBytes) : 0;
   const int fit_full = static_cast<int>((kMaxSmem - fixed) / kStageBytes);
-  int want = static_cast<int>(nchunks < 6 ? nchunks : 6);
+  int want = static_cast<int>(nchunks < 12 ? nchunks : 12);
   if (want < 2) want = 2;
   int depth = fit_half >= 2 ? (want < fit_half ? want : fit_half) : (want < fit_full ? want : fit_full);
   const int forced = env_int("TSR_STAGES", 0);
@@ -509,7 +579,8 @@ int staged_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_
   if (int rc = q4k_tensor_map(w, n, nb, &map)) return rc;
   StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
                  static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0),
-                 static_cast<unsigned long long>(m * n)};
+                 static_cast<unsigned long long>(m * n),
+                 reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(std::strtoull(std::getenv("TSR_TRACE_PTR") ? std::getenv("TSR_TRACE_PTR") : "0", nullptr, 10)))};
   if (ncols <= 8) return launch_staged<1>(map, p, n, split, nchunks, st);
   return launch_staged<2>(map, p, n, split, nchunks, st);
 }
