@@ -257,7 +257,13 @@ def gpu_arm(args):
     logits_n = weights[-1][1]
     logits_buf = backend.AllocateBuffer(logits_n * 4)
     logits_host = np.empty(logits_n, dtype=np.float32)
-    reduce_view = torch.as_tensor(CudaArrayView(out_buf.Handle(), workload.HIDDEN), device=f"cuda:{local}") if world > 1 else None
+    reduce_view, comm = None, None
+    if world > 1 and args.allreduce == "nccl":
+        reduce_view = torch.as_tensor(CudaArrayView(out_buf.Handle(), workload.HIDDEN), device=f"cuda:{local}")
+    elif world > 1:
+        from tessera_b200.tp import TpComm
+        comm = TpComm(local, rank, world, workload.HIDDEN)
+        comm.connect(dist)
 
     def run_step(only=None):
         for p, n, k, w in weights:
@@ -266,7 +272,10 @@ def gpu_arm(args):
             dst = logits_buf if p.name == "output" else out_buf
             proj.ProjectBatch(p.dtype, dev_act[p.act], w, dst, 1, n, k)
             if world > 1 and p.kind == workload.ROW:
-                dist.all_reduce(reduce_view)
+                if comm is not None:
+                    comm.allreduce(out_buf.Handle(), workload.HIDDEN, backend.stream())
+                else:
+                    dist.all_reduce(reduce_view)
 
     h2d_bytes = host_act["x"].nbytes
     d2h_bytes = logits_host.nbytes
@@ -347,7 +356,7 @@ def gpu_arm(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 accumulate over Q4_K/Q6_K (int8 digits on the staged path)",
-        "data": "synthetic", "config": config_dict(world),
+        "data": "synthetic", "config": dict(config_dict(world), allreduce=(args.allreduce if world > 1 else "none")),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
         "gpu_launches": launches_per_step * args.steps,
         "launches_per_step": launches_per_step,
@@ -362,6 +371,8 @@ def gpu_arm(args):
     if rank == 0:
         print(json.dumps(line))
     backend.Synchronize()
+    if comm is not None and comm.error_count() != 0:
+        raise RuntimeError("a tensor-parallel wait on a peer gave up; the results are not valid")
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -373,6 +384,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
+                    help="row-parallel reduce: peer-memory push all-reduce (default) or NCCL (comparison)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)

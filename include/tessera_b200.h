@@ -148,6 +148,33 @@ int tsr_fill(int32_t* data, int32_t value, uint64_t n, void* stream);
 int tsr_dequantize(int fmt, const void* w, const float* row_scale, float* out, uint64_t n,
                    uint64_t k, void* stream);
 
+/* ---- tensor-parallel sum all-reduce over NVLink peer memory ---------------
+ * Replaces the rank-0 gather/add/broadcast of TpReduce
+ * (src/models/qwen3_5/trunk.cpp:226-266) and the host-staged AllReduceSum
+ * (include/tessera/backend.hpp:1048-1058, src/core/buffer.cpp:216-251): every
+ * rank pushes its fp32 partial into a slot on every peer, and each rank adds
+ * the slots in rank order, so all ranks hold bit-identical sums.
+ *
+ * One communicator per rank.  tsr_tp_create allocates the rank's exchange
+ * memory (cudaMalloc) sized for vectors of up to max_floats.  Ranks living in
+ * one process attach each other's block directly (tsr_tp_local_block +
+ * tsr_tp_attach_local, peer access is enabled on the way); ranks in separate
+ * processes exchange the 64-byte handle of tsr_tp_ipc_handle out of band and
+ * call tsr_tp_attach_ipc.  tsr_tp_allreduce sums `count` floats in place
+ * (count a multiple of 4, data 16-byte aligned); every rank must issue the
+ * same sequence of calls.  It may be captured in a CUDA graph.  Waits on
+ * peers are bounded: when one gives up the call still returns and
+ * tsr_tp_error_count becomes non-zero. */
+typedef struct tsr_tp_comm tsr_tp_comm;
+int tsr_tp_create(int device, int rank, int world, uint64_t max_floats, tsr_tp_comm** out);
+void tsr_tp_destroy(tsr_tp_comm* comm);
+int tsr_tp_local_block(tsr_tp_comm* comm, void** block, uint64_t* bytes);
+int tsr_tp_ipc_handle(tsr_tp_comm* comm, void* handle64);
+int tsr_tp_attach_ipc(tsr_tp_comm* comm, int peer_rank, const void* handle64);
+int tsr_tp_attach_local(tsr_tp_comm* comm, int peer_rank, int peer_device, void* peer_block);
+int tsr_tp_allreduce(tsr_tp_comm* comm, float* data, uint64_t count, void* stream);
+int tsr_tp_error_count(tsr_tp_comm* comm, uint32_t* count);
+
 #ifdef __cplusplus
 }
 #endif

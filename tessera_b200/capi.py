@@ -81,6 +81,14 @@ SIGNATURES = {
     "tsr_add": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
     "tsr_fill": (C.c_int, [_vp, C.c_int32, _u64, _vp]),
     "tsr_dequantize": (C.c_int, [C.c_int, _vp, _vp, _vp, _u64, _u64, _vp]),
+    "tsr_tp_create": (C.c_int, [C.c_int, C.c_int, C.c_int, _u64, C.POINTER(_vp)]),
+    "tsr_tp_destroy": (None, [_vp]),
+    "tsr_tp_local_block": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_u64)]),
+    "tsr_tp_ipc_handle": (C.c_int, [_vp, _vp]),
+    "tsr_tp_attach_ipc": (C.c_int, [_vp, C.c_int, _vp]),
+    "tsr_tp_attach_local": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
+    "tsr_tp_allreduce": (C.c_int, [_vp, _vp, _u64, _vp]),
+    "tsr_tp_error_count": (C.c_int, [_vp, C.POINTER(C.c_uint32)]),
 }
 
 

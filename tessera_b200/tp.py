@@ -1,0 +1,73 @@
+"""Tensor-parallel helpers: the peer-memory sum all-reduce and the shard maps.
+
+The reference runs one thread per rank inside one process and reduces the
+row-parallel partials through rank 0 (src/core/tensor_parallel.cpp,
+src/models/qwen3_5/trunk.cpp:226-266 of the reference).  This module drives
+the C ABI's `tsr_tp_*` calls, for ranks inside one process (`attach_local`)
+or one process per GPU (`connect`, which swaps the IPC handles through
+torch.distributed).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+
+
+class TpComm:
+    def __init__(self, device: int, rank: int, world: int, max_floats: int):
+        self.lib = capi.load_library()
+        self.rank, self.world, self.device = rank, world, device
+        comm = C.c_void_p()
+        capi.check(self.lib.tsr_tp_create(device, rank, world, max_floats, C.byref(comm)), "tsr_tp_create")
+        self.comm = comm
+
+    def local_block(self) -> int:
+        ptr, size = C.c_void_p(), C.c_uint64()
+        capi.check(self.lib.tsr_tp_local_block(self.comm, C.byref(ptr), C.byref(size)))
+        return ptr.value
+
+    def ipc_handle(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        capi.check(self.lib.tsr_tp_ipc_handle(self.comm, buf), "tsr_tp_ipc_handle")
+        return buf.raw
+
+    def attach_ipc(self, peer_rank: int, handle: bytes) -> None:
+        capi.check(self.lib.tsr_tp_attach_ipc(self.comm, peer_rank, C.c_char_p(handle)), "tsr_tp_attach_ipc")
+
+    def attach_local(self, peer: "TpComm") -> None:
+        capi.check(self.lib.tsr_tp_attach_local(self.comm, peer.rank, peer.device, peer.local_block()),
+                   "tsr_tp_attach_local")
+
+    def connect(self, dist) -> None:
+        """One process per GPU: exchange the IPC handles through `dist`
+        (an initialised torch.distributed module) and map every peer."""
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.ipc_handle())
+        for r, h in enumerate(handles):
+            if r != self.rank:
+                self.attach_ipc(r, h)
+        dist.barrier()
+
+    def allreduce(self, data_ptr: int, count: int, stream: int) -> None:
+        capi.check(self.lib.tsr_tp_allreduce(self.comm, data_ptr, count, stream), "tsr_tp_allreduce")
+
+    def error_count(self) -> int:
+        n = C.c_uint32()
+        capi.check(self.lib.tsr_tp_error_count(self.comm, C.byref(n)))
+        return n.value
+
+    def close(self) -> None:
+        if self.comm:
+            self.lib.tsr_tp_destroy(self.comm)
+            self.comm = None
+
+
+def rank_order_sum(partials):
+    """What every rank must end with: ((p0 + p1) + p2) + ... in fp32."""
+    acc = np.array(partials[0], dtype=np.float32, copy=True)
+    for p in partials[1:]:
+        acc = acc + np.asarray(p, dtype=np.float32)
+    return acc

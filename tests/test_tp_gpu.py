@@ -1,0 +1,89 @@
+"""The peer-memory all-reduce on GPUs: one rank, two ranks in one process
+(the reference's thread-per-rank layout), graph replay, and the bounded wait."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from tessera_b200 import capi
+from tessera_b200.backend import CreateBackend
+from tessera_b200.tp import TpComm, rank_order_sum
+
+pytestmark = pytest.mark.gpu
+
+
+def device_count():
+    n = C.c_int()
+    capi.load_library().tsr_device_count(C.byref(n))
+    return n.value
+
+
+def make_backend(index):
+    b = CreateBackend()
+    b.SetDeviceIndex(index)
+    b.Init()
+    return b
+
+
+def test_single_rank_is_the_identity(backend):
+    comm = TpComm(0, 0, 1, 5120)
+    x = np.random.default_rng(0).standard_normal(5120).astype(np.float32)
+    buf = backend.upload(x)
+    for _ in range(3):
+        comm.allreduce(buf.Handle(), 5120, backend.stream())
+    assert np.array_equal(backend.download(buf, np.float32, 5120), x)
+    assert comm.error_count() == 0
+    with pytest.raises(capi.StatusError):
+        comm.allreduce(buf.Handle(), 5122, backend.stream())   # not a multiple of 4
+    with pytest.raises(capi.StatusError):
+        comm.allreduce(buf.Handle(), 1 << 20, backend.stream())  # beyond the capacity
+    backend.Synchronize()
+    comm.close()
+
+
+def test_wait_for_a_silent_peer_gives_up_with_a_status(backend):
+    """Rank 1 never launches: rank 0's wait runs out, the kernel returns and
+    the communicator reports it; the context stays usable."""
+    c0 = TpComm(0, 0, 2, 1024)
+    c1 = TpComm(0, 1, 2, 1024)
+    c0.attach_local(c1)
+    x = np.ones(1024, dtype=np.float32)
+    buf = backend.upload(x)
+    c0.allreduce(buf.Handle(), 1024, backend.stream())
+    backend.Synchronize()
+    assert c0.error_count() >= 1
+    buf2 = backend.upload(x)
+    assert np.array_equal(backend.download(buf2, np.float32, 1024), x)
+    c0.close()
+    c1.close()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ranks_in_one_process(world):
+    if device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    backends = [make_backend(i) for i in range(world)]
+    count = 16 * 5120
+    comms = [TpComm(i, i, world, count) for i in range(world)]
+    for a in comms:
+        for b in comms:
+            if a is not b:
+                a.attach_local(b)
+    g = np.random.default_rng(3)
+    for it in range(4):
+        n = 5120 if it % 2 == 0 else count
+        parts = [(g.standard_normal(n) * 10.0 ** r).astype(np.float32) for r in range(world)]
+        bufs = [backends[r].upload(parts[r]) for r in range(world)]
+        for r in range(world):
+            comms[r].allreduce(bufs[r].Handle(), n, backends[r].stream())
+        want = rank_order_sum(parts)
+        for r in range(world):
+            got = backends[r].download(bufs[r], np.float32, n)
+            assert np.array_equal(got, want), (it, r)
+    assert all(c.error_count() == 0 for c in comms)
+    for b in backends:
+        b.Synchronize()
+    for c in comms:
+        c.close()
+    for b in backends:
+        b.close()
