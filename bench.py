@@ -293,12 +293,12 @@ def gpu_arm(args):
         launches_per_step = launches[0]
         backend.Synchronize()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
             run_step()
         dominant = ("ffn_gate", "ffn_up")
         launches[0] = 0
         dom_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(dom_graph, stream=stream):
+        with torch.cuda.graph(dom_graph, stream=stream, capture_error_mode="thread_local"):
             run_step(only=dominant)
         dom_launches = launches[0]
 

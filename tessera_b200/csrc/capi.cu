@@ -54,11 +54,10 @@ struct tsr_context {
     // The current device is per host thread and the reference drives one
     // backend from different threads over time (a fresh thread per
     // tensor-parallel step): re-select on every entry.
-    static thread_local int selected = -1;
-    if (selected == device) return tsr::kOk;
+    // cudaSetDevice on the already-current device is a cheap no-op; no cache
+    // is kept because other entry points of the library also switch devices.
     const cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) return fail(e, "cudaSetDevice");
-    selected = device;
     return tsr::kOk;
   }
   unsigned char* window(int* index) {

@@ -213,6 +213,8 @@ int tsr_tp_allreduce(tsr_tp_comm* c, float* data, uint64_t count, void* stream) 
   if (!c || !data || count == 0 || count > c->capacity || count % 4 != 0 ||
       (reinterpret_cast<uintptr_t>(data) & 15u))
     return tsr::kInvalidArgument;
+  // The current device is per host thread; one thread may drive several ranks.
+  if (cudaSetDevice(c->device) != cudaSuccess) return tsr::kDeviceError;
   Peers peers{};
   for (int p = 0; p < c->world; ++p) {
     if (!c->attached[p]) return tsr::kInvalidArgument;
