@@ -148,6 +148,29 @@ int tsr_fill(int32_t* data, int32_t value, uint64_t n, void* stream);
 int tsr_dequantize(int fmt, const void* w, const float* row_scale, float* out, uint64_t n,
                    uint64_t k, void* stream);
 
+/* ---- split-K Q4_K projection without any device allocation ----------------
+ * No counterpart in the reference: there the caller allocates the split-K
+ * partial buffer through Backend::AllocateBuffer.
+ *
+ * For hosts that must not allocate while they run: an engine that has handed
+ * out all device memory at load time, or a decode loop that cannot afford
+ * the device-wide synchronisation of cudaMalloc.  C[m,n] = A . dq(W)^T is
+ * computed as up to eight k chunks whose partial sums live in a fixed 4 MiB
+ * array inside the library (every GPU that loads the library holds it until
+ * the process exits), followed by the ordered sum of the chunks.  The call
+ * makes no cudaMalloc/cudaFree and uses no allocating library routine.
+ *   - m*n may not exceed tsr_gemm_q4k_noalloc_max_outputs() (1,048,576);
+ *     larger shapes are refused with TSR_INVALID_ARGUMENT.
+ *   - The first call on a device looks up the array's device address; make
+ *     that call before starting any stream capture on that device.
+ *   - All calls on a device share the one array: calls whose kernels can
+ *     overlap on the GPU (different streams) race on it.  Nothing needs
+ *     clearing between calls; every partial that is read was just written.
+ * Same pointer and alignment rules as tsr_gemm_q4k. */
+uint64_t tsr_gemm_q4k_noalloc_max_outputs(void);
+int tsr_gemm_q4k_noalloc(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                         void* stream);
+
 /* ---- tensor-parallel sum all-reduce over NVLink peer memory ---------------
  * Replaces the rank-0 gather/add/broadcast of TpReduce
  * (src/models/qwen3_5/trunk.cpp:226-266) and the host-staged AllReduceSum

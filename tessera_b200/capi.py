@@ -81,6 +81,8 @@ SIGNATURES = {
     "tsr_add": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
     "tsr_fill": (C.c_int, [_vp, C.c_int32, _u64, _vp]),
     "tsr_dequantize": (C.c_int, [C.c_int, _vp, _vp, _vp, _u64, _u64, _vp]),
+    "tsr_gemm_q4k_noalloc_max_outputs": (_u64, []),
+    "tsr_gemm_q4k_noalloc": (C.c_int, [_vp, _vp, _vp, _u64, _u64, _u64, _vp]),
     "tsr_tp_create": (C.c_int, [C.c_int, C.c_int, C.c_int, _u64, C.POINTER(_vp)]),
     "tsr_tp_destroy": (None, [_vp]),
     "tsr_tp_local_block": (C.c_int, [_vp, C.POINTER(_vp), C.POINTER(_u64)]),
