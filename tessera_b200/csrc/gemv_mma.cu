@@ -7,11 +7,12 @@
 //   --per-sub-block integer scale, per-block fp32 scale--> C.
 //
 // Weights are the A operand (16 weight rows per warp), activations the B
-// operand.  Each fp32 activation row is expanded, once per CTA, into int8
-// "digit" columns a ~= s*(q1 + q2/254 + q3/254^2) (three digits for m <= 2,
-// two above), so the dot products are exact integer arithmetic and the only
-// rounding is the <= 6e-8 (three digits) or <= 1.6e-5 (two digits) relative
-// quantisation of the activation against its row maximum.  One MMA covers
+// operand.  Each 256-element block of an fp32 activation row is expanded,
+// once per CTA, into signed base-256 int8 "digit" columns
+// a ~= unit*(q1*65536 + q2*256 + q3) (three digits for m <= 2, two above), so
+// the dot products are exact integer arithmetic and the only rounding is the
+// <= 1.2e-7 (three digits) or <= 3.1e-5 (two digits) quantisation of the
+// activation relative to the largest magnitude of its block.  One MMA covers
 // exactly one 32-element Q4_K sub-block, whose 6-bit scale multiplies the
 // integer partial sum; the fp16 super-block scale d is applied in fp32 once
 // per block.  The -dmin*mn*sum(a) term of the format
@@ -86,170 +87,146 @@ __device__ __forceinline__ void mma_u8s8_zero(int (&d)[4], uint32_t a0, uint32_t
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// Quantise four activations to int8 digits; digit t of the four values comes
-// back packed in w[t] (two's complement bytes), with the digit sums in sum[t].
-// Rounding uses the 1.5*2^23 magic constant: after t = x*inv + magic the low
-// mantissa byte of t is the two's-complement integer rint(x*inv), which stays
-// within [-127,127] because the scale is the row maximum / 127, so neither a
-// conversion instruction nor a clamp is needed.
-__device__ __forceinline__ void quantise4(float4 x, float inv_s, float s, uint32_t (&w)[3]) {
-  const float v[4] = {x.x, x.y, x.z, x.w};
-  constexpr float kMagic = 12582912.0f;
-  const float s2 = s * (1.0f / 254.0f);
-  const float inv2 = inv_s * 254.0f, inv3 = inv2 * 254.0f;
-  uint32_t t1[4], t2[4], t3[4];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const float a1 = fmaf(v[e], inv_s, kMagic);
-    float r = fmaf(-(a1 - kMagic), s, v[e]);
-    const float a2 = fmaf(r, inv2, kMagic);
-    r = fmaf(-(a2 - kMagic), s2, r);
-    const float a3 = fmaf(r, inv3, kMagic);
-    t1[e] = __float_as_uint(a1);
-    t2[e] = __float_as_uint(a2);
-    t3[e] = __float_as_uint(a3);
+// Quantise four activations to signed base-256 digits.  With c = 2^shift / s
+// the value X = rint(x * c) fits 23 bits, so t = x*c + 1.5*2^23 holds X in its
+// low mantissa bits; adding 0x8080 and flipping those two bits turns the three
+// low bytes of the word into balanced digits (X = q1*65536 + q2*256 + q3 with
+// q2, q3 in [-128,127]).  No conversion instruction and no clamp is needed.
+// Three digits use shift 15 (|X| <= 127*2^15 < 2^22), two digits shift 7.
+// w[0] is the most significant digit of the four values, packed one per byte.
+__device__ __forceinline__ void quantise4(float4 x, float c, int terms, uint32_t (&w)[3]) {
+  constexpr float kMagic = 12582912.0f;                        // 1.5 * 2^23
+  constexpr uint32_t kBias = 0x8080u - 0x4B400000u;            // remove the magic, add the digit bias
+  const uint32_t y0 = (__float_as_uint(fmaf(x.x, c, kMagic)) + kBias) ^ 0x8080u;
+  const uint32_t y1 = (__float_as_uint(fmaf(x.y, c, kMagic)) + kBias) ^ 0x8080u;
+  const uint32_t y2 = (__float_as_uint(fmaf(x.z, c, kMagic)) + kBias) ^ 0x8080u;
+  const uint32_t y3 = (__float_as_uint(fmaf(x.w, c, kMagic)) + kBias) ^ 0x8080u;
+  // byte j of every word -> one word per digit
+  const uint32_t lo01 = __byte_perm(y0, y1, 0x5140), lo23 = __byte_perm(y2, y3, 0x5140);  // bytes 0,1 of each
+  const uint32_t b2 = __byte_perm(__byte_perm(y0, y1, 0x0062), __byte_perm(y2, y3, 0x0062), 0x5410);
+  const uint32_t b1 = __byte_perm(lo01, lo23, 0x7632);
+  const uint32_t b0 = __byte_perm(lo01, lo23, 0x5410);
+  if (terms == 3) {
+    w[0] = b2;
+    w[1] = b1;
+    w[2] = b0;
+  } else {
+    w[0] = b1;
+    w[1] = b0;
+    w[2] = 0;
   }
-  // gather the low bytes of four words into one
-  w[0] = __byte_perm(__byte_perm(t1[0], t1[1], 0x0040), __byte_perm(t1[2], t1[3], 0x0040), 0x5410);
-  w[1] = __byte_perm(__byte_perm(t2[0], t2[1], 0x0040), __byte_perm(t2[2], t2[3], 0x0040), 0x5410);
-  w[2] = __byte_perm(__byte_perm(t3[0], t3[1], 0x0040), __byte_perm(t3[2], t3[3], 0x0040), 0x5410);
-}
-
-// Activation staging.  Layout in shared memory:
-//   act : [block][sub-block 0..7][column][32 bytes]   int8 digits in k order
-//   sums: [block][digit plane 0..1][column][8 bytes]  per-sub-block digit sums
-//         S = D0 + 128*D1 with D0 in [-64,63]
-//   cscale[column] = s_row * 254^-digit
-__device__ __forceinline__ void stage_store(const StagedParams& p, int i, int k, float4 x, float inv_s,
-                                            float s, unsigned char* act) {
-  uint32_t w[3];
-  quantise4(x, inv_s, s, w);
-  // (block*8 + sub-block) = k / 32
-  unsigned char* dst = act + ((k >> 5) * p.ncols + i * p.terms) * 32 + (k & 31);
-  *reinterpret_cast<uint32_t*>(dst) = w[0];
-  *reinterpret_cast<uint32_t*>(dst + 32) = w[1];
-  if (p.terms > 2) *reinterpret_cast<uint32_t*>(dst + 64) = w[2];
-}
-
-// Digit sums of every (sub-block, column) from the staged bytes: one thread
-// per sub-block walks its columns.
-__device__ __forceinline__ void stage_sums(const StagedParams& p, const unsigned char* act,
-                                           unsigned char* sums) {
-  const int items = p.per * 8;  // block*8 + sub-block
-  for (int bs = threadIdx.x; bs < items; bs += kThreads) {
-    const int bl = bs >> 3, sb = bs & 7;
-    const unsigned char* src = act + static_cast<size_t>(bs) * p.ncols * 32;
-    unsigned char* d0p = sums + (bl * 2 * p.ncols) * 8 + sb;
-    unsigned char* d1p = d0p + p.ncols * 8;
-    for (int col = 0; col < p.ncols; ++col) {
-      const uint4 u0 = *reinterpret_cast<const uint4*>(src + col * 32);
-      const uint4 u1 = *reinterpret_cast<const uint4*>(src + col * 32 + 16);
-      int s0 = __dp4a(static_cast<int>(u0.x), 0x01010101, 0);
-      int s1 = __dp4a(static_cast<int>(u0.y), 0x01010101, 0);
-      int s2 = __dp4a(static_cast<int>(u0.z), 0x01010101, 0);
-      int s3 = __dp4a(static_cast<int>(u0.w), 0x01010101, 0);
-      s0 = __dp4a(static_cast<int>(u1.x), 0x01010101, s0);
-      s1 = __dp4a(static_cast<int>(u1.y), 0x01010101, s1);
-      s2 = __dp4a(static_cast<int>(u1.z), 0x01010101, s2);
-      s3 = __dp4a(static_cast<int>(u1.w), 0x01010101, s3);
-      const int sacc = (s0 + s1) + (s2 + s3);
-      const int d1 = (sacc + 64) >> 7;
-      d0p[col * 8] = static_cast<unsigned char>(sacc - 128 * d1);
-      d1p[col * 8] = static_cast<unsigned char>(d1);
-    }
-  }
-}
-
-__device__ __forceinline__ float4 load_quad(const StagedParams& p, const float* arow, int k0, int q) {
-  if (k0 + q * 4 < p.k) return __ldg(reinterpret_cast<const float4*>(arow + q * 4));
-  return make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
 __device__ __forceinline__ float abs_max4(float m, float4 x) {
   return fmaxf(m, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
 }
 
-template <typename AfterFirstLoads>
-__device__ __forceinline__ void stage_activations(const StagedParams& p, int k0, unsigned char* act,
-                                                  unsigned char* sums, float* cscale, float* red,
-                                                  unsigned long long* tr, AfterFirstLoads after_first_loads) {
-  const int quads = p.per * 64;  // float4 groups per row (a multiple of 64)
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  constexpr int kBatch = 8;
-  constexpr int kWarps = kThreads / 32;
-  const bool small = quads <= kThreads * kBatch;  // the whole row fits in registers
-  for (int i = 0; i < p.m; ++i) {
-    const float* arow = p.a + static_cast<size_t>(i) * p.k + k0;
-    float4 x[kBatch];
-    float amax = 0.0f;
-    if (small) {
+// Activation staging.  Layout in shared memory:
+//   act : [block][sub-block 0..7][column][32 bytes]   int8 digits in k order
+//   sums: [block][digit plane 0..1][column][8 bytes]  per-sub-block digit sums
+//         S = D0 + 128*D1 with D0 in [-64,63]
+//   cs  : [block][kMaxCols] fp32                       column scale s_block * 254^-digit
+// Every 256-element block of an activation row has its own scale (its
+// largest magnitude / 127), so one warp stages a block on its own: lane l
+// owns elements 4l..4l+3 and 128+4l..128+4l+3, the block maximum and the
+// sub-block sums are warp shuffles, and no CTA-wide pass is needed.
+constexpr int kStageBatch = 4;  // blocks whose loads one warp keeps in flight
+
+__device__ __forceinline__ void stage_block(const StagedParams& p, int i, int bl, float4 x0, float4 x1,
+                                            unsigned char* act, unsigned char* sums, float* cs,
+                                            int lane) {
+  float amax = abs_max4(abs_max4(0.0f, x0), x1);
 #pragma unroll
-      for (int b = 0; b < kBatch; ++b) {
-        const int q = threadIdx.x + b * kThreads;
-        x[b] = q < quads ? load_quad(p, arow, k0, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  amax = fminf(amax, 3.0e38f);
+  // x ~= unit * X with X = rint(x / unit), |X| <= 127 * 2^shift
+  const float top = p.terms == 3 ? 32768.0f : 128.0f;
+  const float unit = amax > 0.0f ? amax * (1.0f / 127.0f) / top : 1.0f;
+  const float c = 1.0f / unit;
+  uint32_t w0[3], w1[3];
+  quantise4(x0, c, p.terms, w0);
+  quantise4(x1, c, p.terms, w1);
+  // lane l: elements 4l.. -> sub-block l/8; elements 128+4l.. -> sub-block 4 + l/8
+  const int sb = lane >> 3, in_sb = (lane & 7) * 4;
+  unsigned char* dst0 = act + ((bl * 8 + sb) * p.ncols + i * p.terms) * 32 + in_sb;
+  unsigned char* dst1 = dst0 + 4 * p.ncols * 32;
+  unsigned char* sum0 = sums + ((bl * 2) * p.ncols + i * p.terms) * 8 + sb;
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {
+    if (t < p.terms) {
+      *reinterpret_cast<uint32_t*>(dst0 + t * 32) = w0[t];
+      *reinterpret_cast<uint32_t*>(dst1 + t * 32) = w1[t];
+      int a0 = __dp4a(static_cast<int>(w0[t]), 0x01010101, 0);
+      int a1 = __dp4a(static_cast<int>(w1[t]), 0x01010101, 0);
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) {
+        a0 += __shfl_xor_sync(0xFFFFFFFFu, a0, o);
+        a1 += __shfl_xor_sync(0xFFFFFFFFu, a1, o);
       }
-      // the activation loads are in flight: now queue the weight prefetch behind them
-      if (i == 0) after_first_loads();
-#pragma unroll
-      for (int b = 0; b < kBatch; ++b) amax = abs_max4(amax, x[b]);
-    } else {
-      if (i == 0) after_first_loads();
-      for (int q0 = threadIdx.x; q0 < quads; q0 += kThreads * kBatch) {
-#pragma unroll
-        for (int b = 0; b < kBatch; ++b) {
-          const int q = q0 + b * kThreads;
-          x[b] = q < quads ? load_quad(p, arow, k0, q) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int b = 0; b < kBatch; ++b) amax = abs_max4(amax, x[b]);
-      }
-    }
-    if (tr && threadIdx.x == 0) tr[40] = gtime();
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    if (lane == 0) red[warp] = amax;
-    __syncthreads();
-    float row_max = red[0];
-#pragma unroll
-    for (int wv = 1; wv < kWarps; ++wv) row_max = fmaxf(row_max, red[wv]);
-    __syncthreads();
-    if (tr && threadIdx.x == 0) tr[41] = gtime();
-    // Finite, non-zero scale; an all-zero row quantises to zeros with s = 1.
-    row_max = fminf(row_max, 3.0e38f);
-    const float s = row_max > 0.0f ? row_max * (1.0f / 127.0f) : 1.0f;
-    const float inv_s = 1.0f / s;
-    if (static_cast<int>(threadIdx.x) < p.terms) {
-      float cs = s;
-      for (int t = 0; t < static_cast<int>(threadIdx.x); ++t) cs *= (1.0f / 254.0f);
-      cscale[i * p.terms + threadIdx.x] = cs;
-    }
-    if (small) {
-#pragma unroll
-      for (int b = 0; b < kBatch; ++b) {
-        const int q = threadIdx.x + b * kThreads;
-        // q - lane is a multiple of 32 and quads a multiple of 64: warp-uniform branch
-        if (q < quads) stage_store(p, i, q * 4, x[b], inv_s, s, act);
-      }
-    } else {
-      for (int q0 = threadIdx.x; q0 < quads; q0 += kThreads * kBatch) {
-#pragma unroll
-        for (int b = 0; b < kBatch; ++b) {
-          const int q = q0 + b * kThreads;
-          x[b] = q < quads ? load_quad(p, arow, k0, q) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int b = 0; b < kBatch; ++b) {
-          const int q = q0 + b * kThreads;
-          if (q < quads) stage_store(p, i, q * 4, x[b], inv_s, s, act);
-        }
+      if ((lane & 7) == 0) {
+        const int h0 = (a0 + 64) >> 7, h1 = (a1 + 64) >> 7;
+        unsigned char* sp = sum0 + t * 8;
+        sp[0] = static_cast<unsigned char>(a0 - 128 * h0);
+        sp[4] = static_cast<unsigned char>(a1 - 128 * h1);
+        sp[p.ncols * 8] = static_cast<unsigned char>(h0);
+        sp[p.ncols * 8 + 4] = static_cast<unsigned char>(h1);
       }
     }
   }
-  if (tr && threadIdx.x == 0) tr[42] = gtime();
-  __syncthreads();
-  if (tr && threadIdx.x == 0) tr[43] = gtime();
-  stage_sums(p, act, sums);
-  if (tr && threadIdx.x == 0) tr[44] = gtime();
+  if (lane < p.terms) {
+    // digit `lane` (most significant first) weighs 256^(terms-1-lane) units
+    float weight = unit;
+    for (int t = lane; t < p.terms - 1; ++t) weight *= 256.0f;
+    cs[bl * kMaxCols + i * p.terms + lane] = weight;
+  }
+}
+
+template <typename AfterFirstLoads>
+__device__ __forceinline__ void stage_activations(const StagedParams& p, int k0, unsigned char* act,
+                                                  unsigned char* sums, float* cs,
+                                                  AfterFirstLoads after_first_loads,
+                                                  unsigned long long* tr = nullptr) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // The producer warp only issues the weight copies: its first TMA instruction
+  // can wait on the descriptor fetch, which must not hold up a share of the staging.
+  constexpr int kWarps = kConsumerWarps;
+  if (warp >= kWarps) {
+    // Touch one activation word first: the weight prefetch of all CTAs would
+    // otherwise queue ahead of everybody's activation loads in the memory system.
+    const float probe = __ldg(p.a + (k0 < p.k ? k0 : 0) + lane);
+    if (probe != probe + 1.0f || lane >= 0) after_first_loads();
+    return;
+  }
+  const int items = p.m * p.per;  // (activation row, block) pairs, row-major
+  bool first = true;
+  for (int base = warp; base < items || first; base += kWarps * kStageBatch) {
+    float4 x0[kStageBatch], x1[kStageBatch];
+#pragma unroll
+    for (int u = 0; u < kStageBatch; ++u) {
+      const int it = base + u * kWarps;
+      x0[u] = x1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (it < items) {
+        const int i = it / p.per, bl = it - i * p.per;
+        const int k = k0 + bl * kBlockElems;
+        if (k < p.k) {
+          const float4* src = reinterpret_cast<const float4*>(p.a + static_cast<size_t>(i) * p.k + k);
+          x0[u] = __ldg(src + lane);
+          x1[u] = __ldg(src + 32 + lane);
+        }
+      }
+    }
+    first = false;
+#pragma unroll
+    for (int u = 0; u < kStageBatch; ++u) {
+      const int it = base + u * kWarps;
+      if (it < items) {
+        const int i = it / p.per, bl = it - i * p.per;
+        stage_block(p, i, bl, x0[u], x1[u], act, sums, cs, lane);
+        if (tr && lane == 0 && u == 0 && base == warp) tr[40 + warp] = gtime();
+      }
+    }
+  }
+  if (tr && lane == 0) tr[50 + warp] = gtime();
 }
 
 template <int NCG>
@@ -261,9 +238,8 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   const int nblk_pad = nchunks * kChunkBlocks;
   unsigned char* act = smem + static_cast<size_t>(p.stages) * kStageBytes;
   unsigned char* sums = act + static_cast<size_t>(nblk_pad) * p.ncols * 256;
-  float* cscale = reinterpret_cast<float*>(sums + static_cast<size_t>(nblk_pad) * p.ncols * 16);
-  float* red = cscale + kMaxCols;           // 16 floats
-  float* xchg = red + 16;                   // [4 row groups][32 lanes][NCG*4]
+  float* cs = reinterpret_cast<float*>(sums + static_cast<size_t>(nblk_pad) * p.ncols * 16);  // [block][kMaxCols]
+  float* xchg = cs + static_cast<size_t>(nblk_pad) * kMaxCols;  // [4 row groups][32 lanes][NCG*4]
   float* outbuf = xchg + 4 * 32 * NCG * 4;  // [64 rows][NCG*8]
   uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
   uint64_t* empty = full + p.stages;
@@ -296,7 +272,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   };
   if (tr && tid == 0) tr[1] = gtime();
   if (!(p.debug & 1)) {
-    stage_activations(p, b0 * kBlockElems, act, sums, cscale, red, tr, prologue);
+    stage_activations(p, b0 * kBlockElems, act, sums, cs, prologue, tr);
   } else {
     prologue();
   }
@@ -339,6 +315,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
     sum_blk[g] = sum_plane[g] * 2;
   }
   const uint32_t mask0 = tig == 0 ? 0xFFFFFFFFu : 0u, mask1 = tig == 1 ? 0xFFFFFFFFu : 0u;
+  const float* cs_t = cs + 2 * tig;  // this thread's two columns of a group
   const uint32_t row_off = rowA * kRowPitch;
 
   float o[NCG][4];
@@ -409,10 +386,15 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
           int r0[4], r1[4];
           mma_u8s8_zero(r0, am, bm, 0u, 0u, s0, 0u);
           mma_u8s8_zero(r1, am, bm, 0u, 0u, s1, 0u);
-          o[g][0] = fmaf(dA, static_cast<float>(t1[g][0]), fmaf(-mA, static_cast<float>(r0[0] + 128 * r1[0]), o[g][0]));
-          o[g][1] = fmaf(dA, static_cast<float>(t1[g][1]), fmaf(-mA, static_cast<float>(r0[1] + 128 * r1[1]), o[g][1]));
-          o[g][2] = fmaf(dB, static_cast<float>(t1[g][2]), fmaf(-mB, static_cast<float>(r0[2] + 128 * r1[2]), o[g][2]));
-          o[g][3] = fmaf(dB, static_cast<float>(t1[g][3]), fmaf(-mB, static_cast<float>(r0[3] + 128 * r1[3]), o[g][3]));
+          const float2 c2 = *reinterpret_cast<const float2*>(cs_t + bl * kMaxCols + g * 8);
+          const float u0 = fmaf(dA, static_cast<float>(t1[g][0]), -mA * static_cast<float>(r0[0] + 128 * r1[0]));
+          const float u1 = fmaf(dA, static_cast<float>(t1[g][1]), -mA * static_cast<float>(r0[1] + 128 * r1[1]));
+          const float u2 = fmaf(dB, static_cast<float>(t1[g][2]), -mB * static_cast<float>(r0[2] + 128 * r1[2]));
+          const float u3 = fmaf(dB, static_cast<float>(t1[g][3]), -mB * static_cast<float>(r0[3] + 128 * r1[3]));
+          o[g][0] = fmaf(c2.x, u0, o[g][0]);
+          o[g][1] = fmaf(c2.y, u1, o[g][1]);
+          o[g][2] = fmaf(c2.x, u2, o[g][2]);
+          o[g][3] = fmaf(c2.y, u3, o[g][3]);
         }
       }
     }
@@ -443,7 +425,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
         const int col = g * 8 + 2 * tig + (e & 1);
         const int rr = rowA + (e >> 1) * 8;
         const float v = o[g][e] + xchg[((rg * 32 + lane) * NCG + g) * 4 + e];
-        if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v * cscale[col];
+        if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v;
       }
     }
   }
@@ -502,7 +484,7 @@ int env_int(const char* name, int fallback) {
 
 template <int NCG>
 size_t fixed_smem(uint64_t nblk_pad, int ncols) {
-  return nblk_pad * ncols * (256 + 16) + (kMaxCols + 16) * 4 + 4 * 32 * NCG * 4 * 4 +
+  return nblk_pad * ncols * (256 + 16) + nblk_pad * kMaxCols * 4 + 4 * 32 * NCG * 4 * 4 +
          kTileRows * NCG * 8 * 4 + 2 * 8 * 16 + 128;
 }
 
