@@ -303,8 +303,9 @@ int tsr_synchronize(tsr_context* ctx) {
   const cudaError_t e = cudaStreamSynchronize(ctx->stream);
   if (e != cudaSuccess) return ctx->fail(e, "cudaStreamSynchronize");
   // A staged kernel whose bounded wait ran out has left wrong results behind.
-  unsigned int timeouts = 0;
-  if (tsr::staged_wait_timeouts(&timeouts) == tsr::kOk && timeouts != ctx->seen_timeouts) {
+  unsigned int timeouts = 0, umma = 0;
+  tsr::umma_wait_timeouts(&umma);
+  if (tsr::staged_wait_timeouts(&timeouts) == tsr::kOk && (timeouts += umma) != ctx->seen_timeouts) {
     ctx->seen_timeouts = timeouts;
     ctx->error = "a staged kernel gave up waiting for a TMA copy";
     return tsr::kDeviceError;

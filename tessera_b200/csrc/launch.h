@@ -41,4 +41,10 @@ int staged_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_
 // Number of bounded device waits that gave up since the library was loaded.
 int staged_wait_timeouts(unsigned int* count);
 
+// tcgen05/TMEM tile for small batches (gemm_umma.cu).  fmt: 0 Q4_K, 1 Q6_K,
+// 2 MXFP4, 3 FP8.  kUnsupportedFeature when the shape is outside its range.
+int umma_gemm(int fmt, const float* a, const void* w, const float* scale, float* c, uint64_t m,
+              uint64_t n, uint64_t k, cudaStream_t st);
+int umma_wait_timeouts(unsigned int* count);
+
 }  // namespace tsr

@@ -12,7 +12,7 @@
 
 namespace tsr {
 
-constexpr uint32_t kSpinLimit = 1u << 26;
+constexpr uint32_t kSpinLimit = 1u << 22;  // each poll may itself suspend for a while: seconds at most
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -18,6 +18,20 @@ TOL = 2e-3  # contract: max |y - ref| / max |ref| for fp32-accumulated projectio
 # into int8 digits against its row maximum: three digits (<= 6e-8) for m <= 2,
 # two digits (<= 1.6e-5 per element) for m = 3..8.
 TIGHT = 1e-4
+# The tcgen05 tile (Q4_K m >= 9; Q6_K, FP8 m >= 2) rounds each dequantised weight
+# to fp16 (2^-11), like the reference's own tensor-core tile; MXFP4 weights are
+# exact in fp16.
+FP16_WEIGHTS = 1e-3
+
+
+def bound(dtype, m, k=256):
+    if dtype == "mxfp4":
+        return 2e-5
+    if dtype == "q4k":
+        return 2e-5 if m <= 2 else (TIGHT if m <= 8 else FP16_WEIGHTS)
+    if dtype == "fp8":
+        return FP16_WEIGHTS if (m >= 2 and k % 64 == 0) else 2e-5
+    return 2e-5 if m == 1 else FP16_WEIGHTS  # q6k
 
 
 def run_named(backend, name, buffers, scalars, grid_y=1):
@@ -136,7 +150,7 @@ def test_projections_match_golden(backend, golden):
             sc = [m, n, k, 1] if ("_vec" in kid or "_rows3" in kid) else [m, n, k]
             run_named(backend, kid, [a, w, out], sc)
             got = backend.download(out, np.float32, m * n).reshape(m, n)
-            assert rel_err(got, golden[f"{name}_gemm"]) < TIGHT, kid
+            assert rel_err(got, golden[f"{name}_gemm"]) < bound(name, m), kid
     af = backend.upload(golden["fp8_a"])
     outf = backend.AllocateBuffer(2 * 16 * 4)
     run_named(backend, "gemm_fp8", [af, backend.upload(golden["fp8_w"]), backend.upload(golden["fp8_s"]), outf],
@@ -166,6 +180,8 @@ SHAPES = [
     # (m, n, k): ragged n (not a multiple of 8), split remainders, m = 1..17
     (1, 64, 256), (1, 13, 768), (2, 100, 1024), (3, 40, 512), (4, 24, 2048), (5, 9, 256),
     (7, 33, 1280), (16, 48, 1024), (17, 31, 512),
+    # tcgen05 tile: ragged weight-row tile, more than one 64-token chunk
+    (70, 200, 1024), (130, 136, 512),
 ]
 
 
@@ -188,7 +204,7 @@ def test_project_batch_matches_oracle(backend, oracle, dtype, m, n, k):
     p.ProjectBatch(dtype, backend.upload(a), backend.upload(w), out, m, n, k)
     got = backend.download(out, np.float32, m * n).reshape(m, n)
     assert rel_err(got, ref) < TOL, p.last_kernel
-    assert rel_err(got, ref) < (2e-5 if m <= 2 or m > 8 else TIGHT), p.last_kernel
+    assert rel_err(got, ref) < bound(dtype, m), p.last_kernel
 
 
 @pytest.mark.parametrize("fmt,dtype", [(0, Q4K), (1, Q6K)])
@@ -203,7 +219,8 @@ def test_vec_split_partial_regions(backend, oracle, fmt, dtype, split):
     run_named(backend, f"gemm_{dtype}_vec", [backend.upload(a), backend.upload(w), part], [m, n, k, split],
               grid_y=split)
     got = backend.download(part, np.float32, split * m * n).reshape(split, m, n)
-    assert rel_err(got, part_ref) < 2e-5  # m = 2: three-digit activations
+    # Q4_K m = 2: three-digit staged path; Q6_K: tcgen05 tile when split == 1, fp32 rows kernel otherwise
+    assert rel_err(got, part_ref) < (bound(dtype, m) if split == 1 else 2e-5)
     out = backend.AllocateBuffer(m * n * 4)
     run_named(backend, "gemm_vec_reduce", [part, out], [m * n, split])
     red = backend.download(out, np.float32, m * n)
@@ -218,7 +235,7 @@ def test_fp8_projection_matches_oracle(backend, oracle, m, n, k):
     ref = oracle.gemm_fp8(a, w, s, m, n, k)
     out = backend.AllocateBuffer(m * n * 4)
     run_named(backend, "gemm_fp8", [backend.upload(a), backend.upload(w), backend.upload(s), out], [m, n, k])
-    assert rel_err(backend.download(out, np.float32, m * n).reshape(m, n), ref) < 2e-5
+    assert rel_err(backend.download(out, np.float32, m * n).reshape(m, n), ref) < bound("fp8", m, k)
 
 
 @pytest.mark.parametrize("m", [1, 4, 16])
