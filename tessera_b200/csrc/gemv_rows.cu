@@ -83,9 +83,12 @@ gemv_q4k_rows_kernel(const float* __restrict__ a, const uint8_t* __restrict__ w,
 }
 
 // ---------------------------------------------------------------- Q6_K
-// Lane l of a block: ql[l], ql[32+l], ql[64+l], ql[96+l], qh[l], qh[32+l]
-// (src/core/numerics/quant.cpp:421-449).  210-byte blocks are only 2-byte
-// aligned, so this general path reads bytes.
+// 210-byte blocks are only 2-byte aligned, so this path reads 16-bit words.
+// Lane (h = lane/16, j = lane%16) of a block takes ql[64h+2j..], ql[64h+32+2j..]
+// and qh[32h+2j..]: two adjacent positions of each of the four 32-element runs
+// of half h, i.e. elements 128h + 32*run + 2j + {0,1}
+// (src/core/numerics/quant.cpp:421-449).  Integers become floats through the
+// 2^23 magic constant instead of conversion instructions.
 template <int MR>
 __global__ void __launch_bounds__(256)
 gemv_q6k_rows_kernel(const float* __restrict__ a, const uint8_t* __restrict__ w,
@@ -98,33 +101,49 @@ gemv_q6k_rows_kernel(const float* __restrict__ a, const uint8_t* __restrict__ w,
   const int per = nb / split;
   const int b0 = blockIdx.y * per;
   const uint8_t* wrow = w + static_cast<size_t>(row) * nb * kQ6KBlockBytes;
-  const int is = lane >> 4;
+  const int h = lane >> 4, j = lane & 15;
+  constexpr float kMagic = 8388608.0f + 32.0f;  // (q | 0x4B000000) - kMagic = q - 32
   float acc[MR];
 #pragma unroll
   for (int i = 0; i < MR; ++i) acc[i] = 0.0f;
+#pragma unroll 4
   for (int b = b0; b < b0 + per; ++b) {
-    const uint8_t* blk = wrow + static_cast<size_t>(b) * kQ6KBlockBytes;
-    const float d = fp16_bits_to_float(__ldg(reinterpret_cast<const unsigned short*>(blk + 208)));
+    const unsigned short* blk = reinterpret_cast<const unsigned short*>(wrow + static_cast<size_t>(b) * kQ6KBlockBytes);
+    const uint32_t l0 = __ldg(blk + 32 * h + j);        // ql[64h + 2j, +1]
+    const uint32_t l1 = __ldg(blk + 32 * h + 16 + j);   // ql[64h + 32 + 2j, +1]
+    const uint32_t qh = __ldg(blk + 64 + 16 * h + j);   // qh[32h + 2j, +1]
+    const float d = fp16_bits_to_float(__ldg(blk + 104));
+    // scales of half h: bytes 192 + 8h .. +7; run r of this lane uses byte (j>>3) + 2r
+    const uint32_t s01 = __ldg(blk + 96 + 4 * h + 0), s23 = __ldg(blk + 96 + 4 * h + 1);
+    const uint32_t s45 = __ldg(blk + 96 + 4 * h + 2), s67 = __ldg(blk + 96 + 4 * h + 3);
+    const int sh = 8 * (j >> 3);
+    const float sc[4] = {static_cast<float>(static_cast<signed char>((s01 >> sh) & 0xFF)),
+                         static_cast<float>(static_cast<signed char>((s23 >> sh) & 0xFF)),
+                         static_cast<float>(static_cast<signed char>((s45 >> sh) & 0xFF)),
+                         static_cast<float>(static_cast<signed char>((s67 >> sh) & 0xFF))};
+    // runs: 0 = low nibble of l0, 1 = low nibble of l1, 2 = high nibble of l0, 3 = high nibble of l1
+    float wv[4][2];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint32_t l0 = __ldg(blk + 64 * h + lane), l1 = __ldg(blk + 64 * h + 32 + lane);
-      const uint32_t qh = __ldg(blk + 128 + 32 * h + lane);
-      const signed char* sc = reinterpret_cast<const signed char*>(blk + 192 + 8 * h + is);
-      const float q[4] = {
-          static_cast<float>(static_cast<int>((l0 & 15u) | ((qh & 3u) << 4)) - 32),
-          static_cast<float>(static_cast<int>((l1 & 15u) | (((qh >> 2) & 3u) << 4)) - 32),
-          static_cast<float>(static_cast<int>((l0 >> 4) | (((qh >> 4) & 3u) << 4)) - 32),
-          static_cast<float>(static_cast<int>((l1 >> 4) | (((qh >> 6) & 3u) << 4)) - 32)};
-      float wv[4];
+    for (int r = 0; r < 4; ++r) {
+      const uint32_t lw = (r & 1) ? l1 : l0;
+      const uint32_t nib = (r & 2) ? (lw >> 4) : lw;
+      const uint32_t hi2 = qh >> (2 * r);
+      const uint32_t q0 = (nib & 0xFu) | ((hi2 & 3u) << 4);
+      const uint32_t q1 = ((nib >> 8) & 0xFu) | (((hi2 >> 8) & 3u) << 4);
+      const float ds = d * sc[r];
+      wv[r][0] = ds * (__uint_as_float(q0 | 0x4B000000u) - kMagic);
+      wv[r][1] = ds * (__uint_as_float(q1 | 0x4B000000u) - kMagic);
+    }
+    const int kbase = b * kBlockElems + 128 * h + 2 * j;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) wv[e] = d * static_cast<float>(__ldg(sc + 2 * e)) * q[e];
-      const int kbase = b * kBlockElems + 128 * h + lane;
+    for (int i = 0; i < MR; ++i) {
+      if (i < mrows) {
+        const float* ar = a + static_cast<size_t>(i) * k + kbase;
 #pragma unroll
-      for (int i = 0; i < MR; ++i) {
-        if (i < mrows) {
-          const float* ar = a + static_cast<size_t>(i) * k + kbase;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) acc[i] = fmaf(__ldg(ar + 32 * e), wv[e], acc[i]);
+        for (int r = 0; r < 4; ++r) {
+          const float2 x = __ldg(reinterpret_cast<const float2*>(ar + 32 * r));
+          acc[i] = fmaf(x.x, wv[r][0], acc[i]);
+          acc[i] = fmaf(x.y, wv[r][1], acc[i]);
         }
       }
     }
