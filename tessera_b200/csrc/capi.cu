@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -71,6 +72,42 @@ struct tsr_context {
     return stage + static_cast<size_t>(i) * kStageWindow;
   }
 };
+
+namespace tsr {
+
+// Last output range written by a launch of this library, per stream.
+bool pdl_allowed(cudaStream_t stream, const void* read_ptr, size_t read_bytes, const void* out_ptr,
+                 size_t out_bytes) {
+  static const bool enabled = [] {
+    const char* v = std::getenv("TSR_PDL");
+    return v == nullptr || std::atoi(v) != 0;
+  }();
+  struct Last {
+    cudaStream_t stream;
+    const unsigned char* ptr;
+    size_t bytes;
+  };
+  static std::mutex mutex;
+  static Last table[16] = {};
+  std::lock_guard<std::mutex> lock(mutex);
+  Last* slot = nullptr;
+  for (Last& l : table)
+    if (l.ptr != nullptr && l.stream == stream) slot = &l;
+  bool ok = enabled;
+  if (slot != nullptr) {
+    const auto* r = static_cast<const unsigned char*>(read_ptr);
+    if (r < slot->ptr + slot->bytes && slot->ptr < r + read_bytes) ok = false;  // previous output is our weight
+  }
+  if (slot == nullptr) {
+    static int next = 0;
+    slot = &table[next];
+    next = (next + 1) % 16;
+  }
+  *slot = Last{stream, static_cast<const unsigned char*>(out_ptr), out_bytes};
+  return ok;
+}
+
+}  // namespace tsr
 
 extern "C" {
 

@@ -52,6 +52,8 @@ quantize_fp8_kernel(float* __restrict__ data, const float* __restrict__ in,
 __global__ void vec_reduce_kernel(const float* __restrict__ part, float* __restrict__ c,
                                   size_t total, int split) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  pdl_wait();     // the partials come from the kernel just ahead
+  pdl_trigger();  // the next projection may start prefetching its weights
   if (i >= total) return;
   float acc = 0.0f;
   for (int s = 0; s < split; ++s) acc += part[s * total + i];
@@ -168,8 +170,11 @@ int tsr_quantize_fp8_pack(const float* in, void* out, float* scale, uint64_t row
 
 int tsr_gemm_vec_reduce(const float* part, float* c, uint64_t total, uint64_t split, void* stream) {
   if (!part || !c || total == 0 || split == 0) return kInvalidArgument;
-  vec_reduce_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      part, c, total, static_cast<int>(split));
+  auto st = static_cast<cudaStream_t>(stream);
+  // reads the partial buffer only after its wait, so it can always be a programmatic dependent
+  const bool pdl = pdl_allowed(st, nullptr, 0, c, total * 4);
+  launch_kernel(vec_reduce_kernel, dim3(blocks_for(total, 256)), dim3(256), 0, st, pdl, part, c,
+                static_cast<size_t>(total), static_cast<int>(split));
   return check_launch();
 }
 

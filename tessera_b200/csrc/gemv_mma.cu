@@ -61,6 +61,7 @@ struct StagedParams {
   int terms;   // int8 digits per activation row
   int ncols;   // m * terms
   int debug;   // experiment switches: 1 skips activation staging, 2 skips the block math
+  int pdl;     // launched as a programmatic dependent: prefetch weights, then wait for the stream
   unsigned long long region_stride;
   unsigned long long* trace;  // optional per-CTA timeline (experiments only)
 };
@@ -271,10 +272,20 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
     }
   };
   if (tr && tid == 0) tr[1] = gtime();
-  if (!(p.debug & 1)) {
-    stage_activations(p, b0 * kBlockElems, act, sums, cs, prologue, tr);
-  } else {
+  if (p.pdl) {
+    // Weights are not written by the kernel ahead of us (the launcher checked):
+    // start their prefetch, then wait for that kernel's results to be visible.
     prologue();
+    pdl_wait();
+    pdl_trigger();
+  }
+  auto deferred_prologue = [&]() {
+    if (!p.pdl) prologue();
+  };
+  if (!(p.debug & 1)) {
+    stage_activations(p, b0 * kBlockElems, act, sums, cs, deferred_prologue, tr);
+  } else {
+    deferred_prologue();
   }
   __syncthreads();
   if (tr && tid == 0) tr[2] = gtime();
@@ -489,8 +500,8 @@ size_t fixed_smem(uint64_t nblk_pad, int ncols) {
 }
 
 template <int NCG>
-int launch_staged(const CUtensorMap& map, StagedParams p, uint64_t n, uint64_t split, uint64_t nchunks,
-                  cudaStream_t st) {
+int launch_staged(const CUtensorMap& map, const void* w, StagedParams p, uint64_t n, uint64_t split,
+                  uint64_t nchunks, cudaStream_t st) {
   const size_t fixed = fixed_smem<NCG>(nchunks * kChunkBlocks, p.ncols);
   if (fixed + 2 * kStageBytes > static_cast<size_t>(kMaxSmem)) return kUnsupportedFeature;
   // Ring depth: two CTAs per SM when two stages each still fit in half of
@@ -512,7 +523,9 @@ int launch_staged(const CUtensorMap& map, StagedParams p, uint64_t n, uint64_t s
     attr = true;
   }
   const dim3 grid(static_cast<unsigned>((n + kTileRows - 1) / kTileRows), static_cast<unsigned>(split));
-  gemv_q4k_staged_kernel<NCG><<<grid, kThreads, smem, st>>>(map, p);
+  const size_t w_bytes = n * (static_cast<size_t>(p.k) / kBlockElems) * kQ4KBlockBytes;
+  p.pdl = pdl_allowed(st, w, w_bytes, p.c, split * p.region_stride * 4) ? 1 : 0;
+  launch_kernel(gemv_q4k_staged_kernel<NCG>, grid, dim3(kThreads), smem, st, p.pdl != 0, map, p);
   return check_launch();
 }
 
@@ -560,11 +573,11 @@ int staged_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_
   CUtensorMap map;
   if (int rc = q4k_tensor_map(w, n, nb, &map)) return rc;
   StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
-                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0),
+                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0,
                  static_cast<unsigned long long>(m * n),
                  reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(std::strtoull(std::getenv("TSR_TRACE_PTR") ? std::getenv("TSR_TRACE_PTR") : "0", nullptr, 10)))};
-  if (ncols <= 8) return launch_staged<1>(map, p, n, split, nchunks, st);
-  return launch_staged<2>(map, p, n, split, nchunks, st);
+  if (ncols <= 8) return launch_staged<1>(map, w, p, n, split, nchunks, st);
+  return launch_staged<2>(map, w, p, n, split, nchunks, st);
 }
 
 int staged_wait_timeouts(unsigned int* count) {

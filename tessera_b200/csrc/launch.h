@@ -22,6 +22,40 @@ inline int check_launch() {
   return kDeviceError;
 }
 
+// ---- programmatic dependent launch -----------------------------------------
+// A kernel launched with `pdl` set may begin while the previous kernel of the
+// stream is still running; it must execute pdl_wait() before it touches
+// anything that kernel wrote (or writes anything that kernel reads), and calls
+// pdl_trigger() after that wait so that at most two kernels ever overlap.
+// Before the wait the staged kernels only prefetch weights, so the launcher
+// drops the attribute when the previous launch of this library on the stream
+// wrote into the weight range (pdl_allowed).
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+// True when a kernel that reads [read_ptr, +read_bytes) before its pdl_wait()
+// may overlap the previous launch on `stream`; records [out_ptr, +out_bytes) as
+// the range this launch writes.
+bool pdl_allowed(cudaStream_t stream, const void* read_ptr, size_t read_bytes, const void* out_ptr,
+                 size_t out_bytes);
+
 // General warp-per-row family (gemv_rows.cu).
 int rows_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
                   uint64_t split, cudaStream_t st);
