@@ -48,6 +48,8 @@ int tsr_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_t n
     return kInvalidArgument;
   if (!aligned16(a) || (reinterpret_cast<uintptr_t>(w) & 1u) || !aligned16(c))
     return kInvalidArgument;
+  const int rc = staged_gemm_q6k(a, w, c, m, n, k, split, static_cast<cudaStream_t>(stream));
+  if (rc != kUnsupportedFeature) return rc;
   if (m >= 2 && split == 1) {
     const int rt = umma_gemm(1, a, w, nullptr, c, m, n, k, static_cast<cudaStream_t>(stream));
     if (rt != kUnsupportedFeature) return rt;

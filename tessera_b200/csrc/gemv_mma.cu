@@ -32,6 +32,7 @@
 #include "codec.cuh"
 #include "launch.h"
 #include "pipeline.cuh"
+#include "staged_common.cuh"
 
 namespace tsr {
 
@@ -46,189 +47,11 @@ constexpr int kChunkBlocks = kBoxBlocks * kBoxesPerStage;
 constexpr int kRowPitch = kBoxBlocks * kQ4KBlockBytes;
 constexpr int kBoxBytes = kTileRows * kRowPitch;        // 18432
 constexpr int kStageBytes = kBoxesPerStage * kBoxBytes;  // 18432
-constexpr int kConsumerWarps = 8;
+constexpr int kConsumerWarps = staged::kStagedConsumerWarps;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;
-constexpr int kMaxSmem = 227 * 1024;
-constexpr int kMaxCols = 16;
+constexpr int kThreads = staged::kStagedThreads;
 
-struct StagedParams {
-  const float* a;
-  float* c;
-  int m, n, k;
-  int per;     // blocks per split chunk
-  int stages;  // ring depth
-  int terms;   // int8 digits per activation row
-  int ncols;   // m * terms
-  int debug;   // experiment switches: 1 skips activation staging, 2 skips the block math
-  int pdl;     // launched as a programmatic dependent: prefetch weights, then wait for the stream
-  unsigned long long region_stride;
-  unsigned long long* trace;  // optional per-CTA timeline (experiments only)
-};
-
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ uint4 lds128(const unsigned char* p) {
-  return *reinterpret_cast<const uint4*>(p);
-}
-__device__ __forceinline__ uint2 lds64(const unsigned char* p) {
-  return *reinterpret_cast<const uint2*>(p);
-}
-
-// D(16x8, s32) = A(16x32, u8, row) * B(32x8, s8, col), zero accumulate input
-__device__ __forceinline__ void mma_u8s8_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                              uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%10,%10,%10,%10};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
-
-// Quantise four activations to signed base-256 digits.  With c = 2^shift / s
-// the value X = rint(x * c) fits 23 bits, so t = x*c + 1.5*2^23 holds X in its
-// low mantissa bits; adding 0x8080 and flipping those two bits turns the three
-// low bytes of the word into balanced digits (X = q1*65536 + q2*256 + q3 with
-// q2, q3 in [-128,127]).  No conversion instruction and no clamp is needed.
-// Three digits use shift 15 (|X| <= 127*2^15 < 2^22), two digits shift 7.
-// w[0] is the most significant digit of the four values, packed one per byte.
-__device__ __forceinline__ void quantise4(float4 x, float c, int terms, uint32_t (&w)[3]) {
-  constexpr float kMagic = 12582912.0f;                        // 1.5 * 2^23
-  constexpr uint32_t kBias = 0x8080u - 0x4B400000u;            // remove the magic, add the digit bias
-  const uint32_t y0 = (__float_as_uint(fmaf(x.x, c, kMagic)) + kBias) ^ 0x8080u;
-  const uint32_t y1 = (__float_as_uint(fmaf(x.y, c, kMagic)) + kBias) ^ 0x8080u;
-  const uint32_t y2 = (__float_as_uint(fmaf(x.z, c, kMagic)) + kBias) ^ 0x8080u;
-  const uint32_t y3 = (__float_as_uint(fmaf(x.w, c, kMagic)) + kBias) ^ 0x8080u;
-  // byte j of every word -> one word per digit
-  const uint32_t lo01 = __byte_perm(y0, y1, 0x5140), lo23 = __byte_perm(y2, y3, 0x5140);  // bytes 0,1 of each
-  const uint32_t b2 = __byte_perm(__byte_perm(y0, y1, 0x0062), __byte_perm(y2, y3, 0x0062), 0x5410);
-  const uint32_t b1 = __byte_perm(lo01, lo23, 0x7632);
-  const uint32_t b0 = __byte_perm(lo01, lo23, 0x5410);
-  if (terms == 3) {
-    w[0] = b2;
-    w[1] = b1;
-    w[2] = b0;
-  } else {
-    w[0] = b1;
-    w[1] = b0;
-    w[2] = 0;
-  }
-}
-
-__device__ __forceinline__ float abs_max4(float m, float4 x) {
-  return fmaxf(m, fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
-}
-
-// Activation staging.  Layout in shared memory:
-//   act : [block][sub-block 0..7][column][32 bytes]   int8 digits in k order
-//   sums: [block][digit plane 0..1][column][8 bytes]  per-sub-block digit sums
-//         S = D0 + 128*D1 with D0 in [-64,63]
-//   cs  : [block][kMaxCols] fp32                       column scale s_block * 254^-digit
-// Every 256-element block of an activation row has its own scale (its
-// largest magnitude / 127), so one warp stages a block on its own: lane l
-// owns elements 4l..4l+3 and 128+4l..128+4l+3, the block maximum and the
-// sub-block sums are warp shuffles, and no CTA-wide pass is needed.
-constexpr int kStageBatch = 4;  // blocks whose loads one warp keeps in flight
-
-__device__ __forceinline__ void stage_block(const StagedParams& p, int i, int bl, float4 x0, float4 x1,
-                                            unsigned char* act, unsigned char* sums, float* cs,
-                                            int lane) {
-  float amax = abs_max4(abs_max4(0.0f, x0), x1);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-  amax = fminf(amax, 3.0e38f);
-  // x ~= unit * X with X = rint(x / unit), |X| <= 127 * 2^shift
-  const float top = p.terms == 3 ? 32768.0f : 128.0f;
-  const float unit = amax > 0.0f ? amax * (1.0f / 127.0f) / top : 1.0f;
-  const float c = 1.0f / unit;
-  uint32_t w0[3], w1[3];
-  quantise4(x0, c, p.terms, w0);
-  quantise4(x1, c, p.terms, w1);
-  // lane l: elements 4l.. -> sub-block l/8; elements 128+4l.. -> sub-block 4 + l/8
-  const int sb = lane >> 3, in_sb = (lane & 7) * 4;
-  unsigned char* dst0 = act + ((bl * 8 + sb) * p.ncols + i * p.terms) * 32 + in_sb;
-  unsigned char* dst1 = dst0 + 4 * p.ncols * 32;
-  unsigned char* sum0 = sums + ((bl * 2) * p.ncols + i * p.terms) * 8 + sb;
-#pragma unroll
-  for (int t = 0; t < 3; ++t) {
-    if (t < p.terms) {
-      *reinterpret_cast<uint32_t*>(dst0 + t * 32) = w0[t];
-      *reinterpret_cast<uint32_t*>(dst1 + t * 32) = w1[t];
-      int a0 = __dp4a(static_cast<int>(w0[t]), 0x01010101, 0);
-      int a1 = __dp4a(static_cast<int>(w1[t]), 0x01010101, 0);
-#pragma unroll
-      for (int o = 1; o < 8; o <<= 1) {
-        a0 += __shfl_xor_sync(0xFFFFFFFFu, a0, o);
-        a1 += __shfl_xor_sync(0xFFFFFFFFu, a1, o);
-      }
-      if ((lane & 7) == 0) {
-        const int h0 = (a0 + 64) >> 7, h1 = (a1 + 64) >> 7;
-        unsigned char* sp = sum0 + t * 8;
-        sp[0] = static_cast<unsigned char>(a0 - 128 * h0);
-        sp[4] = static_cast<unsigned char>(a1 - 128 * h1);
-        sp[p.ncols * 8] = static_cast<unsigned char>(h0);
-        sp[p.ncols * 8 + 4] = static_cast<unsigned char>(h1);
-      }
-    }
-  }
-  if (lane < p.terms) {
-    // digit `lane` (most significant first) weighs 256^(terms-1-lane) units
-    float weight = unit;
-    for (int t = lane; t < p.terms - 1; ++t) weight *= 256.0f;
-    cs[bl * kMaxCols + i * p.terms + lane] = weight;
-  }
-}
-
-template <typename AfterFirstLoads>
-__device__ __forceinline__ void stage_activations(const StagedParams& p, int k0, unsigned char* act,
-                                                  unsigned char* sums, float* cs,
-                                                  AfterFirstLoads after_first_loads,
-                                                  unsigned long long* tr = nullptr) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  // The producer warp only issues the weight copies: its first TMA instruction
-  // can wait on the descriptor fetch, which must not hold up a share of the staging.
-  constexpr int kWarps = kConsumerWarps;
-  if (warp >= kWarps) {
-    // Touch one activation word first: the weight prefetch of all CTAs would
-    // otherwise queue ahead of everybody's activation loads in the memory system.
-    const float probe = __ldg(p.a + (k0 < p.k ? k0 : 0) + lane);
-    if (probe != probe + 1.0f || lane >= 0) after_first_loads();
-    return;
-  }
-  const int items = p.m * p.per;  // (activation row, block) pairs, row-major
-  bool first = true;
-  for (int base = warp; base < items || first; base += kWarps * kStageBatch) {
-    float4 x0[kStageBatch], x1[kStageBatch];
-#pragma unroll
-    for (int u = 0; u < kStageBatch; ++u) {
-      const int it = base + u * kWarps;
-      x0[u] = x1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (it < items) {
-        const int i = it / p.per, bl = it - i * p.per;
-        const int k = k0 + bl * kBlockElems;
-        if (k < p.k) {
-          const float4* src = reinterpret_cast<const float4*>(p.a + static_cast<size_t>(i) * p.k + k);
-          x0[u] = __ldg(src + lane);
-          x1[u] = __ldg(src + 32 + lane);
-        }
-      }
-    }
-    first = false;
-#pragma unroll
-    for (int u = 0; u < kStageBatch; ++u) {
-      const int it = base + u * kWarps;
-      if (it < items) {
-        const int i = it / p.per, bl = it - i * p.per;
-        stage_block(p, i, bl, x0[u], x1[u], act, sums, cs, lane);
-        if (tr && lane == 0 && u == 0 && base == warp) tr[40 + warp] = gtime();
-      }
-    }
-  }
-  if (tr && lane == 0) tr[50 + warp] = gtime();
-}
+using namespace staged;
 
 template <int NCG>
 __global__ void __launch_bounds__(kThreads)
@@ -283,7 +106,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
     if (!p.pdl) prologue();
   };
   if (!(p.debug & 1)) {
-    stage_activations(p, b0 * kBlockElems, act, sums, cs, deferred_prologue, tr);
+    stage_activations<8>(p, b0 * kBlockElems, act, sums, cs, deferred_prologue, tr);
   } else {
     deferred_prologue();
   }

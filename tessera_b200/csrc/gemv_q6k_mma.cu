@@ -1,0 +1,440 @@
+// Staged tensor-pipe GEMV for Q6_K weights (m = 1..8 activation rows).
+//
+// Same structure as the Q4_K kernel (gemv_mma.cu): one CTA per 64-row tile
+// and split chunk, a TMA-fed ring of shared-memory stages, weights as the A
+// operand of an int8 mma.sync, activations as signed base-256 digit columns,
+// integer group scales applied to the s32 partial sums, the fp16 block scale
+// in fp32.
+//
+// What Q6_K changes (block = ql[128] qh[64] int8 scales[16] fp16 d, 210 bytes;
+// value = d * sc[g] * (q - 32), 16 elements per scale group;
+// src/core/numerics/quant.cpp:421-449 of the reference):
+//   * A row of 210-byte blocks is only 8-byte aligned (k/256 a multiple of 4),
+//     and TMA wants 16-byte strides.  Two tensor maps solve it: one over the
+//     even rows, one over the odd rows, each with a row pitch of two weight
+//     rows (a multiple of 16 bytes) and, for the odd rows, a base moved down
+//     to the 16-byte boundary.  A stage is the 464-byte window of each row
+//     that contains two blocks, starting at the 16-byte boundary below them;
+//     464 B = 80 mod 128 keeps the 4-byte fragment loads bank-conflict free.
+//     Warps 0,1 of a set own the even rows of the tile, warps 2,3 the odd rows.
+//   * Stages start at even block indices, so the first block of a stage is
+//     word aligned and the second one sits 2 bytes off a word: its words are
+//     assembled from two aligned loads with a funnel shift.
+//   * One MMA (m16n8k16, u8 x s8) per 16-element scale group; the 6-bit value
+//     is the nibble OR the two high bits moved into place.
+//   * The "- 32" is one more pair of MMAs per block: the int8 scales against
+//     the per-group activation digit sums, i.e. sum_g sc[g] * sum_k a[k].
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+#include <mutex>
+#include <unordered_map>
+
+#include "codec.cuh"
+#include "launch.h"
+#include "pipeline.cuh"
+#include "staged_common.cuh"
+
+namespace tsr {
+
+__device__ unsigned int g_q6k_wait_timeouts = 0;
+
+namespace {
+
+using namespace staged;
+
+constexpr int kTileRows = 64;
+constexpr int kHalfRows = kTileRows / 2;                 // rows per tensor map (even / odd)
+constexpr int kChunkBytes = 2 * kQ6KBlockBytes;          // 420: two blocks per stage
+constexpr int kWindowWords = 58;                         // u64 per row window
+constexpr int kRowPitch = kWindowWords * 8;              // 464 = 80 mod 128
+constexpr int kHalfBytes = kHalfRows * kRowPitch;        // one TMA box
+constexpr int kStageBytes = kTileRows * kRowPitch;       // 29696
+constexpr int kConsumerWarps = kStagedConsumerWarps;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kStagedThreads;
+constexpr int kGroups = 16;
+
+__device__ __forceinline__ uint32_t lds32(const unsigned char* p) {
+  return *reinterpret_cast<const uint32_t*>(p);
+}
+// 32-bit value at a shared-memory address that is 2 mod 4 (OFF2) or aligned.
+template <bool OFF2>
+__device__ __forceinline__ uint32_t ldw(const unsigned char* p) {
+  if (OFF2) return __funnelshift_r(lds32(p - 2), lds32(p + 2), 16);
+  return lds32(p);
+}
+
+// D(16x8, s32) = A(16x16, row) * B(16x8, s8, col), zero accumulate input
+__device__ __forceinline__ void mma_k16_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+__device__ __forceinline__ void mma_k16_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
+// Sign-extended byte `idx` of a word of int8 scales: prmt copies the byte and
+// replicates its sign into the three upper bytes (selector nibbles with bit 3 set).
+__device__ __forceinline__ int sext_byte(uint32_t w, int idx) {
+  const uint32_t sel = idx | ((8 | idx) << 4) | ((8 | idx) << 8) | ((8 | idx) << 12);
+  int r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0), "r"(sel));
+  return r;
+}
+
+struct ThreadCtx {
+  const unsigned char* act_t;  // this thread's activation fragment base (column, 4*tig)
+  const unsigned char* sum_t;  // this thread's digit-sum base (column, 4*tig)
+  uint32_t act_sb, act_blk, sum_plane, sum_blk;
+};
+
+// One Q6_K block of one 16-row warp tile.  pa/pb: block start of the thread's two rows.
+template <bool OFF2, int NCG>
+__device__ __forceinline__ void q6k_block(const unsigned char* pa, const unsigned char* pb, int tig,
+                                          int bl, const ThreadCtx (&tc)[NCG], const float* cs_t,
+                                          float (&o)[NCG][4]) {
+  constexpr uint32_t kNib = 0x0F0F0F0Fu, kTwo = 0x30303030u;
+  uint32_t scA[4], scB[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    scA[i] = ldw<OFF2>(pa + 192 + 4 * i);
+    scB[i] = ldw<OFF2>(pb + 192 + 4 * i);
+  }
+  int t1[NCG][4];
+#pragma unroll
+  for (int g = 0; g < NCG; ++g)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) t1[g][e] = 0;
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {      // 128-element half of the block
+#pragma unroll
+    for (int lh = 0; lh < 2; ++lh) {  // 16-element half of each 32-element run
+      const int off = 16 * lh + 4 * tig;
+      const uint32_t la0 = ldw<OFF2>(pa + 64 * h + off), la1 = ldw<OFF2>(pa + 64 * h + 32 + off);
+      const uint32_t ha = ldw<OFF2>(pa + 128 + 32 * h + off);
+      const uint32_t lb0 = ldw<OFF2>(pb + 64 * h + off), lb1 = ldw<OFF2>(pb + 64 * h + 32 + off);
+      const uint32_t hb = ldw<OFF2>(pb + 128 + 32 * h + off);
+      // 6-bit values of the four 32-element runs (low/high nibbles of ql, two bits of qh each)
+      const uint32_t qa[4] = {(la0 & kNib) | ((ha << 4) & kTwo), (la1 & kNib) | ((ha << 2) & kTwo),
+                              ((la0 >> 4) & kNib) | (ha & kTwo), ((la1 >> 4) & kNib) | ((ha >> 2) & kTwo)};
+      const uint32_t qb[4] = {(lb0 & kNib) | ((hb << 4) & kTwo), (lb1 & kNib) | ((hb << 2) & kTwo),
+                              ((lb0 >> 4) & kNib) | (hb & kTwo), ((lb1 >> 4) & kNib) | ((hb >> 2) & kTwo)};
+#pragma unroll
+      for (int pp = 0; pp < 4; ++pp) {
+        // scale group 8h + 2pp + lh: byte 2(pp&1)+lh of scale word 2h + pp/2
+        const int sa = sext_byte(scA[2 * h + (pp >> 1)], 2 * (pp & 1) + lh);
+        const int sb = sext_byte(scB[2 * h + (pp >> 1)], 2 * (pp & 1) + lh);
+#pragma unroll
+        for (int g = 0; g < NCG; ++g) {
+          const uint32_t f = lds32(tc[g].act_t + bl * tc[g].act_blk + (4 * h + pp) * tc[g].act_sb + 16 * lh);
+          int pr[4];
+          mma_k16_u8s8(pr, qa[pp], qb[pp], f);
+          t1[g][0] += sa * pr[0];
+          t1[g][1] += sa * pr[1];
+          t1[g][2] += sb * pr[2];
+          t1[g][3] += sb * pr[3];
+        }
+      }
+    }
+  }
+  // the "- 32": sum over groups of sc[g] * (digit sum of the group); k slots = groups
+  const float dA = fp16_bits_to_float(*reinterpret_cast<const unsigned short*>(pa + 208));
+  const float dB = fp16_bits_to_float(*reinterpret_cast<const unsigned short*>(pb + 208));
+  const uint32_t ma = tig == 0 ? scA[0] : tig == 1 ? scA[1] : tig == 2 ? scA[2] : scA[3];
+  const uint32_t mb = tig == 0 ? scB[0] : tig == 1 ? scB[1] : tig == 2 ? scB[2] : scB[3];
+#pragma unroll
+  for (int g = 0; g < NCG; ++g) {
+    const unsigned char* sp = tc[g].sum_t + bl * tc[g].sum_blk;
+    int r0[4], r1[4];
+    mma_k16_s8s8(r0, ma, mb, lds32(sp));
+    mma_k16_s8s8(r1, ma, mb, lds32(sp + tc[g].sum_plane));
+    const float2 c2 = *reinterpret_cast<const float2*>(cs_t + bl * kMaxCols + g * 8);
+    const float u0 = dA * static_cast<float>(t1[g][0] - 32 * (r0[0] + 128 * r1[0]));
+    const float u1 = dA * static_cast<float>(t1[g][1] - 32 * (r0[1] + 128 * r1[1]));
+    const float u2 = dB * static_cast<float>(t1[g][2] - 32 * (r0[2] + 128 * r1[2]));
+    const float u3 = dB * static_cast<float>(t1[g][3] - 32 * (r0[3] + 128 * r1[3]));
+    o[g][0] = fmaf(c2.x, u0, o[g][0]);
+    o[g][1] = fmaf(c2.y, u1, o[g][1]);
+    o[g][2] = fmaf(c2.x, u2, o[g][2]);
+    o[g][3] = fmaf(c2.y, u3, o[g][3]);
+  }
+}
+
+template <int NCG>
+__global__ void __launch_bounds__(kThreads)
+gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
+                       const __grid_constant__ CUtensorMap map_odd, const StagedParams p,
+                       const int odd_shift) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  unsigned char* act = smem + static_cast<size_t>(p.stages) * kStageBytes;
+  unsigned char* sums = act + static_cast<size_t>(p.per) * p.ncols * 256;
+  float* cs = reinterpret_cast<float*>(sums + static_cast<size_t>(p.per) * p.ncols * 2 * kGroups);
+  float* xchg = cs + static_cast<size_t>(p.per) * kMaxCols;  // [4 row groups][32 lanes][NCG*4]
+  float* outbuf = xchg + 4 * 32 * NCG * 4;                   // [64 rows][NCG*8]
+  uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
+  uint64_t* empty = full + p.stages;
+  const unsigned char* zero_page = reinterpret_cast<const unsigned char*>(empty + p.stages);  // 16 zero bytes
+  const int row0 = blockIdx.x * kTileRows;
+  const int b0 = blockIdx.y * p.per;
+  // Stages cover block pairs (2j, 2j+1) of the row; pairs that straddle the
+  // ends of this CTA's split chunk are loaded whole and half of them skipped.
+  const int pair0 = b0 >> 1;
+  const int nchunks = ((b0 + p.per + 1) >> 1) - pair0;
+  const bool producer = (tid == kConsumerThreads);
+
+  if (tid < 4) reinterpret_cast<uint32_t*>(empty + p.stages)[tid] = 0u;
+  if (producer) {
+    tma_prefetch_descriptor(&map_even);
+    tma_prefetch_descriptor(&map_odd);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kConsumerWarps / 2);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  // Window of chunk c: starts at the 16-byte boundary at or below the pair, in
+  // the byte space of each map (the odd map's base lies odd_shift bytes below
+  // the first odd row).  Coordinates are in u64 units and even: 16-byte rule.
+  auto issue_chunk = [&](int c, int slot) {
+    const uint32_t begin = static_cast<uint32_t>(pair0 + c) * kChunkBytes;
+    unsigned char* dst = smem + static_cast<size_t>(slot) * kStageBytes;
+    mbar_expect_tx(&full[slot], kStageBytes);
+    tma_load_2d(dst, &map_even, static_cast<int>((begin >> 4) * 2), row0 >> 1, &full[slot]);
+    tma_load_2d(dst + kHalfBytes, &map_odd, static_cast<int>(((begin + odd_shift) >> 4) * 2), row0 >> 1,
+                &full[slot]);
+  };
+  auto prologue = [&]() {
+    if (producer) {
+      const int first = nchunks < p.stages ? nchunks : p.stages;
+      for (int c = 0; c < first; ++c) issue_chunk(c, c);
+    }
+  };
+  if (p.pdl) {
+    // Weights are not written by the kernel ahead of us (the launcher checked):
+    // start their prefetch, then wait for that kernel's results to be visible.
+    prologue();
+    pdl_wait();
+    pdl_trigger();
+  }
+  auto deferred_prologue = [&]() {
+    if (!p.pdl) prologue();
+  };
+  if (!(p.debug & 1)) {
+    stage_activations<kGroups>(p, b0 * kBlockElems, act, sums, cs, deferred_prologue, nullptr);
+  } else {
+    deferred_prologue();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      for (int c = p.stages; c < nchunks; ++c) {
+        const int s = c % p.stages, r = c / p.stages;
+        if (!mbar_wait(&empty[s], (r & 1) ^ 1, &g_q6k_wait_timeouts)) break;
+        issue_chunk(c, s);
+      }
+    }
+    return;
+  }
+
+  const int gid = lane >> 2, tig = lane & 3;
+  const int rg = warp & 3, bx = warp >> 2;  // row group; warp set bx takes chunks c = bx (mod 2)
+  const int slot_row = rg * 16 + gid;       // row of the stage: 0..31 even rows, 32..63 odd rows
+  // tile-local index of the weight row behind stage row s: 2 * (s mod 32) + s / 32
+  const int rowA = 2 * (slot_row & 31) + (slot_row >> 5);
+  const uint32_t shift = rg >= 2 ? static_cast<uint32_t>(odd_shift) : 0u;
+  ThreadCtx tc[NCG];
+#pragma unroll
+  for (int g = 0; g < NCG; ++g) {
+    const int col = g * 8 + gid;
+    const bool valid = col < p.ncols;
+    tc[g].act_t = valid ? act + col * 32 + tig * 4 : zero_page;
+    tc[g].act_sb = valid ? p.ncols * 32 : 0;
+    tc[g].act_blk = tc[g].act_sb * 8;
+    tc[g].sum_t = valid ? sums + col * kGroups + tig * 4 : zero_page;
+    tc[g].sum_plane = valid ? p.ncols * kGroups : 0;
+    tc[g].sum_blk = tc[g].sum_plane * 2;
+  }
+  const float* cs_t = cs + 2 * tig;  // this thread's two columns of a group
+  float o[NCG][4];
+#pragma unroll
+  for (int g = 0; g < NCG; ++g)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
+
+  int slot = bx % p.stages, round = bx / p.stages;
+  for (int c = bx; c < nchunks; c += 2) {
+    if (!mbar_wait(&full[slot], round & 1, &g_q6k_wait_timeouts)) break;
+    const uint32_t lead = (static_cast<uint32_t>(pair0 + c) * kChunkBytes + shift) & 15u;
+    const unsigned char* st = smem + static_cast<size_t>(slot) * kStageBytes + slot_row * kRowPitch + lead;
+    const int bl = 2 * (pair0 + c) - b0;  // block index inside the split chunk: -1 for a straddling pair
+    if (!(p.debug & 2)) {
+      if (bl >= 0) q6k_block<false, NCG>(st, st + 8 * kRowPitch, tig, bl, tc, cs_t, o);
+      if (bl + 1 < p.per)
+        q6k_block<true, NCG>(st + kQ6KBlockBytes, st + kQ6KBlockBytes + 8 * kRowPitch, tig, bl + 1, tc, cs_t, o);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[slot]);
+    slot += 2;
+    if (slot >= p.stages) {
+      slot -= p.stages;
+      ++round;
+    }
+  }
+
+  // The two warps of a row group (even and odd chunks) add their partial sums; the
+  // digit columns of each activation row are then combined through shared memory.
+  if (bx == 1) {
+#pragma unroll
+    for (int g = 0; g < NCG; ++g)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) xchg[((rg * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  if (bx == 0) {
+#pragma unroll
+    for (int g = 0; g < NCG; ++g) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int col = g * 8 + 2 * tig + (e & 1);
+        const int rr = rowA + (e >> 1) * 16;  // stage row + 8 is weight row + 16
+        const float v = o[g][e] + xchg[((rg * 32 + lane) * NCG + g) * 4 + e];
+        if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v;
+      }
+    }
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  float* cout = p.c + blockIdx.y * p.region_stride;
+  for (int idx = tid; idx < p.m * kTileRows; idx += kConsumerThreads) {
+    const int i = idx / kTileRows, rr = idx - i * kTileRows;
+    if (row0 + rr < p.n) {
+      float v = 0.0f;
+      for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
+      cout[static_cast<size_t>(i) * p.n + row0 + rr] = v;
+    }
+  }
+}
+
+// ---- tensor-map cache: the pair of maps depends only on (base, rows, blocks per row)
+struct MapKey {
+  const void* base;
+  uint64_t n, nb;
+  bool operator==(const MapKey& o) const { return base == o.base && n == o.n && nb == o.nb; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.base) ^ (k.n * 0x9E3779B97F4A7C15ull) ^ (k.nb << 40);
+  }
+};
+struct MapPair {
+  CUtensorMap even, odd;
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, MapPair, MapKeyHash> g_maps;
+
+int q6k_tensor_maps(const void* w, uint64_t n, uint64_t nb, MapPair* out) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  const MapKey key{w, n, nb};
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return kOk;
+  }
+  const uint64_t row_bytes = nb * kQ6KBlockBytes;  // a multiple of 8
+  const uint64_t shift = row_bytes & 15u;          // 0 or 8
+  const uint64_t strides[1] = {2 * row_bytes};
+  const uint32_t box[2] = {kWindowWords, kHalfRows};
+  // Inner extents end with the row: a window that runs past it reads zeros,
+  // never bytes beyond the allocation.
+  const uint64_t dims_even[2] = {row_bytes / 8, (n + 1) / 2};
+  const uint64_t dims_odd[2] = {(row_bytes + shift) / 8, n / 2};
+  MapPair pair;
+  int rc = encode_tensor_map(&pair.even, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, w, dims_even, strides, box);
+  if (rc != kOk) return rc;
+  rc = encode_tensor_map(&pair.odd, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2,
+                         static_cast<const unsigned char*>(w) + row_bytes - shift, dims_odd, strides, box);
+  if (rc != kOk) return rc;
+  if (g_maps.size() > 65536) g_maps.clear();
+  g_maps.emplace(key, pair);
+  *out = pair;
+  return kOk;
+}
+
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  return v ? std::atoi(v) : fallback;
+}
+
+template <int NCG>
+int launch_q6k(const MapPair& maps, const void* w, StagedParams p, int odd_shift, uint64_t n,
+               uint64_t split, cudaStream_t st) {
+  const size_t per = static_cast<size_t>(p.per);
+  const size_t nchunks = per / 2 + 1;
+  const size_t fixed = per * p.ncols * (256 + 2 * kGroups) + per * kMaxCols * 4 + 4 * 32 * NCG * 4 * 4 +
+                       kTileRows * NCG * 8 * 4 + 2 * 8 * 16 + 128;
+  if (fixed + 2 * kStageBytes > static_cast<size_t>(kMaxSmem)) return kUnsupportedFeature;
+  // Ring depth: two CTAs per SM when two stages each still fit in half of
+  // shared memory, otherwise one CTA with as many stages as fit.
+  const size_t half = kMaxSmem / 2 - 1024;
+  const int fit_half = fixed < half ? static_cast<int>((half - fixed) / kStageBytes) : 0;
+  const int fit_full = static_cast<int>((kMaxSmem - fixed) / kStageBytes);
+  int want = static_cast<int>(nchunks < 8 ? nchunks : 8);
+  if (want < 2) want = 2;
+  int depth = fit_half >= 2 ? (want < fit_half ? want : fit_half) : (want < fit_full ? want : fit_full);
+  const int forced = env_int("TSR_STAGES", 0);
+  if (forced >= 2 && forced <= fit_full && forced <= 16) depth = forced;
+  p.stages = depth;
+  const size_t smem = static_cast<size_t>(depth) * kStageBytes + fixed;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(gemv_q6k_staged_kernel<NCG>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
+    attr = true;
+  }
+  const dim3 grid(static_cast<unsigned>((n + kTileRows - 1) / kTileRows), static_cast<unsigned>(split));
+  const size_t w_bytes = n * (static_cast<size_t>(p.k) / kBlockElems) * kQ6KBlockBytes;
+  p.pdl = pdl_allowed(st, w, w_bytes, p.c, split * p.region_stride * 4) ? 1 : 0;
+  launch_kernel(gemv_q6k_staged_kernel<NCG>, grid, dim3(kThreads), smem, st, p.pdl != 0, maps.even,
+                maps.odd, p, odd_shift);
+  return check_launch();
+}
+
+}  // namespace
+
+// Returns kUnsupportedFeature when the shape is outside what the staged
+// kernel covers; the caller then uses the general warp-per-row family.
+int staged_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                    uint64_t split, cudaStream_t st) {
+  const uint64_t nb = k / kBlockElems;
+  // Rows must be 8-byte aligned inside a 16-byte aligned matrix, and there must be an odd row.
+  if (m > 8 || n < 2 || nb % 4 != 0 || (reinterpret_cast<uintptr_t>(w) & 15u) ||
+      env_int("TSR_DISABLE_STAGED", 0))
+    return kUnsupportedFeature;
+  const uint64_t per = nb / split;
+  const int terms = m <= 2 ? 3 : 2;
+  const int ncols = static_cast<int>(m) * terms;
+  MapPair maps;
+  if (int rc = q6k_tensor_maps(w, n, nb, &maps)) return rc;
+  StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
+                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0,
+                 static_cast<unsigned long long>(m * n), nullptr};
+  const int odd_shift = static_cast<int>((nb * kQ6KBlockBytes) & 15u);
+  if (ncols <= 8) return launch_q6k<1>(maps, w, p, odd_shift, n, split, st);
+  return launch_q6k<2>(maps, w, p, odd_shift, n, split, st);
+}
+
+int staged_q6k_wait_timeouts(unsigned int* count) {
+  return cudaMemcpyFromSymbol(count, g_q6k_wait_timeouts, sizeof(unsigned int)) == cudaSuccess ? kOk : kDeviceError;
+}
+
+}  // namespace tsr

@@ -31,7 +31,10 @@ def bound(dtype, m, k=256):
         return 2e-5 if m <= 2 else (TIGHT if m <= 8 else FP16_WEIGHTS)
     if dtype == "fp8":
         return FP16_WEIGHTS if (m >= 2 and k % 64 == 0) else 2e-5
-    return 2e-5 if m == 1 else FP16_WEIGHTS  # q6k
+    # q6k: staged int8 kernel for m <= 8 when rows are 8-byte aligned (k/256 a multiple of 4)
+    if m <= 8 and (k // 256) % 4 == 0:
+        return 2e-5 if m <= 2 else TIGHT
+    return 2e-5 if m == 1 else FP16_WEIGHTS
 
 
 def run_named(backend, name, buffers, scalars, grid_y=1):
@@ -204,7 +207,24 @@ def test_project_batch_matches_oracle(backend, oracle, dtype, m, n, k):
     p.ProjectBatch(dtype, backend.upload(a), backend.upload(w), out, m, n, k)
     got = backend.download(out, np.float32, m * n).reshape(m, n)
     assert rel_err(got, ref) < TOL, p.last_kernel
-    assert rel_err(got, ref) < bound(dtype, m), p.last_kernel
+    assert rel_err(got, ref) < bound(dtype, m, k), p.last_kernel
+
+
+@pytest.mark.parametrize("m,n,k", [
+    # split chunks of 2, 17 (odd: stages straddle chunk ends), 4, 2, 1 blocks; one row pair; ragged tiles
+    (1, 70, 3072), (2, 1000, 17408), (3, 129, 5120), (8, 65, 4096), (1, 2, 1024), (6, 77, 7168),
+    (1, 4200, 5120), (5, 3, 2048)])
+def test_q6k_staged_projection_matches_oracle(backend, oracle, m, n, k):
+    """Shapes the staged Q6_K kernel takes (m <= 8, k / 256 a multiple of 4), through
+    ProjectBatch so that the split factor is the reference's."""
+    a = synth.activations(m, k, seed=m * 17 + n)
+    w = synth.q6k_weights(n, k, seed=n + 1)
+    ref = oracle.gemm_q6k(a, w, m, n, k)
+    p = Projector(backend)
+    out = backend.AllocateBuffer(m * n * 4)
+    p.ProjectBatch(Q6K, backend.upload(a), backend.upload(w), out, m, n, k)
+    got = backend.download(out, np.float32, m * n).reshape(m, n)
+    assert rel_err(got, ref) < bound(Q6K, m, k), p.last_kernel
 
 
 @pytest.mark.parametrize("fmt,dtype", [(0, Q4K), (1, Q6K)])
@@ -219,8 +239,8 @@ def test_vec_split_partial_regions(backend, oracle, fmt, dtype, split):
     run_named(backend, f"gemm_{dtype}_vec", [backend.upload(a), backend.upload(w), part], [m, n, k, split],
               grid_y=split)
     got = backend.download(part, np.float32, split * m * n).reshape(split, m, n)
-    # Q4_K m = 2: three-digit staged path; Q6_K: tcgen05 tile when split == 1, fp32 rows kernel otherwise
-    assert rel_err(got, part_ref) < (bound(dtype, m) if split == 1 else 2e-5)
+    # m = 2: the three-digit staged int8 path for both formats (k / 256 = 8)
+    assert rel_err(got, part_ref) < bound(dtype, m, k)
     out = backend.AllocateBuffer(m * n * 4)
     run_named(backend, "gemm_vec_reduce", [part, out], [m * n, split])
     red = backend.download(out, np.float32, m * n)
