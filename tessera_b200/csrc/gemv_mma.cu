@@ -97,10 +97,8 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   if (tr && tid == 0) tr[1] = gtime();
   if (p.pdl) {
     // Weights are not written by the kernel ahead of us (the launcher checked):
-    // start their prefetch, then wait for that kernel's results to be visible.
+    // start their prefetch; the wait for that kernel's results is inside the staging.
     prologue();
-    pdl_wait();
-    pdl_trigger();
   }
   auto deferred_prologue = [&]() {
     if (!p.pdl) prologue();
@@ -108,6 +106,10 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   if (!(p.debug & 1)) {
     stage_activations<8>(p, b0 * kBlockElems, act, sums, cs, deferred_prologue, tr);
   } else {
+    if (p.pdl) {
+      pdl_wait();
+      pdl_trigger();
+    }
     deferred_prologue();
   }
   __syncthreads();

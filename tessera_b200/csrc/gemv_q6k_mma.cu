@@ -222,10 +222,8 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
   };
   if (p.pdl) {
     // Weights are not written by the kernel ahead of us (the launcher checked):
-    // start their prefetch, then wait for that kernel's results to be visible.
+    // start their prefetch; the wait for that kernel's results is inside the staging.
     prologue();
-    pdl_wait();
-    pdl_trigger();
   }
   auto deferred_prologue = [&]() {
     if (!p.pdl) prologue();
@@ -233,6 +231,10 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
   if (!(p.debug & 1)) {
     stage_activations<kGroups>(p, b0 * kBlockElems, act, sums, cs, deferred_prologue, nullptr);
   } else {
+    if (p.pdl) {
+      pdl_wait();
+      pdl_trigger();
+    }
     deferred_prologue();
   }
   __syncthreads();

@@ -93,25 +93,26 @@ __device__ __forceinline__ float abs_max4(float m, float4 x) {
 //   sums: [block][digit plane 0..1][column][GROUPS bytes]  digit sums of every
 //         256/GROUPS-element group (GROUPS = 8: Q4_K sub-blocks, 16: Q6_K
 //         scale groups), S = D0 + 128*D1 with D0 in [-64,63]
-//   cs  : [block][kMaxCols] fp32                       column scale s_block * 254^-digit
+//   cs  : [block][kMaxCols] fp32                       column scale s_block * 256^-digit
 // Every 256-element block of an activation row has its own scale (its
 // largest magnitude / 127), so one warp stages a block on its own: lane l
-// owns elements 4l..4l+3 and 128+4l..128+4l+3, the block maximum and the
-// sub-block sums are warp shuffles, and no CTA-wide pass is needed.
-constexpr int kStageBatch = 4;  // blocks whose loads one warp keeps in flight
+// owns elements 4l..4l+3 and 128+4l..128+4l+3, the block maximum is one warp
+// reduction, and no CTA-wide pass is needed.  A warp works on kStageBatch
+// blocks at a time so that their dependent chains overlap.
+constexpr int kStageBatch = 3;
 
-template <int GROUPS>
-__device__ __forceinline__ void stage_block(const StagedParams& p, int i, int bl, float4 x0, float4 x1,
-                                            unsigned char* act, unsigned char* sums, float* cs,
-                                            int lane) {
-  float amax = abs_max4(abs_max4(0.0f, x0), x1);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-  amax = fminf(amax, 3.0e38f);
-  // x ~= unit * X with X = rint(x / unit), |X| <= 127 * 2^shift
-  const float top = p.terms == 3 ? 32768.0f : 128.0f;
-  const float unit = amax > 0.0f ? amax * (1.0f / 127.0f) / top : 1.0f;
-  const float c = 1.0f / unit;
+// Phase 1 of a block: scale, digits, column scales.
+__device__ __forceinline__ void stage_digits(const StagedParams& p, int i, int bl, float4 x0, float4 x1,
+                                             unsigned char* act, float* cs, int lane) {
+  // non-negative floats order like their bit patterns
+  const float amax = fminf(
+      __uint_as_float(__reduce_max_sync(0xFFFFFFFFu, __float_as_uint(abs_max4(abs_max4(0.0f, x0), x1)))),
+      3.0e38f);
+  // x ~= unit * X with X = rint(x / unit), |X| <= 127 * 2^shift.  The floor on
+  // the unit keeps its reciprocal finite for all-zero and denormal-sized blocks.
+  const float inv_top = p.terms == 3 ? (1.0f / (127.0f * 32768.0f)) : (1.0f / (127.0f * 128.0f));
+  const float unit = fmaxf(amax * inv_top, 1.0e-37f);
+  const float c = __frcp_rn(unit);
   uint32_t w0[3], w1[3];
   quantise4(x0, c, p.terms, w0);
   quantise4(x1, c, p.terms, w1);
@@ -119,39 +120,54 @@ __device__ __forceinline__ void stage_block(const StagedParams& p, int i, int bl
   const int sb = lane >> 3, in_sb = (lane & 7) * 4;
   unsigned char* dst0 = act + ((bl * 8 + sb) * p.ncols + i * p.terms) * 32 + in_sb;
   unsigned char* dst1 = dst0 + 4 * p.ncols * 32;
-  constexpr int kLanesPerGroup = 64 / GROUPS;  // 8 lanes per 32-element group, 4 per 16
-  const int grp = lane / kLanesPerGroup;       // group of the first quad; the second is GROUPS/2 later
-  unsigned char* sum0 = sums + ((bl * 2) * p.ncols + i * p.terms) * GROUPS + grp;
-#pragma unroll
-  for (int t = 0; t < 3; ++t) {
-    if (t < p.terms) {
-      *reinterpret_cast<uint32_t*>(dst0 + t * 32) = w0[t];
-      *reinterpret_cast<uint32_t*>(dst1 + t * 32) = w1[t];
-      int a0 = __dp4a(static_cast<int>(w0[t]), 0x01010101, 0);
-      int a1 = __dp4a(static_cast<int>(w1[t]), 0x01010101, 0);
-#pragma unroll
-      for (int o = 1; o < kLanesPerGroup; o <<= 1) {
-        a0 += __shfl_xor_sync(0xFFFFFFFFu, a0, o);
-        a1 += __shfl_xor_sync(0xFFFFFFFFu, a1, o);
-      }
-      if ((lane & (kLanesPerGroup - 1)) == 0) {
-        const int h0 = (a0 + 64) >> 7, h1 = (a1 + 64) >> 7;
-        unsigned char* sp = sum0 + t * GROUPS;
-        sp[0] = static_cast<unsigned char>(a0 - 128 * h0);
-        sp[GROUPS / 2] = static_cast<unsigned char>(a1 - 128 * h1);
-        sp[p.ncols * GROUPS] = static_cast<unsigned char>(h0);
-        sp[p.ncols * GROUPS + GROUPS / 2] = static_cast<unsigned char>(h1);
-      }
-    }
+  *reinterpret_cast<uint32_t*>(dst0) = w0[0];
+  *reinterpret_cast<uint32_t*>(dst1) = w1[0];
+  *reinterpret_cast<uint32_t*>(dst0 + 32) = w0[1];
+  *reinterpret_cast<uint32_t*>(dst1 + 32) = w1[1];
+  if (p.terms == 3) {
+    *reinterpret_cast<uint32_t*>(dst0 + 64) = w0[2];
+    *reinterpret_cast<uint32_t*>(dst1 + 64) = w1[2];
   }
   if (lane < p.terms) {
     // digit `lane` (most significant first) weighs 256^(terms-1-lane) units
-    float weight = unit;
-    for (int t = lane; t < p.terms - 1; ++t) weight *= 256.0f;
+    const float weight = unit * (lane == p.terms - 1 ? 1.0f : lane == p.terms - 2 ? 256.0f : 65536.0f);
     cs[bl * kMaxCols + i * p.terms + lane] = weight;
   }
 }
 
+// Phase 2 of a block, after the warp's digit stores are visible: lane
+// (digit t, sub-block g) of the first 8 * terms lanes sums the 32 digits of
+// its sub-block (two halves for GROUPS = 16) and stores them as two planes.
+template <int GROUPS>
+__device__ __forceinline__ void stage_sums(const StagedParams& p, int i, int bl, const unsigned char* act,
+                                           unsigned char* sums, int lane) {
+  const int t = lane >> 3, g = lane & 7;
+  if (t >= p.terms) return;
+  const int col = i * p.terms + t;
+  const uint4* src = reinterpret_cast<const uint4*>(act + ((bl * 8 + g) * p.ncols + col) * 32);
+  const uint4 u = src[0], v = src[1];
+  const int lo = __dp4a(static_cast<int>(u.x), 0x01010101, __dp4a(static_cast<int>(u.y), 0x01010101, 0)) +
+                 __dp4a(static_cast<int>(u.z), 0x01010101, __dp4a(static_cast<int>(u.w), 0x01010101, 0));
+  const int hi = __dp4a(static_cast<int>(v.x), 0x01010101, __dp4a(static_cast<int>(v.y), 0x01010101, 0)) +
+                 __dp4a(static_cast<int>(v.z), 0x01010101, __dp4a(static_cast<int>(v.w), 0x01010101, 0));
+  unsigned char* sp = sums + ((bl * 2) * p.ncols + col) * GROUPS;
+  const int plane = p.ncols * GROUPS;
+  if (GROUPS == 8) {
+    const int a = lo + hi, h = (a + 64) >> 7;
+    sp[g] = static_cast<unsigned char>(a - 128 * h);
+    sp[plane + g] = static_cast<unsigned char>(h);
+  } else {
+    const int h0 = (lo + 64) >> 7, h1 = (hi + 64) >> 7;
+    const unsigned int d0 = ((lo - 128 * h0) & 0xFF) | (((hi - 128 * h1) & 0xFF) << 8);
+    const unsigned int d1 = (h0 & 0xFF) | ((h1 & 0xFF) << 8);
+    *reinterpret_cast<unsigned short*>(sp + 2 * g) = static_cast<unsigned short>(d0);
+    *reinterpret_cast<unsigned short*>(sp + plane + 2 * g) = static_cast<unsigned short>(d1);
+  }
+}
+
+// Stages the activation blocks [k0, k0 + per*256) of all m rows.  A kernel
+// launched as a programmatic dependent (p.pdl) waits for the stream in here,
+// before its first activation load; every thread of the CTA reaches that wait.
 template <int GROUPS, typename AfterFirstLoads>
 __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0, unsigned char* act,
                                                   unsigned char* sums, float* cs,
@@ -162,6 +178,11 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
   // can wait on the descriptor fetch, which must not hold up a share of the staging.
   constexpr int kWarps = kStagedConsumerWarps;
   if (warp >= kWarps) {
+    if (p.pdl) {
+      pdl_wait();
+      pdl_trigger();
+      return;
+    }
     // Touch one activation word first: the weight prefetch of all CTAs would
     // otherwise queue ahead of everybody's activation loads in the memory system.
     const float probe = __ldg(p.a + (k0 < p.k ? k0 : 0) + lane);
@@ -169,33 +190,41 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
     return;
   }
   const int items = p.m * p.per;  // (activation row, block) pairs, row-major
-  bool first = true;
-  for (int base = warp; base < items || first; base += kWarps * kStageBatch) {
+  if (p.pdl) {
+    // Translate the activation pages while waiting (a prefetch reads no data into this SM).
+    if (lane == 0 && warp < items)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p.a + static_cast<size_t>(warp / p.per) * p.k + k0 +
+                                                     (warp % p.per) * kBlockElems));
+    pdl_wait();
+    pdl_trigger();
+  }
+  if (tr && threadIdx.x == 0) tr[5] = gtime();
+#pragma unroll 1
+  for (int base = warp; base < items; base += kWarps * kStageBatch) {
     float4 x0[kStageBatch], x1[kStageBatch];
+    int row[kStageBatch], blk[kStageBatch];
 #pragma unroll
     for (int u = 0; u < kStageBatch; ++u) {
       const int it = base + u * kWarps;
+      row[u] = it / p.per;
+      blk[u] = it - row[u] * p.per;
       x0[u] = x1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (it < items) {
-        const int i = it / p.per, bl = it - i * p.per;
-        const int k = k0 + bl * kBlockElems;
-        if (k < p.k) {
-          const float4* src = reinterpret_cast<const float4*>(p.a + static_cast<size_t>(i) * p.k + k);
-          x0[u] = __ldg(src + lane);
-          x1[u] = __ldg(src + 32 + lane);
-        }
+      if (it < items && k0 + blk[u] * kBlockElems < p.k) {
+        const float4* src = reinterpret_cast<const float4*>(p.a + static_cast<size_t>(row[u]) * p.k + k0 +
+                                                            blk[u] * kBlockElems);
+        x0[u] = __ldg(src + lane);
+        x1[u] = __ldg(src + 32 + lane);
       }
     }
-    first = false;
+    if (tr && lane == 0 && base == warp) tr[28 + warp] = gtime();
 #pragma unroll
-    for (int u = 0; u < kStageBatch; ++u) {
-      const int it = base + u * kWarps;
-      if (it < items) {
-        const int i = it / p.per, bl = it - i * p.per;
-        stage_block<GROUPS>(p, i, bl, x0[u], x1[u], act, sums, cs, lane);
-        if (tr && lane == 0 && u == 0 && base == warp) tr[40 + warp] = gtime();
-      }
-    }
+    for (int u = 0; u < kStageBatch; ++u)
+      if (base + u * kWarps < items) stage_digits(p, row[u], blk[u], x0[u], x1[u], act, cs, lane);
+    if (tr && lane == 0 && base == warp) tr[40 + warp] = gtime();
+    __syncwarp();
+#pragma unroll
+    for (int u = 0; u < kStageBatch; ++u)
+      if (base + u * kWarps < items) stage_sums<GROUPS>(p, row[u], blk[u], act, sums, lane);
   }
   if (tr && lane == 0) tr[50 + warp] = gtime();
 }
