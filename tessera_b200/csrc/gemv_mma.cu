@@ -40,31 +40,30 @@ __device__ unsigned int g_wait_timeouts = 0;
 
 namespace {
 
-constexpr int kTileRows = 64;   // rows of W per CTA
+// A CTA owns 16 * rgs rows of W (rgs = 1..4 row groups, chosen per launch) and
+// runs two sets of rgs consumer warps; the sets alternate between stages.
 constexpr int kBoxBlocks = 2;   // Q4_K blocks per box row (pitch 288 B)
-constexpr int kBoxesPerStage = 1;  // stages alternate between the two consumer warp sets
-constexpr int kChunkBlocks = kBoxBlocks * kBoxesPerStage;
+constexpr int kChunkBlocks = kBoxBlocks;
 constexpr int kRowPitch = kBoxBlocks * kQ4KBlockBytes;
-constexpr int kBoxBytes = kTileRows * kRowPitch;        // 18432
-constexpr int kStageBytes = kBoxesPerStage * kBoxBytes;  // 18432
-constexpr int kConsumerWarps = staged::kStagedConsumerWarps;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kGroupBytes = 16 * kRowPitch;  // one row group of one stage: 4608
 constexpr int kThreads = staged::kStagedThreads;
 
 using namespace staged;
 
 template <int NCG>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kConsumerWarps = 2 * p.rgs, kConsumerThreads = kConsumerWarps * 32;
+  const int kTileRows = 16 * p.rgs, kStageBytes = p.rgs * kGroupBytes;
   const int nchunks = (p.per + kChunkBlocks - 1) / kChunkBlocks;
   const int nblk_pad = nchunks * kChunkBlocks;
   unsigned char* act = smem + static_cast<size_t>(p.stages) * kStageBytes;
   unsigned char* sums = act + static_cast<size_t>(nblk_pad) * p.ncols * 256;
   float* cs = reinterpret_cast<float*>(sums + static_cast<size_t>(nblk_pad) * p.ncols * 16);  // [block][kMaxCols]
-  float* xchg = cs + static_cast<size_t>(nblk_pad) * kMaxCols;  // [4 row groups][32 lanes][NCG*4]
-  float* outbuf = xchg + 4 * 32 * NCG * 4;  // [64 rows][NCG*8]
+  float* xchg = cs + static_cast<size_t>(nblk_pad) * kMaxCols;  // [row groups][32 lanes][NCG*4]
+  float* outbuf = xchg + p.rgs * 32 * NCG * 4;  // [tile rows][NCG*8]
   uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
   uint64_t* empty = full + p.stages;
   const unsigned char* zero_page = reinterpret_cast<const unsigned char*>(empty + p.stages);  // 16 zero bytes
@@ -79,7 +78,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
     tma_prefetch_descriptor(&tmap);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], kConsumerWarps / 2);
+      mbar_init(&empty[s], p.rgs);
     }
     mbar_fence_init();
   }
@@ -129,7 +128,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   }
 
   const int gid = lane >> 2, tig = lane & 3;
-  const int rg = warp & 3, bx = warp >> 2;  // row group; warp set bx takes chunks c = bx (mod 2)
+  const int bx = warp >= p.rgs ? 1 : 0, rg = warp - bx * p.rgs;  // warp set bx takes chunks c = bx (mod 2)
   const int rowA = rg * 16 + gid;
   constexpr uint32_t kNib = 0x0F0F0F0Fu;
 
@@ -252,7 +251,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
 #pragma unroll
       for (int e = 0; e < 4; ++e) xchg[((rg * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
   if (bx == 0) {
 #pragma unroll
     for (int g = 0; g < NCG; ++g) {
@@ -265,7 +264,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
       }
     }
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
   float* cout = p.c + blockIdx.y * p.region_stride;
   for (int idx = tid; idx < p.m * kTileRows; idx += kConsumerThreads) {
     const int i = idx / kTileRows, rr = idx - i * kTileRows;
@@ -278,23 +277,25 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   if (tr && tid == 0) tr[4] = gtime();
 }
 
-// ---- tensor-map cache: a map depends only on (base, rows, blocks per row)
+// ---- tensor-map cache: a map depends only on (base, rows, blocks per row, box rows)
 struct MapKey {
   const void* base;
   uint64_t n, nb;
-  bool operator==(const MapKey& o) const { return base == o.base && n == o.n && nb == o.nb; }
+  int rgs;
+  bool operator==(const MapKey& o) const { return base == o.base && n == o.n && nb == o.nb && rgs == o.rgs; }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.base) ^ (k.n * 0x9E3779B97F4A7C15ull) ^ (k.nb << 40);
+    return std::hash<const void*>()(k.base) ^ (k.n * 0x9E3779B97F4A7C15ull) ^ (k.nb << 40) ^
+           (static_cast<size_t>(k.rgs) << 60);
   }
 };
 std::mutex g_map_mutex;
 std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 
-int q4k_tensor_map(const void* w, uint64_t n, uint64_t nb, CUtensorMap* out) {
+int q4k_tensor_map(const void* w, uint64_t n, uint64_t nb, int rgs, CUtensorMap* out) {
   std::lock_guard<std::mutex> lock(g_map_mutex);
-  const MapKey key{w, n, nb};
+  const MapKey key{w, n, nb, rgs};
   auto it = g_maps.find(key);
   if (it != g_maps.end()) {
     *out = it->second;
@@ -303,7 +304,7 @@ int q4k_tensor_map(const void* w, uint64_t n, uint64_t nb, CUtensorMap* out) {
   // (18 x u64 = one 144-byte block, blocks of a row, rows)
   const uint64_t dims[3] = {18, nb, n};
   const uint64_t strides[2] = {kQ4KBlockBytes, nb * kQ4KBlockBytes};
-  const uint32_t box[3] = {18, kBoxBlocks, kTileRows};
+  const uint32_t box[3] = {18, kBoxBlocks, static_cast<uint32_t>(16 * rgs)};
   CUtensorMap map;
   const int rc = encode_tensor_map(&map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, w, dims, strides, box);
   if (rc != kOk) return rc;
@@ -319,38 +320,46 @@ int env_int(const char* name, int fallback) {
 }
 
 template <int NCG>
-size_t fixed_smem(uint64_t nblk_pad, int ncols) {
-  return nblk_pad * ncols * (256 + 16) + nblk_pad * kMaxCols * 4 + 4 * 32 * NCG * 4 * 4 +
-         kTileRows * NCG * 8 * 4 + 2 * 8 * 16 + 128;
-}
-
-template <int NCG>
-int launch_staged(const CUtensorMap& map, const void* w, StagedParams p, uint64_t n, uint64_t split,
+int launch_staged(const void* w, StagedParams p, uint64_t n, uint64_t nb, uint64_t split,
                   uint64_t nchunks, cudaStream_t st) {
-  const size_t fixed = fixed_smem<NCG>(nchunks * kChunkBlocks, p.ncols);
-  if (fixed + 2 * kStageBytes > static_cast<size_t>(kMaxSmem)) return kUnsupportedFeature;
-  // Ring depth: two CTAs per SM when two stages each still fit in half of
-  // shared memory, otherwise one CTA with as many stages as fit.
-  const size_t half = kMaxSmem / 2 - 1024;
-  const int fit_half = fixed < half ? static_cast<int>((half - fixed) / kStageBytes) : 0;
-  const int fit_full = static_cast<int>((kMaxSmem - fixed) / kStageBytes);
-  int want = static_cast<int>(nchunks < 12 ? nchunks : 12);
-  if (want < 2) want = 2;
-  int depth = fit_half >= 2 ? (want < fit_half ? want : fit_half) : (want < fit_full ? want : fit_full);
+  const uint64_t nblk_pad = nchunks * kChunkBlocks;
+  auto fixed = [&](int rgs) -> size_t {
+    return nblk_pad * p.ncols * (256 + 16) + nblk_pad * kMaxCols * 4 + rgs * 32 * NCG * 4 * 4 +
+           16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128;
+  };
+  auto stage_bytes = [](int rgs) -> size_t { return static_cast<size_t>(rgs) * kGroupBytes; };
+  static const int regs = kernel_registers(gemv_q4k_staged_kernel<NCG>);
+  StagedPlan plan;
+  if (!plan_staged(n, split, static_cast<uint64_t>(p.per), nchunks, 12, regs, fixed, stage_bytes, &plan))
+    return kUnsupportedFeature;
+  const int forced_rgs = env_int("TSR_RGS", 0);
+  if (forced_rgs >= 1 && forced_rgs <= 4) {
+    plan.rgs = forced_rgs;
+    plan.smem = fixed(forced_rgs) + plan.stages * stage_bytes(forced_rgs);
+  }
   const int forced = env_int("TSR_STAGES", 0);
-  if (forced >= 2 && forced <= fit_full && forced <= 16) depth = forced;
-  p.stages = depth;
-  const size_t smem = static_cast<size_t>(depth) * kStageBytes + fixed;
+  if (forced >= 2 && forced <= 16 &&
+      fixed(plan.rgs) + forced * stage_bytes(plan.rgs) <= static_cast<size_t>(kMaxSmem)) {
+    plan.stages = forced;
+    plan.smem = fixed(plan.rgs) + forced * stage_bytes(plan.rgs);
+  }
+  if (plan.smem > static_cast<size_t>(kMaxSmem)) return kUnsupportedFeature;
+  p.rgs = plan.rgs;
+  p.stages = plan.stages;
+  CUtensorMap map;
+  if (int rc = q4k_tensor_map(w, n, nb, plan.rgs, &map)) return rc;
   static bool attr = false;
   if (!attr) {
     cudaFuncSetAttribute(gemv_q4k_staged_kernel<NCG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          kMaxSmem);
     attr = true;
   }
-  const dim3 grid(static_cast<unsigned>((n + kTileRows - 1) / kTileRows), static_cast<unsigned>(split));
-  const size_t w_bytes = n * (static_cast<size_t>(p.k) / kBlockElems) * kQ4KBlockBytes;
+  const uint64_t th = 16u * plan.rgs;
+  const dim3 grid(static_cast<unsigned>((n + th - 1) / th), static_cast<unsigned>(split));
+  const size_t w_bytes = n * nb * kQ4KBlockBytes;
   p.pdl = pdl_allowed(st, w, w_bytes, p.c, split * p.region_stride * 4) ? 1 : 0;
-  launch_kernel(gemv_q4k_staged_kernel<NCG>, grid, dim3(kThreads), smem, st, p.pdl != 0, map, p);
+  launch_kernel(gemv_q4k_staged_kernel<NCG>, grid, dim3((2 * plan.rgs + 1) * 32), plan.smem, st,
+                p.pdl != 0, map, p);
   return check_launch();
 }
 
@@ -395,14 +404,12 @@ int staged_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_
   const uint64_t nchunks = (per + kChunkBlocks - 1) / kChunkBlocks;
   const int terms = m <= 2 ? 3 : 2;
   const int ncols = static_cast<int>(m) * terms;
-  CUtensorMap map;
-  if (int rc = q4k_tensor_map(w, n, nb, &map)) return rc;
   StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
-                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0,
+                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0, 4,
                  static_cast<unsigned long long>(m * n),
                  reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(std::strtoull(std::getenv("TSR_TRACE_PTR") ? std::getenv("TSR_TRACE_PTR") : "0", nullptr, 10)))};
-  if (ncols <= 8) return launch_staged<1>(map, w, p, n, split, nchunks, st);
-  return launch_staged<2>(map, w, p, n, split, nchunks, st);
+  if (ncols <= 8) return launch_staged<1>(w, p, n, nb, split, nchunks, st);
+  return launch_staged<2>(w, p, n, nb, split, nchunks, st);
 }
 
 int staged_wait_timeouts(unsigned int* count) {

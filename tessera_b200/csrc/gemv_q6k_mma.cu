@@ -16,7 +16,7 @@
 //     to the 16-byte boundary.  A stage is the 464-byte window of each row
 //     that contains two blocks, starting at the 16-byte boundary below them;
 //     464 B = 80 mod 128 keeps the 4-byte fragment loads bank-conflict free.
-//     Warps 0,1 of a set own the even rows of the tile, warps 2,3 the odd rows.
+//     A warp owns 16 consecutive rows: MMA rows 0..7 are its even rows, 8..15 its odd rows.
 //   * Stages start at even block indices, so the first block of a stage is
 //     word aligned and the second one sits 2 bytes off a word: its words are
 //     assembled from two aligned loads with a funnel shift.
@@ -44,15 +44,12 @@ namespace {
 
 using namespace staged;
 
-constexpr int kTileRows = 64;
-constexpr int kHalfRows = kTileRows / 2;                 // rows per tensor map (even / odd)
+// A CTA owns 16 * rgs rows of W (rgs = 1..4 row groups, chosen per launch):
+// 8 * rgs even rows and 8 * rgs odd rows, one TMA box each per stage.
 constexpr int kChunkBytes = 2 * kQ6KBlockBytes;          // 420: two blocks per stage
 constexpr int kWindowWords = 58;                         // u64 per row window
 constexpr int kRowPitch = kWindowWords * 8;              // 464 = 80 mod 128
-constexpr int kHalfBytes = kHalfRows * kRowPitch;        // one TMA box
-constexpr int kStageBytes = kTileRows * kRowPitch;       // 29696
-constexpr int kConsumerWarps = kStagedConsumerWarps;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kGroupHalfBytes = 8 * kRowPitch;           // the even (or odd) rows of one row group: 3712
 constexpr int kThreads = kStagedThreads;
 constexpr int kGroups = 16;
 
@@ -169,17 +166,19 @@ __device__ __forceinline__ void q6k_block(const unsigned char* pa, const unsigne
 }
 
 template <int NCG>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
                        const __grid_constant__ CUtensorMap map_odd, const StagedParams p,
                        const int odd_shift) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kConsumerWarps = 2 * p.rgs, kConsumerThreads = kConsumerWarps * 32;
+  const int kTileRows = 16 * p.rgs, kHalfBytes = p.rgs * kGroupHalfBytes, kStageBytes = 2 * kHalfBytes;
   unsigned char* act = smem + static_cast<size_t>(p.stages) * kStageBytes;
   unsigned char* sums = act + static_cast<size_t>(p.per) * p.ncols * 256;
   float* cs = reinterpret_cast<float*>(sums + static_cast<size_t>(p.per) * p.ncols * 2 * kGroups);
-  float* xchg = cs + static_cast<size_t>(p.per) * kMaxCols;  // [4 row groups][32 lanes][NCG*4]
-  float* outbuf = xchg + 4 * 32 * NCG * 4;                   // [64 rows][NCG*8]
+  float* xchg = cs + static_cast<size_t>(p.per) * kMaxCols;  // [row groups][32 lanes][NCG*4]
+  float* outbuf = xchg + p.rgs * 32 * NCG * 4;               // [tile rows][NCG*8]
   uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
   uint64_t* empty = full + p.stages;
   const unsigned char* zero_page = reinterpret_cast<const unsigned char*>(empty + p.stages);  // 16 zero bytes
@@ -197,7 +196,7 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
     tma_prefetch_descriptor(&map_odd);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], kConsumerWarps / 2);
+      mbar_init(&empty[s], p.rgs);
     }
     mbar_fence_init();
   }
@@ -251,11 +250,11 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
   }
 
   const int gid = lane >> 2, tig = lane & 3;
-  const int rg = warp & 3, bx = warp >> 2;  // row group; warp set bx takes chunks c = bx (mod 2)
-  const int slot_row = rg * 16 + gid;       // row of the stage: 0..31 even rows, 32..63 odd rows
-  // tile-local index of the weight row behind stage row s: 2 * (s mod 32) + s / 32
-  const int rowA = 2 * (slot_row & 31) + (slot_row >> 5);
-  const uint32_t shift = rg >= 2 ? static_cast<uint32_t>(odd_shift) : 0u;
+  const int bx = warp >= p.rgs ? 1 : 0, rg = warp - bx * p.rgs;  // warp set bx takes chunks c = bx (mod 2)
+  // A warp covers 16 consecutive rows: the thread's MMA rows gid and gid + 8 are
+  // the even row 2e and the odd row 2e + 1 of pair e = 8 rg + gid.
+  const int pair = rg * 8 + gid;
+  const int rowA = 2 * pair;
   ThreadCtx tc[NCG];
 #pragma unroll
   for (int g = 0; g < NCG; ++g) {
@@ -278,13 +277,15 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
   int slot = bx % p.stages, round = bx / p.stages;
   for (int c = bx; c < nchunks; c += 2) {
     if (!mbar_wait(&full[slot], round & 1, &g_q6k_wait_timeouts)) break;
-    const uint32_t lead = (static_cast<uint32_t>(pair0 + c) * kChunkBytes + shift) & 15u;
-    const unsigned char* st = smem + static_cast<size_t>(slot) * kStageBytes + slot_row * kRowPitch + lead;
+    const uint32_t begin = static_cast<uint32_t>(pair0 + c) * kChunkBytes;
+    const unsigned char* stage = smem + static_cast<size_t>(slot) * kStageBytes + pair * kRowPitch;
+    const unsigned char* sa = stage + (begin & 15u);
+    const unsigned char* sb = stage + kHalfBytes + ((begin + odd_shift) & 15u);
     const int bl = 2 * (pair0 + c) - b0;  // block index inside the split chunk: -1 for a straddling pair
     if (!(p.debug & 2)) {
-      if (bl >= 0) q6k_block<false, NCG>(st, st + 8 * kRowPitch, tig, bl, tc, cs_t, o);
+      if (bl >= 0) q6k_block<false, NCG>(sa, sb, tig, bl, tc, cs_t, o);
       if (bl + 1 < p.per)
-        q6k_block<true, NCG>(st + kQ6KBlockBytes, st + kQ6KBlockBytes + 8 * kRowPitch, tig, bl + 1, tc, cs_t, o);
+        q6k_block<true, NCG>(sa + kQ6KBlockBytes, sb + kQ6KBlockBytes, tig, bl + 1, tc, cs_t, o);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[slot]);
@@ -303,20 +304,20 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
 #pragma unroll
       for (int e = 0; e < 4; ++e) xchg[((rg * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
   if (bx == 0) {
 #pragma unroll
     for (int g = 0; g < NCG; ++g) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int col = g * 8 + 2 * tig + (e & 1);
-        const int rr = rowA + (e >> 1) * 16;  // stage row + 8 is weight row + 16
+        const int rr = rowA + (e >> 1);  // MMA row + 8 is the odd row of the pair
         const float v = o[g][e] + xchg[((rg * 32 + lane) * NCG + g) * 4 + e];
         if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v;
       }
     }
   }
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
   float* cout = p.c + blockIdx.y * p.region_stride;
   for (int idx = tid; idx < p.m * kTileRows; idx += kConsumerThreads) {
     const int i = idx / kTileRows, rr = idx - i * kTileRows;
@@ -328,15 +329,17 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
   }
 }
 
-// ---- tensor-map cache: the pair of maps depends only on (base, rows, blocks per row)
+// ---- tensor-map cache: the pair of maps depends only on (base, rows, blocks per row, box rows)
 struct MapKey {
   const void* base;
   uint64_t n, nb;
-  bool operator==(const MapKey& o) const { return base == o.base && n == o.n && nb == o.nb; }
+  int rgs;
+  bool operator==(const MapKey& o) const { return base == o.base && n == o.n && nb == o.nb && rgs == o.rgs; }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.base) ^ (k.n * 0x9E3779B97F4A7C15ull) ^ (k.nb << 40);
+    return std::hash<const void*>()(k.base) ^ (k.n * 0x9E3779B97F4A7C15ull) ^ (k.nb << 40) ^
+           (static_cast<size_t>(k.rgs) << 60);
   }
 };
 struct MapPair {
@@ -345,9 +348,9 @@ struct MapPair {
 std::mutex g_map_mutex;
 std::unordered_map<MapKey, MapPair, MapKeyHash> g_maps;
 
-int q6k_tensor_maps(const void* w, uint64_t n, uint64_t nb, MapPair* out) {
+int q6k_tensor_maps(const void* w, uint64_t n, uint64_t nb, int rgs, MapPair* out) {
   std::lock_guard<std::mutex> lock(g_map_mutex);
-  const MapKey key{w, n, nb};
+  const MapKey key{w, n, nb, rgs};
   auto it = g_maps.find(key);
   if (it != g_maps.end()) {
     *out = it->second;
@@ -356,7 +359,7 @@ int q6k_tensor_maps(const void* w, uint64_t n, uint64_t nb, MapPair* out) {
   const uint64_t row_bytes = nb * kQ6KBlockBytes;  // a multiple of 8
   const uint64_t shift = row_bytes & 15u;          // 0 or 8
   const uint64_t strides[1] = {2 * row_bytes};
-  const uint32_t box[2] = {kWindowWords, kHalfRows};
+  const uint32_t box[2] = {kWindowWords, static_cast<uint32_t>(8 * rgs)};
   // Inner extents end with the row: a window that runs past it reads zeros,
   // never bytes beyond the allocation.
   const uint64_t dims_even[2] = {row_bytes / 8, (n + 1) / 2};
@@ -379,35 +382,44 @@ int env_int(const char* name, int fallback) {
 }
 
 template <int NCG>
-int launch_q6k(const MapPair& maps, const void* w, StagedParams p, int odd_shift, uint64_t n,
-               uint64_t split, cudaStream_t st) {
+int launch_q6k(const void* w, StagedParams p, int odd_shift, uint64_t n, uint64_t nb, uint64_t split,
+               cudaStream_t st) {
   const size_t per = static_cast<size_t>(p.per);
-  const size_t nchunks = per / 2 + 1;
-  const size_t fixed = per * p.ncols * (256 + 2 * kGroups) + per * kMaxCols * 4 + 4 * 32 * NCG * 4 * 4 +
-                       kTileRows * NCG * 8 * 4 + 2 * 8 * 16 + 128;
-  if (fixed + 2 * kStageBytes > static_cast<size_t>(kMaxSmem)) return kUnsupportedFeature;
-  // Ring depth: two CTAs per SM when two stages each still fit in half of
-  // shared memory, otherwise one CTA with as many stages as fit.
-  const size_t half = kMaxSmem / 2 - 1024;
-  const int fit_half = fixed < half ? static_cast<int>((half - fixed) / kStageBytes) : 0;
-  const int fit_full = static_cast<int>((kMaxSmem - fixed) / kStageBytes);
-  int want = static_cast<int>(nchunks < 8 ? nchunks : 8);
-  if (want < 2) want = 2;
-  int depth = fit_half >= 2 ? (want < fit_half ? want : fit_half) : (want < fit_full ? want : fit_full);
+  auto fixed = [&](int rgs) -> size_t {
+    return per * p.ncols * (256 + 2 * kGroups) + per * kMaxCols * 4 + rgs * 32 * NCG * 4 * 4 +
+           16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128;
+  };
+  auto stage_bytes = [](int rgs) -> size_t { return static_cast<size_t>(rgs) * 2 * kGroupHalfBytes; };
+  static const int regs = kernel_registers(gemv_q6k_staged_kernel<NCG>);
+  StagedPlan plan;
+  if (!plan_staged(n, split, per, per / 2 + 1, 8, regs, fixed, stage_bytes, &plan)) return kUnsupportedFeature;
+  const int forced_rgs = env_int("TSR_RGS", 0);
+  if (forced_rgs >= 1 && forced_rgs <= 4) {
+    plan.rgs = forced_rgs;
+    plan.smem = fixed(forced_rgs) + plan.stages * stage_bytes(forced_rgs);
+  }
   const int forced = env_int("TSR_STAGES", 0);
-  if (forced >= 2 && forced <= fit_full && forced <= 16) depth = forced;
-  p.stages = depth;
-  const size_t smem = static_cast<size_t>(depth) * kStageBytes + fixed;
+  if (forced >= 2 && forced <= 16 &&
+      fixed(plan.rgs) + forced * stage_bytes(plan.rgs) <= static_cast<size_t>(kMaxSmem)) {
+    plan.stages = forced;
+    plan.smem = fixed(plan.rgs) + forced * stage_bytes(plan.rgs);
+  }
+  if (plan.smem > static_cast<size_t>(kMaxSmem)) return kUnsupportedFeature;
+  p.rgs = plan.rgs;
+  p.stages = plan.stages;
+  MapPair maps;
+  if (int rc = q6k_tensor_maps(w, n, nb, plan.rgs, &maps)) return rc;
   static bool attr = false;
   if (!attr) {
     cudaFuncSetAttribute(gemv_q6k_staged_kernel<NCG>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     attr = true;
   }
-  const dim3 grid(static_cast<unsigned>((n + kTileRows - 1) / kTileRows), static_cast<unsigned>(split));
-  const size_t w_bytes = n * (static_cast<size_t>(p.k) / kBlockElems) * kQ6KBlockBytes;
+  const uint64_t th = 16u * plan.rgs;
+  const dim3 grid(static_cast<unsigned>((n + th - 1) / th), static_cast<unsigned>(split));
+  const size_t w_bytes = n * nb * kQ6KBlockBytes;
   p.pdl = pdl_allowed(st, w, w_bytes, p.c, split * p.region_stride * 4) ? 1 : 0;
-  launch_kernel(gemv_q6k_staged_kernel<NCG>, grid, dim3(kThreads), smem, st, p.pdl != 0, maps.even,
-                maps.odd, p, odd_shift);
+  launch_kernel(gemv_q6k_staged_kernel<NCG>, grid, dim3((2 * plan.rgs + 1) * 32), plan.smem, st,
+                p.pdl != 0, maps.even, maps.odd, p, odd_shift);
   return check_launch();
 }
 
@@ -425,14 +437,12 @@ int staged_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_
   const uint64_t per = nb / split;
   const int terms = m <= 2 ? 3 : 2;
   const int ncols = static_cast<int>(m) * terms;
-  MapPair maps;
-  if (int rc = q6k_tensor_maps(w, n, nb, &maps)) return rc;
   StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
-                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0,
+                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0, 4,
                  static_cast<unsigned long long>(m * n), nullptr};
   const int odd_shift = static_cast<int>((nb * kQ6KBlockBytes) & 15u);
-  if (ncols <= 8) return launch_q6k<1>(maps, w, p, odd_shift, n, split, st);
-  return launch_q6k<2>(maps, w, p, odd_shift, n, split, st);
+  if (ncols <= 8) return launch_q6k<1>(w, p, odd_shift, n, nb, split, st);
+  return launch_q6k<2>(w, p, odd_shift, n, nb, split, st);
 }
 
 int staged_q6k_wait_timeouts(unsigned int* count) {

@@ -13,7 +13,7 @@
 namespace tsr {
 namespace staged {
 
-constexpr int kStagedConsumerWarps = 8;
+constexpr int kStagedConsumerWarps = 8;                         // at most: two sets of four row groups
 constexpr int kStagedThreads = kStagedConsumerWarps * 32 + 32;  // plus the producer warp
 constexpr int kMaxSmem = 227 * 1024;
 constexpr int kMaxCols = 16;
@@ -28,6 +28,7 @@ struct StagedParams {
   int ncols;   // m * terms
   int debug;   // experiment switches: 1 skips activation staging, 2 skips the block math
   int pdl;     // launched as a programmatic dependent: prefetch weights, then wait for the stream
+  int rgs;     // 16-row groups per CTA (1..4): the tile has 16*rgs rows, the CTA 2*rgs consumer warps
   unsigned long long region_stride;
   unsigned long long* trace;  // optional per-CTA timeline (experiments only)
 };
@@ -99,7 +100,7 @@ __device__ __forceinline__ float abs_max4(float m, float4 x) {
 // owns elements 4l..4l+3 and 128+4l..128+4l+3, the block maximum is one warp
 // reduction, and no CTA-wide pass is needed.  A warp works on kStageBatch
 // blocks at a time so that their dependent chains overlap.
-constexpr int kStageBatch = 3;
+constexpr int kStageBatch = 4;
 
 // Phase 1 of a block: scale, digits, column scales.
 __device__ __forceinline__ void stage_digits(const StagedParams& p, int i, int bl, float4 x0, float4 x1,
@@ -176,7 +177,7 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // The producer warp only issues the weight copies: its first TMA instruction
   // can wait on the descriptor fetch, which must not hold up a share of the staging.
-  constexpr int kWarps = kStagedConsumerWarps;
+  const int kWarps = 2 * p.rgs;
   if (warp >= kWarps) {
     if (p.pdl) {
       pdl_wait();
@@ -227,6 +228,71 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
       if (base + u * kWarps < items) stage_sums<GROUPS>(p, row[u], blk[u], act, sums, lane);
   }
   if (tr && lane == 0) tr[50 + warp] = gtime();
+}
+
+// ---- host side: tile height and ring depth for one launch
+struct StagedPlan {
+  int rgs;     // row groups per CTA
+  int stages;  // ring depth
+  size_t smem;
+};
+
+// Picks the tile height (16..64 rows) and the CTAs per SM so that the grid is
+// one wave with as even a load per SM as the shape allows.  The model: a CTA
+// costs a fixed prefix (launch, activation staging, epilogue) plus time
+// proportional to its rows x blocks, SMs work through their CTAs at a fixed
+// rate, and every further wave pays the prefix again.
+//   fixed(rgs)      shared memory besides the ring, in bytes
+//   stage_bytes(rgs) one ring stage
+template <typename FixedFn, typename StageFn>
+inline bool plan_staged(uint64_t n, uint64_t split, uint64_t per, uint64_t nchunks, int max_want,
+                        int regs_per_thread, FixedFn fixed, StageFn stage_bytes, StagedPlan* out) {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    sms = v > 0 ? v : 148;
+  }
+  const double kUnitUs = 0.04, kPrefixUs = 3.4;  // per 16 rows x 1 block on a shared SM; per wave
+  double best = 1e30;
+  bool found = false;
+  for (int rgs = 4; rgs >= 1; --rgs) {
+    const uint64_t th = 16u * rgs;
+    const uint64_t ctas = ((n + th - 1) / th) * split;
+    const size_t fx = fixed(rgs), sb = stage_bytes(rgs);
+    for (int occ = 1; occ <= 4; ++occ) {
+      if (occ > 1 && occ * (2 * rgs + 1) * 32 * regs_per_thread > 65536) break;  // register file
+      const size_t avail = static_cast<size_t>(kMaxSmem) / occ;
+      const size_t reserve = occ > 1 ? 1024 : 0;  // per-CTA reservation of the hardware
+      if (avail < fx + reserve + 2 * sb) break;
+      int depth = static_cast<int>((avail - reserve - fx) / sb);
+      int want = static_cast<int>(nchunks < static_cast<uint64_t>(max_want) ? nchunks : max_want);
+      if (want < 2) want = 2;
+      if (depth > want) depth = want;
+      const uint64_t slots = static_cast<uint64_t>(sms) * occ;
+      const uint64_t waves = (ctas + slots - 1) / slots;
+      const uint64_t per_sm = (ctas + sms - 1) / sms;
+      double cost = per_sm * rgs * per * kUnitUs + waves * kPrefixUs;
+      if (depth < 3 && nchunks > 2) cost *= 1.1;  // a shallow ring stalls on HBM latency
+      if (cost < best - 1e-9) {
+        best = cost;
+        out->rgs = rgs;
+        out->stages = depth;
+        out->smem = fx + static_cast<size_t>(depth) * sb;
+        found = true;
+      }
+    }
+  }
+  return found;
+}
+
+// Registers per thread of a kernel, rounded up to the allocation unit.
+template <typename Kernel>
+inline int kernel_registers(Kernel kernel) {
+  cudaFuncAttributes attr{};
+  if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess || attr.numRegs <= 0) return 128;
+  return (attr.numRegs + 7) & ~7;
 }
 
 }  // namespace staged
