@@ -340,10 +340,11 @@ int tsr_synchronize(tsr_context* ctx) {
   const cudaError_t e = cudaStreamSynchronize(ctx->stream);
   if (e != cudaSuccess) return ctx->fail(e, "cudaStreamSynchronize");
   // A staged kernel whose bounded wait ran out has left wrong results behind.
-  unsigned int timeouts = 0, umma = 0, q6k = 0;
+  unsigned int timeouts = 0, umma = 0, q6k = 0, f16 = 0;
   tsr::umma_wait_timeouts(&umma);
   tsr::staged_q6k_wait_timeouts(&q6k);
-  if (tsr::staged_wait_timeouts(&timeouts) == tsr::kOk && (timeouts += umma + q6k) != ctx->seen_timeouts) {
+  tsr::staged_f16_wait_timeouts(&f16);
+  if (tsr::staged_wait_timeouts(&timeouts) == tsr::kOk && (timeouts += umma + q6k + f16) != ctx->seen_timeouts) {
     ctx->seen_timeouts = timeouts;
     ctx->error = "a staged kernel gave up waiting for a TMA copy";
     return tsr::kDeviceError;

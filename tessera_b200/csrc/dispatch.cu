@@ -62,6 +62,8 @@ int tsr_gemm_mxfp4(const float* a, const void* w, float* c, uint64_t m, uint64_t
   if (!a || !w || !c || !fits_int(m) || !fits_int(n) || !fits_int(k) || k % 32 != 0)
     return kInvalidArgument;
   if (!aligned16(a) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
+  const int rc = staged_gemm_mxfp4(a, w, c, m, n, k, static_cast<cudaStream_t>(stream));
+  if (rc != kUnsupportedFeature) return rc;
   if (m >= 2) {
     const int rt = umma_gemm(2, a, w, nullptr, c, m, n, k, static_cast<cudaStream_t>(stream));
     if (rt != kUnsupportedFeature) return rt;
@@ -73,6 +75,8 @@ int tsr_gemm_fp8(const float* a, const void* w, const float* s, float* c, uint64
                  uint64_t k, void* stream) {
   if (!a || !w || !s || !c || !fits_int(m) || !fits_int(n) || !fits_int(k)) return kInvalidArgument;
   if (!aligned16(a) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
+  const int rc = staged_gemm_fp8(a, w, s, c, m, n, k, static_cast<cudaStream_t>(stream));
+  if (rc != kUnsupportedFeature) return rc;
   if (m >= 2 && k % 64 == 0) {
     const int rt = umma_gemm(3, a, w, s, c, m, n, k, static_cast<cudaStream_t>(stream));
     if (rt != kUnsupportedFeature) return rt;

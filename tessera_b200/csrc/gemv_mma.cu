@@ -117,8 +117,9 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   if (warp == kConsumerWarps) {
     if (lane == 0) {
       for (int c = p.stages; c < nchunks; ++c) {
-        const int s = c % p.stages, r = c / p.stages;
-        if (!mbar_wait(&empty[s], (r & 1) ^ 1, &g_wait_timeouts)) break;
+        const RingUse use = ring_use(c, p.stages);
+        const int s = use.slot;
+        if (!mbar_wait(&empty[s], (use.round & 1) ^ 1, &g_wait_timeouts)) break;
         unsigned char* dst = smem + static_cast<size_t>(s) * kStageBytes;
         mbar_expect_tx(&full[s], kStageBytes);
         tma_load_3d(dst, &tmap, 0, b0 + c * kChunkBlocks, row0, &full[s]);
@@ -159,10 +160,11 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
 
-  int slot = bx % p.stages, round = bx / p.stages;
   for (int c = bx; c < nchunks; c += 2) {
     if (tr && tid == 0 && c < 24) tr[8 + 2 * c] = gtime();
-    if (!mbar_wait(&full[slot], round & 1, &g_wait_timeouts)) break;
+    const RingUse use = ring_use(c, p.stages);
+    const int slot = use.slot;
+    if (!mbar_wait(&full[slot], use.round & 1, &g_wait_timeouts)) break;
     if (tr && tid == 0 && c < 24) tr[9 + 2 * c] = gtime();
     const unsigned char* st = smem + static_cast<size_t>(slot) * kStageBytes + row_off;
     const int blocks_here = (p.debug & 2) ? 0 : min(kBoxBlocks, p.per - c * kChunkBlocks);
@@ -235,11 +237,6 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[slot]);
-    slot += 2;
-    if (slot >= p.stages) {
-      slot -= p.stages;
-      ++round;
-    }
   }
 
   if (tr && tid == 0) tr[3] = gtime();
@@ -366,7 +363,8 @@ int launch_staged(const void* w, StagedParams p, uint64_t n, uint64_t nb, uint64
 }  // namespace
 
 int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType type, uint32_t rank, const void* base,
-                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                      bool swizzle128) {
   using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -390,7 +388,8 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType type, uint32_t rank,
     if (i + 1 < rank) s[i] = strides_bytes[i];
   }
   const CUresult r = encode(map, type, rank, const_cast<void*>(base), d, s, b, e,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? kOk : kInvalidArgument;
 }

@@ -241,8 +241,9 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
   if (warp == kConsumerWarps) {
     if (lane == 0) {
       for (int c = p.stages; c < nchunks; ++c) {
-        const int s = c % p.stages, r = c / p.stages;
-        if (!mbar_wait(&empty[s], (r & 1) ^ 1, &g_q6k_wait_timeouts)) break;
+        const RingUse use = ring_use(c, p.stages);
+        const int s = use.slot;
+        if (!mbar_wait(&empty[s], (use.round & 1) ^ 1, &g_q6k_wait_timeouts)) break;
         issue_chunk(c, s);
       }
     }
@@ -274,9 +275,10 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
 
-  int slot = bx % p.stages, round = bx / p.stages;
   for (int c = bx; c < nchunks; c += 2) {
-    if (!mbar_wait(&full[slot], round & 1, &g_q6k_wait_timeouts)) break;
+    const RingUse use = ring_use(c, p.stages);
+    const int slot = use.slot;
+    if (!mbar_wait(&full[slot], use.round & 1, &g_q6k_wait_timeouts)) break;
     const uint32_t begin = static_cast<uint32_t>(pair0 + c) * kChunkBytes;
     const unsigned char* stage = smem + static_cast<size_t>(slot) * kStageBytes + pair * kRowPitch;
     const unsigned char* sa = stage + (begin & 15u);
@@ -289,11 +291,6 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[slot]);
-    slot += 2;
-    if (slot >= p.stages) {
-      slot -= p.stages;
-      ++round;
-    }
   }
 
   // The two warps of a row group (even and odd chunks) add their partial sums; the

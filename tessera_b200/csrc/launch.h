@@ -68,15 +68,20 @@ int rows_gemm_fp8(const float* a, const void* w, const float* s, float* c, uint6
 int rows_gemm_w4a8(const void* a8, const void* w, const float* as, const void* wref, float* c,
                    uint64_t m, uint64_t n, uint64_t k, uint64_t split, cudaStream_t st);
 
-// Staged tensor-pipe kernels (gemv_mma.cu, gemv_q6k_mma.cu).  kUnsupportedFeature means the
+// Staged tensor-pipe kernels (gemv_mma.cu, gemv_q6k_mma.cu, gemv_f16_mma.cu).  kUnsupportedFeature means the
 // shape is outside their range and the caller uses the general family.
 int staged_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
                     uint64_t split, cudaStream_t st);
 int staged_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
                     uint64_t split, cudaStream_t st);
+int staged_gemm_mxfp4(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                      cudaStream_t st);
+int staged_gemm_fp8(const float* a, const void* w, const float* scale, float* c, uint64_t m, uint64_t n,
+                    uint64_t k, cudaStream_t st);
 // Number of bounded device waits that gave up since the library was loaded.
 int staged_wait_timeouts(unsigned int* count);
 int staged_q6k_wait_timeouts(unsigned int* count);
+int staged_f16_wait_timeouts(unsigned int* count);
 
 // tcgen05/TMEM tile for small batches (gemm_umma.cu).  fmt: 0 Q4_K, 1 Q6_K,
 // 2 MXFP4, 3 FP8.  kUnsupportedFeature when the shape is outside its range.

@@ -54,6 +54,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
   return false;
 }
 
+// Ring slot and use count of chunk c when two consumer groups take the even
+// and the odd chunks.  Each group owns its own slots (group 0 the even ones,
+// group 1 the odd ones; with an odd ring group 0 has one more), so every slot
+// is waited on by one group, in order.  A parity wait only tells the phase
+// before from the phase after: if a slot alternated between the groups, a
+// group that runs ahead would wait on a phase the barrier has not reached and
+// the wait would return at once.
+struct RingUse {
+  int slot, round;
+};
+__device__ __forceinline__ RingUse ring_use(int c, int stages) {
+  const int group = c & 1, j = c >> 1;
+  const int owned = (stages + 1 - group) >> 1;
+  const int idx = j % owned;
+  return {group + 2 * idx, j / owned};
+}
+
 // Tiled TMA load of one 3-D box into shared memory; completion is counted in
 // bytes on `bar`.  The innermost coordinate must keep the 16-byte rule
 // (c0 * element size a multiple of 16); every caller passes c0 = 0.
@@ -113,7 +130,10 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 
 // Host side: encode a tiled tensor map through the driver entry point
 // (resolved at run time; the library does not link libcuda).
+// swizzle128: shared-memory rows of 128 bytes with the 16-byte pieces of row r
+// stored at piece index ^ (r mod 8) (CU_TENSOR_MAP_SWIZZLE_128B).
 int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType type, uint32_t rank, const void* base,
-                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box);
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                      bool swizzle128 = false);
 
 }  // namespace tsr

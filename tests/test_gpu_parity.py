@@ -30,6 +30,8 @@ def bound(dtype, m, k=256):
     if dtype == "q4k":
         return 2e-5 if m <= 2 else (TIGHT if m <= 8 else FP16_WEIGHTS)
     if dtype == "fp8":
+        if m <= 8 and k % 256 == 0:
+            return 2e-5  # staged kernel: two binary16 terms per activation
         return FP16_WEIGHTS if (m >= 2 and k % 64 == 0) else 2e-5
     # q6k: staged int8 kernel for m <= 8 when rows are 8-byte aligned (k/256 a multiple of 4)
     if m <= 8 and (k // 256) % 4 == 0:
@@ -256,6 +258,27 @@ def test_fp8_projection_matches_oracle(backend, oracle, m, n, k):
     out = backend.AllocateBuffer(m * n * 4)
     run_named(backend, "gemm_fp8", [backend.upload(a), backend.upload(w), backend.upload(s), out], [m, n, k])
     assert rel_err(backend.download(out, np.float32, m * n).reshape(m, n), ref) < bound("fp8", m, k)
+
+
+@pytest.mark.parametrize("m,n,k", [
+    # one phase; ragged tiles; several activation phases (m = 8, and k = 17408); tiny n
+    (1, 70, 5120), (4, 129, 1024), (8, 65, 5120), (2, 17, 17408), (1, 4200, 512), (5, 3, 2048)])
+@pytest.mark.parametrize("dtype", ["mxfp4", "fp8"])
+def test_f16_staged_projection_matches_oracle(backend, oracle, dtype, m, n, k):
+    """Shapes the staged binary16 kernel takes (m <= 8, whole 512- or 256-element chunks)."""
+    a = synth.activations(m, k, seed=m * 19 + n)
+    out = backend.AllocateBuffer(m * n * 4)
+    if dtype == "mxfp4":
+        w = synth.mxfp4_weights(n, k, seed=n + 2)
+        ref = oracle.gemm_mxfp4(a, w, m, n, k)
+        run_named(backend, "gemm_mxfp4", [backend.upload(a), backend.upload(w), out], [m, n, k])
+    else:
+        w, s = synth.fp8_weights(n, k, seed=n + 2)
+        ref = oracle.gemm_fp8(a, w, s, m, n, k)
+        run_named(backend, "gemm_fp8", [backend.upload(a), backend.upload(w), backend.upload(s), out], [m, n, k])
+    got = backend.download(out, np.float32, m * n).reshape(m, n)
+    # two binary16 terms per activation: 2^-22 of the block maximum
+    assert rel_err(got, ref) < 2e-5
 
 
 @pytest.mark.parametrize("m", [1, 4, 16])
