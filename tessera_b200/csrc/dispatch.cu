@@ -22,6 +22,22 @@ bool fits_int(uint64_t v) { return v > 0 && v <= 0x7FFFFFFFull; }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Batches of 9..32 activation rows go through the staged GEMV eight rows at a
+// time (the weights stream once per eight rows); above that the tcgen05 tile
+// amortises its dequantisation better.  `launch(i0, rows)` runs rows
+// [i0, i0 + rows) and returns a status.
+constexpr uint64_t kStagedRows = 8, kStagedBatchMax = 32;
+template <typename Launch>
+int staged_in_chunks(uint64_t m, Launch launch) {
+  if (m > kStagedBatchMax) return kUnsupportedFeature;
+  for (uint64_t i0 = 0; i0 < m; i0 += kStagedRows) {
+    const uint64_t rows = m - i0 < kStagedRows ? m - i0 : kStagedRows;
+    const int rc = launch(i0, rows);
+    if (rc != kOk) return rc;  // kUnsupportedFeature can only come from the first chunk
+  }
+  return kOk;
+}
+
 }  // namespace
 
 extern "C" {
@@ -32,7 +48,12 @@ int tsr_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n
       split == 0 || (k / 256) % split != 0 || split > 65535)
     return kInvalidArgument;
   if (!aligned16(a) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
-  const int rc = staged_gemm_q4k(a, w, c, m, n, k, split, static_cast<cudaStream_t>(stream));
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rc = (m > kStagedRows && split == 1)
+                     ? staged_in_chunks(m, [&](uint64_t i0, uint64_t rows) {
+                         return staged_gemm_q4k(a + i0 * k, w, c + i0 * n, rows, n, k, 1, st);
+                       })
+                     : staged_gemm_q4k(a, w, c, m, n, k, split, st);
   if (rc != kUnsupportedFeature) return rc;
   if (m >= 9 && split == 1) {
     const int rt = umma_gemm(0, a, w, nullptr, c, m, n, k, static_cast<cudaStream_t>(stream));
@@ -48,7 +69,12 @@ int tsr_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_t n
     return kInvalidArgument;
   if (!aligned16(a) || (reinterpret_cast<uintptr_t>(w) & 1u) || !aligned16(c))
     return kInvalidArgument;
-  const int rc = staged_gemm_q6k(a, w, c, m, n, k, split, static_cast<cudaStream_t>(stream));
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rc = (m > kStagedRows && split == 1)
+                     ? staged_in_chunks(m, [&](uint64_t i0, uint64_t rows) {
+                         return staged_gemm_q6k(a + i0 * k, w, c + i0 * n, rows, n, k, 1, st);
+                       })
+                     : staged_gemm_q6k(a, w, c, m, n, k, split, st);
   if (rc != kUnsupportedFeature) return rc;
   if (m >= 2 && split == 1) {
     const int rt = umma_gemm(1, a, w, nullptr, c, m, n, k, static_cast<cudaStream_t>(stream));
@@ -62,7 +88,10 @@ int tsr_gemm_mxfp4(const float* a, const void* w, float* c, uint64_t m, uint64_t
   if (!a || !w || !c || !fits_int(m) || !fits_int(n) || !fits_int(k) || k % 32 != 0)
     return kInvalidArgument;
   if (!aligned16(a) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
-  const int rc = staged_gemm_mxfp4(a, w, c, m, n, k, static_cast<cudaStream_t>(stream));
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rc = m > kStagedRows ? staged_in_chunks(m, [&](uint64_t i0, uint64_t rows) {
+    return staged_gemm_mxfp4(a + i0 * k, w, c + i0 * n, rows, n, k, st);
+  }) : staged_gemm_mxfp4(a, w, c, m, n, k, st);
   if (rc != kUnsupportedFeature) return rc;
   if (m >= 2) {
     const int rt = umma_gemm(2, a, w, nullptr, c, m, n, k, static_cast<cudaStream_t>(stream));
@@ -75,7 +104,10 @@ int tsr_gemm_fp8(const float* a, const void* w, const float* s, float* c, uint64
                  uint64_t k, void* stream) {
   if (!a || !w || !s || !c || !fits_int(m) || !fits_int(n) || !fits_int(k)) return kInvalidArgument;
   if (!aligned16(a) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
-  const int rc = staged_gemm_fp8(a, w, s, c, m, n, k, static_cast<cudaStream_t>(stream));
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int rc = m > kStagedRows ? staged_in_chunks(m, [&](uint64_t i0, uint64_t rows) {
+    return staged_gemm_fp8(a + i0 * k, w, s, c + i0 * n, rows, n, k, st);
+  }) : staged_gemm_fp8(a, w, s, c, m, n, k, st);
   if (rc != kUnsupportedFeature) return rc;
   if (m >= 2 && k % 64 == 0) {
     const int rt = umma_gemm(3, a, w, s, c, m, n, k, static_cast<cudaStream_t>(stream));
