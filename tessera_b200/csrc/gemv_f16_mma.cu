@@ -273,6 +273,9 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
 
   bool failed = false;
   int c = bx;
+  // this set's ring slots bx, bx + 2, ... in turn (see ring_use)
+  const int owned = (p.stages + 1 - bx) >> 1;
+  int ring_idx = 0, ring_round = 0;
   for (int first = 0; first < p.nblocks; first += p.pblocks) {
     const int nblk = min(p.pblocks, p.nblocks - first);
     if (first > 0) asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
@@ -281,9 +284,8 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
     const int chunk_end = (first + nblk + kChunkBlocks - 1) / kChunkBlocks;
     for (; c < chunk_end; c += 2) {
       if (failed) continue;
-      const RingUse use = ring_use(c, p.stages);
-      const int slot = use.slot;
-      if (!mbar_wait(&full[slot], use.round & 1, &g_f16_wait_timeouts)) {
+      const int slot = bx + 2 * ring_idx;
+      if (!mbar_wait(&full[slot], ring_round & 1, &g_f16_wait_timeouts)) {
         failed = true;
         continue;
       }
@@ -362,6 +364,10 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[slot]);
+      if (++ring_idx == owned) {
+        ring_idx = 0;
+        ++ring_round;
+      }
     }
   }
 

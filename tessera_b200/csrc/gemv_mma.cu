@@ -160,11 +160,13 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
 
+  // this set's ring slots bx, bx + 2, ... in turn (see ring_use)
+  const int owned = (p.stages + 1 - bx) >> 1;
+  int ring_idx = 0, ring_round = 0;
   for (int c = bx; c < nchunks; c += 2) {
     if (tr && tid == 0 && c < 24) tr[8 + 2 * c] = gtime();
-    const RingUse use = ring_use(c, p.stages);
-    const int slot = use.slot;
-    if (!mbar_wait(&full[slot], use.round & 1, &g_wait_timeouts)) break;
+    const int slot = bx + 2 * ring_idx;
+    if (!mbar_wait(&full[slot], ring_round & 1, &g_wait_timeouts)) break;
     if (tr && tid == 0 && c < 24) tr[9 + 2 * c] = gtime();
     const unsigned char* st = smem + static_cast<size_t>(slot) * kStageBytes + row_off;
     const int blocks_here = (p.debug & 2) ? 0 : min(kBoxBlocks, p.per - c * kChunkBlocks);
@@ -237,6 +239,10 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[slot]);
+    if (++ring_idx == owned) {
+      ring_idx = 0;
+      ++ring_round;
+    }
   }
 
   if (tr && tid == 0) tr[3] = gtime();

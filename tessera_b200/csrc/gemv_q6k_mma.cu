@@ -275,10 +275,12 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
 
+  // this set's ring slots bx, bx + 2, ... in turn (see ring_use)
+  const int owned = (p.stages + 1 - bx) >> 1;
+  int ring_idx = 0, ring_round = 0;
   for (int c = bx; c < nchunks; c += 2) {
-    const RingUse use = ring_use(c, p.stages);
-    const int slot = use.slot;
-    if (!mbar_wait(&full[slot], use.round & 1, &g_q6k_wait_timeouts)) break;
+    const int slot = bx + 2 * ring_idx;
+    if (!mbar_wait(&full[slot], ring_round & 1, &g_q6k_wait_timeouts)) break;
     const uint32_t begin = static_cast<uint32_t>(pair0 + c) * kChunkBytes;
     const unsigned char* stage = smem + static_cast<size_t>(slot) * kStageBytes + pair * kRowPitch;
     const unsigned char* sa = stage + (begin & 15u);
@@ -291,6 +293,10 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty[slot]);
+    if (++ring_idx == owned) {
+      ring_idx = 0;
+      ++ring_round;
+    }
   }
 
   // The two warps of a row group (even and odd chunks) add their partial sums; the
