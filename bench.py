@@ -201,6 +201,78 @@ class CudaArrayView:
         self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 2}
 
 
+def qgemv_table(stream, hbm_peak):
+    """Device time per launch of the single-projection shapes the metric names: the Q4_K
+    decode GEMV (17408 x 5120, m = 1) and the MXFP4 / FP8 projections at m = 1, 4, 16 over
+    5120 x 5120, 17408 x 5120 and 5120 x 17408.  Each case rotates through enough private
+    weight copies to exceed L2 three times over, runs from a CUDA graph and is timed with
+    events on the launching stream; bytes are the algorithmic ones (weights once,
+    activations in, outputs out)."""
+    import ctypes
+    import torch
+    from tessera_b200 import capi
+    lib = capi.load_library()
+    st = ctypes.c_void_p(stream.cuda_stream)
+    shapes = [(17408, 5120), (5120, 5120), (5120, 17408)]
+    cases = [("q4k", 1, 17408, 5120)]
+    cases += [(f, m, n, k) for f in ("mxfp4", "fp8") for (n, k) in shapes for m in (1, 4, 16)]
+    rows, cache = [], {}
+    for fmt, m, n, k in cases:
+        if (fmt, n, k) not in cache:
+            cache.clear()
+            torch.cuda.empty_cache()
+            scale = None
+            if fmt == "q4k":
+                host = synth.q4k_weights(n, k, seed=11)
+            elif fmt == "mxfp4":
+                host = synth.mxfp4_weights(n, k, seed=11)
+            else:
+                host, scale = synth.fp8_weights(n, k, seed=11)
+                scale = torch.from_numpy(scale).cuda()
+            first = torch.from_numpy(host).cuda()
+            copies = max(3, int(np.ceil(400e6 / host.size)))
+            cache[(fmt, n, k)] = ([first] + [first.clone() for _ in range(copies - 1)], scale, host.size)
+        ws, scale, wbytes = cache[(fmt, n, k)]
+        a = torch.from_numpy(synth.activations(m, k, seed=12)).cuda()
+        c = torch.empty(m * n, dtype=torch.float32, device="cuda")
+
+        def launch(i):
+            w = ctypes.c_void_p(ws[i % len(ws)].data_ptr())
+            pa, pc = ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(c.data_ptr())
+            if fmt == "q4k":
+                rc = lib.tsr_gemm_q4k(pa, w, pc, m, n, k, 1, st)
+            elif fmt == "mxfp4":
+                rc = lib.tsr_gemm_mxfp4(pa, w, pc, m, n, k, st)
+            else:
+                rc = lib.tsr_gemm_fp8(pa, w, ctypes.c_void_p(scale.data_ptr()), pc, m, n, k, st)
+            if rc != 0:
+                raise RuntimeError(f"{fmt} projection returned status {rc}")
+        per_graph = 2 * len(ws)
+        with torch.cuda.stream(stream):
+            launch(0)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+                for i in range(per_graph):
+                    launch(i)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (reps * per_graph)
+        gbs = (wbytes + m * k * 4 + m * n * 4) / us / 1e3
+        rows.append({"fmt": fmt, "m": m, "n": n, "k": k, "us": round(us, 2), "gbs": round(gbs, 1),
+                     "frac": round(gbs / hbm_peak, 3)})
+    cache.clear()
+    return rows
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -364,6 +436,11 @@ def gpu_arm(args):
         "roofline": roofline, "clocks": clocks.summary(),
     }
     if rank == 0 and world == 1:
+        # free the step's weights first: the table below wants a few hundred MB per case
+        for _, _, _, buf in weights:
+            buf.release()
+        weights.clear()
+        line["qgemv"] = qgemv_table(stream, peaks["hbm_gbs"])
         from oracle.oracle import Oracle
         threads = os.cpu_count() or 1
         v, sample = run_cpu_sample(Oracle(), threads, 12.0)
