@@ -25,6 +25,7 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 #include <unordered_map>
@@ -60,6 +61,8 @@ struct F16Params {
   int ncols;    // 2 * m
   int pdl;      // launched as a programmatic dependent
   int rgs;      // 16-row groups per CTA
+  int ksplit;   // CTAs of a cluster that share a row tile, each with `cper` consecutive chunks
+  int cper;
 };
 
 template <int FMT>
@@ -105,6 +108,19 @@ __device__ __forceinline__ void cvt_e4m3x4(uint32_t w, uint32_t& lo, uint32_t& h
 __device__ __forceinline__ float e8m0_byte(uint32_t w, int idx) {
   const uint32_t e = __byte_perm(w, 0, 0x4440 + idx);
   return fmaxf(__uint_as_float(e << 23), __uint_as_float(0x00400000u));
+}
+
+// Thread-block cluster barrier (all threads of all CTAs of the cluster) and a
+// load from the shared memory of CTA `rank` of the cluster.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
@@ -181,7 +197,13 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
   const int kConsumerWarps = 2 * p.rgs, kConsumerThreads = kConsumerWarps * 32;
   const int kTileRows = 16 * p.rgs, kStageBytes = p.rgs * kGroupStageBytes;
   const int kScaleBytes = FMT == kFmtMxfp4 ? p.rgs * kGroupScaleBytes : 0;
-  const int nchunks = (p.nblocks + kChunkBlocks - 1) / kChunkBlocks;
+  // K split across the CTAs of a cluster: rank r takes chunks [r * cper, (r + 1) * cper)
+  const int krank = p.ksplit > 1 ? static_cast<int>(blockIdx.x % p.ksplit) : 0;
+  const int c_begin = krank * p.cper;
+  const int nchunks_all = (p.nblocks + kChunkBlocks - 1) / kChunkBlocks;
+  const int nchunks = max(0, min(p.cper, nchunks_all - c_begin));
+  const int kb0 = c_begin * kChunkBlocks;  // first activation block of this CTA
+  const int nblocks = max(0, min(p.nblocks - kb0, nchunks * kChunkBlocks));
   unsigned char* scales = smem + static_cast<size_t>(p.stages) * kStageBytes;
   unsigned char* act = scales + static_cast<size_t>(p.stages) * kScaleBytes;
   float* cs = reinterpret_cast<float*>(act + static_cast<size_t>(p.pblocks) * kBlockElems * p.ncols * 2);
@@ -190,7 +212,7 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
   uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
   uint64_t* empty = full + p.stages;
   const unsigned char* zero_page = reinterpret_cast<const unsigned char*>(empty + p.stages);  // 16 zero bytes
-  const int row0 = blockIdx.x * kTileRows;
+  const int row0 = static_cast<int>(blockIdx.x / p.ksplit) * kTileRows;
   const bool producer = (tid == kConsumerThreads);
 
   if (tid < 4) reinterpret_cast<uint32_t*>(empty + p.stages)[tid] = 0u;
@@ -208,9 +230,9 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
   auto issue_chunk = [&](int c, int slot) {
     mbar_expect_tx(&full[slot], kStageBytes + kScaleBytes);
     // (128 bytes of a row, rows, 128-byte segments of the row): two segments per stage
-    tma_load_3d(smem + static_cast<size_t>(slot) * kStageBytes, &wmap, 0, row0, 2 * c, &full[slot]);
+    tma_load_3d(smem + static_cast<size_t>(slot) * kStageBytes, &wmap, 0, row0, 2 * (c_begin + c), &full[slot]);
     if (FMT == kFmtMxfp4)
-      tma_load_2d(scales + static_cast<size_t>(slot) * kScaleBytes, &smap, 16 * c, row0, &full[slot]);
+      tma_load_2d(scales + static_cast<size_t>(slot) * kScaleBytes, &smap, 16 * (c_begin + c), row0, &full[slot]);
   };
   auto prologue = [&]() {
     if (producer) {
@@ -242,6 +264,10 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
         if (!mbar_wait(&empty[s], (use.round & 1) ^ 1, &g_f16_wait_timeouts)) break;
         issue_chunk(c, s);
       }
+    }
+    if (p.ksplit > 1) {  // the two cluster barriers of the epilogue
+      cluster_sync();
+      cluster_sync();
     }
     return;
   }
@@ -276,10 +302,10 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
   // this set's ring slots bx, bx + 2, ... in turn (see ring_use)
   const int owned = (p.stages + 1 - bx) >> 1;
   int ring_idx = 0, ring_round = 0;
-  for (int first = 0; first < p.nblocks; first += p.pblocks) {
-    const int nblk = min(p.pblocks, p.nblocks - first);
+  for (int first = 0; first < nblocks; first += p.pblocks) {
+    const int nblk = min(p.pblocks, nblocks - first);
     if (first > 0) asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
-    stage_f16<G>(p, first, nblk, act, cs, warp, lane, kConsumerWarps);
+    stage_f16<G>(p, kb0 + first, nblk, act, cs, warp, lane, kConsumerWarps);
     asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
     const int chunk_end = (first + nblk + kChunkBlocks - 1) / kChunkBlocks;
     for (; c < chunk_end; c += 2) {
@@ -393,14 +419,22 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
     }
   }
   asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
-  for (int idx = tid; idx < p.m * kTileRows; idx += kConsumerThreads) {
-    const int i = idx / kTileRows, rr = idx - i * kTileRows;
-    if (row0 + rr < p.n) {
-      float v = outbuf[rr * (NCG * 8) + 2 * i + 1] + outbuf[rr * (NCG * 8) + 2 * i];
-      if (FMT == kFmtFp8) v *= __ldg(p.row_scale + row0 + rr);
-      p.c[static_cast<size_t>(i) * p.n + row0 + rr] = v;
+  // With a K split the CTAs of the cluster hold partial sums of the same tile:
+  // rank 0 adds them in rank order out of its peers' shared memory.
+  if (p.ksplit > 1) cluster_sync();  // every CTA's outbuf is complete
+  if (krank == 0) {
+    for (int idx = tid; idx < p.m * kTileRows; idx += kConsumerThreads) {
+      const int i = idx / kTileRows, rr = idx - i * kTileRows;
+      if (row0 + rr < p.n) {
+        const float* lo = outbuf + rr * (NCG * 8) + 2 * i + 1;
+        float v = lo[0] + lo[-1];
+        for (int r = 1; r < p.ksplit; ++r) v += ld_cluster_f32(lo, r) + ld_cluster_f32(lo - 1, r);
+        if (FMT == kFmtFp8) v *= __ldg(p.row_scale + row0 + rr);
+        p.c[static_cast<size_t>(i) * p.n + row0 + rr] = v;
+      }
     }
   }
+  if (p.ksplit > 1) cluster_sync();  // peers stay resident until they have been read
 }
 
 // ---- tensor-map cache
@@ -464,28 +498,56 @@ int env_int(const char* name, int fallback) {
 template <int FMT, int NCG>
 int launch_f16(const void* w, F16Params p, uint64_t n, uint64_t k, cudaStream_t st) {
   constexpr int kChunkBlocks = Fmt<FMT>::kChunkElems / kBlockElems;
-  const uint64_t nblocks = static_cast<uint64_t>(p.nblocks);
-  const uint64_t nchunks = (nblocks + kChunkBlocks - 1) / kChunkBlocks;
-  // Activation phases: at most ~56 KiB of staged activations at a time, phases of equal
-  // size, a whole number of chunks each.
+  const uint64_t nchunks_all = (static_cast<uint64_t>(p.nblocks) + kChunkBlocks - 1) / kChunkBlocks;
   const uint64_t per_block = static_cast<uint64_t>(kBlockElems) * p.ncols * 2;
   uint64_t max_blocks = (56u * 1024u) / per_block;
   max_blocks -= max_blocks % kChunkBlocks;
   if (max_blocks < 2u * kChunkBlocks) return kUnsupportedFeature;
-  const uint64_t phases = (nblocks + max_blocks - 1) / max_blocks;
-  uint64_t pblocks = (nblocks + phases - 1) / phases;
-  pblocks += (kChunkBlocks - pblocks % kChunkBlocks) % kChunkBlocks;
-  p.pblocks = static_cast<int>(pblocks);
-  auto fixed = [&](int rgs) -> size_t {
-    return 1024 + pblocks * per_block + pblocks * kMaxCols * 4 + rgs * 32 * NCG * 4 * 4 +
-           16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128;
-  };
+  static const int regs = kernel_registers(gemv_f16_staged_kernel<FMT, NCG>);
   auto stage_bytes = [](int rgs) -> size_t {
     return static_cast<size_t>(rgs) * (kGroupStageBytes + (FMT == kFmtMxfp4 ? kGroupScaleBytes : 0));
   };
-  static const int regs = kernel_registers(gemv_f16_staged_kernel<FMT, NCG>);
-  StagedPlan plan;
-  if (!plan_staged(n, 1, nblocks, nchunks, 12, regs, fixed, stage_bytes, &plan)) return kUnsupportedFeature;
+  // Activation phases of a CTA that owns `blocks` blocks: at most ~56 KiB of staged
+  // activations at a time, phases of equal size, a whole number of chunks each.
+  auto phase_blocks = [&](uint64_t blocks) -> uint64_t {
+    const uint64_t phases = (blocks + max_blocks - 1) / max_blocks;
+    uint64_t pblocks = (blocks + phases - 1) / phases;
+    pblocks += (kChunkBlocks - pblocks % kChunkBlocks) % kChunkBlocks;
+    return pblocks;
+  };
+  auto fixed_for = [&](uint64_t pblocks) {
+    return [=](int rgs) -> size_t {
+      return 1024 + pblocks * per_block + pblocks * kMaxCols * 4 + rgs * 32 * NCG * 4 * 4 +
+             16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128;
+    };
+  };
+  // K split over a thread-block cluster (1, 2 or 4 CTAs per row tile): more CTAs
+  // and shorter per-warp chains for shapes with few rows and a long k, at the
+  // price of one exchange through distributed shared memory.  TSR_KSPLIT forces a factor.
+  const int forced_split = env_int("TSR_KSPLIT", 0);
+  StagedPlan plan{};
+  uint64_t best_split = 0, best_cper = 0, best_pblocks = 0;
+  double best_cost = 1e30;
+  for (uint64_t ks = 1; ks <= 4; ks *= 2) {
+    if (forced_split > 0 && static_cast<uint64_t>(forced_split) != ks) continue;
+    const uint64_t cper = (nchunks_all + ks - 1) / ks;
+    if (ks > 1 && (cper < 2 || cper * (ks - 1) >= nchunks_all)) continue;  // every rank has work
+    const uint64_t pblocks = phase_blocks(cper * kChunkBlocks);
+    StagedPlan cand{};
+    if (!plan_staged(n, ks, cper * kChunkBlocks, cper, 12, regs, fixed_for(pblocks), stage_bytes, &cand)) continue;
+    // measured: a cluster launch with its two cluster barriers costs about 5 us
+    // (2 CTAs) to 8 us (4 CTAs) over the plain one, so only a long k pays for it
+    const double cost = cand.cost + (ks == 1 ? 0.0 : ks == 2 ? 5.0 : 8.0);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      plan = cand;
+      best_split = ks;
+      best_cper = cper;
+      best_pblocks = pblocks;
+    }
+  }
+  if (best_split == 0) return kUnsupportedFeature;
+  auto fixed = fixed_for(best_pblocks);
   const int forced_rgs = env_int("TSR_RGS", 0);
   if (forced_rgs >= 1 && forced_rgs <= 4) {
     plan.rgs = forced_rgs;
@@ -498,8 +560,11 @@ int launch_f16(const void* w, F16Params p, uint64_t n, uint64_t k, cudaStream_t 
     plan.smem = fixed(plan.rgs) + forced * stage_bytes(plan.rgs);
   }
   if (plan.smem > static_cast<size_t>(kMaxSmem)) return kUnsupportedFeature;
+  p.pblocks = static_cast<int>(best_pblocks);
   p.rgs = plan.rgs;
   p.stages = plan.stages;
+  p.ksplit = static_cast<int>(best_split);
+  p.cper = static_cast<int>(best_cper);
   MapPair maps;
   if (int rc = f16_tensor_maps(FMT, w, n, k, plan.rgs, &maps)) return rc;
   static bool attr = false;
@@ -509,11 +574,16 @@ int launch_f16(const void* w, F16Params p, uint64_t n, uint64_t k, cudaStream_t 
     attr = true;
   }
   const uint64_t th = 16u * plan.rgs;
-  const dim3 grid(static_cast<unsigned>((n + th - 1) / th));
+  const dim3 grid(static_cast<unsigned>(((n + th - 1) / th) * best_split));
   const size_t w_bytes = FMT == kFmtMxfp4 ? n * (k / 2) + n * (k / 32) : n * k;
   p.pdl = pdl_allowed(st, w, w_bytes, p.c, static_cast<size_t>(p.m) * n * 4) ? 1 : 0;
-  launch_kernel(gemv_f16_staged_kernel<FMT, NCG>, grid, dim3((2 * plan.rgs + 1) * 32), plan.smem, st,
-                p.pdl != 0, maps.weights, maps.scales, p);
+  if (env_int("TSR_PLAN_DEBUG", 0))
+    std::fprintf(stderr, "f16 plan fmt=%d m=%d n=%llu k=%llu: ksplit=%llu cper=%llu pblocks=%llu rgs=%d stages=%d smem=%zu grid=%u cost=%.2f\n",
+                 FMT, p.m, (unsigned long long)n, (unsigned long long)k, (unsigned long long)best_split,
+                 (unsigned long long)best_cper, (unsigned long long)best_pblocks, plan.rgs, plan.stages, plan.smem,
+                 grid.x, best_cost);
+  launch_kernel_cluster(gemv_f16_staged_kernel<FMT, NCG>, grid, dim3((2 * plan.rgs + 1) * 32), plan.smem, st,
+                        p.pdl != 0, static_cast<unsigned>(best_split), maps.weights, maps.scales, p);
   return check_launch();
 }
 
@@ -525,7 +595,7 @@ int staged_f16(const float* a, const void* w, const float* scale, float* c, uint
       env_int("TSR_DISABLE_STAGED", 0))
     return kUnsupportedFeature;
   F16Params p{a, c, scale, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
-              static_cast<int>(k / kBlockElems), 0, 0, static_cast<int>(2 * m), 0, 4};
+              static_cast<int>(k / kBlockElems), 0, 0, static_cast<int>(2 * m), 0, 4, 1, 0};
   if (m <= 4) return launch_f16<FMT, 1>(w, p, n, k, st);
   return launch_f16<FMT, 2>(w, p, n, k, st);
 }

@@ -49,6 +49,34 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   cfg.numAttrs = pdl ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+
+// The same with thread-block clusters of `cluster` consecutive CTAs along x.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                         cudaStream_t stream, bool pdl, unsigned cluster, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned count = 0;
+  if (cluster > 1) {
+    attr[count].id = cudaLaunchAttributeClusterDimension;
+    attr[count].val.clusterDim.x = cluster;
+    attr[count].val.clusterDim.y = 1;
+    attr[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  if (pdl) {
+    attr[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = count;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 #endif
 // True when a kernel that reads [read_ptr, +read_bytes) before its pdl_wait()
 // may overlap the previous launch on `stream`; records [out_ptr, +out_bytes) as

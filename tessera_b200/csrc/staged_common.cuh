@@ -235,6 +235,7 @@ struct StagedPlan {
   int rgs;     // row groups per CTA
   int stages;  // ring depth
   size_t smem;
+  double cost;  // modelled microseconds
 };
 
 // Picks the tile height (16..64 rows) and the CTAs per SM so that the grid is
@@ -254,7 +255,8 @@ inline bool plan_staged(uint64_t n, uint64_t split, uint64_t per, uint64_t nchun
     cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
     sms = v > 0 ? v : 148;
   }
-  const double kUnitUs = 0.04, kPrefixUs = 3.4;  // per 16 rows x 1 block on a shared SM; per wave
+  // per 16 rows x 1 block on a busy SM; per block of one warp's own chunks; per wave
+  const double kUnitUs = 0.04, kWarpBlockUs = 0.5, kPrefixUs = 3.4;
   double best = 1e30;
   bool found = false;
   for (int rgs = 4; rgs >= 1; --rgs) {
@@ -273,13 +275,18 @@ inline bool plan_staged(uint64_t n, uint64_t split, uint64_t per, uint64_t nchun
       const uint64_t slots = static_cast<uint64_t>(sms) * occ;
       const uint64_t waves = (ctas + slots - 1) / slots;
       const uint64_t per_sm = (ctas + sms - 1) / sms;
-      double cost = per_sm * rgs * per * kUnitUs + waves * kPrefixUs;
+      // an SM works through its CTAs at a fixed rate, but a warp cannot go faster
+      // than its own share of the blocks (half: two consumer sets) one after the other
+      const double throughput = per_sm * rgs * per * kUnitUs;
+      const double latency = waves * (per / 2.0) * kWarpBlockUs;
+      double cost = (throughput > latency ? throughput : latency) + waves * kPrefixUs;
       if (depth < 3 && nchunks > 2) cost *= 1.1;  // a shallow ring stalls on HBM latency
       if (cost < best - 1e-9) {
         best = cost;
         out->rgs = rgs;
         out->stages = depth;
         out->smem = fx + static_cast<size_t>(depth) * sb;
+        out->cost = cost;
         found = true;
       }
     }
