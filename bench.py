@@ -31,9 +31,9 @@ from tessera_b200 import synth, workload  # noqa: E402
 
 METRIC = "decode_projection_tok_s"
 UNIT = "tok/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_q4k_vec launch on the
-# 17408 x 5120 Q4_K weight (profiles/gemv_q4k_staged_17408x5120.md)
-TRAFFIC_Q4K_17408x5120 = 50196736 + 14592
+# DRAM bytes (read + write) of one gemm_q4k_vec launch on the 17408 x 5120 Q4_K
+# weight, mean of the two launches in profiles/gemv_q4k_staged_17408x5120.md
+TRAFFIC_Q4K_17408x5120 = 50296574
 
 
 def measured_peaks():
@@ -201,7 +201,7 @@ class CudaArrayView:
         self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 2}
 
 
-def qgemv_table(stream, hbm_peak):
+def qgemv_table(stream, hbm_peak, only=None):
     """Device time per launch of the single-projection shapes the metric names: the Q4_K
     decode GEMV (17408 x 5120, m = 1) and the MXFP4 / FP8 projections at m = 1, 4, 16 over
     5120 x 5120, 17408 x 5120 and 5120 x 17408.  Each case rotates through enough private
@@ -216,6 +216,8 @@ def qgemv_table(stream, hbm_peak):
     shapes = [(17408, 5120), (5120, 5120), (5120, 17408)]
     cases = [("q4k", 1, 17408, 5120)]
     cases += [(f, m, n, k) for f in ("mxfp4", "fp8") for (n, k) in shapes for m in (1, 4, 16)]
+    if only is not None:
+        cases = [only]
     rows, cache = [], {}
     for fmt, m, n, k in cases:
         if (fmt, n, k) not in cache:
@@ -461,11 +463,20 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--case", default=None, metavar="FMT:M:N:K",
+                    help="time one projection (q4k, mxfp4 or fp8) instead of the decode step, e.g. q4k:1:17408:5120")
     ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
                     help="row-parallel reduce: peer-memory push all-reduce (default) or NCCL (comparison)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
+    elif args.case:
+        import torch
+        fmt, m, n, k = args.case.split(":")
+        peaks, kind = measured_peaks()
+        torch.cuda.set_device(0)
+        row = qgemv_table(torch.cuda.Stream(), peaks["hbm_gbs"], only=(fmt, int(m), int(n), int(k)))[0]
+        print(json.dumps({"case": args.case, "peak_kind": kind, **row}))
     else:
         gpu_arm(args)
 
