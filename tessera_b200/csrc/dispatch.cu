@@ -6,6 +6,7 @@
 // for the given (buffers, scalars), not the reference's thread mapping.
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "launch.h"
@@ -22,14 +23,21 @@ bool fits_int(uint64_t v) { return v > 0 && v <= 0x7FFFFFFFull; }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Batches of 9..32 activation rows go through the staged GEMV eight rows at a
+// Batches of 9..16 activation rows go through the staged GEMV eight rows at a
 // time (the weights stream once per eight rows); above that the tcgen05 tile
 // amortises its dequantisation better.  `launch(i0, rows)` runs rows
 // [i0, i0 + rows) and returns a status.
-constexpr uint64_t kStagedRows = 8, kStagedBatchMax = 32;
+constexpr uint64_t kStagedRows = 8;
+uint64_t staged_batch_max() {
+  static const uint64_t v = [] {
+    const char* e = std::getenv("TSR_STAGED_BATCH_MAX");  // experiments: where the tcgen05 tile takes over
+    return e ? static_cast<uint64_t>(std::atoi(e)) : 16u;
+  }();
+  return v;
+}
 template <typename Launch>
 int staged_in_chunks(uint64_t m, Launch launch) {
-  if (m > kStagedBatchMax) return kUnsupportedFeature;
+  if (m > staged_batch_max()) return kUnsupportedFeature;
   for (uint64_t i0 = 0; i0 < m; i0 += kStagedRows) {
     const uint64_t rows = m - i0 < kStagedRows ? m - i0 : kStagedRows;
     const int rc = launch(i0, rows);

@@ -10,8 +10,9 @@
 // reference's own tensor-core tile does (src/backends/rocm/rocm_kernels_wmma.cpp:
 // 54-80 of the reference: weights dequantised to fp16 in shared memory).
 //
-// Per CTA: four producer warps (thread = weight row, and = one operand-B row)
-// dequantise a 64-wide k slab into the canonical K-major no-swizzle UMMA
+// Per CTA: four producer warps (thread = weight row; the operand-B pieces are
+// shared out among all 128 threads) dequantise a 64-wide k slab, from raw
+// bytes loaded four slabs ahead, into the canonical K-major no-swizzle UMMA
 // layout (8x16-byte core matrices; leading-byte offset 128 B along k, stride
 // byte offset 1024 B along rows), fence it to the async proxy and signal a
 // full barrier; one elected thread issues four K=16 MMAs per slab and commits
@@ -20,6 +21,10 @@
 // (warp w owns TMEM lanes 32*(w%4)..), add the hi and lo columns and store C.
 // Every wait is bounded and TMEM is always released.
 #include <cuda_fp16.h>
+
+#include <cstdlib>
+#include <mutex>
+#include <unordered_map>
 #include <cuda_runtime.h>
 
 #include "codec.cuh"
@@ -35,9 +40,11 @@ namespace {
 constexpr int kTileM = 128;       // weight rows per CTA
 constexpr int kSlab = 64;         // k elements per pipeline step
 constexpr int kMaxTokens = 64;    // tokens per CTA (N = 2 * padded tokens <= 128)
-constexpr int kProducerThreads = 128;
-constexpr int kUmmaThreads = kProducerThreads + 32;
+constexpr int kProducerThreads = 256;  // two per weight row
+constexpr int kUmmaThreads = kProducerThreads + 64;  // + the MMA warp and the TMA warp
 constexpr int kASlabBytes = kTileM * kSlab * 2;  // 16384
+constexpr int kBufs = 2;                         // slab buffers in shared memory (a power of two)
+constexpr int kBufShift = 1;
 constexpr uint32_t kLbo = 128, kSbo = (kSlab / 8) * 128;  // bytes
 
 enum Format { kFmtQ4K = 0, kFmtQ6K = 1, kFmtMxFp4 = 2, kFmtFp8 = 3 };
@@ -111,91 +118,175 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// ---- per-format dequantisation of 64 consecutive weights of one row --------
-// `slab` indexes 64-element pieces of the row; out[e] is weight k = 64*slab + e
-// with the reference's arithmetic (src/core/numerics/quant.cpp:656-675,
-// 421-449, 279-297; gemm.cpp:266-270).
+// ---- per-format dequantisation of half a slab (32 consecutive weights) ------
+// Two producer threads share a weight row: `half` 0 takes k = 64*slab + 0..31,
+// `half` 1 the next 32.  The raw bytes are loaded several slabs ahead
+// (RawHalf, registers) so that HBM latency is off the critical path.
+// MXFP4 and FP8 convert to binary16 exactly (cvt.rn.f16x2.e2m1x2 / .e4m3x2);
+// the MXFP4 block scale is a binary16 multiply (exact: a power of two, within
+// the binary16 range for every scale a weight tensor realistically holds; what
+// falls outside rounds exactly as the fp32 product rounded to binary16 would);
+// the FP8 row scale is applied to the accumulator in the epilogue.  Q4_K:
+// nibble -> binary16 by a bit pattern, then one fused multiply-add with the
+// sub-block's d*sc and dmin*mn rounded to binary16.  Reference arithmetic:
+// src/core/numerics/quant.cpp:656-675, 421-449, 279-297; gemm.cpp:266-270.
+struct RawHalf {
+  uint4 q[2];
+  uint32_t x[4];
+};
+
+__device__ __forceinline__ void cvt_e2m1x8_h2(uint32_t w, uint32_t (&h)[4]) {
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3])
+      : "r"(w));
+}
+__device__ __forceinline__ void cvt_e4m3x4_h2(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  asm("{\n\t.reg .b16 l, h;\n\t"
+      "mov.b32 {l, h}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, l;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+      : "=r"(lo), "=r"(hi)
+      : "r"(w));
+}
+__device__ __forceinline__ uint32_t h2_const(float v) {
+  const __half2 h = __float2half2_rn(v);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 template <int FMT>
-__device__ __forceinline__ void dequant64(const UmmaParams& p, int row, int slab, float (&out)[64]) {
+__device__ __forceinline__ void load_raw(const UmmaParams& p, int row, int slab, int half, RawHalf& r) {
   if (FMT == kFmtQ4K) {
     const int nb = p.k / 256, b = slab >> 2, g = slab & 3;
     const unsigned char* blk = p.w + (static_cast<size_t>(row) * nb + b) * kQ4KBlockBytes;
     const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-    const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * g));
-    const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * g));
-    const float d = fp16_bits_to_float(hdr.x & 0xFFFFu), dmin = fp16_bits_to_float(hdr.x >> 16);
-    const uint32_t s[3] = {hdr.y, hdr.z, hdr.w};
-    uint32_t sc0, mn0, sc1, mn1;
-    q4k_scale_min(s, 2 * g, sc0, mn0);
-    q4k_scale_min(s, 2 * g + 1, sc1, mn1);
-    const float dl = d * static_cast<float>(sc0), ml = dmin * static_cast<float>(mn0);
-    const float dh = d * static_cast<float>(sc1), mh = dmin * static_cast<float>(mn1);
-    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    r.x[0] = hdr.x, r.x[1] = hdr.y, r.x[2] = hdr.z, r.x[3] = hdr.w;
+    r.q[0] = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * g));  // both halves: low / high nibbles
+    r.q[1] = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * g));
+  } else if (FMT == kFmtMxFp4) {
+    const unsigned char* nib = p.w + static_cast<size_t>(row) * (p.k / 2) + slab * 32 + half * 16;
+    const unsigned char* scales =
+        p.w + static_cast<size_t>(p.n) * (p.k / 2) + static_cast<size_t>(row) * (p.k / 32) + slab * 2 + half;
+    r.q[0] = __ldg(reinterpret_cast<const uint4*>(nib));
+    r.x[0] = __ldg(scales);
+  } else if (FMT == kFmtFp8) {
+    const unsigned char* wr = p.w + static_cast<size_t>(row) * p.k + slab * 64 + half * 32;
+    r.q[0] = __ldg(reinterpret_cast<const uint4*>(wr));
+    r.q[1] = __ldg(reinterpret_cast<const uint4*>(wr + 16));
+  }
+  // Q6_K: 210-byte blocks are only 2-byte aligned; convert() reads them directly
+}
+
+// out: 32 binary16 values as four 16-byte pieces (8 values each), k order.
+template <int FMT>
+__device__ __forceinline__ void convert(const UmmaParams& p, int row, int slab, int half, const RawHalf& r,
+                                        uint4 (&out)[4]) {
+  uint32_t h[16];
+  if (FMT == kFmtQ4K) {
+    const int sb = 2 * (slab & 3) + half;  // sub-block: low nibbles are the even one
+    const float d = fp16_bits_to_float(r.x[0] & 0xFFFFu), dmin = fp16_bits_to_float(r.x[0] >> 16);
+    const uint32_t s[3] = {r.x[1], r.x[2], r.x[3]};
+    uint32_t sc, mn;
+    q4k_scale_min(s, sb, sc, mn);
+    const uint32_t dl = h2_const(d * static_cast<float>(sc)), ml = h2_const(-dmin * static_cast<float>(mn));
+    const uint32_t qw[8] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w};
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      const uint32_t byte = (qw[e >> 2] >> (8 * (e & 3))) & 0xFFu;
-      out[e] = fmaf(dl, static_cast<float>(byte & 15u), -ml);
-      out[32 + e] = fmaf(dh, static_cast<float>(byte >> 4), -mh);
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t t = (half ? (qw[i] >> 4) : qw[i]) & 0x0F0F0F0Fu;
+      // bytes n0..n3 -> binary16 pairs (1024 + n0, 1024 + n1), (1024 + n2, 1024 + n3)
+      const uint32_t p01 = __byte_perm(t, 0x64646464u, 0x4140), p23 = __byte_perm(t, 0x64646464u, 0x4342);
+      h[2 * i] = hfma2_u32(hsub2_u32(p01, 0x64006400u), dl, ml);
+      h[2 * i + 1] = hfma2_u32(hsub2_u32(p23, 0x64006400u), dl, ml);
     }
   } else if (FMT == kFmtQ6K) {
-    const int nb = p.k / 256, b = slab >> 2, j = slab & 3, h = j >> 1, hi = j & 1;
+    const int nb = p.k / 256, b = slab >> 2, j = slab & 3, hh = j >> 1, hi = j & 1;
     const unsigned char* blk = p.w + (static_cast<size_t>(row) * nb + b) * kQ6KBlockBytes;
     const float d = fp16_bits_to_float(blk[208] | (blk[209] << 8));
-    const unsigned char* ql = blk + 64 * h;
-    const unsigned char* qh = blk + 128 + 32 * h;
-    const signed char* sc = reinterpret_cast<const signed char*>(blk + 192 + 8 * h);
+    const unsigned char* ql = blk + 64 * hh;
+    const unsigned char* qh = blk + 128 + 32 * hh;
+    const signed char* sc = reinterpret_cast<const signed char*>(blk + 192 + 8 * hh);
+    const int pp = 2 * hi + half;  // 0..3: which 32-element run of the 128-element half block
 #pragma unroll
-    for (int part = 0; part < 2; ++part) {
-      const int pp = 2 * hi + part;  // 0..3: which 32-element run of the half
+    for (int l = 0; l < 32; l += 2) {
+      float v[2];
 #pragma unroll
-      for (int l = 0; l < 32; ++l) {
-        const uint32_t lo = ql[32 * (pp & 1) + l];
+      for (int e = 0; e < 2; ++e) {
+        const uint32_t lo = ql[32 * (pp & 1) + l + e];
         const uint32_t nib = (pp & 2) ? (lo >> 4) : (lo & 15u);
-        const int q = static_cast<int>(nib | (((static_cast<uint32_t>(qh[l]) >> (2 * pp)) & 3u) << 4)) - 32;
-        out[32 * part + l] = d * static_cast<float>(sc[l / 16 + 2 * pp]) * static_cast<float>(q);
+        const int q = static_cast<int>(nib | (((static_cast<uint32_t>(qh[l + e]) >> (2 * pp)) & 3u) << 4)) - 32;
+        v[e] = d * static_cast<float>(sc[(l + e) / 16 + 2 * pp]) * static_cast<float>(q);
       }
+      h[l / 2] = pack_h2(v[0], v[1]);
     }
   } else if (FMT == kFmtMxFp4) {
-    const unsigned char* nib = p.w + static_cast<size_t>(row) * (p.k / 2) + slab * 32;
-    const unsigned char* scales = p.w + static_cast<size_t>(p.n) * (p.k / 2) + static_cast<size_t>(row) * (p.k / 32) + slab * 2;
-    const uint4 q0 = __ldg(reinterpret_cast<const uint4*>(nib));
-    const uint4 q1 = __ldg(reinterpret_cast<const uint4*>(nib + 16));
-    const float s0 = e8m0_to_float(scales[0]), s1 = e8m0_to_float(scales[1]);
-    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const uint32_t scale = h2_const(e8m0_to_float(r.x[0] & 0xFFu));
+    const uint32_t qw[4] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w};
 #pragma unroll
-    for (int e = 0; e < 64; ++e)
-      out[e] = (e < 32 ? s0 : s1) * e2m1_to_float((qw[e >> 3] >> (4 * (e & 7))) & 15u);
-  } else {
-    const unsigned char* wr = p.w + static_cast<size_t>(row) * p.k + slab * 64;
-    const float s = __ldg(p.scale + row);
+    for (int i = 0; i < 4; ++i) {
+      uint32_t c[4];
+      cvt_e2m1x8_h2(qw[i], c);
 #pragma unroll
-    for (int v = 0; v < 4; ++v) {
-      const uint4 q = __ldg(reinterpret_cast<const uint4*>(wr + 16 * v));
-      const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-      for (int e = 0; e < 16; ++e) out[16 * v + e] = s * e4m3_to_float((qw[e >> 2] >> (8 * (e & 3))) & 0xFFu);
+      for (int e = 0; e < 4; ++e) h[4 * i + e] = hmul2_u32(c[e], scale);
     }
+  } else {
+    const uint32_t qw[8] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) cvt_e4m3x4_h2(qw[i], h[2 * i], h[2 * i + 1]);
   }
+#pragma unroll
+  for (int kc = 0; kc < 4; ++kc) out[kc] = make_uint4(h[4 * kc], h[4 * kc + 1], h[4 * kc + 2], h[4 * kc + 3]);
 }
 
-// Store 64 values of operand row `r` (k slab) into the canonical layout.
-__device__ __forceinline__ void store_row_slab(unsigned char* tile, int r, const float (&v)[64]) {
-  unsigned char* base = tile + (r >> 3) * kSbo + (r & 7) * 16;
-#pragma unroll
-  for (int kc = 0; kc < 8; ++kc) {
-    uint4 u;
-    u.x = pack_h2(v[8 * kc + 0], v[8 * kc + 1]);
-    u.y = pack_h2(v[8 * kc + 2], v[8 * kc + 3]);
-    u.z = pack_h2(v[8 * kc + 4], v[8 * kc + 5]);
-    u.w = pack_h2(v[8 * kc + 6], v[8 * kc + 7]);
-    *reinterpret_cast<uint4*>(base + kc * kLbo) = u;
-  }
-}
+// ---- raw-weight ring (TMA) ------------------------------------------------------
+// With RING the weight bytes of a 128-row tile arrive by tiled TMA copies, a
+// stage of several slabs at a time, in a ring of kRawStages stages; the
+// producers read their 16-byte pieces from shared memory.  Per-thread global
+// loads (thread = row) touch 32 different lines per warp instruction and ran
+// at an eighth of the memory rate.  Stage layouts:
+//   FP8   [2 segments][128 rows][128 B], 128-byte swizzle       (256 k, 4 slabs)
+//   MXFP4 the same for the nibbles (512 k, 8 slabs) + [128 rows][16 scale bytes]
+//   Q4_K  [128 rows][144 B]: one block per row                  (256 k, 4 slabs)
+// Q6_K (2-byte aligned blocks) and shapes whose k is not a whole number of
+// segments keep the direct loads (RING = false).
+constexpr int kRawStages = 3;
+template <int FMT>
+struct RingFmt {
+  static constexpr int kSlabsPerStage = FMT == kFmtMxFp4 ? 8 : 4;
+  static constexpr int kWeightBytes = FMT == kFmtQ4K ? kTileM * kQ4KBlockBytes : 2 * kTileM * 128;
+  static constexpr int kScaleBytes = FMT == kFmtMxFp4 ? kTileM * 16 : 0;
+  static constexpr int kStageBytes = kWeightBytes + kScaleBytes;
+  static constexpr int kStagePitch = (kStageBytes + 1023) & ~1023;  // stages start on 1 KiB boundaries (swizzle)
+};
 
 template <int FMT>
+__device__ __forceinline__ void read_raw(const unsigned char* stage, int trow, int si, int half, RawHalf& r) {
+  if (FMT == kFmtQ4K) {
+    const unsigned char* blk = stage + trow * kQ4KBlockBytes;
+    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+    r.x[0] = hdr.x, r.x[1] = hdr.y, r.x[2] = hdr.z, r.x[3] = hdr.w;
+    r.q[0] = *reinterpret_cast<const uint4*>(blk + 16 + 32 * si);
+    r.q[1] = *reinterpret_cast<const uint4*>(blk + 32 + 32 * si);
+  } else {
+    // byte offset of this thread's pieces inside the 256 stage bytes of its row
+    const int off = FMT == kFmtFp8 ? si * 64 + half * 32 : si * 32 + half * 16;
+    const unsigned char* seg = stage + (off >> 7) * (kTileM * 128) + trow * 128;
+    const int c = (off >> 4) & 7, x = trow & 7;
+    r.q[0] = *reinterpret_cast<const uint4*>(seg + ((c ^ x) << 4));
+    if (FMT == kFmtFp8) r.q[1] = *reinterpret_cast<const uint4*>(seg + (((c + 1) ^ x) << 4));
+    if (FMT == kFmtMxFp4) r.x[0] = stage[RingFmt<FMT>::kWeightBytes + trow * 16 + si * 2 + half];
+  }
+}
+
+template <int FMT, bool RING>
 __global__ void __launch_bounds__(kUmmaThreads)
-gemm_umma_kernel(const UmmaParams p) {
-  extern __shared__ __align__(1024) unsigned char smem[];
+gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
+                 const UmmaParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row0 = blockIdx.x * kTileM;
   const int tok0 = blockIdx.y * kMaxTokens;
@@ -203,93 +294,183 @@ gemm_umma_kernel(const UmmaParams p) {
   const int tok_pad = (tokens + 7) & ~7;      // hi rows [0, tok_pad), lo rows [tok_pad, 2*tok_pad)
   const int n_cols = 2 * tok_pad;             // multiple of 16, <= 128
   const int b_slab_bytes = n_cols * kSlab * 2;
-  unsigned char* a_tile[2] = {smem, smem + kASlabBytes};
-  unsigned char* b_tile[2] = {smem + 2 * kASlabBytes, smem + 2 * kASlabBytes + b_slab_bytes};
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kASlabBytes + 2 * b_slab_bytes);
-  uint64_t* full = bars;       // [2] producers -> MMA
-  uint64_t* empty = bars + 2;  // [2] MMA -> producers
-  uint64_t* done = bars + 4;   // accumulator complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  constexpr int kRingBytes = RING ? kRawStages * RingFmt<FMT>::kStagePitch : 0;
+  unsigned char* const ring = smem;                            // [kRawStages][kStagePitch]
+  unsigned char* const a_tiles = smem + kRingBytes;            // [kBufs][kASlabBytes]
+  unsigned char* const b_tiles = a_tiles + kBufs * kASlabBytes;  // [kBufs][b_slab_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(b_tiles + kBufs * b_slab_bytes);
+  uint64_t* full = bars;                 // [kBufs] producers -> MMA
+  uint64_t* empty = bars + kBufs;        // [kBufs] MMA -> producers
+  uint64_t* done = bars + 2 * kBufs;     // accumulator complete
+  uint64_t* raw_full = done + 1;         // [kRawStages] TMA -> producers
+  uint64_t* raw_empty = raw_full + kRawStages;  // [kRawStages] producers -> TMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_empty + kRawStages);
   uint32_t tmem_cols = 32;
   while (tmem_cols < static_cast<uint32_t>(n_cols)) tmem_cols <<= 1;
   const int nslabs = p.k / kSlab;
+  constexpr int kProducerWarps = kProducerThreads / 32;  // then one MMA warp, then one TMA warp
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&full[s], kProducerThreads);
+    for (int s = 0; s < kBufs; ++s) {
+      mbar_init(&full[s], kProducerThreads / 32);  // one arrival per producer warp
       mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < kRawStages; ++s) {
+      mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], kProducerThreads / 32);
     }
     mbar_init(done, 1);
     mbar_fence_init();
   }
-  if (warp == 4) tmem_alloc(tmem_slot, tmem_cols);
+  if (warp == kProducerWarps) tmem_alloc(tmem_slot, tmem_cols);
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool failed = false;
 
-  if (warp < 4) {
+  if (warp < kProducerWarps) {
     // ---------------- producers: dequantise A rows, convert B rows ---------
-    const int wrow = row0 + tid;  // weight row of this thread
-    for (int s = 0; s < nslabs && !failed; ++s) {
-      const int buf = s & 1, round = s >> 1;
-      if (round > 0 && !mbar_wait(&empty[buf], (round - 1) & 1, &g_umma_timeouts)) {
-        failed = true;
-        break;
+    const int trow = tid & (kTileM - 1), half = tid >> 7;  // warps 0-3: first 32 k of a slab, warps 4-7: the rest
+    const int wrow = row0 + trow;
+    const bool have_row = wrow < p.n;
+    // Without the ring: raw bytes by direct loads, a group of kAhead slabs at a time, one group ahead.
+    constexpr int kAhead = 4;
+    RawHalf raw[2][kAhead];
+    auto load_group = [&](int first_slab, RawHalf (&dst)[kAhead]) {
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u)
+        if (have_row && first_slab + u < nslabs) load_raw<FMT>(p, wrow, first_slab + u, half, dst[u]);
+    };
+    if (!RING) {
+      load_group(0, raw[0]);
+      load_group(kAhead, raw[1]);
+    }
+    // operand B: the slab has n_cols rows of eight 16-byte pieces; thread t converts pieces
+    // t, t + 256, ... (at most kBPieces; eight consecutive threads read 256 consecutive bytes of
+    // one token), from activations it loaded two slabs earlier
+    const int b_pieces = n_cols * (kSlab / 8);
+    constexpr int kBPieces = (2 * kMaxTokens * (kSlab / 8) + kProducerThreads - 1) / kProducerThreads;
+    float4 bx[2][kBPieces][2];
+    auto load_b = [&](int slab, float4 (&dst)[kBPieces][2]) {
+#pragma unroll
+      for (int i = 0; i < kBPieces; ++i) {
+        const int g = tid + i * kProducerThreads;
+        dst[i][0] = dst[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (g < b_pieces && slab < nslabs) {
+          const int r = g >> 3, kc = g & 7;
+          const int tok = r < tok_pad ? r : r - tok_pad;
+          if (tok < tokens) {
+            const float4* src =
+                reinterpret_cast<const float4*>(p.a + static_cast<size_t>(tok0 + tok) * p.k + slab * kSlab + kc * 8);
+            dst[i][0] = __ldg(src);
+            dst[i][1] = __ldg(src + 1);
+          }
+        }
       }
-      float v[64];
-      if (wrow < p.n) {
-        dequant64<FMT>(p, wrow, s, v);
-      } else {
+    };
+    load_b(0, bx[0]);
+    load_b(1, bx[1]);
+    for (int s0 = 0; s0 < nslabs && !failed; s0 += 2 * kAhead) {
 #pragma unroll
-        for (int e = 0; e < 64; ++e) v[e] = 0.0f;
-      }
-      store_row_slab(a_tile[buf], tid, v);
-      if (tid < n_cols) {
-        const int tok = tid < tok_pad ? tid : tid - tok_pad;
-        const bool lo_part = tid >= tok_pad;
-        if (tok < tokens) {
-          const float4* src = reinterpret_cast<const float4*>(p.a + static_cast<size_t>(tok0 + tok) * p.k + s * kSlab);
+      for (int uu = 0; uu < 2 * kAhead; ++uu) {
+        const int grp = uu / kAhead, u = uu % kAhead;
+        const int s = s0 + uu;
+        if (s >= nslabs || failed) break;
+        const int buf = s & (kBufs - 1), round = s >> kBufShift;
+        if (round > 0 && !mbar_wait(&empty[buf], (round - 1) & 1, &g_umma_timeouts)) {
+          failed = true;
+          break;
+        }
+        uint4 piece4[4] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u),
+                           make_uint4(0u, 0u, 0u, 0u)};
+        if (RING) {
+          constexpr int kPer = RingFmt<FMT>::kSlabsPerStage;
+          const int st = s / kPer, si = s - st * kPer;
+          const int slot = st % kRawStages, rround = st / kRawStages;
+          if (si == 0 && !mbar_wait(&raw_full[slot], rround & 1, &g_umma_timeouts)) {
+            failed = true;
+            break;
+          }
+          RawHalf rr;
+          read_raw<FMT>(ring + slot * RingFmt<FMT>::kStagePitch, trow, si, half, rr);
+          if (have_row) convert<FMT>(p, wrow, s, half, rr, piece4);
+          if (si == kPer - 1 || s == nslabs - 1) {  // this warp is done with the stage
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&raw_empty[slot]);
+          }
+        } else if (have_row) {
+          convert<FMT>(p, wrow, s, half, raw[grp][u], piece4);
+          if (u == kAhead - 1) load_group(s + 1 + kAhead, raw[grp]);  // this group's registers are free again
+        }
+        unsigned char* a_dst = a_tiles + buf * kASlabBytes + (trow >> 3) * kSbo + (trow & 7) * 16 + half * 4 * kLbo;
 #pragma unroll
-          for (int q = 0; q < 16; ++q) {
-            const float4 x = __ldg(src + q);
-            const float xs[4] = {x.x, x.y, x.z, x.w};
+        for (int kc = 0; kc < 4; ++kc) *reinterpret_cast<uint4*>(a_dst + kc * kLbo) = piece4[kc];
+        // operand B from the activations loaded two slabs ago; then reload for slab s + 2
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+        for (int i = 0; i < kBPieces; ++i) {
+          const int g = tid + i * kProducerThreads;
+          if (g < b_pieces) {
+            const int r = g >> 3, kc = g & 7;
+            const bool lo_part = r >= tok_pad;
+            const float4 x0 = bx[u & 1][i][0], x1 = bx[u & 1][i][1];
+            const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
               const float cx = fminf(fmaxf(xs[e], -65504.0f), 65504.0f);
               const float hi = __half2float(__float2half_rn(cx));
-              v[4 * q + e] = lo_part ? fminf(fmaxf(xs[e] - hi, -65504.0f), 65504.0f) : cx;
+              o[e] = lo_part ? fminf(fmaxf(xs[e] - hi, -65504.0f), 65504.0f) : cx;
             }
+            *reinterpret_cast<uint4*>(b_tiles + buf * b_slab_bytes + (r >> 3) * kSbo + (r & 7) * 16 + kc * kLbo) =
+                make_uint4(pack_h2(o[0], o[1]), pack_h2(o[2], o[3]), pack_h2(o[4], o[5]), pack_h2(o[6], o[7]));
           }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 64; ++e) v[e] = 0.0f;
         }
-        store_row_slab(b_tile[buf], tid, v);
+        load_b(s + 2, bx[u & 1]);
+        // every thread orders its own stores before the async proxy; 256 arrivals on one
+        // barrier word would serialise, so one lane per warp arrives for the warp
+        fence_async_proxy();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[buf]);
       }
-      fence_async_proxy();
-      mbar_arrive(&full[buf]);
     }
-  } else if (lane == 0) {
-    // ---------------- MMA issuer --------------------------------------------
-    const uint32_t idesc = instr_desc(static_cast<uint32_t>(n_cols));
-    for (int s = 0; s < nslabs; ++s) {
-      const int buf = s & 1, round = s >> 1;
-      if (!mbar_wait(&full[buf], round & 1, &g_umma_timeouts)) {
-        failed = true;
-        break;
-      }
-      tcgen05_fence_after();
-      const uint32_t a_addr = smem_u32(a_tile[buf]), b_addr = smem_u32(b_tile[buf]);
+  } else if (warp == kProducerWarps) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ------------------------------------------
+      const uint32_t idesc = instr_desc(static_cast<uint32_t>(n_cols));
+      for (int s = 0; s < nslabs; ++s) {
+        const int buf = s & (kBufs - 1), round = s >> kBufShift;
+        if (!mbar_wait(&full[buf], round & 1, &g_umma_timeouts)) {
+          failed = true;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t a_addr = smem_u32(a_tiles + buf * kASlabBytes), b_addr = smem_u32(b_tiles + buf * b_slab_bytes);
 #pragma unroll
-      for (int kk = 0; kk < kSlab / 16; ++kk) {
-        umma_f16(tmem_base, smem_desc(a_addr + kk * 2 * kLbo), smem_desc(b_addr + kk * 2 * kLbo), idesc,
-                 (s > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < kSlab / 16; ++kk) {
+          umma_f16(tmem_base, smem_desc(a_addr + kk * 2 * kLbo), smem_desc(b_addr + kk * 2 * kLbo), idesc,
+                   (s > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[buf]);  // the slab buffer is free once these MMAs have read it
       }
-      umma_commit(&empty[buf]);  // the slab buffer is free once these MMAs have read it
+      umma_commit(done);
     }
-    umma_commit(done);
+  } else if (RING && lane == 0) {
+    // ---------------- TMA issuer: raw weight stages -------------------------
+    constexpr int kPer = RingFmt<FMT>::kSlabsPerStage;
+    const int nstages = (nslabs + kPer - 1) / kPer;
+    for (int st = 0; st < nstages; ++st) {
+      const int slot = st % kRawStages, rround = st / kRawStages;
+      if (rround > 0 && !mbar_wait(&raw_empty[slot], (rround - 1) & 1, &g_umma_timeouts)) break;
+      unsigned char* dst = ring + slot * RingFmt<FMT>::kStagePitch;
+      mbar_expect_tx(&raw_full[slot], RingFmt<FMT>::kStageBytes);
+      if (FMT == kFmtQ4K) {
+        tma_load_3d(dst, &wmap, 0, st, row0, &raw_full[slot]);      // (18 x u64, block, rows)
+      } else {
+        tma_load_3d(dst, &wmap, 0, row0, 2 * st, &raw_full[slot]);  // (128 B, rows, segments)
+        if (FMT == kFmtMxFp4) tma_load_2d(dst + RingFmt<FMT>::kWeightBytes, &smap, 16 * st, row0, &raw_full[slot]);
+      }
+    }
   }
 
   // ---------------- epilogue: TMEM -> registers -> C ------------------------
@@ -299,6 +480,7 @@ gemm_umma_kernel(const UmmaParams p) {
     tcgen05_fence_after();
     if (ok) {
       const int out_row = row0 + tid;
+      const float out_scale = (FMT == kFmtFp8 && out_row < p.n) ? __ldg(p.scale + out_row) : 1.0f;
       const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
       for (int c0 = 0; c0 < tok_pad; c0 += 8) {
         float hi[8], lo[8];
@@ -307,29 +489,101 @@ gemm_umma_kernel(const UmmaParams p) {
         if (out_row < p.n) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            if (c0 + j < tokens) p.c[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = hi[j] + lo[j];
+            if (c0 + j < tokens) p.c[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = (hi[j] + lo[j]) * out_scale;
         }
       }
     }
   }
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem_base, tmem_cols);
+  if (warp == kProducerWarps) tmem_dealloc(tmem_base, tmem_cols);
 }
 
-template <int FMT>
-int launch_umma(const UmmaParams& p, cudaStream_t st) {
+// ---- tensor maps of the raw ring (cached per weight tensor) ---------------------
+struct RingMaps {
+  CUtensorMap weights, scales;
+};
+struct RingKey {
+  const void* base;
+  uint64_t n, k;
+  int fmt;
+  bool operator==(const RingKey& o) const { return base == o.base && n == o.n && k == o.k && fmt == o.fmt; }
+};
+struct RingKeyHash {
+  size_t operator()(const RingKey& x) const {
+    return std::hash<const void*>()(x.base) ^ (x.n * 0x9E3779B97F4A7C15ull) ^ (x.k << 40) ^ (static_cast<size_t>(x.fmt) << 60);
+  }
+};
+std::mutex g_ring_mutex;
+std::unordered_map<RingKey, RingMaps, RingKeyHash> g_ring_maps;
+
+int ring_maps(int fmt, const void* w, uint64_t n, uint64_t k, RingMaps* out) {
+  std::lock_guard<std::mutex> lock(g_ring_mutex);
+  const RingKey key{w, n, k, fmt};
+  auto it = g_ring_maps.find(key);
+  if (it != g_ring_maps.end()) {
+    *out = it->second;
+    return kOk;
+  }
+  RingMaps maps{};
+  int rc;
+  if (fmt == kFmtQ4K) {
+    const uint64_t nb = k / 256;
+    const uint64_t dims[3] = {18, nb, n};
+    const uint64_t strides[2] = {kQ4KBlockBytes, nb * kQ4KBlockBytes};
+    const uint32_t box[3] = {18, 1, kTileM};
+    rc = encode_tensor_map(&maps.weights, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, w, dims, strides, box);
+    maps.scales = maps.weights;
+  } else {
+    const uint64_t row_bytes = fmt == kFmtMxFp4 ? k / 2 : k;
+    const uint64_t dims[3] = {128, n, row_bytes / 128};
+    const uint64_t strides[2] = {row_bytes, 128};
+    const uint32_t box[3] = {128, kTileM, 2};
+    rc = encode_tensor_map(&maps.weights, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w, dims, strides, box, true);
+    maps.scales = maps.weights;
+    if (rc == kOk && fmt == kFmtMxFp4) {
+      const uint64_t sdims[2] = {k / 32, n};
+      const uint64_t sstrides[1] = {k / 32};
+      const uint32_t sbox[2] = {16, kTileM};
+      rc = encode_tensor_map(&maps.scales, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                             static_cast<const unsigned char*>(w) + n * (k / 2), sdims, sstrides, sbox);
+    }
+  }
+  if (rc != kOk) return rc;
+  if (g_ring_maps.size() > 65536) g_ring_maps.clear();
+  g_ring_maps.emplace(key, maps);
+  *out = maps;
+  return kOk;
+}
+
+template <int FMT, bool RING>
+int launch_umma_impl(const UmmaParams& p, const RingMaps& maps, cudaStream_t st) {
   const int tok_pad = ((p.m < kMaxTokens ? p.m : kMaxTokens) + 7) & ~7;
-  const size_t smem = 2 * kASlabBytes + 2 * static_cast<size_t>(2 * tok_pad) * kSlab * 2 + 64 + 1024;
+  const size_t ring = RING ? static_cast<size_t>(kRawStages) * RingFmt<FMT>::kStagePitch : 0;
+  const size_t smem = 1024 + ring + kBufs * kASlabBytes + kBufs * static_cast<size_t>(2 * tok_pad) * kSlab * 2 + 256;
   static bool attr = false;
   if (!attr) {
-    cudaFuncSetAttribute(gemm_umma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    cudaFuncSetAttribute(gemm_umma_kernel<FMT, RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     attr = true;
   }
   const dim3 grid(static_cast<unsigned>((p.n + kTileM - 1) / kTileM),
                   static_cast<unsigned>((p.m + kMaxTokens - 1) / kMaxTokens));
-  gemm_umma_kernel<FMT><<<grid, kUmmaThreads, smem, st>>>(p);
+  gemm_umma_kernel<FMT, RING><<<grid, kUmmaThreads, smem, st>>>(maps.weights, maps.scales, p);
   return check_launch();
+}
+
+template <int FMT>
+int launch_umma(const UmmaParams& p, cudaStream_t st) {
+  // the ring wants whole segments (and 16-byte scale rows for MXFP4) and 16-byte aligned weights
+  const bool aligned = (reinterpret_cast<uintptr_t>(p.w) & 15u) == 0;
+  const bool ring = aligned && (FMT == kFmtQ4K || (FMT == kFmtFp8 && p.k % 128 == 0) ||
+                                (FMT == kFmtMxFp4 && p.k % 512 == 0));
+  RingMaps maps{};
+  if (ring && FMT != kFmtQ6K) {
+    if (int rc = ring_maps(FMT, p.w, static_cast<uint64_t>(p.n), static_cast<uint64_t>(p.k), &maps)) return rc;
+    return launch_umma_impl<FMT, FMT != kFmtQ6K>(p, maps, st);
+  }
+  return launch_umma_impl<FMT, false>(p, maps, st);
 }
 
 }  // namespace

@@ -184,7 +184,7 @@ def test_w4a8_matches_golden(backend, golden):
 SHAPES = [
     # (m, n, k): ragged n (not a multiple of 8), split remainders, m = 1..17
     (1, 64, 256), (1, 13, 768), (2, 100, 1024), (3, 40, 512), (4, 24, 2048), (5, 9, 256),
-    (7, 33, 1280), (16, 48, 1024), (17, 31, 512),
+    (7, 33, 1280), (16, 48, 1024), (17, 31, 512), (24, 300, 2048),
     # tcgen05 tile: ragged weight-row tile, more than one 64-token chunk
     (70, 200, 1024), (130, 136, 512),
 ]
