@@ -344,12 +344,15 @@ def gpu_arm(args):
             if only is not None and p.name not in only:
                 continue
             dst = logits_buf if p.name == "output" else out_buf
+            if world > 1 and p.kind == workload.ROW and comm is not None:
+                # row-parallel: the split-K reduce rides in the all-reduce kernel
+                part, split = proj.ProjectGemvPartials(p.dtype, dev_act[p.act], w, 1, n, k)
+                launches[0] += 1
+                comm.reduce_allreduce(part.Handle(), split, out_buf.Handle(), workload.HIDDEN, backend.stream())
+                continue
             proj.ProjectBatch(p.dtype, dev_act[p.act], w, dst, 1, n, k)
             if world > 1 and p.kind == workload.ROW:
-                if comm is not None:
-                    comm.allreduce(out_buf.Handle(), workload.HIDDEN, backend.stream())
-                else:
-                    dist.all_reduce(reduce_view)
+                dist.all_reduce(reduce_view)
 
     h2d_bytes = host_act["x"].nbytes
     d2h_bytes = logits_host.nbytes

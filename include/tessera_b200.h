@@ -187,7 +187,15 @@ int tsr_gemm_q4k_noalloc(const float* a, const void* w, float* c, uint64_t m, ui
  * (count a multiple of 4, data 16-byte aligned); every rank must issue the
  * same sequence of calls.  It may be captured in a CUDA graph.  Waits on
  * peers are bounded: when one gives up the call still returns and
- * tsr_tp_error_count becomes non-zero. */
+ * tsr_tp_error_count becomes non-zero.
+ *
+ * tsr_tp_reduce_allreduce fuses the split-K reduce of a row-parallel projection
+ * into the all-reduce: `partials` holds `split` regions of `count` floats (what
+ * gemm_*_vec with a split scalar writes); each rank adds its regions in region
+ * order (the order of gemm_vec_reduce, decode_internal.hpp:1325-1345) while it
+ * pushes, and `out` receives the sum over ranks in rank order: the same bits as
+ * gemm_vec_reduce followed by tsr_tp_allreduce, one launch instead of two.  The
+ * reference has no such call (it reduces, then TpReduce). */
 typedef struct tsr_tp_comm tsr_tp_comm;
 int tsr_tp_create(int device, int rank, int world, uint64_t max_floats, tsr_tp_comm** out);
 void tsr_tp_destroy(tsr_tp_comm* comm);
@@ -196,6 +204,8 @@ int tsr_tp_ipc_handle(tsr_tp_comm* comm, void* handle64);
 int tsr_tp_attach_ipc(tsr_tp_comm* comm, int peer_rank, const void* handle64);
 int tsr_tp_attach_local(tsr_tp_comm* comm, int peer_rank, int peer_device, void* peer_block);
 int tsr_tp_allreduce(tsr_tp_comm* comm, float* data, uint64_t count, void* stream);
+int tsr_tp_reduce_allreduce(tsr_tp_comm* comm, const float* partials, uint64_t split, float* out,
+                            uint64_t count, void* stream);
 int tsr_tp_error_count(tsr_tp_comm* comm, uint32_t* count);
 
 #ifdef __cplusplus

@@ -90,6 +90,7 @@ SIGNATURES = {
     "tsr_tp_attach_ipc": (C.c_int, [_vp, C.c_int, _vp]),
     "tsr_tp_attach_local": (C.c_int, [_vp, C.c_int, C.c_int, _vp]),
     "tsr_tp_allreduce": (C.c_int, [_vp, _vp, _u64, _vp]),
+    "tsr_tp_reduce_allreduce": (C.c_int, [_vp, _vp, _u64, _vp, _u64, _vp]),
     "tsr_tp_error_count": (C.c_int, [_vp, C.POINTER(C.c_uint32)]),
 }
 

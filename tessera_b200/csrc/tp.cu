@@ -50,7 +50,7 @@ __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) 
 }
 
 __global__ void __launch_bounds__(256)
-tp_allreduce_kernel(float* __restrict__ data, size_t count, Peers peers, int rank, int world,
+tp_allreduce_kernel(const float* src, int split, float* dst, size_t count, Peers peers, int rank, int world,
                     size_t capacity, int chunks_cap, unsigned int* my_count, unsigned int* error) {
   __shared__ unsigned int s_epoch;
   const int chunk = blockIdx.x;
@@ -62,7 +62,19 @@ tp_allreduce_kernel(float* __restrict__ data, size_t count, Peers peers, int ran
   const bool active = idx < count;
   float4 mine = make_float4(0.f, 0.f, 0.f, 0.f);
   if (active) {
-    mine = *reinterpret_cast<const float4*>(data + idx);
+    if (split == 1) {
+      mine = *reinterpret_cast<const float4*>(src + idx);
+    } else {
+      // the split-K partial regions of a row-parallel projection, added in region
+      // order exactly as gemm_vec_reduce adds them (starting from 0.0f)
+      for (int s = 0; s < split; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(src + static_cast<size_t>(s) * count + idx);
+        mine.x += v.x;
+        mine.y += v.y;
+        mine.z += v.z;
+        mine.w += v.w;
+      }
+    }
     // push: my partial into slot `rank` of every rank (my own included)
     for (int p = 0; p < world; ++p) {
       float* dst = peers.slots[p] + parity_off + static_cast<size_t>(rank) * capacity + idx;
@@ -97,7 +109,7 @@ tp_allreduce_kernel(float* __restrict__ data, size_t count, Peers peers, int ran
       acc.z += v.z;
       acc.w += v.w;
     }
-    *reinterpret_cast<float4*>(data + idx) = acc;
+    *reinterpret_cast<float4*>(dst + idx) = acc;
   }
   if (threadIdx.x == 0) my_count[chunk] = epoch;
 }
@@ -209,9 +221,23 @@ int tsr_tp_attach_local(tsr_tp_comm* c, int peer_rank, int peer_device, void* pe
   return tsr::kOk;
 }
 
+namespace {
+int launch_allreduce(tsr_tp_comm* c, const float* src, uint64_t split, float* dst, uint64_t count, void* stream);
+}
+
 int tsr_tp_allreduce(tsr_tp_comm* c, float* data, uint64_t count, void* stream) {
-  if (!c || !data || count == 0 || count > c->capacity || count % 4 != 0 ||
-      (reinterpret_cast<uintptr_t>(data) & 15u))
+  return launch_allreduce(c, data, 1, data, count, stream);
+}
+
+int tsr_tp_reduce_allreduce(tsr_tp_comm* c, const float* partials, uint64_t split, float* out, uint64_t count,
+                            void* stream) {
+  return launch_allreduce(c, partials, split, out, count, stream);
+}
+
+namespace {
+int launch_allreduce(tsr_tp_comm* c, const float* src, uint64_t split, float* data, uint64_t count, void* stream) {
+  if (!c || !src || !data || count == 0 || count > c->capacity || count % 4 != 0 || split == 0 || split > 65535 ||
+      (reinterpret_cast<uintptr_t>(data) & 15u) || (reinterpret_cast<uintptr_t>(src) & 15u))
     return tsr::kInvalidArgument;
   // The current device is per host thread; one thread may drive several ranks.
   if (cudaSetDevice(c->device) != cudaSuccess) return tsr::kDeviceError;
@@ -223,9 +249,11 @@ int tsr_tp_allreduce(tsr_tp_comm* c, float* data, uint64_t count, void* stream) 
   }
   const unsigned grid = static_cast<unsigned>((count + kChunkFloats - 1) / kChunkFloats);
   tp_allreduce_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      data, count, peers, c->rank, c->world, c->capacity, c->chunks, c->counts(), c->error());
+      src, static_cast<int>(split), data, count, peers, c->rank, c->world, c->capacity, c->chunks, c->counts(),
+      c->error());
   return tsr::check_launch();
 }
+}  // namespace
 
 int tsr_tp_error_count(tsr_tp_comm* c, uint32_t* count) {
   if (!c || !count) return tsr::kInvalidArgument;

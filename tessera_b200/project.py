@@ -100,6 +100,21 @@ class Projector:
                                                      scalars=[m, n, k, split]))
         self._reduce(part, out, total, split)
 
+    def ProjectGemvPartials(self, dtype: str, a, w, m, n, k):
+        """The GEMV half of ProjectGemvDevice: launches gemm_*_vec and returns (partials, split)
+        without the gemm_vec_reduce, for a caller that fuses the reduce into the tensor-parallel
+        all-reduce (TpComm.reduce_allreduce).  No reference counterpart."""
+        gemm = self.kernel(GemmKernelName(dtype))
+        if gemm is None or not gemm.Id().endswith("_vec"):
+            raise StatusError(StatusCode.UnsupportedFeature, dtype)
+        self.last_kernel = gemm.Id()
+        total = m * n
+        split = GemmVecSplit(total, k)
+        part = self._part(split * total * 4)
+        self.backend.LaunchKernel(gemm, KernelLaunch(grid_x=(total + 7) // 8, grid_y=split, buffers=[a, w, part],
+                                                     scalars=[m, n, k, split]))
+        return part, split
+
     def ProjectGemvRowsDevice(self, gemm, a, w, out, m, n, k) -> None:
         """internal.hpp:154-199."""
         total = m * n

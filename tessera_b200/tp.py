@@ -54,6 +54,11 @@ class TpComm:
     def allreduce(self, data_ptr: int, count: int, stream: int) -> None:
         capi.check(self.lib.tsr_tp_allreduce(self.comm, data_ptr, count, stream), "tsr_tp_allreduce")
 
+    def reduce_allreduce(self, partials_ptr: int, split: int, out_ptr: int, count: int, stream: int) -> None:
+        """Split-K reduce of `split` regions of `count` floats fused with the all-reduce."""
+        capi.check(self.lib.tsr_tp_reduce_allreduce(self.comm, partials_ptr, split, out_ptr, count, stream),
+                   "tsr_tp_reduce_allreduce")
+
     def error_count(self) -> int:
         n = C.c_uint32()
         capi.check(self.lib.tsr_tp_error_count(self.comm, C.byref(n)))

@@ -41,6 +41,21 @@ def test_single_rank_is_the_identity(backend):
     comm.close()
 
 
+@pytest.mark.parametrize("split", [1, 4, 5])
+def test_fused_split_reduce_on_one_rank_equals_vec_reduce(backend, oracle, split):
+    """tsr_tp_reduce_allreduce at world 1 is gemm_vec_reduce: same order, same bits."""
+    comm = TpComm(0, 0, 1, 5120)
+    parts = np.random.default_rng(split).standard_normal((split, 5120)).astype(np.float32)
+    src = backend.upload(parts.reshape(-1))
+    out = backend.AllocateBuffer(5120 * 4)
+    comm.reduce_allreduce(src.Handle(), split, out.Handle(), 5120, backend.stream())
+    got = backend.download(out, np.float32, 5120)
+    want = oracle.gemm_vec_reduce(parts) if split > 1 else parts[0]
+    assert np.array_equal(got, want)
+    assert comm.error_count() == 0
+    comm.close()
+
+
 def test_wait_for_a_silent_peer_gives_up_with_a_status(backend):
     """Rank 1 never launches: rank 0's wait runs out, the kernel returns and
     the communicator reports it; the context stays usable."""
@@ -80,6 +95,22 @@ def test_ranks_in_one_process(world):
         for r in range(world):
             got = backends[r].download(bufs[r], np.float32, n)
             assert np.array_equal(got, want), (it, r)
+    # fused split-K reduce + all-reduce: region-order sums per rank, then the rank-order sum
+    split = 4
+    regions = [(g.standard_normal((split, 5120))).astype(np.float32) for _ in range(world)]
+    srcs = [backends[r].upload(regions[r].reshape(-1)) for r in range(world)]
+    outs = [backends[r].AllocateBuffer(5120 * 4) for r in range(world)]
+    for r in range(world):
+        comms[r].reduce_allreduce(srcs[r].Handle(), split, outs[r].Handle(), 5120, backends[r].stream())
+    local = []
+    for r in range(world):
+        acc = np.zeros(5120, dtype=np.float32)
+        for s_ in range(split):
+            acc = acc + regions[r][s_]
+        local.append(acc)
+    want = rank_order_sum(local)
+    for r in range(world):
+        assert np.array_equal(backends[r].download(outs[r], np.float32, 5120), want), r
     assert all(c.error_count() == 0 for c in comms)
     for b in backends:
         b.Synchronize()
