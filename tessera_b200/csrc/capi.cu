@@ -11,6 +11,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <unordered_map>
 #include <string>
 
 #include "launch.h"
@@ -105,6 +106,23 @@ bool pdl_allowed(cudaStream_t stream, const void* read_ptr, size_t read_bytes, c
   }
   *slot = Last{stream, static_cast<const unsigned char*>(out_ptr), out_bytes};
   return ok;
+}
+
+int allow_dynamic_smem(const void* kernel, int bytes) {
+  static std::mutex mutex;
+  static std::unordered_map<const void*, unsigned long long> done;  // kernel -> device bit mask
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return kDeviceError;
+  const unsigned long long bit = 1ull << (dev & 63);
+  std::lock_guard<std::mutex> lock(mutex);
+  unsigned long long& mask = done[kernel];
+  if (mask & bit) return kOk;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return kDeviceError;
+  }
+  mask |= bit;
+  return kOk;
 }
 
 }  // namespace tsr

@@ -561,11 +561,7 @@ int launch_umma_impl(const UmmaParams& p, const RingMaps& maps, cudaStream_t st)
   const int tok_pad = ((p.m < kMaxTokens ? p.m : kMaxTokens) + 7) & ~7;
   const size_t ring = RING ? static_cast<size_t>(kRawStages) * RingFmt<FMT>::kStagePitch : 0;
   const size_t smem = 1024 + ring + kBufs * kASlabBytes + kBufs * static_cast<size_t>(2 * tok_pad) * kSlab * 2 + 256;
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(gemm_umma_kernel<FMT, RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    attr = true;
-  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemm_umma_kernel<FMT, RING>), 227 * 1024)) return rc;
   const dim3 grid(static_cast<unsigned>((p.n + kTileM - 1) / kTileM),
                   static_cast<unsigned>((p.m + kMaxTokens - 1) / kMaxTokens));
   gemm_umma_kernel<FMT, RING><<<grid, kUmmaThreads, smem, st>>>(maps.weights, maps.scales, p);

@@ -567,12 +567,7 @@ int launch_f16(const void* w, F16Params p, uint64_t n, uint64_t k, cudaStream_t 
   p.cper = static_cast<int>(best_cper);
   MapPair maps;
   if (int rc = f16_tensor_maps(FMT, w, n, k, plan.rgs, &maps)) return rc;
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(gemv_f16_staged_kernel<FMT, NCG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         kMaxSmem);
-    attr = true;
-  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_f16_staged_kernel<FMT, NCG>), kMaxSmem)) return rc;
   const uint64_t th = 16u * plan.rgs;
   const dim3 grid(static_cast<unsigned>(((n + th - 1) / th) * best_split));
   const size_t w_bytes = FMT == kFmtMxfp4 ? n * (k / 2) + n * (k / 32) : n * k;

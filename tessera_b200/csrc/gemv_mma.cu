@@ -70,8 +70,6 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   const int row0 = blockIdx.x * kTileRows;
   const int b0 = blockIdx.y * p.per;
   const bool producer = (tid == kConsumerThreads);
-  unsigned long long* tr = p.trace ? p.trace + (blockIdx.y * gridDim.x + blockIdx.x) * 64 : nullptr;
-  if (tr && tid == 0) tr[0] = gtime();
 
   if (tid < 4) reinterpret_cast<uint32_t*>(empty + p.stages)[tid] = 0u;
   if (producer) {
@@ -93,7 +91,6 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
       }
     }
   };
-  if (tr && tid == 0) tr[1] = gtime();
   if (p.pdl) {
     // Weights are not written by the kernel ahead of us (the launcher checked):
     // start their prefetch; the wait for that kernel's results is inside the staging.
@@ -103,7 +100,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
     if (!p.pdl) prologue();
   };
   if (!(p.debug & 1)) {
-    stage_activations<8>(p, b0 * kBlockElems, act, sums, cs, deferred_prologue, tr);
+    stage_activations<8>(p, b0 * kBlockElems, act, sums, cs, deferred_prologue);
   } else {
     if (p.pdl) {
       pdl_wait();
@@ -112,7 +109,6 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
     deferred_prologue();
   }
   __syncthreads();
-  if (tr && tid == 0) tr[2] = gtime();
 
   if (warp == kConsumerWarps) {
     if (lane == 0) {
@@ -131,7 +127,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   const int gid = lane >> 2, tig = lane & 3;
   const int bx = warp >= p.rgs ? 1 : 0, rg = warp - bx * p.rgs;  // warp set bx takes chunks c = bx (mod 2)
   const int rowA = rg * 16 + gid;
-  constexpr uint32_t kNib = 0x0F0F0F0Fu;
+  constexpr uint32_t kNib = 0x0F0F0F0Fu, kHiNib = 0xF0F0F0F0u;
 
   // Per-thread fragment addresses.  A lane whose column does not exist reads
   // the zero page with zero strides, so the loop needs no predicates.
@@ -164,10 +160,8 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   const int owned = (p.stages + 1 - bx) >> 1;
   int ring_idx = 0, ring_round = 0;
   for (int c = bx; c < nchunks; c += 2) {
-    if (tr && tid == 0 && c < 24) tr[8 + 2 * c] = gtime();
     const int slot = bx + 2 * ring_idx;
     if (!mbar_wait(&full[slot], ring_round & 1, &g_wait_timeouts)) break;
-    if (tr && tid == 0 && c < 24) tr[9 + 2 * c] = gtime();
     const unsigned char* st = smem + static_cast<size_t>(slot) * kStageBytes + row_off;
     const int blocks_here = (p.debug & 2) ? 0 : min(kBoxBlocks, p.per - c * kChunkBlocks);
 #pragma unroll
@@ -183,11 +177,13 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
         const uint32_t scB[2] = {hb.y & 0x3F3F3F3Fu, (hb.w & kNib) | ((hb.y >> 2) & 0x30303030u)};
         const uint32_t mnB[2] = {hb.z & 0x3F3F3F3Fu, ((hb.w >> 4) & kNib) | ((hb.z >> 2) & 0x30303030u)};
 
-        int t1[NCG][4];
+        // t1: low-nibble sub-blocks; t16: high-nibble sub-blocks, whose weights enter the MMA
+        // as 16 q (the nibble masked in place, no shift); the 16 is taken out again below
+        int t1[NCG][4], t16[NCG][4];
 #pragma unroll
         for (int g = 0; g < NCG; ++g)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) t1[g][e] = 0;
+          for (int e = 0; e < 4; ++e) t1[g][e] = t16[g][e] = 0;
 
 #pragma unroll
         for (int grp = 0; grp < 4; ++grp) {
@@ -204,19 +200,23 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
             const uint2 fh = lds64(ab + (2 * grp + 1) * act_sb[g]);
             int pl[4], ph[4];
             mma_u8s8_zero(pl, qa.x & kNib, qb.x & kNib, qa.y & kNib, qb.y & kNib, fl.x, fl.y);
-            mma_u8s8_zero(ph, (qa.x >> 4) & kNib, (qb.x >> 4) & kNib, (qa.y >> 4) & kNib,
-                          (qb.y >> 4) & kNib, fh.x, fh.y);
-            t1[g][0] += sclA * pl[0] + schA * ph[0];
-            t1[g][1] += sclA * pl[1] + schA * ph[1];
-            t1[g][2] += sclB * pl[2] + schB * ph[2];
-            t1[g][3] += sclB * pl[3] + schB * ph[3];
+            mma_u8s8_zero(ph, qa.x & kHiNib, qb.x & kHiNib, qa.y & kHiNib, qb.y & kHiNib, fh.x, fh.y);
+            t1[g][0] += sclA * pl[0];
+            t1[g][1] += sclA * pl[1];
+            t1[g][2] += sclB * pl[2];
+            t1[g][3] += sclB * pl[3];
+            t16[g][0] += schA * ph[0];
+            t16[g][1] += schA * ph[1];
+            t16[g][2] += schB * ph[2];
+            t16[g][3] += schB * ph[3];
           }
         }
         // min term: k slots 0..7 are the sub-blocks; lanes tig 0/1 hold mins 0..3 / 4..7
         const uint32_t am = (mnA[0] & mask0) | (mnA[1] & mask1);
         const uint32_t bm = (mnB[0] & mask0) | (mnB[1] & mask1);
-        const float dA = fp16_bits_to_float(ha.x & 0xFFFFu), mA = fp16_bits_to_float(ha.x >> 16);
-        const float dB = fp16_bits_to_float(hb.x & 0xFFFFu), mB = fp16_bits_to_float(hb.x >> 16);
+        // the sums below are 16 x the block's integer dot product (all of them < 2^31): d / 16 is exact
+        const float dA = fp16_bits_to_float(ha.x & 0xFFFFu) * 0.0625f, mA = fp16_bits_to_float(ha.x >> 16);
+        const float dB = fp16_bits_to_float(hb.x & 0xFFFFu) * 0.0625f, mB = fp16_bits_to_float(hb.x >> 16);
 #pragma unroll
         for (int g = 0; g < NCG; ++g) {
           const unsigned char* sp = sum_t[g] + bl * sum_blk[g];
@@ -226,10 +226,10 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
           mma_u8s8_zero(r0, am, bm, 0u, 0u, s0, 0u);
           mma_u8s8_zero(r1, am, bm, 0u, 0u, s1, 0u);
           const float2 c2 = *reinterpret_cast<const float2*>(cs_t + bl * kMaxCols + g * 8);
-          const float u0 = fmaf(dA, static_cast<float>(t1[g][0]), -mA * static_cast<float>(r0[0] + 128 * r1[0]));
-          const float u1 = fmaf(dA, static_cast<float>(t1[g][1]), -mA * static_cast<float>(r0[1] + 128 * r1[1]));
-          const float u2 = fmaf(dB, static_cast<float>(t1[g][2]), -mB * static_cast<float>(r0[2] + 128 * r1[2]));
-          const float u3 = fmaf(dB, static_cast<float>(t1[g][3]), -mB * static_cast<float>(r0[3] + 128 * r1[3]));
+          const float u0 = fmaf(dA, static_cast<float>(16 * t1[g][0] + t16[g][0]), -mA * static_cast<float>(r0[0] + 128 * r1[0]));
+          const float u1 = fmaf(dA, static_cast<float>(16 * t1[g][1] + t16[g][1]), -mA * static_cast<float>(r0[1] + 128 * r1[1]));
+          const float u2 = fmaf(dB, static_cast<float>(16 * t1[g][2] + t16[g][2]), -mB * static_cast<float>(r0[2] + 128 * r1[2]));
+          const float u3 = fmaf(dB, static_cast<float>(16 * t1[g][3] + t16[g][3]), -mB * static_cast<float>(r0[3] + 128 * r1[3]));
           o[g][0] = fmaf(c2.x, u0, o[g][0]);
           o[g][1] = fmaf(c2.y, u1, o[g][1]);
           o[g][2] = fmaf(c2.x, u2, o[g][2]);
@@ -245,7 +245,6 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
     }
   }
 
-  if (tr && tid == 0) tr[3] = gtime();
   // The two warps of a row group (even and odd chunks) add their partial sums; the
   // digit columns of each activation row are then combined through shared memory.
   if (bx == 1) {
@@ -277,7 +276,6 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
       cout[static_cast<size_t>(i) * p.n + row0 + rr] = v;
     }
   }
-  if (tr && tid == 0) tr[4] = gtime();
 }
 
 // ---- tensor-map cache: a map depends only on (base, rows, blocks per row, box rows)
@@ -351,12 +349,7 @@ int launch_staged(const void* w, StagedParams p, uint64_t n, uint64_t nb, uint64
   p.stages = plan.stages;
   CUtensorMap map;
   if (int rc = q4k_tensor_map(w, n, nb, plan.rgs, &map)) return rc;
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(gemv_q4k_staged_kernel<NCG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         kMaxSmem);
-    attr = true;
-  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q4k_staged_kernel<NCG>), kMaxSmem)) return rc;
   const uint64_t th = 16u * plan.rgs;
   const dim3 grid(static_cast<unsigned>((n + th - 1) / th), static_cast<unsigned>(split));
   const size_t w_bytes = n * nb * kQ4KBlockBytes;
@@ -411,8 +404,7 @@ int staged_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_
   const int ncols = static_cast<int>(m) * terms;
   StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
                  static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0, 4,
-                 static_cast<unsigned long long>(m * n),
-                 reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(std::strtoull(std::getenv("TSR_TRACE_PTR") ? std::getenv("TSR_TRACE_PTR") : "0", nullptr, 10)))};
+                 static_cast<unsigned long long>(m * n)};
   if (ncols <= 8) return launch_staged<1>(w, p, n, nb, split, nchunks, st);
   return launch_staged<2>(w, p, n, nb, split, nchunks, st);
 }

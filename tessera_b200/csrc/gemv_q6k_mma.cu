@@ -228,7 +228,7 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
     if (!p.pdl) prologue();
   };
   if (!(p.debug & 1)) {
-    stage_activations<kGroups>(p, b0 * kBlockElems, act, sums, cs, deferred_prologue, nullptr);
+    stage_activations<kGroups>(p, b0 * kBlockElems, act, sums, cs, deferred_prologue);
   } else {
     if (p.pdl) {
       pdl_wait();
@@ -412,11 +412,7 @@ int launch_q6k(const void* w, StagedParams p, int odd_shift, uint64_t n, uint64_
   p.stages = plan.stages;
   MapPair maps;
   if (int rc = q6k_tensor_maps(w, n, nb, plan.rgs, &maps)) return rc;
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(gemv_q6k_staged_kernel<NCG>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
-    attr = true;
-  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q6k_staged_kernel<NCG>), kMaxSmem)) return rc;
   const uint64_t th = 16u * plan.rgs;
   const dim3 grid(static_cast<unsigned>((n + th - 1) / th), static_cast<unsigned>(split));
   const size_t w_bytes = n * nb * kQ6KBlockBytes;
@@ -442,7 +438,7 @@ int staged_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_
   const int ncols = static_cast<int>(m) * terms;
   StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
                  static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0, 4,
-                 static_cast<unsigned long long>(m * n), nullptr};
+                 static_cast<unsigned long long>(m * n)};
   const int odd_shift = static_cast<int>((nb * kQ6KBlockBytes) & 15u);
   if (ncols <= 8) return launch_q6k<1>(w, p, odd_shift, n, nb, split, st);
   return launch_q6k<2>(w, p, odd_shift, n, nb, split, st);

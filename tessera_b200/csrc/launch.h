@@ -78,6 +78,11 @@ inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, di
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 #endif
+// Raises the dynamic shared-memory limit of `kernel` on the current device, once per
+// (kernel, device): the attribute belongs to the device, and one process may drive
+// several GPUs (the reference runs its tensor-parallel ranks as threads).
+int allow_dynamic_smem(const void* kernel, int bytes);
+
 // True when a kernel that reads [read_ptr, +read_bytes) before its pdl_wait()
 // may overlap the previous launch on `stream`; records [out_ptr, +out_bytes) as
 // the range this launch writes.

@@ -30,14 +30,8 @@ struct StagedParams {
   int pdl;     // launched as a programmatic dependent: prefetch weights, then wait for the stream
   int rgs;     // 16-row groups per CTA (1..4): the tile has 16*rgs rows, the CTA 2*rgs consumer warps
   unsigned long long region_stride;
-  unsigned long long* trace;  // optional per-CTA timeline (experiments only)
 };
 
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
 __device__ __forceinline__ uint4 lds128(const unsigned char* p) {
   return *reinterpret_cast<const uint4*>(p);
 }
@@ -172,8 +166,7 @@ __device__ __forceinline__ void stage_sums(const StagedParams& p, int i, int bl,
 template <int GROUPS, typename AfterFirstLoads>
 __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0, unsigned char* act,
                                                   unsigned char* sums, float* cs,
-                                                  AfterFirstLoads after_first_loads,
-                                                  unsigned long long* tr = nullptr) {
+                                                  AfterFirstLoads after_first_loads) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // The producer warp only issues the weight copies: its first TMA instruction
   // can wait on the descriptor fetch, which must not hold up a share of the staging.
@@ -199,7 +192,6 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
     pdl_wait();
     pdl_trigger();
   }
-  if (tr && threadIdx.x == 0) tr[5] = gtime();
 #pragma unroll 1
   for (int base = warp; base < items; base += kWarps * kStageBatch) {
     float4 x0[kStageBatch], x1[kStageBatch];
@@ -217,17 +209,14 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
         x1[u] = __ldg(src + 32 + lane);
       }
     }
-    if (tr && lane == 0 && base == warp) tr[28 + warp] = gtime();
 #pragma unroll
     for (int u = 0; u < kStageBatch; ++u)
       if (base + u * kWarps < items) stage_digits(p, row[u], blk[u], x0[u], x1[u], act, cs, lane);
-    if (tr && lane == 0 && base == warp) tr[40 + warp] = gtime();
     __syncwarp();
 #pragma unroll
     for (int u = 0; u < kStageBatch; ++u)
       if (base + u * kWarps < items) stage_sums<GROUPS>(p, row[u], blk[u], act, sums, lane);
   }
-  if (tr && lane == 0) tr[50 + warp] = gtime();
 }
 
 // ---- host side: tile height and ring depth for one launch

@@ -95,6 +95,19 @@ def test_ranks_in_one_process(world):
         for r in range(world):
             got = backends[r].download(bufs[r], np.float32, n)
             assert np.array_equal(got, want), (it, r)
+    # every device of the process runs the staged kernels (their shared-memory limit is a
+    # per-device attribute): the same small projection on each rank's backend
+    from oracle.oracle import Oracle
+    from tessera_b200 import synth
+    from tessera_b200.project import Projector, Q4K
+    a = synth.activations(1, 1024, seed=9)
+    w = synth.q4k_weights(96, 1024, seed=9)
+    ref = Oracle().gemm_q4k(a, w, 1, 96, 1024)
+    for r in range(world):
+        out = backends[r].AllocateBuffer(96 * 4)
+        Projector(backends[r]).ProjectBatch(Q4K, backends[r].upload(a), backends[r].upload(w), out, 1, 96, 1024)
+        got = backends[r].download(out, np.float32, 96).reshape(1, 96)
+        assert np.abs(got - ref).max() / np.abs(ref).max() < 2e-5, r
     # fused split-K reduce + all-reduce: region-order sums per rank, then the rank-order sum
     split = 4
     regions = [(g.standard_normal((split, 5120))).astype(np.float32) for _ in range(world)]
