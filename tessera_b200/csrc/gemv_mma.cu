@@ -1,10 +1,11 @@
 // Staged tensor-pipe GEMV for Q4_K weights (m = 1..8 activation rows).
 //
-// Data path, per CTA (one 64-row tile of W, one split chunk of k):
-//   HBM --TMA 3-D box (64 rows x 2 blocks x 144 B per stage)--> shared
+// Data path, per CTA (one tile of 16..64 rows of W, one split chunk of k):
+//   HBM --TMA 3-D box (tile rows x 2 blocks x 144 B per stage)--> shared
 //   memory ring --LDS.64 per thread--> packed nibbles --one LOP3 per four
 //   weights--> u8 A fragments --mma.sync m16n8k32 (s32 accumulate)--> registers
 //   --per-sub-block integer scale, per-block fp32 scale--> C.
+// Tile height, CTAs per SM and ring depth come from staged_common.cuh::plan_staged.
 //
 // Weights are the A operand (16 weight rows per warp), activations the B
 // operand.  Each 256-element block of an fp32 activation row is expanded,

@@ -1,6 +1,6 @@
 // Staged tensor-pipe GEMV for Q6_K weights (m = 1..8 activation rows).
 //
-// Same structure as the Q4_K kernel (gemv_mma.cu): one CTA per 64-row tile
+// Same structure as the Q4_K kernel (gemv_mma.cu): one CTA per tile of 16..64 rows
 // and split chunk, a TMA-fed ring of shared-memory stages, weights as the A
 // operand of an int8 mma.sync, activations as signed base-256 digit columns,
 // integer group scales applied to the s32 partial sums, the fp16 block scale

@@ -1,6 +1,8 @@
 // Pieces shared by the staged tensor-pipe GEMV kernels (Q4_K: gemv_mma.cu,
-// Q6_K: gemv_q6k_mma.cu): launch parameters, shared-memory loads, the int8
-// digit expansion of the activations and its staging into shared memory.
+// Q6_K: gemv_q6k_mma.cu, MXFP4/FP8: gemv_f16_mma.cu): launch parameters,
+// shared-memory loads, the int8 digit expansion of the activations and its
+// staging into shared memory (the two K-quant kernels), and the host-side
+// launch plan (tile height, CTAs per SM, ring depth) that all three use.
 #pragma once
 
 #include <cuda_runtime.h>
