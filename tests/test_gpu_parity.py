@@ -281,6 +281,48 @@ def test_f16_staged_projection_matches_oracle(backend, oracle, dtype, m, n, k):
     assert rel_err(got, ref) < 2e-5
 
 
+def _sample_rows(n, count=96, seed=0):
+    rows = np.random.default_rng(seed).choice(n, size=count, replace=False)
+    return np.unique(np.concatenate([rows, [0, 1, 63, 64, n - 65, n - 64, n - 2, n - 1]]))
+
+
+@pytest.mark.parametrize("dtype,m,n,k", [
+    ("q4k", 1, 17408, 5120),    # the single-GEMV measurement config
+    ("q4k", 1, 5120, 17408),    # split 4, 17 blocks per chunk
+    ("q6k", 1, 5120, 17408),
+    ("mxfp4", 1, 17408, 5120), ("mxfp4", 4, 5120, 17408),   # cluster K split on the second
+    ("fp8", 4, 17408, 5120), ("fp8", 1, 5120, 17408),
+    ("mxfp4", 16, 5120, 5120), ("fp8", 48, 17408, 5120),    # staged in chunks of 8; tcgen05 tile
+])
+def test_full_size_projection_on_sampled_rows(backend, oracle, dtype, m, n, k):
+    """The measured shapes at full size: the whole projection runs on the GPU, and about a
+    hundred weight rows (random ones plus the edges of the first and last tiles) are checked
+    against the oracle run on just those rows (a row of C depends on one row of W only)."""
+    a = synth.activations(m, k, seed=n % 97 + m)
+    rows = _sample_rows(n, seed=m)
+    out = backend.AllocateBuffer(m * n * 4)
+    ab = backend.upload(a)
+    if dtype in ("q4k", "q6k"):
+        w = synth.q4k_weights(n, k, seed=21) if dtype == "q4k" else synth.q6k_weights(n, k, seed=21)
+        Projector(backend).ProjectBatch(dtype, ab, backend.upload(w), out, m, n, k)
+        sub = np.ascontiguousarray(w.reshape(n, -1)[rows]).reshape(-1)
+        ref = (oracle.gemm_q4k if dtype == "q4k" else oracle.gemm_q6k)(a, sub, m, len(rows), k)
+    elif dtype == "mxfp4":
+        w = synth.mxfp4_weights(n, k, seed=21)
+        run_named(backend, "gemm_mxfp4", [ab, backend.upload(w), out], [m, n, k])
+        nib, sc = w[: n * k // 2].reshape(n, -1), w[n * k // 2:].reshape(n, -1)
+        sub = np.concatenate([np.ascontiguousarray(nib[rows]).reshape(-1), np.ascontiguousarray(sc[rows]).reshape(-1)])
+        ref = oracle.gemm_mxfp4(a, sub, m, len(rows), k)
+    else:
+        w, s = synth.fp8_weights(n, k, seed=21)
+        run_named(backend, "gemm_fp8", [ab, backend.upload(w), backend.upload(s), out], [m, n, k])
+        sub = np.ascontiguousarray(w.reshape(n, k)[rows]).reshape(-1)
+        ref = oracle.gemm_fp8(a, sub, np.ascontiguousarray(s[rows]), m, len(rows), k)
+    got = backend.download(out, np.float32, m * n).reshape(m, n)
+    assert np.isfinite(got).all()
+    assert rel_err(got[:, rows], ref) < bound(dtype, m, k)
+
+
 @pytest.mark.parametrize("m", [1, 4, 16])
 def test_w4a8_qdq_then_projection(backend, oracle, m):
     """The W4A8 variant of the measurement configs: per-token FP8
