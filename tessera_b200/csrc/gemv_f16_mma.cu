@@ -28,6 +28,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "codec.cuh"
@@ -44,7 +45,6 @@ namespace {
 using namespace staged;
 
 constexpr int kFmtMxfp4 = 0, kFmtFp8 = 1;
-constexpr int kThreads = kStagedThreads;
 constexpr int kSegBytes = 128;
 constexpr int kGroupStageBytes = 2 * 16 * kSegBytes;  // one 16-row group of one stage: 4096
 constexpr int kGroupScaleBytes = 16 * 16;             // MXFP4: 16 scale bytes per row and stage
@@ -183,8 +183,10 @@ __device__ __forceinline__ void stage_f16(const F16Params& p, int first, int nbl
   }
 }
 
-template <int FMT, int NCG>
-__global__ void __launch_bounds__(kThreads, 2)
+// SETS consumer warp sets (2, or 4 for launches with at most one CTA per SM: the sets split
+// the chunks of k among them, which shortens every warp's chain of dependent chunks).
+template <int FMT, int NCG, int SETS>
+__global__ void __launch_bounds__((SETS * 4 + 1) * 32, SETS == 2 ? 2 : 1)
 gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                        const F16Params p) {
   constexpr int G = Fmt<FMT>::kGroup;
@@ -194,7 +196,7 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
   // the swizzle pattern is a function of the address: stages start on 1 KiB boundaries
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kConsumerWarps = 2 * p.rgs, kConsumerThreads = kConsumerWarps * 32;
+  const int kConsumerWarps = SETS * p.rgs, kConsumerThreads = kConsumerWarps * 32;
   const int kTileRows = 16 * p.rgs, kStageBytes = p.rgs * kGroupStageBytes;
   const int kScaleBytes = FMT == kFmtMxfp4 ? p.rgs * kGroupScaleBytes : 0;
   // K split across the CTAs of a cluster: rank r takes chunks [r * cper, (r + 1) * cper)
@@ -207,8 +209,8 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
   unsigned char* scales = smem + static_cast<size_t>(p.stages) * kStageBytes;
   unsigned char* act = scales + static_cast<size_t>(p.stages) * kScaleBytes;
   float* cs = reinterpret_cast<float*>(act + static_cast<size_t>(p.pblocks) * kBlockElems * p.ncols * 2);
-  float* xchg = cs + static_cast<size_t>(p.pblocks) * kMaxCols;  // [row groups][32 lanes][NCG*4]
-  float* outbuf = xchg + p.rgs * 32 * NCG * 4;                    // [tile rows][NCG*8]
+  float* xchg = cs + static_cast<size_t>(p.pblocks) * kMaxCols;  // [SETS - 1][row groups][32 lanes][NCG*4]
+  float* outbuf = xchg + (SETS - 1) * p.rgs * 32 * NCG * 4;       // [tile rows][NCG*8]
   uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
   uint64_t* empty = full + p.stages;
   const unsigned char* zero_page = reinterpret_cast<const unsigned char*>(empty + p.stages);  // 16 zero bytes
@@ -259,7 +261,7 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
     }
     if (lane == 0) {
       for (int c = p.stages; c < nchunks; ++c) {
-        const RingUse use = ring_use(c, p.stages);
+        const RingUse use = ring_use(c, p.stages, SETS);
         const int s = use.slot;
         if (!mbar_wait(&empty[s], (use.round & 1) ^ 1, &g_f16_wait_timeouts)) break;
         issue_chunk(c, s);
@@ -273,7 +275,7 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
   }
 
   const int gid = lane >> 2, tig = lane & 3;
-  const int bx = warp >= p.rgs ? 1 : 0, rg = warp - bx * p.rgs;  // warp set bx takes chunks c = bx (mod 2)
+  const int bx = warp / p.rgs, rg = warp - bx * p.rgs;  // warp set bx takes chunks c = bx (mod SETS)
   const int rowA = rg * 16 + gid;
   // Per-thread fragment addresses.  A lane whose column does not exist reads
   // the zero page with a zero stride, so the loop needs no predicates.
@@ -299,8 +301,8 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
 
   bool failed = false;
   int c = bx;
-  // this set's ring slots bx, bx + 2, ... in turn (see ring_use)
-  const int owned = (p.stages + 1 - bx) >> 1;
+  // this set's ring slots bx, bx + SETS, ... in turn (see ring_use)
+  const int owned = (p.stages - bx + SETS - 1) / SETS;
   int ring_idx = 0, ring_round = 0;
   for (int first = 0; first < nblocks; first += p.pblocks) {
     const int nblk = min(p.pblocks, nblocks - first);
@@ -308,9 +310,9 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
     stage_f16<G>(p, kb0 + first, nblk, act, cs, warp, lane, kConsumerWarps);
     asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
     const int chunk_end = (first + nblk + kChunkBlocks - 1) / kChunkBlocks;
-    for (; c < chunk_end; c += 2) {
+    for (; c < chunk_end; c += SETS) {
       if (failed) continue;
-      const int slot = bx + 2 * ring_idx;
+      const int slot = bx + SETS * ring_idx;
       if (!mbar_wait(&full[slot], ring_round & 1, &g_f16_wait_timeouts)) {
         failed = true;
         continue;
@@ -399,11 +401,11 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
 
   // The two warps of a row group (even and odd chunks) add their partial sums; the
   // hi and lo columns of each activation row are then combined through shared memory.
-  if (bx == 1) {
+  if (bx > 0) {
 #pragma unroll
     for (int g = 0; g < NCG; ++g)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) xchg[((rg * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
+      for (int e = 0; e < 4; ++e) xchg[((((bx - 1) * p.rgs + rg) * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
   }
   asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
   if (bx == 0) {
@@ -413,7 +415,9 @@ gemv_f16_staged_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
       for (int e = 0; e < 4; ++e) {
         const int col = g * 8 + 2 * tig + (e & 1);
         const int rr = rowA + (e >> 1) * 8;
-        const float v = o[g][e] + xchg[((rg * 32 + lane) * NCG + g) * 4 + e];
+        float v = o[g][e];
+#pragma unroll
+        for (int sx = 0; sx < SETS - 1; ++sx) v += xchg[(((sx * p.rgs + rg) * 32 + lane) * NCG + g) * 4 + e];
         if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v;
       }
     }
@@ -495,15 +499,16 @@ int env_int(const char* name, int fallback) {
   return v ? std::atoi(v) : fallback;
 }
 
-template <int FMT, int NCG>
-int launch_f16(const void* w, F16Params p, uint64_t n, uint64_t k, cudaStream_t st) {
+// With `cost_only` the launch is planned but not issued, and its modelled time returned.
+template <int FMT, int NCG, int SETS>
+int launch_f16(const void* w, F16Params p, uint64_t n, uint64_t k, cudaStream_t st, double* cost_only) {
   constexpr int kChunkBlocks = Fmt<FMT>::kChunkElems / kBlockElems;
   const uint64_t nchunks_all = (static_cast<uint64_t>(p.nblocks) + kChunkBlocks - 1) / kChunkBlocks;
   const uint64_t per_block = static_cast<uint64_t>(kBlockElems) * p.ncols * 2;
   uint64_t max_blocks = (56u * 1024u) / per_block;
   max_blocks -= max_blocks % kChunkBlocks;
   if (max_blocks < 2u * kChunkBlocks) return kUnsupportedFeature;
-  static const int regs = kernel_registers(gemv_f16_staged_kernel<FMT, NCG>);
+  static const int regs = kernel_registers(gemv_f16_staged_kernel<FMT, NCG, SETS>);
   auto stage_bytes = [](int rgs) -> size_t {
     return static_cast<size_t>(rgs) * (kGroupStageBytes + (FMT == kFmtMxfp4 ? kGroupScaleBytes : 0));
   };
@@ -517,7 +522,7 @@ int launch_f16(const void* w, F16Params p, uint64_t n, uint64_t k, cudaStream_t 
   };
   auto fixed_for = [&](uint64_t pblocks) {
     return [=](int rgs) -> size_t {
-      return 1024 + pblocks * per_block + pblocks * kMaxCols * 4 + rgs * 32 * NCG * 4 * 4 +
+      return 1024 + pblocks * per_block + pblocks * kMaxCols * 4 + (SETS - 1) * rgs * 32 * NCG * 4 * 4 +
              16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128;
     };
   };
@@ -534,7 +539,7 @@ int launch_f16(const void* w, F16Params p, uint64_t n, uint64_t k, cudaStream_t 
     if (ks > 1 && (cper < 2 || cper * (ks - 1) >= nchunks_all)) continue;  // every rank has work
     const uint64_t pblocks = phase_blocks(cper * kChunkBlocks);
     StagedPlan cand{};
-    if (!plan_staged(n, ks, cper * kChunkBlocks, cper, 12, regs, fixed_for(pblocks), stage_bytes, &cand)) continue;
+    if (!plan_staged(n, ks, cper * kChunkBlocks, cper, 12, regs, fixed_for(pblocks), stage_bytes, &cand, SETS)) continue;
     // measured: a cluster launch with its two cluster barriers costs about 5 us
     // (2 CTAs) to 8 us (4 CTAs) over the plain one, so only a long k pays for it
     const double cost = cand.cost + (ks == 1 ? 0.0 : ks == 2 ? 5.0 : 8.0);
@@ -547,6 +552,10 @@ int launch_f16(const void* w, F16Params p, uint64_t n, uint64_t k, cudaStream_t 
     }
   }
   if (best_split == 0) return kUnsupportedFeature;
+  if (cost_only != nullptr) {
+    *cost_only = best_cost;
+    return kOk;
+  }
   auto fixed = fixed_for(best_pblocks);
   const int forced_rgs = env_int("TSR_RGS", 0);
   if (forced_rgs >= 1 && forced_rgs <= 4) {
@@ -554,7 +563,7 @@ int launch_f16(const void* w, F16Params p, uint64_t n, uint64_t k, cudaStream_t 
     plan.smem = fixed(forced_rgs) + plan.stages * stage_bytes(forced_rgs);
   }
   const int forced = env_int("TSR_STAGES", 0);
-  if (forced >= 2 && forced <= 16 &&
+  if (forced >= SETS && forced <= 16 &&
       fixed(plan.rgs) + forced * stage_bytes(plan.rgs) <= static_cast<size_t>(kMaxSmem)) {
     plan.stages = forced;
     plan.smem = fixed(plan.rgs) + forced * stage_bytes(plan.rgs);
@@ -567,17 +576,17 @@ int launch_f16(const void* w, F16Params p, uint64_t n, uint64_t k, cudaStream_t 
   p.cper = static_cast<int>(best_cper);
   MapPair maps;
   if (int rc = f16_tensor_maps(FMT, w, n, k, plan.rgs, &maps)) return rc;
-  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_f16_staged_kernel<FMT, NCG>), kMaxSmem)) return rc;
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_f16_staged_kernel<FMT, NCG, SETS>), kMaxSmem)) return rc;
   const uint64_t th = 16u * plan.rgs;
   const dim3 grid(static_cast<unsigned>(((n + th - 1) / th) * best_split));
   const size_t w_bytes = FMT == kFmtMxfp4 ? n * (k / 2) + n * (k / 32) : n * k;
   p.pdl = pdl_allowed(st, w, w_bytes, p.c, static_cast<size_t>(p.m) * n * 4) ? 1 : 0;
   if (env_int("TSR_PLAN_DEBUG", 0))
-    std::fprintf(stderr, "f16 plan fmt=%d m=%d n=%llu k=%llu: ksplit=%llu cper=%llu pblocks=%llu rgs=%d stages=%d smem=%zu grid=%u cost=%.2f\n",
-                 FMT, p.m, (unsigned long long)n, (unsigned long long)k, (unsigned long long)best_split,
+    std::fprintf(stderr, "f16 plan fmt=%d sets=%d m=%d n=%llu k=%llu: ksplit=%llu cper=%llu pblocks=%llu rgs=%d stages=%d smem=%zu grid=%u cost=%.2f\n",
+                 FMT, SETS, p.m, (unsigned long long)n, (unsigned long long)k, (unsigned long long)best_split,
                  (unsigned long long)best_cper, (unsigned long long)best_pblocks, plan.rgs, plan.stages, plan.smem,
                  grid.x, best_cost);
-  launch_kernel_cluster(gemv_f16_staged_kernel<FMT, NCG>, grid, dim3((2 * plan.rgs + 1) * 32), plan.smem, st,
+  launch_kernel_cluster(gemv_f16_staged_kernel<FMT, NCG, SETS>, grid, dim3((SETS * plan.rgs + 1) * 32), plan.smem, st,
                         p.pdl != 0, static_cast<unsigned>(best_split), maps.weights, maps.scales, p);
   return check_launch();
 }
@@ -591,8 +600,22 @@ int staged_f16(const float* a, const void* w, const float* scale, float* c, uint
     return kUnsupportedFeature;
   F16Params p{a, c, scale, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
               static_cast<int>(k / kBlockElems), 0, 0, static_cast<int>(2 * m), 0, 4, 1, 0};
-  if (m <= 4) return launch_f16<FMT, 1>(w, p, n, k, st);
-  return launch_f16<FMT, 2>(w, p, n, k, st);
+  // two consumer sets, or four when the model says the warps' own chains of chunks
+  // (not the SM's throughput) set the time: few CTAs, long k
+  auto run = [&](auto ncg) -> int {
+    constexpr int kNcg = decltype(ncg)::value;
+    double c2 = 0.0, c4 = 0.0;
+    const int r2 = launch_f16<FMT, kNcg, 2>(w, p, n, k, st, &c2);
+    const int r4 = launch_f16<FMT, kNcg, 4>(w, p, n, k, st, &c4);
+    const int forced_sets = env_int("TSR_SETS", 0);
+    const bool four = forced_sets == 4 ? r4 == kOk : forced_sets == 2 ? r2 != kOk && r4 == kOk
+                                                                      : r4 == kOk && (r2 != kOk || c4 + 0.3 < c2);
+    if (four) return launch_f16<FMT, kNcg, 4>(w, p, n, k, st, nullptr);
+    if (r2 != kOk) return r2;
+    return launch_f16<FMT, kNcg, 2>(w, p, n, k, st, nullptr);
+  };
+  if (m <= 4) return run(std::integral_constant<int, 1>{});
+  return run(std::integral_constant<int, 2>{});
 }
 
 }  // namespace

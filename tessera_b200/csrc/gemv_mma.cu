@@ -28,6 +28,7 @@
 
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "codec.cuh"
@@ -47,24 +48,25 @@ constexpr int kBoxBlocks = 2;   // Q4_K blocks per box row (pitch 288 B)
 constexpr int kChunkBlocks = kBoxBlocks;
 constexpr int kRowPitch = kBoxBlocks * kQ4KBlockBytes;
 constexpr int kGroupBytes = 16 * kRowPitch;  // one row group of one stage: 4608
-constexpr int kThreads = staged::kStagedThreads;
 
 using namespace staged;
 
-template <int NCG>
-__global__ void __launch_bounds__(kThreads, 2)
+// SETS consumer warp sets (2, or 4 for launches whose warps would otherwise each walk a long
+// chain of chunks on a mostly idle SM: the sets split the chunks of k among them).
+template <int NCG, int SETS>
+__global__ void __launch_bounds__((SETS * 4 + 1) * 32, SETS == 2 ? 2 : 1)
 gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kConsumerWarps = 2 * p.rgs, kConsumerThreads = kConsumerWarps * 32;
+  const int kConsumerWarps = SETS * p.rgs, kConsumerThreads = kConsumerWarps * 32;
   const int kTileRows = 16 * p.rgs, kStageBytes = p.rgs * kGroupBytes;
   const int nchunks = (p.per + kChunkBlocks - 1) / kChunkBlocks;
   const int nblk_pad = nchunks * kChunkBlocks;
   unsigned char* act = smem + static_cast<size_t>(p.stages) * kStageBytes;
   unsigned char* sums = act + static_cast<size_t>(nblk_pad) * p.ncols * 256;
   float* cs = reinterpret_cast<float*>(sums + static_cast<size_t>(nblk_pad) * p.ncols * 16);  // [block][kMaxCols]
-  float* xchg = cs + static_cast<size_t>(nblk_pad) * kMaxCols;  // [row groups][32 lanes][NCG*4]
-  float* outbuf = xchg + p.rgs * 32 * NCG * 4;  // [tile rows][NCG*8]
+  float* xchg = cs + static_cast<size_t>(nblk_pad) * kMaxCols;  // [SETS - 1][row groups][32 lanes][NCG*4]
+  float* outbuf = xchg + (SETS - 1) * p.rgs * 32 * NCG * 4;  // [tile rows][NCG*8]
   uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
   uint64_t* empty = full + p.stages;
   const unsigned char* zero_page = reinterpret_cast<const unsigned char*>(empty + p.stages);  // 16 zero bytes
@@ -114,7 +116,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   if (warp == kConsumerWarps) {
     if (lane == 0) {
       for (int c = p.stages; c < nchunks; ++c) {
-        const RingUse use = ring_use(c, p.stages);
+        const RingUse use = ring_use(c, p.stages, SETS);
         const int s = use.slot;
         if (!mbar_wait(&empty[s], (use.round & 1) ^ 1, &g_wait_timeouts)) break;
         unsigned char* dst = smem + static_cast<size_t>(s) * kStageBytes;
@@ -126,7 +128,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   }
 
   const int gid = lane >> 2, tig = lane & 3;
-  const int bx = warp >= p.rgs ? 1 : 0, rg = warp - bx * p.rgs;  // warp set bx takes chunks c = bx (mod 2)
+  const int bx = warp / p.rgs, rg = warp - bx * p.rgs;  // warp set bx takes chunks c = bx (mod SETS)
   const int rowA = rg * 16 + gid;
   constexpr uint32_t kNib = 0x0F0F0F0Fu, kHiNib = 0xF0F0F0F0u;
 
@@ -157,11 +159,11 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
 
-  // this set's ring slots bx, bx + 2, ... in turn (see ring_use)
-  const int owned = (p.stages + 1 - bx) >> 1;
+  // this set's ring slots bx, bx + SETS, ... in turn (see ring_use)
+  const int owned = (p.stages - bx + SETS - 1) / SETS;
   int ring_idx = 0, ring_round = 0;
-  for (int c = bx; c < nchunks; c += 2) {
-    const int slot = bx + 2 * ring_idx;
+  for (int c = bx; c < nchunks; c += SETS) {
+    const int slot = bx + SETS * ring_idx;
     if (!mbar_wait(&full[slot], ring_round & 1, &g_wait_timeouts)) break;
     const unsigned char* st = smem + static_cast<size_t>(slot) * kStageBytes + row_off;
     const int blocks_here = (p.debug & 2) ? 0 : min(kBoxBlocks, p.per - c * kChunkBlocks);
@@ -248,11 +250,11 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
 
   // The two warps of a row group (even and odd chunks) add their partial sums; the
   // digit columns of each activation row are then combined through shared memory.
-  if (bx == 1) {
+  if (bx > 0) {
 #pragma unroll
     for (int g = 0; g < NCG; ++g)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) xchg[((rg * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
+      for (int e = 0; e < 4; ++e) xchg[((((bx - 1) * p.rgs + rg) * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
   }
   asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
   if (bx == 0) {
@@ -262,7 +264,9 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
       for (int e = 0; e < 4; ++e) {
         const int col = g * 8 + 2 * tig + (e & 1);
         const int rr = rowA + (e >> 1) * 8;
-        const float v = o[g][e] + xchg[((rg * 32 + lane) * NCG + g) * 4 + e];
+        float v = o[g][e];
+#pragma unroll
+        for (int sx = 0; sx < SETS - 1; ++sx) v += xchg[(((sx * p.rgs + rg) * 32 + lane) * NCG + g) * 4 + e];
         if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v;
       }
     }
@@ -321,41 +325,47 @@ int env_int(const char* name, int fallback) {
   return v ? std::atoi(v) : fallback;
 }
 
-template <int NCG>
+// With `cost_only` the launch is planned but not issued, and its modelled time returned.
+template <int NCG, int SETS>
 int launch_staged(const void* w, StagedParams p, uint64_t n, uint64_t nb, uint64_t split,
-                  uint64_t nchunks, cudaStream_t st) {
+                  uint64_t nchunks, cudaStream_t st, double* cost_only) {
   const uint64_t nblk_pad = nchunks * kChunkBlocks;
   auto fixed = [&](int rgs) -> size_t {
-    return nblk_pad * p.ncols * (256 + 16) + nblk_pad * kMaxCols * 4 + rgs * 32 * NCG * 4 * 4 +
+    return nblk_pad * p.ncols * (256 + 16) + nblk_pad * kMaxCols * 4 + (SETS - 1) * rgs * 32 * NCG * 4 * 4 +
            16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128;
   };
   auto stage_bytes = [](int rgs) -> size_t { return static_cast<size_t>(rgs) * kGroupBytes; };
-  static const int regs = kernel_registers(gemv_q4k_staged_kernel<NCG>);
+  static const int regs = kernel_registers(gemv_q4k_staged_kernel<NCG, SETS>);
   StagedPlan plan;
-  if (!plan_staged(n, split, static_cast<uint64_t>(p.per), nchunks, 12, regs, fixed, stage_bytes, &plan))
+  if (!plan_staged(n, split, static_cast<uint64_t>(p.per), nchunks, 12, regs, fixed, stage_bytes, &plan, SETS))
     return kUnsupportedFeature;
+  if (cost_only != nullptr) {
+    *cost_only = plan.cost;
+    return kOk;
+  }
   const int forced_rgs = env_int("TSR_RGS", 0);
   if (forced_rgs >= 1 && forced_rgs <= 4) {
     plan.rgs = forced_rgs;
     plan.smem = fixed(forced_rgs) + plan.stages * stage_bytes(forced_rgs);
   }
   const int forced = env_int("TSR_STAGES", 0);
-  if (forced >= 2 && forced <= 16 &&
+  if (forced >= SETS && forced <= 16 &&
       fixed(plan.rgs) + forced * stage_bytes(plan.rgs) <= static_cast<size_t>(kMaxSmem)) {
     plan.stages = forced;
     plan.smem = fixed(plan.rgs) + forced * stage_bytes(plan.rgs);
   }
   if (plan.smem > static_cast<size_t>(kMaxSmem)) return kUnsupportedFeature;
   p.rgs = plan.rgs;
+  p.sets = SETS;
   p.stages = plan.stages;
   CUtensorMap map;
   if (int rc = q4k_tensor_map(w, n, nb, plan.rgs, &map)) return rc;
-  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q4k_staged_kernel<NCG>), kMaxSmem)) return rc;
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q4k_staged_kernel<NCG, SETS>), kMaxSmem)) return rc;
   const uint64_t th = 16u * plan.rgs;
   const dim3 grid(static_cast<unsigned>((n + th - 1) / th), static_cast<unsigned>(split));
   const size_t w_bytes = n * nb * kQ4KBlockBytes;
   p.pdl = pdl_allowed(st, w, w_bytes, p.c, split * p.region_stride * 4) ? 1 : 0;
-  launch_kernel(gemv_q4k_staged_kernel<NCG>, grid, dim3((2 * plan.rgs + 1) * 32), plan.smem, st,
+  launch_kernel(gemv_q4k_staged_kernel<NCG, SETS>, grid, dim3((SETS * plan.rgs + 1) * 32), plan.smem, st,
                 p.pdl != 0, map, p);
   return check_launch();
 }
@@ -404,10 +414,24 @@ int staged_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_
   const int terms = m <= 2 ? 3 : 2;
   const int ncols = static_cast<int>(m) * terms;
   StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
-                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0, 4,
+                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0, 4, 2,
                  static_cast<unsigned long long>(m * n)};
-  if (ncols <= 8) return launch_staged<1>(w, p, n, nb, split, nchunks, st);
-  return launch_staged<2>(w, p, n, nb, split, nchunks, st);
+  // two consumer sets, or four when the model says the warps' own chains of chunks
+  // (not the SM's throughput) set the time: few CTAs, long k
+  auto run = [&](auto ncg) -> int {
+    constexpr int kNcg = decltype(ncg)::value;
+    double c2 = 0.0, c4 = 0.0;
+    const int r2 = launch_staged<kNcg, 2>(w, p, n, nb, split, nchunks, st, &c2);
+    const int r4 = launch_staged<kNcg, 4>(w, p, n, nb, split, nchunks, st, &c4);
+    const int forced_sets = env_int("TSR_SETS", 0);
+    const bool four = forced_sets == 4 ? r4 == kOk : forced_sets == 2 ? r2 != kOk && r4 == kOk
+                                                                      : r4 == kOk && (r2 != kOk || c4 + 0.3 < c2);
+    if (four) return launch_staged<kNcg, 4>(w, p, n, nb, split, nchunks, st, nullptr);
+    if (r2 != kOk) return r2;
+    return launch_staged<kNcg, 2>(w, p, n, nb, split, nchunks, st, nullptr);
+  };
+  if (ncols <= 8) return run(std::integral_constant<int, 1>{});
+  return run(std::integral_constant<int, 2>{});
 }
 
 int staged_wait_timeouts(unsigned int* count) {

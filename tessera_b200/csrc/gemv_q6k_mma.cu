@@ -437,7 +437,7 @@ int staged_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_
   const int terms = m <= 2 ? 3 : 2;
   const int ncols = static_cast<int>(m) * terms;
   StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
-                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0, 4,
+                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0, 4, 2,
                  static_cast<unsigned long long>(m * n)};
   const int odd_shift = static_cast<int>((nb * kQ6KBlockBytes) & 15u);
   if (ncols <= 8) return launch_q6k<1>(w, p, odd_shift, n, nb, split, st);

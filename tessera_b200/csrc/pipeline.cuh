@@ -54,21 +54,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsign
   return false;
 }
 
-// Ring slot and use count of chunk c when two consumer groups take the even
-// and the odd chunks.  Each group owns its own slots (group 0 the even ones,
-// group 1 the odd ones; with an odd ring group 0 has one more), so every slot
-// is waited on by one group, in order.  A parity wait only tells the phase
+// Ring slot and use count of chunk c when `groups` consumer groups (two unless
+// said otherwise) take the chunks round-robin.  Each group owns its own slots
+// (group g the slots g, g + groups, ...; the ring has at least one per group),
+// so every slot is waited on by one group, in order.  A parity wait only tells the phase
 // before from the phase after: if a slot alternated between the groups, a
 // group that runs ahead would wait on a phase the barrier has not reached and
 // the wait would return at once.
 struct RingUse {
   int slot, round;
 };
-__device__ __forceinline__ RingUse ring_use(int c, int stages) {
-  const int group = c & 1, j = c >> 1;
-  const int owned = (stages + 1 - group) >> 1;
+__device__ __forceinline__ RingUse ring_use(int c, int stages, int groups = 2) {
+  const int group = c % groups, j = c / groups;
+  const int owned = (stages - group + groups - 1) / groups;
   const int idx = j % owned;
-  return {group + 2 * idx, j / owned};
+  return {group + groups * idx, j / owned};
 }
 
 // Tiled TMA load of one 3-D box into shared memory; completion is counted in

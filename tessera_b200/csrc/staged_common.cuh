@@ -15,7 +15,7 @@
 namespace tsr {
 namespace staged {
 
-constexpr int kStagedConsumerWarps = 8;                         // at most: two sets of four row groups
+constexpr int kStagedConsumerWarps = 8;                         // two sets of four row groups
 constexpr int kStagedThreads = kStagedConsumerWarps * 32 + 32;  // plus the producer warp
 constexpr int kMaxSmem = 227 * 1024;
 constexpr int kMaxCols = 16;
@@ -30,7 +30,8 @@ struct StagedParams {
   int ncols;   // m * terms
   int debug;   // experiment switches: 1 skips activation staging, 2 skips the block math
   int pdl;     // launched as a programmatic dependent: prefetch weights, then wait for the stream
-  int rgs;     // 16-row groups per CTA (1..4): the tile has 16*rgs rows, the CTA 2*rgs consumer warps
+  int rgs;     // 16-row groups per CTA (1..4): the tile has 16*rgs rows
+  int sets;    // consumer warp sets (2 or 4): sets*rgs consumer warps; set s takes the chunks c = s (mod sets)
   unsigned long long region_stride;
 };
 
@@ -172,7 +173,7 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // The producer warp only issues the weight copies: its first TMA instruction
   // can wait on the descriptor fetch, which must not hold up a share of the staging.
-  const int kWarps = 2 * p.rgs;
+  const int kWarps = p.sets * p.rgs;
   if (warp >= kWarps) {
     if (p.pdl) {
       pdl_wait();
@@ -238,7 +239,8 @@ struct StagedPlan {
 //   stage_bytes(rgs) one ring stage
 template <typename FixedFn, typename StageFn>
 inline bool plan_staged(uint64_t n, uint64_t split, uint64_t per, uint64_t nchunks, int max_want,
-                        int regs_per_thread, FixedFn fixed, StageFn stage_bytes, StagedPlan* out) {
+                        int regs_per_thread, FixedFn fixed, StageFn stage_bytes, StagedPlan* out,
+                        int sets = 2) {
   static int sms = 0;
   if (sms == 0) {
     int dev = 0, v = 0;
@@ -255,23 +257,23 @@ inline bool plan_staged(uint64_t n, uint64_t split, uint64_t per, uint64_t nchun
     const uint64_t ctas = ((n + th - 1) / th) * split;
     const size_t fx = fixed(rgs), sb = stage_bytes(rgs);
     for (int occ = 1; occ <= 4; ++occ) {
-      if (occ > 1 && occ * (2 * rgs + 1) * 32 * regs_per_thread > 65536) break;  // register file
+      if (occ > 1 && occ * (sets * rgs + 1) * 32 * regs_per_thread > 65536) break;  // register file
       const size_t avail = static_cast<size_t>(kMaxSmem) / occ;
       const size_t reserve = occ > 1 ? 1024 : 0;  // per-CTA reservation of the hardware
-      if (avail < fx + reserve + 2 * sb) break;
+      if (avail < fx + reserve + sets * sb) break;  // every consumer set owns at least one slot
       int depth = static_cast<int>((avail - reserve - fx) / sb);
       int want = static_cast<int>(nchunks < static_cast<uint64_t>(max_want) ? nchunks : max_want);
-      if (want < 2) want = 2;
+      if (want < sets) want = sets;
       if (depth > want) depth = want;
       const uint64_t slots = static_cast<uint64_t>(sms) * occ;
       const uint64_t waves = (ctas + slots - 1) / slots;
       const uint64_t per_sm = (ctas + sms - 1) / sms;
       // an SM works through its CTAs at a fixed rate, but a warp cannot go faster
-      // than its own share of the blocks (half: two consumer sets) one after the other
+      // than its own share of the blocks (one consumer set's) one after the other
       const double throughput = per_sm * rgs * per * kUnitUs;
-      const double latency = waves * (per / 2.0) * kWarpBlockUs;
+      const double latency = waves * (static_cast<double>(per) / sets) * kWarpBlockUs;
       double cost = (throughput > latency ? throughput : latency) + waves * kPrefixUs;
-      if (depth < 3 && nchunks > 2) cost *= 1.1;  // a shallow ring stalls on HBM latency
+      if (depth < sets + 1 && nchunks > static_cast<uint64_t>(sets)) cost *= 1.1;  // a shallow ring stalls on HBM latency
       if (cost < best - 1e-9) {
         best = cost;
         out->rgs = rgs;
