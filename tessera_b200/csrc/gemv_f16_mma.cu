@@ -609,7 +609,7 @@ int staged_f16(const float* a, const void* w, const float* scale, float* c, uint
     const int r4 = launch_f16<FMT, kNcg, 4>(w, p, n, k, st, &c4);
     const int forced_sets = env_int("TSR_SETS", 0);
     const bool four = forced_sets == 4 ? r4 == kOk : forced_sets == 2 ? r2 != kOk && r4 == kOk
-                                                                      : r4 == kOk && (r2 != kOk || c4 + 0.3 < c2);
+                                                                      : r4 == kOk && (r2 != kOk || (four_sets_worthwhile(n, 1) && c4 + 0.3 < c2));
     if (four) return launch_f16<FMT, kNcg, 4>(w, p, n, k, st, nullptr);
     if (r2 != kOk) return r2;
     return launch_f16<FMT, kNcg, 2>(w, p, n, k, st, nullptr);

@@ -425,7 +425,7 @@ int staged_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_
     const int r4 = launch_staged<kNcg, 4>(w, p, n, nb, split, nchunks, st, &c4);
     const int forced_sets = env_int("TSR_SETS", 0);
     const bool four = forced_sets == 4 ? r4 == kOk : forced_sets == 2 ? r2 != kOk && r4 == kOk
-                                                                      : r4 == kOk && (r2 != kOk || c4 + 0.3 < c2);
+                                                                      : r4 == kOk && (r2 != kOk || (four_sets_worthwhile(n, split) && c4 + 0.3 < c2));
     if (four) return launch_staged<kNcg, 4>(w, p, n, nb, split, nchunks, st, nullptr);
     if (r2 != kOk) return r2;
     return launch_staged<kNcg, 2>(w, p, n, nb, split, nchunks, st, nullptr);

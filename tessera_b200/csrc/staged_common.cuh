@@ -230,6 +230,23 @@ struct StagedPlan {
   double cost;  // modelled microseconds
 };
 
+inline int device_sms() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    sms = v > 0 ? v : 148;
+  }
+  return sms;
+}
+
+// Four consumer sets pay off when 64-row tiles would leave a good part of the SMs without a
+// CTA (measured: 80 and 68 CTAs on 148 SMs gain 0.5-1 us, 136 CTAs gain nothing).
+inline bool four_sets_worthwhile(uint64_t n, uint64_t split) {
+  return ((n + 63) / 64) * split * 10 <= static_cast<uint64_t>(device_sms()) * 6;
+}
+
 // Picks the tile height (16..64 rows) and the CTAs per SM so that the grid is
 // one wave with as even a load per SM as the shape allows.  The model: a CTA
 // costs a fixed prefix (launch, activation staging, epilogue) plus time
@@ -241,13 +258,7 @@ template <typename FixedFn, typename StageFn>
 inline bool plan_staged(uint64_t n, uint64_t split, uint64_t per, uint64_t nchunks, int max_want,
                         int regs_per_thread, FixedFn fixed, StageFn stage_bytes, StagedPlan* out,
                         int sets = 2) {
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    sms = v > 0 ? v : 148;
-  }
+  const int sms = device_sms();
   // per 16 rows x 1 block on a busy SM; per block of one warp's own chunks; per wave
   const double kUnitUs = 0.04, kWarpBlockUs = 0.5, kPrefixUs = 3.4;
   double best = 1e30;
