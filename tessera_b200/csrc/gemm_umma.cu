@@ -25,6 +25,7 @@
 #include <cstdlib>
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 #include <cuda_runtime.h>
 
 #include "codec.cuh"
@@ -41,7 +42,8 @@ constexpr int kTileM = 128;       // weight rows per CTA
 constexpr int kSlab = 64;         // k elements per pipeline step
 constexpr int kMaxTokens = 64;    // tokens per CTA (N = 2 * padded tokens <= 128)
 constexpr int kProducerThreads = 256;  // two per weight row
-constexpr int kUmmaThreads = kProducerThreads + 64;  // + the MMA warp and the TMA warp
+constexpr int kUmmaThreads = kProducerThreads + 96;  // + the MMA warp, the weight TMA warp, the activation copy warp
+constexpr int kBSlabPitch = 2 * kMaxTokens * kSlab * 2;  // bytes per slab of pre-converted activations (16 KiB)
 constexpr int kASlabBytes = kTileM * kSlab * 2;  // 16384
 constexpr int kBufs = 2;                         // slab buffers in shared memory (a power of two)
 constexpr int kBufShift = 1;
@@ -55,6 +57,7 @@ struct UmmaParams {
   const float* scale;  // FP8 row scales
   float* c;
   int m, n, k;
+  const unsigned char* bpre;  // activations already in operand layout (convert_activations_kernel), or null
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------
@@ -241,6 +244,43 @@ __device__ __forceinline__ void convert(const UmmaParams& p, int row, int slab, 
   for (int kc = 0; kc < 4; ++kc) out[kc] = make_uint4(h[4 * kc], h[4 * kc + 1], h[4 * kc + 2], h[4 * kc + 3]);
 }
 
+// ---- operand B ------------------------------------------------------------------
+// Eight consecutive activations of one token -> one 16-byte piece of binary16:
+// the clamped value itself (hi rows) or what binary16 lost of it (lo rows).
+__device__ __forceinline__ uint4 convert_b_piece(float4 x0, float4 x1, bool lo_part) {
+  const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+  float o[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float cx = fminf(fmaxf(xs[e], -65504.0f), 65504.0f);
+    const float hi = __half2float(__float2half_rn(cx));
+    o[e] = lo_part ? fminf(fmaxf(xs[e] - hi, -65504.0f), 65504.0f) : cx;
+  }
+  return make_uint4(pack_h2(o[0], o[1]), pack_h2(o[2], o[3]), pack_h2(o[4], o[5]), pack_h2(o[6], o[7]));
+}
+
+// Converts the activations once per launch into the operand-B layout of every
+// (token chunk, slab): out[(chunk * nslabs + slab) * kBSlabPitch + ...], so that the
+// tiles fetch a slab with one bulk copy instead of converting it in every CTA.
+__global__ void __launch_bounds__(256)
+convert_activations_kernel(const float* __restrict__ a, unsigned char* __restrict__ out, int m, int k) {
+  const int slab = blockIdx.x, chunk = blockIdx.y, nslabs = gridDim.x;
+  const int tok0 = chunk * kMaxTokens;
+  const int tokens = min(kMaxTokens, m - tok0);
+  const int tok_pad = (tokens + 7) & ~7, n_cols = 2 * tok_pad;
+  unsigned char* dst = out + (static_cast<size_t>(chunk) * nslabs + slab) * kBSlabPitch;
+  for (int g = threadIdx.x; g < n_cols * (kSlab / 8); g += blockDim.x) {
+    const int r = g >> 3, kc = g & 7;
+    const int tok = r < tok_pad ? r : r - tok_pad;
+    uint4 piece = make_uint4(0u, 0u, 0u, 0u);
+    if (tok < tokens) {
+      const float4* src = reinterpret_cast<const float4*>(a + static_cast<size_t>(tok0 + tok) * k + slab * kSlab + kc * 8);
+      piece = convert_b_piece(__ldg(src), __ldg(src + 1), r >= tok_pad);
+    }
+    *reinterpret_cast<uint4*>(dst + (r >> 3) * kSbo + (r & 7) * 16 + kc * kLbo) = piece;
+  }
+}
+
 // ---- raw-weight ring (TMA) ------------------------------------------------------
 // With RING the weight bytes of a 128-row tile arrive by tiled TMA copies, a
 // stage of several slabs at a time, in a ring of kRawStages stages; the
@@ -304,16 +344,18 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   uint64_t* done = bars + 2 * kBufs;     // accumulator complete
   uint64_t* raw_full = done + 1;         // [kRawStages] TMA -> producers
   uint64_t* raw_empty = raw_full + kRawStages;  // [kRawStages] producers -> TMA
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(raw_empty + kRawStages);
+  uint64_t* b_full = raw_empty + kRawStages;    // [kBufs] activation copy -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_full + kBufs);
   uint32_t tmem_cols = 32;
   while (tmem_cols < static_cast<uint32_t>(n_cols)) tmem_cols <<= 1;
   const int nslabs = p.k / kSlab;
-  constexpr int kProducerWarps = kProducerThreads / 32;  // then one MMA warp, then one TMA warp
+  constexpr int kProducerWarps = kProducerThreads / 32;  // then the MMA warp, the weight TMA warp, the activation copy warp
 
   if (tid == 0) {
     for (int s = 0; s < kBufs; ++s) {
       mbar_init(&full[s], kProducerThreads / 32);  // one arrival per producer warp
       mbar_init(&empty[s], 1);
+      mbar_init(&b_full[s], 1);
     }
     for (int s = 0; s < kRawStages; ++s) {
       mbar_init(&raw_full[s], 1);
@@ -369,8 +411,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
         }
       }
     };
-    load_b(0, bx[0]);
-    load_b(1, bx[1]);
+    const bool convert_b = p.bpre == nullptr;
+    if (convert_b) {
+      load_b(0, bx[0]);
+      load_b(1, bx[1]);
+    }
     for (int s0 = 0; s0 < nslabs && !failed; s0 += 2 * kAhead) {
 #pragma unroll
       for (int uu = 0; uu < 2 * kAhead; ++uu) {
@@ -406,27 +451,19 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
         unsigned char* a_dst = a_tiles + buf * kASlabBytes + (trow >> 3) * kSbo + (trow & 7) * 16 + half * 4 * kLbo;
 #pragma unroll
         for (int kc = 0; kc < 4; ++kc) *reinterpret_cast<uint4*>(a_dst + kc * kLbo) = piece4[kc];
-        // operand B from the activations loaded two slabs ago; then reload for slab s + 2
+        if (convert_b) {
+          // operand B from the activations loaded two slabs ago; then reload for slab s + 2
 #pragma unroll
-        for (int i = 0; i < kBPieces; ++i) {
-          const int g = tid + i * kProducerThreads;
-          if (g < b_pieces) {
-            const int r = g >> 3, kc = g & 7;
-            const bool lo_part = r >= tok_pad;
-            const float4 x0 = bx[u & 1][i][0], x1 = bx[u & 1][i][1];
-            const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-            float o[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float cx = fminf(fmaxf(xs[e], -65504.0f), 65504.0f);
-              const float hi = __half2float(__float2half_rn(cx));
-              o[e] = lo_part ? fminf(fmaxf(xs[e] - hi, -65504.0f), 65504.0f) : cx;
+          for (int i = 0; i < kBPieces; ++i) {
+            const int g = tid + i * kProducerThreads;
+            if (g < b_pieces) {
+              const int r = g >> 3, kc = g & 7;
+              *reinterpret_cast<uint4*>(b_tiles + buf * b_slab_bytes + (r >> 3) * kSbo + (r & 7) * 16 + kc * kLbo) =
+                  convert_b_piece(bx[u & 1][i][0], bx[u & 1][i][1], r >= tok_pad);
             }
-            *reinterpret_cast<uint4*>(b_tiles + buf * b_slab_bytes + (r >> 3) * kSbo + (r & 7) * 16 + kc * kLbo) =
-                make_uint4(pack_h2(o[0], o[1]), pack_h2(o[2], o[3]), pack_h2(o[4], o[5]), pack_h2(o[6], o[7]));
           }
+          load_b(s + 2, bx[u & 1]);
         }
-        load_b(s + 2, bx[u & 1]);
         // every thread orders its own stores before the async proxy; 256 arrivals on one
         // barrier word would serialise, so one lane per warp arrives for the warp
         fence_async_proxy();
@@ -440,7 +477,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       const uint32_t idesc = instr_desc(static_cast<uint32_t>(n_cols));
       for (int s = 0; s < nslabs; ++s) {
         const int buf = s & (kBufs - 1), round = s >> kBufShift;
-        if (!mbar_wait(&full[buf], round & 1, &g_umma_timeouts)) {
+        if (!mbar_wait(&full[buf], round & 1, &g_umma_timeouts) ||
+            (p.bpre != nullptr && !mbar_wait(&b_full[buf], round & 1, &g_umma_timeouts))) {
           failed = true;
           break;
         }
@@ -455,7 +493,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       }
       umma_commit(done);
     }
-  } else if (RING && lane == 0) {
+  } else if (warp == kProducerWarps + 1 && RING && lane == 0) {
     // ---------------- TMA issuer: raw weight stages -------------------------
     constexpr int kPer = RingFmt<FMT>::kSlabsPerStage;
     const int nstages = (nslabs + kPer - 1) / kPer;
@@ -470,6 +508,18 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
         tma_load_3d(dst, &wmap, 0, row0, 2 * st, &raw_full[slot]);  // (128 B, rows, segments)
         if (FMT == kFmtMxFp4) tma_load_2d(dst + RingFmt<FMT>::kWeightBytes, &smap, 16 * st, row0, &raw_full[slot]);
       }
+    }
+  }
+
+  if (warp == kProducerWarps + 2 && lane == 0 && p.bpre != nullptr) {
+    // ---------------- activation copy: one bulk copy per slab ----------------
+    const unsigned char* src = p.bpre + static_cast<size_t>(blockIdx.y) * nslabs * kBSlabPitch;
+    for (int s = 0; s < nslabs; ++s) {
+      const int buf = s & (kBufs - 1), round = s >> kBufShift;
+      if (round > 0 && !mbar_wait(&empty[buf], (round - 1) & 1, &g_umma_timeouts)) break;
+      mbar_expect_tx(&b_full[buf], static_cast<uint32_t>(b_slab_bytes));
+      bulk_load(b_tiles + buf * b_slab_bytes, src + static_cast<size_t>(s) * kBSlabPitch,
+                static_cast<uint32_t>(b_slab_bytes), &b_full[buf]);
     }
   }
 
@@ -556,14 +606,55 @@ int ring_maps(int fmt, const void* w, uint64_t n, uint64_t k, RingMaps* out) {
   return kOk;
 }
 
+// Device scratch for the pre-converted activations, one buffer per (device, stream),
+// grown on demand and never freed before exit (a captured graph may hold the pointer).
+// Returns null when the stream is being captured and no large enough buffer exists yet:
+// the tiles then convert the activations themselves.
+unsigned char* activation_scratch(cudaStream_t st, size_t bytes) {
+  struct Entry {
+    int device;
+    cudaStream_t stream;
+    unsigned char* ptr;
+    size_t bytes;
+  };
+  static std::mutex mutex;
+  static std::vector<Entry> table;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lock(mutex);
+  for (const Entry& e : table)
+    if (e.device == dev && e.stream == st && e.bytes >= bytes) return e.ptr;
+  cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &status) != cudaSuccess || status != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  size_t want = 4u << 20;
+  while (want < bytes) want <<= 1;
+  void* ptr = nullptr;
+  if (cudaMalloc(&ptr, want) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  table.push_back(Entry{dev, st, static_cast<unsigned char*>(ptr), want});
+  return static_cast<unsigned char*>(ptr);
+}
+
 template <int FMT, bool RING>
-int launch_umma_impl(const UmmaParams& p, const RingMaps& maps, cudaStream_t st) {
+int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st) {
   const int tok_pad = ((p.m < kMaxTokens ? p.m : kMaxTokens) + 7) & ~7;
   const size_t ring = RING ? static_cast<size_t>(kRawStages) * RingFmt<FMT>::kStagePitch : 0;
   const size_t smem = 1024 + ring + kBufs * kASlabBytes + kBufs * static_cast<size_t>(2 * tok_pad) * kSlab * 2 + 256;
   if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemm_umma_kernel<FMT, RING>), 227 * 1024)) return rc;
   const dim3 grid(static_cast<unsigned>((p.n + kTileM - 1) / kTileM),
                   static_cast<unsigned>((p.m + kMaxTokens - 1) / kMaxTokens));
+  // activations -> operand layout once per launch, when scratch is to be had
+  const int nslabs = p.k / kSlab;
+  p.bpre = activation_scratch(st, static_cast<size_t>(grid.y) * nslabs * kBSlabPitch);
+  if (p.bpre != nullptr) {
+    convert_activations_kernel<<<dim3(nslabs, grid.y), 256, 0, st>>>(p.a, const_cast<unsigned char*>(p.bpre), p.m, p.k);
+    if (int rc = check_launch()) return rc;
+  }
   gemm_umma_kernel<FMT, RING><<<grid, kUmmaThreads, smem, st>>>(maps.weights, maps.scales, p);
   return check_launch();
 }
@@ -590,7 +681,7 @@ int umma_gemm(int fmt, const float* a, const void* w, const float* scale, float*
               uint64_t k, cudaStream_t st) {
   if (k % kSlab != 0 || (fmt <= 1 && k % 256 != 0)) return kUnsupportedFeature;
   const UmmaParams p{a, static_cast<const unsigned char*>(w), scale, c, static_cast<int>(m),
-                     static_cast<int>(n), static_cast<int>(k)};
+                     static_cast<int>(n), static_cast<int>(k), nullptr};
   switch (fmt) {
     case kFmtQ4K: return launch_umma<kFmtQ4K>(p, st);
     case kFmtQ6K: return launch_umma<kFmtQ6K>(p, st);
