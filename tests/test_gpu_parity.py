@@ -293,6 +293,7 @@ def _sample_rows(n, count=96, seed=0):
     ("mxfp4", 1, 17408, 5120), ("mxfp4", 4, 5120, 17408),   # cluster K split on the second
     ("fp8", 4, 17408, 5120), ("fp8", 1, 5120, 17408),
     ("mxfp4", 16, 5120, 5120), ("fp8", 48, 17408, 5120),    # staged in chunks of 8; tcgen05 tile
+    ("q4k", 16, 17408, 5120), ("fp8", 12, 17408, 5120),     # enough rows: the tile takes m = 9..16 too
 ])
 def test_full_size_projection_on_sampled_rows(backend, oracle, dtype, m, n, k):
     """The measured shapes at full size: the whole projection runs on the GPU, and about a
