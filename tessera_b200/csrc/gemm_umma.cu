@@ -416,6 +416,41 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       load_b(0, bx[0]);
       load_b(1, bx[1]);
     }
+    if (RING && !convert_b) {
+      // The common case (weights from the ring, activations from the scratch copy) as one
+      // rolled loop: nothing here lives in per-slab registers, and the unrolled form
+      // below spent a fifth of its issue slots waiting for instruction fetch.
+#pragma unroll 1
+      for (int s = 0; s < nslabs; ++s) {
+        const int buf = s & (kBufs - 1), round = s >> kBufShift;
+        if (round > 0 && !mbar_wait(&empty[buf], (round - 1) & 1, &g_umma_timeouts)) {
+          failed = true;
+          break;
+        }
+        constexpr int kPer = RingFmt<FMT>::kSlabsPerStage;
+        const int st = s / kPer, si = s - st * kPer;
+        const int slot = st % kRawStages, rround = st / kRawStages;
+        if (si == 0 && !mbar_wait(&raw_full[slot], rround & 1, &g_umma_timeouts)) {
+          failed = true;
+          break;
+        }
+        uint4 piece4[4] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u),
+                           make_uint4(0u, 0u, 0u, 0u)};
+        RawHalf rr;
+        read_raw<FMT>(ring + slot * RingFmt<FMT>::kStagePitch, trow, si, half, rr);
+        if (have_row) convert<FMT>(p, wrow, s, half, rr, piece4);
+        if (si == kPer - 1 || s == nslabs - 1) {  // this warp is done with the stage
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&raw_empty[slot]);
+        }
+        unsigned char* a_dst = a_tiles + buf * kASlabBytes + (trow >> 3) * kSbo + (trow & 7) * 16 + half * 4 * kLbo;
+#pragma unroll
+        for (int kc = 0; kc < 4; ++kc) *reinterpret_cast<uint4*>(a_dst + kc * kLbo) = piece4[kc];
+        fence_async_proxy();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[buf]);
+      }
+    } else
     for (int s0 = 0; s0 < nslabs && !failed; s0 += 2 * kAhead) {
 #pragma unroll
       for (int uu = 0; uu < 2 * kAhead; ++uu) {
