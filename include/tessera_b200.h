@@ -100,6 +100,54 @@ int tsr_launch(tsr_context* ctx, int kernel, const uint32_t grid[3], const uint3
                const void* const* buffers, const size_t* buffer_bytes, int n_buffers,
                const uint64_t* scalars, int n_scalars);
 
+/* The same launch as a record, and a call that submits an array of them in order
+ * (it stops at the first one that fails and returns that status; *done, when
+ * given, receives how many were accepted).  For bindings whose per-call cost is
+ * high: a decode loop submits the same few hundred launches every token. */
+typedef struct tsr_launch_desc {
+  int32_t kernel;
+  uint32_t grid[3];
+  uint32_t block[3];
+  int32_t n_buffers;
+  int32_t n_scalars;
+  const void* const* buffers;
+  const size_t* buffer_bytes;
+  const uint64_t* scalars;
+} tsr_launch_desc;
+int tsr_launch_many(tsr_context* ctx, const tsr_launch_desc* launches, size_t count, size_t* done);
+
+/* ---- deferred submission -------------------------------------------------
+ * The reference issues on the order of 500-1000 launches per decoded token
+ * (src/backends/rocm/rocm_backend.cpp:697-699) and its Vulkan backend already
+ * records launches into a command buffer that is submitted at the next
+ * synchronisation point (src/backends/vulkan/vulkan_compute.hpp:117-122).
+ * With tsr_set_deferred(ctx, 1), tsr_launch checks its arguments and queues;
+ * the queue is issued, in order, by the next copy, tsr_synchronize, tsr_free,
+ * tsr_flush or tsr_destroy on the context.  Before it is issued the queue is
+ * rewritten where the kernels allow it:
+ *   - gemm_q4k_vec / gemm_q6k_vec / gemm_*_rows<R> with a split, followed by the
+ *     gemm_vec_reduce of its partial buffer, becomes one launch that writes the
+ *     final output (the caller's partial buffer is then not written);
+ *   - consecutive Q4_K (or Q6_K) projections that read the same activations with
+ *     the same m and k become one launch over up to four weight tensors.
+ * A queue that repeats (same kernels, buffers and scalars) is replayed as a CUDA
+ * graph from its second appearance on; on = 2 defers and merges without graphs.
+ * Results stay within the projection tolerance of the separate launches but
+ * are not bit-identical to them (another split of k).  Hosts that also call
+ * the typed launchers below on the same stream must flush first. */
+int tsr_set_deferred(tsr_context* ctx, int on);
+int tsr_flush(tsr_context* ctx);
+/* Counters since the context was created: accepted tsr_launch calls, kernels
+ * they became on the device (graph replays included), CUDA graph launches. */
+int tsr_launch_stats(tsr_context* ctx, uint64_t* api_launches, uint64_t* device_kernels,
+                     uint64_t* graph_launches);
+/* One launch for `count` (1..4) projections C_i[m, n_i] = A . dq(W_i)^T that share
+ * A (m <= 8 rows of k floats) and the weight format (fmt 0 Q4_K, 1 Q6_K); what
+ * the deferred queue emits for QKV or gate/up.  Issued on the context's stream
+ * after its queue.  No reference counterpart (one LaunchKernel per projection). */
+int tsr_gemv_group(tsr_context* ctx, int fmt, const float* a, const void* const* w, float* const* c,
+                   const uint64_t* n, int count, uint64_t m, uint64_t k);
+
 /* ---- typed launchers (what tsr_launch dispatches to) ---------------------
  * `stream` is a cudaStream_t.  Shapes follow C[m,n] = A[m,k] . dq(W[n,k])^T.
  * All pointers are device pointers; A, C and scale vectors need 16-byte
@@ -148,6 +196,23 @@ int tsr_fill(int32_t* data, int32_t value, uint64_t n, void* stream);
 int tsr_dequantize(int fmt, const void* w, const float* row_scale, float* out, uint64_t n,
                    uint64_t k, void* stream);
 
+/* ---- tensor-parallel weight slicing at load time (host memory) ---------------
+ * SliceTensor2D / SliceMxFp4, src/core/loaders/tensor_slice.cpp:50-159, for
+ * fmt 0 Q4_K, 1 Q6_K, 2 MXFP4 (blob then scales, kept so), 3 FP8 bytes; kind is
+ * the reference's ParallelKind (include/tessera/types.hpp:29-34): 0 replicated,
+ * 1 column (rows [rows*rank/world, rows*(rank+1)/world)), 2 row (input columns,
+ * whole quantisation blocks).  Unlike the reference, a row split need not be
+ * even: rank r keeps blocks [nb*r/world, nb*(r+1)/world) of the nb blocks of a
+ * row, which equals the reference's range whenever it accepts the split and
+ * makes K = 17408 on 8 ranks possible (tensor_slice.cpp:145-147 rejects it).
+ * tsr_slice_shape reports the slice's rows, columns, first kept column (the
+ * activations of a row-parallel projection are cut with the same range) and
+ * byte size; tsr_slice_tensor copies it.  Host pointers; no device is needed. */
+int tsr_slice_shape(int fmt, int kind, uint64_t rows, uint64_t cols, int rank, int world,
+                    uint64_t* out_rows, uint64_t* out_cols, uint64_t* col_begin, uint64_t* out_bytes);
+int tsr_slice_tensor(int fmt, int kind, uint64_t rows, uint64_t cols, int rank, int world,
+                     const void* src, size_t src_bytes, void* dst, size_t dst_bytes);
+
 /* ---- split-K Q4_K projection without any device allocation ----------------
  * No counterpart in the reference: there the caller allocates the split-K
  * partial buffer through Backend::AllocateBuffer.
@@ -161,8 +226,11 @@ int tsr_dequantize(int fmt, const void* w, const float* row_scale, float* out, u
  * makes no cudaMalloc/cudaFree and uses no allocating library routine.
  *   - m*n may not exceed tsr_gemm_q4k_noalloc_max_outputs() (1,048,576);
  *     larger shapes are refused with TSR_INVALID_ARGUMENT.
- *   - The first call on a device looks up the array's device address; make
- *     that call before starting any stream capture on that device.
+ *   - The first call on a device looks up the array's device address, and the
+ *     first launch of each kernel loads its code: make one call per shape
+ *     family at load time, before any stream capture on that device.
+ *   - Batches (m >= 9) whose block count k/256 has no divisor up to 8 that
+ *     fits the array run unsplit, straight into c, also without allocating.
  *   - All calls on a device share the one array: calls whose kernels can
  *     overlap on the GPU (different streams) race on it.  Nothing needs
  *     clearing between calls; every partial that is read was just written.
@@ -195,8 +263,23 @@ int tsr_gemm_q4k_noalloc(const float* a, const void* w, float* c, uint64_t m, ui
  * order (the order of gemm_vec_reduce, decode_internal.hpp:1325-1345) while it
  * pushes, and `out` receives the sum over ranks in rank order: the same bits as
  * gemm_vec_reduce followed by tsr_tp_allreduce, one launch instead of two.  The
- * reference has no such call (it reduces, then TpReduce). */
+ * reference has no such call (it reduces, then TpReduce).
+ *
+ * max_floats (and world) must be the same on every rank: each rank computes its
+ * peers' offsets from its own values, and attaching a peer whose block was made
+ * with other values fails with TSR_INVALID_ARGUMENT.
+ *
+ * tsr_tp_bind makes `comm` the communicator of a context (same device; NULL
+ * unbinds).  The kernel ids gemm_q4k_vec_allreduce / gemm_q6k_vec_allreduce
+ * (buffers A, W, C; scalars m, n, k) then run a row-parallel projection of this
+ * rank's k range and end, in the same launch, with the sum over ranks: the tile
+ * that finishes stores its partial sums into every peer, publishes a flag, waits
+ * (bounded) for the peers' flags and adds the ranks in rank order.  allreduce_sum
+ * (buffer X; scalars m, n) sums an [m][n] matrix in place with the same tiles.
+ * Every rank must issue the same sequence of these ids; without a bound
+ * communicator they compute the single-rank result. */
 typedef struct tsr_tp_comm tsr_tp_comm;
+int tsr_tp_bind(tsr_context* ctx, tsr_tp_comm* comm);
 int tsr_tp_create(int device, int rank, int world, uint64_t max_floats, tsr_tp_comm** out);
 void tsr_tp_destroy(tsr_tp_comm* comm);
 int tsr_tp_local_block(tsr_tp_comm* comm, void** block, uint64_t* bytes);

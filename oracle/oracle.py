@@ -23,9 +23,11 @@ _sz = C.c_size_t
 _p = C.c_void_p
 
 
-def build(reference_root: str = "/root/reference") -> None:
-    subprocess.run(["make", "-C", _HERE, f"REFERENCE={reference_root}"], check=True,
-                   stdout=subprocess.DEVNULL)
+def build(reference_root: str | None = None) -> None:
+    """Runs the Makefile beside this file; `reference_root` overrides its default
+    location of the reference checkout."""
+    cmd = ["make", "-C", _HERE] + ([f"REFERENCE={reference_root}"] if reference_root else [])
+    subprocess.run(cmd, check=True, stdout=subprocess.DEVNULL)
 
 
 def reference_available() -> bool:
@@ -52,6 +54,22 @@ class Oracle:
         fn = getattr(self.lib, self.pre + name)
         fn.restype, fn.argtypes = restype, argtypes
         return fn
+
+    def slice_tensor2d(self, dtype: int, rows: int, cols: int, kind: int, rank: int, world: int, src: np.ndarray):
+        """The reference's SliceTensor2D (reference build only).  dtype is the reference's DType
+        value (F4E2M1 6, Q4K 10, Q6K 12, F8E4M3 3).  Returns (bytes, rows, cols) or the negative
+        status code the reference answered with."""
+        assert self.reference
+        fn = self.lib.ref_slice_tensor2d
+        fn.restype = C.c_longlong
+        fn.argtypes = [C.c_int, _sz, _sz, C.c_int, C.c_int, C.c_int, _p, _sz, _p, _sz, C.POINTER(_sz), C.POINTER(_sz)]
+        src = np.ascontiguousarray(src.reshape(-1).view(np.uint8))
+        dst = np.empty(src.nbytes, dtype=np.uint8)
+        r, c = _sz(), _sz()
+        n = fn(dtype, rows, cols, kind, rank, world, _ptr(src), src.nbytes, _ptr(dst), dst.nbytes, C.byref(r), C.byref(c))
+        if n < 0:
+            return int(n)
+        return dst[:n].copy(), r.value, c.value
 
     # ---- scalar codecs (vectorised by looping in Python: small inputs only)
     def _map(self, name, restype, argtype, values, out_dtype):

@@ -7,8 +7,10 @@
 // calls the reference's public functions.
 #include <cstddef>
 #include <cstdint>
+#include <cstring>
 #include <span>
 
+#include "core/loaders/tensor_slice.hpp"
 #include "core/numerics/gemm.hpp"
 #include "core/numerics/quant.hpp"
 
@@ -100,6 +102,21 @@ int ref_gemm_mxfp4_fp8(const std::uint8_t* a_fp8, const float* as, const std::ui
                        std::size_t k) {
   return Code(tc::GemmMxFp4Fp8Ref(Bytes(a_fp8, m * k), {as, m}, Bytes(w_fp8, n * k),
                                   Bytes(wref, n), {c, m * n}, m, n, k));
+}
+
+// SliceTensor2D (src/core/loaders/tensor_slice.cpp:105-159).  Returns the slice's byte count, or
+// minus the status code; out_rows/out_cols receive the slice's shape.
+long long ref_slice_tensor2d(int dtype, std::size_t rows, std::size_t cols, int kind, int rank, int world,
+                             const std::uint8_t* src, std::size_t src_bytes, std::uint8_t* dst,
+                             std::size_t dst_bytes, std::size_t* out_rows, std::size_t* out_cols) {
+  auto sliced = tc::SliceTensor2D(static_cast<tessera::DType>(dtype), rows, cols,
+                                  static_cast<tessera::ParallelKind>(kind), rank, world, Bytes(src, src_bytes));
+  if (!sliced) return -static_cast<long long>(sliced.error());
+  if (sliced->bytes.size() > dst_bytes) return -1;
+  std::memcpy(dst, sliced->bytes.data(), sliced->bytes.size());
+  *out_rows = sliced->rows;
+  *out_cols = sliced->cols;
+  return static_cast<long long>(sliced->bytes.size());
 }
 
 }  // extern "C"

@@ -238,6 +238,33 @@ class CudaBackend:
     def Synchronize(self) -> None:
         self._check(self._lib.tsr_synchronize(self._need()))
 
+    # -- deferred submission and tensor parallelism (no reference counterpart) --
+    def SetDeferred(self, mode: int) -> None:
+        """0: every LaunchKernel is issued at once; 1: launches queue until the next copy or
+        synchronisation, are merged where the kernels allow it, and a repeating queue is
+        replayed as a CUDA graph; 2: as 1 without graphs."""
+        self._check(self._lib.tsr_set_deferred(self._need(), mode))
+
+    def Flush(self) -> None:
+        self._check(self._lib.tsr_flush(self._need()))
+
+    def LaunchStats(self):
+        """(LaunchKernel calls accepted, kernels they became on the device, CUDA graph launches)."""
+        a, d, g = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        self._check(self._lib.tsr_launch_stats(self._need(), C.byref(a), C.byref(d), C.byref(g)))
+        return a.value, d.value, g.value
+
+    def BindTensorParallel(self, comm) -> None:
+        """Makes `comm` (a tessera_b200.tp.TpComm, or None) the communicator of the
+        gemm_*_vec_allreduce and allreduce_sum kernel ids."""
+        self._check(self._lib.tsr_tp_bind(self._need(), comm.comm if comm is not None else None))
+
+    def LaunchMany(self, batch: "LaunchBatch") -> None:
+        """Submits a pre-marshalled list of launches (same checks as LaunchKernel)."""
+        descs, count = batch.descriptors()
+        if count:
+            self._check(self._lib.tsr_launch_many(self._need(), descs, count, None))
+
     # -- conveniences for tests and the benchmark ---------------------------
     def upload(self, arr: np.ndarray) -> Buffer:
         buf = self.AllocateBuffer(max(arr.nbytes, 1))
@@ -248,6 +275,49 @@ class CudaBackend:
         out = np.empty(count, dtype=dtype)
         self.CopyD2HAt(buf, offset, out)
         return out
+
+
+class LaunchBatch:
+    """ctypes arguments of a fixed sequence of launches, built once: a decode loop issues the
+    same launches every token, and marshalling them in Python each time would cost more than
+    the launches themselves (the C++ backend has no such cost)."""
+
+    def __init__(self):
+        self.items = []
+        self._keep = []
+        self._descs = None
+
+    def add(self, kernel: Kernel, launch: KernelLaunch) -> None:
+        invalid = ValidateLaunch(launch)
+        if invalid != StatusCode.Ok:
+            raise StatusError(invalid, "ValidateLaunch")
+        nb, ns = len(launch.buffers), len(launch.scalars)
+        bufs = (C.c_void_p * max(nb, 1))(*[b.Handle() for b in launch.buffers])
+        sizes = (C.c_size_t * max(nb, 1))(*[b.Size() for b in launch.buffers])
+        scal = (C.c_uint64 * max(ns, 1))(*[int(s) & 0xFFFFFFFFFFFFFFFF for s in launch.scalars])
+        grid = (C.c_uint32 * 3)(launch.grid_x, launch.grid_y, launch.grid_z)
+        block = (C.c_uint32 * 3)(launch.block_x, launch.block_y, launch.block_z)
+        self._keep.append(list(launch.buffers))
+        self.items.append((kernel.Handle() - 1, grid, block, bufs, sizes, nb, scal, ns))
+        self._descs = None
+
+    def descriptors(self):
+        """(array of tsr_launch_desc, count) for tsr_launch_many."""
+        if self._descs is None:
+            arr = (capi.LaunchDesc * max(len(self.items), 1))()
+            for d, (kernel, grid, block, bufs, sizes, nb, scal, ns) in zip(arr, self.items):
+                d.kernel = kernel
+                d.grid[:] = list(grid)
+                d.block[:] = list(block)
+                d.n_buffers, d.n_scalars = nb, ns
+                d.buffers = C.cast(bufs, C.POINTER(C.c_void_p))
+                d.buffer_bytes = C.cast(sizes, C.POINTER(C.c_size_t))
+                d.scalars = C.cast(scal, C.POINTER(C.c_uint64))
+            self._descs = arr
+        return self._descs, len(self.items)
+
+    def __len__(self):
+        return len(self.items)
 
 
 def CreateBackend(stream: Optional[int] = None) -> CudaBackend:

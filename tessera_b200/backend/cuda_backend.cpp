@@ -13,6 +13,7 @@
 // No computation happens in this file; every method forwards to the C ABI.
 #include <cstddef>
 #include <cstdint>
+#include <cstdlib>
 #include <expected>
 #include <memory>
 #include <span>
@@ -69,6 +70,15 @@ class CudaBackend final : public Backend {
                std::to_string(device_index_));
       return std::unexpected(FromCode(code));
     }
+    // Launches queue until the next copy or synchronisation, are merged where
+    // the kernels allow it and replayed as a CUDA graph when they repeat: the
+    // core issues hundreds of launches per token (rocm_backend.cpp:697-699).
+    // TESSERA_CUDA_DEFERRED=0 issues every launch at once, =2 merges without graphs.
+    int deferred = 1;
+    if (const char* v = std::getenv("TESSERA_CUDA_DEFERRED")) {
+      deferred = std::atoi(v);
+    }
+    tsr_set_deferred(ctx_, deferred);
     char name[256] = {};
     tsr_device_name(device_index_, name, sizeof(name));
     device_name_ = name;

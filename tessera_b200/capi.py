@@ -41,6 +41,16 @@ def library_path() -> str:
 
 _lib = None
 
+
+class LaunchDesc(C.Structure):
+    """tsr_launch_desc of include/tessera_b200.h."""
+
+    _fields_ = [("kernel", C.c_int32), ("grid", C.c_uint32 * 3), ("block", C.c_uint32 * 3),
+                ("n_buffers", C.c_int32), ("n_scalars", C.c_int32),
+                ("buffers", C.POINTER(C.c_void_p)), ("buffer_bytes", C.POINTER(C.c_size_t)),
+                ("scalars", C.POINTER(C.c_uint64))]
+
+
 _u64 = C.c_uint64
 _vp = C.c_void_p
 _sz = C.c_size_t
@@ -68,6 +78,13 @@ SIGNATURES = {
     "tsr_kernel_lookup": (C.c_int, [C.c_char_p]),
     "tsr_launch": (C.c_int, [_vp, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
                              C.POINTER(_vp), C.POINTER(_sz), C.c_int, C.POINTER(_u64), C.c_int]),
+    "tsr_launch_many": (C.c_int, [_vp, C.POINTER(LaunchDesc), _sz, C.POINTER(_sz)]),
+    "tsr_set_deferred": (C.c_int, [_vp, C.c_int]),
+    "tsr_flush": (C.c_int, [_vp]),
+    "tsr_launch_stats": (C.c_int, [_vp, C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u64)]),
+    "tsr_gemv_group": (C.c_int, [_vp, C.c_int, _vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_u64), C.c_int,
+                                 _u64, _u64]),
+    "tsr_tp_bind": (C.c_int, [_vp, _vp]),
     "tsr_gemm_q4k": (C.c_int, [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp]),
     "tsr_gemm_q6k": (C.c_int, [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp]),
     "tsr_gemm_vec_reduce": (C.c_int, [_vp, _vp, _u64, _u64, _vp]),
@@ -81,6 +98,9 @@ SIGNATURES = {
     "tsr_add": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
     "tsr_fill": (C.c_int, [_vp, C.c_int32, _u64, _vp]),
     "tsr_dequantize": (C.c_int, [C.c_int, _vp, _vp, _vp, _u64, _u64, _vp]),
+    "tsr_slice_shape": (C.c_int, [C.c_int, C.c_int, _u64, _u64, C.c_int, C.c_int, C.POINTER(_u64), C.POINTER(_u64),
+                                  C.POINTER(_u64), C.POINTER(_u64)]),
+    "tsr_slice_tensor": (C.c_int, [C.c_int, C.c_int, _u64, _u64, C.c_int, C.c_int, _vp, _sz, _vp, _sz]),
     "tsr_gemm_q4k_noalloc_max_outputs": (_u64, []),
     "tsr_gemm_q4k_noalloc": (C.c_int, [_vp, _vp, _vp, _u64, _u64, _u64, _vp]),
     "tsr_tp_create": (C.c_int, [C.c_int, C.c_int, C.c_int, _u64, C.POINTER(_vp)]),

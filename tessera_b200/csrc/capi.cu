@@ -14,13 +14,19 @@
 #include <unordered_map>
 #include <string>
 
+#include "context.h"
 #include "launch.h"
 #include "tessera_b200.h"
 
 namespace {
 
-constexpr size_t kStageWindow = 4u << 20;  // bytes per pinned staging window
-constexpr int kStageWindows = 8;
+using tsr::kStageWindow;
+using tsr::kStageWindows;
+
+// Floats of split-K scratch and arrival counters every context holds for the
+// launches that split k among CTAs and add the chunks themselves.
+constexpr size_t kScratchFloats = 4u << 20;  // 16 MiB
+constexpr size_t kScratchTickets = 16384;
 
 int map_cuda(cudaError_t e) {
   if (e == cudaSuccess) return tsr::kOk;
@@ -29,83 +35,116 @@ int map_cuda(cudaError_t e) {
   return tsr::kDeviceError;
 }
 
+// One word of pinned, mapped host memory for the whole process: a device wait
+// that gives up raises it (pipeline.cuh), tsr_synchronize reads it.
+unsigned int* host_error_word() {
+  static unsigned int* word = [] {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, 64, cudaHostAllocPortable | cudaHostAllocMapped) != cudaSuccess) {
+      cudaGetLastError();
+      return static_cast<unsigned int*>(nullptr);
+    }
+    std::memset(p, 0, 64);
+    return static_cast<unsigned int*>(p);
+  }();
+  return word;
+}
+
+// Points the kernels of every file at the error word, once per device.
+void publish_error_word(int device) {
+  static std::mutex mutex;
+  static bool done[64] = {};
+  std::lock_guard<std::mutex> lock(mutex);
+  if (device < 0 || device >= 64 || done[device]) return;
+  unsigned int* word = host_error_word();
+  if (word == nullptr) return;
+  tsr::staged_set_error_word(word);
+  tsr::staged_q6k_set_error_word(word);
+  tsr::staged_f16_set_error_word(word);
+  tsr::umma_set_error_word(word);
+  done[device] = true;
+}
+
 }  // namespace
 
-struct tsr_context {
-  int device = 0;
-  cudaStream_t stream = nullptr;
-  bool owns_stream = false;
-  std::string error;
-  // Pinned staging ring for host<->device copies: a window is reused only
-  // after the copy that read or wrote it has completed (event guard).
-  unsigned char* stage = nullptr;
-  cudaEvent_t stage_done[kStageWindows] = {};
-  bool stage_busy[kStageWindows] = {};
-  int stage_next = 0;
-  bool peer_enabled[64] = {};
-  unsigned int seen_timeouts = 0;
-  std::mutex mutex;
+int tsr_context::fail(cudaError_t e, const char* what) {
+  char buf[256];
+  std::snprintf(buf, sizeof(buf), "%s: %s", what, cudaGetErrorString(e));
+  error = buf;
+  return map_cuda(e);
+}
 
-  int fail(cudaError_t e, const char* what) {
-    char buf[256];
-    std::snprintf(buf, sizeof(buf), "%s: %s", what, cudaGetErrorString(e));
-    error = buf;
-    return map_cuda(e);
+int tsr_context::select() {
+  // The current device is per host thread and the reference drives one
+  // backend from different threads over time (a fresh thread per
+  // tensor-parallel step): re-select on every entry.
+  // cudaSetDevice on the already-current device is a cheap no-op; no cache
+  // is kept because other entry points of the library also switch devices.
+  const cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) return fail(e, "cudaSetDevice");
+  return tsr::kOk;
+}
+
+unsigned char* tsr_context::window(int* index) {
+  const int i = stage_next;
+  stage_next = (stage_next + 1) % kStageWindows;
+  if (stage_busy[i]) {
+    cudaEventSynchronize(stage_done[i]);
+    stage_busy[i] = false;
   }
-  int select() {
-    // The current device is per host thread and the reference drives one
-    // backend from different threads over time (a fresh thread per
-    // tensor-parallel step): re-select on every entry.
-    // cudaSetDevice on the already-current device is a cheap no-op; no cache
-    // is kept because other entry points of the library also switch devices.
-    const cudaError_t e = cudaSetDevice(device);
-    if (e != cudaSuccess) return fail(e, "cudaSetDevice");
-    return tsr::kOk;
-  }
-  unsigned char* window(int* index) {
-    const int i = stage_next;
-    stage_next = (stage_next + 1) % kStageWindows;
-    if (stage_busy[i]) {
-      cudaEventSynchronize(stage_done[i]);
-      stage_busy[i] = false;
-    }
-    *index = i;
-    return stage + static_cast<size_t>(i) * kStageWindow;
-  }
-};
+  *index = i;
+  return stage + static_cast<size_t>(i) * kStageWindow;
+}
 
 namespace tsr {
 
-// Last output range written by a launch of this library, per stream.
-bool pdl_allowed(cudaStream_t stream, const void* read_ptr, size_t read_bytes, const void* out_ptr,
-                 size_t out_bytes) {
+// Output ranges written by the last launch of this library, per stream.
+bool pdl_allowed_ranges(cudaStream_t stream, const void* const* reads, const size_t* read_bytes, int nreads,
+                        const void* const* writes, const size_t* write_bytes, int nwrites) {
   static const bool enabled = [] {
     const char* v = std::getenv("TSR_PDL");
     return v == nullptr || std::atoi(v) != 0;
   }();
+  constexpr int kRanges = 4;
   struct Last {
     cudaStream_t stream;
-    const unsigned char* ptr;
-    size_t bytes;
+    bool used;
+    int count;
+    const unsigned char* ptr[kRanges];
+    size_t bytes[kRanges];
   };
   static std::mutex mutex;
   static Last table[16] = {};
   std::lock_guard<std::mutex> lock(mutex);
   Last* slot = nullptr;
   for (Last& l : table)
-    if (l.ptr != nullptr && l.stream == stream) slot = &l;
+    if (l.used && l.stream == stream) slot = &l;
   bool ok = enabled;
   if (slot != nullptr) {
-    const auto* r = static_cast<const unsigned char*>(read_ptr);
-    if (r < slot->ptr + slot->bytes && slot->ptr < r + read_bytes) ok = false;  // previous output is our weight
+    for (int i = 0; i < nreads; ++i) {
+      const auto* r = static_cast<const unsigned char*>(reads[i]);
+      for (int j = 0; j < slot->count; ++j)
+        if (r < slot->ptr[j] + slot->bytes[j] && slot->ptr[j] < r + read_bytes[i]) ok = false;  // previous output is our weight
+    }
   }
   if (slot == nullptr) {
     static int next = 0;
     slot = &table[next];
     next = (next + 1) % 16;
   }
-  *slot = Last{stream, static_cast<const unsigned char*>(out_ptr), out_bytes};
+  slot->stream = stream;
+  slot->used = true;
+  slot->count = nwrites < kRanges ? nwrites : kRanges;
+  for (int j = 0; j < slot->count; ++j) {
+    slot->ptr[j] = static_cast<const unsigned char*>(writes[j]);
+    slot->bytes[j] = write_bytes[j];
+  }
   return ok;
+}
+
+bool pdl_allowed(cudaStream_t stream, const void* read_ptr, size_t read_bytes, const void* out_ptr,
+                 size_t out_bytes) {
+  return pdl_allowed_ranges(stream, &read_ptr, &read_bytes, 1, &out_ptr, &out_bytes, 1);
 }
 
 int allow_dynamic_smem(const void* kernel, int bytes) {
@@ -191,6 +230,24 @@ static int create_common(int device_index, cudaStream_t borrowed, bool borrow, t
   }
   for (int i = 0; i < kStageWindows; ++i)
     cudaEventCreateWithFlags(&ctx->stage_done[i], cudaEventDisableTiming);
+  // Split-K scratch of the merged launches, held for the life of the context so
+  // that no launch ever allocates (graphs keep its address).
+  void* scratch = nullptr;
+  e = cudaMalloc(&scratch, kScratchFloats * 4 + kScratchTickets * 4);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    cudaFreeHost(ctx->stage);
+    if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return map_cuda(e);
+  }
+  ctx->scratch.part = static_cast<float*>(scratch);
+  ctx->scratch.part_floats = kScratchFloats;
+  ctx->scratch.tickets = reinterpret_cast<unsigned int*>(ctx->scratch.part + kScratchFloats);
+  ctx->scratch.ntickets = kScratchTickets;
+  cudaMemset(ctx->scratch.tickets, 0, kScratchTickets * 4);
+  publish_error_word(device_index);
+  if (const unsigned int* word = host_error_word()) ctx->seen_error_word = *reinterpret_cast<const volatile unsigned int*>(word);
   // Keep freed pool memory cached: a mid-step scratch growth must not pay
   // for a device allocation twice.
   cudaMemPool_t pool;
@@ -213,7 +270,11 @@ int tsr_create_on_stream(int device_index, void* cuda_stream, tsr_context** out)
 void tsr_destroy(tsr_context* ctx) {
   if (!ctx) return;
   cudaSetDevice(ctx->device);
+  tsr::flush_pending(ctx);
   cudaStreamSynchronize(ctx->stream);
+  for (auto& g : ctx->graphs)
+    if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+  cudaFree(ctx->scratch.part);
   for (int i = 0; i < kStageWindows; ++i) cudaEventDestroy(ctx->stage_done[i]);
   cudaFreeHost(ctx->stage);
   if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
@@ -259,6 +320,7 @@ int tsr_free(tsr_context* ctx, int kind, void* handle) {
   if (!ctx) return tsr::kInvalidArgument;
   if (!handle) return tsr::kOk;
   if (int s = ctx->select()) return s;
+  if (int s = tsr::flush_pending(ctx)) return s;  // a queued launch may use the buffer
   cudaError_t e;
   if (kind == TSR_MEM_DEVICE) {
     e = cudaFreeAsync(handle, ctx->stream);
@@ -273,6 +335,7 @@ int tsr_copy_h2d(tsr_context* ctx, void* dst, size_t dst_offset, const void* src
   if (!ctx || (!dst && bytes) || (!src && bytes)) return tsr::kInvalidArgument;
   if (bytes == 0) return tsr::kOk;
   if (int s = ctx->select()) return s;
+  if (int s = tsr::flush_pending(ctx)) return s;
   std::lock_guard<std::mutex> lock(ctx->mutex);
   auto* d = static_cast<unsigned char*>(dst) + dst_offset;
   const auto* h = static_cast<const unsigned char*>(src);
@@ -294,6 +357,7 @@ int tsr_copy_d2h(tsr_context* ctx, const void* src, size_t src_offset, void* dst
   if (!ctx || (!dst && bytes) || (!src && bytes)) return tsr::kInvalidArgument;
   if (bytes == 0) return tsr::kOk;
   if (int s = ctx->select()) return s;
+  if (int s = tsr::flush_pending(ctx)) return s;
   std::lock_guard<std::mutex> lock(ctx->mutex);
   const auto* d = static_cast<const unsigned char*>(src) + src_offset;
   auto* h = static_cast<unsigned char*>(dst);
@@ -325,6 +389,7 @@ int tsr_copy_d2d(tsr_context* ctx, const void* src, size_t src_offset, void* dst
   if (!ctx || (!dst && bytes) || (!src && bytes)) return tsr::kInvalidArgument;
   if (bytes == 0) return tsr::kOk;
   if (int s = ctx->select()) return s;
+  if (int s = tsr::flush_pending(ctx)) return s;
   const cudaError_t e = cudaMemcpyAsync(static_cast<unsigned char*>(dst) + dst_offset,
                                         static_cast<const unsigned char*>(src) + src_offset, bytes,
                                         cudaMemcpyDeviceToDevice, ctx->stream);
@@ -335,6 +400,7 @@ int tsr_copy_peer(tsr_context* ctx, void* dst, int src_device, const void* src, 
   if (!ctx || (!dst && bytes) || (!src && bytes)) return tsr::kInvalidArgument;
   if (bytes == 0) return tsr::kOk;
   if (int s = ctx->select()) return s;
+  if (int s = tsr::flush_pending(ctx)) return s;
   if (src_device != ctx->device && src_device >= 0 && src_device < 64 &&
       !ctx->peer_enabled[src_device]) {
     int can = 0;
@@ -355,18 +421,56 @@ int tsr_copy_peer(tsr_context* ctx, void* dst, int src_device, const void* src, 
 int tsr_synchronize(tsr_context* ctx) {
   if (!ctx) return tsr::kInvalidArgument;
   if (int s = ctx->select()) return s;
+  if (int s = tsr::flush_pending(ctx)) return s;
   const cudaError_t e = cudaStreamSynchronize(ctx->stream);
   if (e != cudaSuccess) return ctx->fail(e, "cudaStreamSynchronize");
-  // A staged kernel whose bounded wait ran out has left wrong results behind.
-  unsigned int timeouts = 0, umma = 0, q6k = 0, f16 = 0;
-  tsr::umma_wait_timeouts(&umma);
-  tsr::staged_q6k_wait_timeouts(&q6k);
-  tsr::staged_f16_wait_timeouts(&f16);
-  if (tsr::staged_wait_timeouts(&timeouts) == tsr::kOk && (timeouts += umma + q6k + f16) != ctx->seen_timeouts) {
-    ctx->seen_timeouts = timeouts;
-    ctx->error = "a staged kernel gave up waiting for a TMA copy";
-    return tsr::kDeviceError;
+  // A kernel whose bounded wait ran out has left wrong results behind: it raised the
+  // host-visible error word.  Only then are the per-file counters worth a copy each.
+  const unsigned int* word = host_error_word();
+  const unsigned int raised = word ? *reinterpret_cast<const volatile unsigned int*>(word) : 0u;
+  if (word == nullptr || raised != 0u) {
+    unsigned int timeouts = 0, umma = 0, q6k = 0, f16 = 0;
+    tsr::umma_wait_timeouts(&umma);
+    tsr::staged_q6k_wait_timeouts(&q6k);
+    tsr::staged_f16_wait_timeouts(&f16);
+    if (tsr::staged_wait_timeouts(&timeouts) == tsr::kOk && (timeouts += umma + q6k + f16) != ctx->seen_timeouts) {
+      ctx->seen_timeouts = timeouts;
+      ctx->error = "a staged kernel gave up waiting for a TMA copy";
+      return tsr::kDeviceError;
+    }
   }
+  return tsr::kOk;
+}
+
+int tsr_set_deferred(tsr_context* ctx, int on) {
+  if (!ctx) return tsr::kInvalidArgument;
+  if (int s = ctx->select()) return s;
+  if (int s = tsr::flush_pending(ctx)) return s;
+  ctx->deferred = on != 0;
+  ctx->use_graphs = on != 2;
+  return tsr::kOk;
+}
+
+int tsr_flush(tsr_context* ctx) {
+  if (!ctx) return tsr::kInvalidArgument;
+  if (int s = ctx->select()) return s;
+  return tsr::flush_pending(ctx);
+}
+
+int tsr_launch_stats(tsr_context* ctx, uint64_t* api_launches, uint64_t* device_kernels, uint64_t* graph_launches) {
+  if (!ctx) return tsr::kInvalidArgument;
+  if (api_launches) *api_launches = ctx->stats.api_launches;
+  if (device_kernels) *device_kernels = ctx->stats.device_kernels;
+  if (graph_launches) *graph_launches = ctx->stats.graph_launches;
+  return tsr::kOk;
+}
+
+int tsr_tp_bind(tsr_context* ctx, tsr_tp_comm* comm) {
+  if (!ctx) return tsr::kInvalidArgument;
+  if (int s = ctx->select()) return s;
+  if (int s = tsr::flush_pending(ctx)) return s;
+  if (comm != nullptr && tsr::tp_device_of(comm) != ctx->device) return tsr::kInvalidArgument;
+  ctx->tp = comm;
   return tsr::kOk;
 }
 

@@ -8,14 +8,13 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 
+#include "context.h"
 #include "launch.h"
 #include "tessera_b200.h"
 
 using namespace tsr;
-
-struct tsr_context;
-extern "C" void* tsr_context_stream(const tsr_context* ctx);
 
 namespace {
 
@@ -59,6 +58,23 @@ int staged_in_chunks(uint64_t m, uint64_t n, Launch launch) {
 
 }  // namespace
 
+namespace tsr {
+int gemm_q4k_dispatch(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                      uint64_t split, cudaStream_t st, bool allow_scratch) {
+  const int rc = (m > kStagedRows && split == 1)
+                     ? staged_in_chunks(m, n, [&](uint64_t i0, uint64_t rows) {
+                         return staged_gemm_q4k(a + i0 * k, w, c + i0 * n, rows, n, k, 1, st);
+                       })
+                     : staged_gemm_q4k(a, w, c, m, n, k, split, st);
+  if (rc != kUnsupportedFeature) return rc;
+  if (m >= 9 && split == 1) {
+    const int rt = umma_gemm(0, a, w, nullptr, c, m, n, k, st, allow_scratch);
+    if (rt != kUnsupportedFeature) return rt;
+  }
+  return rows_gemm_q4k(a, w, c, m, n, k, split, st);
+}
+}  // namespace tsr
+
 extern "C" {
 
 int tsr_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
@@ -67,18 +83,7 @@ int tsr_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n
       split == 0 || (k / 256) % split != 0 || split > 65535)
     return kInvalidArgument;
   if (!aligned16(a) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
-  const cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int rc = (m > kStagedRows && split == 1)
-                     ? staged_in_chunks(m, n, [&](uint64_t i0, uint64_t rows) {
-                         return staged_gemm_q4k(a + i0 * k, w, c + i0 * n, rows, n, k, 1, st);
-                       })
-                     : staged_gemm_q4k(a, w, c, m, n, k, split, st);
-  if (rc != kUnsupportedFeature) return rc;
-  if (m >= 9 && split == 1) {
-    const int rt = umma_gemm(0, a, w, nullptr, c, m, n, k, static_cast<cudaStream_t>(stream));
-    if (rt != kUnsupportedFeature) return rt;
-  }
-  return rows_gemm_q4k(a, w, c, m, n, k, split, static_cast<cudaStream_t>(stream));
+  return gemm_q4k_dispatch(a, w, c, m, n, k, split, static_cast<cudaStream_t>(stream), true);
 }
 
 int tsr_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
@@ -159,6 +164,8 @@ struct Args {
   int nsc;
   uint32_t grid_y;
   cudaStream_t stream;
+  bool dry;          // check the arguments only (a deferred launch is checked when it is made)
+  tsr_context* ctx;  // for the ids that need the context's scratch or communicator
 };
 
 bool shape(const Args& a, int nbuf, int nsc) { return a.nbuf == nbuf && a.nsc == nsc; }
@@ -179,6 +186,7 @@ int block_gemm(const Args& a, uint64_t split, uint64_t rows_required) {
   if (!holds(a, 0, m * k * 4) || !holds(a, 1, n * (k / 256) * BLOCK_BYTES) ||
       !holds(a, 2, split * m * n * 4))
     return kInvalidArgument;
+  if (a.dry) return kOk;
   auto* A = static_cast<const float*>(a.buf[0]);
   auto* C = static_cast<float*>(const_cast<void*>(a.buf[2]));
   return Q6 ? tsr_gemm_q6k(A, a.buf[1], C, m, n, k, split, a.stream)
@@ -215,6 +223,7 @@ int k_vec_reduce(const Args& a) {
   const uint64_t total = a.sc[0], split = a.sc[1];
   if (total == 0 || split == 0 || !holds(a, 0, split * total * 4) || !holds(a, 1, total * 4))
     return kInvalidArgument;
+  if (a.dry) return kOk;
   return tsr_gemm_vec_reduce(static_cast<const float*>(a.buf[0]),
                              static_cast<float*>(const_cast<void*>(a.buf[1])), total, split,
                              a.stream);
@@ -228,6 +237,7 @@ int k_mxfp4(const Args& a) {
   if (!dims_ok(m, n, k) || k % 32 != 0) return kInvalidArgument;
   if (!holds(a, 0, m * k * 4) || !holds(a, 1, n * (k / 2) + n * (k / 32)) || !holds(a, 2, m * n * 4))
     return kInvalidArgument;
+  if (a.dry) return kOk;
   return tsr_gemm_mxfp4(static_cast<const float*>(a.buf[0]), a.buf[1],
                         static_cast<float*>(const_cast<void*>(a.buf[2])), m, n, k, a.stream);
 }
@@ -243,6 +253,7 @@ int k_mxfp4_wmma(const Args& a) {
   if (!holds(a, 0, m * k) || !holds(a, 1, n * (k / 2) + n * (k / 32)) || !holds(a, 2, m * 4) ||
       !holds(a, 3, n) || !holds(a, 4, split * m * n * 4))
     return kInvalidArgument;
+  if (a.dry) return kOk;
   return tsr_gemm_mxfp4_w4a8(a.buf[0], a.buf[1], static_cast<const float*>(a.buf[2]), a.buf[3],
                              static_cast<float*>(const_cast<void*>(a.buf[4])), m, n, k, split,
                              a.stream);
@@ -254,6 +265,7 @@ int k_row_ref(const Args& a) {
   const uint64_t n = a.sc[0], k = a.sc[1];
   if (!dims_ok(1, n, k) || k % 32 != 0) return kInvalidArgument;
   if (!holds(a, 0, n * (k / 2) + n * (k / 32)) || !holds(a, 1, n)) return kInvalidArgument;
+  if (a.dry) return kOk;
   return tsr_mxfp4_row_ref(a.buf[0], const_cast<void*>(a.buf[1]), n, k, a.stream);
 }
 
@@ -265,6 +277,7 @@ int k_fp8(const Args& a) {
   if (!holds(a, 0, m * k * 4) || !holds(a, 1, n * k) || !holds(a, 2, n * 4) ||
       !holds(a, 3, m * n * 4))
     return kInvalidArgument;
+  if (a.dry) return kOk;
   return tsr_gemm_fp8(static_cast<const float*>(a.buf[0]), a.buf[1],
                       static_cast<const float*>(a.buf[2]),
                       static_cast<float*>(const_cast<void*>(a.buf[3])), m, n, k, a.stream);
@@ -276,6 +289,7 @@ int k_quant(const Args& a) {
   const uint64_t rows = a.sc[0], cols = a.sc[1];
   if (!dims_ok(rows, cols, 1) || !holds(a, 0, rows * cols * 4) || !holds(a, 1, rows * 4))
     return kInvalidArgument;
+  if (a.dry) return kOk;
   return tsr_quantize_fp8(static_cast<float*>(const_cast<void*>(a.buf[0])),
                           static_cast<float*>(const_cast<void*>(a.buf[1])), rows, cols, a.stream);
 }
@@ -288,6 +302,7 @@ int k_quant_pack(const Args& a) {
   if (!dims_ok(rows, cols, 1) || cols % 4 != 0 || !holds(a, 0, rows * cols * 4) ||
       !holds(a, 1, rows * cols) || !holds(a, 2, rows * 4))
     return kInvalidArgument;
+  if (a.dry) return kOk;
   return tsr_quantize_fp8_pack(static_cast<const float*>(a.buf[0]), const_cast<void*>(a.buf[1]),
                                static_cast<float*>(const_cast<void*>(a.buf[2])), rows, cols,
                                a.stream);
@@ -297,6 +312,7 @@ int k_quant_pack(const Args& a) {
 int k_round(const Args& a) {
   if (!shape(a, 1, 1)) return kInvalidArgument;
   if (a.sc[0] == 0 || !holds(a, 0, a.sc[0] * 4)) return kInvalidArgument;
+  if (a.dry) return kOk;
   return tsr_round_bf16(static_cast<float*>(const_cast<void*>(a.buf[0])), a.sc[0], a.stream);
 }
 
@@ -306,6 +322,7 @@ int k_add(const Args& a) {
   const uint64_t n = a.sc[0];
   if (n == 0 || !holds(a, 0, n * 4) || !holds(a, 1, n * 4) || !holds(a, 2, n * 4))
     return kInvalidArgument;
+  if (a.dry) return kOk;
   return tsr_add(static_cast<const float*>(a.buf[0]), static_cast<const float*>(a.buf[1]),
                  static_cast<float*>(const_cast<void*>(a.buf[2])), n, a.stream);
 }
@@ -315,8 +332,66 @@ int k_fill(const Args& a) {
   if (!shape(a, 1, 2)) return kInvalidArgument;
   const uint64_t n = a.sc[1];
   if (n == 0 || !holds(a, 0, n * 4)) return kInvalidArgument;
+  if (a.dry) return kOk;
   return tsr_fill(static_cast<int32_t*>(const_cast<void*>(a.buf[0])),
                   static_cast<int32_t>(a.sc[0]), n, a.stream);
+}
+
+// Sum over tensor-parallel ranks of an [m][n] fp32 matrix in place, on the communicator
+// bound to the context (tsr_tp_bind).  With one rank (or none bound) it is the identity.
+int tp_sum_in_place(const Args& a, float* data, uint64_t m, uint64_t n) {
+  if (a.ctx == nullptr || a.ctx->tp == nullptr) return kOk;
+  return tp_allreduce_tiled(a.ctx->tp, data, m, n, static_cast<uint64_t>(tp_tile_rows(n)), a.stream);
+}
+
+// One or several projections that share A as one staged launch which splits k as it
+// sees fit, adds the chunks itself and, with `tp`, ends with the sum over ranks.
+// fmt: 0 Q4_K, 1 Q6_K.  kUnsupportedFeature: the caller issues the pieces one by one.
+int fused_group(tsr_context* ctx, int fmt, const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k,
+                bool with_tp, cudaStream_t st) {
+  if (ctx == nullptr) return kUnsupportedFeature;
+  TpTail tail{};
+  const TpTail* tp = nullptr;
+  if (with_tp && ctx->tp != nullptr) {
+    if (int rc = tp_tail_of(ctx->tp, &tail)) return rc;
+    if (tail.world > 1) tp = &tail;
+  }
+  return fmt == 0 ? staged_group_q4k(a, t, count, m, k, 0, &ctx->scratch, tp, st)
+                  : staged_group_q6k(a, t, count, m, k, 0, &ctx->scratch, tp, st);
+}
+
+// gemm_q4k_vec_allreduce / gemm_q6k_vec_allreduce: buffers A, W, C; scalars m, n, k.
+// Row-parallel projection of this rank's k range followed by the sum over the ranks of
+// the bound communicator; C receives the same bits on every rank.  No reference id:
+// there the projection is followed by TpReduce (src/models/qwen3_5/trunk.cpp:226-266).
+template <uint64_t BLOCK_BYTES, bool Q6>
+int k_block_allreduce(const Args& a) {
+  if (!shape(a, 3, 3)) return kInvalidArgument;
+  const uint64_t m = a.sc[0], n = a.sc[1], k = a.sc[2];
+  if (!dims_ok(m, n, k) || k % 256 != 0 || n % 4 != 0) return kInvalidArgument;
+  if (!holds(a, 0, m * k * 4) || !holds(a, 1, n * (k / 256) * BLOCK_BYTES) || !holds(a, 2, m * n * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  auto* A = static_cast<const float*>(a.buf[0]);
+  auto* C = static_cast<float*>(const_cast<void*>(a.buf[2]));
+  const GroupTarget t{a.buf[1], C, n};
+  const int rc = fused_group(a.ctx, Q6 ? 1 : 0, A, &t, 1, m, k, true, a.stream);
+  if (rc != kUnsupportedFeature) return rc;
+  // outside the staged kernels' range: the projection by itself, then the same tiles' sum
+  const int rp = Q6 ? tsr_gemm_q6k(A, a.buf[1], C, m, n, k, 1, a.stream) : tsr_gemm_q4k(A, a.buf[1], C, m, n, k, 1, a.stream);
+  if (rp != kOk) return rp;
+  return tp_sum_in_place(a, C, m, n);
+}
+
+// allreduce_sum: buffer X; scalars m, n.  X[m][n] becomes its sum over the ranks of the
+// bound communicator (the job of TpReduce, trunk.cpp:226-266, for callers that keep
+// their own projection launches).
+int k_allreduce_sum(const Args& a) {
+  if (!shape(a, 1, 2)) return kInvalidArgument;
+  const uint64_t m = a.sc[0], n = a.sc[1];
+  if (!dims_ok(m, n, 1) || n % 4 != 0 || !holds(a, 0, m * n * 4)) return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tp_sum_in_place(a, static_cast<float*>(const_cast<void*>(a.buf[0])), m, n);
 }
 
 struct Entry {
@@ -356,10 +431,214 @@ const Entry kTable[] = {
     {"quantize_fp8", k_quant},
     {"quantize_fp8_pack", k_quant_pack},
     {"quantize_fp8_pack_rows", k_quant_pack},
+    {"gemm_q4k_vec_allreduce", k_block_allreduce<144, false>},
+    {"gemm_q6k_vec_allreduce", k_block_allreduce<210, true>},
+    {"allreduce_sum", k_allreduce_sum},
 };
 constexpr int kCount = static_cast<int>(sizeof(kTable) / sizeof(kTable[0]));
 
 }  // namespace
+
+// ------------------------------------------------- deferred submission
+//
+// In deferred mode tsr_launch only queues.  When the queue is flushed (a copy, a
+// synchronisation, tsr_flush) it is rewritten before it is issued:
+//   * gemm_<q4k|q6k>_vec / _rows<R> with a split followed by the gemm_vec_reduce of
+//     its partial buffer becomes one projection that writes the final output (the
+//     launch picks its own split of k and adds the chunks itself; the caller's partial
+//     buffer is then not written);
+//   * consecutive projections of one format that read the same activations with the
+//     same m and k become one launch over up to four weight tensors.
+// Everything else is issued as it was queued, in order.  A rewritten queue that has
+// been flushed before is replayed as a CUDA graph (captured on its second appearance,
+// keyed by a hash of the queue as the caller made it).
+namespace {
+
+struct Projection {
+  int fmt;  // 0 Q4_K, 1 Q6_K
+  const float* a;
+  GroupTarget t;
+  uint64_t m, k;
+  size_t ops;  // queue entries it stands for: 1, or 2 with the reduce
+};
+
+bool name_starts(const char* name, const char* prefix) { return std::strncmp(name, prefix, std::strlen(prefix)) == 0; }
+bool name_ends(const char* name, const char* suffix) {
+  const size_t a = std::strlen(name), b = std::strlen(suffix);
+  return a >= b && std::strcmp(name + a - b, suffix) == 0;
+}
+
+bool as_projection(const std::vector<PendingLaunch>& q, size_t i, Projection* out) {
+  const PendingLaunch& op = q[i];
+  const char* name = kTable[op.kernel].name;
+  int fmt;
+  if (name_starts(name, "gemm_q4k")) fmt = 0;
+  else if (name_starts(name, "gemm_q6k")) fmt = 1;
+  else return false;
+  if (name_ends(name, "_allreduce") || op.nbuf != 3 || (op.nsc != 3 && op.nsc != 4)) return false;
+  const uint64_t m = op.sc[0], n = op.sc[1], k = op.sc[2], split = op.nsc == 4 ? op.sc[3] : 1;
+  if (m > 8) return false;
+  *out = Projection{fmt, static_cast<const float*>(op.buf[0]),
+                    GroupTarget{op.buf[1], static_cast<float*>(const_cast<void*>(op.buf[2])), n}, m, k, 1};
+  if (split == 1) return true;
+  if (i + 1 >= q.size()) return false;
+  const PendingLaunch& red = q[i + 1];
+  if (std::strcmp(kTable[red.kernel].name, "gemm_vec_reduce") != 0 || red.buf[0] != op.buf[2] ||
+      red.sc[0] != m * n || red.sc[1] != split)
+    return false;
+  out->t.c = static_cast<float*>(const_cast<void*>(red.buf[1]));
+  out->ops = 2;
+  return true;
+}
+
+bool overlaps(const void* p, size_t pb, const void* q, size_t qb) {
+  const auto* a = static_cast<const unsigned char*>(p);
+  const auto* b = static_cast<const unsigned char*>(q);
+  return a < b + qb && b < a + pb;
+}
+
+int issue_one(tsr_context* ctx, const PendingLaunch& op) {
+  const Args a{op.buf, op.bytes, op.nbuf, op.sc, op.nsc, op.grid_y, ctx->stream, false, ctx};
+  return kTable[op.kernel].fn(a);
+}
+
+// Issues the queue `q` on the context's stream, rewritten as described above.
+int issue_queue(tsr_context* ctx, const std::vector<PendingLaunch>& q) {
+  size_t i = 0;
+  while (i < q.size()) {
+    Projection first;
+    if (!as_projection(q, i, &first)) {
+      if (int rc = issue_one(ctx, q[i])) return rc;
+      ++i;
+      continue;
+    }
+    GroupTarget t[kMaxGroup];
+    int count = 0;
+    size_t end = i;
+    const size_t a_bytes = first.m * first.k * 4;
+    while (count < kMaxGroup && end < q.size()) {
+      Projection next;
+      if (!as_projection(q, end, &next)) break;
+      if (next.fmt != first.fmt || next.a != first.a || next.m != first.m || next.k != first.k) break;
+      // an output that lands in the shared activations would change what later members read
+      if (overlaps(next.t.c, next.m * next.t.n * 4, first.a, a_bytes)) {
+        if (count == 0) {
+          t[count++] = next.t;
+          end += next.ops;
+        }
+        break;
+      }
+      t[count++] = next.t;
+      end += next.ops;
+    }
+    const int rc = fused_group(ctx, first.fmt, first.a, t, count, first.m, first.k, false, ctx->stream);
+    if (rc == kUnsupportedFeature) {
+      for (size_t j = i; j < end; ++j)
+        if (int r = issue_one(ctx, q[j])) return r;
+    } else if (rc != kOk) {
+      return rc;
+    }
+    i = end;
+  }
+  return kOk;
+}
+
+uint64_t mix(uint64_t h, uint64_t v) {
+  h ^= v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+  h *= 0xFF51AFD7ED558CCDull;
+  return h ^ (h >> 29);
+}
+
+uint64_t queue_hash(const tsr_context* ctx, const std::vector<PendingLaunch>& q) {
+  uint64_t h = mix(0x243F6A8885A308D3ull, reinterpret_cast<uintptr_t>(ctx->tp));
+  for (const PendingLaunch& op : q) {
+    h = mix(h, (static_cast<uint64_t>(op.kernel) << 40) ^ (static_cast<uint64_t>(op.grid_y) << 8) ^
+                   (static_cast<uint64_t>(op.nbuf) << 4) ^ static_cast<uint64_t>(op.nsc));
+    for (int i = 0; i < op.nbuf; ++i) h = mix(h, reinterpret_cast<uintptr_t>(op.buf[i]));
+    for (int i = 0; i < op.nsc; ++i) h = mix(h, op.sc[i]);
+  }
+  return h;
+}
+
+constexpr size_t kMaxGraphs = 32;
+constexpr size_t kMinGraphOps = 8;  // shorter queues are cheaper to issue than to look up
+
+}  // namespace
+
+namespace tsr {
+
+int flush_pending(tsr_context* ctx) {
+  if (ctx->pending.empty()) return kOk;
+  std::vector<PendingLaunch> q;
+  q.swap(ctx->pending);
+  ++ctx->stats.flushes;
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(ctx->stream, &capturing) != cudaSuccess) {
+    cudaGetLastError();
+    capturing = cudaStreamCaptureStatusNone;
+  }
+  const bool graphs = ctx->use_graphs && capturing == cudaStreamCaptureStatusNone && q.size() >= kMinGraphOps;
+  uint64_t hash = 0;
+  if (graphs) {
+    hash = queue_hash(ctx, q);
+    auto it = ctx->graphs.find(hash);
+    if (it != ctx->graphs.end() && it->second.ops == q.size()) {
+      it->second.last_use = ++ctx->use_clock;
+      const cudaError_t e = cudaGraphLaunch(it->second.exec, ctx->stream);
+      if (e != cudaSuccess) return ctx->fail(e, "cudaGraphLaunch");
+      ctx->stats.device_kernels += it->second.kernels;
+      ++ctx->stats.graph_launches;
+      return kOk;
+    }
+    if (ctx->seen_queues[hash]++ >= 1) {
+      // second appearance: capture the rewritten queue, keep it, replay it
+      const uint64_t before = launch_counter().load();
+      if (cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+        const int rc = issue_queue(ctx, q);
+        cudaGraph_t graph = nullptr;
+        const cudaError_t ec = cudaStreamEndCapture(ctx->stream, &graph);
+        cudaGraphExec_t exec = nullptr;
+        if (rc == kOk && ec == cudaSuccess && graph != nullptr &&
+            cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) {
+          cudaGraphDestroy(graph);
+          if (ctx->graphs.size() >= kMaxGraphs) {
+            auto oldest = ctx->graphs.begin();
+            for (auto g = ctx->graphs.begin(); g != ctx->graphs.end(); ++g)
+              if (g->second.last_use < oldest->second.last_use) oldest = g;
+            // the stream may still be running it
+            cudaStreamSynchronize(ctx->stream);
+            cudaGraphExecDestroy(oldest->second.exec);
+            ctx->graphs.erase(oldest);
+          }
+          CachedGraph cg;
+          cg.exec = exec;
+          cg.last_use = ++ctx->use_clock;
+          cg.kernels = launch_counter().load() - before;
+          cg.ops = q.size();
+          ctx->graphs[hash] = cg;
+          ctx->seen_queues.erase(hash);
+          const cudaError_t e = cudaGraphLaunch(exec, ctx->stream);
+          if (e != cudaSuccess) return ctx->fail(e, "cudaGraphLaunch");
+          ctx->stats.device_kernels += cg.kernels;
+          ++ctx->stats.graph_launches;
+          return kOk;
+        }
+        if (graph != nullptr) cudaGraphDestroy(graph);
+        cudaGetLastError();  // nothing ran during the failed capture: issue the queue directly below
+      } else {
+        cudaGetLastError();
+      }
+    }
+    if (ctx->seen_queues.size() > 4096) ctx->seen_queues.clear();
+  }
+  const uint64_t before = launch_counter().load();
+  const int rc = issue_queue(ctx, q);
+  ctx->stats.device_kernels += launch_counter().load() - before;
+  if (rc != kOk) ctx->error = "a deferred launch failed when the queue was issued";
+  return rc;
+}
+
+}  // namespace tsr
 
 extern "C" {
 
@@ -381,7 +660,8 @@ int tsr_launch(tsr_context* ctx, int kernel, const uint32_t grid[3], const uint3
                const uint64_t* scalars, int n_scalars) {
   if (!ctx || kernel < 0 || kernel >= kCount) return kInvalidArgument;
   // ValidateLaunch, include/tessera/backend.hpp:138-148.
-  if (n_buffers < 0 || n_buffers > 16 || n_scalars < 0 || n_scalars > 16) return kInvalidArgument;
+  if (n_buffers < 0 || n_buffers > kMaxLaunchBuffers || n_scalars < 0 || n_scalars > kMaxLaunchScalars)
+    return kInvalidArgument;
   if ((n_buffers && (!buffers || !buffer_bytes)) || (n_scalars && !scalars)) return kInvalidArgument;
   uint32_t grid_y = 0;
   if (grid) {
@@ -391,13 +671,66 @@ int tsr_launch(tsr_context* ctx, int kernel, const uint32_t grid[3], const uint3
   if (block && (block[0] == 0 || block[1] == 0 || block[2] == 0)) return kInvalidArgument;
   for (int i = 0; i < n_buffers; ++i)
     if (!buffers[i]) return kInvalidArgument;
-  int device = 0;
-  cudaGetDevice(&device);
-  extern int tsr_context_device(const tsr_context*);
-  if (device != tsr_context_device(ctx)) cudaSetDevice(tsr_context_device(ctx));
-  Args a{buffers, buffer_bytes, n_buffers, scalars, n_scalars, grid_y,
-         static_cast<cudaStream_t>(tsr_context_stream(ctx))};
-  return kTable[kernel].fn(a);
+  if (int rc = ctx->select()) return rc;
+  Args a{buffers, buffer_bytes, n_buffers, scalars, n_scalars, grid_y, ctx->stream, ctx->deferred, ctx};
+  if (!ctx->deferred) {
+    const uint64_t before = launch_counter().load();
+    const int rc = kTable[kernel].fn(a);
+    ctx->stats.device_kernels += launch_counter().load() - before;
+    if (rc == kOk) ++ctx->stats.api_launches;
+    return rc;
+  }
+  // deferred: the arguments are checked now, the launch is made when the queue is flushed
+  if (int rc = kTable[kernel].fn(a)) return rc;
+  PendingLaunch op{};
+  op.kernel = kernel;
+  op.grid_y = grid_y;
+  op.nbuf = n_buffers;
+  op.nsc = n_scalars;
+  for (int i = 0; i < n_buffers; ++i) {
+    op.buf[i] = buffers[i];
+    op.bytes[i] = buffer_bytes[i];
+  }
+  for (int i = 0; i < n_scalars; ++i) op.sc[i] = scalars[i];
+  ctx->pending.push_back(op);
+  ++ctx->stats.api_launches;
+  return kOk;
+}
+
+int tsr_launch_many(tsr_context* ctx, const tsr_launch_desc* launches, size_t count, size_t* done) {
+  if (done) *done = 0;
+  if (!ctx || (!launches && count)) return kInvalidArgument;
+  for (size_t i = 0; i < count; ++i) {
+    const tsr_launch_desc& d = launches[i];
+    const int rc = tsr_launch(ctx, d.kernel, d.grid, d.block, d.buffers, d.buffer_bytes, d.n_buffers, d.scalars,
+                              d.n_scalars);
+    if (rc != kOk) return rc;
+    if (done) *done = i + 1;
+  }
+  return kOk;
+}
+
+int tsr_gemv_group(tsr_context* ctx, int fmt, const float* a, const void* const* w, float* const* c,
+                   const uint64_t* n, int count, uint64_t m, uint64_t k) {
+  if (!ctx || !a || !w || !c || !n || count < 1 || count > kMaxGroup || (fmt != 0 && fmt != 1) || !fits_int(m) ||
+      !fits_int(k) || k % 256 != 0 || !aligned16(a))
+    return kInvalidArgument;
+  GroupTarget t[kMaxGroup];
+  for (int i = 0; i < count; ++i) {
+    if (!w[i] || !c[i] || !fits_int(n[i]) || !aligned16(c[i]) || !aligned16(w[i])) return kInvalidArgument;
+    t[i] = GroupTarget{w[i], c[i], n[i]};
+  }
+  if (int rc = ctx->select()) return rc;
+  if (int rc = flush_pending(ctx)) return rc;
+  int rc = fused_group(ctx, fmt, a, t, count, m, k, false, ctx->stream);
+  if (rc == kUnsupportedFeature) {
+    for (int i = 0; i < count; ++i) {
+      rc = fmt == 0 ? tsr_gemm_q4k(a, w[i], c[i], m, n[i], k, 1, ctx->stream)
+                    : tsr_gemm_q6k(a, w[i], c[i], m, n[i], k, 1, ctx->stream);
+      if (rc != kOk) return rc;
+    }
+  }
+  return rc;
 }
 
 }  // extern "C"

@@ -644,7 +644,8 @@ int ring_maps(int fmt, const void* w, uint64_t n, uint64_t k, RingMaps* out) {
 // Device scratch for the pre-converted activations, one buffer per (device, stream),
 // grown on demand and never freed before exit (a captured graph may hold the pointer).
 // Returns null when the stream is being captured and no large enough buffer exists yet:
-// the tiles then convert the activations themselves.
+// the tiles then convert the activations themselves.  The memory comes from the
+// stream-ordered pool, so growing it never synchronises the device.
 unsigned char* activation_scratch(cudaStream_t st, size_t bytes) {
   struct Entry {
     int device;
@@ -667,7 +668,7 @@ unsigned char* activation_scratch(cudaStream_t st, size_t bytes) {
   size_t want = 4u << 20;
   while (want < bytes) want <<= 1;
   void* ptr = nullptr;
-  if (cudaMalloc(&ptr, want) != cudaSuccess) {
+  if (cudaMallocAsync(&ptr, want, st) != cudaSuccess) {
     cudaGetLastError();
     return nullptr;
   }
@@ -676,7 +677,7 @@ unsigned char* activation_scratch(cudaStream_t st, size_t bytes) {
 }
 
 template <int FMT, bool RING>
-int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st) {
+int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st, bool allow_scratch) {
   const int tok_pad = ((p.m < kMaxTokens ? p.m : kMaxTokens) + 7) & ~7;
   const size_t ring = RING ? static_cast<size_t>(kRawStages) * RingFmt<FMT>::kStagePitch : 0;
   const size_t smem = 1024 + ring + kBufs * kASlabBytes + kBufs * static_cast<size_t>(2 * tok_pad) * kSlab * 2 + 256;
@@ -685,7 +686,7 @@ int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st) {
                   static_cast<unsigned>((p.m + kMaxTokens - 1) / kMaxTokens));
   // activations -> operand layout once per launch, when scratch is to be had
   const int nslabs = p.k / kSlab;
-  p.bpre = activation_scratch(st, static_cast<size_t>(grid.y) * nslabs * kBSlabPitch);
+  p.bpre = allow_scratch ? activation_scratch(st, static_cast<size_t>(grid.y) * nslabs * kBSlabPitch) : nullptr;
   if (p.bpre != nullptr) {
     convert_activations_kernel<<<dim3(nslabs, grid.y), 256, 0, st>>>(p.a, const_cast<unsigned char*>(p.bpre), p.m, p.k);
     if (int rc = check_launch()) return rc;
@@ -695,7 +696,7 @@ int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st) {
 }
 
 template <int FMT>
-int launch_umma(const UmmaParams& p, cudaStream_t st) {
+int launch_umma(const UmmaParams& p, cudaStream_t st, bool allow_scratch) {
   // the ring wants whole segments (and 16-byte scale rows for MXFP4) and 16-byte aligned weights
   const bool aligned = (reinterpret_cast<uintptr_t>(p.w) & 15u) == 0;
   const bool ring = aligned && (FMT == kFmtQ4K || (FMT == kFmtFp8 && p.k % 128 == 0) ||
@@ -703,28 +704,32 @@ int launch_umma(const UmmaParams& p, cudaStream_t st) {
   RingMaps maps{};
   if (ring && FMT != kFmtQ6K) {
     if (int rc = ring_maps(FMT, p.w, static_cast<uint64_t>(p.n), static_cast<uint64_t>(p.k), &maps)) return rc;
-    return launch_umma_impl<FMT, FMT != kFmtQ6K>(p, maps, st);
+    return launch_umma_impl<FMT, FMT != kFmtQ6K>(p, maps, st, allow_scratch);
   }
-  return launch_umma_impl<FMT, false>(p, maps, st);
+  return launch_umma_impl<FMT, false>(p, maps, st, allow_scratch);
 }
 
 }  // namespace
 
 // fmt: 0 Q4_K, 1 Q6_K, 2 MXFP4 (packed blob||scales), 3 FP8 (+ row scales).
 // Returns kUnsupportedFeature when the shape is outside the tile's range.
+// With allow_scratch false the launch never asks for device memory: the tiles
+// convert the activations themselves instead of reading a pre-converted copy.
 int umma_gemm(int fmt, const float* a, const void* w, const float* scale, float* c, uint64_t m, uint64_t n,
-              uint64_t k, cudaStream_t st) {
+              uint64_t k, cudaStream_t st, bool allow_scratch) {
   if (k % kSlab != 0 || (fmt <= 1 && k % 256 != 0)) return kUnsupportedFeature;
   const UmmaParams p{a, static_cast<const unsigned char*>(w), scale, c, static_cast<int>(m),
                      static_cast<int>(n), static_cast<int>(k), nullptr};
   switch (fmt) {
-    case kFmtQ4K: return launch_umma<kFmtQ4K>(p, st);
-    case kFmtQ6K: return launch_umma<kFmtQ6K>(p, st);
-    case kFmtMxFp4: return launch_umma<kFmtMxFp4>(p, st);
-    case kFmtFp8: return launch_umma<kFmtFp8>(p, st);
+    case kFmtQ4K: return launch_umma<kFmtQ4K>(p, st, allow_scratch);
+    case kFmtQ6K: return launch_umma<kFmtQ6K>(p, st, allow_scratch);
+    case kFmtMxFp4: return launch_umma<kFmtMxFp4>(p, st, allow_scratch);
+    case kFmtFp8: return launch_umma<kFmtFp8>(p, st, allow_scratch);
     default: return kInvalidArgument;
   }
 }
+
+int umma_set_error_word(unsigned int* word) { return set_host_error_word(word); }
 
 int umma_wait_timeouts(unsigned int* count) {
   return cudaMemcpyFromSymbol(count, g_umma_timeouts, sizeof(unsigned int)) == cudaSuccess ? kOk : kDeviceError;

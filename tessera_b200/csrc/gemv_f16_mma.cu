@@ -632,6 +632,8 @@ int staged_gemm_fp8(const float* a, const void* w, const float* scale, float* c,
   return staged_f16<kFmtFp8>(a, w, scale, c, m, n, k, st);
 }
 
+int staged_f16_set_error_word(unsigned int* word) { return set_host_error_word(word); }
+
 int staged_f16_wait_timeouts(unsigned int* count) {
   return cudaMemcpyFromSymbol(count, g_f16_wait_timeouts, sizeof(unsigned int)) == cudaSuccess ? kOk : kDeviceError;
 }

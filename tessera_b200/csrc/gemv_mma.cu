@@ -35,6 +35,7 @@
 #include "launch.h"
 #include "pipeline.cuh"
 #include "staged_common.cuh"
+#include "tp_device.cuh"
 
 namespace tsr {
 
@@ -51,11 +52,18 @@ constexpr int kGroupBytes = 16 * kRowPitch;  // one row group of one stage: 4608
 
 using namespace staged;
 
+struct alignas(64) Q4KMaps {
+  CUtensorMap m[kMaxGroup];
+};
+
 // SETS consumer warp sets (2, or 4 for launches whose warps would otherwise each walk a long
 // chain of chunks on a mostly idle SM: the sets split the chunks of k among them).
+// A CTA works through the tiles blockIdx.x, blockIdx.x + gridDim.x, ... of the launch's tile
+// list, all on split chunk blockIdx.y of k: the activations are staged once, and the weight
+// ring keeps streaming across tile boundaries.
 template <int NCG, int SETS>
 __global__ void __launch_bounds__((SETS * 4 + 1) * 32, SETS == 2 ? 2 : 1)
-gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedParams p) {
+gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const __grid_constant__ StagedParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kConsumerWarps = SETS * p.rgs, kConsumerThreads = kConsumerWarps * 32;
@@ -70,13 +78,16 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
   uint64_t* empty = full + p.stages;
   const unsigned char* zero_page = reinterpret_cast<const unsigned char*>(empty + p.stages);  // 16 zero bytes
-  const int row0 = blockIdx.x * kTileRows;
+  unsigned int* s_words = reinterpret_cast<unsigned int*>(empty + p.stages) + 4;              // [0] flag, [1] epoch
   const int b0 = blockIdx.y * p.per;
+  const int my_tiles = (p.total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                       static_cast<int>(gridDim.x);
+  const int total_chunks = my_tiles * nchunks;
   const bool producer = (tid == kConsumerThreads);
 
   if (tid < 4) reinterpret_cast<uint32_t*>(empty + p.stages)[tid] = 0u;
   if (producer) {
-    tma_prefetch_descriptor(&tmap);
+    for (int g = 0; g < p.ntargets; ++g) tma_prefetch_descriptor(&maps.m[g]);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], p.rgs);
@@ -84,14 +95,20 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
     mbar_fence_init();
   }
   __syncthreads();
+  // chunk j of this CTA's sequence: chunk j % nchunks of its (j / nchunks)-th tile
+  auto issue = [&](int j, int slot) {
+    const int it = j / nchunks, c = j - it * nchunks;
+    const int tile = blockIdx.x + it * gridDim.x;
+    const int g = target_of_tile(p, tile);
+    const int row0 = (tile - p.tgt[g].tile_begin) * kTileRows;
+    unsigned char* dst = smem + static_cast<size_t>(slot) * kStageBytes;
+    mbar_expect_tx(&full[slot], kStageBytes);
+    tma_load_3d(dst, &maps.m[g], 0, b0 + c * kChunkBlocks, row0, &full[slot]);
+  };
   auto prologue = [&]() {
     if (producer) {
-      const int first = nchunks < p.stages ? nchunks : p.stages;
-      for (int c = 0; c < first; ++c) {
-        unsigned char* dst = smem + static_cast<size_t>(c) * kStageBytes;
-        mbar_expect_tx(&full[c], kStageBytes);
-        tma_load_3d(dst, &tmap, 0, b0 + c * kChunkBlocks, row0, &full[c]);
-      }
+      const int first = total_chunks < p.stages ? total_chunks : p.stages;
+      for (int j = 0; j < first; ++j) issue(j, j);
     }
   };
   if (p.pdl) {
@@ -111,24 +128,23 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
     }
     deferred_prologue();
   }
+  if (tid == 0 && p.tp.world > 1) s_words[1] = tp_call_epoch(p.tp);  // the stream's earlier work is complete here
   __syncthreads();
 
   if (warp == kConsumerWarps) {
     if (lane == 0) {
-      for (int c = p.stages; c < nchunks; ++c) {
-        const RingUse use = ring_use(c, p.stages, SETS);
-        const int s = use.slot;
-        if (!mbar_wait(&empty[s], (use.round & 1) ^ 1, &g_wait_timeouts)) break;
-        unsigned char* dst = smem + static_cast<size_t>(s) * kStageBytes;
-        mbar_expect_tx(&full[s], kStageBytes);
-        tma_load_3d(dst, &tmap, 0, b0 + c * kChunkBlocks, row0, &full[s]);
+      for (int j = p.stages; j < total_chunks; ++j) {
+        const RingUse use = ring_use(j, p.stages, SETS);
+        if (!mbar_wait(&empty[use.slot], (use.round & 1) ^ 1, &g_wait_timeouts)) break;
+        issue(j, use.slot);
       }
     }
     return;
   }
 
+  const unsigned int epoch = s_words[1];
   const int gid = lane >> 2, tig = lane & 3;
-  const int bx = warp / p.rgs, rg = warp - bx * p.rgs;  // warp set bx takes chunks c = bx (mod SETS)
+  const int bx = warp / p.rgs, rg = warp - bx * p.rgs;  // warp set bx takes chunks j = bx (mod SETS)
   const int rowA = rg * 16 + gid;
   constexpr uint32_t kNib = 0x0F0F0F0Fu, kHiNib = 0xF0F0F0F0u;
 
@@ -153,134 +169,144 @@ gemv_q4k_staged_kernel(const __grid_constant__ CUtensorMap tmap, const StagedPar
   const float* cs_t = cs + 2 * tig;  // this thread's two columns of a group
   const uint32_t row_off = rowA * kRowPitch;
 
-  float o[NCG][4];
-#pragma unroll
-  for (int g = 0; g < NCG; ++g)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
-
   // this set's ring slots bx, bx + SETS, ... in turn (see ring_use)
   const int owned = (p.stages - bx + SETS - 1) / SETS;
   int ring_idx = 0, ring_round = 0;
-  for (int c = bx; c < nchunks; c += SETS) {
-    const int slot = bx + SETS * ring_idx;
-    if (!mbar_wait(&full[slot], ring_round & 1, &g_wait_timeouts)) break;
-    const unsigned char* st = smem + static_cast<size_t>(slot) * kStageBytes + row_off;
-    const int blocks_here = (p.debug & 2) ? 0 : min(kBoxBlocks, p.per - c * kChunkBlocks);
-#pragma unroll
-    for (int bi = 0; bi < kBoxBlocks; ++bi) {
-      if (bi < blocks_here) {
-        const int bl = c * kChunkBlocks + bi;
-        const unsigned char* pa = st + bi * kQ4KBlockBytes;
-        const unsigned char* pb = pa + 8 * kRowPitch;
-        const uint4 ha = lds128(pa), hb = lds128(pb);
-        // 6-bit scales and mins of the 8 sub-blocks as bytes (quant.cpp:58-70)
-        const uint32_t scA[2] = {ha.y & 0x3F3F3F3Fu, (ha.w & kNib) | ((ha.y >> 2) & 0x30303030u)};
-        const uint32_t mnA[2] = {ha.z & 0x3F3F3F3Fu, ((ha.w >> 4) & kNib) | ((ha.z >> 2) & 0x30303030u)};
-        const uint32_t scB[2] = {hb.y & 0x3F3F3F3Fu, (hb.w & kNib) | ((hb.y >> 2) & 0x30303030u)};
-        const uint32_t mnB[2] = {hb.z & 0x3F3F3F3Fu, ((hb.w >> 4) & kNib) | ((hb.z >> 2) & 0x30303030u)};
-
-        // t1: low-nibble sub-blocks; t16: high-nibble sub-blocks, whose weights enter the MMA
-        // as 16 q (the nibble masked in place, no shift); the 16 is taken out again below
-        int t1[NCG][4], t16[NCG][4];
-#pragma unroll
-        for (int g = 0; g < NCG; ++g)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) t1[g][e] = t16[g][e] = 0;
-
-#pragma unroll
-        for (int grp = 0; grp < 4; ++grp) {
-          const uint2 qa = lds64(pa + 16 + 32 * grp + 8 * tig);
-          const uint2 qb = lds64(pb + 16 + 32 * grp + 8 * tig);
-          const int sclA = __byte_perm(scA[grp >> 1], 0, 0x4440 + 2 * (grp & 1));
-          const int schA = __byte_perm(scA[grp >> 1], 0, 0x4441 + 2 * (grp & 1));
-          const int sclB = __byte_perm(scB[grp >> 1], 0, 0x4440 + 2 * (grp & 1));
-          const int schB = __byte_perm(scB[grp >> 1], 0, 0x4441 + 2 * (grp & 1));
-#pragma unroll
-          for (int g = 0; g < NCG; ++g) {
-            const unsigned char* ab = act_t[g] + bl * act_blk[g];
-            const uint2 fl = lds64(ab + (2 * grp) * act_sb[g]);
-            const uint2 fh = lds64(ab + (2 * grp + 1) * act_sb[g]);
-            int pl[4], ph[4];
-            mma_u8s8_zero(pl, qa.x & kNib, qb.x & kNib, qa.y & kNib, qb.y & kNib, fl.x, fl.y);
-            mma_u8s8_zero(ph, qa.x & kHiNib, qb.x & kHiNib, qa.y & kHiNib, qb.y & kHiNib, fh.x, fh.y);
-            t1[g][0] += sclA * pl[0];
-            t1[g][1] += sclA * pl[1];
-            t1[g][2] += sclB * pl[2];
-            t1[g][3] += sclB * pl[3];
-            t16[g][0] += schA * ph[0];
-            t16[g][1] += schA * ph[1];
-            t16[g][2] += schB * ph[2];
-            t16[g][3] += schB * ph[3];
-          }
-        }
-        // min term: k slots 0..7 are the sub-blocks; lanes tig 0/1 hold mins 0..3 / 4..7
-        const uint32_t am = (mnA[0] & mask0) | (mnA[1] & mask1);
-        const uint32_t bm = (mnB[0] & mask0) | (mnB[1] & mask1);
-        // the sums below are 16 x the block's integer dot product (all of them < 2^31): d / 16 is exact
-        const float dA = fp16_bits_to_float(ha.x & 0xFFFFu) * 0.0625f, mA = fp16_bits_to_float(ha.x >> 16);
-        const float dB = fp16_bits_to_float(hb.x & 0xFFFFu) * 0.0625f, mB = fp16_bits_to_float(hb.x >> 16);
-#pragma unroll
-        for (int g = 0; g < NCG; ++g) {
-          const unsigned char* sp = sum_t[g] + bl * sum_blk[g];
-          const uint32_t s0 = *reinterpret_cast<const uint32_t*>(sp);
-          const uint32_t s1 = *reinterpret_cast<const uint32_t*>(sp + sum_plane[g]);
-          int r0[4], r1[4];
-          mma_u8s8_zero(r0, am, bm, 0u, 0u, s0, 0u);
-          mma_u8s8_zero(r1, am, bm, 0u, 0u, s1, 0u);
-          const float2 c2 = *reinterpret_cast<const float2*>(cs_t + bl * kMaxCols + g * 8);
-          const float u0 = fmaf(dA, static_cast<float>(16 * t1[g][0] + t16[g][0]), -mA * static_cast<float>(r0[0] + 128 * r1[0]));
-          const float u1 = fmaf(dA, static_cast<float>(16 * t1[g][1] + t16[g][1]), -mA * static_cast<float>(r0[1] + 128 * r1[1]));
-          const float u2 = fmaf(dB, static_cast<float>(16 * t1[g][2] + t16[g][2]), -mB * static_cast<float>(r0[2] + 128 * r1[2]));
-          const float u3 = fmaf(dB, static_cast<float>(16 * t1[g][3] + t16[g][3]), -mB * static_cast<float>(r0[3] + 128 * r1[3]));
-          o[g][0] = fmaf(c2.x, u0, o[g][0]);
-          o[g][1] = fmaf(c2.y, u1, o[g][1]);
-          o[g][2] = fmaf(c2.x, u2, o[g][2]);
-          o[g][3] = fmaf(c2.y, u3, o[g][3]);
-        }
-      }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[slot]);
-    if (++ring_idx == owned) {
-      ring_idx = 0;
-      ++ring_round;
-    }
-  }
-
-  // The two warps of a row group (even and odd chunks) add their partial sums; the
-  // digit columns of each activation row are then combined through shared memory.
-  if (bx > 0) {
+  int j = bx;           // next chunk of this set in the CTA's sequence
+  bool failed = false;  // a bounded wait gave up: skip the remaining waits, keep the barriers
+  for (int it = 0; it < my_tiles; ++it) {
+    const int tile = blockIdx.x + it * gridDim.x;
+    const StagedTarget& tg = p.tgt[target_of_tile(p, tile)];
+    const int row0 = (tile - tg.tile_begin) * kTileRows;
+    float o[NCG][4];
 #pragma unroll
     for (int g = 0; g < NCG; ++g)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) xchg[((((bx - 1) * p.rgs + rg) * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
-  }
-  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
-  if (bx == 0) {
+      for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
+
+    const int jbase = it * nchunks, jend = jbase + nchunks;
+    for (; j < jend && !failed; j += SETS) {
+      const int c = j - jbase;
+      const int slot = bx + SETS * ring_idx;
+      if (!mbar_wait(&full[slot], ring_round & 1, &g_wait_timeouts)) {
+        failed = true;
+        break;
+      }
+      const unsigned char* st = smem + static_cast<size_t>(slot) * kStageBytes + row_off;
+      const int blocks_here = (p.debug & 2) ? 0 : min(kBoxBlocks, p.per - c * kChunkBlocks);
 #pragma unroll
-    for (int g = 0; g < NCG; ++g) {
+      for (int bi = 0; bi < kBoxBlocks; ++bi) {
+        if (bi < blocks_here) {
+          const int bl = c * kChunkBlocks + bi;
+          const unsigned char* pa = st + bi * kQ4KBlockBytes;
+          const unsigned char* pb = pa + 8 * kRowPitch;
+          const uint4 ha = lds128(pa), hb = lds128(pb);
+          // 6-bit scales and mins of the 8 sub-blocks as bytes (quant.cpp:58-70)
+          const uint32_t scA[2] = {ha.y & 0x3F3F3F3Fu, (ha.w & kNib) | ((ha.y >> 2) & 0x30303030u)};
+          const uint32_t mnA[2] = {ha.z & 0x3F3F3F3Fu, ((ha.w >> 4) & kNib) | ((ha.z >> 2) & 0x30303030u)};
+          const uint32_t scB[2] = {hb.y & 0x3F3F3F3Fu, (hb.w & kNib) | ((hb.y >> 2) & 0x30303030u)};
+          const uint32_t mnB[2] = {hb.z & 0x3F3F3F3Fu, ((hb.w >> 4) & kNib) | ((hb.z >> 2) & 0x30303030u)};
+
+          // t1: low-nibble sub-blocks; t16: high-nibble sub-blocks, whose weights enter the MMA
+          // as 16 q (the nibble masked in place, no shift); the 16 is taken out again below
+          int t1[NCG][4], t16[NCG][4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int col = g * 8 + 2 * tig + (e & 1);
-        const int rr = rowA + (e >> 1) * 8;
-        float v = o[g][e];
+          for (int g = 0; g < NCG; ++g)
 #pragma unroll
-        for (int sx = 0; sx < SETS - 1; ++sx) v += xchg[(((sx * p.rgs + rg) * 32 + lane) * NCG + g) * 4 + e];
-        if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v;
+            for (int e = 0; e < 4; ++e) t1[g][e] = t16[g][e] = 0;
+
+#pragma unroll
+          for (int grp = 0; grp < 4; ++grp) {
+            const uint2 qa = lds64(pa + 16 + 32 * grp + 8 * tig);
+            const uint2 qb = lds64(pb + 16 + 32 * grp + 8 * tig);
+            const int sclA = __byte_perm(scA[grp >> 1], 0, 0x4440 + 2 * (grp & 1));
+            const int schA = __byte_perm(scA[grp >> 1], 0, 0x4441 + 2 * (grp & 1));
+            const int sclB = __byte_perm(scB[grp >> 1], 0, 0x4440 + 2 * (grp & 1));
+            const int schB = __byte_perm(scB[grp >> 1], 0, 0x4441 + 2 * (grp & 1));
+#pragma unroll
+            for (int g = 0; g < NCG; ++g) {
+              const unsigned char* ab = act_t[g] + bl * act_blk[g];
+              const uint2 fl = lds64(ab + (2 * grp) * act_sb[g]);
+              const uint2 fh = lds64(ab + (2 * grp + 1) * act_sb[g]);
+              int pl[4], ph[4];
+              mma_u8s8_zero(pl, qa.x & kNib, qb.x & kNib, qa.y & kNib, qb.y & kNib, fl.x, fl.y);
+              mma_u8s8_zero(ph, qa.x & kHiNib, qb.x & kHiNib, qa.y & kHiNib, qb.y & kHiNib, fh.x, fh.y);
+              t1[g][0] += sclA * pl[0];
+              t1[g][1] += sclA * pl[1];
+              t1[g][2] += sclB * pl[2];
+              t1[g][3] += sclB * pl[3];
+              t16[g][0] += schA * ph[0];
+              t16[g][1] += schA * ph[1];
+              t16[g][2] += schB * ph[2];
+              t16[g][3] += schB * ph[3];
+            }
+          }
+          // min term: k slots 0..7 are the sub-blocks; lanes tig 0/1 hold mins 0..3 / 4..7
+          const uint32_t am = (mnA[0] & mask0) | (mnA[1] & mask1);
+          const uint32_t bm = (mnB[0] & mask0) | (mnB[1] & mask1);
+          // the sums below are 16 x the block's integer dot product (all of them < 2^31): d / 16 is exact
+          const float dA = fp16_bits_to_float(ha.x & 0xFFFFu) * 0.0625f, mA = fp16_bits_to_float(ha.x >> 16);
+          const float dB = fp16_bits_to_float(hb.x & 0xFFFFu) * 0.0625f, mB = fp16_bits_to_float(hb.x >> 16);
+#pragma unroll
+          for (int g = 0; g < NCG; ++g) {
+            const unsigned char* sp = sum_t[g] + bl * sum_blk[g];
+            const uint32_t s0 = *reinterpret_cast<const uint32_t*>(sp);
+            const uint32_t s1 = *reinterpret_cast<const uint32_t*>(sp + sum_plane[g]);
+            int r0[4], r1[4];
+            mma_u8s8_zero(r0, am, bm, 0u, 0u, s0, 0u);
+            mma_u8s8_zero(r1, am, bm, 0u, 0u, s1, 0u);
+            const float2 c2 = *reinterpret_cast<const float2*>(cs_t + bl * kMaxCols + g * 8);
+            const float u0 = fmaf(dA, static_cast<float>(16 * t1[g][0] + t16[g][0]), -mA * static_cast<float>(r0[0] + 128 * r1[0]));
+            const float u1 = fmaf(dA, static_cast<float>(16 * t1[g][1] + t16[g][1]), -mA * static_cast<float>(r0[1] + 128 * r1[1]));
+            const float u2 = fmaf(dB, static_cast<float>(16 * t1[g][2] + t16[g][2]), -mB * static_cast<float>(r0[2] + 128 * r1[2]));
+            const float u3 = fmaf(dB, static_cast<float>(16 * t1[g][3] + t16[g][3]), -mB * static_cast<float>(r0[3] + 128 * r1[3]));
+            o[g][0] = fmaf(c2.x, u0, o[g][0]);
+            o[g][1] = fmaf(c2.y, u1, o[g][1]);
+            o[g][2] = fmaf(c2.x, u2, o[g][2]);
+            o[g][3] = fmaf(c2.y, u3, o[g][3]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[slot]);
+      if (++ring_idx == owned) {
+        ring_idx = 0;
+        ++ring_round;
       }
     }
-  }
-  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
-  float* cout = p.c + blockIdx.y * p.region_stride;
-  for (int idx = tid; idx < p.m * kTileRows; idx += kConsumerThreads) {
-    const int i = idx / kTileRows, rr = idx - i * kTileRows;
-    if (row0 + rr < p.n) {
-      float v = 0.0f;
-      for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
-      cout[static_cast<size_t>(i) * p.n + row0 + rr] = v;
+
+    // The warps of a row group (one per set) add their partial sums; the digit
+    // columns of each activation row are then combined through shared memory.
+    if (bx > 0) {
+#pragma unroll
+      for (int g = 0; g < NCG; ++g)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) xchg[((((bx - 1) * p.rgs + rg) * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
     }
+    asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
+    if (bx == 0) {
+#pragma unroll
+      for (int g = 0; g < NCG; ++g) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = g * 8 + 2 * tig + (e & 1);
+          const int rr = rowA + (e >> 1) * 8;
+          float v = o[g][e];
+#pragma unroll
+          for (int sx = 0; sx < SETS - 1; ++sx) v += xchg[(((sx * p.rgs + rg) * 32 + lane) * NCG + g) * 4 + e];
+          if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v;
+        }
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
+    finish_tile(p, tg, tile, row0, kTileRows, blockIdx.y, gridDim.y, epoch, tid, kConsumerThreads, s_words,
+                [&](int i, int rr) {
+                  float v = 0.0f;
+                  for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
+                  return v;
+                });
   }
+  if (tid == 0 && p.tp.world > 1) tp_cta_leaves(p.tp, epoch, gridDim.x * gridDim.y);
 }
 
 // ---- tensor-map cache: a map depends only on (base, rows, blocks per row, box rows)
@@ -325,48 +351,91 @@ int env_int(const char* name, int fallback) {
   return v ? std::atoi(v) : fallback;
 }
 
-// With `cost_only` the launch is planned but not issued, and its modelled time returned.
+// Plans and issues one launch with SETS consumer sets; with `cost_only` the launch is planned
+// but not issued, and its modelled time returned.
 template <int NCG, int SETS>
-int launch_staged(const void* w, StagedParams p, uint64_t n, uint64_t nb, uint64_t split,
-                  uint64_t nchunks, cudaStream_t st, double* cost_only) {
-  const uint64_t nblk_pad = nchunks * kChunkBlocks;
-  auto fixed = [&](int rgs) -> size_t {
-    return nblk_pad * p.ncols * (256 + 16) + nblk_pad * kMaxCols * 4 + (SETS - 1) * rgs * 32 * NCG * 4 * 4 +
+int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k, uint64_t caller_split,
+                 const FusedScratch* scratch, const TpTail* tp, cudaStream_t st, double* cost_only) {
+  const uint64_t nb = k / kBlockElems;
+  const int terms = m <= 2 ? 3 : 2;
+  const int ncols = static_cast<int>(m) * terms;
+  auto chunks_of = [](uint64_t per) -> uint64_t { return (per + kChunkBlocks - 1) / kChunkBlocks; };
+  auto fixed = [&](int rgs, uint64_t per) -> size_t {
+    const uint64_t nblk_pad = chunks_of(per) * kChunkBlocks;
+    return nblk_pad * ncols * (256 + 16) + nblk_pad * kMaxCols * 4 + (SETS - 1) * rgs * 32 * NCG * 4 * 4 +
            16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128;
   };
   auto stage_bytes = [](int rgs) -> size_t { return static_cast<size_t>(rgs) * kGroupBytes; };
   static const int regs = kernel_registers(gemv_q4k_staged_kernel<NCG, SETS>);
-  StagedPlan plan;
-  if (!plan_staged(n, split, static_cast<uint64_t>(p.per), nchunks, 12, regs, fixed, stage_bytes, &plan, SETS))
+  uint64_t rows[kMaxGroup];
+  for (int i = 0; i < count; ++i) rows[i] = t[i].n;
+  GroupPlan plan;
+  if (!plan_group(rows, count, nb, caller_split, SETS, regs, 12, fixed, stage_bytes, chunks_of, &plan))
     return kUnsupportedFeature;
   if (cost_only != nullptr) {
     *cost_only = plan.cost;
     return kOk;
   }
-  const int forced_rgs = env_int("TSR_RGS", 0);
-  if (forced_rgs >= 1 && forced_rgs <= 4) {
-    plan.rgs = forced_rgs;
-    plan.smem = fixed(forced_rgs) + plan.stages * stage_bytes(forced_rgs);
-  }
   const int forced = env_int("TSR_STAGES", 0);
   if (forced >= SETS && forced <= 16 &&
-      fixed(plan.rgs) + forced * stage_bytes(plan.rgs) <= static_cast<size_t>(kMaxSmem)) {
+      fixed(plan.rgs, nb / plan.split) + forced * stage_bytes(plan.rgs) <= static_cast<size_t>(kMaxSmem)) {
     plan.stages = forced;
-    plan.smem = fixed(plan.rgs) + forced * stage_bytes(plan.rgs);
+    plan.smem = fixed(plan.rgs, nb / plan.split) + forced * stage_bytes(plan.rgs);
   }
   if (plan.smem > static_cast<size_t>(kMaxSmem)) return kUnsupportedFeature;
+
+  StagedParams p{};
+  p.a = a;
+  p.m = static_cast<int>(m);
+  p.k = static_cast<int>(k);
+  p.per = static_cast<int>(nb / plan.split);
+  p.stages = plan.stages;
+  p.terms = terms;
+  p.ncols = ncols;
+  p.debug = env_int("TSR_DEBUG", 0);
   p.rgs = plan.rgs;
   p.sets = SETS;
-  p.stages = plan.stages;
-  CUtensorMap map;
-  if (int rc = q4k_tensor_map(w, n, nb, plan.rgs, &map)) return rc;
-  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q4k_staged_kernel<NCG, SETS>), kMaxSmem)) return rc;
+  p.ntargets = count;
+  p.split_mode = caller_split != 0 ? kSplitCaller : kSplitInLaunch;
+  Q4KMaps maps{};
   const uint64_t th = 16u * plan.rgs;
-  const dim3 grid(static_cast<unsigned>((n + th - 1) / th), static_cast<unsigned>(split));
-  const size_t w_bytes = n * nb * kQ4KBlockBytes;
-  p.pdl = pdl_allowed(st, w, w_bytes, p.c, split * p.region_stride * 4) ? 1 : 0;
+  uint64_t tiles = 0;
+  const void* reads[kMaxGroup];
+  size_t read_bytes[kMaxGroup];
+  const void* writes[kMaxGroup];
+  size_t write_bytes[kMaxGroup];
+  for (int i = 0; i < count; ++i) {
+    p.tgt[i] = StagedTarget{t[i].c, static_cast<int>(t[i].n), static_cast<int>(tiles), 0};
+    tiles += (t[i].n + th - 1) / th;
+    if (int rc = q4k_tensor_map(t[i].w, t[i].n, nb, plan.rgs, &maps.m[i])) return rc;
+    reads[i] = t[i].w;
+    read_bytes[i] = t[i].n * nb * kQ4KBlockBytes;
+    writes[i] = t[i].c;
+    write_bytes[i] = (caller_split != 0 ? caller_split : 1) * m * t[i].n * 4;
+  }
+  p.total_tiles = static_cast<int>(tiles);
+  if (p.split_mode == kSplitInLaunch && plan.split > 1) {
+    const size_t need = static_cast<size_t>(plan.split) * tiles * m * th;
+    if (scratch == nullptr || scratch->part == nullptr || need > scratch->part_floats || tiles > scratch->ntickets)
+      return kUnsupportedFeature;
+    p.part = scratch->part;
+    p.tickets = scratch->tickets;
+  }
+  if (tp != nullptr && tp->world > 1) {
+    if (tiles > tp->tiles_cap || m * t[0].n > tp->capacity || count != 1 || p.split_mode != kSplitInLaunch)
+      return kUnsupportedFeature;
+    // every CTA of the launch must be resident at once: a tile waits for its peers' flags
+    if (static_cast<uint64_t>(plan.grid_x) * plan.split > static_cast<uint64_t>(device_sms()) * plan.occ)
+      return kUnsupportedFeature;
+    p.tp = *tp;
+  } else {
+    p.tp.world = 1;
+  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q4k_staged_kernel<NCG, SETS>), kMaxSmem)) return rc;
+  const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.split));
+  p.pdl = pdl_allowed_ranges(st, reads, read_bytes, count, writes, write_bytes, count) ? 1 : 0;
   launch_kernel(gemv_q4k_staged_kernel<NCG, SETS>, grid, dim3((SETS * plan.rgs + 1) * 32), plan.smem, st,
-                p.pdl != 0, map, p);
+                p.pdl != 0, maps, p);
   return check_launch();
 }
 
@@ -404,35 +473,40 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType type, uint32_t rank,
   return r == CUDA_SUCCESS ? kOk : kInvalidArgument;
 }
 
-// Returns kUnsupportedFeature when the shape is outside what the staged
+// Returns kUnsupportedFeature when the launch is outside what the staged
 // kernel covers; the caller then uses the general warp-per-row family.
-int staged_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
-                    uint64_t split, cudaStream_t st) {
-  if (m > 8 || env_int("TSR_DISABLE_STAGED", 0)) return kUnsupportedFeature;
-  const uint64_t nb = k / kBlockElems, per = nb / split;
-  const uint64_t nchunks = (per + kChunkBlocks - 1) / kChunkBlocks;
-  const int terms = m <= 2 ? 3 : 2;
-  const int ncols = static_cast<int>(m) * terms;
-  StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
-                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0, 4, 2,
-                 static_cast<unsigned long long>(m * n)};
+// caller_split >= 1: chunk y of k goes to region y of each target (the caller
+// adds the regions); caller_split == 0: the launch splits k as it sees fit and
+// adds the chunks itself (needs `scratch` when it does split).
+int staged_group_q4k(const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k, uint64_t caller_split,
+                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st) {
+  if (m > 8 || count < 1 || count > kMaxGroup || env_int("TSR_DISABLE_STAGED", 0)) return kUnsupportedFeature;
+  const int ncols = static_cast<int>(m) * (m <= 2 ? 3 : 2);
   // two consumer sets, or four when the model says the warps' own chains of chunks
   // (not the SM's throughput) set the time: few CTAs, long k
   auto run = [&](auto ncg) -> int {
     constexpr int kNcg = decltype(ncg)::value;
     double c2 = 0.0, c4 = 0.0;
-    const int r2 = launch_staged<kNcg, 2>(w, p, n, nb, split, nchunks, st, &c2);
-    const int r4 = launch_staged<kNcg, 4>(w, p, n, nb, split, nchunks, st, &c4);
+    const int r2 = launch_group<kNcg, 2>(a, t, count, m, k, caller_split, scratch, tp, st, &c2);
+    const int r4 = launch_group<kNcg, 4>(a, t, count, m, k, caller_split, scratch, tp, st, &c4);
     const int forced_sets = env_int("TSR_SETS", 0);
     const bool four = forced_sets == 4 ? r4 == kOk : forced_sets == 2 ? r2 != kOk && r4 == kOk
-                                                                      : r4 == kOk && (r2 != kOk || (four_sets_worthwhile(n, split) && c4 + 0.3 < c2));
-    if (four) return launch_staged<kNcg, 4>(w, p, n, nb, split, nchunks, st, nullptr);
+                                                                      : r4 == kOk && (r2 != kOk || c4 + 0.3 < c2);
+    if (four) return launch_group<kNcg, 4>(a, t, count, m, k, caller_split, scratch, tp, st, nullptr);
     if (r2 != kOk) return r2;
-    return launch_staged<kNcg, 2>(w, p, n, nb, split, nchunks, st, nullptr);
+    return launch_group<kNcg, 2>(a, t, count, m, k, caller_split, scratch, tp, st, nullptr);
   };
   if (ncols <= 8) return run(std::integral_constant<int, 1>{});
   return run(std::integral_constant<int, 2>{});
 }
+
+int staged_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                    uint64_t split, cudaStream_t st) {
+  const GroupTarget t{w, c, n};
+  return staged_group_q4k(a, &t, 1, m, k, split, nullptr, nullptr, st);
+}
+
+int staged_set_error_word(unsigned int* word) { return set_host_error_word(word); }
 
 int staged_wait_timeouts(unsigned int* count) {
   return cudaMemcpyFromSymbol(count, g_wait_timeouts, sizeof(unsigned int)) == cudaSuccess ? kOk : kDeviceError;

@@ -55,7 +55,11 @@ uint64_t tsr_gemm_q4k_noalloc_max_outputs(void) { return kScratchFloats; }
 
 int tsr_gemm_q4k_noalloc(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
                          void* stream) {
-  if (!a || !w || !c || m == 0 || n == 0 || k == 0 || k % 256 != 0) return tsr::kInvalidArgument;
+  if (!a || !w || !c || m == 0 || n == 0 || k == 0 || k % 256 != 0 || m > 0x7FFFFFFFull ||
+      n > 0x7FFFFFFFull || k > 0x7FFFFFFFull)
+    return tsr::kInvalidArgument;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(c)) & 15u)
+    return tsr::kInvalidArgument;
   const uint64_t outputs = m * n;
   if (outputs > kScratchFloats) return tsr::kInvalidArgument;  // beyond the fixed scratch
   // Largest split of at most 8 that divides the block count and still fits.
@@ -66,7 +70,11 @@ int tsr_gemm_q4k_noalloc(const float* a, const void* w, float* c, uint64_t m, ui
   if (int rc = scratch_for_current_device(&scratch)) return rc;
   // Every element of the regions in use is overwritten by the projection, so
   // nothing has to be cleared between calls.
-  if (int rc = tsr_gemm_q4k(a, w, scratch, m, n, k, split, stream)) return rc;
+  // A batch with no usable split goes straight to c.  Either way no path below
+  // may allocate: the batched tile is told to do without its activation scratch.
+  const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (split == 1) return tsr::gemm_q4k_dispatch(a, w, c, m, n, k, 1, st, false);
+  if (int rc = tsr::gemm_q4k_dispatch(a, w, scratch, m, n, k, split, st, false)) return rc;
   return tsr_gemm_vec_reduce(scratch, c, outputs, split, stream);
 }
 

@@ -35,6 +35,7 @@
 #include "launch.h"
 #include "pipeline.cuh"
 #include "staged_common.cuh"
+#include "tp_device.cuh"
 
 namespace tsr {
 
@@ -165,11 +166,15 @@ __device__ __forceinline__ void q6k_block(const unsigned char* pa, const unsigne
   }
 }
 
+struct alignas(64) Q6KMaps {
+  CUtensorMap even[kMaxGroup], odd[kMaxGroup];
+};
+
+// A CTA works through the tiles blockIdx.x, blockIdx.x + gridDim.x, ... of the launch's tile
+// list, all on split chunk blockIdx.y of k (see gemv_mma.cu).
 template <int NCG>
 __global__ void __launch_bounds__(kThreads, 2)
-gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
-                       const __grid_constant__ CUtensorMap map_odd, const StagedParams p,
-                       const int odd_shift) {
+gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const __grid_constant__ StagedParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kConsumerWarps = 2 * p.rgs, kConsumerThreads = kConsumerWarps * 32;
@@ -182,18 +187,23 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
   uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
   uint64_t* empty = full + p.stages;
   const unsigned char* zero_page = reinterpret_cast<const unsigned char*>(empty + p.stages);  // 16 zero bytes
-  const int row0 = blockIdx.x * kTileRows;
+  unsigned int* s_words = reinterpret_cast<unsigned int*>(empty + p.stages) + 4;              // [0] flag, [1] epoch
   const int b0 = blockIdx.y * p.per;
   // Stages cover block pairs (2j, 2j+1) of the row; pairs that straddle the
   // ends of this CTA's split chunk are loaded whole and half of them skipped.
   const int pair0 = b0 >> 1;
   const int nchunks = ((b0 + p.per + 1) >> 1) - pair0;
+  const int my_tiles = (p.total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                       static_cast<int>(gridDim.x);
+  const int total_chunks = my_tiles * nchunks;
   const bool producer = (tid == kConsumerThreads);
 
   if (tid < 4) reinterpret_cast<uint32_t*>(empty + p.stages)[tid] = 0u;
   if (producer) {
-    tma_prefetch_descriptor(&map_even);
-    tma_prefetch_descriptor(&map_odd);
+    for (int g = 0; g < p.ntargets; ++g) {
+      tma_prefetch_descriptor(&maps.even[g]);
+      tma_prefetch_descriptor(&maps.odd[g]);
+    }
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], p.rgs);
@@ -202,21 +212,27 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
   }
   __syncthreads();
 
-  // Window of chunk c: starts at the 16-byte boundary at or below the pair, in
+  // Chunk j of this CTA's sequence: pair pair0 + j % nchunks of its (j / nchunks)-th tile.
+  // Window of a chunk: starts at the 16-byte boundary at or below the pair, in
   // the byte space of each map (the odd map's base lies odd_shift bytes below
   // the first odd row).  Coordinates are in u64 units and even: 16-byte rule.
-  auto issue_chunk = [&](int c, int slot) {
+  auto issue_chunk = [&](int j, int slot) {
+    const int it = j / nchunks, c = j - it * nchunks;
+    const int tile = blockIdx.x + it * gridDim.x;
+    const int g = target_of_tile(p, tile);
+    const int row0 = (tile - p.tgt[g].tile_begin) * kTileRows;
+    const int odd_shift = p.tgt[g].aux;
     const uint32_t begin = static_cast<uint32_t>(pair0 + c) * kChunkBytes;
     unsigned char* dst = smem + static_cast<size_t>(slot) * kStageBytes;
     mbar_expect_tx(&full[slot], kStageBytes);
-    tma_load_2d(dst, &map_even, static_cast<int>((begin >> 4) * 2), row0 >> 1, &full[slot]);
-    tma_load_2d(dst + kHalfBytes, &map_odd, static_cast<int>(((begin + odd_shift) >> 4) * 2), row0 >> 1,
+    tma_load_2d(dst, &maps.even[g], static_cast<int>((begin >> 4) * 2), row0 >> 1, &full[slot]);
+    tma_load_2d(dst + kHalfBytes, &maps.odd[g], static_cast<int>(((begin + odd_shift) >> 4) * 2), row0 >> 1,
                 &full[slot]);
   };
   auto prologue = [&]() {
     if (producer) {
-      const int first = nchunks < p.stages ? nchunks : p.stages;
-      for (int c = 0; c < first; ++c) issue_chunk(c, c);
+      const int first = total_chunks < p.stages ? total_chunks : p.stages;
+      for (int j = 0; j < first; ++j) issue_chunk(j, j);
     }
   };
   if (p.pdl) {
@@ -236,22 +252,23 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
     }
     deferred_prologue();
   }
+  if (tid == 0 && p.tp.world > 1) s_words[1] = tp_call_epoch(p.tp);  // the stream's earlier work is complete here
   __syncthreads();
 
   if (warp == kConsumerWarps) {
     if (lane == 0) {
-      for (int c = p.stages; c < nchunks; ++c) {
-        const RingUse use = ring_use(c, p.stages);
-        const int s = use.slot;
-        if (!mbar_wait(&empty[s], (use.round & 1) ^ 1, &g_q6k_wait_timeouts)) break;
-        issue_chunk(c, s);
+      for (int j = p.stages; j < total_chunks; ++j) {
+        const RingUse use = ring_use(j, p.stages);
+        if (!mbar_wait(&empty[use.slot], (use.round & 1) ^ 1, &g_q6k_wait_timeouts)) break;
+        issue_chunk(j, use.slot);
       }
     }
     return;
   }
 
+  const unsigned int epoch = s_words[1];
   const int gid = lane >> 2, tig = lane & 3;
-  const int bx = warp >= p.rgs ? 1 : 0, rg = warp - bx * p.rgs;  // warp set bx takes chunks c = bx (mod 2)
+  const int bx = warp >= p.rgs ? 1 : 0, rg = warp - bx * p.rgs;  // warp set bx takes chunks j = bx (mod 2)
   // A warp covers 16 consecutive rows: the thread's MMA rows gid and gid + 8 are
   // the even row 2e and the odd row 2e + 1 of pair e = 8 rg + gid.
   const int pair = rg * 8 + gid;
@@ -269,67 +286,79 @@ gemv_q6k_staged_kernel(const __grid_constant__ CUtensorMap map_even,
     tc[g].sum_blk = tc[g].sum_plane * 2;
   }
   const float* cs_t = cs + 2 * tig;  // this thread's two columns of a group
-  float o[NCG][4];
-#pragma unroll
-  for (int g = 0; g < NCG; ++g)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
 
   // this set's ring slots bx, bx + 2, ... in turn (see ring_use)
   const int owned = (p.stages + 1 - bx) >> 1;
   int ring_idx = 0, ring_round = 0;
-  for (int c = bx; c < nchunks; c += 2) {
-    const int slot = bx + 2 * ring_idx;
-    if (!mbar_wait(&full[slot], ring_round & 1, &g_q6k_wait_timeouts)) break;
-    const uint32_t begin = static_cast<uint32_t>(pair0 + c) * kChunkBytes;
-    const unsigned char* stage = smem + static_cast<size_t>(slot) * kStageBytes + pair * kRowPitch;
-    const unsigned char* sa = stage + (begin & 15u);
-    const unsigned char* sb = stage + kHalfBytes + ((begin + odd_shift) & 15u);
-    const int bl = 2 * (pair0 + c) - b0;  // block index inside the split chunk: -1 for a straddling pair
-    if (!(p.debug & 2)) {
-      if (bl >= 0) q6k_block<false, NCG>(sa, sb, tig, bl, tc, cs_t, o);
-      if (bl + 1 < p.per)
-        q6k_block<true, NCG>(sa + kQ6KBlockBytes, sb + kQ6KBlockBytes, tig, bl + 1, tc, cs_t, o);
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[slot]);
-    if (++ring_idx == owned) {
-      ring_idx = 0;
-      ++ring_round;
-    }
-  }
-
-  // The two warps of a row group (even and odd chunks) add their partial sums; the
-  // digit columns of each activation row are then combined through shared memory.
-  if (bx == 1) {
+  int j = bx;           // next chunk of this set in the CTA's sequence
+  bool failed = false;  // a bounded wait gave up: skip the remaining waits, keep the barriers
+  for (int it = 0; it < my_tiles; ++it) {
+    const int tile = blockIdx.x + it * gridDim.x;
+    const StagedTarget& tg = p.tgt[target_of_tile(p, tile)];
+    const int row0 = (tile - tg.tile_begin) * kTileRows;
+    const int odd_shift = tg.aux;
+    float o[NCG][4];
 #pragma unroll
     for (int g = 0; g < NCG; ++g)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) xchg[((rg * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
-  }
-  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
-  if (bx == 0) {
-#pragma unroll
-    for (int g = 0; g < NCG; ++g) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int col = g * 8 + 2 * tig + (e & 1);
-        const int rr = rowA + (e >> 1);  // MMA row + 8 is the odd row of the pair
-        const float v = o[g][e] + xchg[((rg * 32 + lane) * NCG + g) * 4 + e];
-        if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v;
+      for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
+
+    const int jbase = it * nchunks, jend = jbase + nchunks;
+    for (; j < jend && !failed; j += 2) {
+      const int c = j - jbase;
+      const int slot = bx + 2 * ring_idx;
+      if (!mbar_wait(&full[slot], ring_round & 1, &g_q6k_wait_timeouts)) {
+        failed = true;
+        break;
+      }
+      const uint32_t begin = static_cast<uint32_t>(pair0 + c) * kChunkBytes;
+      const unsigned char* stage = smem + static_cast<size_t>(slot) * kStageBytes + pair * kRowPitch;
+      const unsigned char* sa = stage + (begin & 15u);
+      const unsigned char* sb = stage + kHalfBytes + ((begin + odd_shift) & 15u);
+      const int bl = 2 * (pair0 + c) - b0;  // block index inside the split chunk: -1 for a straddling pair
+      if (!(p.debug & 2)) {
+        if (bl >= 0) q6k_block<false, NCG>(sa, sb, tig, bl, tc, cs_t, o);
+        if (bl + 1 < p.per)
+          q6k_block<true, NCG>(sa + kQ6KBlockBytes, sb + kQ6KBlockBytes, tig, bl + 1, tc, cs_t, o);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[slot]);
+      if (++ring_idx == owned) {
+        ring_idx = 0;
+        ++ring_round;
       }
     }
-  }
-  asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
-  float* cout = p.c + blockIdx.y * p.region_stride;
-  for (int idx = tid; idx < p.m * kTileRows; idx += kConsumerThreads) {
-    const int i = idx / kTileRows, rr = idx - i * kTileRows;
-    if (row0 + rr < p.n) {
-      float v = 0.0f;
-      for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
-      cout[static_cast<size_t>(i) * p.n + row0 + rr] = v;
+
+    // The two warps of a row group (even and odd chunks) add their partial sums; the
+    // digit columns of each activation row are then combined through shared memory.
+    if (bx == 1) {
+#pragma unroll
+      for (int g = 0; g < NCG; ++g)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) xchg[((rg * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
     }
+    asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
+    if (bx == 0) {
+#pragma unroll
+      for (int g = 0; g < NCG; ++g) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = g * 8 + 2 * tig + (e & 1);
+          const int rr = rowA + (e >> 1);  // MMA row + 8 is the odd row of the pair
+          const float v = o[g][e] + xchg[((rg * 32 + lane) * NCG + g) * 4 + e];
+          if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v;
+        }
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
+    finish_tile(p, tg, tile, row0, kTileRows, blockIdx.y, gridDim.y, epoch, tid, kConsumerThreads, s_words,
+                [&](int i, int rr) {
+                  float v = 0.0f;
+                  for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
+                  return v;
+                });
   }
+  if (tid == 0 && p.tp.world > 1) tp_cta_leaves(p.tp, epoch, gridDim.x * gridDim.y);
 }
 
 // ---- tensor-map cache: the pair of maps depends only on (base, rows, blocks per row, box rows)
@@ -385,64 +414,113 @@ int env_int(const char* name, int fallback) {
 }
 
 template <int NCG>
-int launch_q6k(const void* w, StagedParams p, int odd_shift, uint64_t n, uint64_t nb, uint64_t split,
-               cudaStream_t st) {
-  const size_t per = static_cast<size_t>(p.per);
-  auto fixed = [&](int rgs) -> size_t {
-    return per * p.ncols * (256 + 2 * kGroups) + per * kMaxCols * 4 + rgs * 32 * NCG * 4 * 4 +
+int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k, uint64_t caller_split,
+                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st) {
+  const uint64_t nb = k / kBlockElems;
+  const int terms = m <= 2 ? 3 : 2;
+  const int ncols = static_cast<int>(m) * terms;
+  auto fixed = [&](int rgs, uint64_t per) -> size_t {
+    return per * ncols * (256 + 2 * kGroups) + per * kMaxCols * 4 + rgs * 32 * NCG * 4 * 4 +
            16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128;
   };
   auto stage_bytes = [](int rgs) -> size_t { return static_cast<size_t>(rgs) * 2 * kGroupHalfBytes; };
+  auto chunks_of = [](uint64_t per) -> uint64_t { return per / 2 + 1; };
   static const int regs = kernel_registers(gemv_q6k_staged_kernel<NCG>);
-  StagedPlan plan;
-  if (!plan_staged(n, split, per, per / 2 + 1, 8, regs, fixed, stage_bytes, &plan)) return kUnsupportedFeature;
-  const int forced_rgs = env_int("TSR_RGS", 0);
-  if (forced_rgs >= 1 && forced_rgs <= 4) {
-    plan.rgs = forced_rgs;
-    plan.smem = fixed(forced_rgs) + plan.stages * stage_bytes(forced_rgs);
-  }
+  uint64_t rows[kMaxGroup];
+  for (int i = 0; i < count; ++i) rows[i] = t[i].n;
+  GroupPlan plan;
+  if (!plan_group(rows, count, nb, caller_split, 2, regs, 8, fixed, stage_bytes, chunks_of, &plan))
+    return kUnsupportedFeature;
   const int forced = env_int("TSR_STAGES", 0);
   if (forced >= 2 && forced <= 16 &&
-      fixed(plan.rgs) + forced * stage_bytes(plan.rgs) <= static_cast<size_t>(kMaxSmem)) {
+      fixed(plan.rgs, nb / plan.split) + forced * stage_bytes(plan.rgs) <= static_cast<size_t>(kMaxSmem)) {
     plan.stages = forced;
-    plan.smem = fixed(plan.rgs) + forced * stage_bytes(plan.rgs);
+    plan.smem = fixed(plan.rgs, nb / plan.split) + forced * stage_bytes(plan.rgs);
   }
   if (plan.smem > static_cast<size_t>(kMaxSmem)) return kUnsupportedFeature;
-  p.rgs = plan.rgs;
+
+  StagedParams p{};
+  p.a = a;
+  p.m = static_cast<int>(m);
+  p.k = static_cast<int>(k);
+  p.per = static_cast<int>(nb / plan.split);
   p.stages = plan.stages;
-  MapPair maps;
-  if (int rc = q6k_tensor_maps(w, n, nb, plan.rgs, &maps)) return rc;
-  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q6k_staged_kernel<NCG>), kMaxSmem)) return rc;
+  p.terms = terms;
+  p.ncols = ncols;
+  p.debug = env_int("TSR_DEBUG", 0);
+  p.rgs = plan.rgs;
+  p.sets = 2;
+  p.ntargets = count;
+  p.split_mode = caller_split != 0 ? kSplitCaller : kSplitInLaunch;
+  Q6KMaps maps{};
   const uint64_t th = 16u * plan.rgs;
-  const dim3 grid(static_cast<unsigned>((n + th - 1) / th), static_cast<unsigned>(split));
-  const size_t w_bytes = n * nb * kQ6KBlockBytes;
-  p.pdl = pdl_allowed(st, w, w_bytes, p.c, split * p.region_stride * 4) ? 1 : 0;
-  launch_kernel(gemv_q6k_staged_kernel<NCG>, grid, dim3((2 * plan.rgs + 1) * 32), plan.smem, st,
-                p.pdl != 0, maps.even, maps.odd, p, odd_shift);
+  const int odd_shift = static_cast<int>((nb * kQ6KBlockBytes) & 15u);
+  uint64_t tiles = 0;
+  const void* reads[kMaxGroup];
+  size_t read_bytes[kMaxGroup];
+  const void* writes[kMaxGroup];
+  size_t write_bytes[kMaxGroup];
+  for (int i = 0; i < count; ++i) {
+    p.tgt[i] = StagedTarget{t[i].c, static_cast<int>(t[i].n), static_cast<int>(tiles), odd_shift};
+    tiles += (t[i].n + th - 1) / th;
+    MapPair pair;
+    if (int rc = q6k_tensor_maps(t[i].w, t[i].n, nb, plan.rgs, &pair)) return rc;
+    maps.even[i] = pair.even;
+    maps.odd[i] = pair.odd;
+    reads[i] = t[i].w;
+    read_bytes[i] = t[i].n * nb * kQ6KBlockBytes;
+    writes[i] = t[i].c;
+    write_bytes[i] = (caller_split != 0 ? caller_split : 1) * m * t[i].n * 4;
+  }
+  p.total_tiles = static_cast<int>(tiles);
+  if (p.split_mode == kSplitInLaunch && plan.split > 1) {
+    const size_t need = static_cast<size_t>(plan.split) * tiles * m * th;
+    if (scratch == nullptr || scratch->part == nullptr || need > scratch->part_floats || tiles > scratch->ntickets)
+      return kUnsupportedFeature;
+    p.part = scratch->part;
+    p.tickets = scratch->tickets;
+  }
+  if (tp != nullptr && tp->world > 1) {
+    if (tiles > tp->tiles_cap || m * t[0].n > tp->capacity || count != 1 || p.split_mode != kSplitInLaunch)
+      return kUnsupportedFeature;
+    // every CTA of the launch must be resident at once: a tile waits for its peers' flags
+    if (static_cast<uint64_t>(plan.grid_x) * plan.split > static_cast<uint64_t>(device_sms()) * plan.occ)
+      return kUnsupportedFeature;
+    p.tp = *tp;
+  } else {
+    p.tp.world = 1;
+  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q6k_staged_kernel<NCG>), kMaxSmem)) return rc;
+  const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.split));
+  p.pdl = pdl_allowed_ranges(st, reads, read_bytes, count, writes, write_bytes, count) ? 1 : 0;
+  launch_kernel(gemv_q6k_staged_kernel<NCG>, grid, dim3((2 * plan.rgs + 1) * 32), plan.smem, st, p.pdl != 0, maps, p);
   return check_launch();
 }
 
 }  // namespace
 
-// Returns kUnsupportedFeature when the shape is outside what the staged
+// Returns kUnsupportedFeature when the launch is outside what the staged
 // kernel covers; the caller then uses the general warp-per-row family.
+int staged_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k, uint64_t caller_split,
+                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st) {
+  const uint64_t nb = k / kBlockElems;
+  if (m > 8 || count < 1 || count > kMaxGroup || nb % 4 != 0 || env_int("TSR_DISABLE_STAGED", 0))
+    return kUnsupportedFeature;
+  // Rows must be 8-byte aligned inside a 16-byte aligned matrix, and there must be an odd row.
+  for (int i = 0; i < count; ++i)
+    if (t[i].n < 2 || (reinterpret_cast<uintptr_t>(t[i].w) & 15u)) return kUnsupportedFeature;
+  const int ncols = static_cast<int>(m) * (m <= 2 ? 3 : 2);
+  if (ncols <= 8) return launch_group_q6k<1>(a, t, count, m, k, caller_split, scratch, tp, st);
+  return launch_group_q6k<2>(a, t, count, m, k, caller_split, scratch, tp, st);
+}
+
 int staged_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
                     uint64_t split, cudaStream_t st) {
-  const uint64_t nb = k / kBlockElems;
-  // Rows must be 8-byte aligned inside a 16-byte aligned matrix, and there must be an odd row.
-  if (m > 8 || n < 2 || nb % 4 != 0 || (reinterpret_cast<uintptr_t>(w) & 15u) ||
-      env_int("TSR_DISABLE_STAGED", 0))
-    return kUnsupportedFeature;
-  const uint64_t per = nb / split;
-  const int terms = m <= 2 ? 3 : 2;
-  const int ncols = static_cast<int>(m) * terms;
-  StagedParams p{a, c, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k),
-                 static_cast<int>(per), 0, terms, ncols, env_int("TSR_DEBUG", 0), 0, 4, 2,
-                 static_cast<unsigned long long>(m * n)};
-  const int odd_shift = static_cast<int>((nb * kQ6KBlockBytes) & 15u);
-  if (ncols <= 8) return launch_q6k<1>(w, p, odd_shift, n, nb, split, st);
-  return launch_q6k<2>(w, p, odd_shift, n, nb, split, st);
+  const GroupTarget t{w, c, n};
+  return staged_group_q6k(a, &t, 1, m, k, split, nullptr, nullptr, st);
 }
+
+int staged_q6k_set_error_word(unsigned int* word) { return set_host_error_word(word); }
 
 int staged_q6k_wait_timeouts(unsigned int* count) {
   return cudaMemcpyFromSymbol(count, g_q6k_wait_timeouts, sizeof(unsigned int)) == cudaSuccess ? kOk : kDeviceError;

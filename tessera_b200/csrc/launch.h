@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace tsr {
 
 // Status values equal tessera::StatusCode (include/tessera/types.hpp:38-48).
@@ -13,8 +15,16 @@ constexpr int kUnsupportedFeature = 4;
 constexpr int kOutOfMemory = 5;
 constexpr int kDeviceError = 6;
 
+// Kernel launches this library has issued in this process (every launcher ends with
+// check_launch(), which counts); a captured graph replays as many as were captured.
+inline std::atomic<uint64_t>& launch_counter() {
+  static std::atomic<uint64_t> count{0};
+  return count;
+}
+
 // Maps the pending launch error (cudaGetLastError) to a status.
 inline int check_launch() {
+  launch_counter().fetch_add(1, std::memory_order_relaxed);
   const cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) return kOk;
   if (e == cudaErrorMemoryAllocation) return kOutOfMemory;
@@ -83,11 +93,57 @@ inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, di
 // several GPUs (the reference runs its tensor-parallel ranks as threads).
 int allow_dynamic_smem(const void* kernel, int bytes);
 
+// Multi-range form of pdl_allowed (a launch over several weight tensors): true when none of the
+// `reads` ranges overlaps a range the previous launch of this library on `stream` wrote; records
+// `writes` (up to four ranges) as what this launch writes.
+// Invariant the staged kernels rely on: before its pdl_wait() a kernel reads weight bytes only, and
+// a weight range is only ever written by a copy (a stream-ordered memcpy is never overlapped) or by
+// a launch of this library that registers its output here.  A foreign kernel that writes weights
+// must be followed by a stream synchronisation or by a launch without the programmatic attribute.
+bool pdl_allowed_ranges(cudaStream_t stream, const void* const* reads, const size_t* read_bytes, int nreads,
+                        const void* const* writes, const size_t* write_bytes, int nwrites);
+
 // True when a kernel that reads [read_ptr, +read_bytes) before its pdl_wait()
 // may overlap the previous launch on `stream`; records [out_ptr, +out_bytes) as
 // the range this launch writes.
 bool pdl_allowed(cudaStream_t stream, const void* read_ptr, size_t read_bytes, const void* out_ptr,
                  size_t out_bytes);
+
+// ---- tensor-parallel tail and multi-target launches ---------------------------
+constexpr int kMaxWorld = 8;
+constexpr int kMaxGroup = 4;  // weight tensors one staged launch can serve
+// What a kernel needs to finish with the sum over tensor-parallel ranks
+// (tp_device.cuh explains the protocol and the memory behind the pointers).
+struct TpTail {
+  int world;  // 1: no collective
+  int rank;
+  unsigned int tiles_cap;
+  unsigned long long capacity;     // floats per slot
+  float* slots[kMaxWorld];         // slot memory of every rank (this rank's own included)
+  unsigned int* flags[kMaxWorld];  // flag arrays of every rank
+  unsigned int* state;             // this rank's state words
+};
+// One weight tensor of a multi-target launch: C[m, n] = A . dq(W)^T.
+struct GroupTarget {
+  const void* w;
+  float* c;
+  uint64_t n;
+};
+// Device scratch of a context for launches that split k among CTAs and add the
+// chunks themselves: partial tiles and one arrival counter per tile (zero at rest).
+struct FusedScratch {
+  float* part;
+  size_t part_floats;
+  unsigned int* tickets;
+  size_t ntickets;
+};
+// Multi-target staged launches (gemv_mma.cu, gemv_q6k_mma.cu): up to four weight tensors that
+// share a, m and k.  caller_split >= 1: chunk y of k goes to region y of each target;
+// caller_split == 0: the launch picks its own split and adds the chunks (and, with `tp`, the ranks).
+int staged_group_q4k(const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k, uint64_t caller_split,
+                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st);
+int staged_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k, uint64_t caller_split,
+                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st);
 
 // General warp-per-row family (gemv_rows.cu).
 int rows_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
@@ -119,7 +175,16 @@ int staged_f16_wait_timeouts(unsigned int* count);
 // tcgen05/TMEM tile for small batches (gemm_umma.cu).  fmt: 0 Q4_K, 1 Q6_K,
 // 2 MXFP4, 3 FP8.  kUnsupportedFeature when the shape is outside its range.
 int umma_gemm(int fmt, const float* a, const void* w, const float* scale, float* c, uint64_t m,
-              uint64_t n, uint64_t k, cudaStream_t st);
+              uint64_t n, uint64_t k, cudaStream_t st, bool allow_scratch = true);
+// What tsr_gemm_q4k runs after its argument checks.  allow_scratch false keeps every path
+// away from device allocations (the allocation-free entry point uses it).
+int gemm_q4k_dispatch(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                      uint64_t split, cudaStream_t st, bool allow_scratch);
 int umma_wait_timeouts(unsigned int* count);
+// Point the kernels of each file at the host-visible error word (see pipeline.cuh); once per device.
+int staged_set_error_word(unsigned int* word);
+int staged_q6k_set_error_word(unsigned int* word);
+int staged_f16_set_error_word(unsigned int* word);
+int umma_set_error_word(unsigned int* word);
 
 }  // namespace tsr

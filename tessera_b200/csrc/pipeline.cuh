@@ -46,11 +46,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Host-visible error word (pinned, mapped memory shared by every kernel file of the
+// library): a wait that gives up also raises it, so the host learns of a failure by
+// reading one word of its own memory instead of copying counters back from the device.
+// Each translation unit holds its own copy of the pointer, set per device by
+// set_host_error_word() of that unit.
+static __device__ unsigned int* g_host_error_word = nullptr;
+static inline int set_host_error_word(unsigned int* word) {
+  return cudaMemcpyToSymbol(g_host_error_word, &word, sizeof(word)) == cudaSuccess ? 0 : 6;
+}
+
 // Returns false when the wait gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* timeouts) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
     if (mbar_try_wait(bar, parity)) return true;
   atomicAdd(timeouts, 1u);
+  if (g_host_error_word != nullptr) *reinterpret_cast<volatile unsigned int*>(g_host_error_word) = 1u;
   return false;
 }
 

@@ -8,9 +8,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+
 #include "codec.cuh"
 #include "launch.h"
 #include "pipeline.cuh"
+#include "tp_device.cuh"
 
 namespace tsr {
 namespace staged {
@@ -20,10 +23,24 @@ constexpr int kStagedThreads = kStagedConsumerWarps * 32 + 32;  // plus the prod
 constexpr int kMaxSmem = 227 * 1024;
 constexpr int kMaxCols = 16;
 
+// One weight tensor of a launch.  All targets of a launch share the activations,
+// m, k, the split and the tile height; the launch's tile list is the
+// concatenation of the targets' row tiles.
+struct StagedTarget {
+  float* c;        // [m][n] outputs (or `split` such regions when the split is left to the caller)
+  int n;           // weight rows
+  int tile_begin;  // index of this target's first tile in the launch's tile list
+  int aux;         // format specific (Q6_K: byte shift of the odd-row tensor map)
+};
+
+enum : int {
+  kSplitCaller = 0,    // chunk y of k goes to region y of each target (stride m*n): the caller adds them
+  kSplitInLaunch = 1,  // the last CTA of a tile to finish adds the chunks in chunk order
+};
+
 struct StagedParams {
   const float* a;
-  float* c;
-  int m, n, k;
+  int m, k;
   int per;     // blocks per split chunk
   int stages;  // ring depth
   int terms;   // int8 digits per activation row
@@ -32,8 +49,23 @@ struct StagedParams {
   int pdl;     // launched as a programmatic dependent: prefetch weights, then wait for the stream
   int rgs;     // 16-row groups per CTA (1..4): the tile has 16*rgs rows
   int sets;    // consumer warp sets (2 or 4): sets*rgs consumer warps; set s takes the chunks c = s (mod sets)
-  unsigned long long region_stride;
+  int ntargets, total_tiles;
+  int split_mode;
+  StagedTarget tgt[kMaxGroup];
+  // kSplitInLaunch: partial tiles [chunk][tile][m][tile rows] and one arrival count per tile (zero at rest)
+  float* part;
+  unsigned int* tickets;
+  TpTail tp;  // sum over tensor-parallel ranks after the local sum (world 1: none)
 };
+
+// Which target a tile of the launch's tile list belongs to.
+__device__ __forceinline__ int target_of_tile(const StagedParams& p, int tile) {
+  int g = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxGroup; ++i)
+    if (i < p.ntargets && tile >= p.tgt[i].tile_begin) g = i;
+  return g;
+}
 
 __device__ __forceinline__ uint4 lds128(const unsigned char* p) {
   return *reinterpret_cast<const uint4*>(p);
@@ -222,6 +254,105 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
   }
 }
 
+// What the consumer threads of a CTA do once a tile's sums sit in shared memory
+// (`value(i, rr)` returns the sum of activation row i and tile row rr): write
+// them out, or first add the split chunks of k (kSplitInLaunch) and then the
+// tensor-parallel ranks.  Every consumer thread of the CTA calls this with the
+// same arguments; it synchronises them on named barrier 1.  s_flag is one word
+// of shared memory.  Returns nothing; a CTA that was not the last of its tile
+// simply leaves without writing outputs.
+template <typename ValueFn>
+__device__ __forceinline__ void finish_tile(const StagedParams& p, const StagedTarget& tg, int tile, int row0,
+                                            int tile_rows, int chunk_y, int nsplit, unsigned int epoch, int tid,
+                                            int nthreads, unsigned int* s_flag, ValueFn value) {
+  const int items = p.m * tile_rows;
+  if (p.split_mode == kSplitCaller) {
+    float* cout = tg.c + static_cast<size_t>(chunk_y) * p.m * tg.n;
+    for (int idx = tid; idx < items; idx += nthreads) {
+      const int i = idx / tile_rows, rr = idx - i * tile_rows;
+      if (row0 + rr < tg.n) cout[static_cast<size_t>(i) * tg.n + row0 + rr] = value(i, rr);
+    }
+    return;
+  }
+  // items <= 8 * 64 and nthreads >= 64: at most eight values per thread
+  constexpr int kMaxPer = 8;
+  float v[kMaxPer];
+#pragma unroll
+  for (int u = 0; u < kMaxPer; ++u) {
+    const int idx = tid + u * nthreads;
+    v[u] = 0.0f;
+    if (idx < items) {
+      const int i = idx / tile_rows, rr = idx - i * tile_rows;
+      v[u] = value(i, rr);
+    }
+  }
+  if (nsplit > 1) {
+    const size_t tile_floats = static_cast<size_t>(items);
+    float* mine = p.part + (static_cast<size_t>(chunk_y) * p.total_tiles + tile) * tile_floats;
+#pragma unroll
+    for (int u = 0; u < kMaxPer; ++u) {
+      const int idx = tid + u * nthreads;
+      if (idx < items) __stcg(mine + idx, v[u]);
+    }
+    __threadfence();
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    if (tid == 0) {
+      const unsigned int t = atomicAdd(p.tickets + tile, 1u);
+      *s_flag = (t == static_cast<unsigned int>(nsplit - 1)) ? 1u : 0u;
+      if (*s_flag) p.tickets[tile] = 0u;  // every chunk has arrived: ready for the next launch
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    if (*s_flag == 0u) return;
+    __threadfence();
+    // chunk order, starting from zero: the order of the reference's gemm_vec_reduce
+    const float* base = p.part + static_cast<size_t>(tile) * tile_floats;
+#pragma unroll
+    for (int u = 0; u < kMaxPer; ++u) {
+      const int idx = tid + u * nthreads;
+      if (idx < items) {
+        float acc = 0.0f;
+        for (int y = 0; y < nsplit; ++y) acc += __ldcg(base + static_cast<size_t>(y) * p.total_tiles * tile_floats + idx);
+        v[u] = acc;
+      }
+    }
+  }
+  if (p.tp.world > 1) {
+    const size_t mine = tp_slot_offset(p.tp, epoch, p.tp.rank);
+#pragma unroll
+    for (int u = 0; u < kMaxPer; ++u) {
+      const int idx = tid + u * nthreads;
+      if (idx < items) {
+        const int i = idx / tile_rows, rr = idx - i * tile_rows;
+        if (row0 + rr < tg.n) {
+          const size_t e = static_cast<size_t>(i) * tg.n + row0 + rr;
+          for (int r = 0; r < p.tp.world; ++r) p.tp.slots[r][mine + e] = v[u];
+        }
+      }
+    }
+    tp_publish_and_wait(p.tp, epoch, tile, tid, 1, nthreads);
+#pragma unroll
+    for (int u = 0; u < kMaxPer; ++u) {
+      const int idx = tid + u * nthreads;
+      if (idx < items) {
+        const int i = idx / tile_rows, rr = idx - i * tile_rows;
+        if (row0 + rr < tg.n) {
+          const size_t e = static_cast<size_t>(i) * tg.n + row0 + rr;
+          tg.c[e] = tp_rank_order_sum(p.tp, epoch, e);
+        }
+      }
+    }
+    return;
+  }
+#pragma unroll
+  for (int u = 0; u < kMaxPer; ++u) {
+    const int idx = tid + u * nthreads;
+    if (idx < items) {
+      const int i = idx / tile_rows, rr = idx - i * tile_rows;
+      if (row0 + rr < tg.n) tg.c[static_cast<size_t>(i) * tg.n + row0 + rr] = v[u];
+    }
+  }
+}
+
 // ---- host side: tile height and ring depth for one launch
 struct StagedPlan {
   int rgs;     // row groups per CTA
@@ -292,6 +423,95 @@ inline bool plan_staged(uint64_t n, uint64_t split, uint64_t per, uint64_t nchun
         out->smem = fx + static_cast<size_t>(depth) * sb;
         out->cost = cost;
         found = true;
+      }
+    }
+  }
+  return found;
+}
+
+// ---- launch plan of the multi-target kernels (Q4_K, Q6_K)
+struct GroupPlan {
+  int rgs, stages, sets, split, grid_x, occ;
+  size_t smem;
+  double cost;  // modelled microseconds
+};
+
+inline int env_plan_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  return v ? std::atoi(v) : fallback;
+}
+
+// Picks the tile height, the CTAs per SM, the ring depth and (when the split is
+// the launch's own business, fixed_split == 0) the number of k chunks for a
+// launch over `count` weight tensors of n[i] rows and nb blocks per row.  The
+// grid is never larger than the SMs can hold at once: a CTA works through
+// several tiles instead, so the activation staging is paid once per CTA.
+//   fixed(rgs, per)   shared memory besides the ring, in bytes, for `per` blocks per chunk
+//   stage_bytes(rgs)  one ring stage
+//   nchunks(per)      ring stages one tile of `per` blocks needs
+template <typename FixedFn, typename StageFn, typename ChunksFn>
+inline bool plan_group(const uint64_t* n, int count, uint64_t nb, uint64_t fixed_split, int sets,
+                       int regs_per_thread, int max_want, FixedFn fixed, StageFn stage_bytes, ChunksFn nchunks,
+                       GroupPlan* out) {
+  const int sms = device_sms();
+  // per 16 rows x 1 block on a busy SM; per block of one warp's own chunks; per CTA
+  const double kUnitUs = 0.04, kWarpBlockUs = 0.5, kPrefixUs = 3.0, kStageBlockUs = 0.02, kTicketUs = 1.2;
+  const int ring_max = env_plan_int("TSR_RING_MAX", max_want);
+  const int force_rgs = env_plan_int("TSR_RGS", 0), force_split = env_plan_int("TSR_SPLIT", 0);
+  const int force_grid = env_plan_int("TSR_GRID", 0), force_occ = env_plan_int("TSR_OCC", 0);
+  double best = 1e30;
+  bool found = false;
+  for (uint64_t split = 1; split <= 8 && split <= nb; ++split) {
+    if (fixed_split != 0 && split != fixed_split) continue;
+    if (fixed_split == 0 && force_split > 0 && split != static_cast<uint64_t>(force_split)) continue;
+    if (nb % split != 0) continue;
+    const uint64_t per = nb / split;
+    const uint64_t chunks_per_tile = nchunks(per);
+    for (int rgs = 4; rgs >= 1; --rgs) {
+      if (force_rgs >= 1 && force_rgs <= 4 && rgs != force_rgs) continue;
+      const uint64_t th = 16u * rgs;
+      uint64_t tiles = 0;
+      for (int i = 0; i < count; ++i) tiles += (n[i] + th - 1) / th;
+      const size_t fx = fixed(rgs, per), sb = stage_bytes(rgs);
+      for (int occ = 1; occ <= 4; ++occ) {
+        if (force_occ > 0 && occ != force_occ) continue;
+        if (occ > 1 && occ * (sets * rgs + 1) * 32 * regs_per_thread > 65536) break;  // register file
+        if (occ > 1 && sets == 4) break;  // the four-set kernels are built for one CTA per SM
+        const size_t avail = static_cast<size_t>(kMaxSmem) / occ;
+        const size_t reserve = occ > 1 ? 1024 : 0;  // per-CTA reservation of the hardware
+        if (avail < fx + reserve + sets * sb) break;  // every consumer set owns at least one slot
+        const uint64_t slots = static_cast<uint64_t>(sms) * occ;
+        uint64_t grid_x = slots / split;
+        if (grid_x == 0) grid_x = 1;
+        if (grid_x > tiles) grid_x = tiles;
+        if (force_grid > 0) grid_x = static_cast<uint64_t>(force_grid) < tiles ? force_grid : tiles;
+        const uint64_t tiles_per_cta = (tiles + grid_x - 1) / grid_x;
+        const uint64_t total_chunks = tiles_per_cta * chunks_per_tile;
+        int depth = static_cast<int>((avail - reserve - fx) / sb);
+        int want = static_cast<int>(total_chunks < static_cast<uint64_t>(ring_max) ? total_chunks : ring_max);
+        if (want < sets) want = sets;
+        if (depth > want) depth = want;
+        const uint64_t ctas = grid_x * split;
+        const uint64_t ctas_per_sm = (ctas + sms - 1) / sms;
+        // an SM works through its CTAs' tiles at a fixed rate, but a warp cannot go faster
+        // than its own share of the blocks (one consumer set's) one after the other
+        const double throughput = static_cast<double>(ctas_per_sm * tiles_per_cta * rgs * per) * kUnitUs;
+        const double latency = static_cast<double>(tiles_per_cta) * (static_cast<double>(per) / sets) * kWarpBlockUs;
+        double cost = kPrefixUs + kStageBlockUs * per + (throughput > latency ? throughput : latency) +
+                      (split > 1 && fixed_split == 0 ? kTicketUs : 0.0);
+        if (depth < sets + 1 && total_chunks > static_cast<uint64_t>(sets)) cost *= 1.1;  // a shallow ring stalls on HBM latency
+        if (cost < best - 1e-9) {
+          best = cost;
+          out->rgs = rgs;
+          out->stages = depth;
+          out->sets = sets;
+          out->split = static_cast<int>(split);
+          out->grid_x = static_cast<int>(grid_x);
+          out->occ = occ;
+          out->smem = fx + static_cast<size_t>(depth) * sb;
+          out->cost = cost;
+          found = true;
+        }
       }
     }
   }

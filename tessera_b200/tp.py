@@ -70,6 +70,31 @@ class TpComm:
             self.comm = None
 
 
+FMT_Q4K, FMT_Q6K, FMT_MXFP4, FMT_FP8 = 0, 1, 2, 3
+REPLICATED, COLUMN, ROW = 0, 1, 2  # the reference's ParallelKind (include/tessera/types.hpp:29-34)
+
+
+def slice_shape(fmt: int, kind: int, rows: int, cols: int, rank: int, world: int):
+    """(rows, cols, first kept column, bytes) of a rank's slice (tsr_slice_shape)."""
+    lib = capi.load_library()
+    r, c, c0, b = C.c_uint64(), C.c_uint64(), C.c_uint64(), C.c_uint64()
+    capi.check(lib.tsr_slice_shape(fmt, kind, rows, cols, rank, world, C.byref(r), C.byref(c), C.byref(c0),
+                                   C.byref(b)), "tsr_slice_shape")
+    return r.value, c.value, c0.value, b.value
+
+
+def slice_tensor(fmt: int, kind: int, rows: int, cols: int, rank: int, world: int, src: np.ndarray) -> np.ndarray:
+    """A rank's slice of a packed weight tensor (uint8 array), as SliceTensor2D of the reference
+    cuts it (src/core/loaders/tensor_slice.cpp:105-159), through the C ABI's tsr_slice_tensor."""
+    lib = capi.load_library()
+    src = np.ascontiguousarray(src.reshape(-1).view(np.uint8))
+    _, _, _, nbytes = slice_shape(fmt, kind, rows, cols, rank, world)
+    dst = np.empty(nbytes, dtype=np.uint8)
+    capi.check(lib.tsr_slice_tensor(fmt, kind, rows, cols, rank, world, src.ctypes.data, src.nbytes,
+                                    dst.ctypes.data, dst.nbytes), "tsr_slice_tensor")
+    return dst
+
+
 def rank_order_sum(partials):
     """What every rank must end with: ((p0 + p1) + p2) + ... in fp32."""
     acc = np.array(partials[0], dtype=np.float32, copy=True)

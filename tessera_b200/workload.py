@@ -78,17 +78,17 @@ def decode_projections() -> List[Projection]:
 
 
 def shard(p: Projection, rank: int, world: int):
-    """(n_local, k_local) of this rank.  Column: contiguous row range.  Row: a
-    contiguous range of 256-element blocks; when the block count does not
-    divide evenly the first (blocks % world) ranks take one block more."""
+    """(n_local, k_local) of this rank, by the rule of the library's slicer
+    (tsr_slice_shape).  Column: rows [n*rank/world, n*(rank+1)/world).  Row: the
+    256-element blocks [nb*rank/world, nb*(rank+1)/world) of the nb blocks of a
+    row, so a block count that does not divide evenly (68 blocks on 8 ranks)
+    gives ranks of 8 and 9 blocks."""
     if world == 1:
         return p.n, p.k
     if p.kind == COLUMN:
-        base, extra = divmod(p.n, world)
-        return base + (1 if rank < extra else 0), p.k
+        return p.n * (rank + 1) // world - p.n * rank // world, p.k
     blocks = p.k // 256
-    base, extra = divmod(blocks, world)
-    return p.n, (base + (1 if rank < extra else 0)) * 256
+    return p.n, (blocks * (rank + 1) // world - blocks * rank // world) * 256
 
 
 def total_weight_bytes(rank: int = 0, world: int = 1) -> int:

@@ -52,3 +52,12 @@ def rel_err(y, r):
     y = np.asarray(y, dtype=np.float64)
     r = np.asarray(r, dtype=np.float64)
     return float(np.abs(y - r).max() / max(np.abs(r).max(), 1e-30))
+
+
+def per_element_ok(y, r, tol=2e-3):
+    """The per-element form of the projection bound: |y - r| <= tol*|r| + tol*rms(r) for every
+    output, which also holds outputs near zero to the scale of the whole vector."""
+    y = np.asarray(y, dtype=np.float64)
+    r = np.asarray(r, dtype=np.float64)
+    rms = float(np.sqrt(np.mean(r * r)))
+    return bool(np.all(np.abs(y - r) <= tol * np.abs(r) + tol * rms))

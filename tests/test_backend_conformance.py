@@ -6,7 +6,7 @@ import subprocess
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-BINARY = os.path.join(ROOT, "oracle", "_ref", "backend_conformance")
+BINARY = os.path.join(ROOT, "tests", "cpp", "build", "backend_conformance")
 
 
 @pytest.mark.gpu

@@ -131,3 +131,62 @@ def test_ranks_in_one_process(world):
         c.close()
     for b in backends:
         b.close()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("fmt,m", [("q4k", 1), ("q4k", 16), ("q6k", 1), ("q6k", 4), ("mxfp4", 1), ("mxfp4", 16)])
+def test_row_parallel_projection_matches_the_unsharded_one(world, fmt, m):
+    """The down projection's shape in k (17408: 68 blocks, uneven on 8 ranks), cut for every rank
+    by the library's slicer from one full tensor, projected per rank and summed over ranks by the
+    launch itself (Q4_K, Q6_K at m <= 8) or by allreduce_sum: within 2e-3 of the un-sharded CPU
+    reference, and the same bits on every rank."""
+    if device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    from oracle.oracle import Oracle
+    from tessera_b200 import tp_check
+    n, k = 640, 17408
+    case = tp_check.make_case(fmt, m, n, k, seed=21)
+    oracle = Oracle()
+    ref = {"q4k": oracle.gemm_q4k, "q6k": oracle.gemm_q6k, "mxfp4": oracle.gemm_mxfp4}[fmt](
+        case.activations, case.weight, m, n, k)
+    backends = [make_backend(i) for i in range(world)]
+    comms = [TpComm(i, i, world, 16 * 5120) for i in range(world)]
+    for a in comms:
+        for b in comms:
+            if a is not b:
+                a.attach_local(b)
+    outs = []
+    for r in range(world):
+        backends[r].BindTensorParallel(comms[r])
+        a, w, k_local = tp_check.rank_inputs(case, r, world)
+        ab, wb = backends[r].upload(a), backends[r].upload(w)
+        out = backends[r].AllocateBuffer(m * n * 4)
+        outs.append((ab, wb, out, k_local))
+    for rep in range(2):
+        for r in range(world):   # nothing here blocks: the kernels of all ranks meet on the GPUs
+            ab, wb, out, k_local = outs[r]
+            tp_check.launch_rank(backends[r], case, ab, wb, out, k_local)
+        got = [backends[r].download(outs[r][2], np.float32, m * n).reshape(m, n) for r in range(world)]
+        for r in range(world):
+            assert tp_check.max_rel_err(got[r], ref) < 2e-3, (rep, r, tp_check.max_rel_err(got[r], ref))
+            assert np.array_equal(got[r], got[0]), (rep, r)
+    assert all(c.error_count() == 0 for c in comms)
+    for r in range(world):
+        backends[r].BindTensorParallel(None)
+        backends[r].Synchronize()
+    for c in comms:
+        c.close()
+    for b in backends:
+        b.close()
+
+
+def test_peer_with_another_capacity_is_refused(backend):
+    """Every rank computes its peers' offsets from its own capacity: a block made with another
+    one must not be attached."""
+    c0 = TpComm(0, 0, 2, 1024)
+    c1 = TpComm(0, 1, 2, 4096)
+    with pytest.raises(capi.StatusError) as e:
+        c0.attach_local(c1)
+    assert e.value.code == capi.StatusCode.InvalidArgument
+    c0.close()
+    c1.close()
