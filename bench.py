@@ -31,9 +31,6 @@ from tessera_b200 import synth, workload  # noqa: E402
 
 METRIC = "decode_projection_tok_s"
 UNIT = "tok/s"
-# DRAM bytes (read + write) of one gemm_q4k_vec launch on the 17408 x 5120 Q4_K
-# weight, mean of the two launches in profiles/gemv_q4k_staged_17408x5120.md
-TRAFFIC_Q4K_17408x5120 = 50285000
 
 
 def measured_peaks():
@@ -52,6 +49,7 @@ def config_dict(world: int):
         "parameters": workload.total_parameters(),
         "weight_bytes_per_rank": workload.total_weight_bytes(0, world),
         "parallelism": f"tp{world}",
+        "allreduce": "none" if world == 1 else "in the row-parallel launch, peer stores over NVLink",
         "cache": "weights streamed per step exceed L2 a hundredfold; no flush needed",
     }
 
@@ -184,7 +182,7 @@ def reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / value, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": config_dict(1),
+        "config": config_dict(args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": total,
@@ -194,13 +192,6 @@ def reference_arm(args):
 
 # --------------------------------------------------------------------------
 # GPU arm
-class CudaArrayView:
-    """Exposes a backend buffer to torch (for the NCCL all-reduce) without a copy."""
-
-    def __init__(self, ptr: int, count: int):
-        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 2}
-
-
 def qgemv_table(stream, hbm_peak, only=None):
     """Device time per launch of the single-projection shapes the metric names: the Q4_K
     decode GEMV (17408 x 5120, m = 1) and the MXFP4 / FP8 projections at m = 1, 4, 16 over
@@ -214,7 +205,7 @@ def qgemv_table(stream, hbm_peak, only=None):
     lib = capi.load_library()
     st = ctypes.c_void_p(stream.cuda_stream)
     shapes = [(17408, 5120), (5120, 5120), (5120, 17408)]
-    cases = [("q4k", 1, 17408, 5120)]
+    cases = [("q4k", 1, 17408, 5120), ("q6k", 1, 17408, 5120)]
     cases += [(f, m, n, k) for f in ("mxfp4", "fp8") for (n, k) in shapes for m in (1, 4, 16)]
     if only is not None:
         cases = [only]
@@ -226,6 +217,8 @@ def qgemv_table(stream, hbm_peak, only=None):
             scale = None
             if fmt == "q4k":
                 host = synth.q4k_weights(n, k, seed=11)
+            elif fmt == "q6k":
+                host = synth.q6k_weights(n, k, seed=11)
             elif fmt == "mxfp4":
                 host = synth.mxfp4_weights(n, k, seed=11)
             else:
@@ -243,6 +236,8 @@ def qgemv_table(stream, hbm_peak, only=None):
             pa, pc = ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(c.data_ptr())
             if fmt == "q4k":
                 rc = lib.tsr_gemm_q4k(pa, w, pc, m, n, k, 1, st)
+            elif fmt == "q6k":
+                rc = lib.tsr_gemm_q6k(pa, w, pc, m, n, k, 1, st)
             elif fmt == "mxfp4":
                 rc = lib.tsr_gemm_mxfp4(pa, w, pc, m, n, k, st)
             else:
@@ -275,12 +270,139 @@ def qgemv_table(stream, hbm_peak, only=None):
     return rows
 
 
+class Recorder:
+    """Stands in for the backend while the projection planner runs: kernels and buffers come
+    from the real backend, launches are recorded instead of issued.  The recorded list is the
+    reference's own launch sequence for the step (gemm_*_vec, gemm_vec_reduce, ...), submitted
+    later with one tsr_launch_many call per step."""
+
+    def __init__(self, backend, batch):
+        self.backend, self.batch = backend, batch
+
+    def LoadKernel(self, name, code=b""):
+        return self.backend.LoadKernel(name, code)
+
+    def AllocateBuffer(self, nbytes, kind=0):
+        return self.backend.AllocateBuffer(nbytes, kind)
+
+    def LaunchKernel(self, kernel, launch):
+        self.batch.add(kernel, launch)
+
+
+def profile_traffic(name):
+    """`dram_bytes_per_launch: N` of a committed ncu summary, or None."""
+    path = os.path.join(ROOT, "profiles", name)
+    try:
+        with open(path) as f:
+            for line in f:
+                if line.strip().startswith("dram_bytes_per_launch:"):
+                    return int(line.split(":", 1)[1].strip().split()[0])
+    except OSError:
+        pass
+    return None
+
+
+def tp_parity(backend, comm, dist, rank, world, local):
+    """Config 2 on the running ranks, outside the timed region: the 17408 -> 5120 down projection
+    and the 6144 -> 5120 output projection, Q4_K, Q6_K and MXFP4, m = 1 and 16.  Every rank cuts
+    its k range out of one full seeded tensor with the library's slicer, projects it and the
+    library sums over ranks; the result is compared on all outputs with the same projection of
+    the whole tensor on this GPU (the un-sharded TP = 1 result) and, by checksum, across ranks.
+    The flat collective is checked bit for bit against the rank-order sum of the gathered inputs."""
+    import hashlib
+    from tessera_b200 import tp_check
+    from tessera_b200.backend import KernelLaunch
+    from tessera_b200.tp import rank_order_sum
+    worst, identical, cases = 0.0, True, []
+    for fmt, n, k in (("q4k", 5120, 17408), ("mxfp4", 5120, 17408), ("q6k", 5120, 17408), ("q4k", 5120, 6144)):
+        for m in (1, 16):
+            case = tp_check.make_case(fmt, m, n, k, seed=7)
+            a, w, k_local = tp_check.rank_inputs(case, rank, world)
+            ab, wb = backend.upload(a), backend.upload(w)
+            out = backend.AllocateBuffer(m * n * 4)
+            fa, fw = backend.upload(case.activations), backend.upload(case.weight)
+            full = backend.AllocateBuffer(m * n * 4)
+            tp_check.launch_unsharded(backend, case, fa, fw, full)
+            want = backend.download(full, np.float32, m * n)
+            for rep in range(2):  # the second pass replays what the first one queued
+                tp_check.launch_rank(backend, case, ab, wb, out, k_local)
+                got = backend.download(out, np.float32, m * n)
+                err = tp_check.max_rel_err(got, want)
+                worst = max(worst, err)
+                sums = [None] * world
+                dist.all_gather_object(sums, hashlib.sha1(got.tobytes()).hexdigest())
+                identical = identical and len(set(sums)) == 1
+            cases.append({"fmt": fmt, "m": m, "n": n, "k": k, "k_local": k_local, "max_rel_err": err})
+            for buf in (ab, wb, out, fa, fw, full):
+                buf.release()
+    # flat all-reduce and its [m][n] form against the rank-order sum of everybody's input
+    exact = True
+    kern = backend.LoadKernel("allreduce_sum")
+    for m, n in ((1, 5120), (16, 5120), (3, 520)):
+        x = (np.random.default_rng(100 + rank).standard_normal(m * n) * 10.0 ** rank).astype(np.float32)
+        xb = backend.upload(x)
+        backend.LaunchKernel(kern, KernelLaunch(buffers=[xb], scalars=[m, n]))
+        got = backend.download(xb, np.float32, m * n)
+        parts = [None] * world
+        dist.all_gather_object(parts, x)
+        exact = exact and bool(np.array_equal(got, rank_order_sum(parts)))
+        xb.release()
+    errors = comm.error_count()
+    result = {"max_rel_err": worst, "ranks_bit_identical": bool(identical), "allreduce_equals_rank_order_sum": exact,
+              "tolerance": 2e-3, "peer_wait_errors": errors, "cases": cases}
+    flags = [None] * world
+    dist.all_gather_object(flags, (worst, identical, exact, errors))
+    ok = all(f[0] <= 2e-3 and f[1] and f[2] and f[3] == 0 for f in flags)
+    return result, ok
+
+
+def collective_table(backend, dist, stream, local):
+    """The library's peer-memory all-reduce and NCCL's on the same payloads (the row-parallel
+    partial sums of m = 1 and m = 16: 20 KB and 320 KB of fp32), issued back to back without
+    graphs, timed with events on the launching stream, max over ranks."""
+    import torch
+    from tessera_b200.backend import KernelLaunch
+    kern = backend.LoadKernel("allreduce_sum")
+    rows = []
+    for m in (1, 16):
+        n = workload.HIDDEN
+        xb = backend.upload(np.ones(m * n, dtype=np.float32))
+        t = torch.ones(m * n, dtype=torch.float32, device=f"cuda:{local}")
+        reps = 200
+
+        def peer():
+            for _ in range(reps):
+                backend.LaunchKernel(kern, KernelLaunch(buffers=[xb], scalars=[m, n]))
+            backend.Flush()
+
+        def nccl():
+            for _ in range(reps):
+                dist.all_reduce(t)
+        times = {}
+        for name, fn in (("peer_us", peer), ("nccl_us", nccl)):
+            fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ms = torch.tensor([e0.elapsed_time(e1)], device=f"cuda:{local}")
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            times[name] = round(float(ms.item()) * 1e3 / reps, 2)
+        rows.append({"floats": m * n, "bytes": m * n * 4, **times})
+        xb.release()
+    return rows
+
+
 def gpu_arm(args):
     import torch
     import torch.distributed as dist
 
-    from tessera_b200.backend import CreateBackend
-    from tessera_b200.project import Projector
+    from tessera_b200.backend import CreateBackend, KernelLaunch, LaunchBatch
+    from tessera_b200.project import GemmKernelName, Projector
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -292,92 +414,97 @@ def gpu_arm(args):
     backend = CreateBackend(stream=stream.cuda_stream)
     backend.SetDeviceIndex(local)
     backend.Init()
-    proj = Projector(backend)
-    launches = [0]
-    raw_launch = backend.LaunchKernel
-
-    def counted(kernel, launch):
-        launches[0] += 1
-        raw_launch(kernel, launch)
-    backend.LaunchKernel = counted
-
-    plan = workload.decode_projections()
-    # ---- weights: one seeded host tensor per distinct local shape, a private
-    # device copy per projection (distinct addresses, so nothing stays in L2)
-    templates = {}
-    weights = []
-    for p in plan:
-        n, k = workload.shard(p, rank, world)
-        key = (p.dtype, n, k)
-        if key not in templates:
-            host = synth.q4k_weights(n, k, seed=3) if p.dtype == "q4k" else synth.q6k_weights(n, k, seed=3)
-            templates[key] = backend.upload(host)
-        buf = backend.AllocateBuffer(templates[key].Size())
-        backend.CopyD2D(templates[key], 0, buf, 0, buf.Size())
-        weights.append((p, n, k, buf))
-    backend.Synchronize()
-    for t in templates.values():
-        t.release()
-    templates.clear()
-
-    # ---- activations (host, pinned by the backend's staging ring) and outputs
-    act_len = {"x": workload.HIDDEN}
-    for p, n, k, _ in weights:
-        act_len[p.act] = max(act_len.get(p.act, 0), k)
-    host_act = {name: synth.activations(1, ln, seed=5, index=i).reshape(-1) for i, (name, ln) in enumerate(act_len.items())}
-    dev_act = {name: backend.upload(h) for name, h in host_act.items()}
-    max_n = max(n for _, n, _, _ in weights)
-    out_buf = backend.AllocateBuffer(max_n * 4)
-    logits_n = weights[-1][1]
-    logits_buf = backend.AllocateBuffer(logits_n * 4)
-    logits_host = np.empty(logits_n, dtype=np.float32)
-    reduce_view, comm = None, None
-    if world > 1 and args.allreduce == "nccl":
-        reduce_view = torch.as_tensor(CudaArrayView(out_buf.Handle(), workload.HIDDEN), device=f"cuda:{local}")
-    elif world > 1:
+    comm = None
+    if world > 1:
         from tessera_b200.tp import TpComm
-        comm = TpComm(local, rank, world, workload.HIDDEN)
+        comm = TpComm(local, rank, world, 16 * workload.HIDDEN)
         comm.connect(dist)
-
-    def run_step(only=None):
-        for p, n, k, w in weights:
-            if only is not None and p.name not in only:
-                continue
-            dst = logits_buf if p.name == "output" else out_buf
-            if world > 1 and p.kind == workload.ROW and comm is not None:
-                # row-parallel: the split-K reduce rides in the all-reduce kernel
-                part, split = proj.ProjectGemvPartials(p.dtype, dev_act[p.act], w, 1, n, k)
-                launches[0] += 1
-                comm.reduce_allreduce(part.Handle(), split, out_buf.Handle(), workload.HIDDEN, backend.stream())
-                continue
-            proj.ProjectBatch(p.dtype, dev_act[p.act], w, dst, 1, n, k)
-            if world > 1 and p.kind == workload.ROW:
-                dist.all_reduce(reduce_view)
-
-    h2d_bytes = host_act["x"].nbytes
-    d2h_bytes = logits_host.nbytes
-
-    def e2e_step(graph):
-        backend.CopyH2D(dev_act["x"], host_act["x"])
-        graph.replay()
-        backend.CopyD2H(logits_buf, logits_host)
+        backend.BindTensorParallel(comm)
+    # Launches queue in the backend until the next copy or synchronisation, are merged there
+    # and replayed as a CUDA graph from the second identical step on (TSR_BENCH_DEFERRED=0:
+    # every launch of the reference's sequence is issued as it is made).
+    deferred = int(os.environ.get("TSR_BENCH_DEFERRED", "1"))
+    backend.SetDeferred(deferred)
 
     with torch.cuda.stream(stream):
-        run_step()  # allocates the split-K scratch and warms the kernel cache before capture
+        parity, parity_ok, collective = None, True, None
+        if world > 1:
+            if not args.no_tp_parity:
+                parity, parity_ok = tp_parity(backend, comm, dist, rank, world, local)
+            if not args.no_collective_table:
+                collective = collective_table(backend, dist, stream, local)
+
+        plan = workload.decode_projections()
+        # ---- weights: one seeded host tensor per distinct local shape, a private
+        # device copy per projection (distinct addresses, so nothing stays in L2)
+        templates = {}
+        weights = []
+        for p in plan:
+            n, k = workload.shard(p, rank, world)
+            key = (p.dtype, n, k)
+            if key not in templates:
+                host = synth.q4k_weights(n, k, seed=3) if p.dtype == "q4k" else synth.q6k_weights(n, k, seed=3)
+                templates[key] = backend.upload(host)
+            buf = backend.AllocateBuffer(templates[key].Size())
+            backend.CopyD2D(templates[key], 0, buf, 0, buf.Size())
+            weights.append((p, n, k, buf))
         backend.Synchronize()
-        launches[0] = 0
-        run_step()
-        launches_per_step = launches[0]
-        backend.Synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
-            run_step()
+        for t in templates.values():
+            t.release()
+        templates.clear()
+
+        # ---- activations (host) and outputs: one output buffer per projection of a layer so
+        # that projections which share their input stay independent of each other
+        act_len = {"x": workload.HIDDEN}
+        for p, n, k, _ in weights:
+            act_len[p.act] = max(act_len.get(p.act, 0), k)
+        host_act = {name: synth.activations(1, ln, seed=5, index=i).reshape(-1)
+                    for i, (name, ln) in enumerate(act_len.items())}
+        dev_act = {name: backend.upload(h) for name, h in host_act.items()}
+        out_bufs = {}
+        for p, n, k, _ in weights:
+            if p.name != "output":
+                out_bufs[p.name] = max(out_bufs.get(p.name, 0), n)
+        out_bufs = {name: backend.AllocateBuffer(n * 4) for name, n in out_bufs.items()}
+        logits_n = weights[-1][1]
+        logits_buf = backend.AllocateBuffer(logits_n * 4)
+        logits_host = np.empty(logits_n, dtype=np.float32)
+
+        def record(only=None):
+            """The reference's launch sequence for the step, as ProjectBatch makes it; the
+            row-parallel projections of a tensor-parallel run use the ids that end with the sum
+            over ranks instead of ProjectBatch + TpReduce."""
+            batch = LaunchBatch()
+            proj = Projector(Recorder(backend, batch))
+            for p, n, k, w in weights:
+                if only is not None and p.name not in only:
+                    continue
+                dst = logits_buf if p.name == "output" else out_bufs[p.name]
+                if world > 1 and p.kind == workload.ROW:
+                    kern = backend.LoadKernel(GemmKernelName(p.dtype) + "_allreduce")
+                    batch.add(kern, KernelLaunch(buffers=[dev_act[p.act], w, dst], scalars=[1, n, k]))
+                    continue
+                proj.ProjectBatch(p.dtype, dev_act[p.act], w, dst, 1, n, k)
+            return batch, proj
+
+        step, keep_step = record(only=set(args.only.split(",")) if args.only else None)
         dominant = ("ffn_gate", "ffn_up")
-        launches[0] = 0
-        dom_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(dom_graph, stream=stream, capture_error_mode="thread_local"):
-            run_step(only=dominant)
-        dom_launches = launches[0]
+        dom, keep_dom = record(only=dominant)
+        h2d_bytes = host_act["x"].nbytes
+        d2h_bytes = logits_host.nbytes
+
+        def run_step():
+            backend.LaunchMany(step)
+            backend.Flush()
+
+        def run_dom():
+            backend.LaunchMany(dom)
+            backend.Flush()
+
+        def e2e_step():
+            backend.CopyH2D(dev_act["x"], host_act["x"])
+            backend.LaunchMany(step)
+            backend.CopyD2H(logits_buf, logits_host)
 
         def barrier():
             if world > 1:
@@ -399,49 +526,71 @@ def gpu_arm(args):
                 ms = float(t.item())
             return ms
 
-        for _ in range(max(args.warmup, 3)):
-            graph.replay()
+        warmup = max(args.warmup, 3)
+        for _ in range(warmup):
+            run_step()
+        backend.Synchronize()
+        api0, dev0, graphs0 = backend.LaunchStats()
         with ClockSampler(local) as clocks:
-            ms_total = timed(graph.replay, args.steps)
+            ms_total = timed(run_step, args.steps)
+            api1, dev1, graphs1 = backend.LaunchStats()
             for _ in range(2):
-                e2e_step(graph)
-            ms_e2e = timed(lambda: e2e_step(graph), args.steps)
-            for _ in range(2):
-                dom_graph.replay()
-            ms_dom = timed(dom_graph.replay, args.steps)
+                e2e_step()
+            ms_e2e = timed(e2e_step, args.steps)
+            for _ in range(3):
+                run_dom()
+            backend.Synchronize()
+            _, devd0, _ = backend.LaunchStats()
+            ms_dom = timed(run_dom, args.steps)
+            _, devd1, _ = backend.LaunchStats()
 
     value = args.steps / (ms_total * 1e-3)
     e2e_value = args.steps / (ms_e2e * 1e-3)
-    # ---- roofline of the dominant kernel (gemm_q4k_vec on the ffn_gate/ffn_up shape)
+    kernels_per_step = (dev1 - dev0) // args.steps
+    # ---- roofline of the dominant kernel: the launch that serves ffn_gate and ffn_up of a layer
     peaks, peak_kind = measured_peaks()
     gate = next(x for x in weights if x[0].name == "ffn_gate")
     n_g, k_g = gate[1], gate[2]
-    alg_bytes = workload.weight_bytes("q4k", n_g, k_g) + k_g * 4 + n_g * 4
-    n_dom_kernels = sum(1 for p, _, _, _ in weights if p.name in dominant)
-    t_launch_s = ms_dom * 1e-3 / (args.steps * n_dom_kernels)
+    dom_kernels = max(1, (devd1 - devd0) // args.steps)
+    dom_projections = sum(1 for p, _, _, _ in weights if p.name in dominant)
+    per_launch = dom_projections // dom_kernels  # weight tensors one launch serves
+    alg_bytes = per_launch * (workload.weight_bytes("q4k", n_g, k_g) + n_g * 4) + k_g * 4
+    t_launch_s = ms_dom * 1e-3 / (args.steps * dom_kernels)
     achieved = alg_bytes / t_launch_s / 1e9
+    traffic = profile_traffic("gemv_q4k_group_gate_up.md") if (n_g, k_g, per_launch) == (17408, 5120, 2) else None
     roofline = {
-        "bound": "hbm", "kernel": "gemv_q4k_staged_kernel (gemm_q4k_vec)", "shape": [1, n_g, k_g],
+        "bound": "hbm", "kernel": "gemv_q4k_staged_kernel (ffn_gate + ffn_up of a layer in one launch)"
+                                  if per_launch == 2 else "gemv_q4k_staged_kernel (gemm_q4k_vec)",
+        "shape": [1, per_launch * n_g, k_g], "weights_per_launch": per_launch,
         "achieved": achieved, "peak": peaks["hbm_gbs"], "peak_kind": peak_kind, "unit": "GB/s",
         "frac": achieved / peaks["hbm_gbs"], "us_per_launch": t_launch_s * 1e6,
-        "algorithmic_bytes": alg_bytes,
-        "traffic": TRAFFIC_Q4K_17408x5120 if (n_g, k_g) == (17408, 5120) else None,
-        "launches_timed": args.steps * n_dom_kernels, "kernel_launches_per_replay": dom_launches,
+        "algorithmic_bytes": alg_bytes, "traffic": traffic,
+        "launches_timed": args.steps * dom_kernels,
     }
     step_bytes = workload.total_weight_bytes(rank, world)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32 accumulate over Q4_K/Q6_K (int8 digits on the staged path)",
-        "data": "synthetic", "config": dict(config_dict(world), allreduce=(args.allreduce if world > 1 else "none")),
+        "warmup": warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32 accumulate over Q4_K/Q6_K (int8 digits on the staged path)",
+        "data": "synthetic", "config": config_dict(world),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
-        "gpu_launches": launches_per_step * args.steps,
-        "launches_per_step": launches_per_step,
+        "gpu_launches": kernels_per_step * args.steps,
+        "kernels_per_step": kernels_per_step,
+        "api_launches_per_step": (api1 - api0) // args.steps,
+        "graph_launches_per_step": (graphs1 - graphs0) / args.steps,
+        "submission": {0: "every launch issued as made", 1: "deferred queue, merged launches, CUDA graph replay",
+                       2: "deferred queue, merged launches, no graphs"}.get(deferred, str(deferred)),
         "step_hbm_gbs_per_gpu": step_bytes / (ms_total * 1e-3 / args.steps) / 1e9,
         "roofline": roofline, "clocks": clocks.summary(),
     }
-    if rank == 0 and world == 1:
+    if parity is not None:
+        line["tp_parity"] = parity
+    if collective is not None:
+        line["collective"] = collective
+    if rank == 0 and world == 1 and not args.no_qgemv:
         # free the step's weights first: the table below wants a few hundred MB per case
+        backend.SetDeferred(0)
         for _, _, _, buf in weights:
             buf.release()
         weights.clear()
@@ -453,11 +602,14 @@ def gpu_arm(args):
     if rank == 0:
         print(json.dumps(line))
     backend.Synchronize()
-    if comm is not None and comm.error_count() != 0:
-        raise RuntimeError("a tensor-parallel wait on a peer gave up; the results are not valid")
+    failed = comm is not None and comm.error_count() != 0
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if failed:
+        raise RuntimeError("a tensor-parallel wait on a peer gave up; the results are not valid")
+    if not parity_ok:
+        raise RuntimeError("tensor-parallel parity check failed: " + json.dumps(parity))
 
 
 def main():
@@ -468,8 +620,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, metavar="FMT:M:N:K",
                     help="time one projection (q4k, mxfp4 or fp8) instead of the decode step, e.g. q4k:1:17408:5120")
-    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
-                    help="row-parallel reduce: peer-memory push all-reduce (default) or NCCL (comparison)")
+    ap.add_argument("--only", default=None, metavar="NAMES",
+                    help="experiment: the step holds only these projections (comma separated tensor names)")
+    ap.add_argument("--no-qgemv", action="store_true", help="skip the single-projection table and the CPU baseline")
+    ap.add_argument("--no-tp-parity", action="store_true",
+                    help="experiment: skip the tensor-parallel parity check before the timed region")
+    ap.add_argument("--no-collective-table", action="store_true",
+                    help="skip the peer-memory / NCCL all-reduce comparison of a tensor-parallel run")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)

@@ -212,6 +212,14 @@ int tsr_slice_shape(int fmt, int kind, uint64_t rows, uint64_t cols, int rank, i
                     uint64_t* out_rows, uint64_t* out_cols, uint64_t* col_begin, uint64_t* out_bytes);
 int tsr_slice_tensor(int fmt, int kind, uint64_t rows, uint64_t cols, int rank, int world,
                      const void* src, size_t src_bytes, void* dst, size_t dst_bytes);
+/* The same copy for ranges the caller chose: rows [row_begin, row_end) and columns
+ * [col_begin, col_end) (whole blocks).  For shard maps the kind rule cannot express: a
+ * row split whose ranks hold multiples of four Q6_K blocks (rows of 210-byte blocks are
+ * then 8-byte aligned, which the staged Q6_K kernel needs), or a column split that
+ * follows the uneven k ranges of the row-parallel projection it feeds. */
+int tsr_slice_range(int fmt, uint64_t rows, uint64_t cols, uint64_t row_begin, uint64_t row_end,
+                    uint64_t col_begin, uint64_t col_end, const void* src, size_t src_bytes,
+                    void* dst, size_t dst_bytes);
 
 /* ---- split-K Q4_K projection without any device allocation ----------------
  * No counterpart in the reference: there the caller allocates the split-K

@@ -36,7 +36,8 @@ class StatusError(RuntimeError):
 
 
 def library_path() -> str:
-    return os.path.join(_HERE, "lib", "libtessera_b200.so")
+    """The built library beside this package, or the file TESSERA_B200_LIBRARY names."""
+    return os.environ.get("TESSERA_B200_LIBRARY") or os.path.join(_HERE, "lib", "libtessera_b200.so")
 
 
 _lib = None
@@ -100,6 +101,7 @@ SIGNATURES = {
     "tsr_dequantize": (C.c_int, [C.c_int, _vp, _vp, _vp, _u64, _u64, _vp]),
     "tsr_slice_shape": (C.c_int, [C.c_int, C.c_int, _u64, _u64, C.c_int, C.c_int, C.POINTER(_u64), C.POINTER(_u64),
                                   C.POINTER(_u64), C.POINTER(_u64)]),
+    "tsr_slice_range": (C.c_int, [C.c_int, _u64, _u64, _u64, _u64, _u64, _u64, _vp, _sz, _vp, _sz]),
     "tsr_slice_tensor": (C.c_int, [C.c_int, C.c_int, _u64, _u64, C.c_int, C.c_int, _vp, _sz, _vp, _sz]),
     "tsr_gemm_q4k_noalloc_max_outputs": (_u64, []),
     "tsr_gemm_q4k_noalloc": (C.c_int, [_vp, _vp, _vp, _u64, _u64, _u64, _vp]),

@@ -89,11 +89,6 @@ int flush_pending(tsr_context* ctx);
 // The tail parameters / device of a communicator (tp.cu).
 int tp_tail_of(const tsr_tp_comm* comm, TpTail* out);
 int tp_device_of(const tsr_tp_comm* comm);
-// Sum over ranks of an [m][n] fp32 matrix in place, exchanged in tiles of `tile_rows`
-// rows: the same tiles, flags and order as a row-parallel GEMV launch that ends with
-// the collective, so ranks may mix the two within one call (tp.cu).
-int tp_allreduce_tiled(tsr_tp_comm* comm, float* data, uint64_t m, uint64_t n, uint64_t tile_rows, cudaStream_t st);
-// Tile height (weight rows) of every row-parallel launch over n rows: a function of n
-// alone, because all ranks must cut the output into the same tiles.
-inline int tp_tile_rows(uint64_t n) { return n >= 16384 ? 64 : 32; }
+// Sum over ranks of an [m][n] fp32 matrix in place (tp.cu).
+int tp_allreduce_matrix(tsr_tp_comm* comm, float* data, uint64_t m, uint64_t n, cudaStream_t st);
 }  // namespace tsr

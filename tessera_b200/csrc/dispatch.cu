@@ -341,7 +341,7 @@ int k_fill(const Args& a) {
 // bound to the context (tsr_tp_bind).  With one rank (or none bound) it is the identity.
 int tp_sum_in_place(const Args& a, float* data, uint64_t m, uint64_t n) {
   if (a.ctx == nullptr || a.ctx->tp == nullptr) return kOk;
-  return tp_allreduce_tiled(a.ctx->tp, data, m, n, static_cast<uint64_t>(tp_tile_rows(n)), a.stream);
+  return tp_allreduce_matrix(a.ctx->tp, data, m, n, a.stream);
 }
 
 // One or several projections that share A as one staged launch which splits k as it
@@ -354,6 +354,12 @@ int fused_group(tsr_context* ctx, int fmt, const float* a, const GroupTarget* t,
   const TpTail* tp = nullptr;
   if (with_tp && ctx->tp != nullptr) {
     if (int rc = tp_tail_of(ctx->tp, &tail)) return rc;
+    // TSR_TP_FUSED=0 (experiments): the projection and the sum over ranks as two launches
+    static const bool fused = [] {
+      const char* v = std::getenv("TSR_TP_FUSED");
+      return v == nullptr || std::atoi(v) != 0;
+    }();
+    if (tail.world > 1 && !fused) return kUnsupportedFeature;
     if (tail.world > 1) tp = &tail;
   }
   return fmt == 0 ? staged_group_q4k(a, t, count, m, k, 0, &ctx->scratch, tp, st)
@@ -368,7 +374,7 @@ template <uint64_t BLOCK_BYTES, bool Q6>
 int k_block_allreduce(const Args& a) {
   if (!shape(a, 3, 3)) return kInvalidArgument;
   const uint64_t m = a.sc[0], n = a.sc[1], k = a.sc[2];
-  if (!dims_ok(m, n, k) || k % 256 != 0 || n % 4 != 0) return kInvalidArgument;
+  if (!dims_ok(m, n, k) || k % 256 != 0) return kInvalidArgument;
   if (!holds(a, 0, m * k * 4) || !holds(a, 1, n * (k / 256) * BLOCK_BYTES) || !holds(a, 2, m * n * 4))
     return kInvalidArgument;
   if (a.dry) return kOk;
@@ -389,7 +395,7 @@ int k_block_allreduce(const Args& a) {
 int k_allreduce_sum(const Args& a) {
   if (!shape(a, 1, 2)) return kInvalidArgument;
   const uint64_t m = a.sc[0], n = a.sc[1];
-  if (!dims_ok(m, n, 1) || n % 4 != 0 || !holds(a, 0, m * n * 4)) return kInvalidArgument;
+  if (!dims_ok(m, n, 1) || !holds(a, 0, m * n * 4)) return kInvalidArgument;
   if (a.dry) return kOk;
   return tp_sum_in_place(a, static_cast<float*>(const_cast<void*>(a.buf[0])), m, n);
 }

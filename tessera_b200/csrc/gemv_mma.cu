@@ -32,6 +32,7 @@
 #include <unordered_map>
 
 #include "codec.cuh"
+#include "context.h"
 #include "launch.h"
 #include "pipeline.cuh"
 #include "staged_common.cuh"
@@ -63,7 +64,7 @@ struct alignas(64) Q4KMaps {
 // ring keeps streaming across tile boundaries.
 template <int NCG, int SETS>
 __global__ void __launch_bounds__((SETS * 4 + 1) * 32, SETS == 2 ? 2 : 1)
-gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const __grid_constant__ StagedParams p) {
+gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kConsumerWarps = SETS * p.rgs, kConsumerThreads = kConsumerWarps * 32;
@@ -87,7 +88,9 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const __grid_consta
 
   if (tid < 4) reinterpret_cast<uint32_t*>(empty + p.stages)[tid] = 0u;
   if (producer) {
-    for (int g = 0; g < p.ntargets; ++g) tma_prefetch_descriptor(&maps.m[g]);
+#pragma unroll
+    for (int g = 0; g < kMaxGroup; ++g)
+      if (g < p.ntargets) tma_prefetch_descriptor(&maps.m[g]);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], p.rgs);
@@ -95,20 +98,29 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const __grid_consta
     mbar_fence_init();
   }
   __syncthreads();
-  // chunk j of this CTA's sequence: chunk j % nchunks of its (j / nchunks)-th tile
-  auto issue = [&](int j, int slot) {
-    const int it = j / nchunks, c = j - it * nchunks;
-    const int tile = blockIdx.x + it * gridDim.x;
-    const int g = target_of_tile(p, tile);
-    const int row0 = (tile - p.tgt[g].tile_begin) * kTileRows;
+  // The producer walks the CTA's chunk sequence (tile after tile, chunk after chunk) with a
+  // cursor: map and first row change only when a tile begins.
+  int p_it = 0, p_c = 0, p_row0 = 0;
+  const CUtensorMap* p_map = &maps.m[0];
+  auto issue_next = [&](int slot) {
+    if (p_c == 0) {
+      const int tile = blockIdx.x + p_it * gridDim.x;
+      const int g = target_of_tile(p, tile);
+      p_row0 = (tile - target_by_index(p, g).tile_begin) * kTileRows;
+      p_map = map_by_index(maps.m, g);
+    }
     unsigned char* dst = smem + static_cast<size_t>(slot) * kStageBytes;
     mbar_expect_tx(&full[slot], kStageBytes);
-    tma_load_3d(dst, &maps.m[g], 0, b0 + c * kChunkBlocks, row0, &full[slot]);
+    tma_load_3d(dst, p_map, 0, b0 + p_c * kChunkBlocks, p_row0, &full[slot]);
+    if (++p_c == nchunks) {
+      p_c = 0;
+      ++p_it;
+    }
   };
   auto prologue = [&]() {
     if (producer) {
       const int first = total_chunks < p.stages ? total_chunks : p.stages;
-      for (int j = 0; j < first; ++j) issue(j, j);
+      for (int j = 0; j < first; ++j) issue_next(j);
     }
   };
   if (p.pdl) {
@@ -130,13 +142,20 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const __grid_consta
   }
   if (tid == 0 && p.tp.world > 1) s_words[1] = tp_call_epoch(p.tp);  // the stream's earlier work is complete here
   __syncthreads();
+  if (p.tp.world > 1 && warp < kConsumerWarps) {
+    const size_t cta = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
+    tp_reset_previous(p.tp, s_words[1], cta * kConsumerThreads + tid,
+                      static_cast<size_t>(gridDim.x) * gridDim.y * kConsumerThreads);
+  }
 
   if (warp == kConsumerWarps) {
     if (lane == 0) {
+      RingCursor<SETS> cursor;
+      cursor.start_after_fill(p.stages);
       for (int j = p.stages; j < total_chunks; ++j) {
-        const RingUse use = ring_use(j, p.stages, SETS);
+        const RingUse use = cursor.next();
         if (!mbar_wait(&empty[use.slot], (use.round & 1) ^ 1, &g_wait_timeouts)) break;
-        issue(j, use.slot);
+        issue_next(use.slot);
       }
     }
     return;
@@ -176,8 +195,6 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const __grid_consta
   bool failed = false;  // a bounded wait gave up: skip the remaining waits, keep the barriers
   for (int it = 0; it < my_tiles; ++it) {
     const int tile = blockIdx.x + it * gridDim.x;
-    const StagedTarget& tg = p.tgt[target_of_tile(p, tile)];
-    const int row0 = (tile - tg.tile_begin) * kTileRows;
     float o[NCG][4];
 #pragma unroll
     for (int g = 0; g < NCG; ++g)
@@ -299,6 +316,8 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const __grid_consta
       }
     }
     asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
+    const StagedTarget tg = target_by_index(p, target_of_tile(p, tile));
+    const int row0 = (tile - tg.tile_begin) * kTileRows;
     finish_tile(p, tg, tile, row0, kTileRows, blockIdx.y, gridDim.y, epoch, tid, kConsumerThreads, s_words,
                 [&](int i, int rr) {
                   float v = 0.0f;
@@ -306,7 +325,10 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const __grid_consta
                   return v;
                 });
   }
-  if (tid == 0 && p.tp.world > 1) tp_cta_leaves(p.tp, epoch, gridDim.x * gridDim.y);
+  if (p.tp.world > 1) {
+    asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");  // every thread's share of the reset is done
+    if (tid == 0) tp_cta_leaves(p.tp, epoch, gridDim.x * gridDim.y, static_cast<unsigned int>(p.m) * p.tgt[0].n);
+  }
 }
 
 // ---- tensor-map cache: a map depends only on (base, rows, blocks per row, box rows)
@@ -370,7 +392,7 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
   uint64_t rows[kMaxGroup];
   for (int i = 0; i < count; ++i) rows[i] = t[i].n;
   GroupPlan plan;
-  if (!plan_group(rows, count, nb, caller_split, SETS, regs, 12, fixed, stage_bytes, chunks_of, &plan))
+  if (!plan_group(rows, count, nb, static_cast<int>(m), caller_split, SETS, 0, regs, 12, 0.5, fixed, stage_bytes, chunks_of, &plan))
     return kUnsupportedFeature;
   if (cost_only != nullptr) {
     *cost_only = plan.cost;
@@ -422,9 +444,8 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
     p.tickets = scratch->tickets;
   }
   if (tp != nullptr && tp->world > 1) {
-    if (tiles > tp->tiles_cap || m * t[0].n > tp->capacity || count != 1 || p.split_mode != kSplitInLaunch)
-      return kUnsupportedFeature;
-    // every CTA of the launch must be resident at once: a tile waits for its peers' flags
+    if (m * t[0].n > tp->capacity || count != 1 || p.split_mode != kSplitInLaunch) return kUnsupportedFeature;
+    // every CTA of the launch must be resident at once: a tile waits for its peers' values
     if (static_cast<uint64_t>(plan.grid_x) * plan.split > static_cast<uint64_t>(device_sms()) * plan.occ)
       return kUnsupportedFeature;
     p.tp = *tp;

@@ -29,9 +29,11 @@
 
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "codec.cuh"
+#include "context.h"
 #include "launch.h"
 #include "pipeline.cuh"
 #include "staged_common.cuh"
@@ -172,18 +174,20 @@ struct alignas(64) Q6KMaps {
 
 // A CTA works through the tiles blockIdx.x, blockIdx.x + gridDim.x, ... of the launch's tile
 // list, all on split chunk blockIdx.y of k (see gemv_mma.cu).
-template <int NCG>
-__global__ void __launch_bounds__(kThreads, 2)
-gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const __grid_constant__ StagedParams p) {
+// SETS consumer warp sets (2, or 4 where each warp's chain of blocks would otherwise be long on
+// a mostly idle SM): set s takes the chunks j = s (mod SETS) of the CTA's sequence.
+template <int NCG, int SETS>
+__global__ void __launch_bounds__((SETS * 4 + 1) * 32, SETS == 2 ? 2 : 1)
+gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kConsumerWarps = 2 * p.rgs, kConsumerThreads = kConsumerWarps * 32;
+  const int kConsumerWarps = SETS * p.rgs, kConsumerThreads = kConsumerWarps * 32;
   const int kTileRows = 16 * p.rgs, kHalfBytes = p.rgs * kGroupHalfBytes, kStageBytes = 2 * kHalfBytes;
   unsigned char* act = smem + static_cast<size_t>(p.stages) * kStageBytes;
   unsigned char* sums = act + static_cast<size_t>(p.per) * p.ncols * 256;
   float* cs = reinterpret_cast<float*>(sums + static_cast<size_t>(p.per) * p.ncols * 2 * kGroups);
-  float* xchg = cs + static_cast<size_t>(p.per) * kMaxCols;  // [row groups][32 lanes][NCG*4]
-  float* outbuf = xchg + p.rgs * 32 * NCG * 4;               // [tile rows][NCG*8]
+  float* xchg = cs + static_cast<size_t>(p.per) * kMaxCols;  // [SETS - 1][row groups][32 lanes][NCG*4]
+  float* outbuf = xchg + (SETS - 1) * p.rgs * 32 * NCG * 4;  // [tile rows][NCG*8]
   uint64_t* full = reinterpret_cast<uint64_t*>(outbuf + kTileRows * NCG * 8);
   uint64_t* empty = full + p.stages;
   const unsigned char* zero_page = reinterpret_cast<const unsigned char*>(empty + p.stages);  // 16 zero bytes
@@ -200,9 +204,12 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const __grid_consta
 
   if (tid < 4) reinterpret_cast<uint32_t*>(empty + p.stages)[tid] = 0u;
   if (producer) {
-    for (int g = 0; g < p.ntargets; ++g) {
-      tma_prefetch_descriptor(&maps.even[g]);
-      tma_prefetch_descriptor(&maps.odd[g]);
+#pragma unroll
+    for (int g = 0; g < kMaxGroup; ++g) {
+      if (g < p.ntargets) {
+        tma_prefetch_descriptor(&maps.even[g]);
+        tma_prefetch_descriptor(&maps.odd[g]);
+      }
     }
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
@@ -212,27 +219,38 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const __grid_consta
   }
   __syncthreads();
 
-  // Chunk j of this CTA's sequence: pair pair0 + j % nchunks of its (j / nchunks)-th tile.
+  // The producer walks the CTA's chunk sequence (tile after tile, pair after pair) with a
+  // cursor: maps, first row and the odd map's shift change only when a tile begins.
   // Window of a chunk: starts at the 16-byte boundary at or below the pair, in
   // the byte space of each map (the odd map's base lies odd_shift bytes below
   // the first odd row).  Coordinates are in u64 units and even: 16-byte rule.
-  auto issue_chunk = [&](int j, int slot) {
-    const int it = j / nchunks, c = j - it * nchunks;
-    const int tile = blockIdx.x + it * gridDim.x;
-    const int g = target_of_tile(p, tile);
-    const int row0 = (tile - p.tgt[g].tile_begin) * kTileRows;
-    const int odd_shift = p.tgt[g].aux;
-    const uint32_t begin = static_cast<uint32_t>(pair0 + c) * kChunkBytes;
+  int p_it = 0, p_c = 0, p_row0 = 0, p_shift = 0;
+  const CUtensorMap* p_even = &maps.even[0];
+  const CUtensorMap* p_odd = &maps.odd[0];
+  auto issue_next = [&](int slot) {
+    if (p_c == 0) {
+      const int tile = blockIdx.x + p_it * gridDim.x;
+      const int g = target_of_tile(p, tile);
+      const StagedTarget tgt = target_by_index(p, g);
+      p_row0 = (tile - tgt.tile_begin) * kTileRows;
+      p_shift = tgt.aux;
+      p_even = map_by_index(maps.even, g);
+      p_odd = map_by_index(maps.odd, g);
+    }
+    const uint32_t begin = static_cast<uint32_t>(pair0 + p_c) * kChunkBytes;
     unsigned char* dst = smem + static_cast<size_t>(slot) * kStageBytes;
     mbar_expect_tx(&full[slot], kStageBytes);
-    tma_load_2d(dst, &maps.even[g], static_cast<int>((begin >> 4) * 2), row0 >> 1, &full[slot]);
-    tma_load_2d(dst + kHalfBytes, &maps.odd[g], static_cast<int>(((begin + odd_shift) >> 4) * 2), row0 >> 1,
-                &full[slot]);
+    tma_load_2d(dst, p_even, static_cast<int>((begin >> 4) * 2), p_row0 >> 1, &full[slot]);
+    tma_load_2d(dst + kHalfBytes, p_odd, static_cast<int>(((begin + p_shift) >> 4) * 2), p_row0 >> 1, &full[slot]);
+    if (++p_c == nchunks) {
+      p_c = 0;
+      ++p_it;
+    }
   };
   auto prologue = [&]() {
     if (producer) {
       const int first = total_chunks < p.stages ? total_chunks : p.stages;
-      for (int j = 0; j < first; ++j) issue_chunk(j, j);
+      for (int j = 0; j < first; ++j) issue_next(j);
     }
   };
   if (p.pdl) {
@@ -254,13 +272,20 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const __grid_consta
   }
   if (tid == 0 && p.tp.world > 1) s_words[1] = tp_call_epoch(p.tp);  // the stream's earlier work is complete here
   __syncthreads();
+  if (p.tp.world > 1 && warp < kConsumerWarps) {
+    const size_t cta = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
+    tp_reset_previous(p.tp, s_words[1], cta * kConsumerThreads + tid,
+                      static_cast<size_t>(gridDim.x) * gridDim.y * kConsumerThreads);
+  }
 
   if (warp == kConsumerWarps) {
     if (lane == 0) {
+      RingCursor<SETS> cursor;
+      cursor.start_after_fill(p.stages);
       for (int j = p.stages; j < total_chunks; ++j) {
-        const RingUse use = ring_use(j, p.stages);
+        const RingUse use = cursor.next();
         if (!mbar_wait(&empty[use.slot], (use.round & 1) ^ 1, &g_q6k_wait_timeouts)) break;
-        issue_chunk(j, use.slot);
+        issue_next(use.slot);
       }
     }
     return;
@@ -268,7 +293,7 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const __grid_consta
 
   const unsigned int epoch = s_words[1];
   const int gid = lane >> 2, tig = lane & 3;
-  const int bx = warp >= p.rgs ? 1 : 0, rg = warp - bx * p.rgs;  // warp set bx takes chunks j = bx (mod 2)
+  const int bx = warp / p.rgs, rg = warp - bx * p.rgs;  // warp set bx takes chunks j = bx (mod SETS)
   // A warp covers 16 consecutive rows: the thread's MMA rows gid and gid + 8 are
   // the even row 2e and the odd row 2e + 1 of pair e = 8 rg + gid.
   const int pair = rg * 8 + gid;
@@ -287,14 +312,14 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const __grid_consta
   }
   const float* cs_t = cs + 2 * tig;  // this thread's two columns of a group
 
-  // this set's ring slots bx, bx + 2, ... in turn (see ring_use)
-  const int owned = (p.stages + 1 - bx) >> 1;
+  // this set's ring slots bx, bx + SETS, ... in turn (see ring_use)
+  const int owned = (p.stages - bx + SETS - 1) / SETS;
   int ring_idx = 0, ring_round = 0;
   int j = bx;           // next chunk of this set in the CTA's sequence
   bool failed = false;  // a bounded wait gave up: skip the remaining waits, keep the barriers
   for (int it = 0; it < my_tiles; ++it) {
     const int tile = blockIdx.x + it * gridDim.x;
-    const StagedTarget& tg = p.tgt[target_of_tile(p, tile)];
+    const StagedTarget tg = target_by_index(p, target_of_tile(p, tile));
     const int row0 = (tile - tg.tile_begin) * kTileRows;
     const int odd_shift = tg.aux;
     float o[NCG][4];
@@ -304,9 +329,9 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const __grid_consta
       for (int e = 0; e < 4; ++e) o[g][e] = 0.0f;
 
     const int jbase = it * nchunks, jend = jbase + nchunks;
-    for (; j < jend && !failed; j += 2) {
+    for (; j < jend && !failed; j += SETS) {
       const int c = j - jbase;
-      const int slot = bx + 2 * ring_idx;
+      const int slot = bx + SETS * ring_idx;
       if (!mbar_wait(&full[slot], ring_round & 1, &g_q6k_wait_timeouts)) {
         failed = true;
         break;
@@ -329,13 +354,13 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const __grid_consta
       }
     }
 
-    // The two warps of a row group (even and odd chunks) add their partial sums; the
-    // digit columns of each activation row are then combined through shared memory.
-    if (bx == 1) {
+    // The warps of a row group (one per set) add their partial sums; the digit
+    // columns of each activation row are then combined through shared memory.
+    if (bx > 0) {
 #pragma unroll
       for (int g = 0; g < NCG; ++g)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) xchg[((rg * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
+        for (int e = 0; e < 4; ++e) xchg[((((bx - 1) * p.rgs + rg) * 32 + lane) * NCG + g) * 4 + e] = o[g][e];
     }
     asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
     if (bx == 0) {
@@ -345,7 +370,9 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const __grid_consta
         for (int e = 0; e < 4; ++e) {
           const int col = g * 8 + 2 * tig + (e & 1);
           const int rr = rowA + (e >> 1);  // MMA row + 8 is the odd row of the pair
-          const float v = o[g][e] + xchg[((rg * 32 + lane) * NCG + g) * 4 + e];
+          float v = o[g][e];
+#pragma unroll
+          for (int sx = 0; sx < SETS - 1; ++sx) v += xchg[(((sx * p.rgs + rg) * 32 + lane) * NCG + g) * 4 + e];
           if (col < p.ncols) outbuf[rr * (NCG * 8) + col] = v;
         }
       }
@@ -358,7 +385,10 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const __grid_consta
                   return v;
                 });
   }
-  if (tid == 0 && p.tp.world > 1) tp_cta_leaves(p.tp, epoch, gridDim.x * gridDim.y);
+  if (p.tp.world > 1) {
+    asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");  // every thread's share of the reset is done
+    if (tid == 0) tp_cta_leaves(p.tp, epoch, gridDim.x * gridDim.y, static_cast<unsigned int>(p.m) * p.tgt[0].n);
+  }
 }
 
 // ---- tensor-map cache: the pair of maps depends only on (base, rows, blocks per row, box rows)
@@ -413,26 +443,30 @@ int env_int(const char* name, int fallback) {
   return v ? std::atoi(v) : fallback;
 }
 
-template <int NCG>
+template <int NCG, int SETS>
 int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k, uint64_t caller_split,
-                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st) {
+                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st, double* cost_only) {
   const uint64_t nb = k / kBlockElems;
   const int terms = m <= 2 ? 3 : 2;
   const int ncols = static_cast<int>(m) * terms;
   auto fixed = [&](int rgs, uint64_t per) -> size_t {
-    return per * ncols * (256 + 2 * kGroups) + per * kMaxCols * 4 + rgs * 32 * NCG * 4 * 4 +
+    return per * ncols * (256 + 2 * kGroups) + per * kMaxCols * 4 + (SETS - 1) * rgs * 32 * NCG * 4 * 4 +
            16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128;
   };
   auto stage_bytes = [](int rgs) -> size_t { return static_cast<size_t>(rgs) * 2 * kGroupHalfBytes; };
   auto chunks_of = [](uint64_t per) -> uint64_t { return per / 2 + 1; };
-  static const int regs = kernel_registers(gemv_q6k_staged_kernel<NCG>);
+  static const int regs = kernel_registers(gemv_q6k_staged_kernel<NCG, SETS>);
   uint64_t rows[kMaxGroup];
   for (int i = 0; i < count; ++i) rows[i] = t[i].n;
   GroupPlan plan;
-  if (!plan_group(rows, count, nb, caller_split, 2, regs, 8, fixed, stage_bytes, chunks_of, &plan))
+  if (!plan_group(rows, count, nb, static_cast<int>(m), caller_split, SETS, 0, regs, 8, 0.85, fixed, stage_bytes, chunks_of, &plan))
     return kUnsupportedFeature;
+  if (cost_only != nullptr) {
+    *cost_only = plan.cost;
+    return kOk;
+  }
   const int forced = env_int("TSR_STAGES", 0);
-  if (forced >= 2 && forced <= 16 &&
+  if (forced >= SETS && forced <= 16 &&
       fixed(plan.rgs, nb / plan.split) + forced * stage_bytes(plan.rgs) <= static_cast<size_t>(kMaxSmem)) {
     plan.stages = forced;
     plan.smem = fixed(plan.rgs, nb / plan.split) + forced * stage_bytes(plan.rgs);
@@ -449,7 +483,7 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
   p.ncols = ncols;
   p.debug = env_int("TSR_DEBUG", 0);
   p.rgs = plan.rgs;
-  p.sets = 2;
+  p.sets = SETS;
   p.ntargets = count;
   p.split_mode = caller_split != 0 ? kSplitCaller : kSplitInLaunch;
   Q6KMaps maps{};
@@ -481,19 +515,19 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
     p.tickets = scratch->tickets;
   }
   if (tp != nullptr && tp->world > 1) {
-    if (tiles > tp->tiles_cap || m * t[0].n > tp->capacity || count != 1 || p.split_mode != kSplitInLaunch)
-      return kUnsupportedFeature;
-    // every CTA of the launch must be resident at once: a tile waits for its peers' flags
+    if (m * t[0].n > tp->capacity || count != 1 || p.split_mode != kSplitInLaunch) return kUnsupportedFeature;
+    // every CTA of the launch must be resident at once: a tile waits for its peers' values
     if (static_cast<uint64_t>(plan.grid_x) * plan.split > static_cast<uint64_t>(device_sms()) * plan.occ)
       return kUnsupportedFeature;
     p.tp = *tp;
   } else {
     p.tp.world = 1;
   }
-  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q6k_staged_kernel<NCG>), kMaxSmem)) return rc;
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q6k_staged_kernel<NCG, SETS>), kMaxSmem)) return rc;
   const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.split));
   p.pdl = pdl_allowed_ranges(st, reads, read_bytes, count, writes, write_bytes, count) ? 1 : 0;
-  launch_kernel(gemv_q6k_staged_kernel<NCG>, grid, dim3((2 * plan.rgs + 1) * 32), plan.smem, st, p.pdl != 0, maps, p);
+  launch_kernel(gemv_q6k_staged_kernel<NCG, SETS>, grid, dim3((SETS * plan.rgs + 1) * 32), plan.smem, st, p.pdl != 0,
+                maps, p);
   return check_launch();
 }
 
@@ -510,8 +544,21 @@ int staged_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
   for (int i = 0; i < count; ++i)
     if (t[i].n < 2 || (reinterpret_cast<uintptr_t>(t[i].w) & 15u)) return kUnsupportedFeature;
   const int ncols = static_cast<int>(m) * (m <= 2 ? 3 : 2);
-  if (ncols <= 8) return launch_group_q6k<1>(a, t, count, m, k, caller_split, scratch, tp, st);
-  return launch_group_q6k<2>(a, t, count, m, k, caller_split, scratch, tp, st);
+  // two consumer sets, or four when the model says the warps' own chains of blocks set the time
+  auto run = [&](auto ncg) -> int {
+    constexpr int kNcg = decltype(ncg)::value;
+    double c2 = 0.0, c4 = 0.0;
+    const int r2 = launch_group_q6k<kNcg, 2>(a, t, count, m, k, caller_split, scratch, tp, st, &c2);
+    const int r4 = launch_group_q6k<kNcg, 4>(a, t, count, m, k, caller_split, scratch, tp, st, &c4);
+    const int forced_sets = env_int("TSR_SETS", 0);
+    const bool four = forced_sets == 4 ? r4 == kOk : forced_sets == 2 ? r2 != kOk && r4 == kOk
+                                                                      : r4 == kOk && (r2 != kOk || c4 + 0.3 < c2);
+    if (four) return launch_group_q6k<kNcg, 4>(a, t, count, m, k, caller_split, scratch, tp, st, nullptr);
+    if (r2 != kOk) return r2;
+    return launch_group_q6k<kNcg, 2>(a, t, count, m, k, caller_split, scratch, tp, st, nullptr);
+  };
+  if (ncols <= 8) return run(std::integral_constant<int, 1>{});
+  return run(std::integral_constant<int, 2>{});
 }
 
 int staged_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,

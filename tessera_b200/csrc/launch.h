@@ -111,17 +111,18 @@ bool pdl_allowed(cudaStream_t stream, const void* read_ptr, size_t read_bytes, c
 
 // ---- tensor-parallel tail and multi-target launches ---------------------------
 constexpr int kMaxWorld = 8;
-constexpr int kMaxGroup = 4;  // weight tensors one staged launch can serve
+#ifndef TSR_MAX_GROUP
+#define TSR_MAX_GROUP 4
+#endif
+constexpr int kMaxGroup = TSR_MAX_GROUP;  // weight tensors one staged launch can serve
 // What a kernel needs to finish with the sum over tensor-parallel ranks
 // (tp_device.cuh explains the protocol and the memory behind the pointers).
 struct TpTail {
   int world;  // 1: no collective
   int rank;
-  unsigned int tiles_cap;
-  unsigned long long capacity;     // floats per slot
-  float* slots[kMaxWorld];         // slot memory of every rank (this rank's own included)
-  unsigned int* flags[kMaxWorld];  // flag arrays of every rank
-  unsigned int* state;             // this rank's state words
+  unsigned long long capacity;  // floats per slot
+  float* slots[kMaxWorld];      // slot memory of every rank (this rank's own included)
+  unsigned int* state;          // this rank's state words
 };
 // One weight tensor of a multi-target launch: C[m, n] = A . dq(W)^T.
 struct GroupTarget {

@@ -82,6 +82,41 @@ __device__ __forceinline__ RingUse ring_use(int c, int stages, int groups = 2) {
   return {group + groups * idx, j / owned};
 }
 
+// The producer's walk through the chunks that follow the first `stages` ones (which fill the
+// ring slot by slot): the same (slot, round) sequence as ring_use(j) for j = stages, stages + 1,
+// ..., kept in registers without divisions -- the producer thread sits on the refill path of
+// every stage, and each instruction between a consumer's release and the next copy counts.
+template <int GROUPS>
+struct RingCursor {
+  int idx[GROUPS], rnd[GROUPS], owned[GROUPS];
+  int grp;
+  __device__ __forceinline__ void start_after_fill(int stages) {
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) {
+      owned[g] = (stages - g + GROUPS - 1) / GROUPS;
+      idx[g] = 0;  // every group has used each of its slots once
+      rnd[g] = 1;
+    }
+    grp = stages % GROUPS;
+  }
+  __device__ __forceinline__ RingUse next() {
+    RingUse use{0, 0};
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) {
+      if (grp == g) {
+        use.slot = g + GROUPS * idx[g];
+        use.round = rnd[g];
+        if (++idx[g] == owned[g]) {
+          idx[g] = 0;
+          ++rnd[g];
+        }
+      }
+    }
+    grp = grp + 1 == GROUPS ? 0 : grp + 1;
+    return use;
+  }
+};
+
 // Tiled TMA load of one 3-D box into shared memory; completion is counted in
 // bytes on `bar`.  The innermost coordinate must keep the 16-byte rule
 // (c0 * element size a multiple of 16); every caller passes c0 = 0.

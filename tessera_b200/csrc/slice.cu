@@ -85,27 +85,38 @@ int tsr_slice_shape(int fmt, int kind, uint64_t rows, uint64_t cols, int rank, i
   return tsr::kOk;
 }
 
-int tsr_slice_tensor(int fmt, int kind, uint64_t rows, uint64_t cols, int rank, int world, const void* src,
-                     size_t src_bytes, void* dst, size_t dst_bytes) {
-  Range g;
+int tsr_slice_range(int fmt, uint64_t rows, uint64_t cols, uint64_t row_begin, uint64_t row_end, uint64_t col_begin,
+                    uint64_t col_end, const void* src, size_t src_bytes, void* dst, size_t dst_bytes) {
   Unit unit;
-  if (!src || !dst) return tsr::kInvalidArgument;
-  if (int rc = plan(fmt, kind, rows, cols, rank, world, &g, &unit)) return rc;
-  const uint64_t units = cols / unit.elements;
-  if (tensor_bytes(fmt, rows, units, unit) > src_bytes) return tsr::kInvalidArgument;
-  const uint64_t keep_rows = g.r1 - g.r0, keep_units = g.u1 - g.u0;
-  if (tensor_bytes(fmt, keep_rows, keep_units, unit) > dst_bytes) return tsr::kInvalidArgument;
+  if (!src || !dst || !unit_of(fmt, &unit) || rows == 0 || cols == 0 || cols % unit.elements != 0 ||
+      row_begin >= row_end || row_end > rows || col_begin >= col_end || col_end > cols ||
+      col_begin % unit.elements != 0 || col_end % unit.elements != 0)
+    return tsr::kInvalidArgument;
+  const uint64_t units = cols / unit.elements, u0 = col_begin / unit.elements, u1 = col_end / unit.elements;
+  const uint64_t keep_rows = row_end - row_begin, keep_units = u1 - u0;
+  if (tensor_bytes(fmt, rows, units, unit) > src_bytes || tensor_bytes(fmt, keep_rows, keep_units, unit) > dst_bytes)
+    return tsr::kInvalidArgument;
   const auto* s = static_cast<const unsigned char*>(src);
   auto* d = static_cast<unsigned char*>(dst);
   const uint64_t row_bytes = units * unit.bytes, kept = keep_units * unit.bytes;
   for (uint64_t r = 0; r < keep_rows; ++r)
-    std::memcpy(d + r * kept, s + (g.r0 + r) * row_bytes + g.u0 * unit.bytes, kept);
-  if (fmt == 2) {  // the E8M0 side table, one byte per unit, sliced the same way
+    std::memcpy(d + r * kept, s + (row_begin + r) * row_bytes + u0 * unit.bytes, kept);
+  if (fmt == 2) {
     const unsigned char* ss = s + rows * row_bytes;
     unsigned char* ds = d + keep_rows * kept;
-    for (uint64_t r = 0; r < keep_rows; ++r) std::memcpy(ds + r * keep_units, ss + (g.r0 + r) * units + g.u0, keep_units);
+    for (uint64_t r = 0; r < keep_rows; ++r)
+      std::memcpy(ds + r * keep_units, ss + (row_begin + r) * units + u0, keep_units);
   }
   return tsr::kOk;
+}
+
+int tsr_slice_tensor(int fmt, int kind, uint64_t rows, uint64_t cols, int rank, int world, const void* src,
+                     size_t src_bytes, void* dst, size_t dst_bytes) {
+  Range g;
+  Unit unit;
+  if (int rc = plan(fmt, kind, rows, cols, rank, world, &g, &unit)) return rc;
+  return tsr_slice_range(fmt, rows, cols, g.r0, g.r1, g.u0 * unit.elements, g.u1 * unit.elements, src, src_bytes, dst,
+                         dst_bytes);
 }
 
 }  // extern "C"

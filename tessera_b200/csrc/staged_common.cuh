@@ -5,9 +5,11 @@
 // launch plan (tile height, CTAs per SM, ring depth) that all three use.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdio>
 #include <cstdlib>
 
 #include "codec.cuh"
@@ -58,13 +60,31 @@ struct StagedParams {
   TpTail tp;  // sum over tensor-parallel ranks after the local sum (world 1: none)
 };
 
-// Which target a tile of the launch's tile list belongs to.
+// Which target a tile of the launch's tile list belongs to, and that target by value.
+// The kernel parameters are read with constant indices only (a run-time index into a
+// parameter array would make the compiler keep the whole array in registers or copy it
+// to local memory), hence the unrolled compares.
 __device__ __forceinline__ int target_of_tile(const StagedParams& p, int tile) {
   int g = 0;
 #pragma unroll
   for (int i = 1; i < kMaxGroup; ++i)
     if (i < p.ntargets && tile >= p.tgt[i].tile_begin) g = i;
   return g;
+}
+__device__ __forceinline__ StagedTarget target_by_index(const StagedParams& p, int g) {
+  StagedTarget t = p.tgt[0];
+#pragma unroll
+  for (int i = 1; i < kMaxGroup; ++i)
+    if (g == i) t = p.tgt[i];
+  return t;
+}
+// Address of element g of an array of kMaxGroup tensor maps in the kernel parameters.
+__device__ __forceinline__ const CUtensorMap* map_by_index(const CUtensorMap* maps, int g) {
+  const CUtensorMap* m = &maps[0];
+#pragma unroll
+  for (int i = 1; i < kMaxGroup; ++i)
+    if (g == i) m = &maps[i];
+  return m;
 }
 
 __device__ __forceinline__ uint4 lds128(const unsigned char* p) {
@@ -294,16 +314,18 @@ __device__ __forceinline__ void finish_tile(const StagedParams& p, const StagedT
       const int idx = tid + u * nthreads;
       if (idx < items) __stcg(mine + idx, v[u]);
     }
-    __threadfence();
+    // The CTA's stores are ordered before the ticket by the barrier (CTA scope) and the
+    // ticket's release (GPU scope); the last CTA's acquire on the ticket and its barrier
+    // order the other chunks' stores before the loads below.  No thread needs a full fence.
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     if (tid == 0) {
-      const unsigned int t = atomicAdd(p.tickets + tile, 1u);
+      unsigned int t;
+      asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(t) : "l"(p.tickets + tile) : "memory");
       *s_flag = (t == static_cast<unsigned int>(nsplit - 1)) ? 1u : 0u;
       if (*s_flag) p.tickets[tile] = 0u;  // every chunk has arrived: ready for the next launch
     }
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     if (*s_flag == 0u) return;
-    __threadfence();
     // chunk order, starting from zero: the order of the reference's gemm_vec_reduce
     const float* base = p.part + static_cast<size_t>(tile) * tile_floats;
 #pragma unroll
@@ -317,19 +339,17 @@ __device__ __forceinline__ void finish_tile(const StagedParams& p, const StagedT
     }
   }
   if (p.tp.world > 1) {
+    // every thread sends its own values to all ranks, then waits for the same elements of
+    // all ranks in its own slots: no barrier, no flag (tp_device.cuh)
     const size_t mine = tp_slot_offset(p.tp, epoch, p.tp.rank);
 #pragma unroll
     for (int u = 0; u < kMaxPer; ++u) {
       const int idx = tid + u * nthreads;
       if (idx < items) {
         const int i = idx / tile_rows, rr = idx - i * tile_rows;
-        if (row0 + rr < tg.n) {
-          const size_t e = static_cast<size_t>(i) * tg.n + row0 + rr;
-          for (int r = 0; r < p.tp.world; ++r) p.tp.slots[r][mine + e] = v[u];
-        }
+        if (row0 + rr < tg.n) tp_push(p.tp, mine + static_cast<size_t>(i) * tg.n + row0 + rr, v[u]);
       }
     }
-    tp_publish_and_wait(p.tp, epoch, tile, tid, 1, nthreads);
 #pragma unroll
     for (int u = 0; u < kMaxPer; ++u) {
       const int idx = tid + u * nthreads;
@@ -337,7 +357,7 @@ __device__ __forceinline__ void finish_tile(const StagedParams& p, const StagedT
         const int i = idx / tile_rows, rr = idx - i * tile_rows;
         if (row0 + rr < tg.n) {
           const size_t e = static_cast<size_t>(i) * tg.n + row0 + rr;
-          tg.c[e] = tp_rank_order_sum(p.tp, epoch, e);
+          tg.c[e] = tp_wait_sum(p.tp, epoch, e);
         }
       }
     }
@@ -450,15 +470,23 @@ inline int env_plan_int(const char* name, int fallback) {
 //   stage_bytes(rgs)  one ring stage
 //   nchunks(per)      ring stages one tile of `per` blocks needs
 template <typename FixedFn, typename StageFn, typename ChunksFn>
-inline bool plan_group(const uint64_t* n, int count, uint64_t nb, uint64_t fixed_split, int sets,
-                       int regs_per_thread, int max_want, FixedFn fixed, StageFn stage_bytes, ChunksFn nchunks,
-                       GroupPlan* out) {
+inline bool plan_group(const uint64_t* n, int count, uint64_t nb, int m, uint64_t fixed_split, int sets,
+                       int fixed_rgs, int regs_per_thread, int max_want, double block_us, FixedFn fixed,
+                       StageFn stage_bytes, ChunksFn nchunks, GroupPlan* out) {
   const int sms = device_sms();
-  // per 16 rows x 1 block on a busy SM; per block of one warp's own chunks; per CTA
-  const double kUnitUs = 0.04, kWarpBlockUs = 0.5, kPrefixUs = 3.0, kStageBlockUs = 0.02, kTicketUs = 1.2;
+  // Measured on B200 (Q4_K, m = 1): a busy SM gets through one 16-row x 256-column block in
+  // about 0.053 us whatever the tiling; one warp needs `block_us` (0.5 us Q4_K) for each block
+  // of its own chain; a launch costs about 2.6 us before and after its weights, plus the
+  // activation staging (0.25 us per round of one block per consumer warp); a split inside the
+  // launch pays a ticket round trip and a pass over the partial sums at the very end of every
+  // tile, where nothing overlaps it (measured 3-4 us: no cheaper than a reduce launch, so it
+  // only wins where it shortens a long chain, as for Q6_K rows of 68 blocks).
+  const double kUnitUs = 0.053 * (block_us / 0.5), kPrefixUs = 2.6, kStageRoundUs = 0.25;
+  const double kTicketUs = 3.5, kTicketTileUs = 1.5, kWaveUs = 2.0;
   const int ring_max = env_plan_int("TSR_RING_MAX", max_want);
   const int force_rgs = env_plan_int("TSR_RGS", 0), force_split = env_plan_int("TSR_SPLIT", 0);
   const int force_grid = env_plan_int("TSR_GRID", 0), force_occ = env_plan_int("TSR_OCC", 0);
+  const int force_persist = env_plan_int("TSR_PERSIST", -1);
   double best = 1e30;
   bool found = false;
   for (uint64_t split = 1; split <= 8 && split <= nb; ++split) {
@@ -468,53 +496,71 @@ inline bool plan_group(const uint64_t* n, int count, uint64_t nb, uint64_t fixed
     const uint64_t per = nb / split;
     const uint64_t chunks_per_tile = nchunks(per);
     for (int rgs = 4; rgs >= 1; --rgs) {
-      if (force_rgs >= 1 && force_rgs <= 4 && rgs != force_rgs) continue;
+      if (fixed_rgs != 0 && rgs != fixed_rgs) continue;
+      if (fixed_rgs == 0 && force_rgs >= 1 && force_rgs <= 4 && rgs != force_rgs) continue;
       const uint64_t th = 16u * rgs;
       uint64_t tiles = 0;
       for (int i = 0; i < count; ++i) tiles += (n[i] + th - 1) / th;
       const size_t fx = fixed(rgs, per), sb = stage_bytes(rgs);
+      const int warps = sets * rgs;
       for (int occ = 1; occ <= 4; ++occ) {
         if (force_occ > 0 && occ != force_occ) continue;
-        if (occ > 1 && occ * (sets * rgs + 1) * 32 * regs_per_thread > 65536) break;  // register file
+        if (occ > 1 && occ * (warps + 1) * 32 * regs_per_thread > 65536) break;  // register file
         if (occ > 1 && sets == 4) break;  // the four-set kernels are built for one CTA per SM
         const size_t avail = static_cast<size_t>(kMaxSmem) / occ;
         const size_t reserve = occ > 1 ? 1024 : 0;  // per-CTA reservation of the hardware
         if (avail < fx + reserve + sets * sb) break;  // every consumer set owns at least one slot
         const uint64_t slots = static_cast<uint64_t>(sms) * occ;
-        uint64_t grid_x = slots / split;
-        if (grid_x == 0) grid_x = 1;
-        if (grid_x > tiles) grid_x = tiles;
-        if (force_grid > 0) grid_x = static_cast<uint64_t>(force_grid) < tiles ? force_grid : tiles;
-        const uint64_t tiles_per_cta = (tiles + grid_x - 1) / grid_x;
-        const uint64_t total_chunks = tiles_per_cta * chunks_per_tile;
-        int depth = static_cast<int>((avail - reserve - fx) / sb);
-        int want = static_cast<int>(total_chunks < static_cast<uint64_t>(ring_max) ? total_chunks : ring_max);
-        if (want < sets) want = sets;
-        if (depth > want) depth = want;
-        const uint64_t ctas = grid_x * split;
-        const uint64_t ctas_per_sm = (ctas + sms - 1) / sms;
-        // an SM works through its CTAs' tiles at a fixed rate, but a warp cannot go faster
-        // than its own share of the blocks (one consumer set's) one after the other
-        const double throughput = static_cast<double>(ctas_per_sm * tiles_per_cta * rgs * per) * kUnitUs;
-        const double latency = static_cast<double>(tiles_per_cta) * (static_cast<double>(per) / sets) * kWarpBlockUs;
-        double cost = kPrefixUs + kStageBlockUs * per + (throughput > latency ? throughput : latency) +
-                      (split > 1 && fixed_split == 0 ? kTicketUs : 0.0);
-        if (depth < sets + 1 && total_chunks > static_cast<uint64_t>(sets)) cost *= 1.1;  // a shallow ring stalls on HBM latency
-        if (cost < best - 1e-9) {
-          best = cost;
-          out->rgs = rgs;
-          out->stages = depth;
-          out->sets = sets;
-          out->split = static_cast<int>(split);
-          out->grid_x = static_cast<int>(grid_x);
-          out->occ = occ;
-          out->smem = fx + static_cast<size_t>(depth) * sb;
-          out->cost = cost;
-          found = true;
+        // a grid the SMs hold at once, each CTA working through several tiles -- or, when that
+        // would be at most two rounds, one CTA per tile (no tile loop, but a second prefix)
+        for (int persist = 1; persist >= 0; --persist) {
+          if (force_persist >= 0 && persist != force_persist) continue;
+          uint64_t grid_x = slots / split;
+          if (grid_x == 0) grid_x = 1;
+          if (grid_x > tiles) grid_x = tiles;
+          if (!persist) {
+            if (grid_x == tiles || tiles * split > 2 * slots) continue;  // same plan, or too many rounds
+            grid_x = tiles;
+          }
+          if (force_grid > 0) grid_x = static_cast<uint64_t>(force_grid) < tiles ? force_grid : tiles;
+          const uint64_t tiles_per_cta = (tiles + grid_x - 1) / grid_x;
+          const uint64_t total_chunks = tiles_per_cta * chunks_per_tile;
+          int depth = static_cast<int>((avail - reserve - fx) / sb);
+          int want = static_cast<int>(total_chunks < static_cast<uint64_t>(ring_max) ? total_chunks : ring_max);
+          if (want < sets) want = sets;
+          if (depth > want) depth = want;
+          const uint64_t ctas = grid_x * split;
+          const uint64_t waves = (ctas + slots - 1) / slots;
+          const uint64_t ctas_per_sm = (ctas + sms - 1) / sms;
+          // an SM works through its CTAs' tiles at a fixed rate, but a warp cannot go faster
+          // than its own share of the blocks (one consumer set's) one after the other
+          const double throughput = static_cast<double>(ctas_per_sm * tiles_per_cta * rgs * per) * kUnitUs;
+          const double chain = static_cast<double>(waves * tiles_per_cta) * ((per + sets - 1) / sets) * block_us;
+          const double staging = kStageRoundUs * static_cast<double>((m * per + warps - 1) / warps);
+          double cost = kPrefixUs + staging + (throughput > chain ? throughput : chain) + (waves - 1) * kWaveUs +
+                        (sets == 4 ? 0.4 : 0.0);
+          if (split > 1 && fixed_split == 0) cost += kTicketUs + kTicketTileUs * static_cast<double>(tiles_per_cta);
+          if (depth < sets + 1 && total_chunks > static_cast<uint64_t>(sets)) cost *= 1.1;  // a shallow ring stalls on HBM latency
+          if (cost < best - 1e-9) {
+            best = cost;
+            out->rgs = rgs;
+            out->stages = depth;
+            out->sets = sets;
+            out->split = static_cast<int>(split);
+            out->grid_x = static_cast<int>(grid_x);
+            out->occ = occ;
+            out->smem = fx + static_cast<size_t>(depth) * sb;
+            out->cost = cost;
+            found = true;
+          }
         }
       }
     }
   }
+  if (found && env_plan_int("TSR_PLAN_DEBUG", 0))
+    std::fprintf(stderr, "plan: targets %d nb %llu sets %d -> rgs %d occ %d split %d grid_x %d stages %d smem %zu cost %.1f us\n",
+                 count, static_cast<unsigned long long>(nb), sets, out->rgs, out->occ, out->split, out->grid_x,
+                 out->stages, out->smem, out->cost);
   return found;
 }
 

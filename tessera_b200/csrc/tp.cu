@@ -20,64 +20,34 @@ namespace {
 
 using namespace tsr;
 
-constexpr int kChunkFloats = 1024;  // tile of the flat all-reduce: 256 threads x float4
+constexpr int kChunkFloats = 1024;  // elements per CTA: 256 threads x 4
 
-// Sum over ranks of an [m][n] matrix (n a multiple of 4), one CTA per tile of
-// `tile_rows` columns of it (tile_rows a multiple of 4): tile t holds elements
-// i*n + t*tile_rows + r for all i < m, r < tile_rows.  The flat all-reduce of
-// `count` floats is the case m = 1, n = count, tile_rows = 1024.  `src` holds
-// `split` regions of m*n floats that are added in region order first.
+// Sum over ranks of `count` floats: thread t of CTA b owns elements 4 * (256 b + t) .. + 3.
+// `src` holds `split` regions of `count` floats that are added in region order first
+// (exactly as gemm_vec_reduce adds them, starting from 0.0f).
 __global__ void __launch_bounds__(256)
-tp_allreduce_kernel(const float* src, int split, float* dst, int m, size_t n, int tile_rows, const TpTail tp) {
+tp_allreduce_kernel(const float* src, int split, float* dst, size_t count, const TpTail tp) {
   __shared__ unsigned int s_epoch;
-  const int tile = blockIdx.x;
   if (threadIdx.x == 0) s_epoch = tp_call_epoch(tp);
   __syncthreads();
   const unsigned int epoch = s_epoch;
-  const int row_quads = tile_rows >> 2, quads = m * row_quads;
-  const size_t region = static_cast<size_t>(m) * n;
-  const size_t mine_off = tp_slot_offset(tp, epoch, tp.rank);
-  for (int q = threadIdx.x; q < quads; q += 256) {
-    const int i = q / row_quads, rq = q - i * row_quads;
-    const size_t row = static_cast<size_t>(tile) * tile_rows + rq * 4;
-    if (row >= n) continue;
-    const size_t e = static_cast<size_t>(i) * n + row;
-    float4 mine;
-    if (split == 1) {
-      mine = *reinterpret_cast<const float4*>(src + e);
-    } else {
-      // the split-K partial regions of a row-parallel projection, added in region
-      // order exactly as gemm_vec_reduce adds them (starting from 0.0f)
-      mine = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int s = 0; s < split; ++s) {
-        const float4 v = *reinterpret_cast<const float4*>(src + static_cast<size_t>(s) * region + e);
-        mine.x += v.x;
-        mine.y += v.y;
-        mine.z += v.z;
-        mine.w += v.w;
+  const size_t gtid = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
+  tp_reset_previous(tp, epoch, gtid, static_cast<size_t>(gridDim.x) * 256);
+  const size_t e0 = gtid * 4;
+  if (e0 < count) {
+    float mine[4] = {0.f, 0.f, 0.f, 0.f};
+    const int lanes = count - e0 < 4 ? static_cast<int>(count - e0) : 4;
+    for (int s = 0; s < split; ++s)
+      for (int j = 0; j < lanes; ++j) {
+        const float v = src[static_cast<size_t>(s) * count + e0 + j];
+        mine[j] = split == 1 ? v : mine[j] + v;
       }
-    }
-    // push: my partial into slot `rank` of every rank (my own included)
-    for (int r = 0; r < tp.world; ++r) *reinterpret_cast<float4*>(tp.slots[r] + mine_off + e) = mine;
+    const size_t off = tp_slot_offset(tp, epoch, tp.rank) + e0;
+    for (int j = 0; j < lanes; ++j) tp_push(tp, off + j, mine[j]);
+    for (int j = 0; j < lanes; ++j) dst[e0 + j] = tp_wait_sum(tp, epoch, e0 + j);
   }
-  tp_publish_and_wait(tp, epoch, tile, threadIdx.x, 0, 256);
-  const float* base = tp.slots[tp.rank] + tp_slot_offset(tp, epoch, 0);
-  for (int q = threadIdx.x; q < quads; q += 256) {
-    const int i = q / row_quads, rq = q - i * row_quads;
-    const size_t row = static_cast<size_t>(tile) * tile_rows + rq * 4;
-    if (row >= n) continue;
-    const size_t e = static_cast<size_t>(i) * n + row;
-    float4 acc = __ldcg(reinterpret_cast<const float4*>(base + e));
-    for (int r = 1; r < tp.world; ++r) {
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(base + static_cast<size_t>(r) * tp.capacity + e));
-      acc.x += v.x;
-      acc.y += v.y;
-      acc.z += v.z;
-      acc.w += v.w;
-    }
-    *reinterpret_cast<float4*>(dst + e) = acc;
-  }
-  if (threadIdx.x == 0) tp_cta_leaves(tp, epoch, gridDim.x);
+  __syncthreads();
+  if (threadIdx.x == 0) tp_cta_leaves(tp, epoch, gridDim.x, static_cast<unsigned int>(count));
 }
 
 }  // namespace
@@ -85,7 +55,6 @@ tp_allreduce_kernel(const float* src, int split, float* dst, int m, size_t n, in
 struct tsr_tp_comm {
   int device = 0, rank = 0, world = 1;
   size_t capacity = 0;  // floats per slot
-  unsigned int tiles_cap = 0;
   unsigned char* block = nullptr;  // local exchange memory
   size_t block_bytes = 0;
   void* peer_block[kMaxWorld] = {};
@@ -93,12 +62,9 @@ struct tsr_tp_comm {
   bool attached[kMaxWorld] = {};
 
   static constexpr size_t kPrefixBytes = (kTpHeaderWords + kTpStateWords) * 4;
-  size_t slots_bytes() const { return 2ull * world * capacity * 4; }
+  size_t slots_bytes() const { return 3ull * world * capacity * 4; }
   unsigned int* state(void* base) const { return reinterpret_cast<unsigned int*>(base) + kTpHeaderWords; }
   float* slots(void* base) const { return reinterpret_cast<float*>(static_cast<unsigned char*>(base) + kPrefixBytes); }
-  unsigned int* flags(void* base) const {
-    return reinterpret_cast<unsigned int*>(static_cast<unsigned char*>(base) + kPrefixBytes + slots_bytes());
-  }
   // Every rank computes its peers' offsets from its own capacity and world, so a
   // peer created with other values must be refused: its header says what it holds.
   int check_peer_header(const void* peer) const {
@@ -107,20 +73,17 @@ struct tsr_tp_comm {
       cudaGetLastError();
       return tsr::kDeviceError;
     }
-    if (h[0] != kTpMagic || h[1] != static_cast<unsigned int>(world) || h[2] != static_cast<unsigned int>(capacity) ||
-        h[3] != tiles_cap)
+    if (h[0] != kTpMagic || h[1] != static_cast<unsigned int>(world) || h[2] != static_cast<unsigned int>(capacity))
       return tsr::kInvalidArgument;
     return tsr::kOk;
   }
   bool tail(TpTail* out) const {
     out->world = world;
     out->rank = rank;
-    out->tiles_cap = tiles_cap;
     out->capacity = capacity;
     for (int p = 0; p < world; ++p) {
       if (!attached[p]) return false;
       out->slots[p] = slots(peer_block[p]);
-      out->flags[p] = flags(peer_block[p]);
     }
     out->state = state(block);
     return true;
@@ -137,31 +100,24 @@ int tp_device_of(const tsr_tp_comm* comm) { return comm ? comm->device : -1; }
 }  // namespace tsr
 
 namespace {
-int launch_tiled(tsr_tp_comm* c, const float* src, uint64_t split, float* data, uint64_t m, uint64_t n,
-                 uint64_t tile_rows, cudaStream_t stream) {
-  if (!c || !src || !data || m == 0 || n == 0 || m > 65535 || m * n > c->capacity || n % 4 != 0 || tile_rows == 0 ||
-      tile_rows % 4 != 0 || split == 0 || split > 65535 || (reinterpret_cast<uintptr_t>(data) & 15u) ||
-      (reinterpret_cast<uintptr_t>(src) & 15u))
+int launch_allreduce(tsr_tp_comm* c, const float* src, uint64_t split, float* data, uint64_t count, void* stream) {
+  if (!c || !src || !data || count == 0 || count > c->capacity || split == 0 || split > 65535 ||
+      (reinterpret_cast<uintptr_t>(data) & 3u) || (reinterpret_cast<uintptr_t>(src) & 3u))
     return tsr::kInvalidArgument;
-  const uint64_t tiles = (n + tile_rows - 1) / tile_rows;
-  if (tiles > c->tiles_cap) return tsr::kInvalidArgument;
   // The current device is per host thread; one thread may drive several ranks.
   if (cudaSetDevice(c->device) != cudaSuccess) return tsr::kDeviceError;
   TpTail tail{};
   if (!c->tail(&tail)) return tsr::kInvalidArgument;
-  tp_allreduce_kernel<<<static_cast<unsigned>(tiles), 256, 0, stream>>>(src, static_cast<int>(split), data,
-                                                                        static_cast<int>(m), n,
-                                                                        static_cast<int>(tile_rows), tail);
+  const unsigned grid = static_cast<unsigned>((count + kChunkFloats - 1) / kChunkFloats);
+  tp_allreduce_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(src, static_cast<int>(split), data, count,
+                                                                          tail);
   return tsr::check_launch();
-}
-int launch_allreduce(tsr_tp_comm* c, const float* src, uint64_t split, float* data, uint64_t count, void* stream) {
-  return launch_tiled(c, src, split, data, 1, count, kChunkFloats, static_cast<cudaStream_t>(stream));
 }
 }  // namespace
 
 namespace tsr {
-int tp_allreduce_tiled(tsr_tp_comm* comm, float* data, uint64_t m, uint64_t n, uint64_t tile_rows, cudaStream_t st) {
-  return launch_tiled(comm, data, 1, data, m, n, tile_rows, st);
+int tp_allreduce_matrix(tsr_tp_comm* comm, float* data, uint64_t m, uint64_t n, cudaStream_t st) {
+  return launch_allreduce(comm, data, 1, data, m * n, st);
 }
 }  // namespace tsr
 
@@ -180,16 +136,15 @@ int tsr_tp_create(int device, int rank, int world, uint64_t max_floats, tsr_tp_c
     delete c;
     return tsr::kInvalidArgument;
   }
-  c->tiles_cap = static_cast<unsigned int>(c->capacity / 16);  // a GEMV tile has at least 16 outputs
-  c->block_bytes = tsr_tp_comm::kPrefixBytes + c->slots_bytes() + static_cast<size_t>(world) * c->tiles_cap * 4;
+  c->block_bytes = tsr_tp_comm::kPrefixBytes + c->slots_bytes();
   if (cudaMalloc(&c->block, c->block_bytes) != cudaSuccess) {
     cudaGetLastError();
     delete c;
     return tsr::kOutOfMemory;
   }
-  cudaMemset(c->block, 0, c->block_bytes);
-  const unsigned int header[4] = {kTpMagic, static_cast<unsigned int>(world), static_cast<unsigned int>(c->capacity),
-                                  c->tiles_cap};
+  cudaMemset(c->block, 0, tsr_tp_comm::kPrefixBytes);
+  cudaMemset(c->block + tsr_tp_comm::kPrefixBytes, 0xFF, c->slots_bytes());  // every slot word: "not arrived"
+  const unsigned int header[4] = {kTpMagic, static_cast<unsigned int>(world), static_cast<unsigned int>(c->capacity), 0u};
   cudaMemcpy(c->block, header, sizeof(header), cudaMemcpyHostToDevice);
   cudaDeviceSynchronize();
   c->peer_block[rank] = c->block;

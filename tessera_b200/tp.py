@@ -95,6 +95,19 @@ def slice_tensor(fmt: int, kind: int, rows: int, cols: int, rank: int, world: in
     return dst
 
 
+def slice_range(fmt: int, rows: int, cols: int, row_begin: int, row_end: int, col_begin: int, col_end: int,
+                src: np.ndarray) -> np.ndarray:
+    """Rows [row_begin, row_end) and columns [col_begin, col_end) of a packed weight tensor
+    (tsr_slice_range): shard maps the kind rule cannot express."""
+    lib = capi.load_library()
+    src = np.ascontiguousarray(src.reshape(-1).view(np.uint8))
+    unit, ubytes = {FMT_Q4K: (256, 144), FMT_Q6K: (256, 210), FMT_MXFP4: (32, 17), FMT_FP8: (1, 1)}[fmt]
+    dst = np.empty((row_end - row_begin) * ((col_end - col_begin) // unit) * ubytes, dtype=np.uint8)
+    capi.check(lib.tsr_slice_range(fmt, rows, cols, row_begin, row_end, col_begin, col_end, src.ctypes.data,
+                                   src.nbytes, dst.ctypes.data, dst.nbytes), "tsr_slice_range")
+    return dst
+
+
 def rank_order_sum(partials):
     """What every rank must end with: ((p0 + p1) + p2) + ... in fp32."""
     acc = np.array(partials[0], dtype=np.float32, copy=True)

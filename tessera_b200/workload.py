@@ -77,18 +77,32 @@ def decode_projections() -> List[Projection]:
     return out
 
 
+def row_blocks(dtype: str, blocks: int, rank: int, world: int):
+    """Block range [b0, b1) of a row-parallel projection's k on this rank: blocks*rank/world
+    rounded down, the rule of the library's slicer (tsr_slice_shape) -- counted in units of
+    four blocks for Q6_K where the count allows it, because rows of 210-byte blocks are 8-byte
+    aligned (what the staged Q6_K kernel needs) only when they hold a multiple of four."""
+    unit = 4 if (dtype == "q6k" and blocks % 4 == 0 and blocks // 4 >= world) else 1
+    units = blocks // unit
+    return unit * (units * rank // world), unit * (units * (rank + 1) // world)
+
+
 def shard(p: Projection, rank: int, world: int):
-    """(n_local, k_local) of this rank, by the rule of the library's slicer
-    (tsr_slice_shape).  Column: rows [n*rank/world, n*(rank+1)/world).  Row: the
-    256-element blocks [nb*rank/world, nb*(rank+1)/world) of the nb blocks of a
-    row, so a block count that does not divide evenly (68 blocks on 8 ranks)
-    gives ranks of 8 and 9 blocks."""
+    """(n_local, k_local) of this rank.  Column: rows [n*rank/world, n*(rank+1)/world), except
+    ffn_gate / ffn_up, whose rows are the k range of the layer's ffn_down on this rank (the
+    rank's slice of the FFN activation is produced where it is consumed).  Row: whole
+    256-element blocks, see row_blocks: 68 blocks on 8 ranks gives ranks of 8 and 9 blocks
+    (Q4_K) or of 8 and 12 (Q6_K)."""
     if world == 1:
         return p.n, p.k
+    if p.name in ("ffn_gate", "ffn_up"):
+        down = "q6k" if p.layer % 2 == 1 else "q4k"
+        b0, b1 = row_blocks(down, FFN // 256, rank, world)
+        return (b1 - b0) * 256, p.k
     if p.kind == COLUMN:
         return p.n * (rank + 1) // world - p.n * rank // world, p.k
-    blocks = p.k // 256
-    return p.n, (blocks * (rank + 1) // world - blocks * rank // world) * 256
+    b0, b1 = row_blocks(p.dtype, p.k // 256, rank, world)
+    return p.n, (b1 - b0) * 256
 
 
 def total_weight_bytes(rank: int = 0, world: int = 1) -> int:

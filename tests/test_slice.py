@@ -102,3 +102,23 @@ def test_bad_arguments_are_refused():
                                 dst.nbytes) == capi.StatusCode.InvalidArgument
     assert lib.tsr_slice_tensor(FMT_Q4K, COLUMN, 4, 512, 0, 2, w.ctypes.data, 100, dst.ctypes.data,
                                 dst.nbytes) == capi.StatusCode.InvalidArgument
+
+
+def test_explicit_ranges_cut_the_same_bytes():
+    from tessera_b200.tp import slice_range
+    n, k = 12, 17408
+    w = make(FMT_Q6K, n, k, seed=10)
+    full = w.reshape(n, k // 256, 210)
+    # a Q6_K row split in units of four blocks: every rank's rows stay 8-byte aligned
+    got = slice_range(FMT_Q6K, n, k, 0, n, 56 * 256, 68 * 256, w).reshape(n, 12, 210)
+    assert np.array_equal(got, full[:, 56:68])
+    # a column split that follows an uneven k range of the projection it feeds
+    got = slice_range(FMT_Q6K, n, k, 3, 10, 0, k, w).reshape(7, k // 256, 210)
+    assert np.array_equal(got, full[3:10])
+    wm = make(FMT_MXFP4, n, 1024, seed=11)
+    got = slice_range(FMT_MXFP4, n, 1024, 2, 6, 256, 768, wm)
+    blob, sc = wm[: n * 512].reshape(n, 512), wm[n * 512:].reshape(n, 32)
+    assert np.array_equal(got[: 4 * 256].reshape(4, 256), blob[2:6, 128:384])
+    assert np.array_equal(got[4 * 256:].reshape(4, 16), sc[2:6, 8:24])
+    with pytest.raises(capi.StatusError):
+        slice_range(FMT_Q6K, n, k, 0, n, 100, 356, w)   # not on block boundaries

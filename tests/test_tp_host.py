@@ -34,9 +34,20 @@ def test_shards_cover_every_projection_at_every_world_size():
         for r in range(world):
             total += workload.total_weight_bytes(r, world)
         assert total == workload.total_weight_bytes(0, 1)
-    # the 17408-wide down projection has 68 blocks: at 8 ranks four take 9 and four take 8
-    down = next(p for p in workload.decode_projections() if p.name == "ffn_down")
-    assert sorted(workload.shard(down, r, 8)[1] // 256 for r in range(8)) == [8] * 4 + [9] * 4
+    # the 17408-wide down projection has 68 blocks: at 8 ranks four take 9 and four take 8 (Q4_K);
+    # a Q6_K one is cut in units of four blocks (8-byte aligned rows): seven ranks of 8, one of 12
+    downs = [p for p in workload.decode_projections() if p.name == "ffn_down"]
+    q4 = next(p for p in downs if p.dtype == "q4k")
+    q6 = next(p for p in downs if p.dtype == "q6k")
+    assert sorted(workload.shard(q4, r, 8)[1] // 256 for r in range(8)) == [8] * 4 + [9] * 4
+    assert sorted(workload.shard(q6, r, 8)[1] // 256 for r in range(8)) == [8] * 7 + [12]
+    # gate and up of a layer produce exactly the slice of the FFN activation its down projection reads
+    for world in (2, 4, 8):
+        for layer in (0, 1):
+            gate = next(p for p in workload.decode_projections() if p.name == "ffn_gate" and p.layer == layer)
+            down = next(p for p in downs if p.layer == layer)
+            for r in range(world):
+                assert workload.shard(gate, r, world)[0] == workload.shard(down, r, world)[1]
 
 
 def test_slice_helpers_match_column_ranges():
