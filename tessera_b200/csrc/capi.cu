@@ -62,6 +62,7 @@ void publish_error_word(int device) {
   tsr::staged_q6k_set_error_word(word);
   tsr::staged_f16_set_error_word(word);
   tsr::umma_set_error_word(word);
+  tsr::umma_f8_set_error_word(word);
   done[device] = true;
 }
 
@@ -429,11 +430,12 @@ int tsr_synchronize(tsr_context* ctx) {
   const unsigned int* word = host_error_word();
   const unsigned int raised = word ? *reinterpret_cast<const volatile unsigned int*>(word) : 0u;
   if (word == nullptr || raised != 0u) {
-    unsigned int timeouts = 0, umma = 0, q6k = 0, f16 = 0;
+    unsigned int timeouts = 0, umma = 0, q6k = 0, f16 = 0, f8 = 0;
     tsr::umma_wait_timeouts(&umma);
+    tsr::umma_f8_wait_timeouts(&f8);
     tsr::staged_q6k_wait_timeouts(&q6k);
     tsr::staged_f16_wait_timeouts(&f16);
-    if (tsr::staged_wait_timeouts(&timeouts) == tsr::kOk && (timeouts += umma + q6k + f16) != ctx->seen_timeouts) {
+    if (tsr::staged_wait_timeouts(&timeouts) == tsr::kOk && (timeouts += umma + q6k + f16 + f8) != ctx->seen_timeouts) {
       ctx->seen_timeouts = timeouts;
       ctx->error = "a staged kernel gave up waiting for a TMA copy";
       return tsr::kDeviceError;

@@ -129,6 +129,11 @@ int tsr_gemm_fp8(const float* a, const void* w, const float* s, float* c, uint64
   if (!a || !w || !s || !c || !fits_int(m) || !fits_int(n) || !fits_int(k)) return kInvalidArgument;
   if (!aligned16(a) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
   const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (m >= 2) {
+    // batches: the weights go from HBM to the tensor core without a thread touching them
+    const int rt = umma_f8_gemm(a, w, s, c, m, n, k, st);
+    if (rt != kUnsupportedFeature) return rt;
+  }
   const int rc = m > kStagedRows ? staged_in_chunks(m, n, [&](uint64_t i0, uint64_t rows) {
     return staged_gemm_fp8(a + i0 * k, w, s, c + i0 * n, rows, n, k, st);
   }) : staged_gemm_fp8(a, w, s, c, m, n, k, st);

@@ -646,7 +646,11 @@ int ring_maps(int fmt, const void* w, uint64_t n, uint64_t k, RingMaps* out) {
 // Returns null when the stream is being captured and no large enough buffer exists yet:
 // the tiles then convert the activations themselves.  The memory comes from the
 // stream-ordered pool, so growing it never synchronises the device.
-unsigned char* activation_scratch(cudaStream_t st, size_t bytes) {
+unsigned char* activation_scratch(cudaStream_t st, size_t bytes) { return stream_scratch(st, bytes); }
+
+}  // namespace
+
+unsigned char* stream_scratch(cudaStream_t st, size_t bytes) {
   struct Entry {
     int device;
     cudaStream_t stream;
@@ -675,6 +679,8 @@ unsigned char* activation_scratch(cudaStream_t st, size_t bytes) {
   table.push_back(Entry{dev, st, static_cast<unsigned char*>(ptr), want});
   return static_cast<unsigned char*>(ptr);
 }
+
+namespace {
 
 template <int FMT, bool RING>
 int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st, bool allow_scratch) {

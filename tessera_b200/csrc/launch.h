@@ -182,6 +182,16 @@ int umma_gemm(int fmt, const float* a, const void* w, const float* scale, float*
 int gemm_q4k_dispatch(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
                       uint64_t split, cudaStream_t st, bool allow_scratch);
 int umma_wait_timeouts(unsigned int* count);
+// Device scratch of a (device, stream) pair, grown on demand from the stream-ordered pool and
+// kept until exit (a captured graph may hold the pointer).  Null when the stream is being
+// captured and no large enough buffer exists yet.  Work on one stream uses it in stream order.
+unsigned char* stream_scratch(cudaStream_t st, size_t bytes);
+// tcgen05 tile over 8-bit weights read straight from shared memory (gemm_f8_umma.cu): FP8
+// weights, 2..21 activation rows.  kUnsupportedFeature when the shape is outside its range.
+int umma_f8_gemm(const float* a, const void* w, const float* scale, float* c, uint64_t m, uint64_t n, uint64_t k,
+                 cudaStream_t st);
+int umma_f8_wait_timeouts(unsigned int* count);
+int umma_f8_set_error_word(unsigned int* word);
 // Point the kernels of each file at the host-visible error word (see pipeline.cuh); once per device.
 int staged_set_error_word(unsigned int* word);
 int staged_q6k_set_error_word(unsigned int* word);
