@@ -113,6 +113,11 @@ int tsr_gemm_mxfp4(const float* a, const void* w, float* c, uint64_t m, uint64_t
     return kInvalidArgument;
   if (!aligned16(a) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
   const cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (m >= 2) {
+    // batches: nibbles and scales go from HBM to the tensor core without a thread touching a weight
+    const int rt = umma_mxfp4_gemm(a, w, c, m, n, k, st);
+    if (rt != kUnsupportedFeature) return rt;
+  }
   const int rc = m > kStagedRows ? staged_in_chunks(m, n, [&](uint64_t i0, uint64_t rows) {
     return staged_gemm_mxfp4(a + i0 * k, w, c + i0 * n, rows, n, k, st);
   }) : staged_gemm_mxfp4(a, w, c, m, n, k, st);

@@ -190,6 +190,11 @@ unsigned char* stream_scratch(cudaStream_t st, size_t bytes);
 // weights, 2..21 activation rows.  kUnsupportedFeature when the shape is outside its range.
 int umma_f8_gemm(const float* a, const void* w, const float* scale, float* c, uint64_t m, uint64_t n, uint64_t k,
                  cudaStream_t st);
+// The same tile over MXFP4 weights (block-scaled MMA with the weights' own E8M0 scales): fp32
+// activations, 2..21 rows; or E4M3 activation codes with per-row factors (W4A8), up to 64 rows.
+int umma_mxfp4_gemm(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k, cudaStream_t st);
+int umma_mxfp4_w4a8(const void* a8, const float* as, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
+                    cudaStream_t st);
 int umma_f8_wait_timeouts(unsigned int* count);
 int umma_f8_set_error_word(unsigned int* word);
 // Point the kernels of each file at the host-visible error word (see pipeline.cuh); once per device.

@@ -30,6 +30,8 @@ def bound(dtype, m, k=256):
     if dtype == "q4k":
         return 2e-5 if m <= 2 else (TIGHT if m <= 8 else FP16_WEIGHTS)
     if dtype == "fp8":
+        if 2 <= m <= 21 and k % 128 == 0 and k >= 256:
+            return 5e-5  # tcgen05 kind::f8f6f4 tile: activations as three E4M3 terms (12 significant bits)
         if m <= 8 and k % 256 == 0:
             return 2e-5  # staged kernel: two binary16 terms per activation
         return FP16_WEIGHTS if (m >= 2 and k % 64 == 0) else 2e-5
