@@ -206,7 +206,7 @@ def qgemv_table(stream, hbm_peak, only=None):
     st = ctypes.c_void_p(stream.cuda_stream)
     shapes = [(17408, 5120), (5120, 5120), (5120, 17408)]
     cases = [("q4k", 1, 17408, 5120), ("q6k", 1, 17408, 5120)]
-    cases += [(f, m, n, k) for f in ("mxfp4", "fp8") for (n, k) in shapes for m in (1, 4, 16)]
+    cases += [(f, m, n, k) for f in ("mxfp4", "fp8", "w4a8") for (n, k) in shapes for m in (1, 4, 16)]
     if only is not None:
         cases = [only]
     rows, cache = [], {}
@@ -219,7 +219,7 @@ def qgemv_table(stream, hbm_peak, only=None):
                 host = synth.q4k_weights(n, k, seed=11)
             elif fmt == "q6k":
                 host = synth.q6k_weights(n, k, seed=11)
-            elif fmt == "mxfp4":
+            elif fmt in ("mxfp4", "w4a8"):
                 host = synth.mxfp4_weights(n, k, seed=11)
             else:
                 host, scale = synth.fp8_weights(n, k, seed=11)
@@ -230,6 +230,11 @@ def qgemv_table(stream, hbm_peak, only=None):
         ws, scale, wbytes = cache[(fmt, n, k)]
         a = torch.from_numpy(synth.activations(m, k, seed=12)).cuda()
         c = torch.empty(m * n, dtype=torch.float32, device="cuda")
+        # W4A8: per-token FP8 codes and factors (quantize_fp8_pack_rows), then the unsplit
+        # gemm_mxfp4_wmma contract; the row-reference bytes are not read by the unsplit launch
+        a8 = torch.empty(m * k, dtype=torch.uint8, device="cuda")
+        a_scale = torch.empty(m, dtype=torch.float32, device="cuda")
+        wref = torch.zeros(n, dtype=torch.uint8, device="cuda")
 
         def launch(i):
             w = ctypes.c_void_p(ws[i % len(ws)].data_ptr())
@@ -240,6 +245,11 @@ def qgemv_table(stream, hbm_peak, only=None):
                 rc = lib.tsr_gemm_q6k(pa, w, pc, m, n, k, 1, st)
             elif fmt == "mxfp4":
                 rc = lib.tsr_gemm_mxfp4(pa, w, pc, m, n, k, st)
+            elif fmt == "w4a8":
+                rc = lib.tsr_quantize_fp8_pack(pa, ctypes.c_void_p(a8.data_ptr()), ctypes.c_void_p(a_scale.data_ptr()),
+                                               m, k, st)
+                rc = rc or lib.tsr_gemm_mxfp4_w4a8(ctypes.c_void_p(a8.data_ptr()), w, ctypes.c_void_p(a_scale.data_ptr()),
+                                                   ctypes.c_void_p(wref.data_ptr()), pc, m, n, k, 1, st)
             else:
                 rc = lib.tsr_gemm_fp8(pa, w, ctypes.c_void_p(scale.data_ptr()), pc, m, n, k, st)
             if rc != 0:

@@ -157,6 +157,16 @@ int tsr_gemm_mxfp4_w4a8(const void* a_fp8, const void* w, const float* as, const
       k % 32 != 0 || split == 0 || split > 65535)
     return kInvalidArgument;
   if (!aligned16(a_fp8) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
+  if (split == 1) {
+    // Unsplit: the block-scaled tensor-core tile, E4M3 activation codes against the nibbles with
+    // their own E8M0 scales.  The reference folds each weight into an E4M3 byte relative to the
+    // row's largest scale first (FoldMxFp4ToFp8, src/core/numerics/quant.cpp:846-924), which is
+    // exact while a block's scale is within 2^8 of that largest one and drops bits beyond; the
+    // tile never drops them, so it equals the reference there and is closer to the unfolded
+    // product elsewhere.  wref is not needed.
+    const int rt = umma_mxfp4_w4a8(a_fp8, as, w, c, m, n, k, static_cast<cudaStream_t>(stream));
+    if (rt != kUnsupportedFeature) return rt;
+  }
   return rows_gemm_w4a8(a_fp8, w, as, wref, c, m, n, k, split, static_cast<cudaStream_t>(stream));
 }
 
