@@ -368,10 +368,13 @@ def tp_parity(backend, comm, dist, rank, world, local):
 
 def collective_table(backend, dist, stream, local):
     """The library's peer-memory all-reduce and NCCL's on the same payloads (the row-parallel
-    partial sums of m = 1 and m = 16: 20 KB and 320 KB of fp32), issued back to back without
-    graphs, timed with events on the launching stream, max over ranks."""
+    partial sums of m = 1 and m = 16: 20 KB and 320 KB of fp32), 200 calls back to back, timed
+    with events on the launching stream, max over ranks.  peer_us: the calls go through the
+    backend's deferred queue and replay as one CUDA graph, as they do inside a decode step;
+    peer_eager_us and nccl_eager_us: every call issued by the host as it is made (both then
+    include the host's per-call cost)."""
     import torch
-    from tessera_b200.backend import KernelLaunch
+    from tessera_b200.backend import KernelLaunch, LaunchBatch
     kern = backend.LoadKernel("allreduce_sum")
     rows = []
     for m in (1, 16):
@@ -379,18 +382,26 @@ def collective_table(backend, dist, stream, local):
         xb = backend.upload(np.ones(m * n, dtype=np.float32))
         t = torch.ones(m * n, dtype=torch.float32, device=f"cuda:{local}")
         reps = 200
+        batch = LaunchBatch()
+        for _ in range(reps):
+            batch.add(kern, KernelLaunch(buffers=[xb], scalars=[m, n]))
 
-        def peer():
+        def peer_graph():
+            backend.LaunchMany(batch)
+            backend.Flush()
+
+        def peer_eager():
             for _ in range(reps):
                 backend.LaunchKernel(kern, KernelLaunch(buffers=[xb], scalars=[m, n]))
-            backend.Flush()
+                backend.Flush()
 
         def nccl():
             for _ in range(reps):
                 dist.all_reduce(t)
         times = {}
-        for name, fn in (("peer_us", peer), ("nccl_us", nccl)):
-            fn()
+        for name, fn in (("peer_us", peer_graph), ("peer_eager_us", peer_eager), ("nccl_eager_us", nccl)):
+            for _ in range(3):  # the third identical queue is already a graph replay
+                fn()
             torch.cuda.synchronize()
             dist.barrier()
             torch.cuda.synchronize()

@@ -113,7 +113,7 @@ int tsr_gemm_mxfp4(const float* a, const void* w, float* c, uint64_t m, uint64_t
     return kInvalidArgument;
   if (!aligned16(a) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
   const cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (m >= 2) {
+  {
     // batches: nibbles and scales go from HBM to the tensor core without a thread touching a weight
     const int rt = umma_mxfp4_gemm(a, w, c, m, n, k, st);
     if (rt != kUnsupportedFeature) return rt;
@@ -134,7 +134,7 @@ int tsr_gemm_fp8(const float* a, const void* w, const float* s, float* c, uint64
   if (!a || !w || !s || !c || !fits_int(m) || !fits_int(n) || !fits_int(k)) return kInvalidArgument;
   if (!aligned16(a) || !aligned16(w) || !aligned16(c)) return kInvalidArgument;
   const cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (m >= 2) {
+  {
     // batches: the weights go from HBM to the tensor core without a thread touching them
     const int rt = umma_f8_gemm(a, w, s, c, m, n, k, st);
     if (rt != kUnsupportedFeature) return rt;

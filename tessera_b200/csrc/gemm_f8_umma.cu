@@ -564,13 +564,13 @@ int launch_tile(int fmt, const float* a, const unsigned char* codes, const float
 // or no scratch is to be had (a stream that is being captured before its first plain launch).
 int umma_f8_gemm(const float* a, const void* w, const float* scale, float* c, uint64_t m, uint64_t n, uint64_t k,
                  cudaStream_t st) {
-  if (m < 2 || k % 16 != 0) return kUnsupportedFeature;
+  if (m < static_cast<uint64_t>(env_int("TSR_TILE_MIN_M", 2)) || k % 16 != 0) return kUnsupportedFeature;
   return launch_tile(kFp8, a, nullptr, nullptr, w, scale, c, m, n, k, st);
 }
 
 // MXFP4 weights (nibbles, then the E8M0 side table), fp32 activations, 2 <= m <= 21.
 int umma_mxfp4_gemm(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k, cudaStream_t st) {
-  if (m < 2 || env_int("TSR_DISABLE_MX_UMMA", 0)) return kUnsupportedFeature;
+  if (m < static_cast<uint64_t>(env_int("TSR_TILE_MIN_M", 2)) || env_int("TSR_DISABLE_MX_UMMA", 0)) return kUnsupportedFeature;
   return launch_tile(kMxFp4, a, nullptr, nullptr, w, nullptr, c, m, n, k, st);
 }
 
