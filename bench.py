@@ -205,12 +205,20 @@ def qgemv_table(stream, hbm_peak, only=None):
     lib = capi.load_library()
     st = ctypes.c_void_p(stream.cuda_stream)
     shapes = [(17408, 5120), (5120, 5120), (5120, 17408)]
-    cases = [("q4k", 1, 17408, 5120), ("q6k", 1, 17408, 5120)]
+    cases = [("q4k", 1, 17408, 5120), ("q4k", 1, 17408, 5120, 2), ("q6k", 1, 17408, 5120)]
     cases += [(f, m, n, k) for f in ("mxfp4", "fp8", "w4a8") for (n, k) in shapes for m in (1, 4, 16)]
     if only is not None:
         cases = [only]
     rows, cache = [], {}
-    for fmt, m, n, k in cases:
+    group_backend = None
+    for case in cases:
+        fmt, m, n, k = case[:4]
+        group = case[4] if len(case) > 4 else 1   # weight tensors per launch (Q4_K / Q6_K: tsr_gemv_group)
+        if group > 1 and group_backend is None:
+            from tessera_b200.backend import CreateBackend
+            group_backend = CreateBackend(stream=stream.cuda_stream)
+            group_backend.SetDeviceIndex(torch.cuda.current_device())
+            group_backend.Init()
         if (fmt, n, k) not in cache:
             cache.clear()
             torch.cuda.empty_cache()
@@ -226,6 +234,7 @@ def qgemv_table(stream, hbm_peak, only=None):
                 scale = torch.from_numpy(scale).cuda()
             first = torch.from_numpy(host).cuda()
             copies = max(3, int(np.ceil(400e6 / host.size)))
+            copies = (copies + group - 1) // group * group
             cache[(fmt, n, k)] = ([first] + [first.clone() for _ in range(copies - 1)], scale, host.size)
         ws, scale, wbytes = cache[(fmt, n, k)]
         a = torch.from_numpy(synth.activations(m, k, seed=12)).cuda()
@@ -236,10 +245,17 @@ def qgemv_table(stream, hbm_peak, only=None):
         a_scale = torch.empty(m, dtype=torch.float32, device="cuda")
         wref = torch.zeros(n, dtype=torch.uint8, device="cuda")
 
+        outs = [torch.empty(m * n, dtype=torch.float32, device="cuda") for _ in range(group)]
+
         def launch(i):
             w = ctypes.c_void_p(ws[i % len(ws)].data_ptr())
             pa, pc = ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(c.data_ptr())
-            if fmt == "q4k":
+            if group > 1:
+                wp = (ctypes.c_void_p * group)(*[ws[(i * group + j) % len(ws)].data_ptr() for j in range(group)])
+                cp = (ctypes.c_void_p * group)(*[o.data_ptr() for o in outs])
+                nn = (ctypes.c_uint64 * group)(*([n] * group))
+                rc = lib.tsr_gemv_group(group_backend._ctx, 0 if fmt == "q4k" else 1, pa, wp, cp, nn, group, m, k)
+            elif fmt == "q4k":
                 rc = lib.tsr_gemm_q4k(pa, w, pc, m, n, k, 1, st)
             elif fmt == "q6k":
                 rc = lib.tsr_gemm_q6k(pa, w, pc, m, n, k, 1, st)
@@ -254,7 +270,7 @@ def qgemv_table(stream, hbm_peak, only=None):
                 rc = lib.tsr_gemm_fp8(pa, w, ctypes.c_void_p(scale.data_ptr()), pc, m, n, k, st)
             if rc != 0:
                 raise RuntimeError(f"{fmt} projection returned status {rc}")
-        per_graph = 2 * len(ws)
+        per_graph = 2 * len(ws) // group
         with torch.cuda.stream(stream):
             launch(0)
             torch.cuda.synchronize()
@@ -273,10 +289,15 @@ def qgemv_table(stream, hbm_peak, only=None):
             e1.record(stream)
             torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / (reps * per_graph)
-        gbs = (wbytes + m * k * 4 + m * n * 4) / us / 1e3
-        rows.append({"fmt": fmt, "m": m, "n": n, "k": k, "us": round(us, 2), "gbs": round(gbs, 1),
-                     "frac": round(gbs / hbm_peak, 3)})
+        gbs = (group * (wbytes + m * n * 4) + m * k * 4) / us / 1e3
+        row = {"fmt": fmt, "m": m, "n": n, "k": k, "us": round(us, 2), "gbs": round(gbs, 1),
+               "frac": round(gbs / hbm_peak, 3)}
+        if group > 1:
+            row["weights_per_launch"] = group
+        rows.append(row)
     cache.clear()
+    if group_backend is not None:
+        group_backend.close()
     return rows
 
 
@@ -639,8 +660,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default=None, metavar="FMT:M:N:K",
-                    help="time one projection (q4k, mxfp4 or fp8) instead of the decode step, e.g. q4k:1:17408:5120")
+    ap.add_argument("--case", default=None, metavar="FMT:M:N:K[:G]",
+                    help="time one projection (q4k, q6k, mxfp4, fp8, w4a8) instead of the decode step, e.g. "
+                         "q4k:1:17408:5120; G > 1 (q4k, q6k): G weight tensors of that shape in one launch")
     ap.add_argument("--only", default=None, metavar="NAMES",
                     help="experiment: the step holds only these projections (comma separated tensor names)")
     ap.add_argument("--no-qgemv", action="store_true", help="skip the single-projection table and the CPU baseline")
@@ -653,10 +675,12 @@ def main():
         reference_arm(args)
     elif args.case:
         import torch
-        fmt, m, n, k = args.case.split(":")
+        fields = args.case.split(":")
+        fmt, (m, n, k) = fields[0], fields[1:4]
+        only = (fmt, int(m), int(n), int(k)) + ((int(fields[4]),) if len(fields) > 4 else ())
         peaks, kind = measured_peaks()
         torch.cuda.set_device(0)
-        row = qgemv_table(torch.cuda.Stream(), peaks["hbm_gbs"], only=(fmt, int(m), int(n), int(k)))[0]
+        row = qgemv_table(torch.cuda.Stream(), peaks["hbm_gbs"], only=only)[0]
         print(json.dumps({"case": args.case, "peak_kind": kind, **row}))
     else:
         gpu_arm(args)

@@ -264,10 +264,7 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
   if (!(p.debug & 1)) {
     stage_activations<kGroups>(p, b0 * kBlockElems, act, sums, cs, deferred_prologue);
   } else {
-    if (p.pdl) {
-      pdl_wait();
-      pdl_trigger();
-    }
+    if (p.pdl) pdl_wait();
     deferred_prologue();
   }
   if (tid == 0 && p.tp.world > 1) s_words[1] = tp_call_epoch(p.tp);  // the stream's earlier work is complete here
@@ -354,6 +351,7 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
       }
     }
 
+    if (it == my_tiles - 1) pdl_trigger();  // the next launch may come in under this CTA's epilogue
     // The warps of a row group (one per set) add their partial sums; the digit
     // columns of each activation row are then combined through shared memory.
     if (bx > 0) {
@@ -526,6 +524,11 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
   if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q6k_staged_kernel<NCG, SETS>), kMaxSmem)) return rc;
   const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.split));
   p.pdl = pdl_allowed_ranges(st, reads, read_bytes, count, writes, write_bytes, count) ? 1 : 0;
+  {
+    const int mode = env_int("TSR_PDL_MODE", 1);  // experiments: which launches may start before their predecessor ends
+    if (mode == 2 && plan.occ < 2) p.pdl = 0;
+    if (mode == 3 && plan.sets != 4) p.pdl = 0;
+  }
   launch_kernel(gemv_q6k_staged_kernel<NCG, SETS>, grid, dim3((SETS * plan.rgs + 1) * 32), plan.smem, st, p.pdl != 0,
                 maps, p);
   return check_launch();

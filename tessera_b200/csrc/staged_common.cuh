@@ -218,6 +218,10 @@ __device__ __forceinline__ void stage_sums(const StagedParams& p, int i, int bl,
 // Stages the activation blocks [k0, k0 + per*256) of all m rows.  A kernel
 // launched as a programmatic dependent (p.pdl) waits for the stream in here,
 // before its first activation load; every thread of the CTA reaches that wait.
+// The kernels let their own dependents go late, when a CTA has consumed the last
+// chunk of its last tile: measured on a decode step of mixed launches, letting
+// them go right after the wait (so that the next launch's CTAs sit resident,
+// their first weights fetched, for the whole main loop) cost 11 % of the step.
 template <int GROUPS, typename AfterFirstLoads>
 __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0, unsigned char* act,
                                                   unsigned char* sums, float* cs,
@@ -229,7 +233,6 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
   if (warp >= kWarps) {
     if (p.pdl) {
       pdl_wait();
-      pdl_trigger();
       return;
     }
     // Touch one activation word first: the weight prefetch of all CTAs would
@@ -245,7 +248,6 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
       asm volatile("prefetch.global.L2 [%0];" ::"l"(p.a + static_cast<size_t>(warp / p.per) * p.k + k0 +
                                                      (warp % p.per) * kBlockElems));
     pdl_wait();
-    pdl_trigger();
   }
 #pragma unroll 1
   for (int base = warp; base < items; base += kWarps * kStageBatch) {
@@ -476,13 +478,14 @@ inline bool plan_group(const uint64_t* n, int count, uint64_t nb, int m, uint64_
   const int sms = device_sms();
   // Measured on B200 (Q4_K, m = 1): a busy SM gets through one 16-row x 256-column block in
   // about 0.053 us whatever the tiling; one warp needs `block_us` (0.5 us Q4_K) for each block
-  // of its own chain; a launch costs about 2.6 us before and after its weights, plus the
+  // of its own chain; every tile of a CTA ends with about 0.5 us of exchange and output; a
+  // launch costs about 2.6 us before and after its weights, plus the
   // activation staging (0.25 us per round of one block per consumer warp); a split inside the
   // launch pays a ticket round trip and a pass over the partial sums at the very end of every
   // tile, where nothing overlaps it (measured 3-4 us: no cheaper than a reduce launch, so it
   // only wins where it shortens a long chain, as for Q6_K rows of 68 blocks).
   const double kUnitUs = 0.053 * (block_us / 0.5), kPrefixUs = 2.6, kStageRoundUs = 0.25;
-  const double kTicketUs = 3.5, kTicketTileUs = 1.5, kWaveUs = 2.0;
+  const double kTicketUs = 3.5, kTicketTileUs = 1.5, kWaveUs = 2.0, kTileUs = 0.5;
   const int ring_max = env_plan_int("TSR_RING_MAX", max_want);
   const int force_rgs = env_plan_int("TSR_RGS", 0), force_split = env_plan_int("TSR_SPLIT", 0);
   const int force_grid = env_plan_int("TSR_GRID", 0), force_occ = env_plan_int("TSR_OCC", 0);
@@ -534,11 +537,14 @@ inline bool plan_group(const uint64_t* n, int count, uint64_t nb, int m, uint64_
           const uint64_t ctas_per_sm = (ctas + sms - 1) / sms;
           // an SM works through its CTAs' tiles at a fixed rate, but a warp cannot go faster
           // than its own share of the blocks (one consumer set's) one after the other
-          const double throughput = static_cast<double>(ctas_per_sm * tiles_per_cta * rgs * per) * kUnitUs;
+          // (four sets spend a little more on adding their partial sums per tile)
+          const double throughput =
+              static_cast<double>(ctas_per_sm * tiles_per_cta * rgs * per) * kUnitUs * (sets == 4 ? 1.05 : 1.0);
           const double chain = static_cast<double>(waves * tiles_per_cta) * ((per + sets - 1) / sets) * block_us;
           const double staging = kStageRoundUs * static_cast<double>((m * per + warps - 1) / warps);
+          // every tile of a CTA ends with the exchange between the sets and the output pass
           double cost = kPrefixUs + staging + (throughput > chain ? throughput : chain) + (waves - 1) * kWaveUs +
-                        (sets == 4 ? 0.4 : 0.0);
+                        kTileUs * static_cast<double>(waves * tiles_per_cta) + (sets == 4 ? 0.4 : 0.0);
           if (split > 1 && fixed_split == 0) cost += kTicketUs + kTicketTileUs * static_cast<double>(tiles_per_cta);
           if (depth < sets + 1 && total_chunks > static_cast<uint64_t>(sets)) cost *= 1.1;  // a shallow ring stalls on HBM latency
           if (cost < best - 1e-9) {
