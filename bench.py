@@ -366,6 +366,42 @@ def tp_parity(backend, comm, dist, rank, world, local):
             cases.append({"fmt": fmt, "m": m, "n": n, "k": k, "k_local": k_local, "max_rel_err": err})
             for buf in (ab, wb, out, fa, fw, full):
                 buf.release()
+    # the end of an FFN block (silu_mul, down projection with the sum over ranks, residual add:
+    # one launch per rank once queued) against the same three steps over the whole k
+    for fmt, m in (("q4k", 1), ("q6k", 1), ("q4k", 4)):
+        n, k = 5120, 17408
+        case = tp_check.make_case(fmt, m, n, k, seed=11)
+        gen = np.random.default_rng(12)
+        up_full = gen.standard_normal((m, k)).astype(np.float32)
+        resid = gen.standard_normal(m * n).astype(np.float32)
+        _, w, k_local = tp_check.rank_inputs(case, rank, world)
+        from tessera_b200.tp import ROW, slice_shape
+        _, cols, c0, _ = slice_shape(tp_check.FORMATS[fmt], ROW, n, k, rank, world)
+        bufs = {
+            "g": backend.upload(np.ascontiguousarray(case.activations[:, c0:c0 + cols])),
+            "u": backend.upload(np.ascontiguousarray(up_full[:, c0:c0 + cols])),
+            "act": backend.AllocateBuffer(m * cols * 4), "w": backend.upload(w), "down": backend.AllocateBuffer(m * n * 4),
+            "res": backend.upload(resid), "fin": backend.AllocateBuffer(m * n * 4),
+            "fg": backend.upload(case.activations), "fu": backend.upload(up_full), "fact": backend.AllocateBuffer(m * k * 4),
+            "fw": backend.upload(case.weight), "fdown": backend.AllocateBuffer(m * n * 4), "ffin": backend.AllocateBuffer(m * n * 4),
+        }
+        tp_check.launch_ffn_tail(backend, case, bufs["fg"], bufs["fu"], bufs["fact"], bufs["fw"], bufs["fdown"], bufs["res"],
+                                 bufs["ffin"], k, sharded=False)
+        want = backend.download(bufs["ffin"], np.float32, m * n)
+        want_act = backend.download(bufs["fact"], np.float32, m * k).reshape(m, k)[:, c0:c0 + cols]
+        for rep in range(2):
+            tp_check.launch_ffn_tail(backend, case, bufs["g"], bufs["u"], bufs["act"], bufs["w"], bufs["down"], bufs["res"],
+                                     bufs["fin"], k_local, sharded=True)
+            got = backend.download(bufs["fin"], np.float32, m * n)
+            got_act = backend.download(bufs["act"], np.float32, m * cols).reshape(m, cols)
+            err = max(tp_check.max_rel_err(got, want), tp_check.max_rel_err(got_act, want_act))
+            worst = max(worst, err)
+            sums = [None] * world
+            dist.all_gather_object(sums, hashlib.sha1(got.tobytes()).hexdigest())
+            identical = identical and len(set(sums)) == 1
+        cases.append({"fmt": fmt, "m": m, "n": n, "k": k, "k_local": k_local, "steps": "silu_mul+down+add", "max_rel_err": err})
+        for buf in bufs.values():
+            buf.release()
     # flat all-reduce and its [m][n] form against the rank-order sum of everybody's input
     exact = True
     kern = backend.LoadKernel("allreduce_sum")

@@ -92,7 +92,15 @@ int tsr_synchronize(tsr_context* ctx);
  * chosen here from the scalars; only grid_y of the split-K families is
  * meaningful and it must equal the `split` scalar.  buffer_bytes[i] is the
  * size of buffer i; every launch checks it against the bytes the scalars
- * imply and fails with TSR_INVALID_ARGUMENT instead of reading out of range. */
+ * imply and fails with TSR_INVALID_ARGUMENT instead of reading out of range.
+ *
+ * Ids without a counterpart in the reference's table (this library's own):
+ *   gemm_q4k_vec_allreduce, gemm_q6k_vec_allreduce, allreduce_sum: see the
+ *     tensor-parallel section below;
+ *   gemm_q4k_bf16, gemm_q6k_bf16, gemm_mxfp4_bf16, gemm_fp8_bf16: buffers A (bf16,
+ *     m x k), W, [S: fp8 only], C (bf16, m x n); scalars m, n, k (k a multiple of 8).
+ *     C = RoundBf16Ref (src/core/numerics/quant.cpp:231-243) of the fp32 id's sums on
+ *     the same values; the reference keeps A and C in fp32 (backend.hpp:153-156). */
 int tsr_kernel_count(void);
 const char* tsr_kernel_name(int kernel);
 int tsr_kernel_lookup(const char* name);
@@ -189,6 +197,12 @@ int tsr_round_bf16(float* x, uint64_t n, void* stream);
 /* add, fill: backend.hpp:150-152,258-260 */
 int tsr_add(const float* a, const float* b, float* o, uint64_t n, void* stream);
 int tsr_fill(int32_t* data, int32_t value, uint64_t n, void* stream);
+/* silu_mul: O = silu(G) * U, backend.hpp:257-260; SiluMulRef src/core/numerics/norm.cpp:211-225 */
+int tsr_silu_mul(const float* g, const float* u, float* o, uint64_t n, void* stream);
+/* rmsnorm: Y = X / sqrt(mean(X^2) + eps) * W per row, backend.hpp:212-216; RmsNormRef
+ * src/core/numerics/norm.cpp:7-32 (eps < 0: TSR_INVALID_ARGUMENT) */
+int tsr_rmsnorm(const float* x, const float* w, float* y, uint64_t rows, uint64_t cols, float eps,
+                void* stream);
 /* Dequantise whole blocks to fp32 with the reference's rounding sequence
  * (bit-exact check of the codecs).  fmt: 0 Q4_K (quant.cpp:656-675), 1 Q6_K
  * (quant.cpp:421-449), 2 MXFP4 packed n x k (quant.cpp:279-297), 3 FP8 E4M3

@@ -435,6 +435,38 @@ int orc_round_bf16(float* x, size_t n) {
   return 0;
 }
 
+/* RmsNormRef, src/core/numerics/norm.cpp:7-32: squares added in order with fma, the gain
+ * 1 / sqrt(mean + eps), y = (x * gain) * w. */
+int orc_rmsnorm(const float* x, const float* w, float* y, size_t rows, size_t cols, float eps) {
+  if (rows == 0 || cols == 0 || eps < 0.0f) return -2;
+  for (size_t r = 0; r < rows; ++r) {
+    const float* xr = x + r * cols;
+    float mean = 0.0f;
+    for (size_t c = 0; c < cols; ++c) mean = fmaf(xr[c], xr[c], mean);
+    mean /= (float)cols;
+    const float gain = 1.0f / sqrtf(mean + eps);
+    for (size_t c = 0; c < cols; ++c) y[r * cols + c] = xr[c] * gain * w[c];
+  }
+  return 0;
+}
+
+/* AddRef, src/core/numerics/norm.cpp:196-209 */
+int orc_add(const float* a, const float* b, float* o, size_t n) {
+  if (n == 0) return -2;
+  for (size_t i = 0; i < n; ++i) o[i] = a[i] + b[i];
+  return 0;
+}
+
+/* SiluMulRef, src/core/numerics/norm.cpp:211-225: silu = g / (1 + exp(-g)) */
+int orc_silu_mul(const float* g, const float* u, float* o, size_t n) {
+  if (n == 0) return -2;
+  for (size_t i = 0; i < n; ++i) {
+    const float silu = g[i] / (1.0f + expf(-g[i]));
+    o[i] = silu * u[i];
+  }
+  return 0;
+}
+
 /* --------------------------------------------------------------- W4A8 fold */
 
 /* E4M3 byte of E2M1 magnitude index i scaled by 2^-d; the table is derived

@@ -74,6 +74,9 @@ size_t orc_gemm_vec_split_rule(size_t outputs, size_t k, size_t target); /* deco
 int orc_quantize_fp8(float* data, float* scale, size_t rows, size_t cols);                    /* quant.cpp:180-205 */
 int orc_quantize_fp8_pack(const float* in, uint8_t* out, float* scale, size_t rows, size_t cols); /* quant.cpp:207-229 */
 int orc_round_bf16(float* x, size_t n);                                                       /* quant.cpp:231-243 */
+int orc_rmsnorm(const float* x, const float* w, float* y, size_t rows, size_t cols, float eps);  /* norm.cpp:7-32 */
+int orc_add(const float* a, const float* b, float* o, size_t n);                               /* norm.cpp:196-209 */
+int orc_silu_mul(const float* g, const float* u, float* o, size_t n);                          /* norm.cpp:211-225 */
 
 /* ---- W4A8 fold path ----------------------------------------------------- */
 int orc_mxfp4_row_ref(const uint8_t* scales, uint8_t* wref, size_t rows, size_t cols);        /* mxfp4_row_ref.comp:26-40 */

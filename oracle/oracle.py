@@ -163,6 +163,31 @@ class Oracle:
         assert fn(_ptr(np.ascontiguousarray(data, dtype=np.float32)), _ptr(codes), _ptr(scale), rows, cols) == 0
         return codes, scale
 
+    def rmsnorm(self, x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+        rows, cols = x.shape
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        y = np.empty_like(x)
+        fn = self._fn("rmsnorm", C.c_int, [_p, _p, _p, _sz, _sz, C.c_float])
+        assert fn(_ptr(x), _ptr(w), _ptr(y), rows, cols, eps) == 0
+        return y
+
+    def add(self, a: np.ndarray, b: np.ndarray) -> np.ndarray:
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        b = np.ascontiguousarray(b, dtype=np.float32)
+        o = np.empty_like(a)
+        fn = self._fn("add", C.c_int, [_p, _p, _p, _sz])
+        assert fn(_ptr(a), _ptr(b), _ptr(o), a.size) == 0
+        return o
+
+    def silu_mul(self, g: np.ndarray, u: np.ndarray) -> np.ndarray:
+        g = np.ascontiguousarray(g, dtype=np.float32)
+        u = np.ascontiguousarray(u, dtype=np.float32)
+        o = np.empty_like(g)
+        fn = self._fn("silu_mul", C.c_int, [_p, _p, _p, _sz])
+        assert fn(_ptr(g), _ptr(u), _ptr(o), g.size) == 0
+        return o
+
     def round_bf16(self, x: np.ndarray) -> np.ndarray:
         out = np.ascontiguousarray(x, dtype=np.float32).copy()
         fn = self._fn("round_bf16", C.c_int, [_p, _sz])

@@ -1,6 +1,7 @@
 // C-ABI shim over the reference's own host reference functions
 // (tessera::core::*Ref).  TEST INFRASTRUCTURE ONLY.  It is compiled together
-// with the reference's src/core/numerics/{quant,gemm}.cpp, taken from where
+// with the reference's src/core/numerics/{quant,gemm,norm}.cpp and
+// src/core/loaders/tensor_slice.cpp, taken from where
 // the reference checkout lies, into oracle/_ref/libtessera_ref.so by
 // oracle/Makefile.  It pins the C restatement in oracle.c and can serve as
 // the timed CPU baseline.  No reference source is copied: this file only
@@ -12,6 +13,7 @@
 
 #include "core/loaders/tensor_slice.hpp"
 #include "core/numerics/gemm.hpp"
+#include "core/numerics/norm.hpp"
 #include "core/numerics/quant.hpp"
 
 namespace tc = tessera::core;
@@ -102,6 +104,16 @@ int ref_gemm_mxfp4_fp8(const std::uint8_t* a_fp8, const float* as, const std::ui
                        std::size_t k) {
   return Code(tc::GemmMxFp4Fp8Ref(Bytes(a_fp8, m * k), {as, m}, Bytes(w_fp8, n * k),
                                   Bytes(wref, n), {c, m * n}, m, n, k));
+}
+
+int ref_rmsnorm(const float* x, const float* w, float* y, std::size_t rows, std::size_t cols, float eps) {
+  return Code(tc::RmsNormRef({x, rows * cols}, {w, cols}, {y, rows * cols}, rows, cols, eps));
+}
+int ref_add(const float* a, const float* b, float* o, std::size_t n) {
+  return Code(tc::AddRef({a, n}, {b, n}, {o, n}, n));
+}
+int ref_silu_mul(const float* g, const float* u, float* o, std::size_t n) {
+  return Code(tc::SiluMulRef({g, n}, {u, n}, {o, n}, n));
 }
 
 // SliceTensor2D (src/core/loaders/tensor_slice.cpp:105-159).  Returns the slice's byte count, or

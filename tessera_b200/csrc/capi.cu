@@ -106,7 +106,7 @@ bool pdl_allowed_ranges(cudaStream_t stream, const void* const* reads, const siz
     const char* v = std::getenv("TSR_PDL");
     return v == nullptr || std::atoi(v) != 0;
   }();
-  constexpr int kRanges = 4;
+  constexpr int kRanges = 12;
   struct Last {
     cudaStream_t stream;
     bool used;
@@ -127,6 +127,7 @@ bool pdl_allowed_ranges(cudaStream_t stream, const void* const* reads, const siz
       for (int j = 0; j < slot->count; ++j)
         if (r < slot->ptr[j] + slot->bytes[j] && slot->ptr[j] < r + read_bytes[i]) ok = false;  // previous output is our weight
     }
+    if (slot->count < 0) ok = false;  // more outputs than the table holds: anything may have been written
   }
   if (slot == nullptr) {
     static int next = 0;
@@ -135,7 +136,7 @@ bool pdl_allowed_ranges(cudaStream_t stream, const void* const* reads, const siz
   }
   slot->stream = stream;
   slot->used = true;
-  slot->count = nwrites < kRanges ? nwrites : kRanges;
+  slot->count = nwrites <= kRanges ? nwrites : -1;
   for (int j = 0; j < slot->count; ++j) {
     slot->ptr[j] = static_cast<const unsigned char*>(writes[j]);
     slot->bytes[j] = write_bytes[j];

@@ -347,6 +347,37 @@ int k_add(const Args& a) {
                  static_cast<float*>(const_cast<void*>(a.buf[2])), n, a.stream);
 }
 
+// silu_mul: buffers G, U, O; scalar n (backend.hpp:257-260).
+int k_silu_mul(const Args& a) {
+  if (!shape(a, 3, 1)) return kInvalidArgument;
+  const uint64_t n = a.sc[0];
+  if (n == 0 || !holds(a, 0, n * 4) || !holds(a, 1, n * 4) || !holds(a, 2, n * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_silu_mul(static_cast<const float*>(a.buf[0]), static_cast<const float*>(a.buf[1]),
+                      static_cast<float*>(const_cast<void*>(a.buf[2])), n, a.stream);
+}
+
+float float_of_bits(uint64_t v) {
+  const uint32_t b = static_cast<uint32_t>(v);
+  float f;
+  std::memcpy(&f, &b, 4);
+  return f;
+}
+
+// rmsnorm: buffers X, W, Y; scalars rows, cols, eps as fp32 bits (backend.hpp:212-216).
+int k_rmsnorm(const Args& a) {
+  if (!shape(a, 3, 3)) return kInvalidArgument;
+  const uint64_t rows = a.sc[0], cols = a.sc[1];
+  const float eps = float_of_bits(a.sc[2]);
+  if (!dims_ok(rows, cols, 1) || !(eps >= 0.0f) || !holds(a, 0, rows * cols * 4) || !holds(a, 1, cols * 4) ||
+      !holds(a, 2, rows * cols * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_rmsnorm(static_cast<const float*>(a.buf[0]), static_cast<const float*>(a.buf[1]),
+                     static_cast<float*>(const_cast<void*>(a.buf[2])), rows, cols, eps, a.stream);
+}
+
 // fill: buffer int32; scalars value, count (backend.hpp:151-152).
 int k_fill(const Args& a) {
   if (!shape(a, 1, 2)) return kInvalidArgument;
@@ -368,7 +399,7 @@ int tp_sum_in_place(const Args& a, float* data, uint64_t m, uint64_t n) {
 // sees fit, adds the chunks itself and, with `tp`, ends with the sum over ranks.
 // fmt: 0 Q4_K, 1 Q6_K.  kUnsupportedFeature: the caller issues the pieces one by one.
 int fused_group(tsr_context* ctx, int fmt, const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k,
-                bool with_tp, cudaStream_t st) {
+                bool with_tp, cudaStream_t st, const Prologue* pro = nullptr) {
   if (ctx == nullptr) return kUnsupportedFeature;
   TpTail tail{};
   const TpTail* tp = nullptr;
@@ -382,8 +413,8 @@ int fused_group(tsr_context* ctx, int fmt, const float* a, const GroupTarget* t,
     if (tail.world > 1 && !fused) return kUnsupportedFeature;
     if (tail.world > 1) tp = &tail;
   }
-  return fmt == 0 ? staged_group_q4k(a, t, count, m, k, 0, &ctx->scratch, tp, st)
-                  : staged_group_q6k(a, t, count, m, k, 0, &ctx->scratch, tp, st);
+  return fmt == 0 ? staged_group_q4k(a, t, count, m, k, 0, &ctx->scratch, tp, st, pro)
+                  : staged_group_q6k(a, t, count, m, k, 0, &ctx->scratch, tp, st, pro);
 }
 
 // gemm_q4k_vec_allreduce / gemm_q6k_vec_allreduce: buffers A, W, C; scalars m, n, k.
@@ -420,6 +451,49 @@ int k_allreduce_sum(const Args& a) {
   return tp_sum_in_place(a, static_cast<float*>(const_cast<void*>(a.buf[0])), m, n);
 }
 
+// gemm_<q4k|q6k|mxfp4|fp8>_bf16: the projection with bf16 storage on both sides.  Buffers A
+// (bf16, m x k), W, [S for fp8], C (bf16, m x n); scalars m, n, k.  C = RoundBf16(sum in fp32)
+// (RoundBf16Ref, src/core/numerics/quant.cpp:231-243), the sums being those of the fp32 id on
+// the same values.  No reference id: there activations and outputs are fp32
+// (include/tessera/backend.hpp:153-156) and round_bf16 is a pass of its own.
+// FMT: 0 Q4_K, 1 Q6_K, 2 MXFP4, 3 FP8.
+template <int FMT>
+int k_gemm_bf16(const Args& a) {
+  constexpr int kBufs = FMT == 3 ? 4 : 3;
+  if (!shape(a, kBufs, 3)) return kInvalidArgument;
+  const uint64_t m = a.sc[0], n = a.sc[1], k = a.sc[2];
+  if (!dims_ok(m, n, k)) return kInvalidArgument;
+  if ((FMT <= 1 && k % 256 != 0) || (FMT == 2 && k % 32 != 0) || k % 8 != 0) return kInvalidArgument;
+  const uint64_t w_bytes = FMT == 0 ? n * (k / 256) * 144 : FMT == 1 ? n * (k / 256) * 210 : FMT == 2 ? n * (k / 2) + n * (k / 32) : n * k;
+  if (!holds(a, 0, m * k * 2) || !holds(a, 1, w_bytes) || !holds(a, kBufs - 1, m * n * 2)) return kInvalidArgument;
+  if (FMT == 3 && !holds(a, 2, n * 4)) return kInvalidArgument;
+  if (!aligned16(a.buf[0]) || !aligned16(a.buf[kBufs - 1])) return kInvalidArgument;
+  if (a.dry) return kOk;
+  void* C = const_cast<void*>(a.buf[kBufs - 1]);
+  if (FMT <= 1 && m <= 8) {
+    // the staged kernels read and write bf16 themselves
+    Prologue io{};
+    io.bf16_in = io.bf16_out = true;
+    const GroupTarget t{a.buf[1], static_cast<float*>(C), n};
+    const int rc = fused_group(a.ctx, FMT, static_cast<const float*>(a.buf[0]), &t, 1, m, k, false, a.stream, &io);
+    if (rc != kUnsupportedFeature) return rc;
+  }
+  // elsewhere: fp32 copies of A and C around the fp32 projection
+  const size_t a_bytes = (m * k * 4 + 255) / 256 * 256;
+  unsigned char* scratch = stream_scratch(a.stream, a_bytes + m * n * 4, 1);
+  if (scratch == nullptr) return kUnsupportedFeature;
+  float* a32 = reinterpret_cast<float*>(scratch);
+  float* c32 = reinterpret_cast<float*>(scratch + a_bytes);
+  if (int rc = convert_bf16_to_f32(a.buf[0], a32, m * k, a.stream)) return rc;
+  int rc;
+  if (FMT == 0) rc = tsr_gemm_q4k(a32, a.buf[1], c32, m, n, k, 1, a.stream);
+  else if (FMT == 1) rc = tsr_gemm_q6k(a32, a.buf[1], c32, m, n, k, 1, a.stream);
+  else if (FMT == 2) rc = tsr_gemm_mxfp4(a32, a.buf[1], c32, m, n, k, a.stream);
+  else rc = tsr_gemm_fp8(a32, a.buf[1], static_cast<const float*>(a.buf[2]), c32, m, n, k, a.stream);
+  if (rc != kOk) return rc;
+  return convert_f32_to_bf16(c32, C, m * n, a.stream);
+}
+
 struct Entry {
   const char* name;
   int (*fn)(const Args&);
@@ -428,6 +502,8 @@ struct Entry {
 const Entry kTable[] = {
     {"fill", k_fill},
     {"add", k_add},
+    {"silu_mul", k_silu_mul},
+    {"rmsnorm", k_rmsnorm},
     {"round_bf16", k_round},
     {"gemm_q4k", k_block_plain<144, false>},
     {"gemm_q4k_row", k_block_plain<144, false>},
@@ -460,6 +536,10 @@ const Entry kTable[] = {
     {"gemm_q4k_vec_allreduce", k_block_allreduce<144, false>},
     {"gemm_q6k_vec_allreduce", k_block_allreduce<210, true>},
     {"allreduce_sum", k_allreduce_sum},
+    {"gemm_q4k_bf16", k_gemm_bf16<0>},
+    {"gemm_q6k_bf16", k_gemm_bf16<1>},
+    {"gemm_mxfp4_bf16", k_gemm_bf16<2>},
+    {"gemm_fp8_bf16", k_gemm_bf16<3>},
 };
 constexpr int kCount = static_cast<int>(sizeof(kTable) / sizeof(kTable[0]));
 
@@ -474,7 +554,13 @@ constexpr int kCount = static_cast<int>(sizeof(kTable) / sizeof(kTable[0]));
 //     launch picks its own split of k and adds the chunks itself; the caller's partial
 //     buffer is then not written);
 //   * consecutive projections of one format that read the same activations with the
-//     same m and k become one launch over up to four weight tensors.
+//     same m and k become one launch over up to four weight tensors;
+//   * a silu_mul or rmsnorm whose output is the activation matrix of the projection(s)
+//     queued right after it is folded into that launch's activation staging (the output
+//     buffer is still written, later readers find it);
+//   * an add that follows a single projection (with or without the sum over ranks) and
+//     takes its output as one operand is folded into that launch's output stage (the
+//     projection's own output buffer is still written).
 // Everything else is issued as it was queued, in order.  A rewritten queue that has
 // been flushed before is replayed as a CUDA graph (captured on its second appearance,
 // keyed by a hash of the queue as the caller made it).
@@ -485,7 +571,8 @@ struct Projection {
   const float* a;
   GroupTarget t;
   uint64_t m, k;
-  size_t ops;  // queue entries it stands for: 1, or 2 with the reduce
+  size_t ops;    // queue entries it stands for: 1, or 2 with the reduce
+  bool with_tp;  // an _allreduce id
 };
 
 bool name_starts(const char* name, const char* prefix) { return std::strncmp(name, prefix, std::strlen(prefix)) == 0; }
@@ -493,24 +580,26 @@ bool name_ends(const char* name, const char* suffix) {
   const size_t a = std::strlen(name), b = std::strlen(suffix);
   return a >= b && std::strcmp(name + a - b, suffix) == 0;
 }
+bool is_named(const PendingLaunch& op, const char* name) { return std::strcmp(kTable[op.kernel].name, name) == 0; }
 
 bool as_projection(const std::vector<PendingLaunch>& q, size_t i, Projection* out) {
+  if (i >= q.size()) return false;
   const PendingLaunch& op = q[i];
   const char* name = kTable[op.kernel].name;
   int fmt;
   if (name_starts(name, "gemm_q4k")) fmt = 0;
   else if (name_starts(name, "gemm_q6k")) fmt = 1;
   else return false;
-  if (name_ends(name, "_allreduce") || op.nbuf != 3 || (op.nsc != 3 && op.nsc != 4)) return false;
+  if (op.nbuf != 3 || (op.nsc != 3 && op.nsc != 4)) return false;
+  const bool with_tp = name_ends(name, "_allreduce");
   const uint64_t m = op.sc[0], n = op.sc[1], k = op.sc[2], split = op.nsc == 4 ? op.sc[3] : 1;
   if (m > 8) return false;
   *out = Projection{fmt, static_cast<const float*>(op.buf[0]),
-                    GroupTarget{op.buf[1], static_cast<float*>(const_cast<void*>(op.buf[2])), n}, m, k, 1};
+                    GroupTarget{op.buf[1], static_cast<float*>(const_cast<void*>(op.buf[2])), n}, m, k, 1, with_tp};
   if (split == 1) return true;
   if (i + 1 >= q.size()) return false;
   const PendingLaunch& red = q[i + 1];
-  if (std::strcmp(kTable[red.kernel].name, "gemm_vec_reduce") != 0 || red.buf[0] != op.buf[2] ||
-      red.sc[0] != m * n || red.sc[1] != split)
+  if (!is_named(red, "gemm_vec_reduce") || red.buf[0] != op.buf[2] || red.sc[0] != m * n || red.sc[1] != split)
     return false;
   out->t.c = static_cast<float*>(const_cast<void*>(red.buf[1]));
   out->ops = 2;
@@ -523,6 +612,72 @@ bool overlaps(const void* p, size_t pb, const void* q, size_t qb) {
   return a < b + qb && b < a + pb;
 }
 
+// TSR_FUSE_ELEMENTWISE=0 (experiments): silu_mul, rmsnorm and add stay launches of their own
+bool fuse_elementwise() {
+  static const bool on = [] {
+    const char* v = std::getenv("TSR_FUSE_ELEMENTWISE");
+    return v == nullptr || std::atoi(v) != 0;
+  }();
+  return on;
+}
+
+// q[i] as a step that can run inside the activation staging of the projection after it.
+bool as_prologue(const std::vector<PendingLaunch>& q, size_t i, Prologue* pro, const float** in, uint64_t* rows,
+                 uint64_t* cols) {
+  if (!fuse_elementwise() || i + 1 >= q.size()) return false;
+  const PendingLaunch& op = q[i];
+  Projection next;
+  if (!as_projection(q, i + 1, &next)) return false;
+  if (is_named(op, "silu_mul")) {
+    const size_t bytes = op.sc[0] * 4;
+    if (next.a != op.buf[2] || next.m * next.k != op.sc[0]) return false;
+    if (overlaps(op.buf[2], bytes, op.buf[0], bytes) || overlaps(op.buf[2], bytes, op.buf[1], bytes)) return false;
+    *pro = Prologue{kProSiluMul, static_cast<const float*>(op.buf[1]), static_cast<float*>(const_cast<void*>(op.buf[2])), 0.0f};
+    *in = static_cast<const float*>(op.buf[0]);
+    *rows = next.m;
+    *cols = next.k;
+    return true;
+  }
+  if (is_named(op, "rmsnorm")) {
+    const uint64_t r = op.sc[0], c = op.sc[1];
+    const size_t bytes = r * c * 4;
+    if (next.a != op.buf[2] || next.m != r || next.k != c || c % 4 != 0) return false;
+    if (overlaps(op.buf[2], bytes, op.buf[0], bytes) || overlaps(op.buf[2], bytes, op.buf[1], c * 4)) return false;
+    *pro = Prologue{kProRmsNorm, static_cast<const float*>(op.buf[1]), static_cast<float*>(const_cast<void*>(op.buf[2])),
+                    float_of_bits(op.sc[2])};
+    *in = static_cast<const float*>(op.buf[0]);
+    *rows = r;
+    *cols = c;
+    return true;
+  }
+  return false;
+}
+
+// q[i] as an add that can run in the output stage of the single projection `p` before it.
+bool as_epilogue_add(const std::vector<PendingLaunch>& q, size_t i, const Projection& p, const float* act, size_t act_bytes,
+                     const Prologue* pro, GroupTarget* t) {
+  if (!fuse_elementwise() || i >= q.size() || !is_named(q[i], "add")) return false;
+  const PendingLaunch& op = q[i];
+  const size_t bytes = p.m * p.t.n * 4;
+  if (op.sc[0] != p.m * p.t.n) return false;
+  const void* other;
+  if (op.buf[0] == p.t.c) other = op.buf[1];
+  else if (op.buf[1] == p.t.c) other = op.buf[0];
+  else return false;
+  const void* o = op.buf[2];
+  if (overlaps(other, bytes, p.t.c, bytes)) return false;
+  if (o != other && overlaps(o, bytes, other, bytes)) return false;
+  if (o != p.t.c && overlaps(o, bytes, p.t.c, bytes)) return false;
+  if (overlaps(o, bytes, act, act_bytes)) return false;
+  if (pro != nullptr) {
+    if (overlaps(o, bytes, pro->other, act_bytes)) return false;
+    if (pro->out != nullptr && overlaps(o, bytes, pro->out, act_bytes)) return false;
+  }
+  t->add_src = static_cast<const float*>(other);
+  t->add_out = static_cast<float*>(const_cast<void*>(o));
+  return true;
+}
+
 int issue_one(tsr_context* ctx, const PendingLaunch& op) {
   const Args a{op.buf, op.bytes, op.nbuf, op.sc, op.nsc, op.grid_y, ctx->stream, false, ctx};
   return kTable[op.kernel].fn(a);
@@ -532,22 +687,41 @@ int issue_one(tsr_context* ctx, const PendingLaunch& op) {
 int issue_queue(tsr_context* ctx, const std::vector<PendingLaunch>& q) {
   size_t i = 0;
   while (i < q.size()) {
+    Prologue pro{};
+    const float* pro_in = nullptr;
+    uint64_t pro_rows = 0, pro_cols = 0;
+    const bool has_pro = as_prologue(q, i, &pro, &pro_in, &pro_rows, &pro_cols);
+    const size_t start = has_pro ? i + 1 : i;
     Projection first;
-    if (!as_projection(q, i, &first)) {
+    if (!as_projection(q, start, &first)) {
       if (int rc = issue_one(ctx, q[i])) return rc;
       ++i;
       continue;
     }
     GroupTarget t[kMaxGroup];
     int count = 0;
-    size_t end = i;
+    size_t end = start;
     const size_t a_bytes = first.m * first.k * 4;
-    while (count < kMaxGroup && end < q.size()) {
+    if (first.with_tp) {
+      t[count++] = first.t;
+      end += first.ops;
+    }
+    if (has_pro && (overlaps(first.t.c, first.m * first.t.n * 4, pro_in, a_bytes) ||
+                    overlaps(first.t.c, first.m * first.t.n * 4, pro.other, a_bytes))) {
+      // the projection overwrites what the folded step reads: keep the steps apart
+      if (int rc = issue_one(ctx, q[i])) return rc;
+      ++i;
+      continue;
+    }
+    while (!first.with_tp && count < kMaxGroup && end < q.size()) {
       Projection next;
       if (!as_projection(q, end, &next)) break;
-      if (next.fmt != first.fmt || next.a != first.a || next.m != first.m || next.k != first.k) break;
-      // an output that lands in the shared activations would change what later members read
-      if (overlaps(next.t.c, next.m * next.t.n * 4, first.a, a_bytes)) {
+      if (next.with_tp || next.fmt != first.fmt || next.a != first.a || next.m != first.m || next.k != first.k) break;
+      // an output that lands in the shared activations (or in what they are made from) would
+      // change what later members read
+      const size_t c_bytes = next.m * next.t.n * 4;
+      if (overlaps(next.t.c, c_bytes, first.a, a_bytes) ||
+          (has_pro && (overlaps(next.t.c, c_bytes, pro_in, a_bytes) || overlaps(next.t.c, c_bytes, pro.other, a_bytes)))) {
         if (count == 0) {
           t[count++] = next.t;
           end += next.ops;
@@ -557,7 +731,15 @@ int issue_queue(tsr_context* ctx, const std::vector<PendingLaunch>& q) {
       t[count++] = next.t;
       end += next.ops;
     }
-    const int rc = fused_group(ctx, first.fmt, first.a, t, count, first.m, first.k, false, ctx->stream);
+    if (count == 1) {
+      Projection only = first;
+      only.t = t[0];
+      if (as_epilogue_add(q, end, only, has_pro ? pro_in : first.a, a_bytes, has_pro ? &pro : nullptr, &t[0])) ++end;
+    }
+    // with a prologue the launch reads the prologue's input; the projections' A is its output
+    const float* act = has_pro ? pro_in : first.a;
+    int rc = fused_group(ctx, first.fmt, act, t, count, first.m, first.k, first.with_tp, ctx->stream,
+                         has_pro ? &pro : nullptr);
     if (rc == kUnsupportedFeature) {
       for (size_t j = i; j < end; ++j)
         if (int r = issue_one(ctx, q[j])) return r;

@@ -69,6 +69,20 @@ __global__ void round_bf16_kernel(float* __restrict__ x, size_t n) {
   x[i] = __uint_as_float(u & 0xFFFF0000u);
 }
 
+__global__ void bf16_to_f32_kernel(const unsigned short* __restrict__ src, float* __restrict__ dst, size_t n) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = __uint_as_float(static_cast<uint32_t>(src[i]) << 16);
+}
+
+// the rounding of round_bf16_kernel, stored as the high half
+__global__ void f32_to_bf16_kernel(const float* __restrict__ src, unsigned short* __restrict__ dst, size_t n) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  uint32_t u = __float_as_uint(src[i]);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  dst[i] = static_cast<unsigned short>(u >> 16);
+}
+
 __global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b,
                            float* __restrict__ o, size_t n) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -140,8 +154,50 @@ __global__ void dequantize_kernel(int fmt, const uint8_t* __restrict__ w,
   out[idx] = v;
 }
 
+// O = silu(G) * U (SiluMulRef, src/core/numerics/norm.cpp:211-225)
+__global__ void silu_mul_kernel(const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ o,
+                                size_t n) {
+  const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const float x = g[idx];
+  o[idx] = x / (1.0f + expf(-x)) * u[idx];
+}
+
+// Y = X / sqrt(mean(X^2) + eps) * W, one CTA per row (RmsNormRef, src/core/numerics/norm.cpp:7-32;
+// the reference adds the squares sequentially, here they are added as a tree).
+__global__ void __launch_bounds__(1024)
+rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int cols, float eps) {
+  __shared__ float red[32];
+  const float* row = x + static_cast<size_t>(blockIdx.x) * cols;
+  float s = 0.0f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) s = fmaf(row[c], row[c], s);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    if (threadIdx.x == 0) red[0] = 1.0f / sqrtf(v / static_cast<float>(cols) + eps);
+  }
+  __syncthreads();
+  const float gain = red[0];
+  float* out = y + static_cast<size_t>(blockIdx.x) * cols;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) out[c] = row[c] * gain * w[c];
+}
+
 static unsigned blocks_for(uint64_t n, unsigned per) {
   return static_cast<unsigned>((n + per - 1) / per);
+}
+
+int convert_bf16_to_f32(const void* src, float* dst, uint64_t n, cudaStream_t st) {
+  bf16_to_f32_kernel<<<blocks_for(n, 256), 256, 0, st>>>(static_cast<const unsigned short*>(src), dst, n);
+  return check_launch();
+}
+int convert_f32_to_bf16(const float* src, void* dst, uint64_t n, cudaStream_t st) {
+  f32_to_bf16_kernel<<<blocks_for(n, 256), 256, 0, st>>>(src, static_cast<unsigned short*>(dst), n);
+  return check_launch();
 }
 
 }  // namespace tsr
@@ -187,6 +243,20 @@ int tsr_round_bf16(float* x, uint64_t n, void* stream) {
 int tsr_add(const float* a, const float* b, float* o, uint64_t n, void* stream) {
   if (!a || !b || !o || n == 0) return kInvalidArgument;
   add_kernel<<<blocks_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(a, b, o, n);
+  return check_launch();
+}
+
+int tsr_silu_mul(const float* g, const float* u, float* o, uint64_t n, void* stream) {
+  if (!g || !u || !o || n == 0) return kInvalidArgument;
+  silu_mul_kernel<<<blocks_for(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(g, u, o, n);
+  return check_launch();
+}
+
+int tsr_rmsnorm(const float* x, const float* w, float* y, uint64_t rows, uint64_t cols, float eps, void* stream) {
+  if (!x || !w || !y || rows == 0 || cols == 0 || rows > 0x7FFFFFFFull || cols > 0x7FFFFFFFull || !(eps >= 0.0f))
+    return kInvalidArgument;
+  rmsnorm_kernel<<<static_cast<unsigned>(rows), cols >= 4096 ? 1024 : 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, w, y, static_cast<int>(cols), eps);
   return check_launch();
 }
 

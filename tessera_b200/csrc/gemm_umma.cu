@@ -650,9 +650,12 @@ unsigned char* activation_scratch(cudaStream_t st, size_t bytes) { return stream
 
 }  // namespace
 
-unsigned char* stream_scratch(cudaStream_t st, size_t bytes) {
+// `slot` separates users whose buffers are alive at the same time (0: the tile kernels'
+// operands and partial sums; 1: the fp32 copies around a bf16 projection).
+unsigned char* stream_scratch(cudaStream_t st, size_t bytes, int slot) {
   struct Entry {
     int device;
+    int slot;
     cudaStream_t stream;
     unsigned char* ptr;
     size_t bytes;
@@ -663,7 +666,7 @@ unsigned char* stream_scratch(cudaStream_t st, size_t bytes) {
   if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
   std::lock_guard<std::mutex> lock(mutex);
   for (const Entry& e : table)
-    if (e.device == dev && e.stream == st && e.bytes >= bytes) return e.ptr;
+    if (e.device == dev && e.slot == slot && e.stream == st && e.bytes >= bytes) return e.ptr;
   cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
   if (cudaStreamIsCapturing(st, &status) != cudaSuccess || status != cudaStreamCaptureStatusNone) {
     cudaGetLastError();
@@ -676,7 +679,7 @@ unsigned char* stream_scratch(cudaStream_t st, size_t bytes) {
     cudaGetLastError();
     return nullptr;
   }
-  table.push_back(Entry{dev, st, static_cast<unsigned char*>(ptr), want});
+  table.push_back(Entry{dev, slot, st, static_cast<unsigned char*>(ptr), want});
   return static_cast<unsigned char*>(ptr);
 }
 

@@ -262,7 +262,7 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
     if (!p.pdl) prologue();
   };
   if (!(p.debug & 1)) {
-    stage_activations<kGroups>(p, b0 * kBlockElems, act, sums, cs, deferred_prologue);
+    stage_activations<kGroups>(p, b0 * kBlockElems, act, sums, cs, xchg, deferred_prologue);
   } else {
     if (p.pdl) pdl_wait();
     deferred_prologue();
@@ -443,7 +443,8 @@ int env_int(const char* name, int fallback) {
 
 template <int NCG, int SETS>
 int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k, uint64_t caller_split,
-                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st, double* cost_only) {
+                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st, const Prologue* pro,
+                     double* cost_only) {
   const uint64_t nb = k / kBlockElems;
   const int terms = m <= 2 ? 3 : 2;
   const int ncols = static_cast<int>(m) * terms;
@@ -490,10 +491,29 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
   uint64_t tiles = 0;
   const void* reads[kMaxGroup];
   size_t read_bytes[kMaxGroup];
-  const void* writes[kMaxGroup];
-  size_t write_bytes[kMaxGroup];
+  const void* writes[2 * kMaxGroup + 1];
+  size_t write_bytes[2 * kMaxGroup + 1];
+  int nwrites = count;
+  if (pro != nullptr) {
+    p.a_bf16 = pro->bf16_in ? 1 : 0;
+    p.c_bf16 = pro->bf16_out ? 1 : 0;
+  }
+  if (pro != nullptr && pro->kind != kProNone) {
+    p.pro = pro->kind;
+    p.eps = pro->eps;
+    p.a2 = pro->other;
+    p.a_out = pro->out;
+    if (pro->out != nullptr) {
+      writes[nwrites] = pro->out;
+      write_bytes[nwrites++] = m * k * 4;
+    }
+  }
   for (int i = 0; i < count; ++i) {
-    p.tgt[i] = StagedTarget{t[i].c, static_cast<int>(t[i].n), static_cast<int>(tiles), odd_shift};
+    p.tgt[i] = StagedTarget{t[i].c, static_cast<int>(t[i].n), static_cast<int>(tiles), odd_shift, t[i].add_src, t[i].add_out};
+    if (t[i].add_out != nullptr) {
+      writes[nwrites] = t[i].add_out;
+      write_bytes[nwrites++] = m * t[i].n * 4;
+    }
     tiles += (t[i].n + th - 1) / th;
     MapPair pair;
     if (int rc = q6k_tensor_maps(t[i].w, t[i].n, nb, plan.rgs, &pair)) return rc;
@@ -523,7 +543,7 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
   }
   if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q6k_staged_kernel<NCG, SETS>), kMaxSmem)) return rc;
   const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.split));
-  p.pdl = pdl_allowed_ranges(st, reads, read_bytes, count, writes, write_bytes, count) ? 1 : 0;
+  p.pdl = pdl_allowed_ranges(st, reads, read_bytes, count, writes, write_bytes, nwrites) ? 1 : 0;
   {
     const int mode = env_int("TSR_PDL_MODE", 1);  // experiments: which launches may start before their predecessor ends
     if (mode == 2 && plan.occ < 2) p.pdl = 0;
@@ -539,10 +559,15 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
 // Returns kUnsupportedFeature when the launch is outside what the staged
 // kernel covers; the caller then uses the general warp-per-row family.
 int staged_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k, uint64_t caller_split,
-                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st) {
+                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st, const Prologue* pro) {
   const uint64_t nb = k / kBlockElems;
   if (m > 8 || count < 1 || count > kMaxGroup || nb % 4 != 0 || env_int("TSR_DISABLE_STAGED", 0))
     return kUnsupportedFeature;
+  if (caller_split != 0) {
+    if (pro != nullptr && (pro->kind != kProNone || pro->bf16_in || pro->bf16_out)) return kUnsupportedFeature;
+    for (int i = 0; i < count; ++i)
+      if (t[i].add_out != nullptr) return kUnsupportedFeature;
+  }
   // Rows must be 8-byte aligned inside a 16-byte aligned matrix, and there must be an odd row.
   for (int i = 0; i < count; ++i)
     if (t[i].n < 2 || (reinterpret_cast<uintptr_t>(t[i].w) & 15u)) return kUnsupportedFeature;
@@ -551,14 +576,14 @@ int staged_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
   auto run = [&](auto ncg) -> int {
     constexpr int kNcg = decltype(ncg)::value;
     double c2 = 0.0, c4 = 0.0;
-    const int r2 = launch_group_q6k<kNcg, 2>(a, t, count, m, k, caller_split, scratch, tp, st, &c2);
-    const int r4 = launch_group_q6k<kNcg, 4>(a, t, count, m, k, caller_split, scratch, tp, st, &c4);
+    const int r2 = launch_group_q6k<kNcg, 2>(a, t, count, m, k, caller_split, scratch, tp, st, pro, &c2);
+    const int r4 = launch_group_q6k<kNcg, 4>(a, t, count, m, k, caller_split, scratch, tp, st, pro, &c4);
     const int forced_sets = env_int("TSR_SETS", 0);
     const bool four = forced_sets == 4 ? r4 == kOk : forced_sets == 2 ? r2 != kOk && r4 == kOk
                                                                       : r4 == kOk && (r2 != kOk || c4 + 0.3 < c2);
-    if (four) return launch_group_q6k<kNcg, 4>(a, t, count, m, k, caller_split, scratch, tp, st, nullptr);
+    if (four) return launch_group_q6k<kNcg, 4>(a, t, count, m, k, caller_split, scratch, tp, st, pro, nullptr);
     if (r2 != kOk) return r2;
-    return launch_group_q6k<kNcg, 2>(a, t, count, m, k, caller_split, scratch, tp, st, nullptr);
+    return launch_group_q6k<kNcg, 2>(a, t, count, m, k, caller_split, scratch, tp, st, pro, nullptr);
   };
   if (ncols <= 8) return run(std::integral_constant<int, 1>{});
   return run(std::integral_constant<int, 2>{});

@@ -95,7 +95,7 @@ int allow_dynamic_smem(const void* kernel, int bytes);
 
 // Multi-range form of pdl_allowed (a launch over several weight tensors): true when none of the
 // `reads` ranges overlaps a range the previous launch of this library on `stream` wrote; records
-// `writes` (up to four ranges) as what this launch writes.
+// `writes` as what this launch writes (more than twelve ranges: the next launch is refused).
 // Invariant the staged kernels rely on: before its pdl_wait() a kernel reads weight bytes only, and
 // a weight range is only ever written by a copy (a stream-ordered memcpy is never overlapped) or by
 // a launch of this library that registers its output here.  A foreign kernel that writes weights
@@ -129,6 +129,24 @@ struct GroupTarget {
   const void* w;
   float* c;
   uint64_t n;
+  // add_out[e] = add_src[e] + C[e] written besides C (the reference's "add" after a projection,
+  // include/tessera/backend.hpp:255-256); null: none
+  const float* add_src = nullptr;
+  float* add_out = nullptr;
+};
+// What a staged launch does around its projection: an elementwise step folded into the
+// activation staging, and bf16 storage of the activations and outputs.
+enum : int { kProNone = 0, kProSiluMul = 1, kProRmsNorm = 2 };
+struct Prologue {
+  int kind;            // kProSiluMul: A = silu(a) * other; kProRmsNorm: A = a / sqrt(mean(a^2) + eps) * other
+  const float* other;  // up vector [m][k] / norm weights [k]
+  float* out;          // receives A ([m][k]); may be null
+  float eps;
+  // a points to bf16 values (read as fp32 with a zero low half) / every c points to bf16
+  // storage and receives the sums rounded to nearest even (RoundBf16Ref,
+  // src/core/numerics/quant.cpp:231-243 of the reference).  Not combined with `kind` or an add.
+  bool bf16_in = false;
+  bool bf16_out = false;
 };
 // Device scratch of a context for launches that split k among CTAs and add the
 // chunks themselves: partial tiles and one arrival counter per tile (zero at rest).
@@ -141,10 +159,11 @@ struct FusedScratch {
 // Multi-target staged launches (gemv_mma.cu, gemv_q6k_mma.cu): up to four weight tensors that
 // share a, m and k.  caller_split >= 1: chunk y of k goes to region y of each target;
 // caller_split == 0: the launch picks its own split and adds the chunks (and, with `tp`, the ranks).
+// `pro` (null: none) and the targets' add_src/add_out need caller_split == 0.
 int staged_group_q4k(const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k, uint64_t caller_split,
-                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st);
+                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st, const Prologue* pro = nullptr);
 int staged_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k, uint64_t caller_split,
-                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st);
+                     const FusedScratch* scratch, const TpTail* tp, cudaStream_t st, const Prologue* pro = nullptr);
 
 // General warp-per-row family (gemv_rows.cu).
 int rows_gemm_q4k(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
@@ -185,7 +204,10 @@ int umma_wait_timeouts(unsigned int* count);
 // Device scratch of a (device, stream) pair, grown on demand from the stream-ordered pool and
 // kept until exit (a captured graph may hold the pointer).  Null when the stream is being
 // captured and no large enough buffer exists yet.  Work on one stream uses it in stream order.
-unsigned char* stream_scratch(cudaStream_t st, size_t bytes);
+unsigned char* stream_scratch(cudaStream_t st, size_t bytes, int slot = 0);
+// bf16 <-> fp32 copies on the stream (elementwise.cu); the fp32 -> bf16 direction rounds to nearest even
+int convert_bf16_to_f32(const void* src, float* dst, uint64_t n, cudaStream_t st);
+int convert_f32_to_bf16(const float* src, void* dst, uint64_t n, cudaStream_t st);
 // tcgen05 tile over 8-bit weights read straight from shared memory (gemm_f8_umma.cu): FP8
 // weights, 2..21 activation rows.  kUnsupportedFeature when the shape is outside its range.
 int umma_f8_gemm(const float* a, const void* w, const float* scale, float* c, uint64_t m, uint64_t n, uint64_t k,

@@ -33,6 +33,10 @@ struct StagedTarget {
   int n;           // weight rows
   int tile_begin;  // index of this target's first tile in the launch's tile list
   int aux;         // format specific (Q6_K: byte shift of the odd-row tensor map)
+  // residual add folded into the output: add_out[e] = add_src[e] + C[e] is written besides C
+  // (null: none).  add_out may be add_src or c itself, not a shifted overlap of either.
+  const float* add_src;
+  float* add_out;
 };
 
 enum : int {
@@ -58,7 +62,39 @@ struct StagedParams {
   float* part;
   unsigned int* tickets;
   TpTail tp;  // sum over tensor-parallel ranks after the local sum (world 1: none)
+  // What is done to the activations on their way into shared memory (kProNone: nothing).
+  //   kProSiluMul: a holds the gate, a2 the up vector, the projection reads silu(a) * a2
+  //                (SiluMulRef, src/core/numerics/norm.cpp:211-225 of the reference)
+  //   kProRmsNorm: a2 holds the k norm weights, the projection reads a / sqrt(mean(a^2) + eps) * a2
+  //                row by row (RmsNormRef, src/core/numerics/norm.cpp:7-32)
+  // a_out (may be null) receives those activations, [m][k] like a, written by the CTAs of
+  // tile column 0; it must not overlap a or a2.
+  int pro;
+  float eps;
+  const float* a2;
+  float* a_out;
+  // a holds bf16 values ([m][k], 2 bytes each) / the targets' c are bf16 storage ([m][n], 2 bytes
+  // each; the sums are rounded to nearest even).  The partial sums and the exchange between
+  // ranks stay fp32.
+  int a_bf16, c_bf16;
 };
+
+// Rounds to bf16 like RoundBf16Ref (src/core/numerics/quant.cpp:231-243 of the reference).
+__device__ __forceinline__ unsigned short bf16_bits_rn(float v) {
+  unsigned int u = __float_as_uint(v);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return static_cast<unsigned short>(u >> 16);
+}
+__device__ __forceinline__ void store_output(const StagedParams& p, float* c, size_t e, float v) {
+  if (p.c_bf16)
+    reinterpret_cast<unsigned short*>(c)[e] = bf16_bits_rn(v);
+  else
+    c[e] = v;
+}
+__device__ __forceinline__ float4 bf16x4_to_float4(uint2 b) {
+  return make_float4(__uint_as_float(b.x << 16), __uint_as_float(b.x & 0xFFFF0000u), __uint_as_float(b.y << 16),
+                     __uint_as_float(b.y & 0xFFFF0000u));
+}
 
 // Which target a tile of the launch's tile list belongs to, and that target by value.
 // The kernel parameters are read with constant indices only (a run-time index into a
@@ -222,9 +258,19 @@ __device__ __forceinline__ void stage_sums(const StagedParams& p, int i, int bl,
 // chunk of its last tile: measured on a decode step of mixed launches, letting
 // them go right after the wait (so that the next launch's CTAs sit resident,
 // their first weights fetched, for the whole main loop) cost 11 % of the step.
+__device__ __forceinline__ float4 silu_mul4(float4 g, float4 u) {
+  return make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
+                     g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w);
+}
+__device__ __forceinline__ float4 scale4(float4 x, float gain, float4 w) {
+  return make_float4(x.x * gain * w.x, x.y * gain * w.y, x.z * gain * w.z, x.w * gain * w.w);
+}
+
+// `scratch`: (consumer warps + 1) * m floats of shared memory that nothing else uses
+// during the staging (only touched for kProRmsNorm).
 template <int GROUPS, typename AfterFirstLoads>
 __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0, unsigned char* act,
-                                                  unsigned char* sums, float* cs,
+                                                  unsigned char* sums, float* cs, float* scratch,
                                                   AfterFirstLoads after_first_loads) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // The producer warp only issues the weight copies: its first TMA instruction
@@ -237,7 +283,7 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
     }
     // Touch one activation word first: the weight prefetch of all CTAs would
     // otherwise queue ahead of everybody's activation loads in the memory system.
-    const float probe = __ldg(p.a + (k0 < p.k ? k0 : 0) + lane);
+    const float probe = __ldg(p.a + ((k0 < p.k ? k0 : 0) >> p.a_bf16) + lane);  // bf16: half the bytes per element
     if (probe != probe + 1.0f || lane >= 0) after_first_loads();
     return;
   }
@@ -245,10 +291,36 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
   if (p.pdl) {
     // Translate the activation pages while waiting (a prefetch reads no data into this SM).
     if (lane == 0 && warp < items)
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(p.a + static_cast<size_t>(warp / p.per) * p.k + k0 +
-                                                     (warp % p.per) * kBlockElems));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(
+          p.a + ((static_cast<size_t>(warp / p.per) * p.k + k0 + (warp % p.per) * kBlockElems) >> p.a_bf16)));
     pdl_wait();
   }
+  const float* gain = scratch + kWarps * p.m;
+  if (p.pro == kProRmsNorm) {
+    // Every CTA needs the mean square of whole rows: each warp sums a share, the shares are
+    // added in warp order.
+    const int nthreads = kWarps * 32;
+#pragma unroll 1
+    for (int i = 0; i < p.m; ++i) {
+      const float4* row = reinterpret_cast<const float4*>(p.a + static_cast<size_t>(i) * p.k);
+      float s = 0.0f;
+      for (int q = threadIdx.x; q < p.k / 4; q += nthreads) {
+        const float4 v = __ldg(row + q);
+        s = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, s))));
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+      if (lane == 0) scratch[i * kWarps + warp] = s;
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    if (threadIdx.x < p.m) {
+      float s = 0.0f;
+      for (int w = 0; w < kWarps; ++w) s += scratch[threadIdx.x * kWarps + w];
+      scratch[kWarps * p.m + threadIdx.x] = 1.0f / sqrtf(s / static_cast<float>(p.k) + p.eps);
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+  }
+  const bool writes_out = p.a_out != nullptr && blockIdx.x == 0;
 #pragma unroll 1
   for (int base = warp; base < items; base += kWarps * kStageBatch) {
     float4 x0[kStageBatch], x1[kStageBatch];
@@ -260,10 +332,33 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
       blk[u] = it - row[u] * p.per;
       x0[u] = x1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (it < items && k0 + blk[u] * kBlockElems < p.k) {
-        const float4* src = reinterpret_cast<const float4*>(p.a + static_cast<size_t>(row[u]) * p.k + k0 +
-                                                            blk[u] * kBlockElems);
-        x0[u] = __ldg(src + lane);
-        x1[u] = __ldg(src + 32 + lane);
+        const size_t first = static_cast<size_t>(row[u]) * p.k + k0 + blk[u] * kBlockElems;
+        if (p.a_bf16) {
+          const uint2* src = reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned short*>(p.a) + first);
+          x0[u] = bf16x4_to_float4(__ldg(src + lane));
+          x1[u] = bf16x4_to_float4(__ldg(src + 32 + lane));
+        } else {
+          const float4* src = reinterpret_cast<const float4*>(p.a + first);
+          x0[u] = __ldg(src + lane);
+          x1[u] = __ldg(src + 32 + lane);
+        }
+        if (p.pro != kProNone) {
+          const size_t at = static_cast<size_t>(row[u]) * p.k + k0 + blk[u] * kBlockElems;
+          if (p.pro == kProSiluMul) {
+            const float4* up = reinterpret_cast<const float4*>(p.a2 + at);
+            x0[u] = silu_mul4(x0[u], __ldg(up + lane));
+            x1[u] = silu_mul4(x1[u], __ldg(up + 32 + lane));
+          } else {
+            const float4* nw = reinterpret_cast<const float4*>(p.a2 + k0 + blk[u] * kBlockElems);
+            x0[u] = scale4(x0[u], gain[row[u]], __ldg(nw + lane));
+            x1[u] = scale4(x1[u], gain[row[u]], __ldg(nw + 32 + lane));
+          }
+          if (writes_out) {
+            float4* dst = reinterpret_cast<float4*>(p.a_out + at);
+            dst[lane] = x0[u];
+            dst[32 + lane] = x1[u];
+          }
+        }
       }
     }
 #pragma unroll
@@ -287,35 +382,24 @@ template <typename ValueFn>
 __device__ __forceinline__ void finish_tile(const StagedParams& p, const StagedTarget& tg, int tile, int row0,
                                             int tile_rows, int chunk_y, int nsplit, unsigned int epoch, int tid,
                                             int nthreads, unsigned int* s_flag, ValueFn value) {
-  const int items = p.m * tile_rows;
+  // nthreads is a multiple of tile_rows (two or four warps per 16 rows): a thread keeps one
+  // tile row rr and takes the activation rows i0, i0 + per_pass, ...
+  const int per_pass = nthreads / tile_rows;
+  const int i0 = tid / tile_rows, rr = tid - i0 * tile_rows;
+  const bool row_ok = row0 + rr < tg.n;
+  const size_t col = static_cast<size_t>(row0 + rr);
   if (p.split_mode == kSplitCaller) {
-    float* cout = tg.c + static_cast<size_t>(chunk_y) * p.m * tg.n;
-    for (int idx = tid; idx < items; idx += nthreads) {
-      const int i = idx / tile_rows, rr = idx - i * tile_rows;
-      if (row0 + rr < tg.n) cout[static_cast<size_t>(i) * tg.n + row0 + rr] = value(i, rr);
-    }
+    float* cout = tg.c + static_cast<size_t>(chunk_y) * p.m * tg.n + col;
+#pragma unroll 1
+    for (int i = i0; i < p.m; i += per_pass)
+      if (row_ok) cout[static_cast<size_t>(i) * tg.n] = value(i, rr);
     return;
   }
-  // items <= 8 * 64 and nthreads >= 64: at most eight values per thread
-  constexpr int kMaxPer = 8;
-  float v[kMaxPer];
-#pragma unroll
-  for (int u = 0; u < kMaxPer; ++u) {
-    const int idx = tid + u * nthreads;
-    v[u] = 0.0f;
-    if (idx < items) {
-      const int i = idx / tile_rows, rr = idx - i * tile_rows;
-      v[u] = value(i, rr);
-    }
-  }
+  const size_t tile_floats = static_cast<size_t>(p.m) * tile_rows;
   if (nsplit > 1) {
-    const size_t tile_floats = static_cast<size_t>(items);
-    float* mine = p.part + (static_cast<size_t>(chunk_y) * p.total_tiles + tile) * tile_floats;
-#pragma unroll
-    for (int u = 0; u < kMaxPer; ++u) {
-      const int idx = tid + u * nthreads;
-      if (idx < items) __stcg(mine + idx, v[u]);
-    }
+    float* mine = p.part + (static_cast<size_t>(chunk_y) * p.total_tiles + tile) * tile_floats + rr;
+#pragma unroll 1
+    for (int i = i0; i < p.m; i += per_pass) __stcg(mine + i * tile_rows, value(i, rr));
     // The CTA's stores are ordered before the ticket by the barrier (CTA scope) and the
     // ticket's release (GPU scope); the last CTA's acquire on the ticket and its barrier
     // order the other chunks' stores before the loads below.  No thread needs a full fence.
@@ -328,50 +412,39 @@ __device__ __forceinline__ void finish_tile(const StagedParams& p, const StagedT
     }
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     if (*s_flag == 0u) return;
-    // chunk order, starting from zero: the order of the reference's gemm_vec_reduce
-    const float* base = p.part + static_cast<size_t>(tile) * tile_floats;
-#pragma unroll
-    for (int u = 0; u < kMaxPer; ++u) {
-      const int idx = tid + u * nthreads;
-      if (idx < items) {
-        float acc = 0.0f;
-        for (int y = 0; y < nsplit; ++y) acc += __ldcg(base + static_cast<size_t>(y) * p.total_tiles * tile_floats + idx);
-        v[u] = acc;
-      }
+  }
+  const bool tp = p.tp.world > 1;
+  // with ranks: every thread sends its own values to all ranks, then waits for the same
+  // elements of all ranks in its own slots: no barrier, no flag (tp_device.cuh)
+  const size_t mine_off = tp ? tp_slot_offset(p.tp, epoch, p.tp.rank) : 0;
+  const float* parts = p.part + static_cast<size_t>(tile) * tile_floats + rr;
+#pragma unroll 1
+  for (int i = i0; i < p.m; i += per_pass) {
+    float v;
+    if (nsplit > 1) {
+      // chunk order, starting from zero: the order of the reference's gemm_vec_reduce
+      v = 0.0f;
+#pragma unroll 1
+      for (int y = 0; y < nsplit; ++y) v += __ldcg(parts + static_cast<size_t>(y) * p.total_tiles * tile_floats + i * tile_rows);
+    } else {
+      v = value(i, rr);
+    }
+    if (!row_ok) continue;
+    const size_t e = static_cast<size_t>(i) * tg.n + col;
+    if (tp) {
+      tp_push(p.tp, mine_off + e, v);
+    } else {
+      store_output(p, tg.c, e, v);
+      if (tg.add_out != nullptr) tg.add_out[e] = tg.add_src[e] + v;
     }
   }
-  if (p.tp.world > 1) {
-    // every thread sends its own values to all ranks, then waits for the same elements of
-    // all ranks in its own slots: no barrier, no flag (tp_device.cuh)
-    const size_t mine = tp_slot_offset(p.tp, epoch, p.tp.rank);
-#pragma unroll
-    for (int u = 0; u < kMaxPer; ++u) {
-      const int idx = tid + u * nthreads;
-      if (idx < items) {
-        const int i = idx / tile_rows, rr = idx - i * tile_rows;
-        if (row0 + rr < tg.n) tp_push(p.tp, mine + static_cast<size_t>(i) * tg.n + row0 + rr, v[u]);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kMaxPer; ++u) {
-      const int idx = tid + u * nthreads;
-      if (idx < items) {
-        const int i = idx / tile_rows, rr = idx - i * tile_rows;
-        if (row0 + rr < tg.n) {
-          const size_t e = static_cast<size_t>(i) * tg.n + row0 + rr;
-          tg.c[e] = tp_wait_sum(p.tp, epoch, e);
-        }
-      }
-    }
-    return;
-  }
-#pragma unroll
-  for (int u = 0; u < kMaxPer; ++u) {
-    const int idx = tid + u * nthreads;
-    if (idx < items) {
-      const int i = idx / tile_rows, rr = idx - i * tile_rows;
-      if (row0 + rr < tg.n) tg.c[static_cast<size_t>(i) * tg.n + row0 + rr] = v[u];
-    }
+  if (!tp || !row_ok) return;
+#pragma unroll 1
+  for (int i = i0; i < p.m; i += per_pass) {
+    const size_t e = static_cast<size_t>(i) * tg.n + col;
+    const float v = tp_wait_sum(p.tp, epoch, e);
+    store_output(p, tg.c, e, v);
+    if (tg.add_out != nullptr) tg.add_out[e] = tg.add_src[e] + v;
   }
 }
 

@@ -74,6 +74,23 @@ def launch_unsharded(backend: CudaBackend, case: RowParallelCase, a: Buffer, w: 
     backend.LaunchKernel(backend.LoadKernel(name), KernelLaunch(buffers=[a, w, out], scalars=scalars))
 
 
+def launch_ffn_tail(backend: CudaBackend, case: RowParallelCase, gate: Buffer, up: Buffer, act: Buffer, w: Buffer,
+                    down: Buffer, residual: Buffer, final: Buffer, k_local: int, sharded: bool) -> None:
+    """The end of an FFN block as the reference's forward queues it (silu_mul, down projection,
+    residual add; src/models/qwen3_5/trunk.cpp:440-470 of the reference), on one rank's k range
+    with the sum over ranks (`sharded`) or on the whole k.  Through the deferred queue the three
+    steps become one launch."""
+    m, n = case.m, case.n
+    backend.LaunchKernel(backend.LoadKernel("silu_mul"), KernelLaunch(buffers=[gate, up, act], scalars=[m * k_local]))
+    if sharded:
+        kern = backend.LoadKernel(f"gemm_{case.fmt}_vec_allreduce")
+        backend.LaunchKernel(kern, KernelLaunch(buffers=[act, w, down], scalars=[m, n, k_local]))
+    else:
+        name = f"gemm_{case.fmt}_vec" if m == 1 else f"gemm_{case.fmt}_rows{m}"
+        backend.LaunchKernel(backend.LoadKernel(name), KernelLaunch(buffers=[act, w, down], scalars=[m, n, k_local, 1]))
+    backend.LaunchKernel(backend.LoadKernel("add"), KernelLaunch(buffers=[residual, down, final], scalars=[m * n]))
+
+
 def max_rel_err(y: np.ndarray, r: np.ndarray) -> float:
     y = np.asarray(y, dtype=np.float64)
     r = np.asarray(r, dtype=np.float64)

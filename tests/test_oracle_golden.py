@@ -148,3 +148,13 @@ def test_oracle_equals_reference_build(oracle, reference_oracle):
     q1, s1 = oracle.quantize_fp8(a)
     q2, s2 = reference_oracle.quantize_fp8(a)
     assert np.array_equal(q1, q2) and np.array_equal(s1, s2)
+
+
+def test_elementwise_steps_match_golden(oracle):
+    """RmsNormRef, SiluMulRef, AddRef (src/core/numerics/norm.cpp of the reference)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "elementwise_golden.npz"))
+    for i, eps in enumerate(g["rms_eps"]):
+        assert np.array_equal(oracle.rmsnorm(g["rms_x"], g["rms_w"], float(eps)), g["rms_y"][i])
+    assert np.array_equal(oracle.silu_mul(g["silu_g"], g["silu_u"]), g["silu_o"], equal_nan=True)
+    assert np.array_equal(oracle.add(g["add_a"], g["add_b"]), g["add_o"])
