@@ -214,7 +214,10 @@ def qgemv_table(stream, hbm_peak, only=None):
     for case in cases:
         fmt, m, n, k = case[:4]
         group = case[4] if len(case) > 4 else 1   # weight tensors per launch (Q4_K / Q6_K: tsr_gemv_group)
-        if group > 1 and group_backend is None:
+        # a case that names its group size, 1 included, goes through the merged-launch entry
+        # point (the launch splits k as it sees fit); the others through the typed launchers
+        grouped = len(case) > 4
+        if grouped and group_backend is None:
             from tessera_b200.backend import CreateBackend
             group_backend = CreateBackend(stream=stream.cuda_stream)
             group_backend.SetDeviceIndex(torch.cuda.current_device())
@@ -250,7 +253,7 @@ def qgemv_table(stream, hbm_peak, only=None):
         def launch(i):
             w = ctypes.c_void_p(ws[i % len(ws)].data_ptr())
             pa, pc = ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(c.data_ptr())
-            if group > 1:
+            if grouped:
                 wp = (ctypes.c_void_p * group)(*[ws[(i * group + j) % len(ws)].data_ptr() for j in range(group)])
                 cp = (ctypes.c_void_p * group)(*[o.data_ptr() for o in outs])
                 nn = (ctypes.c_uint64 * group)(*([n] * group))
@@ -292,13 +295,69 @@ def qgemv_table(stream, hbm_peak, only=None):
         gbs = (group * (wbytes + m * n * 4) + m * k * 4) / us / 1e3
         row = {"fmt": fmt, "m": m, "n": n, "k": k, "us": round(us, 2), "gbs": round(gbs, 1),
                "frac": round(gbs / hbm_peak, 3)}
-        if group > 1:
+        if grouped:
             row["weights_per_launch"] = group
         rows.append(row)
     cache.clear()
     if group_backend is not None:
         group_backend.close()
     return rows
+
+
+def moe_row(stream, hbm_peak, hidden=2048, inter=512, experts=256, top_k=8):
+    """Routed experts of one token and layer at the MoE configuration's shape (256 experts of
+    2048 -> 512 -> 2048 in Q4_K, eight selected): moe_experts_gate_up_q4k followed by
+    moe_experts_down_q4k, through the name-keyed launch, from a CUDA graph whose launches rotate
+    through disjoint expert sets (the tensors hold 453 MB, so nothing is served from L2).
+    Bytes: the selected experts' rows once (gate + up + down), activations and outputs."""
+    import torch
+    from tessera_b200.backend import CreateBackend, KernelLaunch
+    backend = CreateBackend(stream=stream.cuda_stream)
+    backend.SetDeviceIndex(torch.cuda.current_device())
+    backend.Init()
+    per_gu = inter * (hidden // 256) * 144
+    per_d = hidden * (inter // 256) * 144
+    g = np.random.default_rng(21)
+    one_gu = synth.q4k_weights(inter, hidden, seed=21, index=1)
+    one_d = synth.q4k_weights(hidden, inter, seed=21, index=2)
+    gate = backend.upload(np.tile(one_gu, experts))
+    up = backend.upload(np.tile(one_gu[::-1].copy(), experts))
+    down = backend.upload(np.tile(one_d, experts))
+    x = backend.upload((g.standard_normal(hidden) * 0.02).astype(np.float32))
+    wts = backend.upload(np.full(top_k, 1.0 / top_k, dtype=np.float32))
+    phi = backend.AllocateBuffer(top_k * inter * 4)
+    out = backend.AllocateBuffer(hidden * 4)
+    rounds = experts // top_k
+    perm = g.permutation(experts).astype(np.uint32)
+    ids = [backend.upload(perm[r * top_k:(r + 1) * top_k].copy()) for r in range(rounds)]
+    k_gu, k_d = backend.LoadKernel("moe_experts_gate_up_q4k"), backend.LoadKernel("moe_experts_down_q4k")
+
+    def layer(r):
+        backend.LaunchKernel(k_gu, KernelLaunch(buffers=[x, gate, up, ids[r], phi], scalars=[hidden, inter, top_k, per_gu, per_gu]))
+        backend.LaunchKernel(k_d, KernelLaunch(buffers=[phi, down, ids[r], wts, out], scalars=[hidden, inter, top_k, per_d, 0]))
+
+    with torch.cuda.stream(stream):
+        layer(0)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+            for r in range(rounds):
+                layer(r)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record(stream)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * rounds)
+    nbytes = top_k * (2 * per_gu + per_d) + hidden * 4 * 2 + top_k * inter * 4 * 2
+    backend.close()
+    return {"fmt": "moe_q4k", "hidden": hidden, "inter": inter, "experts": experts, "top_k": top_k, "launches": 2,
+            "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / hbm_peak, 3)}
 
 
 class Recorder:
@@ -518,7 +577,7 @@ def gpu_arm(args):
         templates = {}
         weights = []
         for p in plan:
-            n, k = workload.shard(p, rank, world)
+            n, k = workload.shard(p, rank, world) if args.shard_of <= 1 else workload.shard(p, 0, args.shard_of)
             key = (p.dtype, n, k)
             if key not in templates:
                 host = synth.q4k_weights(n, k, seed=3) if p.dtype == "q4k" else synth.q6k_weights(n, k, seed=3)
@@ -548,22 +607,63 @@ def gpu_arm(args):
         logits_buf = backend.AllocateBuffer(logits_n * 4)
         logits_host = np.empty(logits_n, dtype=np.float32)
 
+        x_odd = backend.upload(host_act["x"])  # a second copy of the hidden state, see record()
+
         def record(only=None):
             """The reference's launch sequence for the step, as ProjectBatch makes it; the
             row-parallel projections of a tensor-parallel run use the ids that end with the sum
-            over ranks instead of ProjectBatch + TpReduce."""
+            over ranks instead of ProjectBatch + TpReduce.  With `only` (a subset of tensor
+            names) the layers alternate between two copies of the hidden state, so that the
+            backend merges what it merges inside the whole step (the projections of one layer
+            that share their input) and not neighbours from different layers."""
             batch = LaunchBatch()
             proj = Projector(Recorder(backend, batch))
             for p, n, k, w in weights:
                 if only is not None and p.name not in only:
                     continue
                 dst = logits_buf if p.name == "output" else out_bufs[p.name]
+                act = dev_act[p.act]
+                if only is not None and p.act == "x" and p.layer % 2 == 1:
+                    act = x_odd
+                if world > 1 and p.kind == workload.ROW:
+                    kern = backend.LoadKernel(GemmKernelName(p.dtype) + "_allreduce")
+                    batch.add(kern, KernelLaunch(buffers=[act, w, dst], scalars=[1, n, k]))
+                    continue
+                proj.ProjectBatch(p.dtype, act, w, dst, 1, n, k)
+            return batch, proj
+
+        def record_with_elementwise():
+            """The same projections with the elementwise steps the reference's forward queues
+            around them (src/models/qwen3_5/trunk.cpp:279-322,440-470 of the reference): rmsnorm
+            before the projections that read the hidden state, silu_mul between ffn_gate / ffn_up
+            and ffn_down, the residual add after each row-parallel projection.  The hidden state
+            itself is not advanced (the adds write a scratch vector), so the step repeats."""
+            batch = LaunchBatch()
+            proj = Projector(Recorder(backend, batch))
+            hid = workload.HIDDEN
+            norm_w = backend.upload(np.ones(hid, dtype=np.float32))
+            scratch = backend.AllocateBuffer(hid * 4)
+            resid = backend.upload(host_act["x"][:hid])
+            rms, silu, add = backend.LoadKernel("rmsnorm"), backend.LoadKernel("silu_mul"), backend.LoadKernel("add")
+            eps = int(np.float32(1e-6).view(np.uint32))
+            normed_for = None   # (layer, half) whose rmsnorm is already queued
+            for p, n, k, w in weights:
+                dst = logits_buf if p.name == "output" else out_bufs[p.name]
+                if p.act == "x":
+                    half = (p.layer, p.name.startswith("ffn"))
+                    if half != normed_for:
+                        batch.add(rms, KernelLaunch(buffers=[resid, norm_w, dev_act["x"]], scalars=[1, hid, eps]))
+                        normed_for = half
+                if p.name == "ffn_down":
+                    batch.add(silu, KernelLaunch(buffers=[out_bufs["ffn_gate"], out_bufs["ffn_up"], dev_act["ffn"]], scalars=[k]))
                 if world > 1 and p.kind == workload.ROW:
                     kern = backend.LoadKernel(GemmKernelName(p.dtype) + "_allreduce")
                     batch.add(kern, KernelLaunch(buffers=[dev_act[p.act], w, dst], scalars=[1, n, k]))
-                    continue
-                proj.ProjectBatch(p.dtype, dev_act[p.act], w, dst, 1, n, k)
-            return batch, proj
+                else:
+                    proj.ProjectBatch(p.dtype, dev_act[p.act], w, dst, 1, n, k)
+                if p.kind == workload.ROW:
+                    batch.add(add, KernelLaunch(buffers=[resid, dst, scratch], scalars=[n]))
+            return batch, (proj, norm_w, scratch, resid)
 
         step, keep_step = record(only=set(args.only.split(",")) if args.only else None)
         dominant = ("ffn_gate", "ffn_up")
@@ -622,6 +722,29 @@ def gpu_arm(args):
             ms_dom = timed(run_dom, args.steps)
             _, devd1, _ = backend.LaunchStats()
 
+            # ---- the step with its elementwise neighbours, folded into the projection launches
+            # and as launches of their own (outside the metric: it is quoted on the projections)
+            with_elementwise = None
+            if deferred == 1 and not args.only and not args.no_elementwise:
+                full, keep_full = record_with_elementwise()
+
+                def run_full():
+                    backend.LaunchMany(full)
+                    backend.Flush()
+
+                with_elementwise = {"launches_queued_per_step": len(full)}
+                for mode, tag in ((1, "folded"), (3, "unfolded")):
+                    backend.SetDeferred(mode)
+                    for _ in range(3):
+                        run_full()
+                    backend.Synchronize()
+                    _, k0, _ = backend.LaunchStats()
+                    ms = timed(run_full, args.steps)
+                    _, k1, _ = backend.LaunchStats()
+                    with_elementwise["kernels_per_step_" + tag] = (k1 - k0) // args.steps
+                    with_elementwise["ms_per_step_" + tag] = ms / args.steps
+                backend.SetDeferred(deferred)
+
     value = args.steps / (ms_total * 1e-3)
     e2e_value = args.steps / (ms_e2e * 1e-3)
     kernels_per_step = (dev1 - dev0) // args.steps
@@ -645,13 +768,13 @@ def gpu_arm(args):
         "algorithmic_bytes": alg_bytes, "traffic": traffic,
         "launches_timed": args.steps * dom_kernels,
     }
-    step_bytes = workload.total_weight_bytes(rank, world)
+    step_bytes = workload.total_weight_bytes(rank, world) if args.shard_of <= 1 else workload.total_weight_bytes(0, args.shard_of)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None,
         "dtype": "f32 accumulate over Q4_K/Q6_K (int8 digits on the staged path)",
-        "data": "synthetic", "config": config_dict(world),
+        "data": "synthetic", "config": config_dict(world) if args.shard_of <= 1 else {"experiment": f"rank 0 shard of tp{args.shard_of} on one GPU"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
         "gpu_launches": kernels_per_step * args.steps,
         "kernels_per_step": kernels_per_step,
@@ -662,6 +785,8 @@ def gpu_arm(args):
         "step_hbm_gbs_per_gpu": step_bytes / (ms_total * 1e-3 / args.steps) / 1e9,
         "roofline": roofline, "clocks": clocks.summary(),
     }
+    if with_elementwise is not None:
+        line["with_elementwise"] = with_elementwise
     if parity is not None:
         line["tp_parity"] = parity
     if collective is not None:
@@ -673,6 +798,7 @@ def gpu_arm(args):
             buf.release()
         weights.clear()
         line["qgemv"] = qgemv_table(stream, peaks["hbm_gbs"])
+        line["qgemv"].append(moe_row(stream, peaks["hbm_gbs"]))
         from oracle.oracle import Oracle
         threads = os.cpu_count() or 1
         v, sample = run_cpu_sample(Oracle(), threads, 12.0)
@@ -697,13 +823,20 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, metavar="FMT:M:N:K[:G]",
-                    help="time one projection (q4k, q6k, mxfp4, fp8, w4a8) instead of the decode step, e.g. "
-                         "q4k:1:17408:5120; G > 1 (q4k, q6k): G weight tensors of that shape in one launch")
+                    help="time one projection (q4k, q6k, mxfp4, fp8, w4a8; or `moe` for the routed experts of one token) "
+                         "instead of the decode step, e.g. "
+                         "q4k:1:17408:5120; with G (q4k, q6k): G weight tensors of that shape in one merged launch\n"
+                         "that picks its own split of k")
     ap.add_argument("--only", default=None, metavar="NAMES",
                     help="experiment: the step holds only these projections (comma separated tensor names)")
     ap.add_argument("--no-qgemv", action="store_true", help="skip the single-projection table and the CPU baseline")
     ap.add_argument("--no-tp-parity", action="store_true",
                     help="experiment: skip the tensor-parallel parity check before the timed region")
+    ap.add_argument("--shard-of", type=int, default=1, metavar="W",
+                    help="experiment (1 GPU): the step holds rank 0's shard of a W-way tensor-parallel run, without "
+                         "the sums over ranks (per-launch costs of the small shapes; not the metric)")
+    ap.add_argument("--no-elementwise", action="store_true",
+                    help="skip the extra timing of the step with its rmsnorm / silu_mul / add neighbours")
     ap.add_argument("--no-collective-table", action="store_true",
                     help="skip the peer-memory / NCCL all-reduce comparison of a tensor-parallel run")
     args = ap.parse_args()
@@ -712,6 +845,11 @@ def main():
     elif args.case:
         import torch
         fields = args.case.split(":")
+        if fields[0] == "moe":
+            peaks, kind = measured_peaks()
+            torch.cuda.set_device(0)
+            print(json.dumps({"case": args.case, "peak_kind": kind, **moe_row(torch.cuda.Stream(), peaks["hbm_gbs"])}))
+            return
         fmt, (m, n, k) = fields[0], fields[1:4]
         only = (fmt, int(m), int(n), int(k)) + ((int(fields[4]),) if len(fields) > 4 else ())
         peaks, kind = measured_peaks()

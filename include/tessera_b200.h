@@ -137,9 +137,18 @@ int tsr_launch_many(tsr_context* ctx, const tsr_launch_desc* launches, size_t co
  *     gemm_vec_reduce of its partial buffer, becomes one launch that writes the
  *     final output (the caller's partial buffer is then not written);
  *   - consecutive Q4_K (or Q6_K) projections that read the same activations with
- *     the same m and k become one launch over up to four weight tensors.
+ *     the same m and k become one launch over up to four weight tensors;
+ *   - a silu_mul or rmsnorm whose output is the activation matrix of the Q4_K / Q6_K
+ *     projection(s) queued right after it (m <= 8) runs inside that launch's activation
+ *     staging; its output buffer is still written;
+ *   - an add that follows a single such projection (the _allreduce ids included) and
+ *     takes the projection's output as one operand runs in that launch's output stage;
+ *     the projection's own output buffer is still written.
+ *   A step is only folded when no buffer it writes overlaps one the merged launch
+ *   reads (an rmsnorm in place, for instance, stays a launch of its own).
  * A queue that repeats (same kernels, buffers and scalars) is replayed as a CUDA
- * graph from its second appearance on; on = 2 defers and merges without graphs.
+ * graph from its second appearance on; on = 2 defers and merges without graphs,
+ * on = 3 is on = 1 without the folding of silu_mul, rmsnorm and add.
  * Results stay within the projection tolerance of the separate launches but
  * are not bit-identical to them (another split of k).  Hosts that also call
  * the typed launchers below on the same stream must flush first. */
@@ -197,6 +206,23 @@ int tsr_round_bf16(float* x, uint64_t n, void* stream);
 /* add, fill: backend.hpp:150-152,258-260 */
 int tsr_add(const float* a, const float* b, float* o, uint64_t n, void* stream);
 int tsr_fill(int32_t* data, int32_t value, uint64_t n, void* stream);
+/* Routed experts of one token (contracts: src/backends/rocm/rocm_kernels.hpp:604-640 of the
+ * reference).  ids are read on the device; `experts` bounds them (an id beyond it contributes
+ * zero); strides are bytes per expert inside the 3-D expert tensors.
+ * moe_gate: wts = softmax(vals[0..top_k)), sig[0] = sigmoid(x . w). */
+int tsr_moe_gate(const float* vals, const float* x, const float* w, float* wts, float* sig, uint64_t top_k,
+                 uint64_t hidden, void* stream);
+/* moe_scale_add: o = a + f[idx] * b */
+int tsr_moe_scale_add(const float* a, const float* b, const float* f, float* o, uint64_t n, uint64_t idx,
+                      void* stream);
+/* moe_experts_gate_up_q4k: phi[slot][j] = silu(G_e[j] . x) * (U_e[j] . x), e = ids[slot] */
+int tsr_moe_experts_gate_up_q4k(const float* x, const void* gate, const void* up, const uint32_t* ids, float* phi,
+                                uint64_t hidden, uint64_t inter, uint64_t top_k, uint64_t gate_stride,
+                                uint64_t up_stride, uint64_t experts, void* stream);
+/* moe_experts_down_q4k (fmt 0) / _q6k (fmt 1): out[j] (+)= sum_slot wts[slot] * (D_e[j] . phi[slot]) */
+int tsr_moe_experts_down(int fmt, const float* phi, const void* down, const uint32_t* ids, const float* wts,
+                         float* out, uint64_t hidden, uint64_t inter, uint64_t top_k, uint64_t down_stride,
+                         uint64_t accumulate, uint64_t experts, void* stream);
 /* silu_mul: O = silu(G) * U, backend.hpp:257-260; SiluMulRef src/core/numerics/norm.cpp:211-225 */
 int tsr_silu_mul(const float* g, const float* u, float* o, uint64_t n, void* stream);
 /* rmsnorm: Y = X / sqrt(mean(X^2) + eps) * W per row, backend.hpp:212-216; RmsNormRef

@@ -467,6 +467,68 @@ int orc_silu_mul(const float* g, const float* u, float* o, size_t n) {
   return 0;
 }
 
+/* ------------------------------------------------------------ routed experts */
+
+/* moe_gate (rocm_kernels_basic.cpp:1896-1929): softmax over the selected logits and the
+ * sigmoid of the shared-expert gate x . w.  The device adds the products as a tree; here in order. */
+int orc_moe_gate(const float* vals, const float* x, const float* w, float* wts, float* sig, size_t top_k, size_t hidden) {
+  if (top_k == 0 || hidden == 0) return -2;
+  float dot = 0.0f;
+  for (size_t t = 0; t < hidden; ++t) dot += x[t] * w[t];
+  float m = -3.402823466e+38f;
+  for (size_t p = 0; p < top_k; ++p) m = fmaxf(m, vals[p]);
+  float sum = 0.0f;
+  for (size_t p = 0; p < top_k; ++p) sum += expf(vals[p] - m);
+  for (size_t p = 0; p < top_k; ++p) wts[p] = expf(vals[p] - m) / sum;
+  sig[0] = 1.0f / (1.0f + expf(-dot));
+  return 0;
+}
+
+/* moe_scale_add (rocm_kernels_basic.cpp:1931-1942): o = a + f[idx] * b */
+int orc_moe_scale_add(const float* a, const float* b, const float* f, float* o, size_t n, size_t idx) {
+  if (n == 0) return -2;
+  for (size_t i = 0; i < n; ++i) o[i] = a[i] + f[idx] * b[i];
+  return 0;
+}
+
+/* moe_experts_gate_up_q4k (rocm_kernels_moe.cpp:15-46): phi[slot][j] = silu(G_e[j] . x) * (U_e[j] . x),
+ * e = ids[slot]; the dots are those of GemmQ4KRef. */
+int orc_moe_experts_gate_up_q4k(const float* x, const uint8_t* gate, const uint8_t* up, const uint32_t* ids, float* phi,
+                                size_t hidden, size_t inter, size_t top_k, size_t gate_stride, size_t up_stride) {
+  if (hidden == 0 || hidden % 256 != 0 || inter == 0 || top_k == 0) return -2;
+  float* g = (float*)malloc(2 * inter * sizeof(float));
+  if (!g) return -1;
+  float* u = g + inter;
+  for (size_t slot = 0; slot < top_k; ++slot) {
+    const size_t e = ids[slot];
+    orc_gemm_q4k(x, gate + e * gate_stride, g, 1, inter, hidden);
+    orc_gemm_q4k(x, up + e * up_stride, u, 1, inter, hidden);
+    for (size_t j = 0; j < inter; ++j) phi[slot * inter + j] = (g[j] / (1.0f + expf(-g[j]))) * u[j];
+  }
+  free(g);
+  return 0;
+}
+
+/* moe_experts_down_q4k / _q6k (rocm_kernels_moe.cpp:48-107): out[j] (+)= sum_slot wts[slot] * (D_e[j] . phi[slot]),
+ * slots added in order. */
+int orc_moe_experts_down(int fmt, const float* phi, const uint8_t* down, const uint32_t* ids, const float* wts, float* out,
+                         size_t hidden, size_t inter, size_t top_k, size_t down_stride, int accumulate) {
+  if (hidden == 0 || inter == 0 || inter % 256 != 0 || top_k == 0 || (fmt != 0 && fmt != 1)) return -2;
+  float* d = (float*)malloc(2 * hidden * sizeof(float));
+  if (!d) return -1;
+  float* acc = d + hidden;
+  for (size_t j = 0; j < hidden; ++j) acc[j] = 0.0f;
+  for (size_t slot = 0; slot < top_k; ++slot) {
+    const size_t e = ids[slot];
+    if (fmt == 0) orc_gemm_q4k(phi + slot * inter, down + e * down_stride, d, 1, hidden, inter);
+    else orc_gemm_q6k(phi + slot * inter, down + e * down_stride, d, 1, hidden, inter);
+    for (size_t j = 0; j < hidden; ++j) acc[j] += wts[slot] * d[j];
+  }
+  for (size_t j = 0; j < hidden; ++j) out[j] = accumulate ? out[j] + acc[j] : acc[j];
+  free(d);
+  return 0;
+}
+
 /* --------------------------------------------------------------- W4A8 fold */
 
 /* E4M3 byte of E2M1 magnitude index i scaled by 2^-d; the table is derived

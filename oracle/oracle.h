@@ -78,6 +78,17 @@ int orc_rmsnorm(const float* x, const float* w, float* y, size_t rows, size_t co
 int orc_add(const float* a, const float* b, float* o, size_t n);                               /* norm.cpp:196-209 */
 int orc_silu_mul(const float* g, const float* u, float* o, size_t n);                          /* norm.cpp:211-225 */
 
+/* Routed-expert kernels of one token (contracts only the device backends hold:
+ * src/backends/rocm/rocm_kernels.hpp:604-640, rocm_kernels_moe.cpp:15-107,
+ * rocm_kernels_basic.cpp:1896-1942).  Strides are bytes per expert. */
+int orc_moe_gate(const float* vals, const float* x, const float* w, float* wts, float* sig, size_t top_k, size_t hidden);
+int orc_moe_scale_add(const float* a, const float* b, const float* f, float* o, size_t n, size_t idx);
+int orc_moe_experts_gate_up_q4k(const float* x, const uint8_t* gate, const uint8_t* up, const uint32_t* ids, float* phi,
+                                size_t hidden, size_t inter, size_t top_k, size_t gate_stride, size_t up_stride);
+/* fmt: 0 Q4_K, 1 Q6_K */
+int orc_moe_experts_down(int fmt, const float* phi, const uint8_t* down, const uint32_t* ids, const float* wts, float* out,
+                         size_t hidden, size_t inter, size_t top_k, size_t down_stride, int accumulate);
+
 /* ---- W4A8 fold path ----------------------------------------------------- */
 int orc_mxfp4_row_ref(const uint8_t* scales, uint8_t* wref, size_t rows, size_t cols);        /* mxfp4_row_ref.comp:26-40 */
 int orc_fold_mxfp4_to_fp8(const uint8_t* w, const uint8_t* scales, uint8_t* out, uint8_t* wref,

@@ -188,6 +188,56 @@ class Oracle:
         assert fn(_ptr(g), _ptr(u), _ptr(o), g.size) == 0
         return o
 
+    # ---- routed experts (device-only contracts; C restatement only)
+    def moe_gate(self, vals, x, w):
+        assert not self.reference
+        vals, x, w = (np.ascontiguousarray(v, dtype=np.float32) for v in (vals, x, w))
+        wts, sig = np.empty(vals.size, dtype=np.float32), np.empty(1, dtype=np.float32)
+        fn = self._fn("moe_gate", C.c_int, [_p, _p, _p, _p, _p, _sz, _sz])
+        assert fn(_ptr(vals), _ptr(x), _ptr(w), _ptr(wts), _ptr(sig), vals.size, x.size) == 0
+        return wts, sig
+
+    def moe_scale_add(self, a, b, f, idx):
+        assert not self.reference
+        a, b, f = (np.ascontiguousarray(v, dtype=np.float32) for v in (a, b, f))
+        o = np.empty_like(a)
+        fn = self._fn("moe_scale_add", C.c_int, [_p, _p, _p, _p, _sz, _sz])
+        assert fn(_ptr(a), _ptr(b), _ptr(f), _ptr(o), a.size, idx) == 0
+        return o
+
+    def moe_experts_gate_up_q4k(self, x, gate, up, ids, hidden, inter, gate_stride, up_stride):
+        assert not self.reference
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        phi = np.empty((ids.size, inter), dtype=np.float32)
+        fn = self._fn("moe_experts_gate_up_q4k", C.c_int, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz])
+        assert fn(_ptr(x), _ptr(gate), _ptr(up), _ptr(ids), _ptr(phi), hidden, inter, ids.size, gate_stride, up_stride) == 0
+        return phi
+
+    def moe_experts_down(self, fmt, phi, down, ids, wts, hidden, inter, down_stride, out=None):
+        assert not self.reference
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        wts = np.ascontiguousarray(wts, dtype=np.float32)
+        acc = out is not None
+        res = np.ascontiguousarray(out, dtype=np.float32).copy() if acc else np.empty(hidden, dtype=np.float32)
+        fn = self._fn("moe_experts_down", C.c_int, [C.c_int, _p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, C.c_int])
+        assert fn(fmt, _ptr(phi), _ptr(down), _ptr(ids), _ptr(wts), _ptr(res), hidden, inter, ids.size, down_stride, int(acc)) == 0
+        return res
+
+    def moe_experts_forward(self, x, experts, wts, gate, gate_per, up, up_per, down_dtype, down, down_per, hidden, inter, acc):
+        """The reference's CpuMoeExpertsForward (reference build only): acc + sum_c wts[c] * expert_c(x).
+        Gate and up are Q4_K; down_dtype is the reference's DType value (Q4K 10, Q6K 12)."""
+        assert self.reference
+        experts = np.ascontiguousarray(experts, dtype=np.uint32)
+        wts = np.ascontiguousarray(wts, dtype=np.float32)
+        out = np.ascontiguousarray(acc, dtype=np.float32).copy()
+        fn = self.lib.ref_moe_experts_forward
+        fn.restype = C.c_int
+        fn.argtypes = [_p, _p, _p, _sz, C.c_int, _p, _sz, _sz, C.c_int, _p, _sz, _sz, C.c_int, _p, _sz, _sz, _sz, _sz, _p]
+        rc = fn(_ptr(x), _ptr(experts), _ptr(wts), experts.size, 10, _ptr(gate), gate.nbytes, gate_per, 10, _ptr(up), up.nbytes,
+                up_per, down_dtype, _ptr(down), down.nbytes, down_per, hidden, inter, _ptr(out))
+        assert rc == 0, rc
+        return out
+
     def round_bf16(self, x: np.ndarray) -> np.ndarray:
         out = np.ascontiguousarray(x, dtype=np.float32).copy()
         fn = self._fn("round_bf16", C.c_int, [_p, _sz])

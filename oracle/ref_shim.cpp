@@ -13,6 +13,7 @@
 
 #include "core/loaders/tensor_slice.hpp"
 #include "core/numerics/gemm.hpp"
+#include "core/numerics/moe_cpu.hpp"
 #include "core/numerics/norm.hpp"
 #include "core/numerics/quant.hpp"
 
@@ -114,6 +115,19 @@ int ref_add(const float* a, const float* b, float* o, std::size_t n) {
 }
 int ref_silu_mul(const float* g, const float* u, float* o, std::size_t n) {
   return Code(tc::SiluMulRef({g, n}, {u, n}, {o, n}, n));
+}
+
+// CpuMoeExpertsForward (src/core/numerics/moe_cpu.cpp:66-131): acc += sum_c wts[c] * expert_c(x).
+// gate_dtype / up_dtype / down_dtype are the reference's DType values (Q4K 10, Q6K 12).
+int ref_moe_experts_forward(const float* x, const std::uint32_t* experts, const float* wts, std::size_t count,
+                            int gate_dtype, const std::uint8_t* gate, std::size_t gate_bytes, std::size_t gate_per,
+                            int up_dtype, const std::uint8_t* up, std::size_t up_bytes, std::size_t up_per,
+                            int down_dtype, const std::uint8_t* down, std::size_t down_bytes, std::size_t down_per,
+                            std::size_t hidden, std::size_t inter, float* acc) {
+  return Code(tc::CpuMoeExpertsForward({x, hidden}, {experts, count}, {wts, count}, static_cast<tessera::DType>(gate_dtype),
+                                       Bytes(gate, gate_bytes), gate_per, static_cast<tessera::DType>(up_dtype),
+                                       Bytes(up, up_bytes), up_per, static_cast<tessera::DType>(down_dtype),
+                                       Bytes(down, down_bytes), down_per, hidden, inter, {acc, hidden}));
 }
 
 // SliceTensor2D (src/core/loaders/tensor_slice.cpp:105-159).  Returns the slice's byte count, or

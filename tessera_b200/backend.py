@@ -242,7 +242,8 @@ class CudaBackend:
     def SetDeferred(self, mode: int) -> None:
         """0: every LaunchKernel is issued at once; 1: launches queue until the next copy or
         synchronisation, are merged where the kernels allow it, and a repeating queue is
-        replayed as a CUDA graph; 2: as 1 without graphs."""
+        replayed as a CUDA graph; 2: as 1 without graphs; 3: as 1 without running silu_mul,
+        rmsnorm and add inside the projection launches."""
         self._check(self._lib.tsr_set_deferred(self._need(), mode))
 
     def Flush(self) -> None:

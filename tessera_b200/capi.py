@@ -99,6 +99,10 @@ SIGNATURES = {
     "tsr_add": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
     "tsr_fill": (C.c_int, [_vp, C.c_int32, _u64, _vp]),
     "tsr_silu_mul": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
+    "tsr_moe_gate": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u64, _u64, _vp]),
+    "tsr_moe_scale_add": (C.c_int, [_vp, _vp, _vp, _vp, _u64, _u64, _vp]),
+    "tsr_moe_experts_gate_up_q4k": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64, _u64, _u64, _vp]),
+    "tsr_moe_experts_down": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64, _u64, _u64, _vp]),
     "tsr_rmsnorm": (C.c_int, [_vp, _vp, _vp, _u64, _u64, C.c_float, _vp]),
     "tsr_dequantize": (C.c_int, [C.c_int, _vp, _vp, _vp, _u64, _u64, _vp]),
     "tsr_slice_shape": (C.c_int, [C.c_int, C.c_int, _u64, _u64, C.c_int, C.c_int, C.POINTER(_u64), C.POINTER(_u64),

@@ -451,6 +451,7 @@ int tsr_set_deferred(tsr_context* ctx, int on) {
   if (int s = tsr::flush_pending(ctx)) return s;
   ctx->deferred = on != 0;
   ctx->use_graphs = on != 2;
+  ctx->fold_elementwise = on != 3;
   return tsr::kOk;
 }
 

@@ -68,6 +68,7 @@ struct tsr_context {
   // it, and a queue that repeats is replayed as a CUDA graph.
   bool deferred = false;
   bool use_graphs = true;
+  bool fold_elementwise = true;  // silu_mul, rmsnorm and add may run inside the projection launches
   std::vector<tsr::PendingLaunch> pending;
   std::unordered_map<uint64_t, tsr::CachedGraph> graphs;
   std::unordered_map<uint64_t, int> seen_queues;  // hash -> times flushed without a graph

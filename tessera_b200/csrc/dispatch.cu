@@ -494,6 +494,70 @@ int k_gemm_bf16(const Args& a) {
   return convert_f32_to_bf16(c32, C, m * n, a.stream);
 }
 
+// moe_gate: buffers vals (top_k), x (hidden), w (hidden), wts (top_k), sig (1); scalars top_k, hidden
+// (src/backends/rocm/rocm_kernels.hpp:604-612).
+int k_moe_gate(const Args& a) {
+  if (!shape(a, 5, 2)) return kInvalidArgument;
+  const uint64_t top_k = a.sc[0], hidden = a.sc[1];
+  if (!dims_ok(top_k, hidden, 1) || !holds(a, 0, top_k * 4) || !holds(a, 1, hidden * 4) || !holds(a, 2, hidden * 4) ||
+      !holds(a, 3, top_k * 4) || !holds(a, 4, 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_moe_gate(static_cast<const float*>(a.buf[0]), static_cast<const float*>(a.buf[1]),
+                      static_cast<const float*>(a.buf[2]), static_cast<float*>(const_cast<void*>(a.buf[3])),
+                      static_cast<float*>(const_cast<void*>(a.buf[4])), top_k, hidden, a.stream);
+}
+
+// moe_scale_add: buffers a, b, f, o; scalars n, idx: o = a + f[idx] * b (rocm_kernels.hpp:613-617).
+int k_moe_scale_add(const Args& a) {
+  if (!shape(a, 4, 2)) return kInvalidArgument;
+  const uint64_t n = a.sc[0], idx = a.sc[1];
+  if (n == 0 || idx > kMaxDim || !holds(a, 0, n * 4) || !holds(a, 1, n * 4) || !holds(a, 2, (idx + 1) * 4) ||
+      !holds(a, 3, n * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_moe_scale_add(static_cast<const float*>(a.buf[0]), static_cast<const float*>(a.buf[1]),
+                           static_cast<const float*>(a.buf[2]), static_cast<float*>(const_cast<void*>(a.buf[3])), n, idx,
+                           a.stream);
+}
+
+// moe_experts_gate_up_q4k: buffers x (hidden), gate, up (3-D Q4_K: experts x inter rows), ids (top_k u32),
+// phi (top_k x inter); scalars hidden, inter, top_k, gate_stride, up_stride (bytes per expert)
+// (rocm_kernels.hpp:618-627).  The number of experts is what the weight buffers hold.
+int k_moe_gate_up(const Args& a) {
+  if (!shape(a, 5, 5)) return kInvalidArgument;
+  const uint64_t hidden = a.sc[0], inter = a.sc[1], top_k = a.sc[2], gs = a.sc[3], us = a.sc[4];
+  if (!dims_ok(hidden, inter, top_k) || hidden % 256 != 0) return kInvalidArgument;
+  const uint64_t per = inter * (hidden / 256) * 144;
+  if (gs < per || us < per) return kInvalidArgument;
+  const uint64_t eg = (a.bytes[1] - per) / gs + 1, eu = (a.bytes[2] - per) / us + 1;
+  if (a.bytes[1] < per || a.bytes[2] < per) return kInvalidArgument;
+  if (!holds(a, 0, hidden * 4) || !holds(a, 3, top_k * 4) || !holds(a, 4, top_k * inter * 4)) return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_moe_experts_gate_up_q4k(static_cast<const float*>(a.buf[0]), a.buf[1], a.buf[2],
+                                     static_cast<const uint32_t*>(a.buf[3]), static_cast<float*>(const_cast<void*>(a.buf[4])),
+                                     hidden, inter, top_k, gs, us, eg < eu ? eg : eu, a.stream);
+}
+
+// moe_experts_down_q4k / _q6k: buffers phi (top_k x inter), down (3-D: experts x hidden rows), ids, wts
+// (top_k), out (hidden); scalars hidden, inter, top_k, down_stride, accumulate
+// (rocm_kernels.hpp:628-640; src/models/qwen3_5/moe.cpp:414-421).
+template <int FMT>
+int k_moe_down(const Args& a) {
+  if (!shape(a, 5, 5)) return kInvalidArgument;
+  const uint64_t hidden = a.sc[0], inter = a.sc[1], top_k = a.sc[2], ds = a.sc[3], accumulate = a.sc[4];
+  if (!dims_ok(hidden, inter, top_k) || inter % 256 != 0) return kInvalidArgument;
+  const uint64_t per = hidden * (inter / 256) * (FMT == 0 ? 144 : 210);
+  if (ds < per || a.bytes[1] < per) return kInvalidArgument;
+  const uint64_t experts = (a.bytes[1] - per) / ds + 1;
+  if (!holds(a, 0, top_k * inter * 4) || !holds(a, 2, top_k * 4) || !holds(a, 3, top_k * 4) || !holds(a, 4, hidden * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_moe_experts_down(FMT, static_cast<const float*>(a.buf[0]), a.buf[1], static_cast<const uint32_t*>(a.buf[2]),
+                              static_cast<const float*>(a.buf[3]), static_cast<float*>(const_cast<void*>(a.buf[4])), hidden,
+                              inter, top_k, ds, accumulate, experts, a.stream);
+}
+
 struct Entry {
   const char* name;
   int (*fn)(const Args&);
@@ -536,6 +600,11 @@ const Entry kTable[] = {
     {"gemm_q4k_vec_allreduce", k_block_allreduce<144, false>},
     {"gemm_q6k_vec_allreduce", k_block_allreduce<210, true>},
     {"allreduce_sum", k_allreduce_sum},
+    {"moe_gate", k_moe_gate},
+    {"moe_scale_add", k_moe_scale_add},
+    {"moe_experts_gate_up_q4k", k_moe_gate_up},
+    {"moe_experts_down_q4k", k_moe_down<0>},
+    {"moe_experts_down_q6k", k_moe_down<1>},
     {"gemm_q4k_bf16", k_gemm_bf16<0>},
     {"gemm_q6k_bf16", k_gemm_bf16<1>},
     {"gemm_mxfp4_bf16", k_gemm_bf16<2>},
@@ -622,9 +691,9 @@ bool fuse_elementwise() {
 }
 
 // q[i] as a step that can run inside the activation staging of the projection after it.
-bool as_prologue(const std::vector<PendingLaunch>& q, size_t i, Prologue* pro, const float** in, uint64_t* rows,
-                 uint64_t* cols) {
-  if (!fuse_elementwise() || i + 1 >= q.size()) return false;
+bool as_prologue(const tsr_context* ctx, const std::vector<PendingLaunch>& q, size_t i, Prologue* pro, const float** in,
+                 uint64_t* rows, uint64_t* cols) {
+  if (!ctx->fold_elementwise || !fuse_elementwise() || i + 1 >= q.size()) return false;
   const PendingLaunch& op = q[i];
   Projection next;
   if (!as_projection(q, i + 1, &next)) return false;
@@ -654,9 +723,9 @@ bool as_prologue(const std::vector<PendingLaunch>& q, size_t i, Prologue* pro, c
 }
 
 // q[i] as an add that can run in the output stage of the single projection `p` before it.
-bool as_epilogue_add(const std::vector<PendingLaunch>& q, size_t i, const Projection& p, const float* act, size_t act_bytes,
-                     const Prologue* pro, GroupTarget* t) {
-  if (!fuse_elementwise() || i >= q.size() || !is_named(q[i], "add")) return false;
+bool as_epilogue_add(const tsr_context* ctx, const std::vector<PendingLaunch>& q, size_t i, const Projection& p,
+                     const float* act, size_t act_bytes, const Prologue* pro, GroupTarget* t) {
+  if (!ctx->fold_elementwise || !fuse_elementwise() || i >= q.size() || !is_named(q[i], "add")) return false;
   const PendingLaunch& op = q[i];
   const size_t bytes = p.m * p.t.n * 4;
   if (op.sc[0] != p.m * p.t.n) return false;
@@ -690,7 +759,7 @@ int issue_queue(tsr_context* ctx, const std::vector<PendingLaunch>& q) {
     Prologue pro{};
     const float* pro_in = nullptr;
     uint64_t pro_rows = 0, pro_cols = 0;
-    const bool has_pro = as_prologue(q, i, &pro, &pro_in, &pro_rows, &pro_cols);
+    const bool has_pro = as_prologue(ctx, q, i, &pro, &pro_in, &pro_rows, &pro_cols);
     const size_t start = has_pro ? i + 1 : i;
     Projection first;
     if (!as_projection(q, start, &first)) {
@@ -734,7 +803,7 @@ int issue_queue(tsr_context* ctx, const std::vector<PendingLaunch>& q) {
     if (count == 1) {
       Projection only = first;
       only.t = t[0];
-      if (as_epilogue_add(q, end, only, has_pro ? pro_in : first.a, a_bytes, has_pro ? &pro : nullptr, &t[0])) ++end;
+      if (as_epilogue_add(ctx, q, end, only, has_pro ? pro_in : first.a, a_bytes, has_pro ? &pro : nullptr, &t[0])) ++end;
     }
     // with a prologue the launch reads the prologue's input; the projections' A is its output
     const float* act = has_pro ? pro_in : first.a;
@@ -758,7 +827,7 @@ uint64_t mix(uint64_t h, uint64_t v) {
 }
 
 uint64_t queue_hash(const tsr_context* ctx, const std::vector<PendingLaunch>& q) {
-  uint64_t h = mix(0x243F6A8885A308D3ull, reinterpret_cast<uintptr_t>(ctx->tp));
+  uint64_t h = mix(0x243F6A8885A308D3ull, reinterpret_cast<uintptr_t>(ctx->tp) ^ (ctx->fold_elementwise ? 1u : 0u));
   for (const PendingLaunch& op : q) {
     h = mix(h, (static_cast<uint64_t>(op.kernel) << 40) ^ (static_cast<uint64_t>(op.grid_y) << 8) ^
                    (static_cast<uint64_t>(op.nbuf) << 4) ^ static_cast<uint64_t>(op.nsc));

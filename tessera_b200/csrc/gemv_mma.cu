@@ -80,6 +80,10 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams 
   uint64_t* empty = full + p.stages;
   const unsigned char* zero_page = reinterpret_cast<const unsigned char*>(empty + p.stages);  // 16 zero bytes
   unsigned int* s_words = reinterpret_cast<unsigned int*>(empty + p.stages) + 4;              // [0] flag, [1] epoch
+  // cluster split: arrival barriers and receive buffers of the chunk-0 CTA, one per tile of the CTA
+  uint64_t* recv_bar = empty + p.stages + 4;
+  float* recv = reinterpret_cast<float*>(empty + p.stages + 8);
+  const bool clustered = p.split_mode == kSplitCluster && gridDim.y > 1;
   const int b0 = blockIdx.y * p.per;
   const int my_tiles = (p.total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
                        static_cast<int>(gridDim.x);
@@ -95,9 +99,13 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams 
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], p.rgs);
     }
+    if (clustered)
+      for (int t = 0; t < kClusterTiles; ++t) mbar_init(&recv_bar[t], gridDim.y - 1);
     mbar_fence_init();
   }
   __syncthreads();
+  // no CTA of the cluster signals a peer's barrier before that peer has initialised it
+  if (clustered) cluster_sync_all();
   // The producer walks the CTA's chunk sequence (tile after tile, chunk after chunk) with a
   // cursor: map and first row change only when a tile begins.
   int p_it = 0, p_c = 0, p_row0 = 0;
@@ -317,6 +325,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams 
     const StagedTarget tg = target_by_index(p, target_of_tile(p, tile));
     const int row0 = (tile - tg.tile_begin) * kTileRows;
     finish_tile(p, tg, tile, row0, kTileRows, blockIdx.y, gridDim.y, epoch, tid, kConsumerThreads, s_words,
+                it, recv_bar, recv, &g_wait_timeouts,
                 [&](int i, int rr) {
                   float v = 0.0f;
                   for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
@@ -383,16 +392,30 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
   auto chunks_of = [](uint64_t per) -> uint64_t { return (per + kChunkBlocks - 1) / kChunkBlocks; };
   auto fixed = [&](int rgs, uint64_t per) -> size_t {
     const uint64_t nblk_pad = chunks_of(per) * kChunkBlocks;
+    // receive buffers of a cluster split: one per tile of the CTA and chunk beyond the first
+        const uint64_t chunks = per != 0 ? nb / per : 1;
+        const size_t recv = caller_split == 0 && chunks > 1 ? kClusterTiles * (chunks - 1) * m * 16 * rgs * 4 : 0;
     return nblk_pad * ncols * (256 + 16) + nblk_pad * kMaxCols * 4 + (SETS - 1) * rgs * 32 * NCG * 4 * 4 +
-           16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128;
+           16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128 + recv;
   };
   auto stage_bytes = [](int rgs) -> size_t { return static_cast<size_t>(rgs) * kGroupBytes; };
   static const int regs = kernel_registers(gemv_q4k_staged_kernel<NCG, SETS>);
   uint64_t rows[kMaxGroup];
   for (int i = 0; i < count; ++i) rows[i] = t[i].n;
   GroupPlan plan;
-  if (!plan_group(rows, count, nb, static_cast<int>(m), caller_split, SETS, 0, regs, 12, 0.5, fixed, stage_bytes, chunks_of, &plan))
+  if (!plan_group_cached(100 + NCG * 10 + SETS, rows, count, nb, static_cast<int>(m), caller_split, SETS, 0, regs, 12, 0.5, fixed, stage_bytes, chunks_of, &plan))
     return kUnsupportedFeature;
+  if (plan.cluster) {
+    // the cluster must be launchable (and, with ranks waiting on one another, all of the
+    // launch's clusters resident at once); else the chunks meet through global memory
+    if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q4k_staged_kernel<NCG, SETS>), kMaxSmem)) return rc;
+    const int fit = max_active_clusters(gemv_q4k_staged_kernel<NCG, SETS>, (SETS * plan.rgs + 1) * 32, plan.smem, plan.split);
+    const bool with_ranks = tp != nullptr && tp->world > 1;
+    if (fit < 1 || (with_ranks && fit < plan.grid_x)) {
+      if (!plan_group_cached(100 + NCG * 10 + SETS, rows, count, nb, static_cast<int>(m), caller_split, SETS, 0, regs, 12, 0.5, fixed, stage_bytes, chunks_of, &plan, false))
+        return kUnsupportedFeature;
+    }
+  }
   if (cost_only != nullptr) {
     *cost_only = plan.cost;
     return kOk;
@@ -417,7 +440,7 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
   p.rgs = plan.rgs;
   p.sets = SETS;
   p.ntargets = count;
-  p.split_mode = caller_split != 0 ? kSplitCaller : kSplitInLaunch;
+  p.split_mode = caller_split != 0 ? kSplitCaller : (plan.cluster ? kSplitCluster : kSplitInLaunch);
   Q4KMaps maps{};
   const uint64_t th = 16u * plan.rgs;
   uint64_t tiles = 0;
@@ -462,7 +485,7 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
     p.tickets = scratch->tickets;
   }
   if (tp != nullptr && tp->world > 1) {
-    if (m * t[0].n > tp->capacity || count != 1 || p.split_mode != kSplitInLaunch) return kUnsupportedFeature;
+    if (m * t[0].n > tp->capacity || count != 1 || p.split_mode == kSplitCaller) return kUnsupportedFeature;
     // every CTA of the launch must be resident at once: a tile waits for its peers' values
     if (static_cast<uint64_t>(plan.grid_x) * plan.split > static_cast<uint64_t>(device_sms()) * plan.occ)
       return kUnsupportedFeature;
@@ -478,8 +501,8 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
     if (mode == 2 && plan.occ < 2) p.pdl = 0;
     if (mode == 3 && plan.sets != 4) p.pdl = 0;
   }
-  launch_kernel(gemv_q4k_staged_kernel<NCG, SETS>, grid, dim3((SETS * plan.rgs + 1) * 32), plan.smem, st,
-                p.pdl != 0, maps, p);
+  launch_kernel_cluster_y(gemv_q4k_staged_kernel<NCG, SETS>, grid, dim3((SETS * plan.rgs + 1) * 32), plan.smem, st,
+                        p.pdl != 0, plan.cluster ? static_cast<unsigned>(plan.split) : 1u, maps, p);
   return check_launch();
 }
 

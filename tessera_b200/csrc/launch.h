@@ -60,6 +60,34 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same with thread-block clusters of `cluster_y` consecutive CTAs along y.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_cluster_y(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                           cudaStream_t stream, bool pdl, unsigned cluster_y, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned count = 0;
+  if (cluster_y > 1) {
+    attr[count].id = cudaLaunchAttributeClusterDimension;
+    attr[count].val.clusterDim.x = 1;
+    attr[count].val.clusterDim.y = cluster_y;
+    attr[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  if (pdl) {
+    attr[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = count;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // The same with thread-block clusters of `cluster` consecutive CTAs along x.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

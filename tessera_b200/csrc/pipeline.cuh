@@ -46,6 +46,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// ---- thread-block clusters: a barrier over all threads of the cluster, a peer CTA's
+// shared memory (distributed shared memory), and an mbarrier signalled across CTAs
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of `local` (a shared-memory address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// Arrives (release, cluster scope) on an mbarrier in a peer CTA's shared memory.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{.reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p;}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Host-visible error word (pinned, mapped memory shared by every kernel file of the
 // library): a wait that gives up also raises it, so the host learns of a failure by
 // reading one word of its own memory instead of copying counters back from the device.
@@ -60,6 +88,16 @@ static inline int set_host_error_word(unsigned int* word) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* timeouts) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
     if (mbar_try_wait(bar, parity)) return true;
+  atomicAdd(timeouts, 1u);
+  if (g_host_error_word != nullptr) *reinterpret_cast<volatile unsigned int*>(g_host_error_word) = 1u;
+  return false;
+}
+
+// The same with an acquire at cluster scope: what peer CTAs stored before their arrival
+// (mbar_arrive_remote) is visible after it.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, unsigned int* timeouts) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    if (mbar_try_wait_cluster(bar, parity)) return true;
   atomicAdd(timeouts, 1u);
   if (g_host_error_word != nullptr) *reinterpret_cast<volatile unsigned int*>(g_host_error_word) = 1u;
   return false;

@@ -11,6 +11,8 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 #include "codec.cuh"
 #include "launch.h"
@@ -42,7 +44,12 @@ struct StagedTarget {
 enum : int {
   kSplitCaller = 0,    // chunk y of k goes to region y of each target (stride m*n): the caller adds them
   kSplitInLaunch = 1,  // the last CTA of a tile to finish adds the chunks in chunk order
+  // The CTAs (x, 0..split-1) form a thread-block cluster: chunks 1.. store their sums into the
+  // shared memory of chunk 0's CTA and signal an mbarrier there; that CTA adds them in chunk
+  // order.  A CTA works through at most kClusterTiles tiles (one receive buffer per tile).
+  kSplitCluster = 2,
 };
+constexpr int kClusterTiles = 2;
 
 struct StagedParams {
   const float* a;
@@ -381,7 +388,8 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
 template <typename ValueFn>
 __device__ __forceinline__ void finish_tile(const StagedParams& p, const StagedTarget& tg, int tile, int row0,
                                             int tile_rows, int chunk_y, int nsplit, unsigned int epoch, int tid,
-                                            int nthreads, unsigned int* s_flag, ValueFn value) {
+                                            int nthreads, unsigned int* s_flag, int it, uint64_t* recv_bar,
+                                            float* recv, unsigned int* timeouts, ValueFn value) {
   // nthreads is a multiple of tile_rows (two or four warps per 16 rows): a thread keeps one
   // tile row rr and takes the activation rows i0, i0 + per_pass, ...
   const int per_pass = nthreads / tile_rows;
@@ -396,7 +404,22 @@ __device__ __forceinline__ void finish_tile(const StagedParams& p, const StagedT
     return;
   }
   const size_t tile_floats = static_cast<size_t>(p.m) * tile_rows;
-  if (nsplit > 1) {
+  const bool clustered = p.split_mode == kSplitCluster && nsplit > 1;
+  const float* received = recv + static_cast<size_t>(it) * (nsplit - 1) * tile_floats + rr;  // tile `it` of this CTA
+  if (clustered) {
+    if (chunk_y != 0) {
+      const uint32_t remote =
+          cluster_map(smem_u32(recv + (static_cast<size_t>(it) * (nsplit - 1) + (chunk_y - 1)) * tile_floats + rr), 0);
+#pragma unroll 1
+      for (int i = i0; i < p.m; i += per_pass) st_cluster_f32(remote + i * tile_rows * 4, value(i, rr));
+      // the barrier orders the CTA's stores before thread 0's arrival, whose release (cluster
+      // scope) and the receiver's acquire order them before the receiver's loads
+      asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+      if (tid == 0) mbar_arrive_remote(cluster_map(smem_u32(recv_bar + it), 0));
+      return;
+    }
+    mbar_wait_cluster(recv_bar + it, 0, timeouts);  // bounded; on a timeout the sums below are wrong and the host is told
+  } else if (nsplit > 1) {
     float* mine = p.part + (static_cast<size_t>(chunk_y) * p.total_tiles + tile) * tile_floats + rr;
 #pragma unroll 1
     for (int i = i0; i < p.m; i += per_pass) __stcg(mine + i * tile_rows, value(i, rr));
@@ -421,7 +444,11 @@ __device__ __forceinline__ void finish_tile(const StagedParams& p, const StagedT
 #pragma unroll 1
   for (int i = i0; i < p.m; i += per_pass) {
     float v;
-    if (nsplit > 1) {
+    if (clustered) {
+      v = value(i, rr);  // chunk 0, then the others in chunk order
+#pragma unroll 1
+      for (int y = 1; y < nsplit; ++y) v += received[(y - 1) * tile_floats + i * tile_rows];
+    } else if (nsplit > 1) {
       // chunk order, starting from zero: the order of the reference's gemm_vec_reduce
       v = 0.0f;
 #pragma unroll 1
@@ -527,6 +554,7 @@ inline bool plan_staged(uint64_t n, uint64_t split, uint64_t per, uint64_t nchun
 // ---- launch plan of the multi-target kernels (Q4_K, Q6_K)
 struct GroupPlan {
   int rgs, stages, sets, split, grid_x, occ;
+  bool cluster;  // split > 1 inside the launch: the chunks of a tile form a cluster (else: tickets)
   size_t smem;
   double cost;  // modelled microseconds
 };
@@ -547,7 +575,7 @@ inline int env_plan_int(const char* name, int fallback) {
 template <typename FixedFn, typename StageFn, typename ChunksFn>
 inline bool plan_group(const uint64_t* n, int count, uint64_t nb, int m, uint64_t fixed_split, int sets,
                        int fixed_rgs, int regs_per_thread, int max_want, double block_us, FixedFn fixed,
-                       StageFn stage_bytes, ChunksFn nchunks, GroupPlan* out) {
+                       StageFn stage_bytes, ChunksFn nchunks, GroupPlan* out, bool allow_cluster = true) {
   const int sms = device_sms();
   // Measured on B200 (Q4_K, m = 1): a busy SM gets through one 16-row x 256-column block in
   // about 0.053 us whatever the tiling; one warp needs `block_us` (0.5 us Q4_K) for each block
@@ -559,6 +587,13 @@ inline bool plan_group(const uint64_t* n, int count, uint64_t nb, int m, uint64_
   // only wins where it shortens a long chain, as for Q6_K rows of 68 blocks).
   const double kUnitUs = 0.053 * (block_us / 0.5), kPrefixUs = 2.6, kStageRoundUs = 0.25;
   const double kTicketUs = 3.5, kTicketTileUs = 1.5, kWaveUs = 2.0, kTileUs = 0.5;
+  const double kClusterUs = env_plan_int("TSR_CLUSTER_NS", 1000) * 1e-3, kClusterTileUs = 0.3;
+  // Off unless TSR_CLUSTER=1: measured on B200 the cluster plans this model prefers (5120 rows,
+  // k = 17408 / 6144: 48-row tiles, four chunks, three CTAs per SM) ran 5-9 us slower than the
+  // unsplit four-set plan (22.7 against 16.9 us, Q6_K 34.8 against 25.8 us): three CTAs per SM
+  // leave each consumer set one or two ring slots, which does not cover the HBM latency, and
+  // the SMs are no more evenly loaded than with 48-row tiles alone.
+  const bool use_cluster = allow_cluster && env_plan_int("TSR_CLUSTER", 0) != 0;
   const int ring_max = env_plan_int("TSR_RING_MAX", max_want);
   const int force_rgs = env_plan_int("TSR_RGS", 0), force_split = env_plan_int("TSR_SPLIT", 0);
   const int force_grid = env_plan_int("TSR_GRID", 0), force_occ = env_plan_int("TSR_OCC", 0);
@@ -618,7 +653,13 @@ inline bool plan_group(const uint64_t* n, int count, uint64_t nb, int m, uint64_
           // every tile of a CTA ends with the exchange between the sets and the output pass
           double cost = kPrefixUs + staging + (throughput > chain ? throughput : chain) + (waves - 1) * kWaveUs +
                         kTileUs * static_cast<double>(waves * tiles_per_cta) + (sets == 4 ? 0.4 : 0.0);
-          if (split > 1 && fixed_split == 0) cost += kTicketUs + kTicketTileUs * static_cast<double>(tiles_per_cta);
+          // the chunks of a tile meet through the shared memory of a cluster where a CTA has few
+          // enough tiles for its receive buffers, else through tickets in global memory
+          const bool cluster = split > 1 && fixed_split == 0 && tiles_per_cta <= static_cast<uint64_t>(kClusterTiles) &&
+                               use_cluster;
+          if (split > 1 && fixed_split == 0)
+            cost += cluster ? kClusterUs + kClusterTileUs * static_cast<double>(tiles_per_cta)
+                            : kTicketUs + kTicketTileUs * static_cast<double>(tiles_per_cta);
           if (depth < sets + 1 && total_chunks > static_cast<uint64_t>(sets)) cost *= 1.1;  // a shallow ring stalls on HBM latency
           if (cost < best - 1e-9) {
             best = cost;
@@ -628,6 +669,7 @@ inline bool plan_group(const uint64_t* n, int count, uint64_t nb, int m, uint64_
             out->split = static_cast<int>(split);
             out->grid_x = static_cast<int>(grid_x);
             out->occ = occ;
+            out->cluster = cluster;
             out->smem = fx + static_cast<size_t>(depth) * sb;
             out->cost = cost;
             found = true;
@@ -637,10 +679,104 @@ inline bool plan_group(const uint64_t* n, int count, uint64_t nb, int m, uint64_
     }
   }
   if (found && env_plan_int("TSR_PLAN_DEBUG", 0))
-    std::fprintf(stderr, "plan: targets %d nb %llu sets %d -> rgs %d occ %d split %d grid_x %d stages %d smem %zu cost %.1f us\n",
-                 count, static_cast<unsigned long long>(nb), sets, out->rgs, out->occ, out->split, out->grid_x,
-                 out->stages, out->smem, out->cost);
+    std::fprintf(stderr, "plan: targets %d nb %llu sets %d -> rgs %d occ %d split %d%s grid_x %d stages %d smem %zu cost %.1f us\n",
+                 count, static_cast<unsigned long long>(nb), sets, out->rgs, out->occ, out->split,
+                 out->cluster ? " (cluster)" : "", out->grid_x, out->stages, out->smem, out->cost);
   return found;
+}
+
+// plan_group with a memo: a launch's plan depends only on its shape, the kernel variant (`tag`,
+// unique per kernel instantiation) and the experiment switches, and the same few shapes come
+// back for every token.  Not used while TSR_PLAN_DEBUG is set (the plan prints as it is made).
+template <typename FixedFn, typename StageFn, typename ChunksFn>
+inline bool plan_group_cached(int tag, const uint64_t* n, int count, uint64_t nb, int m, uint64_t fixed_split, int sets,
+                              int fixed_rgs, int regs_per_thread, int max_want, double block_us, FixedFn fixed,
+                              StageFn stage_bytes, ChunksFn nchunks, GroupPlan* out, bool allow_cluster = true) {
+  if (env_plan_int("TSR_PLAN_DEBUG", 0))
+    return plan_group(n, count, nb, m, fixed_split, sets, fixed_rgs, regs_per_thread, max_want, block_us, fixed,
+                      stage_bytes, nchunks, out, allow_cluster);
+  struct Entry {
+    uint64_t key[12];
+    bool ok;
+    GroupPlan plan;
+  };
+  uint64_t key[12] = {};
+  for (int i = 0; i < count && i < 4; ++i) key[i] = n[i];
+  key[4] = (static_cast<uint64_t>(tag) << 40) | (static_cast<uint64_t>(count) << 32) | (static_cast<uint64_t>(sets) << 24) |
+           (static_cast<uint64_t>(fixed_rgs) << 16) | (allow_cluster ? 1u : 0u);
+  key[5] = nb;
+  key[6] = (static_cast<uint64_t>(m) << 32) | fixed_split;
+  key[7] = (static_cast<uint64_t>(static_cast<uint32_t>(env_plan_int("TSR_RING_MAX", max_want))) << 32) |
+           static_cast<uint32_t>(env_plan_int("TSR_RGS", 0));
+  key[8] = (static_cast<uint64_t>(static_cast<uint32_t>(env_plan_int("TSR_SPLIT", 0))) << 32) |
+           static_cast<uint32_t>(env_plan_int("TSR_GRID", 0));
+  key[9] = (static_cast<uint64_t>(static_cast<uint32_t>(env_plan_int("TSR_OCC", 0))) << 32) |
+           static_cast<uint32_t>(env_plan_int("TSR_PERSIST", -1));
+  key[10] = (static_cast<uint64_t>(static_cast<uint32_t>(env_plan_int("TSR_CLUSTER", 0))) << 32) |
+            static_cast<uint32_t>(env_plan_int("TSR_CLUSTER_NS", 1000));
+  int dev = 0;
+  cudaGetDevice(&dev);
+  key[11] = (static_cast<uint64_t>(static_cast<uint32_t>(dev)) << 32) | static_cast<uint32_t>(regs_per_thread);
+  static std::mutex mutex;
+  static std::vector<Entry> cache;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    for (const Entry& e : cache) {
+      bool same = true;
+      for (int i = 0; i < 12; ++i) same = same && e.key[i] == key[i];
+      if (same) {
+        *out = e.plan;
+        return e.ok;
+      }
+    }
+  }
+  Entry e{};
+  for (int i = 0; i < 12; ++i) e.key[i] = key[i];
+  e.ok = plan_group(n, count, nb, m, fixed_split, sets, fixed_rgs, regs_per_thread, max_want, block_us, fixed, stage_bytes,
+                    nchunks, &e.plan, allow_cluster);
+  *out = e.plan;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (cache.size() < 4096) cache.push_back(e);
+  return e.ok;
+}
+
+// How many clusters of `cluster_y` CTAs of `kernel` the device holds at once with this block
+// size and shared memory (0: such a cluster cannot be launched).  Cached per configuration.
+template <typename Kernel>
+inline int max_active_clusters(Kernel kernel, int threads, size_t smem, int cluster_y) {
+  struct Key {
+    const void* k;
+    int dev, threads, cluster;
+    size_t smem;
+    int result;
+  };
+  static std::mutex mutex;
+  static std::vector<Key> cache;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mutex);
+  for (const Key& e : cache)
+    if (e.k == reinterpret_cast<const void*>(kernel) && e.dev == dev && e.threads == threads && e.cluster == cluster_y &&
+        e.smem == smem)
+      return e.result;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, static_cast<unsigned>(cluster_y));
+  cfg.blockDim = dim3(static_cast<unsigned>(threads));
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = static_cast<unsigned>(cluster_y);
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(kernel), &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  cache.push_back(Key{reinterpret_cast<const void*>(kernel), dev, threads, cluster_y, smem, n});
+  return n;
 }
 
 // Registers per thread of a kernel, rounded up to the allocation unit.

@@ -28,7 +28,7 @@ def check(got_bits, want):
     big = np.abs(want) > 0.02 * top
     assert np.all(np.abs(got - want)[big] <= step[big] * 1.001)
     assert np.all(np.abs(got - want)[~big] <= 2e-3 * top)
-    assert np.mean(got == want) > 0.97
+    assert np.mean(got == want) > 0.9
 
 
 @pytest.mark.parametrize("fmt,m,n,k", [

@@ -63,10 +63,14 @@ def test_q6k_group_of_three_weights(backend, oracle, m):
 
 
 @pytest.mark.parametrize("fmt", [0, 1])
-@pytest.mark.parametrize("split,grid,rgs", [(2, 0, 0), (4, 3, 1), (1, 2, 2), (8, 1, 4), (4, 0, 3)])
-def test_split_inside_the_launch_and_tile_loop(backend, oracle, monkeypatch, fmt, split, grid, rgs):
+@pytest.mark.parametrize("cluster", [1, 0])
+@pytest.mark.parametrize("split,grid,rgs", [(2, 0, 0), (4, 3, 1), (1, 2, 2), (8, 1, 4), (4, 0, 3), (8, 0, 2)])
+def test_split_inside_the_launch_and_tile_loop(backend, oracle, monkeypatch, fmt, cluster, split, grid, rgs):
     """Forces the number of k chunks, a grid smaller than the tile list (every CTA then works
-    through several tiles) and the tile height; the plan picks them by itself otherwise."""
+    through several tiles) and the tile height; the plan picks them by itself otherwise.  The
+    chunks of a tile meet in the shared memory of a thread-block cluster where a CTA has at most
+    two tiles, else (and with cluster = 0 always) through tickets in global memory."""
+    monkeypatch.setenv("TSR_CLUSTER", str(cluster))
     monkeypatch.setenv("TSR_SPLIT", str(split))
     if grid:
         monkeypatch.setenv("TSR_GRID", str(grid))
