@@ -157,6 +157,54 @@ def run_cpu_sample(oracle, threads: int, budget_s: float, pool=None):
         f"{passes} passes, {spent:.1f} s of CPU work on {threads} threads, scaled by rows and multiplicity to a full step")
 
 
+def cpu_qgemv_rows(oracle, threads: int, pool=None, rows: int = 2048):
+    """The CPU implementation on `rows` rows of the 17408 x 5120 decode GEMV in each weight
+    format (m = 1), scaled to the whole matrix: microseconds and GB/s of weight bytes, to stand
+    beside the GPU's single-projection table."""
+    n, k = 17408, 5120
+    a = synth.activations(1, k, seed=2)
+    out = []
+    for fmt in ("q4k", "q6k", "mxfp4", "fp8"):
+        if fmt == "q4k":
+            w, rb, fn = synth.q4k_weights(rows, k, seed=1), (k // 256) * 144, oracle.gemm_q4k
+        elif fmt == "q6k":
+            w, rb, fn = synth.q6k_weights(rows, k, seed=1), (k // 256) * 210, oracle.gemm_q6k
+        elif fmt == "mxfp4":
+            w, rb, fn = synth.mxfp4_weights(rows, k, seed=1), k // 2 + k // 32, oracle.gemm_mxfp4
+        else:
+            (w, sc), rb = synth.fp8_weights(rows, k, seed=1), k + 4
+            fn = lambda a_, w_, m_, n_, k_, threads=0: oracle.gemm_fp8(a_, w_, sc[:n_], m_, n_, k_, threads=threads)
+        parts = None
+        if pool is not None and fmt in ("mxfp4", "fp8"):
+            # row ranges per thread, each repacked in the format's own layout (outside the timing)
+            chunk = (rows + threads - 1) // threads
+            cuts = [(r0, min(rows, r0 + chunk)) for r0 in range(0, rows, chunk)]
+            if fmt == "mxfp4":
+                blob, scales = w[: rows * k // 2], w[rows * k // 2:]
+                parts = [np.concatenate([blob[r0 * k // 2:r1 * k // 2], scales[r0 * k // 32:r1 * k // 32]]) for r0, r1 in cuts]
+            else:
+                parts = [(np.ascontiguousarray(w[r0 * k:r1 * k]), np.ascontiguousarray(sc[r0:r1])) for r0, r1 in cuts]
+        best = None
+        for _ in range(3):
+            t0 = time.perf_counter()
+            if pool is None:
+                fn(a, w, 1, rows, k, threads=threads)
+            elif fmt in ("q4k", "q6k"):
+                chunk = (rows + threads - 1) // threads
+                jobs = [(r0, min(rows, r0 + chunk)) for r0 in range(0, rows, chunk)]
+                list(pool.map(lambda j: fn(a, w[j[0] * rb:j[1] * rb], 1, j[1] - j[0], k), jobs))
+            elif fmt == "mxfp4":
+                list(pool.map(lambda j: oracle.gemm_mxfp4(a, j, 1, j.size // rb, k), parts))
+            else:
+                list(pool.map(lambda j: oracle.gemm_fp8(a, j[0], j[1], 1, j[1].size, k), parts))
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        us = best * 1e6 * n / rows
+        out.append({"fmt": fmt, "m": 1, "n": n, "k": k, "us": round(us, 1), "gbs": round(n * rb / us / 1e3, 2),
+                    "threads": threads, "rows_timed": rows})
+    return out
+
+
 def reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -186,6 +234,7 @@ def reference_arm(args):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_s": total,
+        "qgemv_cpu": cpu_qgemv_rows(oracle, threads, pool),
     }
     print(json.dumps(line))
 
@@ -802,7 +851,8 @@ def gpu_arm(args):
         from oracle.oracle import Oracle
         threads = os.cpu_count() or 1
         v, sample = run_cpu_sample(Oracle(), threads, 12.0)
-        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+                                "qgemv": cpu_qgemv_rows(Oracle(), threads)}
     if rank == 0:
         print(json.dumps(line))
     backend.Synchronize()

@@ -89,24 +89,34 @@ __device__ __forceinline__ void tp_push(const TpTail& tp, size_t off, float v) {
 }
 
 // Waits (bounded) for element e of every source rank in this rank's buffer of call
-// `epoch` and returns their sum in rank order.
+// `epoch` and returns their sum in rank order.  The W slot words are loaded together (one
+// trip to memory when everything has arrived, not W trips one behind the other); only words
+// that still hold the sentinel are polled again.
 __device__ __forceinline__ float tp_wait_sum(const TpTail& tp, unsigned int epoch, size_t e) {
   const float* base = tp_slots_of(tp, tp.rank) + tp_slot_offset(tp, epoch, 0) + e;
-  float acc = 0.0f;
-  for (int r = 0; r < tp.world; ++r) {
-    const float* p = base + static_cast<size_t>(r) * tp.capacity;
-    unsigned int bits = tp_ld(p), polls = 0;
-    while (bits == kTpSentinel) {
-      if (++polls > kTpWaitPolls) {
-        atomicAdd(tp.state + 2, 1u);
-        break;
-      }
-      if (polls > 32) __nanosleep(40);
-      bits = tp_ld(p);
+  unsigned int bits[kMaxWorld];
+#pragma unroll
+  for (int r = 0; r < kMaxWorld; ++r)
+    bits[r] = r < tp.world ? tp_ld(base + static_cast<size_t>(r) * tp.capacity) : 0u;
+  for (unsigned int polls = 0;;) {
+    bool missing = false;
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) missing = missing || bits[r] == kTpSentinel;
+    if (!missing) break;
+    if (++polls > kTpWaitPolls) {
+      atomicAdd(tp.state + 2, 1u);
+      break;
     }
-    const float v = __uint_as_float(bits);
-    acc = r == 0 ? v : acc + v;
+    if (polls > 32) __nanosleep(40);
+    // every word still missing is asked for again, all of them in flight together
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r)
+      if (bits[r] == kTpSentinel) bits[r] = tp_ld(base + static_cast<size_t>(r) * tp.capacity);
   }
+  float acc = __uint_as_float(bits[0]);
+#pragma unroll
+  for (int r = 1; r < kMaxWorld; ++r)
+    if (r < tp.world) acc += __uint_as_float(bits[r]);
   return acc;
 }
 
@@ -127,14 +137,17 @@ __device__ __forceinline__ void tp_reset_previous(const TpTail& tp, unsigned int
 // One thread of every CTA calls this when the CTA has finished all its work (reset
 // included): the last CTA of the grid to arrive completes the call.  `used` = elements
 // this call exchanged.
+// The caller has synchronised the CTA's threads (a barrier) after their resets: the
+// arrival's release then covers them, and the last CTA's acquire sees every CTA's resets
+// before it marks the buffer clean.  The state words are read next by the following kernel
+// of this stream, which the kernel boundary orders; no thread needs a full fence.
 __device__ __forceinline__ void tp_cta_leaves(const TpTail& tp, unsigned int epoch, unsigned int ctas, unsigned int used) {
-  __threadfence();
-  const unsigned int t = atomicAdd(tp.state + 1, 1u);
+  unsigned int t;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(t) : "l"(tp.state + 1) : "memory");
   if (t == ctas - 1) {
     tp.state[1] = 0u;
     tp.state[4 + epoch % 3u] = used;
     tp.state[4 + (epoch + 2u) % 3u] = 0u;  // the previous call's buffer is clean again
-    __threadfence();
     *reinterpret_cast<volatile unsigned int*>(tp.state) = epoch;
   }
 }
