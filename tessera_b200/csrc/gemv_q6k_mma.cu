@@ -176,7 +176,10 @@ struct alignas(64) Q6KMaps {
 // list, all on split chunk blockIdx.y of k (see gemv_mma.cu).
 // SETS consumer warp sets (2, or 4 where each warp's chain of blocks would otherwise be long on
 // a mostly idle SM): set s takes the chunks j = s (mod SETS) of the CTA's sequence.
-template <int NCG, int SETS>
+// PLAIN: any split of k is left to the caller and nothing follows the sums (no ranks, no
+// residual, fp32 output): the general output stage is compiled out.  ONE (with PLAIN): one
+// weight tensor and one tile per CTA: the tile loop and the choice of target go too.
+template <int NCG, int SETS, bool ONE, bool PLAIN>
 __global__ void __launch_bounds__((SETS * 4 + 1) * 32, SETS == 2 ? 2 : 1)
 gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -195,14 +198,15 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
   // cluster split: arrival barriers and receive buffers of the chunk-0 CTA, one per tile of the CTA
   uint64_t* recv_bar = empty + p.stages + 4;
   float* recv = reinterpret_cast<float*>(empty + p.stages + 8);
-  const bool clustered = p.split_mode == kSplitCluster && gridDim.y > 1;
+  const bool clustered = TSR_CLUSTER_SPLIT != 0 && !PLAIN && p.split_mode == kSplitCluster && gridDim.y > 1;
   const int b0 = blockIdx.y * p.per;
   // Stages cover block pairs (2j, 2j+1) of the row; pairs that straddle the
   // ends of this CTA's split chunk are loaded whole and half of them skipped.
   const int pair0 = b0 >> 1;
   const int nchunks = ((b0 + p.per + 1) >> 1) - pair0;
-  const int my_tiles = (p.total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                       static_cast<int>(gridDim.x);
+  const int my_tiles = ONE ? 1
+                            : (p.total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                                  static_cast<int>(gridDim.x);
   const int total_chunks = my_tiles * nchunks;
   const bool producer = (tid == kConsumerThreads);
 
@@ -224,8 +228,10 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
     mbar_fence_init();
   }
   __syncthreads();
+#if TSR_CLUSTER_SPLIT
   // no CTA of the cluster signals a peer's barrier before that peer has initialised it
   if (clustered) cluster_sync_all();
+#endif
 
   // The producer walks the CTA's chunk sequence (tile after tile, pair after pair) with a
   // cursor: maps, first row and the odd map's shift change only when a tile begins.
@@ -236,7 +242,10 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
   const CUtensorMap* p_even = &maps.even[0];
   const CUtensorMap* p_odd = &maps.odd[0];
   auto issue_next = [&](int slot) {
-    if (p_c == 0) {
+    if (ONE) {
+      p_row0 = blockIdx.x * kTileRows;
+      p_shift = p.tgt[0].aux;
+    } else if (p_c == 0) {
       const int tile = blockIdx.x + p_it * gridDim.x;
       const int g = target_of_tile(p, tile);
       const StagedTarget tgt = target_by_index(p, g);
@@ -275,9 +284,9 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
     if (p.pdl) pdl_wait();
     deferred_prologue();
   }
-  if (tid == 0 && p.tp.world > 1) s_words[1] = tp_call_epoch(p.tp);  // the stream's earlier work is complete here
+  if (!PLAIN && tid == 0 && p.tp.world > 1) s_words[1] = tp_call_epoch(p.tp);  // the stream's earlier work is complete here
   __syncthreads();
-  if (p.tp.world > 1 && warp < kConsumerWarps) {
+  if (!PLAIN && p.tp.world > 1 && warp < kConsumerWarps) {
     const size_t cta = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
     tp_reset_previous(p.tp, s_words[1], cta * kConsumerThreads + tid,
                       static_cast<size_t>(gridDim.x) * gridDim.y * kConsumerThreads);
@@ -324,8 +333,8 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
   bool failed = false;  // a bounded wait gave up: skip the remaining waits, keep the barriers
   for (int it = 0; it < my_tiles; ++it) {
     const int tile = blockIdx.x + it * gridDim.x;
-    const StagedTarget tg = target_by_index(p, target_of_tile(p, tile));
-    const int row0 = (tile - tg.tile_begin) * kTileRows;
+    const StagedTarget tg = ONE ? p.tgt[0] : target_by_index(p, target_of_tile(p, tile));
+    const int row0 = ONE ? static_cast<int>(blockIdx.x) * kTileRows : (tile - tg.tile_begin) * kTileRows;
     const int odd_shift = tg.aux;
     float o[NCG][4];
 #pragma unroll
@@ -384,6 +393,19 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
       }
     }
     asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
+    if (PLAIN) {
+      // chunk y of k -> region y of the output (one region when k is not split)
+      float* cout = tg.c + static_cast<size_t>(blockIdx.y) * p.m * tg.n;
+      for (int idx = tid; idx < p.m * kTileRows; idx += kConsumerThreads) {
+        const int i = idx / kTileRows, rr = idx - i * kTileRows;
+        if (row0 + rr < tg.n) {
+          float v = 0.0f;
+          for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
+          cout[static_cast<size_t>(i) * tg.n + row0 + rr] = v;
+        }
+      }
+      continue;
+    }
     finish_tile(p, tg, tile, row0, kTileRows, blockIdx.y, gridDim.y, epoch, tid, kConsumerThreads, s_words,
                 it, recv_bar, recv, &g_q6k_wait_timeouts,
                 [&](int i, int rr) {
@@ -392,7 +414,7 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
                   return v;
                 });
   }
-  if (p.tp.world > 1) {
+  if (!PLAIN && p.tp.world > 1) {
     asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");  // every thread's share of the reset is done
     if (tid == 0) tp_cta_leaves(p.tp, epoch, gridDim.x * gridDim.y, static_cast<unsigned int>(p.m) * p.tgt[0].n);
   }
@@ -466,7 +488,7 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
   };
   auto stage_bytes = [](int rgs) -> size_t { return static_cast<size_t>(rgs) * 2 * kGroupHalfBytes; };
   auto chunks_of = [](uint64_t per) -> uint64_t { return per / 2 + 1; };
-  static const int regs = kernel_registers(gemv_q6k_staged_kernel<NCG, SETS>);
+  static const int regs = kernel_registers(gemv_q6k_staged_kernel<NCG, SETS, false, false>);
   uint64_t rows[kMaxGroup];
   for (int i = 0; i < count; ++i) rows[i] = t[i].n;
   GroupPlan plan;
@@ -475,8 +497,8 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
   if (plan.cluster) {
     // the cluster must be launchable (and, with ranks waiting on one another, all of the
     // launch's clusters resident at once); else the chunks meet through global memory
-    if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q6k_staged_kernel<NCG, SETS>), kMaxSmem)) return rc;
-    const int fit = max_active_clusters(gemv_q6k_staged_kernel<NCG, SETS>, (SETS * plan.rgs + 1) * 32, plan.smem, plan.split);
+    if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q6k_staged_kernel<NCG, SETS, false, false>), kMaxSmem)) return rc;
+    const int fit = max_active_clusters(gemv_q6k_staged_kernel<NCG, SETS, false, false>, (SETS * plan.rgs + 1) * 32, plan.smem, plan.split);
     const bool with_ranks = tp != nullptr && tp->world > 1;
     if (fit < 1 || (with_ranks && fit < plan.grid_x)) {
       if (!plan_group_cached(200 + NCG * 10 + SETS, rows, count, nb, static_cast<int>(m), caller_split, SETS, 0, regs, 8, 0.85, fixed, stage_bytes, chunks_of, &plan, false))
@@ -564,7 +586,14 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
   } else {
     p.tp.world = 1;
   }
-  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q6k_staged_kernel<NCG, SETS>), kMaxSmem)) return rc;
+  // the trimmed variants where nothing but plain projections are asked for (TSR_LEAN=0: experiments)
+  bool plain = p.tp.world == 1 && (p.split_mode == kSplitCaller || plan.split == 1) && p.c_bf16 == 0 &&
+               env_int("TSR_LEAN", 1) != 0;
+  for (int i = 0; i < count; ++i) plain = plain && t[i].add_out == nullptr;
+  const bool one = plain && count == 1 && static_cast<uint64_t>(plan.grid_x) == tiles;
+  if (plain) p.split_mode = kSplitCaller;
+  auto kernel = one ? gemv_q6k_staged_kernel<NCG, SETS, true, true> : plain ? gemv_q6k_staged_kernel<NCG, SETS, false, true> : gemv_q6k_staged_kernel<NCG, SETS, false, false>;
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kernel), kMaxSmem)) return rc;
   const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.split));
   p.pdl = pdl_allowed_ranges(st, reads, read_bytes, count, writes, write_bytes, nwrites) ? 1 : 0;
   {
@@ -572,7 +601,7 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
     if (mode == 2 && plan.occ < 2) p.pdl = 0;
     if (mode == 3 && plan.sets != 4) p.pdl = 0;
   }
-  launch_kernel_cluster_y(gemv_q6k_staged_kernel<NCG, SETS>, grid, dim3((SETS * plan.rgs + 1) * 32), plan.smem, st,
+  launch_kernel_cluster_y(kernel, grid, dim3((SETS * plan.rgs + 1) * 32), plan.smem, st,
                           p.pdl != 0, plan.cluster ? static_cast<unsigned>(plan.split) : 1u, maps, p);
   return check_launch();
 }

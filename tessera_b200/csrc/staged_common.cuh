@@ -50,6 +50,10 @@ enum : int {
   kSplitCluster = 2,
 };
 constexpr int kClusterTiles = 2;
+// The cluster form is compiled only with -DTSR_CLUSTER_SPLIT=1 (experiments).
+#ifndef TSR_CLUSTER_SPLIT
+#define TSR_CLUSTER_SPLIT 0
+#endif
 
 struct StagedParams {
   const float* a;
@@ -404,8 +408,13 @@ __device__ __forceinline__ void finish_tile(const StagedParams& p, const StagedT
     return;
   }
   const size_t tile_floats = static_cast<size_t>(p.m) * tile_rows;
+#if TSR_CLUSTER_SPLIT
   const bool clustered = p.split_mode == kSplitCluster && nsplit > 1;
+#else
+  constexpr bool clustered = false;
+#endif
   const float* received = recv + static_cast<size_t>(it) * (nsplit - 1) * tile_floats + rr;  // tile `it` of this CTA
+#if TSR_CLUSTER_SPLIT
   if (clustered) {
     if (chunk_y != 0) {
       const uint32_t remote =
@@ -419,7 +428,9 @@ __device__ __forceinline__ void finish_tile(const StagedParams& p, const StagedT
       return;
     }
     mbar_wait_cluster(recv_bar + it, 0, timeouts);  // bounded; on a timeout the sums below are wrong and the host is told
-  } else if (nsplit > 1) {
+  } else
+#endif
+  if (nsplit > 1) {
     float* mine = p.part + (static_cast<size_t>(chunk_y) * p.total_tiles + tile) * tile_floats + rr;
 #pragma unroll 1
     for (int i = i0; i < p.m; i += per_pass) __stcg(mine + i * tile_rows, value(i, rr));
@@ -593,7 +604,7 @@ inline bool plan_group(const uint64_t* n, int count, uint64_t nb, int m, uint64_
   // unsplit four-set plan (22.7 against 16.9 us, Q6_K 34.8 against 25.8 us): three CTAs per SM
   // leave each consumer set one or two ring slots, which does not cover the HBM latency, and
   // the SMs are no more evenly loaded than with 48-row tiles alone.
-  const bool use_cluster = allow_cluster && env_plan_int("TSR_CLUSTER", 0) != 0;
+  const bool use_cluster = TSR_CLUSTER_SPLIT != 0 && allow_cluster && env_plan_int("TSR_CLUSTER", 0) != 0;
   const int ring_max = env_plan_int("TSR_RING_MAX", max_want);
   const int force_rgs = env_plan_int("TSR_RGS", 0), force_split = env_plan_int("TSR_SPLIT", 0);
   const int force_grid = env_plan_int("TSR_GRID", 0), force_occ = env_plan_int("TSR_OCC", 0);
