@@ -62,11 +62,14 @@ struct alignas(64) Q4KMaps {
 // A CTA works through the tiles blockIdx.x, blockIdx.x + gridDim.x, ... of the launch's tile
 // list, all on split chunk blockIdx.y of k: the activations are staged once, and the weight
 // ring keeps streaming across tile boundaries.
-// PLAIN: the launch leaves any split of k to the caller and has nothing after the sums (no
-// ranks, no residual, fp32 output): the general output stage is compiled out.  ONE (with
-// PLAIN): one weight tensor and one tile per CTA: the tile loop and the choice of target go too.
-// Measured on the 27B-class step: 4.75 -> 4.53 ms with ONE alone.
-template <int NCG, int SETS, bool ONE, bool PLAIN>
+// OUT selects what follows the sums.  kOutGeneral: everything finish_tile offers (the split of k
+// added inside the launch, ranks, residual, bf16).  kOutPlain: any split of k is left to the
+// caller and nothing follows (fp32 store).  kOutRanks: the sum over tensor-parallel ranks and
+// an optional residual, k not split.  The trimmed forms exist because the general stage costs
+// launches that never use it: the 27B-class step went from 4.75 to 4.13 ms with kOutPlain.
+// ONE (not with kOutGeneral): one weight tensor and one tile per CTA, so the tile loop and the
+// choice of target are compiled out as well.
+template <int NCG, int SETS, bool ONE, int OUT>
 __global__ void __launch_bounds__((SETS * 4 + 1) * 32, SETS == 2 ? 2 : 1)
 gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -87,7 +90,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams 
   // cluster split: arrival barriers and receive buffers of the chunk-0 CTA, one per tile of the CTA
   uint64_t* recv_bar = empty + p.stages + 4;
   float* recv = reinterpret_cast<float*>(empty + p.stages + 8);
-  const bool clustered = TSR_CLUSTER_SPLIT != 0 && !PLAIN && p.split_mode == kSplitCluster && gridDim.y > 1;
+  const bool clustered = TSR_CLUSTER_SPLIT != 0 && OUT == kOutGeneral && p.split_mode == kSplitCluster && gridDim.y > 1;
   const int b0 = blockIdx.y * p.per;
   const int my_tiles = ONE ? 1
                             : (p.total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
@@ -154,9 +157,9 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams 
     if (p.pdl) pdl_wait();
     deferred_prologue();
   }
-  if (!PLAIN && tid == 0 && p.tp.world > 1) s_words[1] = tp_call_epoch(p.tp);  // the stream's earlier work is complete here
+  if (OUT != kOutPlain && tid == 0 && p.tp.world > 1) s_words[1] = tp_call_epoch(p.tp);  // the stream's earlier work is complete here
   __syncthreads();
-  if (!PLAIN && p.tp.world > 1 && warp < kConsumerWarps) {
+  if (OUT != kOutPlain && p.tp.world > 1 && warp < kConsumerWarps) {
     const size_t cta = static_cast<size_t>(blockIdx.y) * gridDim.x + blockIdx.x;
     tp_reset_previous(p.tp, s_words[1], cta * kConsumerThreads + tid,
                       static_cast<size_t>(gridDim.x) * gridDim.y * kConsumerThreads);
@@ -331,7 +334,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams 
       }
     }
     asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");
-    if (PLAIN) {
+    if (OUT == kOutPlain) {
       // chunk y of k -> region y of the output (one region when k is not split)
       const StagedTarget tg = ONE ? p.tgt[0] : target_by_index(p, target_of_tile(p, tile));
       const int row0 = (ONE ? static_cast<int>(blockIdx.x) : tile - tg.tile_begin) * kTileRows;
@@ -346,6 +349,31 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams 
       }
       continue;
     }
+    if (OUT == kOutRanks) {
+      // every thread sends its values to all ranks, then waits for the same elements of all
+      // ranks in its own slots and adds them in rank order (tp_device.cuh)
+      const StagedTarget tg = ONE ? p.tgt[0] : target_by_index(p, target_of_tile(p, tile));
+      const int row0 = (ONE ? static_cast<int>(blockIdx.x) : tile - tg.tile_begin) * kTileRows;
+      const size_t mine = tp_slot_offset(p.tp, epoch, p.tp.rank);
+      for (int idx = tid; idx < p.m * kTileRows; idx += kConsumerThreads) {
+        const int i = idx / kTileRows, rr = idx - i * kTileRows;
+        if (row0 + rr < tg.n) {
+          float v = 0.0f;
+          for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
+          tp_push(p.tp, mine + static_cast<size_t>(i) * tg.n + row0 + rr, v);
+        }
+      }
+      for (int idx = tid; idx < p.m * kTileRows; idx += kConsumerThreads) {
+        const int i = idx / kTileRows, rr = idx - i * kTileRows;
+        if (row0 + rr < tg.n) {
+          const size_t e = static_cast<size_t>(i) * tg.n + row0 + rr;
+          const float v = tp_wait_sum(p.tp, epoch, e);
+          tg.c[e] = v;
+          if (tg.add_out != nullptr) tg.add_out[e] = tg.add_src[e] + v;
+        }
+      }
+      continue;
+    }
     const StagedTarget tg = target_by_index(p, target_of_tile(p, tile));
     const int row0 = (tile - tg.tile_begin) * kTileRows;
     finish_tile(p, tg, tile, row0, kTileRows, blockIdx.y, gridDim.y, epoch, tid, kConsumerThreads, s_words,
@@ -356,7 +384,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams 
                   return v;
                 });
   }
-  if (!PLAIN && p.tp.world > 1) {
+  if (OUT != kOutPlain && p.tp.world > 1) {
     asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");  // every thread's share of the reset is done
     if (tid == 0) tp_cta_leaves(p.tp, epoch, gridDim.x * gridDim.y, static_cast<unsigned int>(p.m) * p.tgt[0].n);
   }
@@ -423,7 +451,7 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
            16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128 + recv;
   };
   auto stage_bytes = [](int rgs) -> size_t { return static_cast<size_t>(rgs) * kGroupBytes; };
-  static const int regs = kernel_registers(gemv_q4k_staged_kernel<NCG, SETS, false, false>);
+  static const int regs = kernel_registers(gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral>);
   uint64_t rows[kMaxGroup];
   for (int i = 0; i < count; ++i) rows[i] = t[i].n;
   GroupPlan plan;
@@ -432,8 +460,8 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
   if (plan.cluster) {
     // the cluster must be launchable (and, with ranks waiting on one another, all of the
     // launch's clusters resident at once); else the chunks meet through global memory
-    if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q4k_staged_kernel<NCG, SETS, false, false>), kMaxSmem)) return rc;
-    const int fit = max_active_clusters(gemv_q4k_staged_kernel<NCG, SETS, false, false>, (SETS * plan.rgs + 1) * 32, plan.smem, plan.split);
+    if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral>), kMaxSmem)) return rc;
+    const int fit = max_active_clusters(gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral>, (SETS * plan.rgs + 1) * 32, plan.smem, plan.split);
     const bool with_ranks = tp != nullptr && tp->world > 1;
     if (fit < 1 || (with_ranks && fit < plan.grid_x)) {
       if (!plan_group_cached(100 + NCG * 10 + SETS, rows, count, nb, static_cast<int>(m), caller_split, SETS, 0, regs, 12, 0.5, fixed, stage_bytes, chunks_of, &plan, false))
@@ -517,13 +545,17 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
   } else {
     p.tp.world = 1;
   }
-  // the trimmed variants where nothing but plain projections are asked for (TSR_LEAN=0: experiments)
-  bool plain = p.tp.world == 1 && (p.split_mode == kSplitCaller || plan.split == 1) && p.c_bf16 == 0 &&
-               env_int("TSR_LEAN", 1) != 0;
-  for (int i = 0; i < count; ++i) plain = plain && t[i].add_out == nullptr;
-  const bool one = plain && count == 1 && static_cast<uint64_t>(plan.grid_x) == tiles;
+  // the trimmed variants where the general output stage is not needed (TSR_LEAN=0: experiments)
+  const bool trim = env_int("TSR_LEAN", 1) != 0 && p.c_bf16 == 0;
+  bool no_add = true;
+  for (int i = 0; i < count; ++i) no_add = no_add && t[i].add_out == nullptr;
+  const bool plain = trim && p.tp.world == 1 && no_add && (p.split_mode == kSplitCaller || plan.split == 1);
+  const bool ranks = trim && p.tp.world > 1 && plan.split == 1;
+  const bool one = count == 1 && static_cast<uint64_t>(plan.grid_x) == tiles;
   if (plain) p.split_mode = kSplitCaller;
-  auto kernel = one ? gemv_q4k_staged_kernel<NCG, SETS, true, true> : plain ? gemv_q4k_staged_kernel<NCG, SETS, false, true> : gemv_q4k_staged_kernel<NCG, SETS, false, false>;
+  auto kernel = plain ? (one ? gemv_q4k_staged_kernel<NCG, SETS, true, kOutPlain> : gemv_q4k_staged_kernel<NCG, SETS, false, kOutPlain>)
+                : ranks ? (one ? gemv_q4k_staged_kernel<NCG, SETS, true, kOutRanks> : gemv_q4k_staged_kernel<NCG, SETS, false, kOutRanks>)
+                        : gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral>;
   if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kernel), kMaxSmem)) return rc;
   const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.split));
   p.pdl = pdl_allowed_ranges(st, reads, read_bytes, count, writes, write_bytes, nwrites) ? 1 : 0;

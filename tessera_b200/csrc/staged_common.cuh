@@ -49,6 +49,8 @@ enum : int {
   // order.  A CTA works through at most kClusterTiles tiles (one receive buffer per tile).
   kSplitCluster = 2,
 };
+// What a kernel variant does after a tile's sums (template parameter OUT of the staged kernels).
+enum : int { kOutGeneral = 0, kOutPlain = 1, kOutRanks = 2 };
 constexpr int kClusterTiles = 2;
 // The cluster form is compiled only with -DTSR_CLUSTER_SPLIT=1 (experiments).
 #ifndef TSR_CLUSTER_SPLIT
@@ -196,7 +198,10 @@ __device__ __forceinline__ float abs_max4(float m, float4 x) {
 // owns elements 4l..4l+3 and 128+4l..128+4l+3, the block maximum is one warp
 // reduction, and no CTA-wide pass is needed.  A warp works on kStageBatch
 // blocks at a time so that their dependent chains overlap.
-constexpr int kStageBatch = 4;
+#ifndef TSR_STAGE_BATCH
+#define TSR_STAGE_BATCH 4
+#endif
+constexpr int kStageBatch = TSR_STAGE_BATCH;
 
 // Phase 1 of a block: scale, digits, column scales.
 __device__ __forceinline__ void stage_digits(const StagedParams& p, int i, int bl, float4 x0, float4 x1,
@@ -307,6 +312,7 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
     pdl_wait();
   }
   const float* gain = scratch + kWarps * p.m;
+#ifndef TSR_STAGE_PLAIN_ONLY
   if (p.pro == kProRmsNorm) {
     // Every CTA needs the mean square of whole rows: each warp sums a share, the shares are
     // added in warp order.
@@ -331,6 +337,7 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
     }
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
   }
+#endif
   const bool writes_out = p.a_out != nullptr && blockIdx.x == 0;
 #pragma unroll 1
   for (int base = warp; base < items; base += kWarps * kStageBatch) {
@@ -344,15 +351,19 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
       x0[u] = x1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (it < items && k0 + blk[u] * kBlockElems < p.k) {
         const size_t first = static_cast<size_t>(row[u]) * p.k + k0 + blk[u] * kBlockElems;
+#ifndef TSR_STAGE_PLAIN_ONLY
         if (p.a_bf16) {
           const uint2* src = reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned short*>(p.a) + first);
           x0[u] = bf16x4_to_float4(__ldg(src + lane));
           x1[u] = bf16x4_to_float4(__ldg(src + 32 + lane));
-        } else {
+        } else
+#endif
+        {
           const float4* src = reinterpret_cast<const float4*>(p.a + first);
           x0[u] = __ldg(src + lane);
           x1[u] = __ldg(src + 32 + lane);
         }
+#ifndef TSR_STAGE_PLAIN_ONLY
         if (p.pro != kProNone) {
           const size_t at = static_cast<size_t>(row[u]) * p.k + k0 + blk[u] * kBlockElems;
           if (p.pro == kProSiluMul) {
@@ -370,6 +381,7 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
             dst[32 + lane] = x1[u];
           }
         }
+#endif
       }
     }
 #pragma unroll
