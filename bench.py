@@ -715,6 +715,8 @@ def gpu_arm(args):
             return batch, (proj, norm_w, scratch, resid)
 
         step, keep_step = record(only=set(args.only.split(",")) if args.only else None)
+        if args.elementwise_step:   # experiment: time the step with its elementwise neighbours as the step
+            step, keep_step = record_with_elementwise()
         dominant = ("ffn_gate", "ffn_up")
         dom, keep_dom = record(only=dominant)
         h2d_bytes = host_act["x"].nbytes
@@ -885,6 +887,8 @@ def main():
     ap.add_argument("--shard-of", type=int, default=1, metavar="W",
                     help="experiment (1 GPU): the step holds rank 0's shard of a W-way tensor-parallel run, without "
                          "the sums over ranks (per-launch costs of the small shapes; not the metric)")
+    ap.add_argument("--elementwise-step", action="store_true",
+                    help="experiment: the timed step is the one with its rmsnorm / silu_mul / add neighbours (not the metric)")
     ap.add_argument("--no-elementwise", action="store_true",
                     help="skip the extra timing of the step with its rmsnorm / silu_mul / add neighbours")
     ap.add_argument("--no-collective-table", action="store_true",

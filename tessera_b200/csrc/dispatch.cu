@@ -401,6 +401,11 @@ int tp_sum_in_place(const Args& a, float* data, uint64_t m, uint64_t n) {
 int fused_group(tsr_context* ctx, int fmt, const float* a, const GroupTarget* t, int count, uint64_t m, uint64_t k,
                 bool with_tp, cudaStream_t st, const Prologue* pro = nullptr) {
   if (ctx == nullptr) return kUnsupportedFeature;
+  // the staged kernels move activations, outputs and the folded steps' vectors 16 bytes at a time
+  if (!aligned16(a) || (pro != nullptr && (!aligned16(pro->other) || !aligned16(pro->out)))) return kUnsupportedFeature;
+  for (int i = 0; i < count; ++i)
+    if (!aligned16(t[i].w) || !aligned16(t[i].c) || !aligned16(t[i].add_src) || !aligned16(t[i].add_out))
+      return kUnsupportedFeature;
   TpTail tail{};
   const TpTail* tp = nullptr;
   if (with_tp && ctx->tp != nullptr) {
@@ -700,6 +705,15 @@ bool as_prologue(const tsr_context* ctx, const std::vector<PendingLaunch>& q, si
   if (is_named(op, "silu_mul")) {
     const size_t bytes = op.sc[0] * 4;
     if (next.a != op.buf[2] || next.m * next.k != op.sc[0]) return false;
+    // every CTA that stages the activations evaluates the step for all of them: with many
+    // row tiles and a long k a kernel of its own is cheaper (measured: 107 CTAs x 17408
+    // elements cost 2.5-8 us inside the launch, about 3 us as a launch)
+    const uint64_t repeated = ((next.t.n + 47) / 48) * next.m * next.k;
+    static const uint64_t limit = [] {
+      const char* v = std::getenv("TSR_FOLD_SILU_LIMIT");
+      return v ? static_cast<uint64_t>(std::atoll(v)) : 1000000ull;
+    }();
+    if (repeated > limit) return false;
     if (overlaps(op.buf[2], bytes, op.buf[0], bytes) || overlaps(op.buf[2], bytes, op.buf[1], bytes)) return false;
     *pro = Prologue{kProSiluMul, static_cast<const float*>(op.buf[1]), static_cast<float*>(const_cast<void*>(op.buf[2])), 0.0f};
     *in = static_cast<const float*>(op.buf[0]);

@@ -196,7 +196,8 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
   unsigned int* s_words = reinterpret_cast<unsigned int*>(empty + p.stages) + 4;              // [0] flag, [1] epoch
   // cluster split: arrival barriers and receive buffers of the chunk-0 CTA, one per tile of the CTA
   uint64_t* recv_bar = empty + p.stages + 4;
-  float* recv = reinterpret_cast<float*>(empty + p.stages + 8);
+  float* rms_gain = reinterpret_cast<float*>(empty + p.stages + 8);  // [m] row gains of kProRmsNormLate
+  float* recv = reinterpret_cast<float*>(empty + p.stages + 12);
   const bool clustered = TSR_CLUSTER_SPLIT != 0 && OUT == kOutGeneral && p.split_mode == kSplitCluster && gridDim.y > 1;
   const int b0 = blockIdx.y * p.per;
   // Stages cover block pairs (2j, 2j+1) of the row; pairs that straddle the
@@ -290,6 +291,9 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
     tp_reset_previous(p.tp, s_words[1], cta * kConsumerThreads + tid,
                       static_cast<size_t>(gridDim.x) * gridDim.y * kConsumerThreads);
   }
+
+  const bool late_gain = PRO && p.pro == kProRmsNormLate;
+  if (late_gain && warp < kConsumerWarps) rms_late_gain(p, xchg, rms_gain, tid, kConsumerThreads);
 
   if (warp == kConsumerWarps) {
     if (lane == 0) {
@@ -400,6 +404,7 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
         if (row0 + rr < tg.n) {
           float v = 0.0f;
           for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
+          if (late_gain) v *= rms_gain[i];
           cout[static_cast<size_t>(i) * tg.n + row0 + rr] = v;
           if (tg.add_out != nullptr) {  // residual folded in (k is not split when there is one)
             const size_t e = static_cast<size_t>(i) * tg.n + row0 + rr;
@@ -418,6 +423,7 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
         if (row0 + rr < tg.n) {
           float v = 0.0f;
           for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
+          if (late_gain) v *= rms_gain[i];
           tp_push(p.tp, mine + static_cast<size_t>(i) * tg.n + row0 + rr, v);
         }
       }
@@ -437,9 +443,10 @@ gemv_q6k_staged_kernel(const __grid_constant__ Q6KMaps maps, const StagedParams 
                 [&](int i, int rr) {
                   float v = 0.0f;
                   for (int t = p.terms - 1; t >= 0; --t) v += outbuf[rr * (NCG * 8) + i * p.terms + t];
-                  return v;
+                  return late_gain ? v * rms_gain[i] : v;
                 });
   }
+  if (late_gain) rms_late_write(p, rms_gain, blockIdx.x, gridDim.x, tid, kConsumerThreads);
   if (OUT != kOutPlain && p.tp.world > 1) {
     asm volatile("bar.sync 1, %0;" ::"r"(kConsumerThreads) : "memory");  // every thread's share of the reset is done
     if (tid == 0) tp_cta_leaves(p.tp, epoch, gridDim.x * gridDim.y, static_cast<unsigned int>(p.m) * p.tgt[0].n);
@@ -510,7 +517,7 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
     const uint64_t chunks = per != 0 ? nb / per : 1;
     const size_t recv = caller_split == 0 && chunks > 1 ? kClusterTiles * (chunks - 1) * m * 16 * rgs * 4 : 0;
     return per * ncols * (256 + 2 * kGroups) + per * kMaxCols * 4 + (SETS - 1) * rgs * 32 * NCG * 4 * 4 +
-           16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 128 + recv;
+           16 * rgs * NCG * 8 * 4 + 2 * 8 * 16 + 160 + recv;
   };
   auto stage_bytes = [](int rgs) -> size_t { return static_cast<size_t>(rgs) * 2 * kGroupHalfBytes; };
   auto chunks_of = [](uint64_t per) -> uint64_t { return per / 2 + 1; };
@@ -617,6 +624,10 @@ int launch_group_q6k(const float* a, const GroupTarget* t, int count, uint64_t m
   const bool trim = env_int("TSR_LEAN", 1) != 0 && p.c_bf16 == 0;
   bool has_add = false;
   for (int i = 0; i < count; ++i) has_add = has_add || t[i].add_out != nullptr;
+  // rmsnorm where every CTA stages whole rows: the gain multiplies the sums instead of the activations
+  if (p.pro == kProRmsNorm && plan.split == 1 && p.a_bf16 == 0 &&
+      m * (nb + 1) <= static_cast<uint64_t>(128) * SETS * plan.rgs * NCG && env_int("TSR_RMS_LATE", 1) != 0)
+    p.pro = kProRmsNormLate;
   const bool has_pro = p.pro != kProNone || p.a_bf16 != 0;
   const bool plain = trim && p.tp.world == 1 && (plan.split == 1 || (p.split_mode == kSplitCaller && !has_add));
   const bool ranks = trim && p.tp.world > 1 && plan.split == 1;

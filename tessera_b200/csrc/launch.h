@@ -164,7 +164,9 @@ struct GroupTarget {
 };
 // What a staged launch does around its projection: an elementwise step folded into the
 // activation staging, and bf16 storage of the activations and outputs.
-enum : int { kProNone = 0, kProSiluMul = 1, kProRmsNorm = 2 };
+// (kProRmsNormLate is chosen by the launchers themselves: the same result, the gain applied to the
+// sums instead of the activations, staged_common.cuh)
+enum : int { kProNone = 0, kProSiluMul = 1, kProRmsNorm = 2, kProRmsNormLate = 3 };
 struct Prologue {
   int kind;            // kProSiluMul: A = silu(a) * other; kProRmsNorm: A = a / sqrt(mean(a^2) + eps) * other
   const float* other;  // up vector [m][k] / norm weights [k]

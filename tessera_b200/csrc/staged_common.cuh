@@ -80,6 +80,10 @@ struct StagedParams {
   //                (SiluMulRef, src/core/numerics/norm.cpp:211-225 of the reference)
   //   kProRmsNorm: a2 holds the k norm weights, the projection reads a / sqrt(mean(a^2) + eps) * a2
   //                row by row (RmsNormRef, src/core/numerics/norm.cpp:7-32)
+  //   kProRmsNormLate: the same where every CTA stages whole rows (k not split): a * a2 is
+  //                staged, the squares are added up on the way, and the row's gain multiplies the
+  //                sums in the output stage (it is a factor of the whole row); a_out is written at
+  //                the end of the kernel, every CTA a share
   // a_out (may be null) receives those activations, [m][k] like a, written by the CTAs of
   // tile column 0; it must not overlap a or a2.
   int pro;
@@ -343,6 +347,7 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
 #pragma unroll 1
   for (int base = warp; base < items; base += kWarps * kStageBatch) {
     float4 x0[kStageBatch], x1[kStageBatch];
+    float4 w0[kStageBatch], w1[kStageBatch];  // kProRmsNormLate only
     int row[kStageBatch], blk[kStageBatch];
 #pragma unroll
     for (int u = 0; u < kStageBatch; ++u) {
@@ -361,7 +366,12 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
           x0[u] = __ldg(src + lane);
           x1[u] = __ldg(src + 32 + lane);
         }
-        if (PRO && p.pro != kProNone) {
+        if (PRO && p.pro == kProRmsNormLate) {
+          // the norm weights of the block; squares and products follow once every load is out
+          const float4* nw = reinterpret_cast<const float4*>(p.a2 + k0 + blk[u] * kBlockElems);
+          w0[u] = __ldg(nw + lane);
+          w1[u] = __ldg(nw + 32 + lane);
+        } else if (PRO && p.pro != kProNone) {
           const size_t at = static_cast<size_t>(row[u]) * p.k + k0 + blk[u] * kBlockElems;
           if (p.pro == kProSiluMul) {
             const float4* up = reinterpret_cast<const float4*>(p.a2 + at);
@@ -380,6 +390,23 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
         }
       }
     }
+    if (PRO && p.pro == kProRmsNormLate) {
+#pragma unroll
+      for (int u = 0; u < kStageBatch; ++u) {
+        const int it = base + u * kWarps;
+        if (it < items) {
+          // squares of this lane's eight values; the warp's total goes to scratch[item]
+          float ss = 0.0f;
+          ss = fmaf(x0[u].x, x0[u].x, fmaf(x0[u].y, x0[u].y, fmaf(x0[u].z, x0[u].z, fmaf(x0[u].w, x0[u].w, ss))));
+          ss = fmaf(x1[u].x, x1[u].x, fmaf(x1[u].y, x1[u].y, fmaf(x1[u].z, x1[u].z, fmaf(x1[u].w, x1[u].w, ss))));
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, o);
+          if (lane == 0) scratch[it] = ss;
+          x0[u] = scale4(x0[u], 1.0f, w0[u]);
+          x1[u] = scale4(x1[u], 1.0f, w1[u]);
+        }
+      }
+    }
 #pragma unroll
     for (int u = 0; u < kStageBatch; ++u)
       if (base + u * kWarps < items) stage_digits(p, row[u], blk[u], x0[u], x1[u], act, cs, lane);
@@ -387,6 +414,42 @@ __device__ __forceinline__ void stage_activations(const StagedParams& p, int k0,
 #pragma unroll
     for (int u = 0; u < kStageBatch; ++u)
       if (base + u * kWarps < items) stage_sums<GROUPS>(p, row[u], blk[u], act, sums, lane);
+  }
+}
+
+// kProRmsNormLate, after the staging and a CTA-wide barrier: consumer thread i < m adds the
+// squares of row i (block order) and stores the row's gain; the consumer threads then meet on
+// barrier 1 (the scratch area is reused by the first tile's output stage).
+__device__ __forceinline__ void rms_late_gain(const StagedParams& p, const float* scratch, float* gain, int tid,
+                                              int nthreads) {
+  if (tid < p.m) {
+    float s = 0.0f;
+    for (int b = 0; b < p.per; ++b) s += scratch[tid * p.per + b];
+    gain[tid] = 1.0f / sqrtf(s / static_cast<float>(p.k) + p.eps);
+  }
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+}
+// kProRmsNormLate, at the end of the kernel: a_out = a * gain * a2 (the rmsnorm's own output
+// buffer) is written by the CTAs that had a tile less than the others (they would idle
+// otherwise), or by all CTAs, a share each, when every CTA had the same number of tiles.
+__device__ __forceinline__ void rms_late_write(const StagedParams& p, const float* gain, int cta, int ctas, int tid,
+                                               int nthreads) {
+  if (p.a_out == nullptr) return;
+  const int with_more = p.total_tiles % ctas;  // CTAs 0 .. with_more-1 have one tile more
+  int writers = ctas, me = cta;
+  if (with_more != 0) {
+    writers = ctas - with_more;
+    me = cta - with_more;
+    if (me < 0) return;
+  }
+  const int per_row = p.k / 4, total = p.m * per_row;
+  const int share = (total + writers - 1) / writers;
+  const int end = min(total, (me + 1) * share);
+  for (int q = me * share + tid; q < end; q += nthreads) {
+    const int i = q / per_row, c4 = q - i * per_row;
+    const float4 x = __ldg(reinterpret_cast<const float4*>(p.a) + q);
+    const float4 w = __ldg(reinterpret_cast<const float4*>(p.a2) + c4);
+    reinterpret_cast<float4*>(p.a_out)[q] = scale4(x, gain[i], w);
   }
 }
 

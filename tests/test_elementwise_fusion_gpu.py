@@ -120,7 +120,7 @@ class Block:
 def test_ffn_block_through_the_deferred_queue(backend, oracle, m, down_fmt, in_place):
     """Eight launches of the reference's sequence (rmsnorm, 2 x (vec [+ reduce]), silu_mul,
     vec + reduce, add) leave the queue as two kernels: [rmsnorm + gate + up] and
-    [silu_mul + down + add]."""
+    [silu_mul + down + add] (three when silu_mul stays a kernel of its own: m = 8 here)."""
     hidden, ffn = 2048, 4096
     blk = Block(backend, oracle, m, hidden, ffn, down_fmt, seed=200 + m, in_place_residual=in_place)
     proj = Projector(backend)
@@ -135,7 +135,9 @@ def test_ffn_block_through_the_deferred_queue(backend, oracle, m, down_fmt, in_p
             blk.issue(backend, proj)
             backend.Synchronize()
             api1, dev1, graphs1 = backend.LaunchStats()
-            assert dev1 - dev0 == 2, dev1 - dev0
+            # silu_mul is folded only while the work every CTA repeats stays small (row tiles x m x k)
+            folded_silu = ((hidden + 47) // 48) * m * ffn <= 1000000
+            assert dev1 - dev0 == (2 if folded_silu else 3), dev1 - dev0
             if rep >= 2 and api1 - api0 >= 8:   # queues of eight launches or more are replayed as graphs
                 assert graphs1 - graphs0 == 1
             blk.check(backend)
