@@ -89,7 +89,6 @@ moe_gate_up_q4k_kernel(const float* __restrict__ x, const uint8_t* __restrict__ 
                        const uint32_t* __restrict__ ids, float* __restrict__ phi, int hidden, int inter, int top_k,
                        size_t gate_stride, size_t up_stride, int experts) {
   extern __shared__ __align__(16) float xs[];
-  pdl_trigger();  // a dependent launch may become resident as soon as this grid leaves room
   for (int t = threadIdx.x; t < hidden / 4; t += blockDim.x)
     reinterpret_cast<float4*>(xs)[t] = __ldg(reinterpret_cast<const float4*>(x) + t);
   __syncthreads();
@@ -144,31 +143,15 @@ template <bool Q6>
 __global__ void __launch_bounds__(kMoeWarps * 32)
 moe_down_kernel(const float* __restrict__ phi, const uint8_t* __restrict__ down, const uint32_t* __restrict__ ids,
                 const float* __restrict__ wts, float* __restrict__ out, int hidden, int inter, int top_k,
-                size_t down_stride, int accumulate, int experts, int pdl) {
+                size_t down_stride, int accumulate, int experts) {
   extern __shared__ __align__(16) float ps[];
-  const int j = blockIdx.x * kMoeWarps + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  const int nb = inter / kBlockElems;
-  if (pdl) {
-    // Launched as a programmatic dependent of the kernel that writes phi: the expert ids and
-    // the weights are older than that kernel (the launcher's caller guarantees it for the ids:
-    // they come from the routing step), so this warp's rows are pulled towards L2 before the wait.
-    if (j < hidden) {
-      const size_t row_bytes = static_cast<size_t>(nb) * (Q6 ? kQ6KBlockBytes : kQ4KBlockBytes);
-      for (int slot = 0; slot < top_k; ++slot) {
-        const uint32_t e = ids[slot];
-        if (e >= static_cast<uint32_t>(experts)) continue;
-        const uint8_t* row = down + e * down_stride + static_cast<size_t>(j) * row_bytes;
-        for (size_t off = static_cast<size_t>(lane) * 128; off < row_bytes; off += 32 * 128)
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(row + off));
-      }
-    }
-    pdl_wait();
-  }
   for (int t = threadIdx.x; t < top_k * inter / 4; t += blockDim.x)
     reinterpret_cast<float4*>(ps)[t] = __ldg(reinterpret_cast<const float4*>(phi) + t);
   __syncthreads();
+  const int j = blockIdx.x * kMoeWarps + (threadIdx.x >> 5);
   if (j >= hidden) return;
+  const int lane = threadIdx.x & 31;
+  const int nb = inter / kBlockElems;
   float acc = 0.0f;
   if (Q6) {
     // a whole warp per block; two (slot, block) pairs are loaded before the first is used
@@ -299,21 +282,18 @@ int tsr_moe_experts_down(int fmt, const float* phi, const void* down, const uint
   const size_t smem = top_k * inter * 4;
   const unsigned blocks = static_cast<unsigned>((hidden + kMoeWarps - 1) / kMoeWarps);
   auto st = static_cast<cudaStream_t>(stream);
-  // phi is the only input written by the launch before this one (moe_experts_gate_up_q4k); the
-  // ids and weights are not, so the kernel may start early and prefetch (see the kernel)
-  const bool pdl = pdl_allowed(st, down, 1, out, hidden * 4);
   if (fmt == 0) {
     if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&moe_down_kernel<false>), 227 * 1024)) return rc;
-    launch_kernel(moe_down_kernel<false>, dim3(blocks), dim3(kMoeWarps * 32), smem, st, pdl, phi,
-                  static_cast<const uint8_t*>(down), ids, wts, out, static_cast<int>(hidden), static_cast<int>(inter),
-                  static_cast<int>(top_k), static_cast<size_t>(down_stride), accumulate != 0 ? 1 : 0,
-                  static_cast<int>(experts), pdl ? 1 : 0);
+    moe_down_kernel<false><<<blocks, kMoeWarps * 32, smem, st>>>(phi, static_cast<const uint8_t*>(down), ids, wts, out,
+                                                                  static_cast<int>(hidden), static_cast<int>(inter),
+                                                                  static_cast<int>(top_k), down_stride,
+                                                                  accumulate != 0 ? 1 : 0, static_cast<int>(experts));
   } else {
     if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&moe_down_kernel<true>), 227 * 1024)) return rc;
-    launch_kernel(moe_down_kernel<true>, dim3(blocks), dim3(kMoeWarps * 32), smem, st, pdl, phi,
-                  static_cast<const uint8_t*>(down), ids, wts, out, static_cast<int>(hidden), static_cast<int>(inter),
-                  static_cast<int>(top_k), static_cast<size_t>(down_stride), accumulate != 0 ? 1 : 0,
-                  static_cast<int>(experts), pdl ? 1 : 0);
+    moe_down_kernel<true><<<blocks, kMoeWarps * 32, smem, st>>>(phi, static_cast<const uint8_t*>(down), ids, wts, out,
+                                                                 static_cast<int>(hidden), static_cast<int>(inter),
+                                                                 static_cast<int>(top_k), down_stride,
+                                                                 accumulate != 0 ? 1 : 0, static_cast<int>(experts));
   }
   return check_launch();
 }
