@@ -223,6 +223,28 @@ int tsr_moe_experts_gate_up_q4k(const float* x, const void* gate, const void* up
 int tsr_moe_experts_down(int fmt, const float* phi, const void* down, const uint32_t* ids, const float* wts,
                          float* out, uint64_t hidden, uint64_t inter, uint64_t top_k, uint64_t down_stride,
                          uint64_t accumulate, uint64_t experts, void* stream);
+/* Elementwise / row-wise steps between the projections (contracts: backend.hpp:217-254,386-390;
+ * arithmetic: the *Ref functions of src/core/numerics/norm.cpp:96-262, attention.cpp:290-334).
+ * sigmoid_gate: O = A * sigmoid(G) */
+int tsr_sigmoid_gate(const float* a, const float* g, float* o, uint64_t n, void* stream);
+/* l2norm: Y = scale * X / sqrt(sum(X^2) + eps) per row */
+int tsr_l2norm(const float* x, float* y, uint64_t rows, uint64_t cols, float eps, float scale, void* stream);
+/* rmsnorm_gated: Y[ybase + i] = X[i] / sqrt(mean(X_row^2) + eps) * W[col] * silu(G[gbase + i]) */
+int tsr_rmsnorm_gated(const float* x, const float* w, const float* gate, float* y, uint64_t rows, uint64_t cols,
+                      float eps, uint64_t gbase, uint64_t ybase, void* stream);
+/* ssm_gate: alpha = exp(a_log[h] * softplus(alpha_raw + dt[h])), beta = sigmoid(beta_raw), rows x heads */
+int tsr_ssm_gate(const float* a_log, const float* dt, const float* alpha_raw, const float* beta_raw, float* alpha,
+                 float* beta, uint64_t heads, uint64_t rows, void* stream);
+/* qgate_split: fused rows x heads x (query | gate) -> Q, G */
+int tsr_qgate_split(const float* fused, float* q, float* gate, uint64_t heads, uint64_t head_dim, uint64_t rows,
+                    void* stream);
+/* repeat_heads: out[r][h] = in[r][h % (num_v_heads / factor)] */
+int tsr_repeat_heads(const float* in, float* out, uint64_t num_v_heads, uint64_t head_k_dim, uint64_t factor,
+                     uint64_t rows, void* stream);
+/* embedding_f32 (kind 0) / embedding_bf16 (1) / embedding_q4k (2): out[row] = table[ids[row]] as fp32,
+ * a zero row for an id >= vocab; cols a multiple of 256 for Q4_K (backend.hpp:261-265) */
+int tsr_embedding(int kind, const uint32_t* ids, const void* table, float* out, uint64_t rows, uint64_t cols,
+                  uint64_t vocab, void* stream);
 /* silu_mul: O = silu(G) * U, backend.hpp:257-260; SiluMulRef src/core/numerics/norm.cpp:211-225 */
 int tsr_silu_mul(const float* g, const float* u, float* o, uint64_t n, void* stream);
 /* rmsnorm: Y = X / sqrt(mean(X^2) + eps) * W per row, backend.hpp:212-216; RmsNormRef

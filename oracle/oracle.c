@@ -467,6 +467,79 @@ int orc_silu_mul(const float* g, const float* u, float* o, size_t n) {
   return 0;
 }
 
+/* SigmoidGateRef, src/core/numerics/norm.cpp:96-110 */
+int orc_sigmoid_gate(const float* a, const float* g, float* o, size_t n) {
+  if (n == 0) return -2;
+  for (size_t i = 0; i < n; ++i) o[i] = a[i] / (1.0f + expf(-g[i]));
+  return 0;
+}
+
+/* L2NormRef, norm.cpp:112-134: squares added in order with fma, gain = scale / sqrt(sum + eps) */
+int orc_l2norm(const float* x, float* y, size_t rows, size_t cols, float eps, float scale) {
+  if (rows == 0 || cols == 0 || eps < 0.0f) return -2;
+  for (size_t r = 0; r < rows; ++r) {
+    const float* xr = x + r * cols;
+    float sum = 0.0f;
+    for (size_t c = 0; c < cols; ++c) sum = fmaf(xr[c], xr[c], sum);
+    const float gain = scale / sqrtf(sum + eps);
+    for (size_t c = 0; c < cols; ++c) y[r * cols + c] = xr[c] * gain;
+  }
+  return 0;
+}
+
+/* RmsNormGatedRef, norm.cpp:136-164 */
+int orc_rmsnorm_gated(const float* x, const float* w, const float* gate, float* y, size_t rows, size_t cols, float eps) {
+  if (rows == 0 || cols == 0 || eps < 0.0f) return -2;
+  for (size_t r = 0; r < rows; ++r) {
+    const float* xr = x + r * cols;
+    const float* gr = gate + r * cols;
+    float mean = 0.0f;
+    for (size_t c = 0; c < cols; ++c) mean = fmaf(xr[c], xr[c], mean);
+    mean /= (float)cols;
+    const float gain = 1.0f / sqrtf(mean + eps);
+    for (size_t c = 0; c < cols; ++c) {
+      const float silu = gr[c] / (1.0f + expf(-gr[c]));
+      y[r * cols + c] = xr[c] * gain * w[c] * silu;
+    }
+  }
+  return 0;
+}
+
+/* SsmGateRef, norm.cpp:228-251 */
+int orc_ssm_gate(const float* a_log, const float* dt, const float* alpha_raw, const float* beta_raw, float* alpha,
+                 float* beta, size_t heads, size_t rows) {
+  if (heads == 0 || rows == 0) return -2;
+  for (size_t r = 0; r < rows; ++r)
+    for (size_t h = 0; h < heads; ++h) {
+      const size_t i = r * heads + h;
+      const float raw = alpha_raw[i] + dt[h];
+      const float softplus = raw > 20.0f ? raw : log1pf(expf(raw));
+      alpha[i] = expf(a_log[h] * softplus);
+      beta[i] = 1.0f / (1.0f + expf(-beta_raw[i]));
+    }
+  return 0;
+}
+
+/* QGateSplitRef, src/core/numerics/attention.cpp:290-313 */
+int orc_qgate_split(const float* fused, float* q, float* gate, size_t heads, size_t head_dim, size_t rows) {
+  if (heads == 0 || head_dim == 0 || rows == 0) return -2;
+  for (size_t rh = 0; rh < rows * heads; ++rh)
+    for (size_t e = 0; e < head_dim; ++e) {
+      q[rh * head_dim + e] = fused[rh * 2 * head_dim + e];
+      gate[rh * head_dim + e] = fused[rh * 2 * head_dim + head_dim + e];
+    }
+  return 0;
+}
+
+/* RepeatHeadsRef, attention.cpp:315-334 (one row) */
+int orc_repeat_heads(const float* in, float* out, size_t num_v_heads, size_t head_k_dim, size_t factor) {
+  if (num_v_heads == 0 || head_k_dim == 0 || factor == 0 || num_v_heads % factor != 0) return -2;
+  const size_t num_k_heads = num_v_heads / factor;
+  for (size_t h = 0; h < num_v_heads; ++h)
+    for (size_t e = 0; e < head_k_dim; ++e) out[h * head_k_dim + e] = in[(h % num_k_heads) * head_k_dim + e];
+  return 0;
+}
+
 /* ------------------------------------------------------------ routed experts */
 
 /* moe_gate (rocm_kernels_basic.cpp:1896-1929): softmax over the selected logits and the

@@ -77,6 +77,14 @@ int orc_round_bf16(float* x, size_t n);                                         
 int orc_rmsnorm(const float* x, const float* w, float* y, size_t rows, size_t cols, float eps);  /* norm.cpp:7-32 */
 int orc_add(const float* a, const float* b, float* o, size_t n);                               /* norm.cpp:196-209 */
 int orc_silu_mul(const float* g, const float* u, float* o, size_t n);                          /* norm.cpp:211-225 */
+int orc_sigmoid_gate(const float* a, const float* g, float* o, size_t n);                      /* norm.cpp:96-110 */
+int orc_l2norm(const float* x, float* y, size_t rows, size_t cols, float eps, float scale);    /* norm.cpp:112-134 */
+int orc_rmsnorm_gated(const float* x, const float* w, const float* gate, float* y, size_t rows, size_t cols,
+                      float eps);                                                              /* norm.cpp:136-164 */
+int orc_ssm_gate(const float* a_log, const float* dt, const float* alpha_raw, const float* beta_raw, float* alpha,
+                 float* beta, size_t heads, size_t rows);                                      /* norm.cpp:228-251 */
+int orc_qgate_split(const float* fused, float* q, float* gate, size_t heads, size_t head_dim, size_t rows); /* attention.cpp:290-313 */
+int orc_repeat_heads(const float* in, float* out, size_t num_v_heads, size_t head_k_dim, size_t factor);    /* attention.cpp:315-334 */
 
 /* Routed-expert kernels of one token (contracts only the device backends hold:
  * src/backends/rocm/rocm_kernels.hpp:604-640, rocm_kernels_moe.cpp:15-107,

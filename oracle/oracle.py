@@ -188,6 +188,51 @@ class Oracle:
         assert fn(_ptr(g), _ptr(u), _ptr(o), g.size) == 0
         return o
 
+    # ---- steps between the projections (both builds)
+    def sigmoid_gate(self, a, g):
+        a, g = (np.ascontiguousarray(v, dtype=np.float32) for v in (a, g))
+        o = np.empty_like(a)
+        assert self._fn("sigmoid_gate", C.c_int, [_p, _p, _p, _sz])(_ptr(a), _ptr(g), _ptr(o), a.size) == 0
+        return o
+
+    def l2norm(self, x, eps, scale):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.empty_like(x)
+        fn = self._fn("l2norm", C.c_int, [_p, _p, _sz, _sz, C.c_float, C.c_float])
+        assert fn(_ptr(x), _ptr(y), x.shape[0], x.shape[1], eps, scale) == 0
+        return y
+
+    def rmsnorm_gated(self, x, w, gate, eps):
+        x, w, gate = (np.ascontiguousarray(v, dtype=np.float32) for v in (x, w, gate))
+        y = np.empty_like(x)
+        fn = self._fn("rmsnorm_gated", C.c_int, [_p, _p, _p, _p, _sz, _sz, C.c_float])
+        assert fn(_ptr(x), _ptr(w), _ptr(gate), _ptr(y), x.shape[0], x.shape[1], eps) == 0
+        return y
+
+    def ssm_gate(self, a_log, dt, alpha_raw, beta_raw):
+        a_log, dt, alpha_raw, beta_raw = (np.ascontiguousarray(v, dtype=np.float32) for v in (a_log, dt, alpha_raw, beta_raw))
+        alpha, beta = np.empty_like(alpha_raw), np.empty_like(beta_raw)
+        fn = self._fn("ssm_gate", C.c_int, [_p, _p, _p, _p, _p, _p, _sz, _sz])
+        assert fn(_ptr(a_log), _ptr(dt), _ptr(alpha_raw), _ptr(beta_raw), _ptr(alpha), _ptr(beta), a_log.size,
+                  alpha_raw.shape[0]) == 0
+        return alpha, beta
+
+    def qgate_split(self, fused, heads, head_dim, rows):
+        fused = np.ascontiguousarray(fused, dtype=np.float32)
+        q = np.empty(rows * heads * head_dim, dtype=np.float32)
+        gate = np.empty_like(q)
+        fn = self._fn("qgate_split", C.c_int, [_p, _p, _p, _sz, _sz, _sz])
+        assert fn(_ptr(fused), _ptr(q), _ptr(gate), heads, head_dim, rows) == 0
+        return q, gate
+
+    def repeat_heads(self, x, num_v_heads, head_k_dim, factor):
+        """One row (the reference's function takes one; the built-in repeats it per row)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty(num_v_heads * head_k_dim, dtype=np.float32)
+        fn = self._fn("repeat_heads", C.c_int, [_p, _p, _sz, _sz, _sz])
+        assert fn(_ptr(x), _ptr(out), num_v_heads, head_k_dim, factor) == 0
+        return out
+
     # ---- routed experts (device-only contracts; C restatement only)
     def moe_gate(self, vals, x, w):
         assert not self.reference

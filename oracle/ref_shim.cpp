@@ -12,6 +12,7 @@
 #include <span>
 
 #include "core/loaders/tensor_slice.hpp"
+#include "core/numerics/attention.hpp"
 #include "core/numerics/gemm.hpp"
 #include "core/numerics/moe_cpu.hpp"
 #include "core/numerics/norm.hpp"
@@ -112,6 +113,29 @@ int ref_rmsnorm(const float* x, const float* w, float* y, std::size_t rows, std:
 }
 int ref_add(const float* a, const float* b, float* o, std::size_t n) {
   return Code(tc::AddRef({a, n}, {b, n}, {o, n}, n));
+}
+int ref_sigmoid_gate(const float* a, const float* g, float* o, std::size_t n) {
+  return Code(tc::SigmoidGateRef({a, n}, {g, n}, {o, n}, n));
+}
+int ref_l2norm(const float* x, float* y, std::size_t rows, std::size_t cols, float eps, float scale) {
+  return Code(tc::L2NormRef({x, rows * cols}, {y, rows * cols}, rows, cols, eps, scale));
+}
+int ref_rmsnorm_gated(const float* x, const float* w, const float* gate, float* y, std::size_t rows, std::size_t cols,
+                      float eps) {
+  return Code(tc::RmsNormGatedRef({x, rows * cols}, {w, cols}, {gate, rows * cols}, {y, rows * cols}, rows, cols, eps));
+}
+int ref_ssm_gate(const float* a_log, const float* dt, const float* alpha_raw, const float* beta_raw, float* alpha,
+                 float* beta, std::size_t heads, std::size_t rows) {
+  return Code(tc::SsmGateRef({a_log, heads}, {dt, heads}, {alpha_raw, rows * heads}, {beta_raw, rows * heads},
+                             {alpha, rows * heads}, {beta, rows * heads}, heads, rows));
+}
+int ref_qgate_split(const float* fused, float* q, float* gate, std::size_t heads, std::size_t head_dim, std::size_t rows) {
+  const std::size_t n = rows * heads * head_dim;
+  return Code(tc::QGateSplitRef({fused, 2 * n}, {q, n}, {gate, n}, heads, head_dim, rows));
+}
+int ref_repeat_heads(const float* in, float* out, std::size_t num_v_heads, std::size_t head_k_dim, std::size_t factor) {
+  return Code(tc::RepeatHeadsRef({in, (num_v_heads / factor) * head_k_dim}, {out, num_v_heads * head_k_dim}, num_v_heads,
+                                 head_k_dim, factor));
 }
 int ref_silu_mul(const float* g, const float* u, float* o, std::size_t n) {
   return Code(tc::SiluMulRef({g, n}, {u, n}, {o, n}, n));

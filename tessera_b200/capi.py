@@ -99,6 +99,13 @@ SIGNATURES = {
     "tsr_add": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
     "tsr_fill": (C.c_int, [_vp, C.c_int32, _u64, _vp]),
     "tsr_silu_mul": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
+    "tsr_sigmoid_gate": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
+    "tsr_embedding": (C.c_int, [C.c_int, _vp, _vp, _vp, _u64, _u64, _u64, _vp]),
+    "tsr_l2norm": (C.c_int, [_vp, _vp, _u64, _u64, C.c_float, C.c_float, _vp]),
+    "tsr_rmsnorm_gated": (C.c_int, [_vp, _vp, _vp, _vp, _u64, _u64, C.c_float, _u64, _u64, _vp]),
+    "tsr_ssm_gate": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _vp]),
+    "tsr_qgate_split": (C.c_int, [_vp, _vp, _vp, _u64, _u64, _u64, _vp]),
+    "tsr_repeat_heads": (C.c_int, [_vp, _vp, _u64, _u64, _u64, _u64, _vp]),
     "tsr_moe_gate": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u64, _u64, _vp]),
     "tsr_moe_scale_add": (C.c_int, [_vp, _vp, _vp, _vp, _u64, _u64, _vp]),
     "tsr_moe_experts_gate_up_q4k": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64, _u64, _u64, _vp]),

@@ -378,6 +378,95 @@ int k_rmsnorm(const Args& a) {
                      static_cast<float*>(const_cast<void*>(a.buf[2])), rows, cols, eps, a.stream);
 }
 
+// sigmoid_gate: buffers A, G, O; scalar n (backend.hpp:217-219).
+int k_sigmoid_gate(const Args& a) {
+  if (!shape(a, 3, 1)) return kInvalidArgument;
+  const uint64_t n = a.sc[0];
+  if (n == 0 || !holds(a, 0, n * 4) || !holds(a, 1, n * 4) || !holds(a, 2, n * 4)) return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_sigmoid_gate(static_cast<const float*>(a.buf[0]), static_cast<const float*>(a.buf[1]),
+                          static_cast<float*>(const_cast<void*>(a.buf[2])), n, a.stream);
+}
+
+// l2norm: buffers X, Y; scalars rows, cols, eps bits, scale bits (backend.hpp:220-223).
+int k_l2norm(const Args& a) {
+  if (!shape(a, 2, 4)) return kInvalidArgument;
+  const uint64_t rows = a.sc[0], cols = a.sc[1];
+  const float eps = float_of_bits(a.sc[2]), scale = float_of_bits(a.sc[3]);
+  if (!dims_ok(rows, cols, 1) || !(eps >= 0.0f) || !holds(a, 0, rows * cols * 4) || !holds(a, 1, rows * cols * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_l2norm(static_cast<const float*>(a.buf[0]), static_cast<float*>(const_cast<void*>(a.buf[1])), rows, cols, eps,
+                    scale, a.stream);
+}
+
+// rmsnorm_gated: buffers X, W, gate, Y; scalars rows, cols, eps bits, gbase, ybase (backend.hpp:224-233).
+int k_rmsnorm_gated(const Args& a) {
+  if (!shape(a, 4, 5)) return kInvalidArgument;
+  const uint64_t rows = a.sc[0], cols = a.sc[1], gbase = a.sc[3], ybase = a.sc[4];
+  const float eps = float_of_bits(a.sc[2]);
+  if (!dims_ok(rows, cols, 1) || !(eps >= 0.0f) || gbase > kMaxDim * 1024 || ybase > kMaxDim * 1024) return kInvalidArgument;
+  if (!holds(a, 0, rows * cols * 4) || !holds(a, 1, cols * 4) || !holds(a, 2, (gbase + rows * cols) * 4) ||
+      !holds(a, 3, (ybase + rows * cols) * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_rmsnorm_gated(static_cast<const float*>(a.buf[0]), static_cast<const float*>(a.buf[1]),
+                           static_cast<const float*>(a.buf[2]), static_cast<float*>(const_cast<void*>(a.buf[3])), rows, cols,
+                           eps, gbase, ybase, a.stream);
+}
+
+// ssm_gate: buffers a_log, dt (heads), alpha_raw, beta_raw, alpha, beta (rows x heads); scalars heads, rows
+// (backend.hpp:234-238).
+int k_ssm_gate(const Args& a) {
+  if (!shape(a, 6, 2)) return kInvalidArgument;
+  const uint64_t heads = a.sc[0], rows = a.sc[1];
+  if (!dims_ok(heads, rows, 1) || !holds(a, 0, heads * 4) || !holds(a, 1, heads * 4)) return kInvalidArgument;
+  for (int i = 2; i < 6; ++i)
+    if (!holds(a, i, rows * heads * 4)) return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_ssm_gate(static_cast<const float*>(a.buf[0]), static_cast<const float*>(a.buf[1]),
+                      static_cast<const float*>(a.buf[2]), static_cast<const float*>(a.buf[3]),
+                      static_cast<float*>(const_cast<void*>(a.buf[4])), static_cast<float*>(const_cast<void*>(a.buf[5])),
+                      heads, rows, a.stream);
+}
+
+// qgate_split: buffers fused, Q, G; scalars heads, head_dim, rows (backend.hpp:386-390).
+int k_qgate_split(const Args& a) {
+  if (!shape(a, 3, 3)) return kInvalidArgument;
+  const uint64_t heads = a.sc[0], dim = a.sc[1], rows = a.sc[2];
+  if (!dims_ok(heads, dim, rows)) return kInvalidArgument;
+  const uint64_t n = rows * heads * dim;
+  if (!holds(a, 0, 2 * n * 4) || !holds(a, 1, n * 4) || !holds(a, 2, n * 4)) return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_qgate_split(static_cast<const float*>(a.buf[0]), static_cast<float*>(const_cast<void*>(a.buf[1])),
+                         static_cast<float*>(const_cast<void*>(a.buf[2])), heads, dim, rows, a.stream);
+}
+
+// repeat_heads: buffers IN, OUT; scalars num_v_heads, head_k_dim, factor, rows (backend.hpp:249-254).
+int k_repeat_heads(const Args& a) {
+  if (!shape(a, 2, 4)) return kInvalidArgument;
+  const uint64_t vh = a.sc[0], dim = a.sc[1], factor = a.sc[2], rows = a.sc[3];
+  if (!dims_ok(vh, dim, rows) || factor == 0 || vh % factor != 0) return kInvalidArgument;
+  if (!holds(a, 0, rows * (vh / factor) * dim * 4) || !holds(a, 1, rows * vh * dim * 4)) return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_repeat_heads(static_cast<const float*>(a.buf[0]), static_cast<float*>(const_cast<void*>(a.buf[1])), vh, dim,
+                          factor, rows, a.stream);
+}
+
+// embedding_f32 / _bf16 / _q4k: buffers ids (u32, rows), table (vocab x cols), out (fp32, rows x cols);
+// scalars rows, cols, vocab (backend.hpp:261-265).
+template <int KIND>
+int k_embedding(const Args& a) {
+  if (!shape(a, 3, 3)) return kInvalidArgument;
+  const uint64_t rows = a.sc[0], cols = a.sc[1], vocab = a.sc[2];
+  if (!dims_ok(rows, cols, vocab) || (KIND == 2 && cols % 256 != 0)) return kInvalidArgument;
+  const uint64_t table = KIND == 0 ? vocab * cols * 4 : KIND == 1 ? vocab * cols * 2 : vocab * (cols / 256) * 144;
+  if (!holds(a, 0, rows * 4) || !holds(a, 1, table) || !holds(a, 2, rows * cols * 4)) return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_embedding(KIND, static_cast<const uint32_t*>(a.buf[0]), a.buf[1], static_cast<float*>(const_cast<void*>(a.buf[2])),
+                       rows, cols, vocab, a.stream);
+}
+
 // fill: buffer int32; scalars value, count (backend.hpp:151-152).
 int k_fill(const Args& a) {
   if (!shape(a, 1, 2)) return kInvalidArgument;
@@ -573,6 +662,15 @@ const Entry kTable[] = {
     {"add", k_add},
     {"silu_mul", k_silu_mul},
     {"rmsnorm", k_rmsnorm},
+    {"sigmoid_gate", k_sigmoid_gate},
+    {"l2norm", k_l2norm},
+    {"rmsnorm_gated", k_rmsnorm_gated},
+    {"ssm_gate", k_ssm_gate},
+    {"qgate_split", k_qgate_split},
+    {"repeat_heads", k_repeat_heads},
+    {"embedding_f32", k_embedding<0>},
+    {"embedding_bf16", k_embedding<1>},
+    {"embedding_q4k", k_embedding<2>},
     {"round_bf16", k_round},
     {"gemm_q4k", k_block_plain<144, false>},
     {"gemm_q4k_row", k_block_plain<144, false>},

@@ -1,0 +1,207 @@
+// Elementwise and row-wise steps of the reference's forward that sit between the
+// projections (src/models/qwen3_5/trunk.cpp:486-501 loads them by these ids):
+// sigmoid_gate, l2norm, rmsnorm_gated, ssm_gate, qgate_split, repeat_heads.
+// Contracts: include/tessera/backend.hpp:217-254,386-390 of the reference; arithmetic:
+// src/core/numerics/norm.cpp:96-262 and attention.cpp:290-334 (the *Ref functions).
+// All of them move a few KB to a few hundred KB per token: one pass, coalesced, fp32.
+#include "codec.cuh"
+#include "launch.h"
+#include "tessera_b200.h"
+
+namespace tsr {
+namespace {
+
+// O = A * sigmoid(G) (SigmoidGateRef: a / (1 + exp(-g)))
+__global__ void sigmoid_gate_kernel(const float* __restrict__ a, const float* __restrict__ g, float* __restrict__ o,
+                                    size_t n) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) o[i] = a[i] / (1.0f + expf(-g[i]));
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+    if (threadIdx.x == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
+// Y = scale * X / sqrt(sum(X^2) + eps), one CTA per row (L2NormRef; the squares are added as a tree)
+__global__ void __launch_bounds__(256)
+l2norm_kernel(const float* __restrict__ x, float* __restrict__ y, int cols, float eps, float scale) {
+  __shared__ float red[32];
+  const float* row = x + static_cast<size_t>(blockIdx.x) * cols;
+  float s = 0.0f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) s = fmaf(row[c], row[c], s);
+  const float gain = scale / sqrtf(block_sum(s, red) + eps);
+  float* out = y + static_cast<size_t>(blockIdx.x) * cols;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) out[c] = row[c] * gain;
+}
+
+// Y[ybase + r*cols + c] = X[r*cols + c] / sqrt(mean(X_r^2) + eps) * W[c] * silu(G[gbase + r*cols + c])
+// (RmsNormGatedRef; the bases address one token's slice of a batched buffer)
+__global__ void __launch_bounds__(256)
+rmsnorm_gated_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ gate,
+                     float* __restrict__ y, int cols, float eps, size_t gbase, size_t ybase) {
+  __shared__ float red[32];
+  const size_t base = static_cast<size_t>(blockIdx.x) * cols;
+  const float* row = x + base;
+  float s = 0.0f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) s = fmaf(row[c], row[c], s);
+  const float gain = 1.0f / sqrtf(block_sum(s, red) / static_cast<float>(cols) + eps);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float g = gate[gbase + base + c];
+    const float silu = g / (1.0f + expf(-g));
+    y[ybase + base + c] = row[c] * gain * w[c] * silu;
+  }
+}
+
+// alpha = exp(a_log[h] * softplus(alpha_raw + dt[h])), beta = sigmoid(beta_raw) (SsmGateRef)
+__global__ void ssm_gate_kernel(const float* __restrict__ a_log, const float* __restrict__ dt,
+                                const float* __restrict__ alpha_raw, const float* __restrict__ beta_raw,
+                                float* __restrict__ alpha, float* __restrict__ beta, size_t heads, size_t total) {
+  const size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= total) return;
+  const size_t h = t % heads;
+  const float raw = alpha_raw[t] + dt[h];
+  const float softplus = raw > 20.0f ? raw : log1pf(expf(raw));
+  alpha[t] = expf(a_log[h] * softplus);
+  beta[t] = 1.0f / (1.0f + expf(-beta_raw[t]));
+}
+
+// fused[(r*heads + h)*2*d + e] -> q[(r*heads + h)*d + e], fused[... + d + e] -> gate[...] (QGateSplitRef)
+__global__ void qgate_split_kernel(const float* __restrict__ fused, float* __restrict__ q, float* __restrict__ gate,
+                                   size_t head_dim, size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t rh = i / head_dim, e = i - rh * head_dim;
+  const float* src = fused + rh * 2 * head_dim;
+  q[i] = src[e];
+  gate[i] = src[head_dim + e];
+}
+
+// out[r][h][e] = in[r][h % (num_v_heads / factor)][e] (RepeatHeadsRef, row by row)
+__global__ void repeat_heads_kernel(const float* __restrict__ in, float* __restrict__ out, size_t num_v_heads,
+                                    size_t head_k_dim, size_t num_k_heads, size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t e = i % head_k_dim, rh = i / head_k_dim;
+  const size_t h = rh % num_v_heads, r = rh / num_v_heads;
+  out[i] = in[(r * num_k_heads + h % num_k_heads) * head_k_dim + e];
+}
+
+// Out[row] = table[ids[row]] as fp32, a zero row for an id outside the table
+// (include/tessera/backend.hpp:261-265).  KIND 0: fp32 table, 1: bf16, 2: Q4_K rows of cols/256
+// blocks, decoded with the reference's rounding sequence (src/core/numerics/quant.cpp:656-675).
+template <int KIND>
+__global__ void embedding_kernel(const uint32_t* __restrict__ ids, const uint8_t* __restrict__ table,
+                                 float* __restrict__ out, size_t cols, size_t vocab, size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t r = i / cols, t = i - r * cols;
+  const size_t id = ids[r];
+  float v = 0.0f;
+  if (id < vocab) {
+    if (KIND == 0) {
+      v = reinterpret_cast<const float*>(table)[id * cols + t];
+    } else if (KIND == 1) {
+      v = __uint_as_float(static_cast<uint32_t>(reinterpret_cast<const unsigned short*>(table)[id * cols + t]) << 16);
+    } else {
+      const uint8_t* blk = table + (id * (cols / 256) + t / 256) * kQ4KBlockBytes;
+      const int e = static_cast<int>(t % 256), g = e / 64, hi = (e % 64) / 32, l = e % 32;
+      const float d = fp16_bits_to_float(blk[0] | (blk[1] << 8));
+      const float dmin = fp16_bits_to_float(blk[2] | (blk[3] << 8));
+      uint32_t s[3];
+      for (int w = 0; w < 3; ++w)
+        s[w] = blk[4 + 4 * w] | (blk[5 + 4 * w] << 8) | (blk[6 + 4 * w] << 16) | (static_cast<uint32_t>(blk[7 + 4 * w]) << 24);
+      uint32_t sc, mn;
+      q4k_scale_min(s, 2 * g + hi, sc, mn);
+      const uint32_t byte = blk[16 + 32 * g + l];
+      const float q = static_cast<float>(hi ? (byte >> 4) : (byte & 15u));
+      v = __fsub_rn(__fmul_rn(__fmul_rn(d, static_cast<float>(sc)), q), __fmul_rn(dmin, static_cast<float>(mn)));
+    }
+  }
+  out[i] = v;
+}
+
+unsigned blocks_of(size_t n) { return static_cast<unsigned>((n + 255) / 256); }
+bool fits31(uint64_t v) { return v > 0 && v <= 0x7FFFFFFFull; }
+
+}  // namespace
+}  // namespace tsr
+
+using namespace tsr;
+
+extern "C" {
+
+int tsr_sigmoid_gate(const float* a, const float* g, float* o, uint64_t n, void* stream) {
+  if (!a || !g || !o || n == 0) return kInvalidArgument;
+  sigmoid_gate_kernel<<<blocks_of(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(a, g, o, n);
+  return check_launch();
+}
+
+int tsr_l2norm(const float* x, float* y, uint64_t rows, uint64_t cols, float eps, float scale, void* stream) {
+  if (!x || !y || !fits31(rows) || !fits31(cols) || !(eps >= 0.0f)) return kInvalidArgument;
+  l2norm_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, static_cast<int>(cols),
+                                                                                            eps, scale);
+  return check_launch();
+}
+
+int tsr_rmsnorm_gated(const float* x, const float* w, const float* gate, float* y, uint64_t rows, uint64_t cols,
+                      float eps, uint64_t gbase, uint64_t ybase, void* stream) {
+  if (!x || !w || !gate || !y || !fits31(rows) || !fits31(cols) || !(eps >= 0.0f)) return kInvalidArgument;
+  rmsnorm_gated_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, w, gate, y, static_cast<int>(cols), eps, gbase, ybase);
+  return check_launch();
+}
+
+int tsr_ssm_gate(const float* a_log, const float* dt, const float* alpha_raw, const float* beta_raw, float* alpha,
+                 float* beta, uint64_t heads, uint64_t rows, void* stream) {
+  if (!a_log || !dt || !alpha_raw || !beta_raw || !alpha || !beta || !fits31(heads) || !fits31(rows)) return kInvalidArgument;
+  const size_t total = heads * rows;
+  ssm_gate_kernel<<<blocks_of(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(a_log, dt, alpha_raw, beta_raw, alpha,
+                                                                                    beta, heads, total);
+  return check_launch();
+}
+
+int tsr_qgate_split(const float* fused, float* q, float* gate, uint64_t heads, uint64_t head_dim, uint64_t rows,
+                    void* stream) {
+  if (!fused || !q || !gate || !fits31(heads) || !fits31(head_dim) || !fits31(rows)) return kInvalidArgument;
+  const size_t total = rows * heads * head_dim;
+  qgate_split_kernel<<<blocks_of(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(fused, q, gate, head_dim, total);
+  return check_launch();
+}
+
+int tsr_embedding(int kind, const uint32_t* ids, const void* table, float* out, uint64_t rows, uint64_t cols,
+                  uint64_t vocab, void* stream) {
+  if (!ids || !table || !out || !fits31(rows) || !fits31(cols) || !fits31(vocab) || kind < 0 || kind > 2 ||
+      (kind == 2 && cols % 256 != 0))
+    return kInvalidArgument;
+  const size_t total = rows * cols;
+  auto st = static_cast<cudaStream_t>(stream);
+  auto* t = static_cast<const uint8_t*>(table);
+  if (kind == 0) embedding_kernel<0><<<blocks_of(total), 256, 0, st>>>(ids, t, out, cols, vocab, total);
+  else if (kind == 1) embedding_kernel<1><<<blocks_of(total), 256, 0, st>>>(ids, t, out, cols, vocab, total);
+  else embedding_kernel<2><<<blocks_of(total), 256, 0, st>>>(ids, t, out, cols, vocab, total);
+  return check_launch();
+}
+
+int tsr_repeat_heads(const float* in, float* out, uint64_t num_v_heads, uint64_t head_k_dim, uint64_t factor,
+                     uint64_t rows, void* stream) {
+  if (!in || !out || !fits31(num_v_heads) || !fits31(head_k_dim) || !fits31(factor) || !fits31(rows) ||
+      num_v_heads % factor != 0)
+    return kInvalidArgument;
+  const size_t total = rows * num_v_heads * head_k_dim;
+  repeat_heads_kernel<<<blocks_of(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(in, out, num_v_heads, head_k_dim,
+                                                                                        num_v_heads / factor, total);
+  return check_launch();
+}
+
+}  // extern "C"

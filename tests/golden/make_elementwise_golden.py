@@ -1,5 +1,6 @@
 """Generates tests/golden/elementwise_golden.npz from the reference's own host functions
-RmsNormRef, AddRef and SiluMulRef (src/core/numerics/norm.cpp of the reference, reached
+RmsNormRef, AddRef, SiluMulRef, SigmoidGateRef, L2NormRef, RmsNormGatedRef, SsmGateRef
+(src/core/numerics/norm.cpp) and QGateSplitRef, RepeatHeadsRef (attention.cpp of the reference, reached
 through oracle/_ref/libtessera_ref.so, which oracle/Makefile builds from the reference
 checkout).  Run from the repository root where the reference checkout is available:
 
@@ -37,6 +38,29 @@ def main() -> None:
     a = (g.standard_normal(777) * 1e3).astype(np.float32)
     b = g.standard_normal(777).astype(np.float32)
     out["add_a"], out["add_b"], out["add_o"] = a, b, ref.add(a, b)
+    # the steps between the projections
+    out["sig_a"], out["sig_g"] = a[:500].copy(), gate[:500].copy()
+    out["sig_o"] = ref.sigmoid_gate(out["sig_a"], out["sig_g"])
+    out["l2_x"] = x
+    out["l2_y"] = ref.l2norm(x, 1e-6, 0.0883883)
+    gx = g.standard_normal((4, 384)).astype(np.float32)
+    gw = (1.0 + 0.2 * g.standard_normal(384)).astype(np.float32)
+    gg = (g.standard_normal((4, 384)) * 3).astype(np.float32)
+    out["rg_x"], out["rg_w"], out["rg_g"] = gx, gw, gg
+    out["rg_y"] = ref.rmsnorm_gated(gx, gw, gg, 1e-6)
+    heads, rows = 48, 3
+    out["ssm_a_log"] = (-np.exp(g.standard_normal(heads))).astype(np.float32)
+    out["ssm_dt"] = g.standard_normal(heads).astype(np.float32)
+    out["ssm_alpha_raw"] = (g.standard_normal((rows, heads)) * 8).astype(np.float32)
+    out["ssm_alpha_raw"][0, :3] = [25.0, -40.0, 19.99]
+    out["ssm_beta_raw"] = (g.standard_normal((rows, heads)) * 4).astype(np.float32)
+    out["ssm_alpha"], out["ssm_beta"] = ref.ssm_gate(out["ssm_a_log"], out["ssm_dt"], out["ssm_alpha_raw"], out["ssm_beta_raw"])
+    fused = g.standard_normal(2 * 6 * 2 * 32).astype(np.float32)
+    out["qg_fused"] = fused
+    out["qg_q"], out["qg_gate"] = ref.qgate_split(fused, 6, 32, 2)
+    rin = g.standard_normal(4 * 16).astype(np.float32)
+    out["rep_in"] = rin
+    out["rep_out"] = ref.repeat_heads(rin, 12, 16, 3)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "elementwise_golden.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes")

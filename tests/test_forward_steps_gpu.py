@@ -1,0 +1,133 @@
+"""The elementwise and row-wise steps between the projections on the GPU against the CPU
+oracle (bit-equal to the reference's *Ref functions, tests/test_oracle_golden.py): same
+formulas; sums of squares are added as a tree on the device, so norms agree to rounding."""
+import numpy as np
+import pytest
+
+from tessera_b200 import capi
+from tessera_b200.backend import KernelLaunch
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(x):
+    return int(np.float32(x).view(np.uint32))
+
+
+def close(y, r, tol):
+    return bool(np.all(np.abs(y - r) <= tol * np.abs(r) + 1e-30))
+
+
+def run(backend, name, buffers, scalars):
+    backend.LaunchKernel(backend.LoadKernel(name), KernelLaunch(buffers=buffers, scalars=scalars))
+
+
+def test_sigmoid_gate(backend, oracle):
+    g = np.random.default_rng(1)
+    n = 6144 + 3
+    a = g.standard_normal(n).astype(np.float32)
+    gate = (g.standard_normal(n) * 6).astype(np.float32)
+    gate[:3] = [0.0, 95.0, -95.0]
+    out = backend.AllocateBuffer(n * 4)
+    run(backend, "sigmoid_gate", [backend.upload(a), backend.upload(gate), out], [n])
+    assert close(backend.download(out, np.float32, n), oracle.sigmoid_gate(a, gate), 4e-7)
+
+
+@pytest.mark.parametrize("rows,cols", [(48, 128), (3, 1000), (1, 17)])
+def test_l2norm(backend, oracle, rows, cols):
+    g = np.random.default_rng(rows + cols)
+    x = (g.standard_normal((rows, cols)) * 5).astype(np.float32)
+    out = backend.AllocateBuffer(x.nbytes)
+    run(backend, "l2norm", [backend.upload(x), out], [rows, cols, bits(1e-6), bits(0.088388)])
+    assert close(backend.download(out, np.float32, x.size).reshape(rows, cols), oracle.l2norm(x, 1e-6, np.float32(0.088388)), 2e-6)
+
+
+def test_rmsnorm_gated_with_bases(backend, oracle):
+    """The gate is read and the output written at element bases inside larger buffers (one
+    token's slice of a batched buffer)."""
+    g = np.random.default_rng(5)
+    rows, cols, gbase, ybase = 48, 128, 6144, 2 * 6144
+    x = g.standard_normal((rows, cols)).astype(np.float32)
+    w = (1 + 0.1 * g.standard_normal(cols)).astype(np.float32)
+    gate_all = (g.standard_normal(gbase + rows * cols + 64) * 3).astype(np.float32)
+    canary = np.float32(9.5e9)
+    y_all = np.full(ybase + rows * cols + 64, canary, dtype=np.float32)
+    yb = backend.upload(y_all)
+    run(backend, "rmsnorm_gated", [backend.upload(x), backend.upload(w), backend.upload(gate_all), yb],
+        [rows, cols, bits(1e-6), gbase, ybase])
+    got = backend.download(yb, np.float32, y_all.size)
+    assert np.all(got[:ybase] == canary) and np.all(got[ybase + rows * cols:] == canary)
+    want = oracle.rmsnorm_gated(x, w, gate_all[gbase:gbase + rows * cols].reshape(rows, cols), 1e-6)
+    assert close(got[ybase:ybase + rows * cols].reshape(rows, cols), want, 3e-6)
+
+
+def test_ssm_gate(backend, oracle):
+    g = np.random.default_rng(6)
+    heads, rows = 48, 5
+    a_log = (-np.exp(g.standard_normal(heads))).astype(np.float32)
+    dt = g.standard_normal(heads).astype(np.float32)
+    alpha_raw = (g.standard_normal((rows, heads)) * 8).astype(np.float32)
+    alpha_raw[0, :3] = [25.0, -40.0, 19.99]
+    beta_raw = (g.standard_normal((rows, heads)) * 4).astype(np.float32)
+    ab, bb = backend.AllocateBuffer(rows * heads * 4), backend.AllocateBuffer(rows * heads * 4)
+    run(backend, "ssm_gate", [backend.upload(a_log), backend.upload(dt), backend.upload(alpha_raw), backend.upload(beta_raw), ab, bb],
+        [heads, rows])
+    alpha, beta = oracle.ssm_gate(a_log, dt, alpha_raw, beta_raw)
+    assert close(backend.download(ab, np.float32, rows * heads).reshape(rows, heads), alpha, 2e-6)
+    assert close(backend.download(bb, np.float32, rows * heads).reshape(rows, heads), beta, 4e-7)
+
+
+def test_qgate_split_and_repeat_heads_are_exact(backend, oracle):
+    g = np.random.default_rng(7)
+    heads, dim, rows = 24, 256, 3
+    fused = g.standard_normal(rows * heads * 2 * dim).astype(np.float32)
+    qb, gb = backend.AllocateBuffer(fused.nbytes // 2), backend.AllocateBuffer(fused.nbytes // 2)
+    run(backend, "qgate_split", [backend.upload(fused), qb, gb], [heads, dim, rows])
+    q, gate = oracle.qgate_split(fused, heads, dim, rows)
+    assert np.array_equal(backend.download(qb, np.float32, q.size), q)
+    assert np.array_equal(backend.download(gb, np.float32, gate.size), gate)
+    vh, kd, factor, rows = 48, 128, 3, 2
+    x = g.standard_normal(rows * (vh // factor) * kd).astype(np.float32)
+    ob = backend.AllocateBuffer(rows * vh * kd * 4)
+    run(backend, "repeat_heads", [backend.upload(x), ob], [vh, kd, factor, rows])
+    want = np.concatenate([oracle.repeat_heads(x.reshape(rows, -1)[r], vh, kd, factor) for r in range(rows)])
+    assert np.array_equal(backend.download(ob, np.float32, want.size), want)
+
+
+def test_steps_check_their_arguments(backend):
+    buf = backend.AllocateBuffer(1024)
+    for name, buffers, scalars in [
+        ("sigmoid_gate", [buf, buf, buf], [1024]),                              # 4096 bytes needed
+        ("l2norm", [buf, buf], [2, 256, bits(-1.0), bits(1.0)]),                 # eps < 0
+        ("rmsnorm_gated", [buf, buf, buf, buf], [1, 128, bits(1e-6), 200, 0]),   # gate base beyond the buffer
+        ("ssm_gate", [buf, buf, buf, buf, buf, buf], [300, 1]),                  # heads beyond the buffers
+        ("qgate_split", [buf, buf, buf], [4, 64, 1]),                            # fused too small
+        ("repeat_heads", [buf, buf], [12, 16, 5, 1]),                            # heads not divisible
+    ]:
+        with pytest.raises(capi.StatusError):
+            run(backend, name, buffers, scalars)
+    backend.Synchronize()
+
+
+@pytest.mark.parametrize("kind", ["f32", "bf16", "q4k"])
+def test_embedding_rows_are_exact(backend, oracle, kind):
+    """out[row] = table[ids[row]] as fp32, a zero row for an id beyond the table; the Q4_K table
+    is decoded with the reference's rounding sequence (bit-equal to DequantizeQ4K)."""
+    from tessera_b200 import synth
+    g = np.random.default_rng(8)
+    vocab, cols = 50, 512
+    ids = np.array([3, 49, 0, 50, 7, 4000000000], dtype=np.uint32)   # two ids outside the table
+    if kind == "f32":
+        table = g.standard_normal((vocab, cols)).astype(np.float32)
+        dense = table
+    elif kind == "bf16":
+        dense = (g.standard_normal((vocab, cols)).astype(np.float32).view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)
+        table = (dense.view(np.uint32) >> 16).astype(np.uint16)
+    else:
+        table = synth.q4k_weights(vocab, cols, seed=8)
+        dense = oracle.dequant_blocks(0, table).reshape(vocab, cols)
+    out = backend.upload(np.full(ids.size * cols, np.float32(7.0)))
+    run(backend, f"embedding_{kind}", [backend.upload(ids), backend.upload(table), out], [ids.size, cols, vocab])
+    got = backend.download(out, np.float32, ids.size * cols).reshape(ids.size, cols)
+    want = np.stack([dense[i] if i < vocab else np.zeros(cols, dtype=np.float32) for i in ids])
+    assert np.array_equal(got, want)

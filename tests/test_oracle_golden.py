@@ -158,3 +158,18 @@ def test_elementwise_steps_match_golden(oracle):
         assert np.array_equal(oracle.rmsnorm(g["rms_x"], g["rms_w"], float(eps)), g["rms_y"][i])
     assert np.array_equal(oracle.silu_mul(g["silu_g"], g["silu_u"]), g["silu_o"], equal_nan=True)
     assert np.array_equal(oracle.add(g["add_a"], g["add_b"]), g["add_o"])
+
+
+def test_steps_between_the_projections_match_golden(oracle):
+    """SigmoidGateRef, L2NormRef, RmsNormGatedRef, SsmGateRef (norm.cpp), QGateSplitRef, RepeatHeadsRef
+    (attention.cpp) of the reference."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "elementwise_golden.npz"))
+    assert np.array_equal(oracle.sigmoid_gate(g["sig_a"], g["sig_g"]), g["sig_o"])
+    assert np.array_equal(oracle.l2norm(g["l2_x"], 1e-6, 0.0883883), g["l2_y"])
+    assert np.array_equal(oracle.rmsnorm_gated(g["rg_x"], g["rg_w"], g["rg_g"], 1e-6), g["rg_y"])
+    alpha, beta = oracle.ssm_gate(g["ssm_a_log"], g["ssm_dt"], g["ssm_alpha_raw"], g["ssm_beta_raw"])
+    assert np.array_equal(alpha, g["ssm_alpha"]) and np.array_equal(beta, g["ssm_beta"])
+    q, gate = oracle.qgate_split(g["qg_fused"], 6, 32, 2)
+    assert np.array_equal(q, g["qg_q"]) and np.array_equal(gate, g["qg_gate"])
+    assert np.array_equal(oracle.repeat_heads(g["rep_in"], 12, 16, 3), g["rep_out"])
