@@ -409,6 +409,51 @@ def moe_row(stream, hbm_peak, hidden=2048, inter=512, experts=256, top_k=8):
             "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / hbm_peak, 3)}
 
 
+def delta_row(stream, hbm_peak, heads=48, dk=128, dv=128, layers=48):
+    """The gated delta-rule step of the linear-attention layers (delta_step_heads, one token):
+    every layer has its own recurrent state (48 heads x 128 x 128 fp32 = 3.1 MB, 151 MB over the 48
+    layers, more than L2), read once and written once per step.  From a CUDA graph of the 48
+    launches; bytes = state in and out, k, q, v, o."""
+    import torch
+    from tessera_b200.backend import CreateBackend, KernelLaunch
+    backend = CreateBackend(stream=stream.cuda_stream)
+    backend.SetDeviceIndex(torch.cuda.current_device())
+    backend.Init()
+    g = np.random.default_rng(31)
+    states = [backend.upload((g.standard_normal(heads * dk * dv) * 0.1).astype(np.float32)) for _ in range(layers)]
+    k = backend.upload((g.standard_normal(heads * dk) * 0.05).astype(np.float32))
+    q = backend.upload(g.standard_normal(heads * dk).astype(np.float32))
+    v = backend.upload(g.standard_normal(heads * dv).astype(np.float32))
+    alpha = backend.upload(np.full(heads, 0.9, dtype=np.float32))
+    beta = backend.upload(np.full(heads, 0.5, dtype=np.float32))
+    o = backend.AllocateBuffer(heads * dv * 4)
+    kern = backend.LoadKernel("delta_step_heads")
+    with torch.cuda.stream(stream):
+        def step():
+            for s_ in states:
+                backend.LaunchKernel(kern, KernelLaunch(buffers=[s_, k, v, q, o, alpha, beta], scalars=[heads, dk, dv, 1, 0, 0, 0]))
+        step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+            step()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record(stream)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * layers)
+    nbytes = 2 * heads * dk * dv * 4 + 2 * heads * dk * 4 + 2 * heads * dv * 4
+    backend.close()
+    return {"fmt": "delta_step_heads", "heads": heads, "dk": dk, "dv": dv, "us": round(us, 2),
+            "gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / hbm_peak, 3)}
+
+
 class Recorder:
     """Stands in for the backend while the projection planner runs: kernels and buffers come
     from the real backend, launches are recorded instead of issued.  The recorded list is the
@@ -850,6 +895,7 @@ def gpu_arm(args):
         weights.clear()
         line["qgemv"] = qgemv_table(stream, peaks["hbm_gbs"])
         line["qgemv"].append(moe_row(stream, peaks["hbm_gbs"]))
+        line["qgemv"].append(delta_row(stream, peaks["hbm_gbs"]))
         from oracle.oracle import Oracle
         threads = os.cpu_count() or 1
         v, sample = run_cpu_sample(Oracle(), threads, 12.0)
@@ -875,7 +921,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, metavar="FMT:M:N:K[:G]",
-                    help="time one projection (q4k, q6k, mxfp4, fp8, w4a8; or `moe` for the routed experts of one token) "
+                    help="time one projection (q4k, q6k, mxfp4, fp8, w4a8; `moe` for the routed experts of one token, `delta` for the delta-rule state step) "
                          "instead of the decode step, e.g. "
                          "q4k:1:17408:5120; with G (q4k, q6k): G weight tensors of that shape in one merged launch\n"
                          "that picks its own split of k")
@@ -899,6 +945,11 @@ def main():
     elif args.case:
         import torch
         fields = args.case.split(":")
+        if fields[0] == "delta":
+            peaks, kind = measured_peaks()
+            torch.cuda.set_device(0)
+            print(json.dumps({"case": args.case, "peak_kind": kind, **delta_row(torch.cuda.Stream(), peaks["hbm_gbs"])}))
+            return
         if fields[0] == "moe":
             peaks, kind = measured_peaks()
             torch.cuda.set_device(0)

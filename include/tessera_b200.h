@@ -245,6 +245,17 @@ int tsr_repeat_heads(const float* in, float* out, uint64_t num_v_heads, uint64_t
  * a zero row for an id >= vocab; cols a multiple of 256 for Q4_K (backend.hpp:261-265) */
 int tsr_embedding(int kind, const uint32_t* ids, const void* table, float* out, uint64_t rows, uint64_t cols,
                   uint64_t vocab, void* stream);
+/* mrope: rows x heads x head_dim rotated in place; pos = rows x (t, h, w) u64 (backend.hpp:378-385; MropeRef) */
+int tsr_mrope(float* io, const uint64_t* pos, uint64_t rows, uint64_t heads, uint64_t head_dim, uint64_t rope_dim,
+              float theta, uint64_t sec_t, uint64_t sec_h, uint64_t sec_w, void* stream);
+/* cast_f32_f16: fp32 -> binary16, round to nearest even; n even (backend.hpp:334-336) */
+int tsr_cast_f32_f16(const float* in, void* out, uint64_t n, void* stream);
+/* delta_step_heads: `rows` gated delta-rule steps on the per-head state (heads x dk x dv at s + sbase, updated
+ * in place when sstride = 0, else row t's state goes to sbase + (t+1)*sstride); k, q rows x heads x dk; v, o
+ * rows x heads x dv; alpha, beta read at abase + t*heads + h; dk <= 256 (backend.hpp:239-248; DeltaStepHeadsRef) */
+int tsr_delta_step_heads(float* s, const float* k, const float* v, const float* q, float* o, const float* alpha,
+                         const float* beta, uint64_t heads, uint64_t dk, uint64_t dv, uint64_t rows, uint64_t sbase,
+                         uint64_t sstride, uint64_t abase, void* stream);
 /* silu_mul: O = silu(G) * U, backend.hpp:257-260; SiluMulRef src/core/numerics/norm.cpp:211-225 */
 int tsr_silu_mul(const float* g, const float* u, float* o, uint64_t n, void* stream);
 /* rmsnorm: Y = X / sqrt(mean(X^2) + eps) * W per row, backend.hpp:212-216; RmsNormRef

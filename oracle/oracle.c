@@ -540,6 +540,52 @@ int orc_repeat_heads(const float* in, float* out, size_t num_v_heads, size_t hea
   return 0;
 }
 
+/* MropeRef, src/core/numerics/attention.cpp: NeoX pairs (j, j + rope_dim/2); pair j turns by the position of
+ * its section times theta^(-2j/rope_dim); angle, cosine and sine in double, products in fp32. */
+int orc_mrope(float* io, const uint64_t* pos, size_t rows, size_t heads, size_t head_dim, size_t rope_dim, size_t sec_t,
+              size_t sec_h, size_t sec_w, double theta) {
+  if (rows == 0 || heads == 0 || head_dim == 0 || rope_dim == 0 || rope_dim > head_dim || (rope_dim % 2) != 0 || !(theta > 0.0))
+    return -2;
+  const size_t pairs = rope_dim / 2;
+  if (sec_t + sec_h + sec_w > pairs) return -2;
+  for (size_t r = 0; r < rows; ++r)
+    for (size_t h = 0; h < heads; ++h) {
+      float* base = io + (r * heads + h) * head_dim;
+      for (size_t j = 0; j < pairs; ++j) {
+        const uint64_t p = j < sec_t ? pos[r * 3] : j < sec_t + sec_h ? pos[r * 3 + 1] : pos[r * 3 + 2];
+        const double angle = (double)p * pow(theta, -2.0 * (double)j / (double)rope_dim);
+        const float c = (float)cos(angle), sn = (float)sin(angle);
+        const float x1 = base[j], x2 = base[j + pairs];
+        base[j] = x1 * c - x2 * sn;
+        base[j + pairs] = x1 * sn + x2 * c;
+      }
+    }
+  return 0;
+}
+
+/* DeltaStepHeadsRef, attention.cpp: per head and state column d: read = sum_j S[j][d] k[j] (fma, in order);
+ * S[j][d] <- alpha (S[j][d] - beta k[j] read) + beta v[d] k[j]; o[d] = sum_j S'[j][d] q[j]. */
+int orc_delta_step_heads(float* s, const float* k, const float* v, const float* q, float* o, const float* alpha,
+                         const float* beta, size_t heads, size_t dk, size_t dv) {
+  if (heads == 0 || dk == 0 || dv == 0) return -2;
+  for (size_t h = 0; h < heads; ++h) {
+    float* st = s + h * dk * dv;
+    const float *kh = k + h * dk, *qh = q + h * dk, *vh = v + h * dv;
+    for (size_t d = 0; d < dv; ++d) {
+      float read = 0.0f;
+      for (size_t j = 0; j < dk; ++j) read = fmaf(st[j * dv + d], kh[j], read);
+      float out = 0.0f;
+      for (size_t j = 0; j < dk; ++j) {
+        const float updated = alpha[h] * (st[j * dv + d] - beta[h] * kh[j] * read) + beta[h] * vh[d] * kh[j];
+        st[j * dv + d] = updated;
+        out = fmaf(updated, qh[j], out);
+      }
+      o[h * dv + d] = out;
+    }
+  }
+  return 0;
+}
+
 /* ------------------------------------------------------------ routed experts */
 
 /* moe_gate (rocm_kernels_basic.cpp:1896-1929): softmax over the selected logits and the

@@ -85,6 +85,11 @@ int orc_ssm_gate(const float* a_log, const float* dt, const float* alpha_raw, co
                  float* beta, size_t heads, size_t rows);                                      /* norm.cpp:228-251 */
 int orc_qgate_split(const float* fused, float* q, float* gate, size_t heads, size_t head_dim, size_t rows); /* attention.cpp:290-313 */
 int orc_repeat_heads(const float* in, float* out, size_t num_v_heads, size_t head_k_dim, size_t factor);    /* attention.cpp:315-334 */
+int orc_mrope(float* io, const uint64_t* pos, size_t rows, size_t heads, size_t head_dim, size_t rope_dim, size_t sec_t,
+              size_t sec_h, size_t sec_w, double theta);                                        /* attention.cpp MropeRef */
+/* one gated delta-rule step on every head's state, in place (attention.cpp DeltaStepHeadsRef) */
+int orc_delta_step_heads(float* s, const float* k, const float* v, const float* q, float* o, const float* alpha,
+                         const float* beta, size_t heads, size_t dk, size_t dv);
 
 /* Routed-expert kernels of one token (contracts only the device backends hold:
  * src/backends/rocm/rocm_kernels.hpp:604-640, rocm_kernels_moe.cpp:15-107,

@@ -233,6 +233,22 @@ class Oracle:
         assert fn(_ptr(x), _ptr(out), num_v_heads, head_k_dim, factor) == 0
         return out
 
+    def mrope(self, io, pos, rows, heads, head_dim, rope_dim, sec_t, sec_h, sec_w, theta):
+        io = np.ascontiguousarray(io, dtype=np.float32).copy()
+        pos = np.ascontiguousarray(pos, dtype=np.uint64)
+        fn = self._fn("mrope", C.c_int, [_p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _sz, C.c_double])
+        assert fn(_ptr(io), _ptr(pos), rows, heads, head_dim, rope_dim, sec_t, sec_h, sec_w, theta) == 0
+        return io
+
+    def delta_step_heads(self, s, k, v, q, alpha, beta, heads, dk, dv):
+        """One step; returns (new state, o)."""
+        s = np.ascontiguousarray(s, dtype=np.float32).copy()
+        k, v, q, alpha, beta = (np.ascontiguousarray(x, dtype=np.float32) for x in (k, v, q, alpha, beta))
+        o = np.empty(heads * dv, dtype=np.float32)
+        fn = self._fn("delta_step_heads", C.c_int, [_p, _p, _p, _p, _p, _p, _p, _sz, _sz, _sz])
+        assert fn(_ptr(s), _ptr(k), _ptr(v), _ptr(q), _ptr(o), _ptr(alpha), _ptr(beta), heads, dk, dv) == 0
+        return s, o
+
     # ---- routed experts (device-only contracts; C restatement only)
     def moe_gate(self, vals, x, w):
         assert not self.reference

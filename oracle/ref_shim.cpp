@@ -137,6 +137,16 @@ int ref_repeat_heads(const float* in, float* out, std::size_t num_v_heads, std::
   return Code(tc::RepeatHeadsRef({in, (num_v_heads / factor) * head_k_dim}, {out, num_v_heads * head_k_dim}, num_v_heads,
                                  head_k_dim, factor));
 }
+int ref_mrope(float* io, const std::uint64_t* pos, std::size_t rows, std::size_t heads, std::size_t head_dim,
+              std::size_t rope_dim, std::size_t sec_t, std::size_t sec_h, std::size_t sec_w, double theta) {
+  return Code(tc::MropeRef({io, rows * heads * head_dim}, {pos, rows * 3}, rows, heads, head_dim, rope_dim, sec_t, sec_h,
+                           sec_w, theta));
+}
+int ref_delta_step_heads(float* s, const float* k, const float* v, const float* q, float* o, const float* alpha,
+                         const float* beta, std::size_t heads, std::size_t dk, std::size_t dv) {
+  return Code(tc::DeltaStepHeadsRef({s, heads * dk * dv}, {k, heads * dk}, {v, heads * dv}, {q, heads * dk}, {o, heads * dv},
+                                    {alpha, heads}, {beta, heads}, heads, dk, dv));
+}
 int ref_silu_mul(const float* g, const float* u, float* o, std::size_t n) {
   return Code(tc::SiluMulRef({g, n}, {u, n}, {o, n}, n));
 }

@@ -100,6 +100,9 @@ SIGNATURES = {
     "tsr_fill": (C.c_int, [_vp, C.c_int32, _u64, _vp]),
     "tsr_silu_mul": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
     "tsr_sigmoid_gate": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
+    "tsr_mrope": (C.c_int, [_vp, _vp, _u64, _u64, _u64, _u64, C.c_float, _u64, _u64, _u64, _vp]),
+    "tsr_cast_f32_f16": (C.c_int, [_vp, _vp, _u64, _vp]),
+    "tsr_delta_step_heads": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _vp]),
     "tsr_embedding": (C.c_int, [C.c_int, _vp, _vp, _vp, _u64, _u64, _u64, _vp]),
     "tsr_l2norm": (C.c_int, [_vp, _vp, _u64, _u64, C.c_float, C.c_float, _vp]),
     "tsr_rmsnorm_gated": (C.c_int, [_vp, _vp, _vp, _vp, _u64, _u64, C.c_float, _u64, _u64, _vp]),

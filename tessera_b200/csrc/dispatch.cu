@@ -467,6 +467,50 @@ int k_embedding(const Args& a) {
                        rows, cols, vocab, a.stream);
 }
 
+// mrope: buffers io (rows x heads x head_dim), pos (rows x 3 u64); scalars rows, heads, head_dim, rope_dim,
+// theta bits, sec_t, sec_h, sec_w (backend.hpp:378-385).
+int k_mrope(const Args& a) {
+  if (!shape(a, 2, 8)) return kInvalidArgument;
+  const uint64_t rows = a.sc[0], heads = a.sc[1], dim = a.sc[2], rdim = a.sc[3];
+  if (!dims_ok(rows, heads, dim) || rdim == 0 || rdim > dim || dim % 2 != 0 || rdim % 2 != 0 ||
+      a.sc[5] > rdim || a.sc[6] > rdim || a.sc[7] > rdim || a.sc[5] + a.sc[6] + a.sc[7] > rdim / 2)
+    return kInvalidArgument;
+  if (!holds(a, 0, rows * heads * dim * 4) || !holds(a, 1, rows * 3 * 8)) return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_mrope(static_cast<float*>(const_cast<void*>(a.buf[0])), static_cast<const uint64_t*>(a.buf[1]), rows, heads, dim,
+                   rdim, float_of_bits(a.sc[4]), a.sc[5], a.sc[6], a.sc[7], a.stream);
+}
+
+// cast_f32_f16: buffers In (fp32), Out (fp16); scalar n, even (backend.hpp:334-336).
+int k_cast_f16(const Args& a) {
+  if (!shape(a, 2, 1)) return kInvalidArgument;
+  const uint64_t n = a.sc[0];
+  if (n == 0 || n % 2 != 0 || !holds(a, 0, n * 4) || !holds(a, 1, n * 2)) return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_cast_f32_f16(static_cast<const float*>(a.buf[0]), const_cast<void*>(a.buf[1]), n, a.stream);
+}
+
+// delta_step_heads: buffers S, k, v, q, o, alpha, beta; scalars heads, dk, dv, rows, sbase, sstride, abase
+// (backend.hpp:239-248).
+int k_delta_step_heads(const Args& a) {
+  if (!shape(a, 7, 7)) return kInvalidArgument;
+  const uint64_t heads = a.sc[0], dk = a.sc[1], dv = a.sc[2], rows = a.sc[3], sbase = a.sc[4], sstride = a.sc[5], abase = a.sc[6];
+  if (!dims_ok(heads, dk, dv) || rows == 0 || rows > kMaxDim || dk > 256 || sbase > kMaxDim * 1024 || sstride > kMaxDim * 1024 ||
+      abase > kMaxDim * 1024)
+    return kInvalidArgument;
+  const uint64_t state = heads * dk * dv;
+  const uint64_t s_need = sbase + (sstride == 0 ? state : rows * sstride + state);
+  if (!holds(a, 0, s_need * 4) || !holds(a, 1, rows * heads * dk * 4) || !holds(a, 2, rows * heads * dv * 4) ||
+      !holds(a, 3, rows * heads * dk * 4) || !holds(a, 4, rows * heads * dv * 4) ||
+      !holds(a, 5, (abase + rows * heads) * 4) || !holds(a, 6, (abase + rows * heads) * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_delta_step_heads(static_cast<float*>(const_cast<void*>(a.buf[0])), static_cast<const float*>(a.buf[1]),
+                              static_cast<const float*>(a.buf[2]), static_cast<const float*>(a.buf[3]),
+                              static_cast<float*>(const_cast<void*>(a.buf[4])), static_cast<const float*>(a.buf[5]),
+                              static_cast<const float*>(a.buf[6]), heads, dk, dv, rows, sbase, sstride, abase, a.stream);
+}
+
 // fill: buffer int32; scalars value, count (backend.hpp:151-152).
 int k_fill(const Args& a) {
   if (!shape(a, 1, 2)) return kInvalidArgument;
@@ -668,6 +712,9 @@ const Entry kTable[] = {
     {"ssm_gate", k_ssm_gate},
     {"qgate_split", k_qgate_split},
     {"repeat_heads", k_repeat_heads},
+    {"mrope", k_mrope},
+    {"cast_f32_f16", k_cast_f16},
+    {"delta_step_heads", k_delta_step_heads},
     {"embedding_f32", k_embedding<0>},
     {"embedding_bf16", k_embedding<1>},
     {"embedding_q4k", k_embedding<2>},

@@ -4,6 +4,8 @@
 // Contracts: include/tessera/backend.hpp:217-254,386-390 of the reference; arithmetic:
 // src/core/numerics/norm.cpp:96-262 and attention.cpp:290-334 (the *Ref functions).
 // All of them move a few KB to a few hundred KB per token: one pass, coalesced, fp32.
+#include <cuda_fp16.h>
+
 #include "codec.cuh"
 #include "launch.h"
 #include "tessera_b200.h"
@@ -131,6 +133,105 @@ __global__ void embedding_kernel(const uint32_t* __restrict__ ids, const uint8_t
   out[i] = v;
 }
 
+// mrope: rows x heads x head_dim fp32 rotated in place, NeoX pairing (j, j + rope_dim/2); pair j turns
+// by pos[section of j] * theta^(-2j / rope_dim) (MropeRef, src/core/numerics/attention.cpp: the angle,
+// its cosine and sine in double precision, then fp32 products).
+__global__ void mrope_kernel(float* __restrict__ io, const unsigned long long* __restrict__ pos, size_t heads,
+                             size_t head_dim, size_t rope_dim, double theta, size_t sec_t, size_t sec_h, size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t pairs = rope_dim / 2;
+  const size_t j = i % pairs, rh = i / pairs, r = rh / heads;
+  const unsigned long long section_pos = j < sec_t ? pos[r * 3] : j < sec_t + sec_h ? pos[r * 3 + 1] : pos[r * 3 + 2];
+  const double angle = static_cast<double>(section_pos) *
+                       pow(theta, -2.0 * static_cast<double>(j) / static_cast<double>(rope_dim));
+  const float c = static_cast<float>(cos(angle)), sn = static_cast<float>(sin(angle));
+  float* base = io + rh * head_dim;
+  const float x1 = base[j], x2 = base[j + pairs];
+  base[j] = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
+  base[j + pairs] = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, c));
+}
+
+// fp32 -> binary16, round to nearest even, two per 32-bit word (backend.hpp:334-336)
+__global__ void cast_f32_f16_kernel(const float* __restrict__ in, __half* __restrict__ out, size_t n) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2half_rn(in[i]);
+}
+
+// delta_step_heads: the gated delta rule, `rows` steps in turn on the recurrent state of every
+// value head (DeltaStepHeadsRef, attention.cpp; indexing of the device contract,
+// src/backends/rocm/rocm_kernels_basic.cpp: the state is read at sbase, row t's updated state
+// goes to sbase + (t+1)*sstride, or back in place after the last row when sstride is 0; alpha
+// and beta are read at abase + t*heads + h).
+//   r = S^T k;  S' = alpha (S - beta k r^T) + beta k v^T;  o = S'^T q     per head
+// A CTA owns 32 state columns of one head: warp w holds rows j = w*dk/4 .. of those columns in
+// registers (lane = column, so every state access is a 128-byte row segment), the four warps'
+// partial sums meet in shared memory.  HBM-bound: the state (heads x dk x dv fp32: 3 MB per layer
+// at 48 x 128 x 128) is read once and written once per call.
+constexpr int kDeltaCols = 32, kDeltaWarps = 4, kDeltaMaxPer = 64;  // dk <= 256
+__global__ void __launch_bounds__(kDeltaCols * kDeltaWarps)
+delta_step_heads_kernel(float* __restrict__ s, const float* __restrict__ k, const float* __restrict__ v,
+                        const float* __restrict__ q, float* __restrict__ o, const float* __restrict__ alpha,
+                        const float* __restrict__ beta, int heads, int dk, int dv, int rows, size_t sbase,
+                        size_t sstride, size_t abase) {
+  __shared__ float part[kDeltaWarps][kDeltaCols];
+  __shared__ float kq[2][256];
+  const int slabs = (dv + kDeltaCols - 1) / kDeltaCols;
+  const int h = blockIdx.x / slabs, d = (blockIdx.x % slabs) * kDeltaCols + (threadIdx.x & 31);
+  const int w = threadIdx.x >> 5;
+  const int per = (dk + kDeltaWarps - 1) / kDeltaWarps, j0 = w * per;
+  const int jn = max(0, min(dk, j0 + per) - j0);
+  const bool col = d < dv;
+  float st[kDeltaMaxPer];
+  const size_t head_state = static_cast<size_t>(h) * dk * dv;
+#pragma unroll
+  for (int jj = 0; jj < kDeltaMaxPer; ++jj)
+    st[jj] = (jj < jn && col) ? s[sbase + head_state + static_cast<size_t>(j0 + jj) * dv + d] : 0.0f;
+  for (int t = 0; t < rows; ++t) {
+    const size_t ko = (static_cast<size_t>(t) * heads + h) * dk, vo = (static_cast<size_t>(t) * heads + h) * dv;
+    __syncthreads();  // the previous row's readers of kq and part are done
+    for (int j = threadIdx.x; j < dk; j += blockDim.x) {
+      kq[0][j] = k[ko + j];
+      kq[1][j] = q[ko + j];
+    }
+    __syncthreads();
+    const float a = alpha[abase + static_cast<size_t>(t) * heads + h], b = beta[abase + static_cast<size_t>(t) * heads + h];
+    const float vb = col ? v[vo + d] : 0.0f;
+    float r = 0.0f;
+#pragma unroll
+    for (int jj = 0; jj < kDeltaMaxPer; ++jj)
+      if (jj < jn) r = fmaf(st[jj], kq[0][j0 + jj], r);
+    part[w][threadIdx.x & 31] = r;
+    __syncthreads();
+    const float read = (part[0][threadIdx.x & 31] + part[1][threadIdx.x & 31]) +
+                       (part[2][threadIdx.x & 31] + part[3][threadIdx.x & 31]);
+    float out = 0.0f;
+#pragma unroll
+    for (int jj = 0; jj < kDeltaMaxPer; ++jj)
+      if (jj < jn) {
+        const float kk = kq[0][j0 + jj];
+        st[jj] = a * (st[jj] - b * kk * read) + b * vb * kk;
+        out = fmaf(st[jj], kq[1][j0 + jj], out);
+      }
+    __syncthreads();  // everybody has read `part`
+    part[w][threadIdx.x & 31] = out;
+    __syncthreads();
+    if (w == 0 && col)
+      o[vo + d] = (part[0][threadIdx.x & 31] + part[1][threadIdx.x & 31]) +
+                  (part[2][threadIdx.x & 31] + part[3][threadIdx.x & 31]);
+    if (sstride != 0 && col) {
+#pragma unroll
+      for (int jj = 0; jj < kDeltaMaxPer; ++jj)
+        if (jj < jn) s[sbase + (static_cast<size_t>(t) + 1) * sstride + head_state + static_cast<size_t>(j0 + jj) * dv + d] = st[jj];
+    }
+  }
+  if (sstride == 0 && col) {
+#pragma unroll
+    for (int jj = 0; jj < kDeltaMaxPer; ++jj)
+      if (jj < jn) s[sbase + head_state + static_cast<size_t>(j0 + jj) * dv + d] = st[jj];
+  }
+}
+
 unsigned blocks_of(size_t n) { return static_cast<unsigned>((n + 255) / 256); }
 bool fits31(uint64_t v) { return v > 0 && v <= 0x7FFFFFFFull; }
 
@@ -190,6 +291,38 @@ int tsr_embedding(int kind, const uint32_t* ids, const void* table, float* out, 
   if (kind == 0) embedding_kernel<0><<<blocks_of(total), 256, 0, st>>>(ids, t, out, cols, vocab, total);
   else if (kind == 1) embedding_kernel<1><<<blocks_of(total), 256, 0, st>>>(ids, t, out, cols, vocab, total);
   else embedding_kernel<2><<<blocks_of(total), 256, 0, st>>>(ids, t, out, cols, vocab, total);
+  return check_launch();
+}
+
+int tsr_mrope(float* io, const uint64_t* pos, uint64_t rows, uint64_t heads, uint64_t head_dim, uint64_t rope_dim,
+              float theta, uint64_t sec_t, uint64_t sec_h, uint64_t sec_w, void* stream) {
+  if (!io || !pos || !fits31(rows) || !fits31(heads) || !fits31(head_dim) || rope_dim == 0 || rope_dim > head_dim ||
+      head_dim % 2 != 0 || rope_dim % 2 != 0 || sec_t + sec_h + sec_w > rope_dim / 2 || !(theta > 0.0f))
+    return kInvalidArgument;
+  const size_t total = rows * heads * (rope_dim / 2);
+  mrope_kernel<<<blocks_of(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      io, reinterpret_cast<const unsigned long long*>(pos), heads, head_dim, rope_dim, static_cast<double>(theta), sec_t,
+      sec_h, total);
+  return check_launch();
+}
+
+int tsr_cast_f32_f16(const float* in, void* out, uint64_t n, void* stream) {
+  if (!in || !out || n == 0 || n % 2 != 0) return kInvalidArgument;
+  cast_f32_f16_kernel<<<blocks_of(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(in, static_cast<__half*>(out), n);
+  return check_launch();
+}
+
+int tsr_delta_step_heads(float* s, const float* k, const float* v, const float* q, float* o, const float* alpha,
+                         const float* beta, uint64_t heads, uint64_t dk, uint64_t dv, uint64_t rows, uint64_t sbase,
+                         uint64_t sstride, uint64_t abase, void* stream) {
+  if (!s || !k || !v || !q || !o || !alpha || !beta || !fits31(heads) || !fits31(dk) || !fits31(dv) || !fits31(rows) ||
+      dk > 256)
+    return kInvalidArgument;
+  const unsigned slabs = static_cast<unsigned>((dv + kDeltaCols - 1) / kDeltaCols);
+  delta_step_heads_kernel<<<static_cast<unsigned>(heads) * slabs, kDeltaCols * kDeltaWarps, 0,
+                            static_cast<cudaStream_t>(stream)>>>(s, k, v, q, o, alpha, beta, static_cast<int>(heads),
+                                                                 static_cast<int>(dk), static_cast<int>(dv),
+                                                                 static_cast<int>(rows), sbase, sstride, abase);
   return check_launch();
 }
 

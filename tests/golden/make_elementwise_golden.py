@@ -1,6 +1,7 @@
 """Generates tests/golden/elementwise_golden.npz from the reference's own host functions
 RmsNormRef, AddRef, SiluMulRef, SigmoidGateRef, L2NormRef, RmsNormGatedRef, SsmGateRef
-(src/core/numerics/norm.cpp) and QGateSplitRef, RepeatHeadsRef (attention.cpp of the reference, reached
+(src/core/numerics/norm.cpp) and QGateSplitRef, RepeatHeadsRef, MropeRef, DeltaStepHeadsRef (attention.cpp of the
+reference, reached
 through oracle/_ref/libtessera_ref.so, which oracle/Makefile builds from the reference
 checkout).  Run from the repository root where the reference checkout is available:
 
@@ -61,6 +62,17 @@ def main() -> None:
     rin = g.standard_normal(4 * 16).astype(np.float32)
     out["rep_in"] = rin
     out["rep_out"] = ref.repeat_heads(rin, 12, 16, 3)
+    io = g.standard_normal(2 * 3 * 64).astype(np.float32)
+    pos = np.array([[5, 2, 9], [4096, 17, 3]], dtype=np.uint64)
+    out["rope_io"], out["rope_pos"] = io, pos
+    out["rope_out"] = ref.mrope(io, pos, 2, 3, 64, 48, 11, 8, 5, 1e7)
+    heads, dk, dv = 3, 20, 24
+    st = (g.standard_normal(heads * dk * dv) * 0.3).astype(np.float32)
+    kk, qq = (g.standard_normal(heads * dk) * 0.2).astype(np.float32), g.standard_normal(heads * dk).astype(np.float32)
+    vv = g.standard_normal(heads * dv).astype(np.float32)
+    al, be = g.random(heads).astype(np.float32), g.random(heads).astype(np.float32)
+    out["ds_s"], out["ds_k"], out["ds_v"], out["ds_q"], out["ds_alpha"], out["ds_beta"] = st, kk, vv, qq, al, be
+    out["ds_s_out"], out["ds_o"] = ref.delta_step_heads(st, kk, vv, qq, al, be, heads, dk, dv)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "elementwise_golden.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes")

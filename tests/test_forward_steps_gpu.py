@@ -131,3 +131,72 @@ def test_embedding_rows_are_exact(backend, oracle, kind):
     got = backend.download(out, np.float32, ids.size * cols).reshape(ids.size, cols)
     want = np.stack([dense[i] if i < vocab else np.zeros(cols, dtype=np.float32) for i in ids])
     assert np.array_equal(got, want)
+
+
+def test_mrope(backend, oracle):
+    """Positions in the thousands: the angle is formed in double precision on both sides; the
+    device's double sine and cosine may differ from the host's in the last bit, which shows as
+    one ulp of an fp32 factor."""
+    g = np.random.default_rng(9)
+    rows, heads, dim, rdim = 3, 24, 256, 64
+    io = g.standard_normal(rows * heads * dim).astype(np.float32)
+    pos = np.array([[7, 7, 7], [4095, 12, 300], [100000, 0, 1]], dtype=np.uint64)
+    buf = backend.upload(io)
+    run(backend, "mrope", [buf, backend.upload(pos)], [rows, heads, dim, rdim, bits(1e7), 11, 11, 10])
+    got = backend.download(buf, np.float32, io.size)
+    want = oracle.mrope(io, pos, rows, heads, dim, rdim, 11, 11, 10, float(np.float32(1e7)))
+    assert np.all(np.abs(got - want) <= 3e-7 * (np.abs(want) + np.abs(io)))
+    untouched = np.arange(io.size) % dim >= rdim
+    assert np.array_equal(got[untouched], io[untouched])
+
+
+def test_cast_f32_f16_rounds_to_nearest_even(backend):
+    g = np.random.default_rng(10)
+    x = np.concatenate([np.float32([0.0, -0.0, 1.0, 65504.0, 65520.0, 1e-8, 6.1e-5, 5.96e-8, 2049.0, 2051.0, -3.3, 1e9]),
+                        (g.standard_normal(1012) * 50).astype(np.float32)])
+    out = backend.AllocateBuffer(x.size * 2)
+    run(backend, "cast_f32_f16", [backend.upload(x), out], [x.size])
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float16)
+    assert np.array_equal(backend.download(out, np.uint16, x.size), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("heads,dk,dv,rows,history", [(48, 128, 128, 1, False), (6, 128, 128, 3, True), (3, 20, 24, 2, False),
+                                                      (2, 256, 40, 1, False)])
+def test_delta_step_heads(backend, oracle, heads, dk, dv, rows, history):
+    """rows steps in turn; with history every step's state goes to its own slot after the input
+    state (slot t + 1), otherwise the state advances in place.  alpha and beta are read at an
+    element base."""
+    g = np.random.default_rng(heads + dk)
+    state = (g.standard_normal(heads * dk * dv) * 0.3).astype(np.float32)
+    k = (g.standard_normal((rows, heads * dk)) * 0.1).astype(np.float32)
+    q = g.standard_normal((rows, heads * dk)).astype(np.float32)
+    v = g.standard_normal((rows, heads * dv)).astype(np.float32)
+    abase = 5
+    alpha = g.random(abase + rows * heads).astype(np.float32)
+    beta = g.random(abase + rows * heads).astype(np.float32)
+    sbase = 16
+    stride = heads * dk * dv if history else 0
+    slots = rows + 1 if history else 1
+    s_all = np.full(sbase + slots * heads * dk * dv + 8, np.float32(-7e7), dtype=np.float32)
+    s_all[sbase:sbase + state.size] = state
+    sb = backend.upload(s_all)
+    ob = backend.AllocateBuffer(rows * heads * dv * 4)
+    run(backend, "delta_step_heads", [sb, backend.upload(k), backend.upload(v), backend.upload(q), ob, backend.upload(alpha),
+                                      backend.upload(beta)], [heads, dk, dv, rows, sbase, stride, abase])
+    got_s = backend.download(sb, np.float32, s_all.size)
+    got_o = backend.download(ob, np.float32, rows * heads * dv).reshape(rows, heads * dv)
+    cur = state
+    for t in range(rows):
+        a_t = alpha[abase + t * heads:abase + (t + 1) * heads]
+        b_t = beta[abase + t * heads:abase + (t + 1) * heads]
+        cur, o = oracle.delta_step_heads(cur, k[t], v[t], q[t], a_t, b_t, heads, dk, dv)
+        assert np.abs(got_o[t] - o).max() <= 2e-5 * max(np.abs(o).max(), 1e-6), t
+        if history:
+            slot = got_s[sbase + (t + 1) * stride:sbase + (t + 2) * stride]
+            assert np.abs(slot - cur).max() <= 2e-6 * np.abs(cur).max(), t
+    if history:
+        assert np.array_equal(got_s[sbase:sbase + state.size], state)          # the input state stays
+    else:
+        assert np.abs(got_s[sbase:sbase + state.size] - cur).max() <= 2e-6 * np.abs(cur).max()
+    assert np.all(got_s[:sbase] == np.float32(-7e7)) and np.all(got_s[sbase + slots * state.size:] == np.float32(-7e7))

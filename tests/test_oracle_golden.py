@@ -173,3 +173,12 @@ def test_steps_between_the_projections_match_golden(oracle):
     q, gate = oracle.qgate_split(g["qg_fused"], 6, 32, 2)
     assert np.array_equal(q, g["qg_q"]) and np.array_equal(gate, g["qg_gate"])
     assert np.array_equal(oracle.repeat_heads(g["rep_in"], 12, 16, 3), g["rep_out"])
+
+
+def test_rope_and_delta_rule_match_golden(oracle):
+    """MropeRef and DeltaStepHeadsRef (src/core/numerics/attention.cpp of the reference)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "elementwise_golden.npz"))
+    assert np.array_equal(oracle.mrope(g["rope_io"], g["rope_pos"], 2, 3, 64, 48, 11, 8, 5, 1e7), g["rope_out"])
+    s, o = oracle.delta_step_heads(g["ds_s"], g["ds_k"], g["ds_v"], g["ds_q"], g["ds_alpha"], g["ds_beta"], 3, 20, 24)
+    assert np.array_equal(s, g["ds_s_out"]) and np.array_equal(o, g["ds_o"])
