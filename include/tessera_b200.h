@@ -256,6 +256,16 @@ int tsr_cast_f32_f16(const float* in, void* out, uint64_t n, void* stream);
 int tsr_delta_step_heads(float* s, const float* k, const float* v, const float* q, float* o, const float* alpha,
                          const float* beta, uint64_t heads, uint64_t dk, uint64_t dv, uint64_t rows, uint64_t sbase,
                          uint64_t sstride, uint64_t abase, void* stream);
+/* conv1d_state: `rows` steps of the causal depthwise convolution over (width - 1) history samples per channel
+ * (newest first, updated in place), SiLU, split into q, k (key_dim each) and v; with hist_stride != 0 row t's
+ * history also goes to hist_hist + (t+1)*hist_stride (src/backends/rocm/rocm_kernels_basic.cpp:2193-2245) */
+int tsr_conv1d_state(const float* qkv, const float* w, float* hist, float* q, float* k, float* v, float* hist_hist,
+                     uint64_t conv_dim, uint64_t width, uint64_t key_dim, uint64_t qkv_offset, uint64_t rows,
+                     uint64_t hist_stride, void* stream);
+/* top_k_rows: the top_k (<= 32) largest logits of each row, descending, and their indices; output row r reads
+ * input row row_base + r; equal values: lowest index first (src/backends/rocm/rocm_kernels.hpp:558-566) */
+int tsr_top_k_rows(const float* logits, uint32_t* ids, float* vals, uint64_t rows, uint64_t vocab, uint64_t top_k,
+                   uint64_t row_base, void* stream);
 /* silu_mul: O = silu(G) * U, backend.hpp:257-260; SiluMulRef src/core/numerics/norm.cpp:211-225 */
 int tsr_silu_mul(const float* g, const float* u, float* o, uint64_t n, void* stream);
 /* rmsnorm: Y = X / sqrt(mean(X^2) + eps) * W per row, backend.hpp:212-216; RmsNormRef

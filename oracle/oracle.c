@@ -586,6 +586,69 @@ int orc_delta_step_heads(float* s, const float* k, const float* v, const float* 
   return 0;
 }
 
+/* Conv1dStepRef, src/core/numerics/conv.cpp: y[c] = sum_i w[c][i] * x[c][i], fma in order (x newest first) */
+int orc_conv1d_step(const float* x, const float* w, float* y, size_t channels, size_t width) {
+  if (channels == 0 || width == 0) return -2;
+  for (size_t c = 0; c < channels; ++c) {
+    float acc = 0.0f;
+    for (size_t i = 0; i < width; ++i) acc = fmaf(w[c * width + i], x[c * width + i], acc);
+    y[c] = acc;
+  }
+  return 0;
+}
+
+/* conv1d_state (device contract, rocm_kernels_basic.cpp:2193-2245): per channel, W in checkpoint tap order
+ * (tap 0 oldest), history newest first; acc = w[last] * current, then fma over the history; SiLU; q/k/v split;
+ * history shifted; optional copy of row t's history to slot t + 1 of hist_hist. */
+int orc_conv1d_state(const float* qkv, const float* w, float* hist, float* q, float* k, float* v, float* hist_hist,
+                     size_t conv_dim, size_t width, size_t key_dim, size_t qkv_offset, size_t rows, size_t hist_stride) {
+  if (conv_dim == 0 || width == 0 || rows == 0 || 2 * key_dim > conv_dim) return -2;
+  const size_t stride = width - 1, value_dim = conv_dim - 2 * key_dim;
+  for (size_t c = 0; c < conv_dim; ++c) {
+    const size_t hbase = c * stride;
+    for (size_t t = 0; t < rows; ++t) {
+      const float current = qkv[qkv_offset + t * conv_dim + c];
+      float acc = w[c * width + (width - 1)] * current;
+      for (size_t i = 1; i < width; ++i) acc = fmaf(w[c * width + (width - 1 - i)], hist[hbase + (i - 1)], acc);
+      const float out = acc / (1.0f + expf(-acc));
+      if (c < key_dim) q[t * key_dim + c] = out;
+      else if (c < 2 * key_dim) k[t * key_dim + (c - key_dim)] = out;
+      else v[t * value_dim + (c - 2 * key_dim)] = out;
+      if (width > 1) {
+        for (size_t i = stride; i > 1; --i) hist[hbase + (i - 1)] = hist[hbase + (i - 2)];
+        hist[hbase] = current;
+      }
+      if (hist_stride != 0)
+        for (size_t i = 0; i < stride; ++i) hist_hist[(t + 1) * hist_stride + hbase + i] = hist[hbase + i];
+    }
+  }
+  return 0;
+}
+
+/* top_k_rows (rocm_kernels.hpp:558-566): the top_k largest of each row, descending; equal values: lowest index first */
+int orc_top_k_rows(const float* logits, uint32_t* ids, float* vals, size_t rows, size_t vocab, size_t top_k, size_t row_base) {
+  if (rows == 0 || vocab == 0 || top_k == 0 || top_k > 32) return -2;
+  for (size_t r = 0; r < rows; ++r) {
+    const float* row = logits + (row_base + r) * vocab;
+    for (size_t p = 0; p < top_k; ++p) {
+      size_t arg = (size_t)-1;
+      float best = -INFINITY;
+      for (size_t c = 0; c < vocab; ++c) {
+        int used = 0;
+        for (size_t t = 0; t < p; ++t) used |= ids[r * top_k + t] == (uint32_t)c && vals[r * top_k + t] == row[c];
+        if (used) continue;
+        if (arg == (size_t)-1 || row[c] > best) {
+          best = row[c];
+          arg = c;
+        }
+      }
+      ids[r * top_k + p] = arg == (size_t)-1 ? 0u : (uint32_t)arg;
+      vals[r * top_k + p] = arg == (size_t)-1 ? -INFINITY : best;
+    }
+  }
+  return 0;
+}
+
 /* ------------------------------------------------------------ routed experts */
 
 /* moe_gate (rocm_kernels_basic.cpp:1896-1929): softmax over the selected logits and the

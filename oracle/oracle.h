@@ -87,6 +87,11 @@ int orc_qgate_split(const float* fused, float* q, float* gate, size_t heads, siz
 int orc_repeat_heads(const float* in, float* out, size_t num_v_heads, size_t head_k_dim, size_t factor);    /* attention.cpp:315-334 */
 int orc_mrope(float* io, const uint64_t* pos, size_t rows, size_t heads, size_t head_dim, size_t rope_dim, size_t sec_t,
               size_t sec_h, size_t sec_w, double theta);                                        /* attention.cpp MropeRef */
+/* device-only contracts (src/backends/rocm/rocm_kernels_basic.cpp:2193-2245, 3178-3245) */
+int orc_conv1d_state(const float* qkv, const float* w, float* hist, float* q, float* k, float* v, float* hist_hist,
+                     size_t conv_dim, size_t width, size_t key_dim, size_t qkv_offset, size_t rows, size_t hist_stride);
+int orc_top_k_rows(const float* logits, uint32_t* ids, float* vals, size_t rows, size_t vocab, size_t top_k, size_t row_base);
+int orc_conv1d_step(const float* x, const float* w, float* y, size_t channels, size_t width);  /* conv.cpp Conv1dStepRef */
 /* one gated delta-rule step on every head's state, in place (attention.cpp DeltaStepHeadsRef) */
 int orc_delta_step_heads(float* s, const float* k, const float* v, const float* q, float* o, const float* alpha,
                          const float* beta, size_t heads, size_t dk, size_t dv);

@@ -249,6 +249,35 @@ class Oracle:
         assert fn(_ptr(s), _ptr(k), _ptr(v), _ptr(q), _ptr(o), _ptr(alpha), _ptr(beta), heads, dk, dv) == 0
         return s, o
 
+    def conv1d_step(self, x, w, channels, width):
+        x, w = (np.ascontiguousarray(t, dtype=np.float32) for t in (x, w))
+        y = np.empty(channels, dtype=np.float32)
+        assert self._fn("conv1d_step", C.c_int, [_p, _p, _p, _sz, _sz])(_ptr(x), _ptr(w), _ptr(y), channels, width) == 0
+        return y
+
+    def conv1d_state(self, qkv, w, hist, conv_dim, width, key_dim, qkv_offset, rows, hist_stride=0, hist_hist=None):
+        """Device contract (C restatement only).  Returns (q, k, v, hist, hist_hist)."""
+        assert not self.reference
+        qkv, w = (np.ascontiguousarray(t, dtype=np.float32) for t in (qkv, w))
+        hist = np.ascontiguousarray(hist, dtype=np.float32).copy()
+        hh = np.zeros(1, dtype=np.float32) if hist_hist is None else np.ascontiguousarray(hist_hist, dtype=np.float32).copy()
+        q = np.empty(rows * key_dim, dtype=np.float32)
+        k = np.empty(rows * key_dim, dtype=np.float32)
+        v = np.empty(rows * (conv_dim - 2 * key_dim), dtype=np.float32)
+        fn = self._fn("conv1d_state", C.c_int, [_p, _p, _p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz])
+        assert fn(_ptr(qkv), _ptr(w), _ptr(hist), _ptr(q), _ptr(k), _ptr(v), _ptr(hh), conv_dim, width, key_dim, qkv_offset,
+                  rows, hist_stride) == 0
+        return q, k, v, hist, hh
+
+    def top_k_rows(self, logits, rows, vocab, top_k, row_base=0):
+        assert not self.reference
+        logits = np.ascontiguousarray(logits, dtype=np.float32)
+        ids = np.zeros(rows * top_k, dtype=np.uint32)
+        vals = np.zeros(rows * top_k, dtype=np.float32)
+        fn = self._fn("top_k_rows", C.c_int, [_p, _p, _p, _sz, _sz, _sz, _sz])
+        assert fn(_ptr(logits), _ptr(ids), _ptr(vals), rows, vocab, top_k, row_base) == 0
+        return ids.reshape(rows, top_k), vals.reshape(rows, top_k)
+
     # ---- routed experts (device-only contracts; C restatement only)
     def moe_gate(self, vals, x, w):
         assert not self.reference

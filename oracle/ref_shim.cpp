@@ -13,6 +13,7 @@
 
 #include "core/loaders/tensor_slice.hpp"
 #include "core/numerics/attention.hpp"
+#include "core/numerics/conv.hpp"
 #include "core/numerics/gemm.hpp"
 #include "core/numerics/moe_cpu.hpp"
 #include "core/numerics/norm.hpp"
@@ -146,6 +147,9 @@ int ref_delta_step_heads(float* s, const float* k, const float* v, const float* 
                          const float* beta, std::size_t heads, std::size_t dk, std::size_t dv) {
   return Code(tc::DeltaStepHeadsRef({s, heads * dk * dv}, {k, heads * dk}, {v, heads * dv}, {q, heads * dk}, {o, heads * dv},
                                     {alpha, heads}, {beta, heads}, heads, dk, dv));
+}
+int ref_conv1d_step(const float* x, const float* w, float* y, std::size_t channels, std::size_t width) {
+  return Code(tc::Conv1dStepRef({x, channels * width}, {w, channels * width}, {y, channels}, channels, width));
 }
 int ref_silu_mul(const float* g, const float* u, float* o, std::size_t n) {
   return Code(tc::SiluMulRef({g, n}, {u, n}, {o, n}, n));

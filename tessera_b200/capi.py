@@ -100,6 +100,8 @@ SIGNATURES = {
     "tsr_fill": (C.c_int, [_vp, C.c_int32, _u64, _vp]),
     "tsr_silu_mul": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
     "tsr_sigmoid_gate": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
+    "tsr_conv1d_state": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64, _u64, _u64, _vp]),
+    "tsr_top_k_rows": (C.c_int, [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp]),
     "tsr_mrope": (C.c_int, [_vp, _vp, _u64, _u64, _u64, _u64, C.c_float, _u64, _u64, _u64, _vp]),
     "tsr_cast_f32_f16": (C.c_int, [_vp, _vp, _u64, _vp]),
     "tsr_delta_step_heads": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _vp]),

@@ -511,6 +511,35 @@ int k_delta_step_heads(const Args& a) {
                               static_cast<const float*>(a.buf[6]), heads, dk, dv, rows, sbase, sstride, abase, a.stream);
 }
 
+// conv1d_state: buffers qkv, W (conv_dim x width), hist (conv_dim x (width-1)), q, k, v, hist_hist; scalars
+// conv_dim, width, key_dim, qkv_offset, rows, hist_stride (src/backends/rocm/rocm_kernels.hpp:580-589).
+int k_conv1d_state(const Args& a) {
+  if (!shape(a, 7, 6)) return kInvalidArgument;
+  const uint64_t cd = a.sc[0], width = a.sc[1], kd = a.sc[2], off = a.sc[3], rows = a.sc[4], hs = a.sc[5];
+  if (!dims_ok(cd, width, rows) || 2 * kd > cd || off > kMaxDim * 1024 || hs > kMaxDim * 1024) return kInvalidArgument;
+  const uint64_t hist = cd * (width - 1), vd = cd - 2 * kd;
+  if (!holds(a, 0, (off + rows * cd) * 4) || !holds(a, 1, cd * width * 4) || !holds(a, 2, hist * 4) ||
+      !holds(a, 3, rows * kd * 4) || !holds(a, 4, rows * kd * 4) || !holds(a, 5, rows * vd * 4) ||
+      (hs != 0 && !holds(a, 6, (rows * hs + hist) * 4)))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  auto f = [&](int i) { return static_cast<float*>(const_cast<void*>(a.buf[i])); };
+  return tsr_conv1d_state(f(0), f(1), f(2), f(3), f(4), f(5), f(6), cd, width, kd, off, rows, hs, a.stream);
+}
+
+// top_k_rows: buffers logits, ids (u32), vals; scalars rows, vocab, top_k, row_base
+// (src/backends/rocm/rocm_kernels.hpp:558-566).
+int k_top_k_rows(const Args& a) {
+  if (!shape(a, 3, 4)) return kInvalidArgument;
+  const uint64_t rows = a.sc[0], vocab = a.sc[1], top_k = a.sc[2], base = a.sc[3];
+  if (!dims_ok(rows, vocab, top_k) || top_k > 32 || base > kMaxDim) return kInvalidArgument;
+  if (!holds(a, 0, (base + rows) * vocab * 4) || !holds(a, 1, rows * top_k * 4) || !holds(a, 2, rows * top_k * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_top_k_rows(static_cast<const float*>(a.buf[0]), static_cast<uint32_t*>(const_cast<void*>(a.buf[1])),
+                        static_cast<float*>(const_cast<void*>(a.buf[2])), rows, vocab, top_k, base, a.stream);
+}
+
 // fill: buffer int32; scalars value, count (backend.hpp:151-152).
 int k_fill(const Args& a) {
   if (!shape(a, 1, 2)) return kInvalidArgument;
@@ -712,6 +741,8 @@ const Entry kTable[] = {
     {"ssm_gate", k_ssm_gate},
     {"qgate_split", k_qgate_split},
     {"repeat_heads", k_repeat_heads},
+    {"conv1d_state", k_conv1d_state},
+    {"top_k_rows", k_top_k_rows},
     {"mrope", k_mrope},
     {"cast_f32_f16", k_cast_f16},
     {"delta_step_heads", k_delta_step_heads},

@@ -168,7 +168,7 @@ __global__ void cast_f32_f16_kernel(const float* __restrict__ in, __half* __rest
 // registers (lane = column, so every state access is a 128-byte row segment), the four warps'
 // partial sums meet in shared memory.  HBM-bound: the state (heads x dk x dv fp32: 3 MB per layer
 // at 48 x 128 x 128) is read once and written once per call.
-constexpr int kDeltaCols = 32, kDeltaWarps = 4, kDeltaMaxPer = 64;  // dk <= 256
+constexpr int kDeltaCols = 32, kDeltaWarps = 4, kDeltaMaxPer = 64;  // dk <= 256 (eight warps measured slower: 6.4 against 5.0 us)
 __global__ void __launch_bounds__(kDeltaCols * kDeltaWarps)
 delta_step_heads_kernel(float* __restrict__ s, const float* __restrict__ k, const float* __restrict__ v,
                         const float* __restrict__ q, float* __restrict__ o, const float* __restrict__ alpha,
@@ -203,8 +203,9 @@ delta_step_heads_kernel(float* __restrict__ s, const float* __restrict__ k, cons
       if (jj < jn) r = fmaf(st[jj], kq[0][j0 + jj], r);
     part[w][threadIdx.x & 31] = r;
     __syncthreads();
-    const float read = (part[0][threadIdx.x & 31] + part[1][threadIdx.x & 31]) +
-                       (part[2][threadIdx.x & 31] + part[3][threadIdx.x & 31]);
+    float read = 0.0f;
+#pragma unroll
+    for (int x = 0; x < kDeltaWarps; ++x) read += part[x][threadIdx.x & 31];
     float out = 0.0f;
 #pragma unroll
     for (int jj = 0; jj < kDeltaMaxPer; ++jj)
@@ -216,9 +217,12 @@ delta_step_heads_kernel(float* __restrict__ s, const float* __restrict__ k, cons
     __syncthreads();  // everybody has read `part`
     part[w][threadIdx.x & 31] = out;
     __syncthreads();
-    if (w == 0 && col)
-      o[vo + d] = (part[0][threadIdx.x & 31] + part[1][threadIdx.x & 31]) +
-                  (part[2][threadIdx.x & 31] + part[3][threadIdx.x & 31]);
+    if (w == 0 && col) {
+      float sum = 0.0f;
+#pragma unroll
+      for (int x = 0; x < kDeltaWarps; ++x) sum += part[x][threadIdx.x & 31];
+      o[vo + d] = sum;
+    }
     if (sstride != 0 && col) {
 #pragma unroll
       for (int jj = 0; jj < kDeltaMaxPer; ++jj)
@@ -229,6 +233,87 @@ delta_step_heads_kernel(float* __restrict__ s, const float* __restrict__ k, cons
 #pragma unroll
     for (int jj = 0; jj < kDeltaMaxPer; ++jj)
       if (jj < jn) s[sbase + head_state + static_cast<size_t>(j0 + jj) * dv + d] = st[jj];
+  }
+}
+
+// conv1d_state: current-step causal depthwise convolution with the history kept on the device, SiLU and
+// the q / k / v split; `rows` steps advance the history in turn.  One thread per channel; W in checkpoint
+// tap order (tap 0 oldest), history newest first, (width - 1) samples per channel; with hist_stride != 0
+// row t's history also goes to slot t + 1 of hist_hist (device contract:
+// src/backends/rocm/rocm_kernels_basic.cpp:2193-2245 of the reference; the convolution itself is
+// Conv1dStepRef, src/core/numerics/conv.cpp).
+__global__ void conv1d_state_kernel(const float* __restrict__ qkv, const float* __restrict__ w, float* __restrict__ hist,
+                                    float* __restrict__ q, float* __restrict__ k, float* __restrict__ v,
+                                    float* __restrict__ hist_hist, size_t conv_dim, size_t width, size_t key_dim,
+                                    size_t qkv_offset, size_t rows, size_t hist_stride) {
+  const size_t c = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (c >= conv_dim) return;
+  const size_t stride = width - 1, hbase = c * stride, value_dim = conv_dim - 2 * key_dim;
+  for (size_t t = 0; t < rows; ++t) {
+    const float current = qkv[qkv_offset + t * conv_dim + c];
+    float acc = __fmul_rn(w[c * width + (width - 1)], current);
+    for (size_t i = 1; i < width; ++i) acc = fmaf(w[c * width + (width - 1 - i)], hist[hbase + (i - 1)], acc);
+    const float out = acc / (1.0f + expf(-acc));
+    if (c < key_dim) q[t * key_dim + c] = out;
+    else if (c < 2 * key_dim) k[t * key_dim + (c - key_dim)] = out;
+    else v[t * value_dim + (c - 2 * key_dim)] = out;
+    if (width > 1) {
+      for (size_t i = stride; i > 1; --i) hist[hbase + (i - 1)] = hist[hbase + (i - 2)];
+      hist[hbase] = current;
+    }
+    if (hist_stride != 0)
+      for (size_t i = 0; i < stride; ++i) hist_hist[(t + 1) * hist_stride + hbase + i] = hist[hbase + i];
+  }
+}
+
+// top_k_rows: the top_k (<= 32) largest of `vocab` fp32 logits of every row, descending, with their
+// indices; output row r reads input row row_base + r (src/backends/rocm/rocm_kernels.hpp:558-566).  One
+// CTA per row; top_k rounds of a block-wide arg-max over the values not taken yet; among equal values the
+// lowest index wins.
+__global__ void __launch_bounds__(256)
+top_k_rows_kernel(const float* __restrict__ logits, uint32_t* __restrict__ ids, float* __restrict__ vals, size_t vocab,
+                  int top_k, size_t row_base) {
+  __shared__ float bv[8];
+  __shared__ uint32_t bi[8];
+  __shared__ uint32_t taken[32];
+  const float* row = logits + (row_base + blockIdx.x) * vocab;
+  for (int p = 0; p < top_k; ++p) {
+    float best = -INFINITY;
+    uint32_t arg = 0xFFFFFFFFu;
+    for (size_t c = threadIdx.x; c < vocab; c += blockDim.x) {
+      const float x = row[c];
+      bool used = false;
+      for (int t = 0; t < p; ++t) used = used || taken[t] == static_cast<uint32_t>(c);
+      if (!used && (x > best || (x == best && static_cast<uint32_t>(c) < arg) || arg == 0xFFFFFFFFu)) {
+        best = x;
+        arg = static_cast<uint32_t>(c);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+      const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, arg, o);
+      if (oi != 0xFFFFFFFFu && (arg == 0xFFFFFFFFu || ov > best || (ov == best && oi < arg))) {
+        best = ov;
+        arg = oi;
+      }
+    }
+    if ((threadIdx.x & 31) == 0) {
+      bv[threadIdx.x >> 5] = best;
+      bi[threadIdx.x >> 5] = arg;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int x = 1; x < 8; ++x)
+        if (bi[x] != 0xFFFFFFFFu && (bi[0] == 0xFFFFFFFFu || bv[x] > bv[0] || (bv[x] == bv[0] && bi[x] < bi[0]))) {
+          bv[0] = bv[x];
+          bi[0] = bi[x];
+        }
+      taken[p] = bi[0];
+      vals[blockIdx.x * top_k + p] = bi[0] == 0xFFFFFFFFu ? -INFINITY : bv[0];
+      ids[blockIdx.x * top_k + p] = bi[0] == 0xFFFFFFFFu ? 0u : bi[0];
+    }
+    __syncthreads();
   }
 }
 
@@ -323,6 +408,25 @@ int tsr_delta_step_heads(float* s, const float* k, const float* v, const float* 
                             static_cast<cudaStream_t>(stream)>>>(s, k, v, q, o, alpha, beta, static_cast<int>(heads),
                                                                  static_cast<int>(dk), static_cast<int>(dv),
                                                                  static_cast<int>(rows), sbase, sstride, abase);
+  return check_launch();
+}
+
+int tsr_conv1d_state(const float* qkv, const float* w, float* hist, float* q, float* k, float* v, float* hist_hist,
+                     uint64_t conv_dim, uint64_t width, uint64_t key_dim, uint64_t qkv_offset, uint64_t rows,
+                     uint64_t hist_stride, void* stream) {
+  if (!qkv || !w || !hist || !q || !k || !v || !fits31(conv_dim) || !fits31(width) || !fits31(rows) || 2 * key_dim > conv_dim ||
+      (hist_stride != 0 && !hist_hist))
+    return kInvalidArgument;
+  conv1d_state_kernel<<<blocks_of(conv_dim), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      qkv, w, hist, q, k, v, hist_hist, conv_dim, width, key_dim, qkv_offset, rows, hist_stride);
+  return check_launch();
+}
+
+int tsr_top_k_rows(const float* logits, uint32_t* ids, float* vals, uint64_t rows, uint64_t vocab, uint64_t top_k,
+                   uint64_t row_base, void* stream) {
+  if (!logits || !ids || !vals || !fits31(rows) || !fits31(vocab) || top_k == 0 || top_k > 32) return kInvalidArgument;
+  top_k_rows_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, ids, vals, vocab, static_cast<int>(top_k), row_base);
   return check_launch();
 }
 

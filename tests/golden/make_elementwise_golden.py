@@ -1,6 +1,6 @@
 """Generates tests/golden/elementwise_golden.npz from the reference's own host functions
 RmsNormRef, AddRef, SiluMulRef, SigmoidGateRef, L2NormRef, RmsNormGatedRef, SsmGateRef
-(src/core/numerics/norm.cpp) and QGateSplitRef, RepeatHeadsRef, MropeRef, DeltaStepHeadsRef (attention.cpp of the
+(src/core/numerics/norm.cpp) and QGateSplitRef, RepeatHeadsRef, MropeRef, DeltaStepHeadsRef (attention.cpp), Conv1dStepRef (conv.cpp of the
 reference, reached
 through oracle/_ref/libtessera_ref.so, which oracle/Makefile builds from the reference
 checkout).  Run from the repository root where the reference checkout is available:
@@ -73,6 +73,9 @@ def main() -> None:
     al, be = g.random(heads).astype(np.float32), g.random(heads).astype(np.float32)
     out["ds_s"], out["ds_k"], out["ds_v"], out["ds_q"], out["ds_alpha"], out["ds_beta"] = st, kk, vv, qq, al, be
     out["ds_s_out"], out["ds_o"] = ref.delta_step_heads(st, kk, vv, qq, al, be, heads, dk, dv)
+    cx, cw = g.standard_normal(40 * 4).astype(np.float32), g.standard_normal(40 * 4).astype(np.float32)
+    out["conv_x"], out["conv_w"] = cx, cw
+    out["conv_y"] = ref.conv1d_step(cx, cw, 40, 4)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "elementwise_golden.npz")
     np.savez_compressed(path, **out)
     print(path, os.path.getsize(path), "bytes")

@@ -200,3 +200,45 @@ def test_delta_step_heads(backend, oracle, heads, dk, dv, rows, history):
     else:
         assert np.abs(got_s[sbase:sbase + state.size] - cur).max() <= 2e-6 * np.abs(cur).max()
     assert np.all(got_s[:sbase] == np.float32(-7e7)) and np.all(got_s[sbase + slots * state.size:] == np.float32(-7e7))
+
+
+@pytest.mark.parametrize("rows,history", [(1, False), (3, True)])
+def test_conv1d_state(backend, oracle, rows, history):
+    g = np.random.default_rng(11 + rows)
+    conv_dim, width, key_dim, offset = 10240, 4, 2048, 64
+    qkv = g.standard_normal(offset + rows * conv_dim).astype(np.float32)
+    w = g.standard_normal(conv_dim * width).astype(np.float32)
+    hist = g.standard_normal(conv_dim * (width - 1)).astype(np.float32)
+    stride = conv_dim * (width - 1) if history else 0
+    hh = np.zeros((rows + 1) * conv_dim * (width - 1) if history else 4, dtype=np.float32)
+    hb, hhb = backend.upload(hist), backend.upload(hh)
+    vd = conv_dim - 2 * key_dim
+    qb, kb, vb = backend.AllocateBuffer(rows * key_dim * 4), backend.AllocateBuffer(rows * key_dim * 4), backend.AllocateBuffer(rows * vd * 4)
+    run(backend, "conv1d_state", [backend.upload(qkv), backend.upload(w), hb, qb, kb, vb, hhb],
+        [conv_dim, width, key_dim, offset, rows, stride])
+    q, k, v, hist2, hh2 = oracle.conv1d_state(qkv, w, hist, conv_dim, width, key_dim, offset, rows, stride, hh if history else None)
+    for buf, want in ((qb, q), (kb, k), (vb, v)):
+        assert close(backend.download(buf, np.float32, want.size), want, 2e-6)
+    assert np.array_equal(backend.download(hb, np.float32, hist.size), hist2)
+    if history:
+        assert np.array_equal(backend.download(hhb, np.float32, hh.size), hh2)
+
+
+def test_top_k_rows(backend, oracle):
+    g = np.random.default_rng(13)
+    rows, vocab, top_k, base = 3, 5000, 8, 2
+    logits = g.standard_normal((base + rows) * vocab).astype(np.float32)
+    logits[base * vocab + 17] = logits[base * vocab + 4000] = 9.0      # a tie: the lower index comes first
+    ib, vb = backend.AllocateBuffer(rows * top_k * 4), backend.AllocateBuffer(rows * top_k * 4)
+    run(backend, "top_k_rows", [backend.upload(logits), ib, vb], [rows, vocab, top_k, base])
+    ids, vals = oracle.top_k_rows(logits, rows, vocab, top_k, base)
+    got_i = backend.download(ib, np.uint32, rows * top_k).reshape(rows, top_k)
+    got_v = backend.download(vb, np.float32, rows * top_k).reshape(rows, top_k)
+    assert np.array_equal(got_i, ids) and np.array_equal(got_v, vals)
+    assert list(got_i[0][:2]) == [17, 4000]
+    full = logits.reshape(base + rows, vocab)[base:]
+    assert np.array_equal(np.sort(full, axis=1)[:, ::-1][:, :top_k], got_v)
+    # routing shape of the MoE configuration: 256 experts, 8 selected
+    lg = g.standard_normal(256).astype(np.float32)
+    run(backend, "top_k_rows", [backend.upload(lg), ib, vb], [1, 256, 8, 0])
+    assert np.array_equal(backend.download(ib, np.uint32, 8), np.argsort(-lg, kind="stable")[:8].astype(np.uint32))

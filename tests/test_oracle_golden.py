@@ -182,3 +182,22 @@ def test_rope_and_delta_rule_match_golden(oracle):
     assert np.array_equal(oracle.mrope(g["rope_io"], g["rope_pos"], 2, 3, 64, 48, 11, 8, 5, 1e7), g["rope_out"])
     s, o = oracle.delta_step_heads(g["ds_s"], g["ds_k"], g["ds_v"], g["ds_q"], g["ds_alpha"], g["ds_beta"], 3, 20, 24)
     assert np.array_equal(s, g["ds_s_out"]) and np.array_equal(o, g["ds_o"])
+
+
+def test_conv_step_matches_golden_and_underlies_conv1d_state(oracle):
+    """Conv1dStepRef (src/core/numerics/conv.cpp of the reference); the device-only conv1d_state contract
+    is that convolution over [current, history] with the taps reversed, then SiLU and the split."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "elementwise_golden.npz"))
+    assert np.array_equal(oracle.conv1d_step(g["conv_x"], g["conv_w"], 40, 4), g["conv_y"])
+    rng = np.random.default_rng(3)
+    c, w_, kd = 40, 4, 10
+    hist = rng.standard_normal(c * (w_ - 1)).astype(np.float32)
+    qkv = rng.standard_normal(c).astype(np.float32)
+    q, k, v, hist2, _ = oracle.conv1d_state(qkv, g["conv_w"], hist, c, w_, kd, 0, 1)
+    xs = np.concatenate([qkv[:, None], hist.reshape(c, w_ - 1)], axis=1).reshape(-1)
+    wr = g["conv_w"].reshape(c, w_)[:, ::-1].copy().reshape(-1)
+    acc = oracle.conv1d_step(xs, wr, c, w_).astype(np.float64)
+    want = (acc / (1 + np.exp(-acc))).astype(np.float32)
+    assert np.abs(np.concatenate([q, k, v]) - want).max() <= 1e-6
+    assert np.array_equal(hist2.reshape(c, w_ - 1)[:, 0], qkv) and np.array_equal(hist2.reshape(c, w_ - 1)[:, 1:], hist.reshape(c, w_ - 1)[:, :-1])
