@@ -454,6 +454,69 @@ def delta_row(stream, hbm_peak, heads=48, dk=128, dv=128, layers=48):
             "gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / hbm_peak, 3)}
 
 
+def attention_row(stream, hbm_peak, tag="f32", n=4096, heads=24, kv_heads=4, head_dim=256, layers=16):
+    """One decode token's attention over the key / value cache (ids attention / attention_q8 / attention_fp8):
+    every full-attention layer has its own cache (4096 keys x 4 kv heads x 256: 33.5 MB in fp32, 8.4 MB in
+    FP8; 16 layers hold more than L2), read once per token.  From a CUDA graph of the 16 launches
+    (two kernels each: chunks, merge); bytes = keys + values + scales + q + out."""
+    import torch
+    from tessera_b200.backend import CreateBackend, KernelLaunch
+    backend = CreateBackend(stream=stream.cuda_stream)
+    backend.SetDeviceIndex(torch.cuda.current_device())
+    backend.Init()
+    g = np.random.default_rng(37)
+    row = kv_heads * head_dim
+    esz = {"f32": 4, "f16": 2, "q8": 1, "fp8": 1}[tag]
+
+    def cache():
+        if tag == "f32":
+            return backend.upload(g.standard_normal((n, row)).astype(np.float32))
+        if tag == "f16":
+            return backend.upload(g.standard_normal((n, row)).astype(np.float16).view(np.uint8))
+        if tag == "q8":
+            return backend.upload(g.integers(-127, 128, (n, row)).astype(np.int8).view(np.uint8))
+        b = g.integers(0, 256, (n, row)).astype(np.uint8)
+        b[(b & 0x7F) == 0x7F] = 0x3C
+        return backend.upload(b)
+    caches = [(cache(), cache()) for _ in range(layers)]
+    scale = backend.upload(np.full(n, 0.01, dtype=np.float32))
+    q = backend.upload(g.standard_normal(heads * head_dim).astype(np.float32))
+    o = backend.AllocateBuffer(heads * head_dim * 4)
+    if tag in ("f32", "f16"):
+        kern = backend.LoadKernel("attention")
+        launches = [KernelLaunch(buffers=[q, k, v, o], scalars=[1, n, heads, kv_heads, head_dim, n - 1, 0, 0, int(tag == "f16"), 1])
+                    for k, v in caches]
+    else:
+        kern = backend.LoadKernel("attention_" + tag)
+        launches = [KernelLaunch(buffers=[q, k, v, scale, scale, o],
+                                 scalars=[1, n, heads, kv_heads, head_dim, n - 1, 0, 0, 0 if tag == "q8" else 2])
+                    for k, v in caches]
+    with torch.cuda.stream(stream):
+        def step():
+            for l in launches:
+                backend.LaunchKernel(kern, l)
+        step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+            step()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 10
+        e0.record(stream)
+        for _ in range(reps):
+            graph.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * layers)
+    nbytes = 2 * n * row * esz + (2 * n * 4 if esz == 1 else 0) + 2 * heads * head_dim * 4
+    backend.close()
+    return {"fmt": "attention_" + tag, "keys": n, "heads": heads, "kv_heads": kv_heads, "head_dim": head_dim,
+            "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / hbm_peak, 3)}
+
+
 class Recorder:
     """Stands in for the backend while the projection planner runs: kernels and buffers come
     from the real backend, launches are recorded instead of issued.  The recorded list is the
@@ -896,6 +959,8 @@ def gpu_arm(args):
         line["qgemv"] = qgemv_table(stream, peaks["hbm_gbs"])
         line["qgemv"].append(moe_row(stream, peaks["hbm_gbs"]))
         line["qgemv"].append(delta_row(stream, peaks["hbm_gbs"]))
+        line["qgemv"].append(attention_row(stream, peaks["hbm_gbs"], "f32"))
+        line["qgemv"].append(attention_row(stream, peaks["hbm_gbs"], "fp8"))
         from oracle.oracle import Oracle
         threads = os.cpu_count() or 1
         v, sample = run_cpu_sample(Oracle(), threads, 12.0)
@@ -921,7 +986,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, metavar="FMT:M:N:K[:G]",
-                    help="time one projection (q4k, q6k, mxfp4, fp8, w4a8; `moe` for the routed experts of one token, `delta` for the delta-rule state step) "
+                    help="time one projection (q4k, q6k, mxfp4, fp8, w4a8; `moe` for the routed experts of one token, `delta` for the delta-rule state step, `attn:f32|f16|q8|fp8[:KEYS]` for one token's attention over the cache) "
                          "instead of the decode step, e.g. "
                          "q4k:1:17408:5120; with G (q4k, q6k): G weight tensors of that shape in one merged launch\n"
                          "that picks its own split of k")
@@ -949,6 +1014,12 @@ def main():
             peaks, kind = measured_peaks()
             torch.cuda.set_device(0)
             print(json.dumps({"case": args.case, "peak_kind": kind, **delta_row(torch.cuda.Stream(), peaks["hbm_gbs"])}))
+            return
+        if fields[0] == "attn":
+            peaks, kind = measured_peaks()
+            torch.cuda.set_device(0)
+            row = attention_row(torch.cuda.Stream(), peaks["hbm_gbs"], fields[1], int(fields[2]) if len(fields) > 2 else 4096)
+            print(json.dumps({"case": args.case, "peak_kind": kind, **row}))
             return
         if fields[0] == "moe":
             peaks, kind = measured_peaks()

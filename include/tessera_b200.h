@@ -266,6 +266,33 @@ int tsr_conv1d_state(const float* qkv, const float* w, float* hist, float* q, fl
  * input row row_base + r; equal values: lowest index first (src/backends/rocm/rocm_kernels.hpp:558-566) */
 int tsr_top_k_rows(const float* logits, uint32_t* ids, float* vals, uint64_t rows, uint64_t vocab, uint64_t top_k,
                    uint64_t row_base, void* stream);
+/* Key / value cache formats of the attention entry points. */
+#define TSR_KV_F32 0  /* fp32 */
+#define TSR_KV_F16 1  /* binary16 */
+#define TSR_KV_INT8 2 /* int8 bytes, one fp32 scale per key row (k_scale, v_scale) */
+#define TSR_KV_INT4 3 /* two's-complement nibbles, element idx in bits 4 (idx % 2) of byte idx / 2, scale per key row */
+#define TSR_KV_FP8 4  /* OCP FP8 E4M3 bytes, scale per key row */
+/* attention / attention_q8 / attention_q4 / attention_fp8: grouped-query attention of m query rows (row
+ * row_base + i of q / out, at position q_base + i) over n key / value rows (n x kv_heads x head_dim); causal: keys
+ * max(0, pos + 1 - window)..min(pos, n - 1) (window 0 = all), else all n; scale 1/sqrt(head_dim); head h reads kv head
+ * h / (heads / kv_heads); k_scale / v_scale only for the scaled formats.  head_dim 128 or 256 and heads / kv_heads
+ * <= 8, else TSR_UNSUPPORTED_FEATURE.  The key range is cut into chunks inside the call (backend.hpp:167-179,283-309;
+ * AttentionRef, AttentionRefF16, AttentionQ8Ref, AttentionQ4Ref, AttentionFp8Ref, src/core/numerics/attention.cpp:45-214) */
+int tsr_attention(int kv_format, const float* q, const void* k, const void* v, const float* k_scale, const float* v_scale,
+                  float* out, uint64_t m, uint64_t n, uint64_t heads, uint64_t kv_heads, uint64_t head_dim, uint64_t q_base,
+                  uint64_t row_base, uint64_t window, uint64_t causal, void* stream);
+/* attention_split, attention_split_gqa, attention_q8_split / _q4_split / _fp8_split: the first half alone, with the
+ * caller's chunk count (<= 64) and partial buffers: chunk s of (row i, head h) at base = (i * heads + h) * split + s
+ * writes pacc[base * head_dim ..], pmax[base], psum[base]; an empty chunk writes (0, -1e30, 0)
+ * (backend.hpp:309-330; src/backends/rocm/rocm_kernels_basic.cpp:278-330) */
+int tsr_attention_split(int kv_format, const float* q, const void* k, const void* v, const float* k_scale,
+                        const float* v_scale, float* pacc, float* pmax, float* psum, uint64_t m, uint64_t n, uint64_t heads,
+                        uint64_t kv_heads, uint64_t head_dim, uint64_t q_base, uint64_t window, uint64_t causal,
+                        uint64_t split, void* stream);
+/* attention_combine: out[(i * heads + h) * head_dim + e] = sum_s w_s pacc / sum_s w_s psum, w_s = exp(pmax_s - max pmax)
+ * (src/backends/rocm/rocm_kernels_basic.cpp:664-686) */
+int tsr_attention_combine(const float* pacc, const float* pmax, const float* psum, float* out, uint64_t m, uint64_t heads,
+                          uint64_t head_dim, uint64_t split, void* stream);
 /* silu_mul: O = silu(G) * U, backend.hpp:257-260; SiluMulRef src/core/numerics/norm.cpp:211-225 */
 int tsr_silu_mul(const float* g, const float* u, float* o, uint64_t n, void* stream);
 /* rmsnorm: Y = X / sqrt(mean(X^2) + eps) * W per row, backend.hpp:212-216; RmsNormRef

@@ -586,6 +586,83 @@ int orc_delta_step_heads(float* s, const float* k, const float* v, const float* 
   return 0;
 }
 
+/* Element idx of a key / value cache as fp32.  kv_format: 0 fp32, 1 binary16, 2 int8, 3 two's-complement nibble
+ * (bits 4 (idx % 2) of byte idx / 2), 4 FP8 E4M3; formats 2..4 times the scale of the element's key row
+ * (AttentionRefF16, AttentionQ8Ref, AttentionQ4Ref, AttentionFp8Ref: src/core/numerics/attention.cpp:45-157). */
+static float cache_element(int kv_format, const void* cache, size_t idx, float scale) {
+  const uint8_t* b = (const uint8_t*)cache;
+  switch (kv_format) {
+    case 0: return ((const float*)cache)[idx];
+    case 1: return orc_fp16_to_float((uint16_t)(b[2 * idx] | ((uint16_t)b[2 * idx + 1] << 8)));
+    case 2: return (float)(int8_t)b[idx] * scale;
+    case 3: {
+      int v = (b[idx / 2] >> ((idx % 2) * 4)) & 0xF;
+      if (v & 0x8) v -= 16;
+      return (float)v * scale;
+    }
+    default: return orc_fp8e4m3_to_float(b[idx]) * scale;
+  }
+}
+
+/* AttentionRef, src/core/numerics/attention.cpp:159-214: per query row i (position q_base + i) and head h: scores
+ * fma(q, k) * 1/sqrt(head_dim) over keys start..last, the row's max, exp(score - max), their sum in key order, then
+ * out[e] = fma(score / sum, v[e]) in key order.  The cache is decoded first, as the reference's wrappers do. */
+int orc_attention(int kv_format, const float* q, const void* k, const void* v, const float* k_scale, const float* v_scale,
+                  float* out, size_t m, size_t n, size_t heads, size_t kv_heads, size_t head_dim, uint64_t q_base,
+                  size_t window, int causal) {
+  if (m == 0 || n == 0 || heads == 0 || kv_heads == 0 || head_dim == 0 || heads % kv_heads != 0) return -2;
+  if (kv_format < 0 || kv_format > 4 || (kv_format >= 2 && (!k_scale || !v_scale))) return -2;
+  const size_t row = kv_heads * head_dim, group = heads / kv_heads;
+  float* kf = (float*)malloc(n * row * sizeof(float));
+  float* vf = (float*)malloc(n * row * sizeof(float));
+  float* scores = (float*)malloc(n * sizeof(float));
+  if (!kf || !vf || !scores) {
+    free(kf), free(vf), free(scores);
+    return -1;
+  }
+  for (size_t j = 0; j < n; ++j)
+    for (size_t d = 0; d < row; ++d) {
+      kf[j * row + d] = cache_element(kv_format, k, j * row + d, kv_format >= 2 ? k_scale[j] : 1.0f);
+      vf[j * row + d] = cache_element(kv_format, v, j * row + d, kv_format >= 2 ? v_scale[j] : 1.0f);
+    }
+  const float scale = 1.0f / sqrtf((float)head_dim);
+  for (size_t i = 0; i < m; ++i) {
+    const size_t pos = (size_t)(q_base + i);
+    const size_t last = causal ? (pos >= n ? n - 1 : pos) : n - 1;
+    size_t start = 0;
+    if (causal) {
+      start = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+      if (start > last) start = last;
+    }
+    for (size_t h = 0; h < heads; ++h) {
+      const size_t kvh = h / group;
+      const float* qr = q + (i * heads + h) * head_dim;
+      float top = 0.0f;
+      for (size_t j = start; j <= last; ++j) {
+        const float* kr = kf + (j * kv_heads + kvh) * head_dim;
+        float dot = 0.0f;
+        for (size_t e = 0; e < head_dim; ++e) dot = fmaf(qr[e], kr[e], dot);
+        dot *= scale;
+        scores[j] = dot;
+        if (j == start || dot > top) top = dot;
+      }
+      float denom = 0.0f;
+      for (size_t j = start; j <= last; ++j) {
+        scores[j] = expf(scores[j] - top);
+        denom += scores[j];
+      }
+      float* o = out + (i * heads + h) * head_dim;
+      for (size_t e = 0; e < head_dim; ++e) {
+        float acc = 0.0f;
+        for (size_t j = start; j <= last; ++j) acc = fmaf(scores[j] / denom, vf[(j * kv_heads + kvh) * head_dim + e], acc);
+        o[e] = acc;
+      }
+    }
+  }
+  free(kf), free(vf), free(scores);
+  return 0;
+}
+
 /* Conv1dStepRef, src/core/numerics/conv.cpp: y[c] = sum_i w[c][i] * x[c][i], fma in order (x newest first) */
 int orc_conv1d_step(const float* x, const float* w, float* y, size_t channels, size_t width) {
   if (channels == 0 || width == 0) return -2;

@@ -255,6 +255,19 @@ class Oracle:
         assert self._fn("conv1d_step", C.c_int, [_p, _p, _p, _sz, _sz])(_ptr(x), _ptr(w), _ptr(y), channels, width) == 0
         return y
 
+    def attention(self, kv_format, q, k, v, m, n, heads, kv_heads, head_dim, q_base=0, window=0, causal=True,
+                  k_scale=None, v_scale=None):
+        """kv_format 0 fp32, 1 fp16, 2 int8, 3 4-bit, 4 FP8 (k, v: arrays of the cache's bytes or floats)."""
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        k, v = np.ascontiguousarray(k), np.ascontiguousarray(v)
+        ks = np.zeros(1, np.float32) if k_scale is None else np.ascontiguousarray(k_scale, dtype=np.float32)
+        vs = np.zeros(1, np.float32) if v_scale is None else np.ascontiguousarray(v_scale, dtype=np.float32)
+        out = np.empty(m * heads * head_dim, dtype=np.float32)
+        fn = self._fn("attention", C.c_int, [C.c_int, _p, _p, _p, _p, _p, _p, _sz, _sz, _sz, _sz, _sz, C.c_uint64, _sz, C.c_int])
+        assert fn(kv_format, _ptr(q), _ptr(k), _ptr(v), _ptr(ks), _ptr(vs), _ptr(out), m, n, heads, kv_heads, head_dim,
+                  q_base, window, 1 if causal else 0) == 0
+        return out.reshape(m, heads * head_dim)
+
     def conv1d_state(self, qkv, w, hist, conv_dim, width, key_dim, qkv_offset, rows, hist_stride=0, hist_hist=None):
         """Device contract (C restatement only).  Returns (q, k, v, hist, hist_hist)."""
         assert not self.reference

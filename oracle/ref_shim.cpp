@@ -151,6 +151,34 @@ int ref_delta_step_heads(float* s, const float* k, const float* v, const float* 
 int ref_conv1d_step(const float* x, const float* w, float* y, std::size_t channels, std::size_t width) {
   return Code(tc::Conv1dStepRef({x, channels * width}, {w, channels * width}, {y, channels}, channels, width));
 }
+// kv_format as in the C oracle: 0 fp32 (AttentionRef), 1 fp16 (AttentionRefF16), 2 int8 (AttentionQ8Ref),
+// 3 4-bit (AttentionQ4Ref), 4 FP8 (AttentionFp8Ref).  Only AttentionRef takes `causal`.
+int ref_attention(int kv_format, const float* q, const void* k, const void* v, const float* k_scale, const float* v_scale,
+                  float* out, std::size_t m, std::size_t n, std::size_t heads, std::size_t kv_heads, std::size_t head_dim,
+                  std::uint64_t q_base, std::size_t window, int causal) {
+  const std::size_t qn = m * heads * head_dim, count = n * kv_heads * head_dim;
+  const auto* kb = static_cast<const std::byte*>(k);
+  const auto* vb = static_cast<const std::byte*>(v);
+  switch (kv_format) {
+    case 0:
+      return Code(tc::AttentionRef({q, qn}, {static_cast<const float*>(k), count}, {static_cast<const float*>(v), count},
+                                   {out, qn}, m, n, heads, kv_heads, head_dim, q_base, window, causal != 0));
+    case 1:
+      if (causal == 0) return -2;
+      return Code(tc::AttentionRefF16({q, qn}, {kb, count * 2}, {vb, count * 2}, {out, qn}, m, n, heads, kv_heads, head_dim,
+                                      q_base, window));
+    case 2:
+      return Code(tc::AttentionQ8Ref({q, qn}, {kb, count}, {vb, count}, {k_scale, n}, {v_scale, n}, {out, qn}, m, n, heads,
+                                     kv_heads, head_dim, q_base, window));
+    case 3:
+      return Code(tc::AttentionQ4Ref({q, qn}, {kb, count / 2}, {vb, count / 2}, {k_scale, n}, {v_scale, n}, {out, qn}, m, n,
+                                     heads, kv_heads, head_dim, q_base, window));
+    case 4:
+      return Code(tc::AttentionFp8Ref({q, qn}, {kb, count}, {vb, count}, {k_scale, n}, {v_scale, n}, {out, qn}, m, n, heads,
+                                      kv_heads, head_dim, q_base, window));
+    default: return -2;
+  }
+}
 int ref_silu_mul(const float* g, const float* u, float* o, std::size_t n) {
   return Code(tc::SiluMulRef({g, n}, {u, n}, {o, n}, n));
 }

@@ -102,6 +102,9 @@ SIGNATURES = {
     "tsr_sigmoid_gate": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
     "tsr_conv1d_state": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64, _u64, _u64, _vp]),
     "tsr_top_k_rows": (C.c_int, [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp]),
+    "tsr_attention": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _vp] + [_u64] * 9 + [_vp]),
+    "tsr_attention_split": (C.c_int, [C.c_int] + [_vp] * 8 + [_u64] * 9 + [_vp]),
+    "tsr_attention_combine": (C.c_int, [_vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp]),
     "tsr_mrope": (C.c_int, [_vp, _vp, _u64, _u64, _u64, _u64, C.c_float, _u64, _u64, _u64, _vp]),
     "tsr_cast_f32_f16": (C.c_int, [_vp, _vp, _u64, _vp]),
     "tsr_delta_step_heads": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _vp]),

@@ -540,6 +540,103 @@ int k_top_k_rows(const Args& a) {
                         static_cast<float*>(const_cast<void*>(a.buf[2])), rows, vocab, top_k, base, a.stream);
 }
 
+// attention: buffers q, k, v, out; scalars m, n, heads, kv_heads, head_dim, q_base, row_base, window, kv_f16, causal
+// (backend.hpp:167-179).
+bool attention_dims_ok(uint64_t m, uint64_t n, uint64_t heads, uint64_t kvh, uint64_t d, uint64_t rb, uint64_t win) {
+  return dims_ok(m, n, heads) && dims_ok(kvh, d, 1) && heads % kvh == 0 && d <= 256 && rb <= kMaxDim && win <= kMaxDim;
+}
+// what the kernel serves (told before anything is queued): head_dim 128 or 256, at most 8 query heads per kv head
+bool attention_served(uint64_t heads, uint64_t kvh, uint64_t d) { return (d == 128 || d == 256) && heads / kvh <= 8; }
+uint64_t cache_bytes(int kv_format, uint64_t elems) {
+  return kv_format == TSR_KV_F32 ? elems * 4 : kv_format == TSR_KV_F16 ? elems * 2 : kv_format == TSR_KV_INT4 ? elems / 2 : elems;
+}
+constexpr int kQuantKv[3] = {TSR_KV_INT8, TSR_KV_INT4, TSR_KV_FP8};  // the reference's `kind` 0, 1, 2
+
+int k_attention(const Args& a) {
+  if (!shape(a, 4, 10)) return kInvalidArgument;
+  const uint64_t m = a.sc[0], n = a.sc[1], heads = a.sc[2], kvh = a.sc[3], d = a.sc[4], qb = a.sc[5], rb = a.sc[6], win = a.sc[7];
+  if (!attention_dims_ok(m, n, heads, kvh, d, rb, win)) return kInvalidArgument;
+  if (!attention_served(heads, kvh, d)) return kUnsupportedFeature;
+  const int fmt = a.sc[8] != 0 ? TSR_KV_F16 : TSR_KV_F32;
+  if (!holds(a, 0, (rb + m) * heads * d * 4) || !holds(a, 1, cache_bytes(fmt, n * kvh * d)) ||
+      !holds(a, 2, cache_bytes(fmt, n * kvh * d)) || !holds(a, 3, (rb + m) * heads * d * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_attention(fmt, static_cast<const float*>(a.buf[0]), a.buf[1], a.buf[2], nullptr, nullptr,
+                       static_cast<float*>(const_cast<void*>(a.buf[3])), m, n, heads, kvh, d, qb, rb, win, a.sc[9], a.stream);
+}
+
+// attention_q8 / attention_q4 / attention_fp8: buffers q, k, v, k_scale, v_scale, out; scalars rows, n, heads,
+// kv_heads, head_dim, q_base, row_base, window, kind (src/core/decode_internal.hpp:243-261; backend.hpp:283-309).
+template <int KIND>
+int k_attention_quant(const Args& a) {
+  if (!shape(a, 6, 9)) return kInvalidArgument;
+  const uint64_t m = a.sc[0], n = a.sc[1], heads = a.sc[2], kvh = a.sc[3], d = a.sc[4], qb = a.sc[5], rb = a.sc[6], win = a.sc[7];
+  if (!attention_dims_ok(m, n, heads, kvh, d, rb, win) || a.sc[8] != static_cast<uint64_t>(KIND)) return kInvalidArgument;
+  if (!attention_served(heads, kvh, d)) return kUnsupportedFeature;
+  const uint64_t cache = cache_bytes(kQuantKv[KIND], n * kvh * d);
+  if (!holds(a, 0, (rb + m) * heads * d * 4) || !holds(a, 1, cache) || !holds(a, 2, cache) || !holds(a, 3, n * 4) ||
+      !holds(a, 4, n * 4) || !holds(a, 5, (rb + m) * heads * d * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_attention(kQuantKv[KIND], static_cast<const float*>(a.buf[0]), a.buf[1], a.buf[2],
+                       static_cast<const float*>(a.buf[3]), static_cast<const float*>(a.buf[4]),
+                       static_cast<float*>(const_cast<void*>(a.buf[5])), m, n, heads, kvh, d, qb, rb, win, 1, a.stream);
+}
+
+// attention_split / attention_split_gqa: buffers q, k, v, pacc, pmax, psum; scalars rows, n, heads, kv_heads, head_dim,
+// q_base, window, kv_f16, causal, split (src/core/decode_internal.hpp:317-343).  One kernel serves both ids: it always
+// reads a key row once for all heads of its kv head.
+int k_attention_split(const Args& a) {
+  if (!shape(a, 6, 10)) return kInvalidArgument;
+  const uint64_t m = a.sc[0], n = a.sc[1], heads = a.sc[2], kvh = a.sc[3], d = a.sc[4], qb = a.sc[5], win = a.sc[6], split = a.sc[9];
+  if (!attention_dims_ok(m, n, heads, kvh, d, 0, win) || split == 0 || split > 64) return kInvalidArgument;
+  if (!attention_served(heads, kvh, d)) return kUnsupportedFeature;
+  const int fmt = a.sc[7] != 0 ? TSR_KV_F16 : TSR_KV_F32;
+  const uint64_t parts = m * heads * split;
+  if (!holds(a, 0, m * heads * d * 4) || !holds(a, 1, cache_bytes(fmt, n * kvh * d)) ||
+      !holds(a, 2, cache_bytes(fmt, n * kvh * d)) || !holds(a, 3, parts * d * 4) || !holds(a, 4, parts * 4) ||
+      !holds(a, 5, parts * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  auto f = [&](int i) { return static_cast<float*>(const_cast<void*>(a.buf[i])); };
+  return tsr_attention_split(fmt, f(0), a.buf[1], a.buf[2], nullptr, nullptr, f(3), f(4), f(5), m, n, heads, kvh, d, qb, win,
+                             a.sc[8], split, a.stream);
+}
+
+// attention_q8_split / _q4_split / _fp8_split: buffers q, k, v, k_scale, v_scale, pacc, pmax, psum; scalars rows, n,
+// heads, kv_heads, head_dim, q_base, window, kind, split (src/core/decode_internal.hpp:348-374).
+template <int KIND>
+int k_attention_quant_split(const Args& a) {
+  if (!shape(a, 8, 9)) return kInvalidArgument;
+  const uint64_t m = a.sc[0], n = a.sc[1], heads = a.sc[2], kvh = a.sc[3], d = a.sc[4], qb = a.sc[5], win = a.sc[6], split = a.sc[8];
+  if (!attention_dims_ok(m, n, heads, kvh, d, 0, win) || a.sc[7] != static_cast<uint64_t>(KIND) || split == 0 || split > 64)
+    return kInvalidArgument;
+  if (!attention_served(heads, kvh, d)) return kUnsupportedFeature;
+  const uint64_t cache = cache_bytes(kQuantKv[KIND], n * kvh * d), parts = m * heads * split;
+  if (!holds(a, 0, m * heads * d * 4) || !holds(a, 1, cache) || !holds(a, 2, cache) || !holds(a, 3, n * 4) ||
+      !holds(a, 4, n * 4) || !holds(a, 5, parts * d * 4) || !holds(a, 6, parts * 4) || !holds(a, 7, parts * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  auto f = [&](int i) { return static_cast<float*>(const_cast<void*>(a.buf[i])); };
+  return tsr_attention_split(kQuantKv[KIND], f(0), a.buf[1], a.buf[2], f(3), f(4), f(5), f(6), f(7), m, n, heads, kvh, d, qb, win,
+                             1, split, a.stream);
+}
+
+// attention_combine: buffers pacc, pmax, psum, out; scalars rows, heads, head_dim, split
+// (src/core/decode_internal.hpp:299-310).
+int k_attention_combine(const Args& a) {
+  if (!shape(a, 4, 4)) return kInvalidArgument;
+  const uint64_t m = a.sc[0], heads = a.sc[1], d = a.sc[2], split = a.sc[3];
+  if (!dims_ok(m, heads, d) || split == 0 || split > kMaxDim) return kInvalidArgument;
+  const uint64_t parts = m * heads * split;
+  if (!holds(a, 0, parts * d * 4) || !holds(a, 1, parts * 4) || !holds(a, 2, parts * 4) || !holds(a, 3, m * heads * d * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  auto f = [&](int i) { return static_cast<float*>(const_cast<void*>(a.buf[i])); };
+  return tsr_attention_combine(f(0), f(1), f(2), f(3), m, heads, d, split, a.stream);
+}
+
 // fill: buffer int32; scalars value, count (backend.hpp:151-152).
 int k_fill(const Args& a) {
   if (!shape(a, 1, 2)) return kInvalidArgument;
@@ -743,6 +840,16 @@ const Entry kTable[] = {
     {"repeat_heads", k_repeat_heads},
     {"conv1d_state", k_conv1d_state},
     {"top_k_rows", k_top_k_rows},
+    {"attention", k_attention},
+    {"attention_q8", k_attention_quant<0>},
+    {"attention_q4", k_attention_quant<1>},
+    {"attention_fp8", k_attention_quant<2>},
+    {"attention_split", k_attention_split},
+    {"attention_split_gqa", k_attention_split},
+    {"attention_q8_split", k_attention_quant_split<0>},
+    {"attention_q4_split", k_attention_quant_split<1>},
+    {"attention_fp8_split", k_attention_quant_split<2>},
+    {"attention_combine", k_attention_combine},
     {"mrope", k_mrope},
     {"cast_f32_f16", k_cast_f16},
     {"delta_step_heads", k_delta_step_heads},

@@ -651,7 +651,7 @@ unsigned char* activation_scratch(cudaStream_t st, size_t bytes) { return stream
 }  // namespace
 
 // `slot` separates users whose buffers are alive at the same time (0: the tile kernels'
-// operands and partial sums; 1: the fp32 copies around a bf16 projection).
+// operands and partial sums; 1: the fp32 copies around a bf16 projection; 2: attention's chunk partials).
 unsigned char* stream_scratch(cudaStream_t st, size_t bytes, int slot) {
   struct Entry {
     int device;

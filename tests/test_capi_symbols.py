@@ -43,7 +43,7 @@ def test_kernel_table_has_the_projection_ids():
     ids = [lib.tsr_kernel_name(i).decode() for i in range(lib.tsr_kernel_count())]
     for name in REQUIRED_IDS:
         assert lib.tsr_kernel_lookup(name.encode()) == ids.index(name)
-    assert lib.tsr_kernel_lookup(b"attention") == -1
+    assert lib.tsr_kernel_lookup(b"layernorm") == -1
     assert lib.tsr_kernel_name(-1) is None
 
 

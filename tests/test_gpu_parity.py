@@ -380,7 +380,7 @@ def test_launch_contract_errors(backend):
     w = backend.AllocateBuffer(8 * 144)
     c = backend.AllocateBuffer(8 * 4)
     with pytest.raises(StatusError) as e:
-        backend.LoadKernel("attention")
+        backend.LoadKernel("layernorm")
     assert e.value.code == StatusCode.UnsupportedFeature
     with pytest.raises(StatusError) as e:
         backend.LoadKernel("gemm_q4k_vec", b"\x01")

@@ -201,3 +201,25 @@ def test_conv_step_matches_golden_and_underlies_conv1d_state(oracle):
     want = (acc / (1 + np.exp(-acc))).astype(np.float32)
     assert np.abs(np.concatenate([q, k, v]) - want).max() <= 1e-6
     assert np.array_equal(hist2.reshape(c, w_ - 1)[:, 0], qkv) and np.array_equal(hist2.reshape(c, w_ - 1)[:, 1:], hist.reshape(c, w_ - 1)[:, :-1])
+
+
+ATTENTION_TAGS = ("f32", "f16", "i8", "i4", "f8")
+
+
+def test_attention_matches_golden(oracle):
+    """AttentionRef and its cache-decoding wrappers (src/core/numerics/attention.cpp:45-214 of the reference):
+    every cache format, the causal prefix, a query row past the cache, a sliding window, the non-causal form."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attention_golden.npz"))
+    m, n, heads, kv_heads, head_dim = (int(x) for x in g["dims"])
+    checked = 0
+    for fmt, tag in enumerate(ATTENTION_TAGS):
+        for si, (q_base, window, causal) in enumerate(g["settings"]):
+            key = f"out_{tag}_{si}"
+            if key not in g:
+                continue
+            y = oracle.attention(fmt, g["q"], g["k_" + tag], g["v_" + tag], m, n, heads, kv_heads, head_dim, int(q_base),
+                                 int(window), bool(causal), g["k_scale"], g["v_scale"])
+            assert np.array_equal(y, g[key]), key
+            checked += 1
+    assert checked == 16
