@@ -248,6 +248,15 @@ int tsr_embedding(int kind, const uint32_t* ids, const void* table, float* out, 
 /* mrope: rows x heads x head_dim rotated in place; pos = rows x (t, h, w) u64 (backend.hpp:378-385; MropeRef) */
 int tsr_mrope(float* io, const uint64_t* pos, uint64_t rows, uint64_t heads, uint64_t head_dim, uint64_t rope_dim,
               float theta, uint64_t sec_t, uint64_t sec_h, uint64_t sec_w, void* stream);
+/* rope: rows x heads x head_dim fp32 rotated in place, NeoX pairing over rope_dim, row r at position pos_base + r
+ * (backend.hpp:162-166; RopeRef, src/core/numerics/attention.cpp:11-43) */
+int tsr_rope(float* io, uint64_t rows, uint64_t heads, uint64_t head_dim, uint64_t rope_dim, uint64_t pos_base, float theta,
+             void* stream);
+/* quantize_q8 (kind 0) / quantize_q4 (kind 1): per row, scale = amax / 127 (/ 7), codes round-half-away(x / scale)
+ * clamped; int8 bytes (cols % 4 == 0), or nibbles with element 2i in the low half of byte i (cols % 8 == 0); the
+ * writers of the int8 / 4-bit key-value cache (backend.hpp:283-298; QuantizeQ8Ref, QuantizeQ4Ref,
+ * src/core/numerics/quant.cpp:123-181) */
+int tsr_quantize_rows(int kind, const float* in, void* out, float* scale, uint64_t rows, uint64_t cols, void* stream);
 /* cast_f32_f16: fp32 -> binary16, round to nearest even; n even (backend.hpp:334-336) */
 int tsr_cast_f32_f16(const float* in, void* out, uint64_t n, void* stream);
 /* delta_step_heads: `rows` gated delta-rule steps on the per-head state (heads x dk x dv at s + sbase, updated

@@ -563,6 +563,55 @@ int orc_mrope(float* io, const uint64_t* pos, size_t rows, size_t heads, size_t 
   return 0;
 }
 
+/* RopeRef, src/core/numerics/attention.cpp:11-43: row r at position pos_base + r, NeoX pairs (j, j + rope_dim / 2) */
+int orc_rope(float* io, size_t rows, size_t heads, size_t head_dim, size_t rope_dim, uint64_t pos_base, double theta) {
+  if (rows == 0 || heads == 0 || head_dim == 0 || rope_dim == 0 || rope_dim > head_dim || (rope_dim % 2) != 0 || !(theta > 0.0))
+    return -2;
+  const size_t half = rope_dim / 2;
+  for (size_t r = 0; r < rows; ++r) {
+    const double pos = (double)(pos_base + r);
+    for (size_t h = 0; h < heads; ++h) {
+      float* base = io + (r * heads + h) * head_dim;
+      for (size_t j = 0; j < half; ++j) {
+        const double angle = pos * pow(theta, -2.0 * (double)j / (double)rope_dim);
+        const float c = (float)cos(angle), sn = (float)sin(angle);
+        const float x1 = base[j], x2 = base[j + half];
+        base[j] = x1 * c - x2 * sn;
+        base[j + half] = x1 * sn + x2 * c;
+      }
+    }
+  }
+  return 0;
+}
+
+/* QuantizeQ8Ref / QuantizeQ4Ref, src/core/numerics/quant.cpp:123-181: limit 127 (bytes) or 7 (nibbles, element 2i low) */
+int orc_quantize_rows(int kind, const float* in, uint8_t* out, float* scale, size_t rows, size_t cols) {
+  if (rows == 0 || cols == 0 || (kind != 0 && kind != 1) || cols % (kind == 0 ? 4 : 8) != 0) return -2;
+  const long limit = kind == 0 ? 127 : 7;
+  for (size_t r = 0; r < rows; ++r) {
+    float amax = 0.0f;
+    for (size_t c = 0; c < cols; ++c) {
+      const float v = fabsf(in[r * cols + c]);
+      if (amax < v) amax = v;
+    }
+    const float s = amax > 0.0f ? amax / (float)limit : 1.0f;
+    scale[r] = s;
+    for (size_t c = 0; c < cols; ++c) {
+      long q = lroundf(in[r * cols + c] / s);
+      if (q < -limit) q = -limit;
+      if (q > limit) q = limit;
+      if (kind == 0) {
+        out[r * cols + c] = (uint8_t)(int8_t)q;
+      } else {
+        uint8_t* b = out + (r * cols + c) / 2;
+        const uint8_t nib = (uint8_t)((uint8_t)q & 0xF);
+        *b = (c % 2 == 0) ? nib : (uint8_t)(*b | (nib << 4));
+      }
+    }
+  }
+  return 0;
+}
+
 /* DeltaStepHeadsRef, attention.cpp: per head and state column d: read = sum_j S[j][d] k[j] (fma, in order);
  * S[j][d] <- alpha (S[j][d] - beta k[j] read) + beta v[d] k[j]; o[d] = sum_j S'[j][d] q[j]. */
 int orc_delta_step_heads(float* s, const float* k, const float* v, const float* q, float* o, const float* alpha,

@@ -240,6 +240,21 @@ class Oracle:
         assert fn(_ptr(io), _ptr(pos), rows, heads, head_dim, rope_dim, sec_t, sec_h, sec_w, theta) == 0
         return io
 
+    def rope(self, io, rows, heads, head_dim, rope_dim, pos_base, theta):
+        io = np.ascontiguousarray(io, dtype=np.float32).copy()
+        fn = self._fn("rope", C.c_int, [_p, _sz, _sz, _sz, _sz, C.c_uint64, C.c_double])
+        assert fn(_ptr(io), rows, heads, head_dim, rope_dim, pos_base, theta) == 0
+        return io
+
+    def quantize_rows(self, kind, data):
+        """kind 0: int8 codes (rows x cols bytes); 1: 4-bit codes (rows x cols / 2 bytes).  Returns (codes, scale)."""
+        rows, cols = data.shape
+        codes = np.zeros((rows, cols if kind == 0 else cols // 2), dtype=np.uint8)
+        scale = np.empty(rows, dtype=np.float32)
+        fn = self._fn("quantize_rows", C.c_int, [C.c_int, _p, _p, _p, _sz, _sz])
+        assert fn(kind, _ptr(np.ascontiguousarray(data, dtype=np.float32)), _ptr(codes), _ptr(scale), rows, cols) == 0
+        return codes, scale
+
     def delta_step_heads(self, s, k, v, q, alpha, beta, heads, dk, dv):
         """One step; returns (new state, o)."""
         s = np.ascontiguousarray(s, dtype=np.float32).copy()

@@ -151,6 +151,14 @@ int ref_delta_step_heads(float* s, const float* k, const float* v, const float* 
 int ref_conv1d_step(const float* x, const float* w, float* y, std::size_t channels, std::size_t width) {
   return Code(tc::Conv1dStepRef({x, channels * width}, {w, channels * width}, {y, channels}, channels, width));
 }
+int ref_rope(float* io, std::size_t rows, std::size_t heads, std::size_t head_dim, std::size_t rope_dim, std::uint64_t pos_base,
+             double theta) {
+  return Code(tc::RopeRef({io, rows * heads * head_dim}, rows, heads, head_dim, rope_dim, pos_base, theta));
+}
+int ref_quantize_rows(int kind, const float* in, std::uint8_t* out, float* scale, std::size_t rows, std::size_t cols) {
+  if (kind == 0) return Code(tc::QuantizeQ8Ref({in, rows * cols}, MutBytes(out, rows * cols), {scale, rows}, rows, cols));
+  return Code(tc::QuantizeQ4Ref({in, rows * cols}, MutBytes(out, rows * cols / 2), {scale, rows}, rows, cols));
+}
 // kv_format as in the C oracle: 0 fp32 (AttentionRef), 1 fp16 (AttentionRefF16), 2 int8 (AttentionQ8Ref),
 // 3 4-bit (AttentionQ4Ref), 4 FP8 (AttentionFp8Ref).  Only AttentionRef takes `causal`.
 int ref_attention(int kv_format, const float* q, const void* k, const void* v, const float* k_scale, const float* v_scale,

@@ -56,7 +56,7 @@ __device__ __forceinline__ void load_raw(const unsigned char* p, uint32_t (&w)[4
 // The N cache elements packed in w, as fp32 (before the key row's scale).
 template <int KV, int N>
 __device__ __forceinline__ void decode(const uint32_t (&w)[4], float (&out)[N]) {
-  if (KV == kKvFp8) {  // two bytes per conversion (every E4M3 value is exact in binary16)
+  if constexpr (KV == kKvFp8) {  // two bytes per conversion (every E4M3 value is exact in binary16)
 #pragma unroll
     for (int i = 0; i < N; i += 2) {
       const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(
@@ -64,21 +64,19 @@ __device__ __forceinline__ void decode(const uint32_t (&w)[4], float (&out)[N]) 
       const float2 f = __half22float2(__half2(h));
       out[i] = f.x, out[i + 1] = f.y;
     }
-    return;
-  }
+  } else {
 #pragma unroll
-  for (int i = 0; i < N; ++i) {
-    if (KV == kKvF32) {
-      out[i] = __uint_as_float(w[i]);
-    } else if (KV == kKvF16) {
-      out[i] = fp16_bits_to_float((w[i / 2] >> (16 * (i % 2))) & 0xFFFFu);
-    } else if (KV == kKvFp8) {
-      out[i] = e4m3_to_float((w[i / 4] >> (8 * (i % 4))) & 0xFFu);
-    } else if (KV == kKvInt8) {
-      out[i] = static_cast<float>(static_cast<signed char>((w[i / 4] >> (8 * (i % 4))) & 0xFFu));
-    } else {
-      // two's-complement nibble i: bits 4 (i % 2) of byte i / 2
-      out[i] = static_cast<float>(static_cast<int>(w[i / 8] << (28 - 4 * (i % 8))) >> 28);
+    for (int i = 0; i < N; ++i) {
+      if (KV == kKvF32) {
+        out[i] = __uint_as_float(w[i]);
+      } else if (KV == kKvF16) {
+        out[i] = fp16_bits_to_float((w[i / 2] >> (16 * (i % 2))) & 0xFFFFu);
+      } else if (KV == kKvInt8) {
+        out[i] = static_cast<float>(static_cast<signed char>((w[i / 4] >> (8 * (i % 4))) & 0xFFu));
+      } else {
+        // two's-complement nibble i: bits 4 (i % 2) of byte i / 2
+        out[i] = static_cast<float>(static_cast<int>(w[i / 8] << (28 - 4 * (i % 8))) >> 28);
+      }
     }
   }
 }
@@ -144,6 +142,37 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_chunk_kernel(con
     }
     return;
   }
+  // The first trip's loads are issued before q is staged.  With 16-bit and narrower caches the later trips' are
+  // issued a phase early (a trip's keys while the trip before it does its softmax and values, its values while
+  // the next scores are formed); the fp32 cache's words need the registers, so its trips load at their start
+  // (measured: 18.3 against 19.8 us per layer at 4096 keys).
+  constexpr bool kEarly = BITS <= 16;
+  const size_t row_bytes = static_cast<size_t>(p.kv_heads) * D * BITS / 8;
+  const unsigned char* kbase = static_cast<const unsigned char*>(p.k) + static_cast<size_t>(kv) * D * BITS / 8;
+  const unsigned char* vbase = static_cast<const unsigned char*>(p.v) + static_cast<size_t>(kv) * D * BITS / 8;
+  uint32_t kraw[NV][4], vraw[4][NVV][4];
+  float kscale = 1.0f, vscale = 1.0f;
+  auto load_keys = [&](int base) {
+    const int j = min(base + grp, c1 - 1);
+#pragma unroll
+    for (int t = 0; t < NV; ++t)
+      load_raw<VEC * BITS / 8>(kbase + j * row_bytes + (t * 8 * VEC + sub * VEC) * BITS / 8, kraw[t]);
+    if (kScaled) kscale = __ldg(p.ks + j), vscale = __ldg(p.vs + j);
+  };
+  auto load_values = [&](int base) {
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const int jj = min(base + kk, c1 - 1);
+#pragma unroll
+      for (int t = 0; t < NVV; ++t)
+        load_raw<VV * BITS / 8>(vbase + jj * row_bytes + (t * 32 * VV + lane * VV) * BITS / 8, vraw[kk][t]);
+    }
+  };
+  const int first = c0 + warp * 4;
+  if (first < c1) {
+    load_keys(first);
+    load_values(first);
+  }
   {
     const float qscale = kLog2e / sqrtf(static_cast<float>(D));
     const float* qrow = p.q + ((p.row_base + i) * p.heads + static_cast<size_t>(kv) * group) * D;
@@ -164,25 +193,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_chunk_kernel(con
 #pragma unroll
     for (int e = 0; e < EV; ++e) acc[g][e] = 0.0f;
   }
-  const size_t row_bytes = static_cast<size_t>(p.kv_heads) * D * BITS / 8;
-  const unsigned char* kbase = static_cast<const unsigned char*>(p.k) + static_cast<size_t>(kv) * D * BITS / 8;
-  const unsigned char* vbase = static_cast<const unsigned char*>(p.v) + static_cast<size_t>(kv) * D * BITS / 8;
-  for (int base = c0 + warp * 4; base < c1; base += kAttnWarps * 4) {
+  for (int base = first; base < c1; base += kAttnWarps * 4) {
     const bool valid = base + grp < c1;
-    const int j = valid ? base + grp : c1 - 1;
-    uint32_t kraw[NV][4], vraw[4][NVV][4];
-#pragma unroll
-    for (int t = 0; t < NV; ++t)
-      load_raw<VEC * BITS / 8>(kbase + j * row_bytes + (t * 8 * VEC + sub * VEC) * BITS / 8, kraw[t]);
-#pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-      const int jj = min(base + kk, c1 - 1);
-#pragma unroll
-      for (int t = 0; t < NVV; ++t)
-        load_raw<VV * BITS / 8>(vbase + jj * row_bytes + (t * 32 * VV + lane * VV) * BITS / 8, vraw[kk][t]);
+    const int next = base + kAttnWarps * 4;
+    if (!kEarly && base != first) {
+      load_keys(base);
+      load_values(base);
     }
-    float kscale = 1.0f, vscale = 1.0f;
-    if (kScaled) kscale = __ldg(p.ks + j), vscale = __ldg(p.vs + j);
+    const float kscale_now = kscale, vscale_now = vscale;  // of this trip's key, before the next trip's loads
     float s[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) s[g] = 0.0f;
@@ -201,6 +219,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_chunk_kernel(con
           s[g] = fmaf(qq.w, kx[4 * u + 3], s[g]);
         }
     }
+    if (kEarly && next < c1) load_keys(next);
 #pragma unroll
     for (int o = 1; o < 8; o <<= 1)
 #pragma unroll
@@ -208,7 +227,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_chunk_kernel(con
     float w[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      const float sc = valid ? s[g] * kscale : kNoKey;
+      const float sc = valid ? s[g] * kscale_now : kNoKey;
       float top = fmaxf(sc, __shfl_xor_sync(0xFFFFFFFFu, sc, 8));
       top = fmaxf(top, __shfl_xor_sync(0xFFFFFFFFu, top, 16));
       if (top > mx[g]) {  // the same in every lane
@@ -220,7 +239,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_chunk_kernel(con
       }
       const float wk = exp2f(sc - mx[g]);
       sm[g] += wk;  // this lane's keys; its 8 lanes hold the same sum
-      w[g] = wk * vscale;
+      w[g] = wk * vscale_now;
     }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
@@ -241,6 +260,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_chunk_kernel(con
         }
       }
     }
+    if (kEarly && next < c1) load_values(next);
   }
   // the warps meet: the CTA's max per head, every warp's share rescaled to it, summed in warp order
 #pragma unroll
@@ -281,17 +301,26 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_chunk_kernel(con
 
 // "attention_combine" (src/backends/rocm/rocm_kernels_basic.cpp:664-686 of the reference):
 // out[row][head][e] = sum_s w_s pacc_s[e] / sum_s w_s psum_s, w_s = exp(pmax_s - max_s pmax_s), chunks in order.
-// One CTA merges 64 output elements of one (row, head): warp 0 finds the max and the denominator, then four
-// quarter-CTAs each sum every fourth chunk (all their loads in flight together) and the quarters meet in order.
+// One CTA merges 64 output elements of one (row, head): four quarter-CTAs each take every fourth chunk and
+// have their partial values in flight (up to 16 each) while warp 0 finds the max and the denominator; the
+// quarters meet in order.
 __global__ void __launch_bounds__(256)
 attention_combine_kernel(const float* __restrict__ pacc, const float* __restrict__ pmax, const float* __restrict__ psum,
                          float* __restrict__ out, int heads, int head_dim, int splits, unsigned long long row_base) {
+  constexpr int kHeld = 16;   // chunks a thread holds in registers: 4 * 16 = 64 chunks without a second round of loads
   __shared__ float w_s[256];  // the weights of the first 256 chunks, computed once
   __shared__ float quarter[4][64];
   __shared__ float top_s, den_s;
   const size_t g = blockIdx.x, base = g * splits;
   const size_t i = g / heads, h = g - i * heads;
   const int lane = threadIdx.x & 31;
+  const int col = threadIdx.x & 63, e = blockIdx.y * 64 + col, part = threadIdx.x >> 6;
+  float held[kHeld];
+#pragma unroll
+  for (int r = 0; r < kHeld; ++r) {
+    const int s = part + 4 * r;
+    held[r] = (s < splits && e < head_dim) ? pacc[(base + s) * head_dim + e] : 0.0f;
+  }
   if (threadIdx.x < 32) {
     float top = kNullMax;
     for (int s = lane; s < splits; s += 32) top = fmaxf(top, pmax[base + s]);
@@ -308,12 +337,15 @@ attention_combine_kernel(const float* __restrict__ pacc, const float* __restrict
     if (lane == 0) top_s = top, den_s = den;
   }
   __syncthreads();
-  const int col = threadIdx.x & 63, e = blockIdx.y * 64 + col, part = threadIdx.x >> 6;
   float num = 0.0f;
   if (e < head_dim) {
     const float top = top_s;
-#pragma unroll 16
-    for (int s = part; s < splits; s += 4) {
+#pragma unroll
+    for (int r = 0; r < kHeld; ++r) {
+      const int s = part + 4 * r;
+      if (s < splits) num = fmaf(w_s[s], held[r], num);
+    }
+    for (int s = part + 4 * kHeld; s < splits; s += 4) {
       const float w = s < 256 ? w_s[s] : expf(pmax[base + s] - top);
       num = fmaf(w, pacc[(base + s) * head_dim + e], num);
     }

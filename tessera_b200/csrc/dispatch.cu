@@ -481,6 +481,30 @@ int k_mrope(const Args& a) {
                    rdim, float_of_bits(a.sc[4]), a.sc[5], a.sc[6], a.sc[7], a.stream);
 }
 
+// rope: buffer io; scalars rows, heads, head_dim, rope_dim, pos_base, theta bits (backend.hpp:162-166).
+int k_rope(const Args& a) {
+  if (!shape(a, 1, 6)) return kInvalidArgument;
+  const uint64_t rows = a.sc[0], heads = a.sc[1], dim = a.sc[2], rdim = a.sc[3];
+  if (!dims_ok(rows, heads, dim) || rdim == 0 || rdim > dim || dim % 2 != 0 || rdim % 2 != 0) return kInvalidArgument;
+  if (!holds(a, 0, rows * heads * dim * 4)) return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_rope(static_cast<float*>(const_cast<void*>(a.buf[0])), rows, heads, dim, rdim, a.sc[4], float_of_bits(a.sc[5]),
+                  a.stream);
+}
+
+// quantize_q8 / quantize_q4: buffers In (fp32 rows x cols), codes, scale; scalars rows, cols (backend.hpp:283-298).
+template <int KIND>
+int k_quantize_rows(const Args& a) {
+  if (!shape(a, 3, 2)) return kInvalidArgument;
+  const uint64_t rows = a.sc[0], cols = a.sc[1];
+  if (!dims_ok(rows, cols, 1) || cols % (KIND == 0 ? 4 : 8) != 0 || !holds(a, 0, rows * cols * 4) ||
+      !holds(a, 1, KIND == 0 ? rows * cols : rows * cols / 2) || !holds(a, 2, rows * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_quantize_rows(KIND, static_cast<const float*>(a.buf[0]), const_cast<void*>(a.buf[1]),
+                           static_cast<float*>(const_cast<void*>(a.buf[2])), rows, cols, a.stream);
+}
+
 // cast_f32_f16: buffers In (fp32), Out (fp16); scalar n, even (backend.hpp:334-336).
 int k_cast_f16(const Args& a) {
   if (!shape(a, 2, 1)) return kInvalidArgument;
@@ -851,6 +875,9 @@ const Entry kTable[] = {
     {"attention_fp8_split", k_attention_quant_split<2>},
     {"attention_combine", k_attention_combine},
     {"mrope", k_mrope},
+    {"rope", k_rope},
+    {"quantize_q8", k_quantize_rows<0>},
+    {"quantize_q4", k_quantize_rows<1>},
     {"cast_f32_f16", k_cast_f16},
     {"delta_step_heads", k_delta_step_heads},
     {"embedding_f32", k_embedding<0>},

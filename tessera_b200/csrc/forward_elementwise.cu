@@ -152,6 +152,59 @@ __global__ void mrope_kernel(float* __restrict__ io, const unsigned long long* _
   base[j + pairs] = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, c));
 }
 
+// rope: the same rotation with one position per row, pos_base + r (RopeRef, src/core/numerics/attention.cpp:11-43)
+__global__ void rope_kernel(float* __restrict__ io, size_t heads, size_t head_dim, size_t rope_dim, unsigned long long pos_base,
+                            double theta, size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t pairs = rope_dim / 2;
+  const size_t j = i % pairs, rh = i / pairs, r = rh / heads;
+  const double angle = static_cast<double>(pos_base + r) * pow(theta, -2.0 * static_cast<double>(j) / static_cast<double>(rope_dim));
+  const float c = static_cast<float>(cos(angle)), sn = static_cast<float>(sin(angle));
+  float* base = io + rh * head_dim;
+  const float x1 = base[j], x2 = base[j + pairs];
+  base[j] = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
+  base[j + pairs] = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, c));
+}
+
+// quantize_q8 / quantize_q4: one CTA per row; scale = amax / LIMIT (1 for a zero row), codes
+// round-half-away(x / scale) clamped to +-LIMIT; int8 bytes, or nibbles with element 2i in the low half
+// (QuantizeQ8Ref, QuantizeQ4Ref, src/core/numerics/quant.cpp:123-181).  Bit-equal: max is exact in any order.
+template <int LIMIT>
+__global__ void __launch_bounds__(256)
+quantize_rows_kernel(const float* __restrict__ in, unsigned char* __restrict__ out, float* __restrict__ scale, int cols) {
+  __shared__ float red[8];
+  const float* row = in + static_cast<size_t>(blockIdx.x) * cols;
+  float amax = 0.0f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) amax = fmaxf(amax, fabsf(row[c]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+  const float s = amax > 0.0f ? __fdiv_rn(amax, static_cast<float>(LIMIT)) : 1.0f;
+  if (threadIdx.x == 0) scale[blockIdx.x] = s;
+  auto code = [&](int c) {
+    const float q = fminf(fmaxf(roundf(__fdiv_rn(row[c], s)), -static_cast<float>(LIMIT)), static_cast<float>(LIMIT));
+    return static_cast<unsigned>(static_cast<int>(q));
+  };
+  if (LIMIT == 127) {  // four bytes per thread and trip
+    uint32_t* o = reinterpret_cast<uint32_t*>(out + static_cast<size_t>(blockIdx.x) * cols);
+    for (int c = threadIdx.x * 4; c < cols; c += blockDim.x * 4)
+      o[c / 4] = (code(c) & 0xFFu) | ((code(c + 1) & 0xFFu) << 8) | ((code(c + 2) & 0xFFu) << 16) | ((code(c + 3) & 0xFFu) << 24);
+  } else {  // eight nibbles
+    uint32_t* o = reinterpret_cast<uint32_t*>(out + static_cast<size_t>(blockIdx.x) * cols / 2);
+    for (int c = threadIdx.x * 8; c < cols; c += blockDim.x * 8) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) word |= (code(c + e) & 0xFu) << (4 * e);
+      o[c / 8] = word;
+    }
+  }
+}
+
 // fp32 -> binary16, round to nearest even, two per 32-bit word (backend.hpp:334-336)
 __global__ void cast_f32_f16_kernel(const float* __restrict__ in, __half* __restrict__ out, size_t n) {
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -388,6 +441,30 @@ int tsr_mrope(float* io, const uint64_t* pos, uint64_t rows, uint64_t heads, uin
   mrope_kernel<<<blocks_of(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       io, reinterpret_cast<const unsigned long long*>(pos), heads, head_dim, rope_dim, static_cast<double>(theta), sec_t,
       sec_h, total);
+  return check_launch();
+}
+
+int tsr_rope(float* io, uint64_t rows, uint64_t heads, uint64_t head_dim, uint64_t rope_dim, uint64_t pos_base, float theta,
+             void* stream) {
+  if (!io || !fits31(rows) || !fits31(heads) || !fits31(head_dim) || rope_dim == 0 || rope_dim > head_dim || rope_dim % 2 != 0 ||
+      !(theta > 0.0f))
+    return kInvalidArgument;
+  const size_t total = rows * heads * (rope_dim / 2);
+  rope_kernel<<<blocks_of(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(io, heads, head_dim, rope_dim, pos_base,
+                                                                             static_cast<double>(theta), total);
+  return check_launch();
+}
+
+int tsr_quantize_rows(int kind, const float* in, void* out, float* scale, uint64_t rows, uint64_t cols, void* stream) {
+  if (!in || !out || !scale || !fits31(rows) || !fits31(cols) || (kind != 0 && kind != 1) || cols % (kind == 0 ? 4 : 8) != 0)
+    return kInvalidArgument;
+  auto st = static_cast<cudaStream_t>(stream);
+  if (kind == 0)
+    quantize_rows_kernel<127><<<static_cast<unsigned>(rows), 256, 0, st>>>(in, static_cast<unsigned char*>(out), scale,
+                                                                          static_cast<int>(cols));
+  else
+    quantize_rows_kernel<7><<<static_cast<unsigned>(rows), 256, 0, st>>>(in, static_cast<unsigned char*>(out), scale,
+                                                                        static_cast<int>(cols));
   return check_launch();
 }
 

@@ -1,7 +1,7 @@
 """Generates tests/golden/attention_golden.npz from the reference's own host functions AttentionRef,
-AttentionRefF16, AttentionQ8Ref, AttentionQ4Ref and AttentionFp8Ref (src/core/numerics/attention.cpp of the
-reference, reached through oracle/_ref/libtessera_ref.so, which oracle/Makefile builds from the reference
-checkout).  Run from the repository root where the reference checkout is available:
+AttentionRefF16, AttentionQ8Ref, AttentionQ4Ref, AttentionFp8Ref and RopeRef (src/core/numerics/attention.cpp of
+the reference) and the cache writers QuantizeQ8Ref and QuantizeQ4Ref (src/core/numerics/quant.cpp), reached through
+oracle/_ref/libtessera_ref.so, which oracle/Makefile builds from the reference checkout.  Run from the repository root where the reference checkout is available:
 
     python tests/golden/make_attention_golden.py
 
@@ -55,6 +55,16 @@ def main() -> None:
                 continue  # only AttentionRef takes the flag
             out[f"out_{tag}_{si}"] = ref.attention(fmt, out["q"], out["k_" + tag], out["v_" + tag], m, n, heads, kv_heads,
                                                    head_dim, q_base, window, bool(causal), out["k_scale"], out["v_scale"])
+    # rope: three rows from position 1021 on, rope_dim 48 of head_dim 64
+    out["rope_io"] = g.standard_normal(3 * 2 * 64).astype(np.float32)
+    out["rope_out"] = ref.rope(out["rope_io"], 3, 2, 64, 48, 1021, 1e6)
+    # the int8 / 4-bit cache writers: ties (x / scale exactly .5), a zero row, values beyond the clamp cannot occur
+    x = (g.standard_normal((5, 256)) * np.float32([[1.0], [1e-3], [50.0], [0.0], [1.0]])).astype(np.float32)
+    x[4, :] = np.round(x[4, :] * 4) / 4
+    x[4, 0] = 127.0 / 4  # amax: scale 0.25, so the row's values are exact multiples of the scale or ties
+    out["kvq_in"] = x
+    out["kvq8_codes"], out["kvq8_scale"] = ref.quantize_rows(0, x)
+    out["kvq4_codes"], out["kvq4_scale"] = ref.quantize_rows(1, x)
     path = os.path.join(ROOT, "tests", "golden", "attention_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -154,3 +154,67 @@ def test_rejects_what_it_does_not_serve(backend):
             run(backend, name, buffers, scalars)
         assert e.value.code == code, name
     backend.Synchronize()
+
+
+def bits(x):
+    return int(np.float32(x).view(np.uint32))
+
+
+def test_rope_against_golden_and_oracle(backend, oracle):
+    """The angle is formed in double precision on both sides; the device's double sine and cosine may differ from
+    the host's in the last bit, which shows as one ulp of an fp32 factor."""
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attention_golden.npz"))
+    buf = backend.upload(g["rope_io"])
+    run(backend, "rope", [buf], [3, 2, 64, 48, 1021, bits(1e6)])
+    got = backend.download(buf, np.float32, g["rope_io"].size)
+    assert np.all(np.abs(got - g["rope_out"]) <= 3e-7 * (np.abs(g["rope_out"]) + np.abs(g["rope_io"])))
+    untouched = np.arange(got.size) % 64 >= 48
+    assert np.array_equal(got[untouched], g["rope_io"][untouched])
+    rng = np.random.default_rng(41)
+    rows, heads, dim, rdim = 5, 24, 256, 64
+    io = rng.standard_normal(rows * heads * dim).astype(np.float32)
+    buf = backend.upload(io)
+    run(backend, "rope", [buf], [rows, heads, dim, rdim, 100000, bits(1e7)])
+    want = oracle.rope(io, rows, heads, dim, rdim, 100000, float(np.float32(1e7)))
+    assert np.all(np.abs(backend.download(buf, np.float32, io.size) - want) <= 3e-7 * (np.abs(want) + np.abs(io)))
+
+
+@pytest.mark.parametrize("kind,name", [(0, "quantize_q8"), (1, "quantize_q4")])
+def test_cache_writers_are_bit_equal(backend, oracle, kind, name):
+    """quantize_q8 / quantize_q4 (the int8 / 4-bit cache rows): golden cases with ties and a zero row, then
+    a cache-sized row; the row maximum is exact in any order, so codes and scales are bit-equal."""
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attention_golden.npz"))
+    tag = "kvq8" if kind == 0 else "kvq4"
+    rng = np.random.default_rng(43 + kind)
+    big = (rng.standard_normal((7, 1024)) * 3).astype(np.float32)
+    for x, want in ((g["kvq_in"], (g[tag + "_codes"], g[tag + "_scale"])), (big, oracle.quantize_rows(kind, big))):
+        rows, cols = x.shape
+        nbytes = rows * cols if kind == 0 else rows * cols // 2
+        codes, scale = backend.AllocateBuffer(nbytes), backend.AllocateBuffer(rows * 4)
+        run(backend, name, [backend.upload(x), codes, scale], [rows, cols])
+        assert np.array_equal(backend.download(codes, np.uint8, nbytes).reshape(want[0].shape), want[0])
+        assert np.array_equal(backend.download(scale, np.float32, rows), want[1])
+    buf = backend.AllocateBuffer(4096)
+    with pytest.raises(capi.StatusError):
+        run(backend, name, [buf, buf, buf], [1, 1020 if kind == 1 else 1022])  # cols not a multiple of 8 / 4
+    backend.Synchronize()
+
+
+def test_written_cache_feeds_attention(backend, oracle):
+    """quantize_q8 rows written by the device, read back by attention_q8: the pair the int8 cache path runs."""
+    rng = np.random.default_rng(47)
+    n, heads, kv_heads, head_dim = 300, 8, 2, 128
+    row = kv_heads * head_dim
+    kf, vf = (rng.standard_normal((n, row)).astype(np.float32) for _ in range(2))
+    q = rng.standard_normal((1, heads * head_dim)).astype(np.float32)
+    bufs = []
+    for x in (kf, vf):
+        codes, scale = backend.AllocateBuffer(n * row), backend.AllocateBuffer(n * 4)
+        run(backend, "quantize_q8", [backend.upload(x), codes, scale], [n, row])
+        bufs += [codes, scale]
+    out = backend.AllocateBuffer(heads * head_dim * 4)
+    run(backend, "attention_q8", [backend.upload(q), bufs[0], bufs[2], bufs[1], bufs[3], out],
+        [1, n, heads, kv_heads, head_dim, n - 1, 0, 0, 0])
+    (kc, ks), (vc, vs) = oracle.quantize_rows(0, kf), oracle.quantize_rows(0, vf)
+    want = oracle.attention(2, q, kc, vc, 1, n, heads, kv_heads, head_dim, n - 1, 0, True, ks, vs)
+    assert near(backend.download(out, np.float32, heads * head_dim).reshape(1, -1), want)

@@ -223,3 +223,14 @@ def test_attention_matches_golden(oracle):
             assert np.array_equal(y, g[key]), key
             checked += 1
     assert checked == 16
+
+
+def test_rope_and_cache_writers_match_golden(oracle):
+    """RopeRef (src/core/numerics/attention.cpp:11-43) and QuantizeQ8Ref / QuantizeQ4Ref (quant.cpp:123-181)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attention_golden.npz"))
+    assert np.array_equal(oracle.rope(g["rope_io"], 3, 2, 64, 48, 1021, 1e6), g["rope_out"])
+    for kind, tag in ((0, "kvq8"), (1, "kvq4")):
+        codes, scale = oracle.quantize_rows(kind, g["kvq_in"])
+        assert np.array_equal(codes, g[tag + "_codes"]) and np.array_equal(scale, g[tag + "_scale"])
+    assert g["kvq8_scale"][3] == 1.0 and not g["kvq8_codes"][3].any()  # the zero row
