@@ -256,6 +256,7 @@ def qgemv_table(stream, hbm_peak, only=None):
     shapes = [(17408, 5120), (5120, 5120), (5120, 17408)]
     cases = [("q4k", 1, 17408, 5120), ("q4k", 1, 17408, 5120, 2), ("q6k", 1, 17408, 5120)]
     cases += [(f, m, n, k) for f in ("mxfp4", "fp8", "w4a8") for (n, k) in shapes for m in (1, 4, 16)]
+    cases += [("bf16", 1, 17408, 5120), ("f32", 1, 256, 2048)]  # a bf16 checkpoint's projection; a router gate
     if only is not None:
         cases = [only]
     rows, cache = [], {}
@@ -281,6 +282,9 @@ def qgemv_table(stream, hbm_peak, only=None):
                 host = synth.q6k_weights(n, k, seed=11)
             elif fmt in ("mxfp4", "w4a8"):
                 host = synth.mxfp4_weights(n, k, seed=11)
+            elif fmt in ("bf16", "f32"):
+                dense = np.random.default_rng(11).standard_normal((n, k)).astype(np.float32) * 0.05
+                host = ((dense.view(np.uint32) >> 16).astype(np.uint16) if fmt == "bf16" else dense).reshape(-1).view(np.uint8)
             else:
                 host, scale = synth.fp8_weights(n, k, seed=11)
                 scale = torch.from_numpy(scale).cuda()
@@ -311,6 +315,8 @@ def qgemv_table(stream, hbm_peak, only=None):
                 rc = lib.tsr_gemm_q4k(pa, w, pc, m, n, k, 1, st)
             elif fmt == "q6k":
                 rc = lib.tsr_gemm_q6k(pa, w, pc, m, n, k, 1, st)
+            elif fmt in ("bf16", "f32"):
+                rc = lib.tsr_gemm_dense(1 if fmt == "bf16" else 0, pa, w, pc, m, n, k, st)
             elif fmt == "mxfp4":
                 rc = lib.tsr_gemm_mxfp4(pa, w, pc, m, n, k, st)
             elif fmt == "w4a8":
@@ -986,7 +992,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default=None, metavar="FMT:M:N:K[:G]",
-                    help="time one projection (q4k, q6k, mxfp4, fp8, w4a8; `moe` for the routed experts of one token, `delta` for the delta-rule state step, `attn:f32|f16|q8|fp8[:KEYS]` for one token's attention over the cache) "
+                    help="time one projection (q4k, q6k, mxfp4, fp8, w4a8, bf16, f32; `moe` for the routed experts of one token, `delta` for the delta-rule state step, `attn:f32|f16|q8|fp8[:KEYS]` for one token's attention over the cache) "
                          "instead of the decode step, e.g. "
                          "q4k:1:17408:5120; with G (q4k, q6k): G weight tensors of that shape in one merged launch\n"
                          "that picks its own split of k")

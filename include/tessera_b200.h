@@ -248,6 +248,10 @@ int tsr_embedding(int kind, const uint32_t* ids, const void* table, float* out, 
 /* mrope: rows x heads x head_dim rotated in place; pos = rows x (t, h, w) u64 (backend.hpp:378-385; MropeRef) */
 int tsr_mrope(float* io, const uint64_t* pos, uint64_t rows, uint64_t heads, uint64_t head_dim, uint64_t rope_dim,
               float theta, uint64_t sec_t, uint64_t sec_h, uint64_t sec_w, void* stream);
+/* gemm_f32, gemm_f32_batched (bf16 = 0) and gemm_bf16, gemm_bf16_batched, gemm_bf16_wmma, gemm_bf16_rows (bf16 = 1):
+ * C (m x n) = A (m x k, fp32) times W^T, W n x k fp32 or bf16, fp32 multiply-adds (backend.hpp:180-190; GemmF32Ref,
+ * GemmBf16Ref, src/core/numerics/gemm.cpp:205-252) */
+int tsr_gemm_dense(int bf16, const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k, void* stream);
 /* rope: rows x heads x head_dim fp32 rotated in place, NeoX pairing over rope_dim, row r at position pos_base + r
  * (backend.hpp:162-166; RopeRef, src/core/numerics/attention.cpp:11-43) */
 int tsr_rope(float* io, uint64_t rows, uint64_t heads, uint64_t head_dim, uint64_t rope_dim, uint64_t pos_base, float theta,

@@ -563,6 +563,23 @@ int orc_mrope(float* io, const uint64_t* pos, size_t rows, size_t heads, size_t 
   return 0;
 }
 
+/* GemmF32Ref / GemmBf16Ref, src/core/numerics/gemm.cpp:205-252: c[i][j] = fma chain over t of a[i][t] and w[j][t]
+ * (bf16 weights widened to fp32) */
+int orc_gemm_dense(int bf16, const float* a, const void* w, float* c, size_t m, size_t n, size_t k) {
+  if (m == 0 || n == 0 || k == 0) return -2;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (size_t i = 0; i < m; ++i)
+    for (size_t j = 0; j < n; ++j) {
+      float acc = 0.0f;
+      for (size_t t = 0; t < k; ++t) {
+        const float wf = bf16 ? orc_bf16_to_float(((const uint16_t*)w)[j * k + t]) : ((const float*)w)[j * k + t];
+        acc = fmaf(a[i * k + t], wf, acc);
+      }
+      c[i * n + j] = acc;
+    }
+  return 0;
+}
+
 /* RopeRef, src/core/numerics/attention.cpp:11-43: row r at position pos_base + r, NeoX pairs (j, j + rope_dim / 2) */
 int orc_rope(float* io, size_t rows, size_t heads, size_t head_dim, size_t rope_dim, uint64_t pos_base, double theta) {
   if (rows == 0 || heads == 0 || head_dim == 0 || rope_dim == 0 || rope_dim > head_dim || (rope_dim % 2) != 0 || !(theta > 0.0))

@@ -92,6 +92,7 @@ int orc_conv1d_state(const float* qkv, const float* w, float* hist, float* q, fl
                      size_t conv_dim, size_t width, size_t key_dim, size_t qkv_offset, size_t rows, size_t hist_stride);
 int orc_top_k_rows(const float* logits, uint32_t* ids, float* vals, size_t rows, size_t vocab, size_t top_k, size_t row_base);
 int orc_conv1d_step(const float* x, const float* w, float* y, size_t channels, size_t width);  /* conv.cpp Conv1dStepRef */
+int orc_gemm_dense(int bf16, const float* a, const void* w, float* c, size_t m, size_t n, size_t k); /* gemm.cpp GemmF32Ref (0), GemmBf16Ref (1) */
 int orc_rope(float* io, size_t rows, size_t heads, size_t head_dim, size_t rope_dim, uint64_t pos_base, double theta); /* attention.cpp RopeRef */
 int orc_quantize_rows(int kind, const float* in, uint8_t* out, float* scale, size_t rows, size_t cols); /* quant.cpp QuantizeQ8Ref (0), QuantizeQ4Ref (1) */
 /* attention.cpp AttentionRef and its cache-decoding wrappers; kv_format 0 fp32, 1 fp16, 2 int8, 3 4-bit, 4 FP8 */

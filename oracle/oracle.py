@@ -240,6 +240,15 @@ class Oracle:
         assert fn(_ptr(io), _ptr(pos), rows, heads, head_dim, rope_dim, sec_t, sec_h, sec_w, theta) == 0
         return io
 
+    def gemm_dense(self, bf16, a, w, m, n, k):
+        """w: fp32 (n x k) or bf16 bit patterns as uint16 (n x k)."""
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        w = np.ascontiguousarray(w)
+        c = np.empty((m, n), dtype=np.float32)
+        fn = self._fn("gemm_dense", C.c_int, [C.c_int, _p, _p, _p, _sz, _sz, _sz])
+        assert fn(1 if bf16 else 0, _ptr(a), _ptr(w), _ptr(c), m, n, k) == 0
+        return c
+
     def rope(self, io, rows, heads, head_dim, rope_dim, pos_base, theta):
         io = np.ascontiguousarray(io, dtype=np.float32).copy()
         fn = self._fn("rope", C.c_int, [_p, _sz, _sz, _sz, _sz, C.c_uint64, C.c_double])

@@ -151,6 +151,10 @@ int ref_delta_step_heads(float* s, const float* k, const float* v, const float* 
 int ref_conv1d_step(const float* x, const float* w, float* y, std::size_t channels, std::size_t width) {
   return Code(tc::Conv1dStepRef({x, channels * width}, {w, channels * width}, {y, channels}, channels, width));
 }
+int ref_gemm_dense(int bf16, const float* a, const void* w, float* c, std::size_t m, std::size_t n, std::size_t k) {
+  if (bf16) return Code(tc::GemmBf16Ref({a, m * k}, {static_cast<const std::byte*>(w), n * k * 2}, {c, m * n}, m, n, k));
+  return Code(tc::GemmF32Ref({a, m * k}, {static_cast<const float*>(w), n * k}, {c, m * n}, m, n, k));
+}
 int ref_rope(float* io, std::size_t rows, std::size_t heads, std::size_t head_dim, std::size_t rope_dim, std::uint64_t pos_base,
              double theta) {
   return Code(tc::RopeRef({io, rows * heads * head_dim}, rows, heads, head_dim, rope_dim, pos_base, theta));

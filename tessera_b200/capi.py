@@ -102,6 +102,7 @@ SIGNATURES = {
     "tsr_sigmoid_gate": (C.c_int, [_vp, _vp, _vp, _u64, _vp]),
     "tsr_conv1d_state": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64, _u64, _u64, _vp]),
     "tsr_top_k_rows": (C.c_int, [_vp, _vp, _vp, _u64, _u64, _u64, _u64, _vp]),
+    "tsr_gemm_dense": (C.c_int, [C.c_int, _vp, _vp, _vp, _u64, _u64, _u64, _vp]),
     "tsr_rope": (C.c_int, [_vp, _u64, _u64, _u64, _u64, _u64, C.c_float, _vp]),
     "tsr_quantize_rows": (C.c_int, [C.c_int, _vp, _vp, _vp, _u64, _u64, _vp]),
     "tsr_attention": (C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _vp] + [_u64] * 9 + [_vp]),

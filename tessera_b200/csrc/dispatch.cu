@@ -481,6 +481,18 @@ int k_mrope(const Args& a) {
                    rdim, float_of_bits(a.sc[4]), a.sc[5], a.sc[6], a.sc[7], a.stream);
 }
 
+// gemm_f32* / gemm_bf16*: buffers A, W, C; scalars m, n, k (backend.hpp:180-190).
+template <int BF16>
+int k_gemm_dense(const Args& a) {
+  if (!shape(a, 3, 3)) return kInvalidArgument;
+  const uint64_t m = a.sc[0], n = a.sc[1], k = a.sc[2];
+  if (!dims_ok(m, n, k) || !holds(a, 0, m * k * 4) || !holds(a, 1, n * k * (BF16 ? 2 : 4)) || !holds(a, 2, m * n * 4))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  return tsr_gemm_dense(BF16, static_cast<const float*>(a.buf[0]), a.buf[1], static_cast<float*>(const_cast<void*>(a.buf[2])), m, n,
+                        k, a.stream);
+}
+
 // rope: buffer io; scalars rows, heads, head_dim, rope_dim, pos_base, theta bits (backend.hpp:162-166).
 int k_rope(const Args& a) {
   if (!shape(a, 1, 6)) return kInvalidArgument;
@@ -876,6 +888,12 @@ const Entry kTable[] = {
     {"attention_combine", k_attention_combine},
     {"mrope", k_mrope},
     {"rope", k_rope},
+    {"gemm_f32", k_gemm_dense<0>},
+    {"gemm_f32_batched", k_gemm_dense<0>},
+    {"gemm_bf16", k_gemm_dense<1>},
+    {"gemm_bf16_batched", k_gemm_dense<1>},
+    {"gemm_bf16_wmma", k_gemm_dense<1>},
+    {"gemm_bf16_rows", k_gemm_dense<1>},
     {"quantize_q8", k_quantize_rows<0>},
     {"quantize_q4", k_quantize_rows<1>},
     {"cast_f32_f16", k_cast_f16},

@@ -198,7 +198,7 @@ int main() {
 
   auto zero = b.AllocateBuffer(0, MemoryKind::Device);
   Report("AllocateBuffer(0) is InvalidArgument", !zero && zero.error() == StatusCode::InvalidArgument);
-  auto miss = b.LoadKernel("attention", {});
+  auto miss = b.LoadKernel("layernorm", {});
   Report("unknown id is UnsupportedFeature", !miss && miss.error() == StatusCode::UnsupportedFeature);
   const std::byte code[1] = {std::byte{1}};
   auto module = b.LoadKernel("gemm_q4k_vec", code);

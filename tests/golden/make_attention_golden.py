@@ -1,6 +1,7 @@
 """Generates tests/golden/attention_golden.npz from the reference's own host functions AttentionRef,
 AttentionRefF16, AttentionQ8Ref, AttentionQ4Ref, AttentionFp8Ref and RopeRef (src/core/numerics/attention.cpp of
-the reference) and the cache writers QuantizeQ8Ref and QuantizeQ4Ref (src/core/numerics/quant.cpp), reached through
+the reference) the cache writers QuantizeQ8Ref and QuantizeQ4Ref (src/core/numerics/quant.cpp) and the unquantised projections
+GemmF32Ref and GemmBf16Ref (src/core/numerics/gemm.cpp), reached through
 oracle/_ref/libtessera_ref.so, which oracle/Makefile builds from the reference checkout.  Run from the repository root where the reference checkout is available:
 
     python tests/golden/make_attention_golden.py
@@ -65,6 +66,12 @@ def main() -> None:
     out["kvq_in"] = x
     out["kvq8_codes"], out["kvq8_scale"] = ref.quantize_rows(0, x)
     out["kvq4_codes"], out["kvq4_scale"] = ref.quantize_rows(1, x)
+    # the unquantised projections: fp32 and bf16 weights (bit patterns), k not a multiple of the vector width
+    out["dense_a"] = g.standard_normal((3, 75)).astype(np.float32)
+    out["dense_w32"] = g.standard_normal((9, 75)).astype(np.float32)
+    out["dense_w16"] = (g.standard_normal((9, 75)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    out["dense_c32"] = ref.gemm_dense(False, out["dense_a"], out["dense_w32"], 3, 9, 75)
+    out["dense_c16"] = ref.gemm_dense(True, out["dense_a"], out["dense_w16"], 3, 9, 75)
     path = os.path.join(ROOT, "tests", "golden", "attention_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -234,3 +234,11 @@ def test_rope_and_cache_writers_match_golden(oracle):
         codes, scale = oracle.quantize_rows(kind, g["kvq_in"])
         assert np.array_equal(codes, g[tag + "_codes"]) and np.array_equal(scale, g[tag + "_scale"])
     assert g["kvq8_scale"][3] == 1.0 and not g["kvq8_codes"][3].any()  # the zero row
+
+
+def test_dense_projections_match_golden(oracle):
+    """GemmF32Ref / GemmBf16Ref (src/core/numerics/gemm.cpp:205-252 of the reference)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attention_golden.npz"))
+    assert np.array_equal(oracle.gemm_dense(False, g["dense_a"], g["dense_w32"], 3, 9, 75), g["dense_c32"])
+    assert np.array_equal(oracle.gemm_dense(True, g["dense_a"], g["dense_w16"], 3, 9, 75), g["dense_c16"])
