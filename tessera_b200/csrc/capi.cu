@@ -391,6 +391,7 @@ int tsr_copy_d2d(tsr_context* ctx, const void* src, size_t src_offset, void* dst
   if (!ctx || (!dst && bytes) || (!src && bytes)) return tsr::kInvalidArgument;
   if (bytes == 0) return tsr::kOk;
   if (int s = ctx->select()) return s;
+  if (ctx->deferred && bytes <= tsr::kQueuedCopyLimit) return tsr::queue_copy(ctx, src, src_offset, dst, dst_offset, bytes);
   if (int s = tsr::flush_pending(ctx)) return s;
   const cudaError_t e = cudaMemcpyAsync(static_cast<unsigned char*>(dst) + dst_offset,
                                         static_cast<const unsigned char*>(src) + src_offset, bytes,

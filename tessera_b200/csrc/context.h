@@ -87,6 +87,9 @@ struct tsr_context {
 namespace tsr {
 // Issues everything in ctx->pending on the context's stream (dispatch.cu).
 int flush_pending(tsr_context* ctx);
+// Device-to-device copies up to this size wait in the queue with the launches around them (dispatch.cu).
+constexpr size_t kQueuedCopyLimit = 1u << 20;
+int queue_copy(tsr_context* ctx, const void* src, size_t src_offset, void* dst, size_t dst_offset, size_t bytes);
 // The tail parameters / device of a communicator (tp.cu).
 int tp_tail_of(const tsr_tp_comm* comm, TpTail* out);
 int tp_device_of(const tsr_tp_comm* comm);

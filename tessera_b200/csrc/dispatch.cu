@@ -683,6 +683,39 @@ int k_fill(const Args& a) {
                   static_cast<int32_t>(a.sc[0]), n, a.stream);
 }
 
+// copy_d2d: buffers src, dst; scalars src_offset, dst_offset, bytes.  The queued form of a small device-to-device
+// copy (the key / value rows a token appends to its cache, src/core/decode_internal.hpp:520-640 of the reference):
+// a copy that flushed the queue would cut a token's launches into one piece per attention layer.
+__global__ void copy_bytes_kernel(const unsigned char* __restrict__ src, unsigned char* __restrict__ dst, size_t bytes,
+                                  int wide) {
+  const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x, threads = static_cast<size_t>(gridDim.x) * blockDim.x;
+  if (wide) {
+    for (size_t i = tid; i < bytes / 16; i += threads) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  } else {
+    for (size_t i = tid; i < bytes; i += threads) dst[i] = src[i];
+  }
+}
+
+int k_copy_d2d(const Args& a) {
+  if (!shape(a, 2, 3)) return kInvalidArgument;
+  const uint64_t so = a.sc[0], d_o = a.sc[1], bytes = a.sc[2];
+  if (bytes == 0 || bytes > kQueuedCopyLimit || so > (1ull << 48) || d_o > (1ull << 48) || !holds(a, 0, so + bytes) ||
+      !holds(a, 1, d_o + bytes))
+    return kInvalidArgument;
+  if (a.dry) return kOk;
+  const unsigned char* src = static_cast<const unsigned char*>(a.buf[0]) + so;
+  unsigned char* dst = static_cast<unsigned char*>(const_cast<void*>(a.buf[1])) + d_o;
+  const bool wide = bytes % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+  // what it writes is registered, so that a launch which reads these bytes as weights ahead of its wait is held back
+  const void* out = dst;
+  const size_t out_bytes = bytes;
+  pdl_allowed_ranges(a.stream, nullptr, nullptr, 0, &out, &out_bytes, 1);
+  const size_t items = wide ? bytes / 16 : bytes;
+  const unsigned blocks = static_cast<unsigned>(items / 256 + 1 < 592 ? items / 256 + 1 : 592);
+  copy_bytes_kernel<<<blocks, 256, 0, a.stream>>>(src, dst, bytes, wide ? 1 : 0);
+  return check_launch();
+}
+
 // Sum over tensor-parallel ranks of an [m][n] fp32 matrix in place, on the communicator
 // bound to the context (tsr_tp_bind).  With one rank (or none bound) it is the identity.
 int tp_sum_in_place(const Args& a, float* data, uint64_t m, uint64_t n) {
@@ -886,6 +919,7 @@ const Entry kTable[] = {
     {"attention_q4_split", k_attention_quant_split<1>},
     {"attention_fp8_split", k_attention_quant_split<2>},
     {"attention_combine", k_attention_combine},
+    {"copy_d2d", k_copy_d2d},
     {"mrope", k_mrope},
     {"rope", k_rope},
     {"gemm_f32", k_gemm_dense<0>},
@@ -1257,6 +1291,23 @@ int flush_pending(tsr_context* ctx) {
   return rc;
 }
 
+}  // namespace tsr
+
+namespace tsr {
+// A device-to-device copy of at most kQueuedCopyLimit bytes joins the deferred queue as a "copy_d2d" launch.
+int queue_copy(tsr_context* ctx, const void* src, size_t src_offset, void* dst, size_t dst_offset, size_t bytes) {
+  static const int id = tsr_kernel_lookup("copy_d2d");
+  PendingLaunch op{};
+  op.kernel = id;
+  op.grid_y = 1;
+  op.nbuf = 2;
+  op.nsc = 3;
+  op.buf[0] = src, op.buf[1] = dst;
+  op.bytes[0] = src_offset + bytes, op.bytes[1] = dst_offset + bytes;
+  op.sc[0] = src_offset, op.sc[1] = dst_offset, op.sc[2] = bytes;
+  ctx->pending.push_back(op);
+  return kOk;
+}
 }  // namespace tsr
 
 extern "C" {
