@@ -203,3 +203,89 @@ def test_full_attention_layer_through_the_deferred_queue(backend, oracle, cache)
             dev.check()
     finally:
         backend.SetDeferred(0)
+
+
+# ---- a linear-attention (gated delta rule) layer, src/models/qwen3_5/trunk.cpp:715-785 of the reference
+K_HEADS, V_HEADS, HEAD_K, HEAD_V, WIDTH = 4, 8, 128, 128, 4
+KEY_DIM, VALUE_DIM = K_HEADS * HEAD_K, V_HEADS * HEAD_V
+CONV_DIM, FACTOR = 2 * KEY_DIM + VALUE_DIM, V_HEADS // K_HEADS
+
+
+class LinearLayer:
+    def __init__(self, oracle, seed):
+        g = np.random.default_rng(seed)
+        self.x = g.standard_normal(HIDDEN).astype(np.float32)
+        self.w = {name: synth.q4k_weights(n, k, seed=seed, index=i) for i, (name, n, k) in enumerate(
+            [("qkv", CONV_DIM, HIDDEN), ("z", VALUE_DIM, HIDDEN), ("out", HIDDEN, VALUE_DIM)])}
+        # the per-head gate projections are fp32 tensors (gemm_f32)
+        self.w_alpha = (g.standard_normal((V_HEADS, HIDDEN)) * 0.05).astype(np.float32)
+        self.w_beta = (g.standard_normal((V_HEADS, HIDDEN)) * 0.05).astype(np.float32)
+        self.norm = (1.0 + 0.1 * g.standard_normal(HIDDEN)).astype(np.float32)
+        self.ssm_norm = (1.0 + 0.1 * g.standard_normal(HEAD_V)).astype(np.float32)
+        self.conv_w = (g.standard_normal((CONV_DIM, WIDTH)) * 0.02).astype(np.float32)
+        self.a_log = (-np.exp(g.standard_normal(V_HEADS))).astype(np.float32)
+        self.dt = g.standard_normal(V_HEADS).astype(np.float32)
+        self.hist = g.standard_normal(CONV_DIM * (WIDTH - 1)).astype(np.float32)
+        self.state = (g.standard_normal(V_HEADS * HEAD_K * HEAD_V) * 0.1).astype(np.float32)
+        self.want = self.reference(oracle)
+
+    def reference(self, o):
+        xn = o.rmsnorm(self.x.reshape(1, -1), self.norm, EPS)
+        qkv = o.gemm_q4k(xn, self.w["qkv"], 1, CONV_DIM, HIDDEN).reshape(-1)
+        z = o.gemm_q4k(xn, self.w["z"], 1, VALUE_DIM, HIDDEN).reshape(-1)
+        beta_raw = o.gemm_dense(False, xn, self.w_beta, 1, V_HEADS, HIDDEN)
+        alpha_raw = o.gemm_dense(False, xn, self.w_alpha, 1, V_HEADS, HIDDEN)
+        alpha, beta = o.ssm_gate(self.a_log, self.dt, alpha_raw, beta_raw)
+        q, k, v, hist, _ = o.conv1d_state(qkv, self.conv_w, self.hist, CONV_DIM, WIDTH, KEY_DIM, 0, 1)
+        q = o.l2norm(q.reshape(K_HEADS, HEAD_K), 1e-6, np.float32(1.0 / np.sqrt(float(HEAD_K)))).reshape(-1)
+        k = o.l2norm(k.reshape(K_HEADS, HEAD_K), 1e-6, np.float32(1.0)).reshape(-1)
+        q_exp, k_exp = o.repeat_heads(q, V_HEADS, HEAD_K, FACTOR), o.repeat_heads(k, V_HEADS, HEAD_K, FACTOR)
+        state, core = o.delta_step_heads(self.state, k_exp, v, q_exp, alpha.reshape(-1), beta.reshape(-1), V_HEADS, HEAD_K, HEAD_V)
+        out = o.rmsnorm_gated(core.reshape(V_HEADS, HEAD_V), self.ssm_norm, z.reshape(V_HEADS, HEAD_V), EPS).reshape(-1)
+        x1 = o.add(self.x, o.gemm_q4k(out.reshape(1, -1), self.w["out"], 1, HIDDEN, VALUE_DIM).reshape(-1))
+        return dict(hist=hist, state=state, core=core, x1=x1)
+
+
+def issue_linear(backend, proj, layer, d):
+    def L(name, buffers, scalars):
+        backend.LaunchKernel(backend.LoadKernel(name), KernelLaunch(buffers=buffers, scalars=scalars))
+    L("rmsnorm", [d["x"], d["norm"], d["xn"]], [1, HIDDEN, bits(EPS)])
+    proj.ProjectBatch(Q4K, d["xn"], d["w_qkv"], d["qkv"], 1, CONV_DIM, HIDDEN)
+    proj.ProjectBatch(Q4K, d["xn"], d["w_z"], d["z"], 1, VALUE_DIM, HIDDEN)
+    L("gemm_f32", [d["xn"], d["w_beta"], d["beta_raw"]], [1, V_HEADS, HIDDEN])
+    L("gemm_f32", [d["xn"], d["w_alpha"], d["alpha_raw"]], [1, V_HEADS, HIDDEN])
+    L("ssm_gate", [d["a_log"], d["dt"], d["alpha_raw"], d["beta_raw"], d["alpha"], d["beta"]], [V_HEADS, 1])
+    L("conv1d_state", [d["qkv"], d["conv_w"], d["hist"], d["q"], d["k"], d["v"], d["hist"]], [CONV_DIM, WIDTH, KEY_DIM, 0, 1, 0])
+    L("l2norm", [d["q"], d["q"]], [K_HEADS, HEAD_K, bits(1e-6), bits(1.0 / np.sqrt(float(HEAD_K)))])
+    L("l2norm", [d["k"], d["k"]], [K_HEADS, HEAD_K, bits(1e-6), bits(1.0)])
+    L("repeat_heads", [d["q"], d["q_exp"]], [V_HEADS, HEAD_K, FACTOR, 1])
+    L("repeat_heads", [d["k"], d["k_exp"]], [V_HEADS, HEAD_K, FACTOR, 1])
+    L("delta_step_heads", [d["state"], d["k_exp"], d["v"], d["q_exp"], d["core"], d["alpha"], d["beta"]],
+      [V_HEADS, HEAD_K, HEAD_V, 1, 0, 0, 0])
+    L("rmsnorm_gated", [d["core"], d["ssm_norm"], d["z"], d["out"]], [V_HEADS, HEAD_V, bits(EPS), 0, 0])
+    proj.ProjectBatch(Q4K, d["out"], d["w_out"], d["proj"], 1, HIDDEN, VALUE_DIM)
+    L("add", [d["x"], d["proj"], d["x"]], [HIDDEN])
+
+
+@pytest.mark.parametrize("deferred", [0, 1])
+def test_linear_attention_layer(backend, oracle, deferred):
+    layer = LinearLayer(oracle, seed=600)
+    up, f = backend.upload, lambda n: backend.AllocateBuffer(n * 4)
+    d = dict(x=up(layer.x), norm=up(layer.norm), ssm_norm=up(layer.ssm_norm), conv_w=up(layer.conv_w), a_log=up(layer.a_log),
+             dt=up(layer.dt), hist=up(layer.hist), state=up(layer.state), w_alpha=up(layer.w_alpha), w_beta=up(layer.w_beta),
+             w_qkv=up(layer.w["qkv"]), w_z=up(layer.w["z"]), w_out=up(layer.w["out"]),
+             xn=f(HIDDEN), qkv=f(CONV_DIM), z=f(VALUE_DIM), beta_raw=f(V_HEADS), alpha_raw=f(V_HEADS), alpha=f(V_HEADS),
+             beta=f(V_HEADS), q=f(KEY_DIM), k=f(KEY_DIM), v=f(VALUE_DIM), q_exp=f(V_HEADS * HEAD_K), k_exp=f(V_HEADS * HEAD_K),
+             core=f(VALUE_DIM), out=f(VALUE_DIM), proj=f(HIDDEN))
+    backend.Synchronize()
+    backend.SetDeferred(deferred)
+    try:
+        issue_linear(backend, Projector(backend), layer, d)
+        backend.Synchronize()
+    finally:
+        backend.SetDeferred(0)
+    want = layer.want
+    assert rel_err(backend.download(d["hist"], np.float32, layer.hist.size), want["hist"]) < 1e-6
+    assert rel_err(backend.download(d["state"], np.float32, layer.state.size), want["state"]) < 1e-4
+    assert rel_err(backend.download(d["core"], np.float32, VALUE_DIM), want["core"]) < 1e-4
+    assert rel_err(backend.download(d["x"], np.float32, HIDDEN), want["x1"]) < 2e-3
