@@ -795,12 +795,82 @@ def gpu_arm(args):
                 proj.ProjectBatch(p.dtype, act, w, dst, 1, n, k)
             return batch, proj
 
-        def record_with_elementwise():
+        def token_mixers(keys):
+            """Buffers and launches of what sits between a layer's input projections and its output
+            projection (src/models/qwen3_5/trunk.cpp:360-455,745-775 of the reference), one decode token
+            at position keys - 1.  Full-attention layers: qgate_split, per-head rmsnorm of q and k,
+            mrope, the cache rows' append, attention over a private fp32 cache of `keys` rows,
+            sigmoid_gate.  Linear-attention layers: ssm_gate, conv1d_state, l2norm, repeat_heads,
+            delta_step_heads on a private recurrent state, rmsnorm_gated.  Returns (emit, keep)."""
+            W = workload
+            f = lambda n: backend.AllocateBuffer(n * 4)
+            load = backend.LoadKernel
+            g = np.random.default_rng(17)
+            q_dim, kv_dim = W.Q_HEADS * W.HEAD_DIM, W.KV_HEADS * W.HEAD_DIM
+            k_heads, head_k = 16, 128
+            key_dim, width = k_heads * head_k, 4
+            eps = int(np.float32(1e-6).view(np.uint32))
+            fb = lambda v: int(np.float32(v).view(np.uint32))
+            full_layers = [l for l in range(W.LAYERS) if l % W.FULL_ATTENTION_INTERVAL == W.FULL_ATTENTION_INTERVAL - 1]
+            row = (g.standard_normal((1, kv_dim)) * 0.5).astype(np.float32)
+            template = backend.upload(np.repeat(row, keys, axis=0))
+            caches = {}
+            for l in full_layers:
+                caches[l] = (backend.AllocateBuffer(keys * kv_dim * 4), backend.AllocateBuffer(keys * kv_dim * 4))
+                for c in caches[l]:
+                    backend.CopyD2D(template, 0, c, 0, c.Size())
+            states = {l: backend.upload((g.standard_normal(W.SSM_HEADS * head_k * 128) * 0.1).astype(np.float32))
+                      for l in range(W.LAYERS) if l not in caches}
+            hists = {l: backend.upload(g.standard_normal(W.SSM_QKV * (width - 1)).astype(np.float32)) for l in states}
+            backend.Synchronize()
+            template.release()
+            b = dict(q=f(q_dim), gate=f(q_dim), pos=backend.upload(np.full((1, 3), keys - 1, dtype=np.uint64)),
+                     head_w=backend.upload(np.ones(W.HEAD_DIM, dtype=np.float32)),
+                     conv_w=backend.upload((g.standard_normal((W.SSM_QKV, width)) * 0.02).astype(np.float32)),
+                     a_log=backend.upload((-np.exp(g.standard_normal(W.SSM_HEADS))).astype(np.float32)),
+                     dt=backend.upload(g.standard_normal(W.SSM_HEADS).astype(np.float32)),
+                     ssm_w=backend.upload(np.ones(128, dtype=np.float32)),
+                     alpha=f(W.SSM_HEADS), beta=f(W.SSM_HEADS), q_l=f(key_dim), k_l=f(key_dim), v_l=f(W.SSM_INNER),
+                     q_exp=f(W.SSM_HEADS * head_k), k_exp=f(W.SSM_HEADS * head_k), core=f(W.SSM_INNER))
+            kern = {n: load(n) for n in ("qgate_split", "rmsnorm", "mrope", "copy_d2d", "attention", "sigmoid_gate", "ssm_gate",
+                                         "conv1d_state", "l2norm", "repeat_heads", "delta_step_heads", "rmsnorm_gated")}
+
+            def emit(batch, layer):
+                add = lambda name, buffers, scalars: batch.add(kern[name], KernelLaunch(buffers=buffers, scalars=scalars))
+                attn = dev_act["attn"]
+                if layer in caches:
+                    kc, vc = caches[layer]
+                    add("qgate_split", [out_bufs["attn_q"], b["q"], b["gate"]], [W.Q_HEADS, W.HEAD_DIM, 1])
+                    add("rmsnorm", [b["q"], b["head_w"], b["q"]], [W.Q_HEADS, W.HEAD_DIM, eps])
+                    add("rmsnorm", [out_bufs["attn_k"], b["head_w"], out_bufs["attn_k"]], [W.KV_HEADS, W.HEAD_DIM, eps])
+                    add("mrope", [b["q"], b["pos"]], [1, W.Q_HEADS, W.HEAD_DIM, 64, fb(1e7), 11, 11, 10])
+                    add("mrope", [out_bufs["attn_k"], b["pos"]], [1, W.KV_HEADS, W.HEAD_DIM, 64, fb(1e7), 11, 11, 10])
+                    add("copy_d2d", [out_bufs["attn_k"], kc], [0, (keys - 1) * kv_dim * 4, kv_dim * 4])
+                    add("copy_d2d", [out_bufs["attn_v"], vc], [0, (keys - 1) * kv_dim * 4, kv_dim * 4])
+                    add("attention", [b["q"], kc, vc, attn], [1, keys, W.Q_HEADS, W.KV_HEADS, W.HEAD_DIM, keys - 1, 0, 0, 0, 1])
+                    add("sigmoid_gate", [attn, b["gate"], attn], [q_dim])
+                else:
+                    add("ssm_gate", [b["a_log"], b["dt"], out_bufs["ssm_alpha"], out_bufs["ssm_beta"], b["alpha"], b["beta"]],
+                        [W.SSM_HEADS, 1])
+                    add("conv1d_state", [out_bufs["attn_qkv"], b["conv_w"], hists[layer], b["q_l"], b["k_l"], b["v_l"], hists[layer]],
+                        [W.SSM_QKV, width, key_dim, 0, 1, 0])
+                    add("l2norm", [b["q_l"], b["q_l"]], [k_heads, head_k, fb(1e-6), fb(1.0 / np.sqrt(float(head_k)))])
+                    add("l2norm", [b["k_l"], b["k_l"]], [k_heads, head_k, fb(1e-6), fb(1.0)])
+                    add("repeat_heads", [b["q_l"], b["q_exp"]], [W.SSM_HEADS, head_k, W.SSM_HEADS // k_heads, 1])
+                    add("repeat_heads", [b["k_l"], b["k_exp"]], [W.SSM_HEADS, head_k, W.SSM_HEADS // k_heads, 1])
+                    add("delta_step_heads", [states[layer], b["k_exp"], b["v_l"], b["q_exp"], b["core"], b["alpha"], b["beta"]],
+                        [W.SSM_HEADS, head_k, 128, 1, 0, 0, 0])
+                    add("rmsnorm_gated", [b["core"], b["ssm_w"], out_bufs["attn_gate"], attn], [W.SSM_HEADS, 128, eps, 0, 0])
+            return emit, (caches, states, hists, b)
+
+        def record_with_elementwise(mixers=None):
             """The same projections with the elementwise steps the reference's forward queues
             around them (src/models/qwen3_5/trunk.cpp:279-322,440-470 of the reference): rmsnorm
             before the projections that read the hidden state, silu_mul between ffn_gate / ffn_up
             and ffn_down, the residual add after each row-parallel projection.  The hidden state
-            itself is not advanced (the adds write a scratch vector), so the step repeats."""
+            itself is not advanced (the adds write a scratch vector), so the step repeats.  With
+            `mixers` (token_mixers' emit) every layer also runs what lies between its input and
+            output projections: the whole forward of the token."""
             batch = LaunchBatch()
             proj = Projector(Recorder(backend, batch))
             hid = workload.HIDDEN
@@ -819,6 +889,8 @@ def gpu_arm(args):
                         normed_for = half
                 if p.name == "ffn_down":
                     batch.add(silu, KernelLaunch(buffers=[out_bufs["ffn_gate"], out_bufs["ffn_up"], dev_act["ffn"]], scalars=[k]))
+                if mixers is not None and p.name in ("attn_output", "ssm_out"):
+                    mixers(batch, p.layer)
                 if world > 1 and p.kind == workload.ROW:
                     kern = backend.LoadKernel(GemmKernelName(p.dtype) + "_allreduce")
                     batch.add(kern, KernelLaunch(buffers=[dev_act[p.act], w, dst], scalars=[1, n, k]))
@@ -889,7 +961,7 @@ def gpu_arm(args):
 
             # ---- the step with its elementwise neighbours, folded into the projection launches
             # and as launches of their own (outside the metric: it is quoted on the projections)
-            with_elementwise = None
+            with_elementwise, full_forward = None, None
             if deferred == 1 and not args.only and not args.no_elementwise:
                 full, keep_full = record_with_elementwise()
 
@@ -909,6 +981,25 @@ def gpu_arm(args):
                     with_elementwise["kernels_per_step_" + tag] = (k1 - k0) // args.steps
                     with_elementwise["ms_per_step_" + tag] = ms / args.steps
                 backend.SetDeferred(deferred)
+                if world == 1 and args.shard_of <= 1:
+                    # the whole forward of one token: the step above plus every layer's token mixer
+                    keys = 4096
+                    emit, keep_mixers = token_mixers(keys)
+                    forward, keep_forward = record_with_elementwise(mixers=emit)
+
+                    def run_forward():
+                        backend.LaunchMany(forward)
+                        backend.Flush()
+
+                    for _ in range(3):
+                        run_forward()
+                    backend.Synchronize()
+                    _, k0, _ = backend.LaunchStats()
+                    ms = timed(run_forward, args.steps)
+                    _, k1, _ = backend.LaunchStats()
+                    full_forward = {"context_keys": keys, "kv_cache": "f32", "launches_queued_per_token": len(forward),
+                                    "kernels_per_token": (k1 - k0) // args.steps, "ms_per_token": ms / args.steps,
+                                    "tok_s": args.steps / (ms * 1e-3)}
 
     value = args.steps / (ms_total * 1e-3)
     e2e_value = args.steps / (ms_e2e * 1e-3)
@@ -952,6 +1043,8 @@ def gpu_arm(args):
     }
     if with_elementwise is not None:
         line["with_elementwise"] = with_elementwise
+    if full_forward is not None:
+        line["full_forward"] = full_forward
     if parity is not None:
         line["tp_parity"] = parity
     if collective is not None:

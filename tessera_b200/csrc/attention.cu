@@ -306,7 +306,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) attention_chunk_kernel(con
 // quarters meet in order.
 __global__ void __launch_bounds__(256)
 attention_combine_kernel(const float* __restrict__ pacc, const float* __restrict__ pmax, const float* __restrict__ psum,
-                         float* __restrict__ out, int heads, int head_dim, int splits, unsigned long long row_base) {
+                         float* __restrict__ out, const float* __restrict__ gate, int heads, int head_dim, int splits,
+                         unsigned long long row_base) {
   constexpr int kHeld = 16;   // chunks a thread holds in registers: 4 * 16 = 64 chunks without a second round of loads
   __shared__ float w_s[256];  // the weights of the first 256 chunks, computed once
   __shared__ float quarter[4][64];
@@ -352,9 +353,12 @@ attention_combine_kernel(const float* __restrict__ pacc, const float* __restrict
   }
   quarter[part][col] = num;
   __syncthreads();
-  if (part == 0 && e < head_dim)
-    out[((row_base + i) * heads + h) * head_dim + e] =
-        (((quarter[0][col] + quarter[1][col]) + quarter[2][col]) + quarter[3][col]) / den_s;
+  if (part == 0 && e < head_dim) {
+    const size_t at = ((row_base + i) * heads + h) * head_dim + e;
+    const float v = (((quarter[0][col] + quarter[1][col]) + quarter[2][col]) + quarter[3][col]) / den_s;
+    // the sigmoid_gate step that follows attention in the reference's layer, when the queue merged it in
+    out[at] = gate != nullptr ? v / (1.0f + expf(-gate[at])) : v;
+  }
 }
 
 template <int KV, int D, int G>
@@ -398,10 +402,10 @@ int run_split(int kvkind, const AttnParams& p, cudaStream_t st) {
   }
 }
 
-int run_combine(const float* pacc, const float* pmax, const float* psum, float* out, uint64_t m, uint64_t heads,
-                uint64_t head_dim, uint64_t splits, uint64_t row_base, cudaStream_t st) {
+int run_combine(const float* pacc, const float* pmax, const float* psum, float* out, const float* gate, uint64_t m,
+                uint64_t heads, uint64_t head_dim, uint64_t splits, uint64_t row_base, cudaStream_t st) {
   const dim3 grid(static_cast<unsigned>(m * heads), static_cast<unsigned>((head_dim + 63) / 64));
-  attention_combine_kernel<<<grid, 256, 0, st>>>(pacc, pmax, psum, out, static_cast<int>(heads), static_cast<int>(head_dim),
+  attention_combine_kernel<<<grid, 256, 0, st>>>(pacc, pmax, psum, out, gate, static_cast<int>(heads), static_cast<int>(head_dim),
                                                  static_cast<int>(splits), row_base);
   return check_launch();
 }
@@ -422,8 +426,8 @@ int check_attention(int kvkind, const float* q, const void* k, const void* v, co
 }
 
 int run_attention(int kvkind, const float* q, const void* k, const void* v, const float* ks, const float* vs, float* out,
-                  uint64_t m, uint64_t n, uint64_t heads, uint64_t kv_heads, uint64_t head_dim, uint64_t q_base,
-                  uint64_t row_base, uint64_t window, uint64_t causal, cudaStream_t st) {
+                  const float* gate, uint64_t m, uint64_t n, uint64_t heads, uint64_t kv_heads, uint64_t head_dim,
+                  uint64_t q_base, uint64_t row_base, uint64_t window, uint64_t causal, cudaStream_t st) {
   if (!out) return kInvalidArgument;
   // as many chunks as keep a CTA busy with kAttnMinKeys keys, counted on the longest row's range
   const uint64_t span = window != 0 && window < n ? window : n;
@@ -442,7 +446,7 @@ int run_attention(int kvkind, const float* q, const void* k, const void* v, cons
   p.pmax = reinterpret_cast<float*>(scratch + acc_bytes);
   p.psum = reinterpret_cast<float*>(scratch + acc_bytes + stat_bytes);
   if (int rc = run_split(kvkind, p, st)) return rc;
-  return run_combine(p.pacc, p.pmax, p.psum, out, m, heads, head_dim, splits, row_base, st);
+  return run_combine(p.pacc, p.pmax, p.psum, out, gate, m, heads, head_dim, splits, row_base, st);
 }
 
 int kv_kind_of(int kv_format) {
@@ -457,6 +461,15 @@ int kv_kind_of(int kv_format) {
 }
 
 }  // namespace
+
+int attention_gated(int kv_format, const float* q, const void* k, const void* v, const float* k_scale, const float* v_scale,
+                    float* out, const float* gate, uint64_t m, uint64_t n, uint64_t heads, uint64_t kv_heads, uint64_t head_dim,
+                    uint64_t q_base, uint64_t row_base, uint64_t window, uint64_t causal, cudaStream_t st) {
+  const int kind = kv_kind_of(kv_format);
+  if (kind < 0) return kInvalidArgument;
+  return run_attention(kind, q, k, v, k_scale, v_scale, out, gate, m, n, heads, kv_heads, head_dim, q_base, row_base, window,
+                       causal, st);
+}
 }  // namespace tsr
 
 using namespace tsr;
@@ -466,10 +479,8 @@ extern "C" {
 int tsr_attention(int kv_format, const float* q, const void* k, const void* v, const float* k_scale, const float* v_scale,
                   float* out, uint64_t m, uint64_t n, uint64_t heads, uint64_t kv_heads, uint64_t head_dim, uint64_t q_base,
                   uint64_t row_base, uint64_t window, uint64_t causal, void* stream) {
-  const int kind = kv_kind_of(kv_format);
-  if (kind < 0) return kInvalidArgument;
-  return run_attention(kind, q, k, v, k_scale, v_scale, out, m, n, heads, kv_heads, head_dim, q_base, row_base, window, causal,
-                       static_cast<cudaStream_t>(stream));
+  return attention_gated(kv_format, q, k, v, k_scale, v_scale, out, nullptr, m, n, heads, kv_heads, head_dim, q_base, row_base,
+                         window, causal, static_cast<cudaStream_t>(stream));
 }
 
 int tsr_attention_split(int kv_format, const float* q, const void* k, const void* v, const float* k_scale,
@@ -491,7 +502,7 @@ int tsr_attention_combine(const float* pacc, const float* pmax, const float* psu
   if (!pacc || !pmax || !psum || !out || m == 0 || heads == 0 || head_dim == 0 || split == 0 || m * heads > 0x7FFFFFFFull ||
       split > 0x7FFFFFFFull || head_dim > 0x7FFFFFFFull)
     return kInvalidArgument;
-  return run_combine(pacc, pmax, psum, out, m, heads, head_dim, split, 0, static_cast<cudaStream_t>(stream));
+  return run_combine(pacc, pmax, psum, out, nullptr, m, heads, head_dim, split, 0, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -1123,6 +1123,119 @@ bool as_epilogue_add(const tsr_context* ctx, const std::vector<PendingLaunch>& q
   return true;
 }
 
+// ---- neighbouring small steps of a token that one kernel serves (launch.h: merged small steps).  Each matcher
+// checks that the launches at q[i...] are exactly the sequence the reference's layer issues on the same buffers,
+// issues the merged kernel and returns how many launches it stood for (0: not this pattern).
+
+float* fbuf(const PendingLaunch& op, int i) { return static_cast<float*>(const_cast<void*>(op.buf[i])); }
+
+// ssm_gate, conv1d_state, l2norm(q), l2norm(k), repeat_heads(q), repeat_heads(k)
+// (src/models/qwen3_5/trunk.cpp:748-766 of the reference)
+size_t merged_linear_mixer_inputs(tsr_context* ctx, const std::vector<PendingLaunch>& q, size_t i, int* rc) {
+  if (!ctx->fold_elementwise || !fuse_elementwise() || i + 6 > q.size()) return 0;
+  const PendingLaunch &gate = q[i], &conv = q[i + 1], &lq = q[i + 2], &lk = q[i + 3], &rq = q[i + 4], &rk = q[i + 5];
+  if (!is_named(gate, "ssm_gate") || !is_named(conv, "conv1d_state") || !is_named(lq, "l2norm") || !is_named(lk, "l2norm") ||
+      !is_named(rq, "repeat_heads") || !is_named(rk, "repeat_heads"))
+    return 0;
+  const uint64_t conv_dim = conv.sc[0], width = conv.sc[1], key_dim = conv.sc[2];
+  if (gate.sc[1] != 1 || conv.sc[4] != 1 || conv.sc[5] != 0 || width == 0 || width > 64) return 0;
+  const uint64_t k_heads = lq.sc[0], cols = lq.sc[1];
+  if (lk.sc[0] != k_heads || lk.sc[1] != cols || k_heads * cols != key_dim || conv_dim % cols != 0 || cols % 32 != 0 || cols > 1024)
+    return 0;
+  if (lq.buf[0] != conv.buf[3] || lq.buf[1] != lq.buf[0] || lk.buf[0] != conv.buf[4] || lk.buf[1] != lk.buf[0]) return 0;
+  const uint64_t v_heads = rq.sc[0], factor = rq.sc[2];
+  if (rq.sc[1] != cols || rk.sc[1] != cols || rk.sc[0] != v_heads || rk.sc[2] != factor || rq.sc[3] != 1 || rk.sc[3] != 1 ||
+      factor == 0 || v_heads != k_heads * factor || rq.buf[0] != conv.buf[3] || rk.buf[0] != conv.buf[4])
+    return 0;
+  // the expanded heads and the gate outputs must be buffers of their own
+  const size_t exp_bytes = v_heads * cols * 4;
+  for (const PendingLaunch* r : {&rq, &rk})
+    if (overlaps(r->buf[1], exp_bytes, conv.buf[0], conv.bytes[0]) || overlaps(r->buf[1], exp_bytes, conv.buf[2], conv.bytes[2]) ||
+        overlaps(r->buf[1], exp_bytes, conv.buf[3], key_dim * 4) || overlaps(r->buf[1], exp_bytes, conv.buf[4], key_dim * 4))
+      return 0;
+  if (overlaps(rq.buf[1], exp_bytes, rk.buf[1], exp_bytes)) return 0;
+  for (int o = 4; o <= 5; ++o)
+    if (overlaps(gate.buf[o], gate.sc[0] * 4, conv.buf[0], conv.bytes[0]) || overlaps(gate.buf[o], gate.sc[0] * 4, conv.buf[2], conv.bytes[2]))
+      return 0;
+  LinearMixerInputs p{};
+  p.a_log = fbuf(gate, 0), p.dt = fbuf(gate, 1), p.alpha_raw = fbuf(gate, 2), p.beta_raw = fbuf(gate, 3);
+  p.alpha = fbuf(gate, 4), p.beta = fbuf(gate, 5), p.gate_heads = static_cast<int>(gate.sc[0]);
+  p.qkv = fbuf(conv, 0), p.conv_w = fbuf(conv, 1), p.hist = fbuf(conv, 2), p.q = fbuf(conv, 3), p.k = fbuf(conv, 4), p.v = fbuf(conv, 5);
+  p.conv_dim = static_cast<int>(conv_dim), p.width = static_cast<int>(width), p.key_dim = static_cast<int>(key_dim);
+  p.qkv_offset = conv.sc[3];
+  p.q_exp = fbuf(rq, 1), p.k_exp = fbuf(rk, 1);
+  p.k_heads = static_cast<int>(k_heads), p.cols = static_cast<int>(cols), p.factor = static_cast<int>(factor);
+  p.eps_q = float_of_bits(lq.sc[2]), p.scale_q = float_of_bits(lq.sc[3]);
+  p.eps_k = float_of_bits(lk.sc[2]), p.scale_k = float_of_bits(lk.sc[3]);
+  *rc = launch_linear_mixer_inputs(p, ctx->stream);
+  return *rc == kUnsupportedFeature ? 0 : 6;
+}
+
+// rmsnorm(q heads), rmsnorm(k heads), mrope(q), mrope(k) [, copy_d2d(k row -> cache), copy_d2d(v row -> cache)]
+// (src/models/qwen3_5/trunk.cpp:374-391 of the reference; the copies are AppendKvRows of an fp32 cache)
+size_t merged_head_norm_rope(tsr_context* ctx, const std::vector<PendingLaunch>& q, size_t i, int* rc) {
+  if (!ctx->fold_elementwise || !fuse_elementwise() || i + 4 > q.size()) return 0;
+  const PendingLaunch &nq = q[i], &nk = q[i + 1], &mq = q[i + 2], &mk = q[i + 3];
+  if (!is_named(nq, "rmsnorm") || !is_named(nk, "rmsnorm") || !is_named(mq, "mrope") || !is_named(mk, "mrope")) return 0;
+  const uint64_t heads = nq.sc[0], kv_heads = nk.sc[0], d = nq.sc[1];
+  if (nk.sc[1] != d || d % 32 != 0 || d > 1024 || nq.buf[2] != nq.buf[0] || nk.buf[2] != nk.buf[0]) return 0;
+  if (mq.buf[0] != nq.buf[0] || mk.buf[0] != nk.buf[0] || mq.buf[1] != mk.buf[1] || mq.sc[0] != 1 || mk.sc[0] != 1 ||
+      mq.sc[1] != heads || mk.sc[1] != kv_heads || mq.sc[2] != d || mk.sc[2] != d)
+    return 0;
+  for (int sidx = 3; sidx < 8; ++sidx)
+    if (mq.sc[sidx] != mk.sc[sidx]) return 0;
+  if (overlaps(nq.buf[0], heads * d * 4, nk.buf[0], kv_heads * d * 4)) return 0;
+  HeadNormRope p{};
+  p.q = fbuf(nq, 0), p.k = fbuf(nk, 0), p.q_w = fbuf(nq, 1), p.k_w = fbuf(nk, 1);
+  p.pos = static_cast<const unsigned long long*>(mq.buf[1]);
+  p.heads = static_cast<int>(heads), p.kv_heads = static_cast<int>(kv_heads), p.head_dim = static_cast<int>(d);
+  p.rope_dim = static_cast<int>(mq.sc[3]), p.theta = float_of_bits(mq.sc[4]);
+  p.sec_t = static_cast<int>(mq.sc[5]), p.sec_h = static_cast<int>(mq.sc[6]);
+  p.eps_q = float_of_bits(nq.sc[2]), p.eps_k = float_of_bits(nk.sc[2]);
+  size_t used = 4;
+  if (i + 6 <= q.size() && is_named(q[i + 4], "copy_d2d") && is_named(q[i + 5], "copy_d2d")) {
+    const PendingLaunch &ck = q[i + 4], &cv = q[i + 5];
+    const uint64_t row_bytes = kv_heads * d * 4;
+    const unsigned char* kdst = static_cast<const unsigned char*>(ck.buf[1]) + ck.sc[1];
+    const unsigned char* vdst = static_cast<const unsigned char*>(cv.buf[1]) + cv.sc[1];
+    const unsigned char* vsrc = static_cast<const unsigned char*>(cv.buf[0]) + cv.sc[0];
+    if (ck.buf[0] == nk.buf[0] && ck.sc[0] == 0 && ck.sc[2] == row_bytes && cv.sc[2] == row_bytes &&
+        reinterpret_cast<uintptr_t>(kdst) % 4 == 0 && reinterpret_cast<uintptr_t>(vdst) % 4 == 0 &&
+        reinterpret_cast<uintptr_t>(vsrc) % 4 == 0 && !overlaps(kdst, row_bytes, nq.buf[0], heads * d * 4) &&
+        !overlaps(kdst, row_bytes, nk.buf[0], row_bytes) && !overlaps(vdst, row_bytes, nq.buf[0], heads * d * 4) &&
+        !overlaps(vdst, row_bytes, nk.buf[0], row_bytes) && !overlaps(vdst, row_bytes, vsrc, row_bytes) &&
+        !overlaps(kdst, row_bytes, vsrc, row_bytes) && !overlaps(kdst, row_bytes, vdst, row_bytes)) {
+      p.k_row = reinterpret_cast<float*>(const_cast<unsigned char*>(kdst));
+      p.v_src = reinterpret_cast<const float*>(vsrc);
+      p.v_row = reinterpret_cast<float*>(const_cast<unsigned char*>(vdst));
+      used = 6;
+    }
+  }
+  *rc = launch_head_norm_rope(p, ctx->stream);
+  return *rc == kUnsupportedFeature ? 0 : used;
+}
+
+// attention (any cache format), sigmoid_gate of its output in place (src/models/qwen3_5/trunk.cpp:441-452)
+size_t merged_attention_gate(tsr_context* ctx, const std::vector<PendingLaunch>& q, size_t i, int* rc) {
+  if (!ctx->fold_elementwise || !fuse_elementwise() || i + 2 > q.size() || !is_named(q[i + 1], "sigmoid_gate")) return 0;
+  const PendingLaunch &at = q[i], &sg = q[i + 1];
+  int fmt;
+  const bool plain = is_named(at, "attention");
+  if (plain) fmt = at.sc[8] != 0 ? TSR_KV_F16 : TSR_KV_F32;
+  else if (is_named(at, "attention_q8")) fmt = TSR_KV_INT8;
+  else if (is_named(at, "attention_q4")) fmt = TSR_KV_INT4;
+  else if (is_named(at, "attention_fp8")) fmt = TSR_KV_FP8;
+  else return 0;
+  const int out_at = plain ? 3 : 5;
+  const uint64_t m = at.sc[0], heads = at.sc[2], d = at.sc[4], row_base = at.sc[6];
+  if (row_base != 0 || sg.sc[0] != m * heads * d || sg.buf[0] != at.buf[out_at] || sg.buf[2] != at.buf[out_at]) return 0;
+  if (overlaps(sg.buf[1], sg.sc[0] * 4, at.buf[out_at], sg.sc[0] * 4)) return 0;
+  *rc = attention_gated(fmt, fbuf(at, 0), at.buf[1], at.buf[2], plain ? nullptr : fbuf(at, 3), plain ? nullptr : fbuf(at, 4),
+                        fbuf(at, out_at), fbuf(sg, 1), m, at.sc[1], heads, at.sc[3], d, at.sc[5], 0, at.sc[7], plain ? at.sc[9] : 1,
+                        ctx->stream);
+  return *rc == kUnsupportedFeature ? 0 : 2;
+}
+
 int issue_one(tsr_context* ctx, const PendingLaunch& op) {
   const Args a{op.buf, op.bytes, op.nbuf, op.sc, op.nsc, op.grid_y, ctx->stream, false, ctx};
   return kTable[op.kernel].fn(a);
@@ -1139,7 +1252,16 @@ int issue_queue(tsr_context* ctx, const std::vector<PendingLaunch>& q) {
     const size_t start = has_pro ? i + 1 : i;
     Projection first;
     if (!as_projection(q, start, &first)) {
-      if (int rc = issue_one(ctx, q[i])) return rc;
+      int rc = kOk;
+      size_t merged = merged_linear_mixer_inputs(ctx, q, i, &rc);
+      if (merged == 0) merged = merged_head_norm_rope(ctx, q, i, &rc);
+      if (merged == 0) merged = merged_attention_gate(ctx, q, i, &rc);
+      if (merged != 0) {
+        if (rc != kOk) return rc;
+        i += merged;
+        continue;
+      }
+      if (int rc1 = issue_one(ctx, q[i])) return rc1;
       ++i;
       continue;
     }

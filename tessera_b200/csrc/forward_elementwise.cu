@@ -319,6 +319,86 @@ __global__ void conv1d_state_kernel(const float* __restrict__ qkv, const float* 
   }
 }
 
+// The steps between a linear-attention layer's input projections and its state step in one launch: CTA b takes
+// channels [b cols, (b + 1) cols) of the convolution (cols = the heads' width = blockDim): the first k_heads CTAs
+// are the q heads, the next k_heads the k heads (convolution, SiLU, l2norm of the head, the head repeated into the
+// expanded layout), the rest value channels (convolution and SiLU); one more CTA evaluates ssm_gate.  Same
+// arithmetic and the same order of additions as conv1d_state_kernel, l2norm_kernel, repeat_heads_kernel and
+// ssm_gate_kernel.
+__global__ void __launch_bounds__(1024) linear_mixer_inputs_kernel(const LinearMixerInputs p) {
+  __shared__ float red[32];
+  const int b = blockIdx.x, tid = threadIdx.x;
+  if (b == static_cast<int>(gridDim.x) - 1) {
+    for (int h = tid; h < p.gate_heads; h += blockDim.x) {
+      const float raw = p.alpha_raw[h] + p.dt[h];
+      const float softplus = raw > 20.0f ? raw : log1pf(expf(raw));
+      p.alpha[h] = expf(p.a_log[h] * softplus);
+      p.beta[h] = 1.0f / (1.0f + expf(-p.beta_raw[h]));
+    }
+    return;
+  }
+  const size_t c = static_cast<size_t>(b) * p.cols + tid;
+  const size_t stride = p.width - 1, hbase = c * stride;
+  const float current = p.qkv[p.qkv_offset + c];
+  float acc = __fmul_rn(p.conv_w[c * p.width + (p.width - 1)], current);
+  for (int i = 1; i < p.width; ++i) acc = fmaf(p.conv_w[c * p.width + (p.width - 1 - i)], p.hist[hbase + (i - 1)], acc);
+  const float out = acc / (1.0f + expf(-acc));
+  if (p.width > 1) {
+    for (size_t i = stride; i > 1; --i) p.hist[hbase + (i - 1)] = p.hist[hbase + (i - 2)];
+    p.hist[hbase] = current;
+  }
+  if (b >= 2 * p.k_heads) {
+    p.v[c - 2 * static_cast<size_t>(p.key_dim)] = out;
+    return;
+  }
+  const bool is_k = b >= p.k_heads;
+  const int head = is_k ? b - p.k_heads : b;
+  const float sum = block_sum(fmaf(out, out, 0.0f), red);
+  const float gain = (is_k ? p.scale_k : p.scale_q) / sqrtf(sum + (is_k ? p.eps_k : p.eps_q));
+  const float y = out * gain;
+  (is_k ? p.k : p.q)[static_cast<size_t>(head) * p.cols + tid] = y;
+  float* expanded = is_k ? p.k_exp : p.q_exp;
+  for (int j = 0; j < p.factor; ++j) expanded[(static_cast<size_t>(j) * p.k_heads + head) * p.cols + tid] = y;
+}
+
+// The steps between a full-attention layer's q / k / v projections and its attention in one launch: CTA r is one
+// head of q (r < heads) or of k: rmsnorm of the head with the per-head weight, mrope of the normalised head, both
+// in place, the k heads also written to their cache row; one more CTA copies the token's v row to the cache.
+// Same arithmetic and order of additions as rmsnorm_kernel and mrope_kernel.
+__global__ void __launch_bounds__(1024) head_norm_rope_kernel(const HeadNormRope p) {
+  __shared__ float red[32];
+  __shared__ float normed[1024];
+  const int r = blockIdx.x, tid = threadIdx.x;
+  if (r == p.heads + p.kv_heads) {
+    for (int t = tid; t < p.kv_heads * p.head_dim; t += blockDim.x) p.v_row[t] = p.v_src[t];
+    return;
+  }
+  const bool is_k = r >= p.heads;
+  float* row = is_k ? p.k + static_cast<size_t>(r - p.heads) * p.head_dim : p.q + static_cast<size_t>(r) * p.head_dim;
+  float* cache = is_k && p.k_row != nullptr ? p.k_row + static_cast<size_t>(r - p.heads) * p.head_dim : nullptr;
+  const float x = row[tid];
+  const float sum = block_sum(fmaf(x, x, 0.0f), red);
+  const float gain = 1.0f / sqrtf(sum / static_cast<float>(p.head_dim) + (is_k ? p.eps_k : p.eps_q));
+  const float y = x * gain * (is_k ? p.k_w : p.q_w)[tid];
+  normed[tid] = y;
+  __syncthreads();
+  const int pairs = p.rope_dim / 2;
+  if (tid < pairs) {
+    const int j = tid;
+    const unsigned long long section_pos = j < p.sec_t ? p.pos[0] : j < p.sec_t + p.sec_h ? p.pos[1] : p.pos[2];
+    const double angle = static_cast<double>(section_pos) *
+                         pow(static_cast<double>(p.theta), -2.0 * static_cast<double>(j) / static_cast<double>(p.rope_dim));
+    const float c = static_cast<float>(cos(angle)), sn = static_cast<float>(sin(angle));
+    const float x1 = normed[j], x2 = normed[j + pairs];
+    const float o1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)), o2 = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, c));
+    row[j] = o1, row[j + pairs] = o2;
+    if (cache != nullptr) cache[j] = o1, cache[j + pairs] = o2;
+  } else if (tid >= p.rope_dim) {
+    row[tid] = y;
+    if (cache != nullptr) cache[tid] = y;
+  }
+}
+
 // top_k_rows: the top_k (<= 32) largest of `vocab` fp32 logits of every row, descending, with their
 // indices; output row r reads input row row_base + r (src/backends/rocm/rocm_kernels.hpp:558-566).  One
 // CTA per row; top_k rounds of a block-wide arg-max over the values not taken yet; among equal values the
@@ -374,6 +454,19 @@ unsigned blocks_of(size_t n) { return static_cast<unsigned>((n + 255) / 256); }
 bool fits31(uint64_t v) { return v > 0 && v <= 0x7FFFFFFFull; }
 
 }  // namespace
+
+int launch_linear_mixer_inputs(const LinearMixerInputs& p, cudaStream_t st) {
+  if (p.cols <= 0 || p.cols > 1024 || p.cols % 32 != 0 || p.conv_dim % p.cols != 0) return kUnsupportedFeature;
+  linear_mixer_inputs_kernel<<<static_cast<unsigned>(p.conv_dim / p.cols + 1), static_cast<unsigned>(p.cols), 0, st>>>(p);
+  return check_launch();
+}
+
+int launch_head_norm_rope(const HeadNormRope& p, cudaStream_t st) {
+  if (p.head_dim <= 0 || p.head_dim > 1024 || p.head_dim % 32 != 0) return kUnsupportedFeature;
+  const unsigned grid = static_cast<unsigned>(p.heads + p.kv_heads + (p.v_row != nullptr ? 1 : 0));
+  head_norm_rope_kernel<<<grid, static_cast<unsigned>(p.head_dim), 0, st>>>(p);
+  return check_launch();
+}
 }  // namespace tsr
 
 using namespace tsr;

@@ -249,6 +249,40 @@ int umma_mxfp4_w4a8(const void* a8, const float* as, const void* w, float* c, ui
                     cudaStream_t st);
 int umma_f8_wait_timeouts(unsigned int* count);
 int umma_f8_set_error_word(unsigned int* word);
+// ---- merged small steps of a token (forward_elementwise.cu, attention.cu): what the deferred queue issues
+// when it finds these steps side by side; each merged kernel repeats the single steps' arithmetic.
+// Linear-attention layer: ssm_gate, conv1d_state (one row, no history slots), l2norm of the q and k heads in
+// place, repeat_heads of both: a CTA per head-sized slice of the convolution's channels.
+struct LinearMixerInputs {
+  const float *a_log, *dt, *alpha_raw, *beta_raw;
+  float *alpha, *beta;
+  int gate_heads;
+  const float *qkv, *conv_w;
+  float *hist, *q, *k, *v;
+  int conv_dim, width, key_dim;
+  size_t qkv_offset;
+  float *q_exp, *k_exp;
+  int k_heads, cols, factor;
+  float eps_q, scale_q, eps_k, scale_k;
+};
+int launch_linear_mixer_inputs(const LinearMixerInputs& p, cudaStream_t st);
+// Full-attention layer: rmsnorm of the q and k heads in place, mrope of both (one row), and the append of the
+// token's k and v rows to an fp32 cache (k_row / v_row null: no append).
+struct HeadNormRope {
+  float *q, *k;
+  const float *q_w, *k_w;
+  const unsigned long long* pos;
+  int heads, kv_heads, head_dim, rope_dim, sec_t, sec_h;
+  float eps_q, eps_k, theta;
+  float* k_row;
+  const float* v_src;
+  float* v_row;
+};
+int launch_head_norm_rope(const HeadNormRope& p, cudaStream_t st);
+// tsr_attention with out = attention * sigmoid(gate) written by the merge kernel (gate null: plain).
+int attention_gated(int kv_format, const float* q, const void* k, const void* v, const float* k_scale, const float* v_scale,
+                    float* out, const float* gate, uint64_t m, uint64_t n, uint64_t heads, uint64_t kv_heads, uint64_t head_dim,
+                    uint64_t q_base, uint64_t row_base, uint64_t window, uint64_t causal, cudaStream_t st);
 // Point the kernels of each file at the host-visible error word (see pipeline.cuh); once per device.
 int staged_set_error_word(unsigned int* word);
 int staged_q6k_set_error_word(unsigned int* word);
