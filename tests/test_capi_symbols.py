@@ -19,6 +19,15 @@ REQUIRED_IDS = [
     "gemm_mxfp4", "gemm_mxfp4_rows", "gemm_mxfp4_batched", "gemm_mxfp4_wmma",
     "gemm_mxfp4_wmma_reduce", "mxfp4_row_ref", "gemm_fp8", "quantize_fp8",
     "quantize_fp8_pack", "quantize_fp8_pack_rows", "round_bf16", "add", "fill",
+    # every other id the reference's Qwen3.5 decode loads (src/models/qwen3_5/trunk.cpp:150-215,486-530,
+    # src/core/decode_device.cpp:170-210 of the reference)
+    "rmsnorm", "silu_mul", "sigmoid_gate", "qgate_split", "mrope", "rope", "repeat_heads", "l2norm", "ssm_gate",
+    "delta_step_heads", "rmsnorm_gated", "conv1d_state", "cast_f32_f16", "quantize_q8", "quantize_q4",
+    "attention", "attention_q8", "attention_q4", "attention_fp8", "attention_split", "attention_split_gqa",
+    "attention_q8_split", "attention_q4_split", "attention_fp8_split", "attention_combine", "top_k_rows",
+    "embedding_f32", "embedding_bf16", "embedding_q4k", "gemm_f32", "gemm_f32_batched", "gemm_bf16",
+    "gemm_bf16_batched", "gemm_bf16_wmma", "moe_gate", "moe_scale_add", "moe_experts_gate_up_q4k",
+    "moe_experts_down_q4k", "moe_experts_down_q6k",
 ]
 
 
