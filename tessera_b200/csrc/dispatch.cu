@@ -1070,6 +1070,9 @@ bool as_prologue(const tsr_context* ctx, const std::vector<PendingLaunch>& q, si
     // every CTA that stages the activations evaluates the step for all of them: with many
     // row tiles and a long k a kernel of its own is cheaper (measured: 107 CTAs x 17408
     // elements cost 2.5-8 us inside the launch, about 3 us as a launch)
+    // ... and inside a launch that ends with the sum over ranks it measured slower than its own kernel at every
+    // world size (per step of 64 layers: 3.89 against 3.57 ms on 2 GPUs, 3.20 against 2.97 ms on 4)
+    if (next.with_tp) return false;
     const uint64_t repeated = ((next.t.n + 47) / 48) * next.m * next.k;
     static const uint64_t limit = [] {
       const char* v = std::getenv("TSR_FOLD_SILU_LIMIT");

@@ -79,7 +79,7 @@ def launch_ffn_tail(backend: CudaBackend, case: RowParallelCase, gate: Buffer, u
     """The end of an FFN block as the reference's forward queues it (silu_mul, down projection,
     residual add; src/models/qwen3_5/trunk.cpp:440-470 of the reference), on one rank's k range
     with the sum over ranks (`sharded`) or on the whole k.  Through the deferred queue the three
-    steps become one launch."""
+    steps become one launch; with the sum over ranks two (the silu_mul stays a kernel of its own there)."""
     m, n = case.m, case.n
     backend.LaunchKernel(backend.LoadKernel("silu_mul"), KernelLaunch(buffers=[gate, up, act], scalars=[m * k_local]))
     if sharded:
