@@ -38,7 +38,7 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             return json.load(f), "measured"
-    return {"hbm_gbs": 6650.0}, "fallback"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
 
 
 def config_dict(world: int):
@@ -241,7 +241,7 @@ def reference_arm(args):
 
 # --------------------------------------------------------------------------
 # GPU arm
-def qgemv_table(stream, hbm_peak, only=None):
+def qgemv_table(stream, hbm_peak, only=None, tensor_peak=None):
     """Device time per launch of the single-projection shapes the metric names: the Q4_K
     decode GEMV (17408 x 5120, m = 1) and the MXFP4 / FP8 projections at m = 1, 4, 16 over
     5120 x 5120, 17408 x 5120 and 5120 x 17408.  Each case rotates through enough private
@@ -257,6 +257,7 @@ def qgemv_table(stream, hbm_peak, only=None):
     cases = [("q4k", 1, 17408, 5120), ("q4k", 1, 17408, 5120, 2), ("q6k", 1, 17408, 5120)]
     cases += [(f, m, n, k) for f in ("mxfp4", "fp8", "w4a8") for (n, k) in shapes for m in (1, 4, 16)]
     cases += [("bf16", 1, 17408, 5120), ("f32", 1, 256, 2048)]  # a bf16 checkpoint's projection; a router gate
+    cases += [("q4k", 512, 17408, 5120), ("q6k", 512, 17408, 5120)]  # a prefill chunk on the tcgen05 tile: tensor-bound
     if only is not None:
         cases = [only]
     rows, cache = [], {}
@@ -352,6 +353,10 @@ def qgemv_table(stream, hbm_peak, only=None):
                "frac": round(gbs / hbm_peak, 3)}
         if grouped:
             row["weights_per_launch"] = group
+        if m >= 128:  # the tensor roofline: 2 m n k over the measured dense bf16 rate
+            row["tflops"] = round(2.0 * m * n * k / us / 1e6, 1)
+            if tensor_peak:
+                row["tensor_frac"] = round(row["tflops"] / tensor_peak, 3)
         rows.append(row)
     cache.clear()
     if group_backend is not None:
@@ -1055,7 +1060,7 @@ def gpu_arm(args):
         for _, _, _, buf in weights:
             buf.release()
         weights.clear()
-        line["qgemv"] = qgemv_table(stream, peaks["hbm_gbs"])
+        line["qgemv"] = qgemv_table(stream, peaks["hbm_gbs"], tensor_peak=peaks.get("bf16_tflops"))
         line["qgemv"].append(moe_row(stream, peaks["hbm_gbs"]))
         line["qgemv"].append(delta_row(stream, peaks["hbm_gbs"]))
         line["qgemv"].append(attention_row(stream, peaks["hbm_gbs"], "f32"))
@@ -1129,7 +1134,7 @@ def main():
         only = (fmt, int(m), int(n), int(k)) + ((int(fields[4]),) if len(fields) > 4 else ())
         peaks, kind = measured_peaks()
         torch.cuda.set_device(0)
-        row = qgemv_table(torch.cuda.Stream(), peaks["hbm_gbs"], only=only)[0]
+        row = qgemv_table(torch.cuda.Stream(), peaks["hbm_gbs"], only=only, tensor_peak=peaks.get("bf16_tflops"))[0]
         print(json.dumps({"case": args.case, "peak_kind": kind, **row}))
     else:
         gpu_arm(args)
