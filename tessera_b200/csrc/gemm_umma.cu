@@ -6,7 +6,8 @@
 // the 128 weight rows of a CTA are the M side of tcgen05.mma (kind::f16, fp32
 // accumulate in TMEM), the tokens are the N side.  Each fp32 activation is
 // split into two fp16 columns (hi = fp16(a), lo = fp16(a - hi)), so the
-// activation keeps ~22 bits; weights are dequantised to fp16 exactly as the
+// activation keeps ~22 bits (Q4_K / Q6_K batches beyond 64 rows: one column,
+// twice the tokens per CTA, see token_chunk); weights are dequantised to fp16 exactly as the
 // reference's own tensor-core tile does (src/backends/rocm/rocm_kernels_wmma.cpp:
 // 54-80 of the reference: weights dequantised to fp16 in shared memory).
 //
@@ -58,7 +59,29 @@ struct UmmaParams {
   float* c;
   int m, n, k;
   const unsigned char* bpre;  // activations already in operand layout (convert_activations_kernel), or null
+  int one_term;               // batches beyond one chunk: a single binary16 term per activation, 128 tokens per CTA
 };
+
+// The tokens of chunk `index`: operand-B rows [0, tok_pad) and [tok_pad, 2 tok_pad).  With two terms the first
+// half holds the tokens' binary16 values and the second what binary16 lost of them; with one term the rows are
+// simply the tokens in order (as the reference's own tensor-core tile has them: binary16 operands,
+// src/backends/rocm/rocm_kernels_wmma.cpp:54-80 of the reference).
+struct TokenChunk {
+  int tok0, tokens, tok_pad;
+};
+__host__ __device__ __forceinline__ TokenChunk token_chunk(int m, int index, int one_term) {
+  const int per = one_term ? 2 * 64 : 64;
+  TokenChunk c;
+  c.tok0 = index * per;
+  c.tokens = m - c.tok0 < per ? m - c.tok0 : per;
+  c.tok_pad = one_term ? (((c.tokens + 1) / 2 + 7) & ~7) : ((c.tokens + 7) & ~7);
+  return c;
+}
+// Row r of operand B: which token of the chunk, and whether it is the lost-bits row.
+__device__ __forceinline__ int row_token(int r, int tok_pad, int one_term, bool* lo_part) {
+  *lo_part = !one_term && r >= tok_pad;
+  return (one_term || r < tok_pad) ? r : r - tok_pad;
+}
 
 // ---- tcgen05 wrappers -------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t ncols) {
@@ -263,19 +286,19 @@ __device__ __forceinline__ uint4 convert_b_piece(float4 x0, float4 x1, bool lo_p
 // (token chunk, slab): out[(chunk * nslabs + slab) * kBSlabPitch + ...], so that the
 // tiles fetch a slab with one bulk copy instead of converting it in every CTA.
 __global__ void __launch_bounds__(256)
-convert_activations_kernel(const float* __restrict__ a, unsigned char* __restrict__ out, int m, int k) {
+convert_activations_kernel(const float* __restrict__ a, unsigned char* __restrict__ out, int m, int k, int one_term) {
   const int slab = blockIdx.x, chunk = blockIdx.y, nslabs = gridDim.x;
-  const int tok0 = chunk * kMaxTokens;
-  const int tokens = min(kMaxTokens, m - tok0);
-  const int tok_pad = (tokens + 7) & ~7, n_cols = 2 * tok_pad;
+  const TokenChunk tc = token_chunk(m, chunk, one_term);
+  const int tok0 = tc.tok0, tokens = tc.tokens, tok_pad = tc.tok_pad, n_cols = 2 * tok_pad;
   unsigned char* dst = out + (static_cast<size_t>(chunk) * nslabs + slab) * kBSlabPitch;
   for (int g = threadIdx.x; g < n_cols * (kSlab / 8); g += blockDim.x) {
     const int r = g >> 3, kc = g & 7;
-    const int tok = r < tok_pad ? r : r - tok_pad;
+    bool lo_part;
+    const int tok = row_token(r, tok_pad, one_term, &lo_part);
     uint4 piece = make_uint4(0u, 0u, 0u, 0u);
     if (tok < tokens) {
       const float4* src = reinterpret_cast<const float4*>(a + static_cast<size_t>(tok0 + tok) * k + slab * kSlab + kc * 8);
-      piece = convert_b_piece(__ldg(src), __ldg(src + 1), r >= tok_pad);
+      piece = convert_b_piece(__ldg(src), __ldg(src + 1), lo_part);
     }
     *reinterpret_cast<uint4*>(dst + (r >> 3) * kSbo + (r & 7) * 16 + kc * kLbo) = piece;
   }
@@ -329,9 +352,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row0 = blockIdx.x * kTileM;
-  const int tok0 = blockIdx.y * kMaxTokens;
-  const int tokens = min(kMaxTokens, p.m - tok0);
-  const int tok_pad = (tokens + 7) & ~7;      // hi rows [0, tok_pad), lo rows [tok_pad, 2*tok_pad)
+  const TokenChunk tc = token_chunk(p.m, blockIdx.y, p.one_term);
+  const int tok0 = tc.tok0, tokens = tc.tokens;
+  const int tok_pad = tc.tok_pad;             // rows [0, tok_pad) and [tok_pad, 2*tok_pad): see token_chunk
   const int n_cols = 2 * tok_pad;             // multiple of 16, <= 128
   const int b_slab_bytes = n_cols * kSlab * 2;
   constexpr int kRingBytes = RING ? kRawStages * RingFmt<FMT>::kStagePitch : 0;
@@ -401,7 +424,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
         dst[i][0] = dst[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (g < b_pieces && slab < nslabs) {
           const int r = g >> 3, kc = g & 7;
-          const int tok = r < tok_pad ? r : r - tok_pad;
+          bool lo_part;
+          const int tok = row_token(r, tok_pad, p.one_term, &lo_part);
           if (tok < tokens) {
             const float4* src =
                 reinterpret_cast<const float4*>(p.a + static_cast<size_t>(tok0 + tok) * p.k + slab * kSlab + kc * 8);
@@ -494,7 +518,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
             if (g < b_pieces) {
               const int r = g >> 3, kc = g & 7;
               *reinterpret_cast<uint4*>(b_tiles + buf * b_slab_bytes + (r >> 3) * kSbo + (r & 7) * 16 + kc * kLbo) =
-                  convert_b_piece(bx[u & 1][i][0], bx[u & 1][i][1], r >= tok_pad);
+                  convert_b_piece(bx[u & 1][i][0], bx[u & 1][i][1], !p.one_term && r >= tok_pad);
             }
           }
           load_b(s + 2, bx[u & 1]);
@@ -573,8 +597,14 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
         tmem_ld8(lane_addr + tok_pad + c0, lo);
         if (out_row < p.n) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            if (c0 + j < tokens) p.c[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = (hi[j] + lo[j]) * out_scale;
+          for (int j = 0; j < 8; ++j) {
+            if (p.one_term) {  // two tokens, not two terms of one
+              if (c0 + j < tokens) p.c[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = hi[j] * out_scale;
+              if (tok_pad + c0 + j < tokens) p.c[static_cast<size_t>(tok0 + tok_pad + c0 + j) * p.n + out_row] = lo[j] * out_scale;
+            } else if (c0 + j < tokens) {
+              p.c[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = (hi[j] + lo[j]) * out_scale;
+            }
+          }
         }
       }
     }
@@ -687,17 +717,21 @@ namespace {
 
 template <int FMT, bool RING>
 int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st, bool allow_scratch) {
-  const int tok_pad = ((p.m < kMaxTokens ? p.m : kMaxTokens) + 7) & ~7;
+  // one binary16 term per activation where the weights are rounded to binary16 anyway (Q4_K, Q6_K: the error
+  // class of the result does not change) and the batch is larger than one two-term chunk; MXFP4 and FP8
+  // weights are exact in binary16, so their batches keep the second term and with it fp32-like results
+  p.one_term = (FMT == kFmtQ4K || FMT == kFmtQ6K) && p.m > kMaxTokens && std::getenv("TSR_TILE_TWO_TERMS") == nullptr ? 1 : 0;
+  const int tok_pad = token_chunk(p.m, 0, p.one_term).tok_pad;  // the first chunk is the largest
   const size_t ring = RING ? static_cast<size_t>(kRawStages) * RingFmt<FMT>::kStagePitch : 0;
   const size_t smem = 1024 + ring + kBufs * kASlabBytes + kBufs * static_cast<size_t>(2 * tok_pad) * kSlab * 2 + 256;
   if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemm_umma_kernel<FMT, RING>), 227 * 1024)) return rc;
-  const dim3 grid(static_cast<unsigned>((p.n + kTileM - 1) / kTileM),
-                  static_cast<unsigned>((p.m + kMaxTokens - 1) / kMaxTokens));
+  const int per_cta = p.one_term ? 2 * kMaxTokens : kMaxTokens;
+  const dim3 grid(static_cast<unsigned>((p.n + kTileM - 1) / kTileM), static_cast<unsigned>((p.m + per_cta - 1) / per_cta));
   // activations -> operand layout once per launch, when scratch is to be had
   const int nslabs = p.k / kSlab;
   p.bpre = allow_scratch ? activation_scratch(st, static_cast<size_t>(grid.y) * nslabs * kBSlabPitch) : nullptr;
   if (p.bpre != nullptr) {
-    convert_activations_kernel<<<dim3(nslabs, grid.y), 256, 0, st>>>(p.a, const_cast<unsigned char*>(p.bpre), p.m, p.k);
+    convert_activations_kernel<<<dim3(nslabs, grid.y), 256, 0, st>>>(p.a, const_cast<unsigned char*>(p.bpre), p.m, p.k, p.one_term);
     if (int rc = check_launch()) return rc;
   }
   gemm_umma_kernel<FMT, RING><<<grid, kUmmaThreads, smem, st>>>(maps.weights, maps.scales, p);
