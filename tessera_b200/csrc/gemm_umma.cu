@@ -44,7 +44,7 @@ constexpr int kSlab = 64;         // k elements per pipeline step
 constexpr int kMaxTokens = 64;    // tokens per CTA (N = 2 * padded tokens <= 128)
 constexpr int kProducerThreads = 256;  // two per weight row
 constexpr int kUmmaThreads = kProducerThreads + 96;  // + the MMA warp, the weight TMA warp, the activation copy warp
-constexpr int kBSlabPitch = 2 * kMaxTokens * kSlab * 2;  // bytes per slab of pre-converted activations (16 KiB)
+constexpr int kBSlabPitch = 256 * kSlab * 2;  // bytes per slab of pre-converted activations: up to 256 operand rows (32 KiB)
 constexpr int kASlabBytes = kTileM * kSlab * 2;  // 16384
 constexpr int kBufs = 2;                         // slab buffers in shared memory (a power of two)
 constexpr int kBufShift = 1;
@@ -59,7 +59,8 @@ struct UmmaParams {
   float* c;
   int m, n, k;
   const unsigned char* bpre;  // activations already in operand layout (convert_activations_kernel), or null
-  int one_term;               // batches beyond one chunk: a single binary16 term per activation, 128 tokens per CTA
+  int one_term;               // batches beyond one chunk: a single binary16 term per activation; 1: 128 tokens per
+                              // CTA, 2: 256 (needs the pre-converted activations)
 };
 
 // The tokens of chunk `index`: operand-B rows [0, tok_pad) and [tok_pad, 2 tok_pad).  With two terms the first
@@ -70,7 +71,7 @@ struct TokenChunk {
   int tok0, tokens, tok_pad;
 };
 __host__ __device__ __forceinline__ TokenChunk token_chunk(int m, int index, int one_term) {
-  const int per = one_term ? 2 * 64 : 64;
+  const int per = one_term == 2 ? 256 : one_term == 1 ? 128 : 64;
   TokenChunk c;
   c.tok0 = index * per;
   c.tokens = m - c.tok0 < per ? m - c.tok0 : per;
@@ -719,17 +720,29 @@ template <int FMT, bool RING>
 int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st, bool allow_scratch) {
   // one binary16 term per activation where the weights are rounded to binary16 anyway (Q4_K, Q6_K: the error
   // class of the result does not change) and the batch is larger than one two-term chunk; MXFP4 and FP8
-  // weights are exact in binary16, so their batches keep the second term and with it fp32-like results
-  p.one_term = (FMT == kFmtQ4K || FMT == kFmtQ6K) && p.m > kMaxTokens && std::getenv("TSR_TILE_TWO_TERMS") == nullptr ? 1 : 0;
-  const int tok_pad = token_chunk(p.m, 0, p.one_term).tok_pad;  // the first chunk is the largest
-  const size_t ring = RING ? static_cast<size_t>(kRawStages) * RingFmt<FMT>::kStagePitch : 0;
-  const size_t smem = 1024 + ring + kBufs * kASlabBytes + kBufs * static_cast<size_t>(2 * tok_pad) * kSlab * 2 + 256;
-  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemm_umma_kernel<FMT, RING>), 227 * 1024)) return rc;
-  const int per_cta = p.one_term ? 2 * kMaxTokens : kMaxTokens;
-  const dim3 grid(static_cast<unsigned>((p.n + kTileM - 1) / kTileM), static_cast<unsigned>((p.m + per_cta - 1) / per_cta));
-  // activations -> operand layout once per launch, when scratch is to be had
+  // weights are exact in binary16, so their batches keep the second term and with it fp32-like results.
+  // Beyond 128 rows a CTA takes 256 tokens (every dequantised weight slab then feeds 256 accumulator columns),
+  // which needs the activations converted ahead of the tiles.
+  const bool narrow = (FMT == kFmtQ4K || FMT == kFmtQ6K) && p.m > kMaxTokens && std::getenv("TSR_TILE_TWO_TERMS") == nullptr;
+  p.one_term = !narrow ? 0 : (p.m > 2 * kMaxTokens && allow_scratch && std::getenv("TSR_TILE_128") == nullptr) ? 2 : 1;
   const int nslabs = p.k / kSlab;
-  p.bpre = allow_scratch ? activation_scratch(st, static_cast<size_t>(grid.y) * nslabs * kBSlabPitch) : nullptr;
+  const size_t ring = RING ? static_cast<size_t>(kRawStages) * RingFmt<FMT>::kStagePitch : 0;
+  dim3 grid;
+  size_t smem = 0;
+  for (;;) {
+    const int tok_pad = token_chunk(p.m, 0, p.one_term).tok_pad;  // the first chunk is the largest
+    const int per_cta = p.one_term == 2 ? 4 * kMaxTokens : p.one_term == 1 ? 2 * kMaxTokens : kMaxTokens;
+    smem = 1024 + ring + kBufs * kASlabBytes + kBufs * static_cast<size_t>(2 * tok_pad) * kSlab * 2 + 256;
+    grid = dim3(static_cast<unsigned>((p.n + kTileM - 1) / kTileM), static_cast<unsigned>((p.m + per_cta - 1) / per_cta));
+    // activations -> operand layout once per launch, when scratch is to be had
+    p.bpre = allow_scratch ? activation_scratch(st, static_cast<size_t>(grid.y) * nslabs * kBSlabPitch) : nullptr;
+    if (p.one_term == 2 && (p.bpre == nullptr || smem > 227 * 1024)) {
+      p.one_term = 1;
+      continue;
+    }
+    break;
+  }
+  if (int rc = allow_dynamic_smem(reinterpret_cast<const void*>(&gemm_umma_kernel<FMT, RING>), 227 * 1024)) return rc;
   if (p.bpre != nullptr) {
     convert_activations_kernel<<<dim3(nslabs, grid.y), 256, 0, st>>>(p.a, const_cast<unsigned char*>(p.bpre), p.m, p.k, p.one_term);
     if (int rc = check_launch()) return rc;

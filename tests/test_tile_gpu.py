@@ -105,10 +105,10 @@ def test_full_size_tiles_on_sampled_rows(backend, oracle, fmt, m, n, k):
     assert rel_err(got[:, rows], ref) < 5e-5
 
 
-@pytest.mark.parametrize("m", [256, 512])
+@pytest.mark.parametrize("m", [100, 256, 300, 512])
 def test_prefill_sized_batches(backend, oracle, m):
     """Chunked-prefill batches through the ids ProjectBatch picks for them (gemm_q4k_wmma,
-    gemm_mxfp4_batched): the binary16 tcgen05 tile, 128 activation rows per CTA with one binary16 term each for
+    gemm_mxfp4_batched): the binary16 tcgen05 tile, 256 activation rows per CTA with one binary16 term each for
     Q4_K, 64 rows with two terms for MXFP4."""
     n, k = 264, 1024
     a = synth.activations(m, k, seed=40)
