@@ -257,7 +257,8 @@ def qgemv_table(stream, hbm_peak, only=None, tensor_peak=None):
     cases = [("q4k", 1, 17408, 5120), ("q4k", 1, 17408, 5120, 2), ("q6k", 1, 17408, 5120)]
     cases += [(f, m, n, k) for f in ("mxfp4", "fp8", "w4a8") for (n, k) in shapes for m in (1, 4, 16)]
     cases += [("bf16", 1, 17408, 5120), ("f32", 1, 256, 2048)]  # a bf16 checkpoint's projection; a router gate
-    cases += [("q4k", 512, 17408, 5120), ("q6k", 512, 17408, 5120)]  # a prefill chunk on the tcgen05 tile: tensor-bound
+    # a prefill chunk on the tcgen05 tile: tensor-bound
+    cases += [("q4k", 512, 17408, 5120), ("q6k", 512, 17408, 5120), ("mxfp4", 512, 17408, 5120), ("fp8", 512, 17408, 5120)]
     if only is not None:
         cases = [only]
     rows, cache = [], {}

@@ -718,12 +718,15 @@ namespace {
 
 template <int FMT, bool RING>
 int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st, bool allow_scratch) {
-  // one binary16 term per activation where the weights are rounded to binary16 anyway (Q4_K, Q6_K: the error
-  // class of the result does not change) and the batch is larger than one two-term chunk; MXFP4 and FP8
-  // weights are exact in binary16, so their batches keep the second term and with it fp32-like results.
+  // One binary16 term per activation for batches larger than one two-term chunk where the weights are
+  // rounded to binary16 anyway (Q4_K, Q6_K: the error class of the result does not change).  MXFP4 and FP8
+  // weights are exact in binary16, so up to 128 rows (verify batches) they keep the second term and with it
+  // fp32-like results; prefill-sized batches take one term as well (the reference quantises those
+  // activations to FP8 or binary16 itself, src/models/qwen3_5/project.cpp:55-85,307-335 of the reference).
   // Beyond 128 rows a CTA takes 256 tokens (every dequantised weight slab then feeds 256 accumulator columns),
   // which needs the activations converted ahead of the tiles.
-  const bool narrow = (FMT == kFmtQ4K || FMT == kFmtQ6K) && p.m > kMaxTokens && std::getenv("TSR_TILE_TWO_TERMS") == nullptr;
+  const int two_term_rows = (FMT == kFmtQ4K || FMT == kFmtQ6K) ? kMaxTokens : 2 * kMaxTokens;
+  const bool narrow = p.m > two_term_rows && std::getenv("TSR_TILE_TWO_TERMS") == nullptr;
   p.one_term = !narrow ? 0 : (p.m > 2 * kMaxTokens && allow_scratch && std::getenv("TSR_TILE_128") == nullptr) ? 2 : 1;
   const int nslabs = p.k / kSlab;
   const size_t ring = RING ? static_cast<size_t>(kRawStages) * RingFmt<FMT>::kStagePitch : 0;

@@ -25,6 +25,8 @@ FP16_WEIGHTS = 1e-3
 
 
 def bound(dtype, m, k=256):
+    if m > 128 and k % 64 == 0:
+        return FP16_WEIGHTS  # prefill-sized batches: one binary16 term per activation on the tcgen05 tile
     if dtype == "mxfp4":
         if 2 <= m <= 21 and k % 128 == 0 and k >= 256:
             return 5e-5  # block-scaled tcgen05 tile: activations as three E4M3 terms (12 significant bits)
