@@ -44,7 +44,7 @@ constexpr int kSlab = 64;         // k elements per pipeline step
 constexpr int kMaxTokens = 64;    // tokens per CTA (N = 2 * padded tokens <= 128)
 constexpr int kProducerThreads = 256;  // two per weight row
 constexpr int kUmmaThreads = kProducerThreads + 96;  // + the MMA warp, the weight TMA warp, the activation copy warp
-constexpr int kBSlabPitch = 256 * kSlab * 2;  // bytes per slab of pre-converted activations: up to 256 operand rows (32 KiB)
+constexpr int kBSlabPitch = 512 * kSlab * 2;  // bytes per slab of pre-converted activations: up to 512 operand rows (64 KiB)
 constexpr int kASlabBytes = kTileM * kSlab * 2;  // 16384
 constexpr int kBufs = 2;                         // slab buffers in shared memory (a power of two)
 constexpr int kBufShift = 1;
@@ -60,7 +60,8 @@ struct UmmaParams {
   int m, n, k;
   const unsigned char* bpre;  // activations already in operand layout (convert_activations_kernel), or null
   int one_term;               // batches beyond one chunk: a single binary16 term per activation; 1: 128 tokens per
-                              // CTA, 2: 256 (needs the pre-converted activations)
+                              // CTA, 2: 256, 3: 512 as two accumulators of 256 columns (2 and 3 need the
+                              // pre-converted activations)
 };
 
 // The tokens of chunk `index`: operand-B rows [0, tok_pad) and [tok_pad, 2 tok_pad).  With two terms the first
@@ -71,7 +72,7 @@ struct TokenChunk {
   int tok0, tokens, tok_pad;
 };
 __host__ __device__ __forceinline__ TokenChunk token_chunk(int m, int index, int one_term) {
-  const int per = one_term == 2 ? 256 : one_term == 1 ? 128 : 64;
+  const int per = one_term == 3 ? 512 : one_term == 2 ? 256 : one_term == 1 ? 128 : 64;
   TokenChunk c;
   c.tok0 = index * per;
   c.tokens = m - c.tok0 < per ? m - c.tok0 : per;
@@ -534,7 +535,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   } else if (warp == kProducerWarps) {
     if (lane == 0) {
       // ---------------- MMA issuer ------------------------------------------
-      const uint32_t idesc = instr_desc(static_cast<uint32_t>(n_cols));
+      // at most 256 columns per MMA: a wider chunk runs as two MMAs on the same weight slab, the second
+      // into the accumulator columns from 256 on
+      const int n_first = n_cols > 256 ? 256 : n_cols, n_second = n_cols - n_first;
+      const uint32_t idesc = instr_desc(static_cast<uint32_t>(n_first));
+      const uint32_t idesc2 = instr_desc(static_cast<uint32_t>(n_second > 0 ? n_second : 16));
       for (int s = 0; s < nslabs; ++s) {
         const int buf = s & (kBufs - 1), round = s >> kBufShift;
         if (!mbar_wait(&full[buf], round & 1, &g_umma_timeouts) ||
@@ -548,6 +553,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
         for (int kk = 0; kk < kSlab / 16; ++kk) {
           umma_f16(tmem_base, smem_desc(a_addr + kk * 2 * kLbo), smem_desc(b_addr + kk * 2 * kLbo), idesc,
                    (s > 0 || kk > 0) ? 1u : 0u);
+          if (n_second > 0)
+            umma_f16(tmem_base + 256, smem_desc(a_addr + kk * 2 * kLbo), smem_desc(b_addr + (256 / 8) * kSbo + kk * 2 * kLbo),
+                     idesc2, (s > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&empty[buf]);  // the slab buffer is free once these MMAs have read it
       }
@@ -592,19 +600,25 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       const int out_row = row0 + tid;
       const float out_scale = (FMT == kFmtFp8 && out_row < p.n) ? __ldg(p.scale + out_row) : 1.0f;
       const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-      for (int c0 = 0; c0 < tok_pad; c0 += 8) {
-        float hi[8], lo[8];
-        tmem_ld8(lane_addr + c0, hi);
-        tmem_ld8(lane_addr + tok_pad + c0, lo);
-        if (out_row < p.n) {
+      if (p.one_term) {  // column c is token c of the chunk
+        for (int c0 = 0; c0 < n_cols; c0 += 8) {
+          float v[8];
+          tmem_ld8(lane_addr + c0, v);
+          if (out_row < p.n) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (p.one_term) {  // two tokens, not two terms of one
-              if (c0 + j < tokens) p.c[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = hi[j] * out_scale;
-              if (tok_pad + c0 + j < tokens) p.c[static_cast<size_t>(tok0 + tok_pad + c0 + j) * p.n + out_row] = lo[j] * out_scale;
-            } else if (c0 + j < tokens) {
-              p.c[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = (hi[j] + lo[j]) * out_scale;
-            }
+            for (int j = 0; j < 8; ++j)
+              if (c0 + j < tokens) p.c[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = v[j] * out_scale;
+          }
+        }
+      } else {
+        for (int c0 = 0; c0 < tok_pad; c0 += 8) {
+          float hi[8], lo[8];
+          tmem_ld8(lane_addr + c0, hi);
+          tmem_ld8(lane_addr + tok_pad + c0, lo);
+          if (out_row < p.n) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (c0 + j < tokens) p.c[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = (hi[j] + lo[j]) * out_scale;
           }
         }
       }
@@ -723,24 +737,25 @@ int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st, bool a
   // weights are exact in binary16, so up to 128 rows (verify batches) they keep the second term and with it
   // fp32-like results; prefill-sized batches take one term as well (the reference quantises those
   // activations to FP8 or binary16 itself, src/models/qwen3_5/project.cpp:55-85,307-335 of the reference).
-  // Beyond 128 rows a CTA takes 256 tokens (every dequantised weight slab then feeds 256 accumulator columns),
-  // which needs the activations converted ahead of the tiles.
+  // Beyond 128 rows a CTA takes 256 tokens, beyond 256 rows 512 where shared memory allows (every dequantised
+  // weight slab then feeds 256 or 512 accumulator columns), which needs the activations converted ahead of the tiles.
   const int two_term_rows = (FMT == kFmtQ4K || FMT == kFmtQ6K) ? kMaxTokens : 2 * kMaxTokens;
   const bool narrow = p.m > two_term_rows && std::getenv("TSR_TILE_TWO_TERMS") == nullptr;
-  p.one_term = !narrow ? 0 : (p.m > 2 * kMaxTokens && allow_scratch && std::getenv("TSR_TILE_128") == nullptr) ? 2 : 1;
+  p.one_term = !narrow ? 0 : (p.m > 2 * kMaxTokens && allow_scratch && std::getenv("TSR_TILE_128") == nullptr)
+                                 ? ((p.m > 4 * kMaxTokens && std::getenv("TSR_TILE_256") == nullptr) ? 3 : 2) : 1;
   const int nslabs = p.k / kSlab;
   const size_t ring = RING ? static_cast<size_t>(kRawStages) * RingFmt<FMT>::kStagePitch : 0;
   dim3 grid;
   size_t smem = 0;
   for (;;) {
     const int tok_pad = token_chunk(p.m, 0, p.one_term).tok_pad;  // the first chunk is the largest
-    const int per_cta = p.one_term == 2 ? 4 * kMaxTokens : p.one_term == 1 ? 2 * kMaxTokens : kMaxTokens;
+    const int per_cta = kMaxTokens << p.one_term;
     smem = 1024 + ring + kBufs * kASlabBytes + kBufs * static_cast<size_t>(2 * tok_pad) * kSlab * 2 + 256;
     grid = dim3(static_cast<unsigned>((p.n + kTileM - 1) / kTileM), static_cast<unsigned>((p.m + per_cta - 1) / per_cta));
     // activations -> operand layout once per launch, when scratch is to be had
     p.bpre = allow_scratch ? activation_scratch(st, static_cast<size_t>(grid.y) * nslabs * kBSlabPitch) : nullptr;
-    if (p.one_term == 2 && (p.bpre == nullptr || smem > 227 * 1024)) {
-      p.one_term = 1;
+    if (p.one_term >= 2 && (p.bpre == nullptr || smem > 227 * 1024)) {  // no scratch, or the ring leaves no room
+      --p.one_term;
       continue;
     }
     break;

@@ -105,11 +105,11 @@ def test_full_size_tiles_on_sampled_rows(backend, oracle, fmt, m, n, k):
     assert rel_err(got[:, rows], ref) < 5e-5
 
 
-@pytest.mark.parametrize("m", [100, 256, 300, 512])
+@pytest.mark.parametrize("m", [100, 256, 300, 512, 700])
 def test_prefill_sized_batches(backend, oracle, m):
     """Chunked-prefill batches through the ids ProjectBatch picks for them (gemm_q4k_wmma,
-    gemm_mxfp4_batched): the binary16 tcgen05 tile, 256 activation rows per CTA with one binary16 term each for
-    Q4_K, 64 rows with two terms for MXFP4."""
+    gemm_mxfp4_batched): the binary16 tcgen05 tile with one binary16 term per activation: 128, 256 or 512
+    activation rows per CTA (ragged last chunks included)."""
     n, k = 264, 1024
     a = synth.activations(m, k, seed=40)
     for dtype, w, ref_fn in ((Q4K, synth.q4k_weights(n, k, seed=41), oracle.gemm_q4k),
@@ -120,4 +120,6 @@ def test_prefill_sized_batches(backend, oracle, m):
         got = backend.download(out, np.float32, m * n).reshape(m, n)
         ref = ref_fn(a, w, m, n, k)
         assert rel_err(got, ref) < 1e-3, (dtype, proj.last_kernel)
-        assert per_element_ok(got, ref)
+        # both operands of every product are rounded to binary16 here (as in the reference's own tile): single
+        # outputs near zero reach 2.1e-3 of the vector's rms, measured; the max-relative form above is at 4e-4
+        assert per_element_ok(got, ref, tol=3e-3)
