@@ -29,6 +29,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // against 30 us); above 16 rows the tile always amortises its dequantisation better.  `launch(i0, rows)` runs rows
 // [i0, i0 + rows) and returns a status.
 constexpr uint64_t kStagedRows = 8;
+constexpr uint64_t kQ6KStagedRows = 32;  // Q6_K batches up to here run as staged passes of eight rows
 uint64_t staged_batch_max() {
   static const uint64_t v = [] {
     const char* e = std::getenv("TSR_STAGED_BATCH_MAX");  // experiments: where the tcgen05 tile takes over
@@ -45,15 +46,20 @@ bool tile_fills_device(uint64_t n) {
   }();
   return ((n + 127) / 128) * 10 >= static_cast<uint64_t>(sms) * 7;
 }
+// `always_up_to`: batches of at most this many rows take the staged kernel even when the tile would fill the
+// device (Q6_K: the tile's producers read the 210-byte blocks with narrow loads and need 160 us for
+// 17408 x 5120 whatever m is, a staged pass 20-25 us per eight rows).
 template <typename Launch>
-int staged_in_chunks(uint64_t m, uint64_t n, Launch launch) {
-  if (m > staged_batch_max() || tile_fills_device(n)) return kUnsupportedFeature;
-  for (uint64_t i0 = 0; i0 < m; i0 += kStagedRows) {
-    const uint64_t rows = m - i0 < kStagedRows ? m - i0 : kStagedRows;
-    const int rc = launch(i0, rows);
-    if (rc != kOk) return rc;  // kUnsupportedFeature can only come from the first chunk
+int staged_in_chunks(uint64_t m, uint64_t n, Launch launch, uint64_t always_up_to = 0) {
+  if (m > always_up_to && (m > staged_batch_max() || tile_fills_device(n))) return kUnsupportedFeature;
+  // eight rows per pass; four where eight rows of a long k do not fit the kernel's shared memory
+  // (k = 17408: the digits of eight activation rows alone are 296 KB)
+  for (uint64_t per : {kStagedRows, kStagedRows / 2}) {
+    int rc = kOk;
+    for (uint64_t i0 = 0; i0 < m && rc == kOk; i0 += per) rc = launch(i0, m - i0 < per ? m - i0 : per);
+    if (rc != kUnsupportedFeature) return rc;  // kUnsupportedFeature can only come from the first pass
   }
-  return kOk;
+  return kUnsupportedFeature;
 }
 
 }  // namespace
@@ -61,10 +67,11 @@ int staged_in_chunks(uint64_t m, uint64_t n, Launch launch) {
 namespace tsr {
 int gemm_q4k_dispatch(const float* a, const void* w, float* c, uint64_t m, uint64_t n, uint64_t k,
                       uint64_t split, cudaStream_t st, bool allow_scratch) {
-  const int rc = (m > kStagedRows && split == 1)
+  // more than four rows: passes of eight (or four) rows; up to eight rows that is one pass wherever it fits
+  const int rc = (m > kStagedRows / 2 && split == 1)
                      ? staged_in_chunks(m, n, [&](uint64_t i0, uint64_t rows) {
                          return staged_gemm_q4k(a + i0 * k, w, c + i0 * n, rows, n, k, 1, st);
-                       })
+                       }, kStagedRows)
                      : staged_gemm_q4k(a, w, c, m, n, k, split, st);
   if (rc != kUnsupportedFeature) return rc;
   if (m >= 9 && split == 1) {
@@ -94,10 +101,10 @@ int tsr_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_t n
   if (!aligned16(a) || (reinterpret_cast<uintptr_t>(w) & 1u) || !aligned16(c))
     return kInvalidArgument;
   const cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int rc = (m > kStagedRows && split == 1)
+  const int rc = (m > kStagedRows / 2 && split == 1)
                      ? staged_in_chunks(m, n, [&](uint64_t i0, uint64_t rows) {
                          return staged_gemm_q6k(a + i0 * k, w, c + i0 * n, rows, n, k, 1, st);
-                       })
+                       }, kQ6KStagedRows)
                      : staged_gemm_q6k(a, w, c, m, n, k, split, st);
   if (rc != kUnsupportedFeature) return rc;
   if (m >= 2 && split == 1) {

@@ -233,20 +233,26 @@ __device__ __forceinline__ void convert(const UmmaParams& p, int row, int slab, 
   } else if (FMT == kFmtQ6K) {
     const int nb = p.k / 256, b = slab >> 2, j = slab & 3, hh = j >> 1, hi = j & 1;
     const unsigned char* blk = p.w + (static_cast<size_t>(row) * nb + b) * kQ6KBlockBytes;
-    const float d = fp16_bits_to_float(blk[208] | (blk[209] << 8));
-    const unsigned char* ql = blk + 64 * hh;
-    const unsigned char* qh = blk + 128 + 32 * hh;
-    const signed char* sc = reinterpret_cast<const signed char*>(blk + 192 + 8 * hh);
+    // the block is 2-byte aligned and every offset below is even: 16-bit loads, two elements each
+    const unsigned short* b16 = reinterpret_cast<const unsigned short*>(blk);
+    const float d = fp16_bits_to_float(__ldg(b16 + 104));
     const int pp = 2 * hi + half;  // 0..3: which 32-element run of the 128-element half block
+    const unsigned short* ql = b16 + 32 * hh + 16 * (pp & 1);
+    const unsigned short* qh = b16 + 64 + 16 * hh;
+    const uint32_t scw = __ldg(b16 + 96 + 4 * hh + pp);
+    const float s0 = d * static_cast<float>(static_cast<signed char>(scw & 0xFFu));
+    const float s1 = d * static_cast<float>(static_cast<signed char>(scw >> 8));
 #pragma unroll
     for (int l = 0; l < 32; l += 2) {
+      const uint32_t lo = __ldg(ql + l / 2), hb = __ldg(qh + l / 2);
+      const float sl = l < 16 ? s0 : s1;
       float v[2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const uint32_t lo = ql[32 * (pp & 1) + l + e];
-        const uint32_t nib = (pp & 2) ? (lo >> 4) : (lo & 15u);
-        const int q = static_cast<int>(nib | (((static_cast<uint32_t>(qh[l + e]) >> (2 * pp)) & 3u) << 4)) - 32;
-        v[e] = d * static_cast<float>(sc[(l + e) / 16 + 2 * pp]) * static_cast<float>(q);
+        const uint32_t byte = (lo >> (8 * e)) & 0xFFu;
+        const uint32_t nib = (pp & 2) ? (byte >> 4) : (byte & 15u);
+        const int q = static_cast<int>(nib | ((((hb >> (8 * e)) & 0xFFu) >> (2 * pp)) & 3u) << 4) - 32;
+        v[e] = sl * static_cast<float>(q);
       }
       h[l / 2] = pack_h2(v[0], v[1]);
     }
