@@ -747,8 +747,32 @@ int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st, bool a
   // weight slab then feeds 256 or 512 accumulator columns), which needs the activations converted ahead of the tiles.
   const int two_term_rows = (FMT == kFmtQ4K || FMT == kFmtQ6K) ? kMaxTokens : 2 * kMaxTokens;
   const bool narrow = p.m > two_term_rows && std::getenv("TSR_TILE_TWO_TERMS") == nullptr;
-  p.one_term = !narrow ? 0 : (p.m > 2 * kMaxTokens && allow_scratch && std::getenv("TSR_TILE_128") == nullptr)
+  // Tokens per CTA: the widest stage is the cheapest per token, but only while the grid still covers the SMs:
+  // relative time of one CTA per stage (measured on Q4_K 17408 x 5120: 491 / 787 / 1018 TFLOP/s at 128 / 256 /
+  // 512 tokens per CTA) times the waves its grid needs.  5120 weight rows are 40 row tiles: 512 tokens in
+  // one chunk would leave 108 SMs idle, two chunks of 256 finish in two thirds of the time.
+  int widest = !narrow ? 0 : (p.m > 2 * kMaxTokens && allow_scratch && std::getenv("TSR_TILE_128") == nullptr)
                                  ? ((p.m > 4 * kMaxTokens && std::getenv("TSR_TILE_256") == nullptr) ? 3 : 2) : 1;
+  if (widest >= 2 && std::getenv("TSR_TILE_WIDEST") == nullptr) {
+    static const int sms = [] {
+      int dev = 0, v = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+      return v > 0 ? v : 148;
+    }();
+    const double unit[4] = {0.0, 0.509, 0.635, 0.982};
+    const long tiles = (p.n + kTileM - 1) / kTileM;
+    double best = 0.0;
+    int pick = widest;
+    for (int mode = widest; mode >= 1; --mode) {
+      const long per = static_cast<long>(kMaxTokens) << mode;
+      const long ctas = tiles * ((p.m + per - 1) / per);
+      const double cost = static_cast<double>((ctas + sms - 1) / sms) * unit[mode];
+      if (mode == widest || cost < best * 0.9) best = cost, pick = mode;  // a narrower stage must win clearly
+    }
+    widest = pick;
+  }
+  p.one_term = widest;
   const int nslabs = p.k / kSlab;
   const size_t ring = RING ? static_cast<size_t>(kRawStages) * RingFmt<FMT>::kStagePitch : 0;
   dim3 grid;
