@@ -32,6 +32,7 @@
 #include "codec.cuh"
 #include "launch.h"
 #include "pipeline.cuh"
+#include "tessera_b200.h"
 
 namespace tsr {
 
@@ -59,6 +60,8 @@ struct UmmaParams {
   float* c;
   int m, n, k;
   const unsigned char* bpre;  // activations already in operand layout (convert_activations_kernel), or null
+  int split_slabs;            // k is cut among gridDim.z CTAs, this many 64-wide slabs each (a multiple of a ring
+                              // stage); CTA z writes its partial sums to region z of c (m x n floats each)
   int one_term;               // batches beyond one chunk: a single binary16 term per activation; 1: 128 tokens per
                               // CTA, 2: 256, 3: 512 as two accumulators of 256 columns (2 and 3 need the
                               // pre-converted activations)
@@ -379,7 +382,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(b_full + kBufs);
   uint32_t tmem_cols = 32;
   while (tmem_cols < static_cast<uint32_t>(n_cols)) tmem_cols <<= 1;
-  const int nslabs = p.k / kSlab;
+  const int total_slabs = p.k / kSlab;
+  const int s_off = gridDim.z > 1 ? static_cast<int>(blockIdx.z) * p.split_slabs : 0;  // this CTA's first slab
+  const int nslabs = gridDim.z > 1 ? min(p.split_slabs, total_slabs - s_off) : total_slabs;
   constexpr int kProducerWarps = kProducerThreads / 32;  // then the MMA warp, the weight TMA warp, the activation copy warp
 
   if (tid == 0) {
@@ -413,7 +418,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     auto load_group = [&](int first_slab, RawHalf (&dst)[kAhead]) {
 #pragma unroll
       for (int u = 0; u < kAhead; ++u)
-        if (have_row && first_slab + u < nslabs) load_raw<FMT>(p, wrow, first_slab + u, half, dst[u]);
+        if (have_row && first_slab + u < nslabs) load_raw<FMT>(p, wrow, s_off + first_slab + u, half, dst[u]);
     };
     if (!RING) {
       load_group(0, raw[0]);
@@ -436,7 +441,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
           const int tok = row_token(r, tok_pad, p.one_term, &lo_part);
           if (tok < tokens) {
             const float4* src =
-                reinterpret_cast<const float4*>(p.a + static_cast<size_t>(tok0 + tok) * p.k + slab * kSlab + kc * 8);
+                reinterpret_cast<const float4*>(p.a + static_cast<size_t>(tok0 + tok) * p.k + (s_off + slab) * kSlab + kc * 8);
             dst[i][0] = __ldg(src);
             dst[i][1] = __ldg(src + 1);
           }
@@ -470,7 +475,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
                            make_uint4(0u, 0u, 0u, 0u)};
         RawHalf rr;
         read_raw<FMT>(ring + slot * RingFmt<FMT>::kStagePitch, trow, si, half, rr);
-        if (have_row) convert<FMT>(p, wrow, s, half, rr, piece4);
+        if (have_row) convert<FMT>(p, wrow, s_off + s, half, rr, piece4);
         if (si == kPer - 1 || s == nslabs - 1) {  // this warp is done with the stage
           __syncwarp();
           if (lane == 0) mbar_arrive(&raw_empty[slot]);
@@ -506,13 +511,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
           }
           RawHalf rr;
           read_raw<FMT>(ring + slot * RingFmt<FMT>::kStagePitch, trow, si, half, rr);
-          if (have_row) convert<FMT>(p, wrow, s, half, rr, piece4);
+          if (have_row) convert<FMT>(p, wrow, s_off + s, half, rr, piece4);
           if (si == kPer - 1 || s == nslabs - 1) {  // this warp is done with the stage
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_empty[slot]);
           }
         } else if (have_row) {
-          convert<FMT>(p, wrow, s, half, raw[grp][u], piece4);
+          convert<FMT>(p, wrow, s_off + s, half, raw[grp][u], piece4);
           if (u == kAhead - 1) load_group(s + 1 + kAhead, raw[grp]);  // this group's registers are free again
         }
         unsigned char* a_dst = a_tiles + buf * kASlabBytes + (trow >> 3) * kSbo + (trow & 7) * 16 + half * 4 * kLbo;
@@ -576,18 +581,19 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       if (rround > 0 && !mbar_wait(&raw_empty[slot], (rround - 1) & 1, &g_umma_timeouts)) break;
       unsigned char* dst = ring + slot * RingFmt<FMT>::kStagePitch;
       mbar_expect_tx(&raw_full[slot], RingFmt<FMT>::kStageBytes);
+      const int sta = s_off / kPer + st;  // the stage's index in the whole k
       if (FMT == kFmtQ4K) {
-        tma_load_3d(dst, &wmap, 0, st, row0, &raw_full[slot]);      // (18 x u64, block, rows)
+        tma_load_3d(dst, &wmap, 0, sta, row0, &raw_full[slot]);      // (18 x u64, block, rows)
       } else {
-        tma_load_3d(dst, &wmap, 0, row0, 2 * st, &raw_full[slot]);  // (128 B, rows, segments)
-        if (FMT == kFmtMxFp4) tma_load_2d(dst + RingFmt<FMT>::kWeightBytes, &smap, 16 * st, row0, &raw_full[slot]);
+        tma_load_3d(dst, &wmap, 0, row0, 2 * sta, &raw_full[slot]);  // (128 B, rows, segments)
+        if (FMT == kFmtMxFp4) tma_load_2d(dst + RingFmt<FMT>::kWeightBytes, &smap, 16 * sta, row0, &raw_full[slot]);
       }
     }
   }
 
   if (warp == kProducerWarps + 2 && lane == 0 && p.bpre != nullptr) {
     // ---------------- activation copy: one bulk copy per slab ----------------
-    const unsigned char* src = p.bpre + static_cast<size_t>(blockIdx.y) * nslabs * kBSlabPitch;
+    const unsigned char* src = p.bpre + (static_cast<size_t>(blockIdx.y) * total_slabs + s_off) * kBSlabPitch;
     for (int s = 0; s < nslabs; ++s) {
       const int buf = s & (kBufs - 1), round = s >> kBufShift;
       if (round > 0 && !mbar_wait(&empty[buf], (round - 1) & 1, &g_umma_timeouts)) break;
@@ -604,6 +610,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     tcgen05_fence_after();
     if (ok) {
       const int out_row = row0 + tid;
+      float* const cz = p.c + (gridDim.z > 1 ? static_cast<size_t>(blockIdx.z) * p.m * p.n : 0);  // this k range's region
       const float out_scale = (FMT == kFmtFp8 && out_row < p.n) ? __ldg(p.scale + out_row) : 1.0f;
       const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
       if (p.one_term) {  // column c is token c of the chunk
@@ -613,7 +620,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
           if (out_row < p.n) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              if (c0 + j < tokens) p.c[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = v[j] * out_scale;
+              if (c0 + j < tokens) cz[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = v[j] * out_scale;
           }
         }
       } else {
@@ -624,7 +631,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
           if (out_row < p.n) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              if (c0 + j < tokens) p.c[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = (hi[j] + lo[j]) * out_scale;
+              if (c0 + j < tokens) cz[static_cast<size_t>(tok0 + c0 + j) * p.n + out_row] = (hi[j] + lo[j]) * out_scale;
           }
         }
       }
@@ -702,7 +709,8 @@ unsigned char* activation_scratch(cudaStream_t st, size_t bytes) { return stream
 }  // namespace
 
 // `slot` separates users whose buffers are alive at the same time (0: the tile kernels'
-// operands and partial sums; 1: the fp32 copies around a bf16 projection; 2: attention's chunk partials).
+// operands and partial sums; 1: the fp32 copies around a bf16 projection; 2: attention's chunk partials; 3: the
+// binary16 tile's partial regions when it cuts k).
 unsigned char* stream_scratch(cudaStream_t st, size_t bytes, int slot) {
   struct Entry {
     int device;
@@ -751,8 +759,13 @@ int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st, bool a
   // relative time of one CTA per stage (measured on Q4_K 17408 x 5120: 491 / 787 / 1018 TFLOP/s at 128 / 256 /
   // 512 tokens per CTA) times the waves its grid needs.  5120 weight rows are 40 row tiles: 512 tokens in
   // one chunk would leave 108 SMs idle, two chunks of 256 finish in two thirds of the time.
+  // ... and where the grid of the widest stage still leaves half of the SMs idle (5120 weight rows: 40 row
+  // tiles), k is cut among up to four CTAs per tile, whose partial sums gemm_vec_reduce adds.
   int widest = !narrow ? 0 : (p.m > 2 * kMaxTokens && allow_scratch && std::getenv("TSR_TILE_128") == nullptr)
                                  ? ((p.m > 4 * kMaxTokens && std::getenv("TSR_TILE_256") == nullptr) ? 3 : 2) : 1;
+  constexpr int kPerStage = RING ? RingFmt<FMT>::kSlabsPerStage : 4;
+  const int stages_total = (p.k / kSlab + kPerStage - 1) / kPerStage;
+  int ksplit = 1;
   if (widest >= 2 && std::getenv("TSR_TILE_WIDEST") == nullptr) {
     static const int sms = [] {
       int dev = 0, v = 0;
@@ -762,13 +775,18 @@ int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st, bool a
     }();
     const double unit[4] = {0.0, 0.509, 0.635, 0.982};
     const long tiles = (p.n + kTileM - 1) / kTileM;
+    const int max_split = (allow_scratch && std::getenv("TSR_TILE_NO_KSPLIT") == nullptr) ? 4 : 1;
     double best = 0.0;
     int pick = widest;
     for (int mode = widest; mode >= 1; --mode) {
       const long per = static_cast<long>(kMaxTokens) << mode;
       const long ctas = tiles * ((p.m + per - 1) / per);
-      const double cost = static_cast<double>((ctas + sms - 1) / sms) * unit[mode];
-      if (mode == widest || cost < best * 0.9) best = cost, pick = mode;  // a narrower stage must win clearly
+      for (int sp = 1; sp <= max_split; ++sp) {
+        if (sp > 1 && (ctas * sp > sms || stages_total / sp < 16)) break;  // one wave, and enough k left per CTA (4096)
+        // a split costs the fill and drain of every CTA's pipeline again and the sum of the partial regions
+        const double cost = static_cast<double>((ctas * sp + sms - 1) / sms) * (unit[mode] / sp + (sp > 1 ? 0.06 : 0.0));
+        if ((mode == widest && sp == 1) || cost < best * 0.9) best = cost, pick = mode, ksplit = sp;  // must win clearly
+      }
     }
     widest = pick;
   }
@@ -795,8 +813,19 @@ int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st, bool a
     convert_activations_kernel<<<dim3(nslabs, grid.y), 256, 0, st>>>(p.a, const_cast<unsigned char*>(p.bpre), p.m, p.k, p.one_term);
     if (int rc = check_launch()) return rc;
   }
+  float* const out = p.c;
+  if (ksplit > 1) {
+    // region z of the partial buffer takes k range z; the buffer is another slot of the stream's scratch
+    p.split_slabs = (stages_total + ksplit - 1) / ksplit * kPerStage;
+    ksplit = (nslabs + p.split_slabs - 1) / p.split_slabs;
+    float* part = ksplit > 1 ? reinterpret_cast<float*>(stream_scratch(st, static_cast<size_t>(ksplit) * p.m * p.n * 4, 3)) : nullptr;
+    if (part == nullptr) ksplit = 1;
+    else p.c = part, grid.z = static_cast<unsigned>(ksplit);
+  }
   gemm_umma_kernel<FMT, RING><<<grid, kUmmaThreads, smem, st>>>(maps.weights, maps.scales, p);
-  return check_launch();
+  if (int rc = check_launch()) return rc;
+  if (ksplit > 1) return tsr_gemm_vec_reduce(p.c, out, static_cast<uint64_t>(p.m) * p.n, static_cast<uint64_t>(ksplit), st);
+  return kOk;
 }
 
 template <int FMT>
