@@ -52,9 +52,10 @@ bool tile_fills_device(uint64_t n) {
 template <typename Launch>
 int staged_in_chunks(uint64_t m, uint64_t n, Launch launch, uint64_t always_up_to = 0) {
   if (m > always_up_to && (m > staged_batch_max() || tile_fills_device(n))) return kUnsupportedFeature;
-  // eight rows per pass; four where eight rows of a long k do not fit the kernel's shared memory
-  // (k = 17408: the digits of eight activation rows alone are 296 KB)
+  // eight rows per pass; up to eight rows as two passes of four where eight rows of a long k do not fit the
+  // kernel's shared memory (k = 17408: the digits of eight activation rows alone are 296 KB)
   for (uint64_t per : {kStagedRows, kStagedRows / 2}) {
+    if (per < kStagedRows && m > kStagedRows) break;  // larger batches of a long k: the tile cuts k among its CTAs
     int rc = kOk;
     for (uint64_t i0 = 0; i0 < m && rc == kOk; i0 += per) rc = launch(i0, m - i0 < per ? m - i0 : per);
     if (rc != kUnsupportedFeature) return rc;  // kUnsupportedFeature can only come from the first pass

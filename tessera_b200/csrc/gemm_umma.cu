@@ -766,19 +766,19 @@ int launch_umma_impl(UmmaParams p, const RingMaps& maps, cudaStream_t st, bool a
   constexpr int kPerStage = RING ? RingFmt<FMT>::kSlabsPerStage : 4;
   const int stages_total = (p.k / kSlab + kPerStage - 1) / kPerStage;
   int ksplit = 1;
-  if (widest >= 2 && std::getenv("TSR_TILE_WIDEST") == nullptr) {
+  if (std::getenv("TSR_TILE_WIDEST") == nullptr) {  // narrower stages only compete from 256 tokens on; the k cut always
     static const int sms = [] {
       int dev = 0, v = 0;
       cudaGetDevice(&dev);
       cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
       return v > 0 ? v : 148;
     }();
-    const double unit[4] = {0.0, 0.509, 0.635, 0.982};
+    const double unit[4] = {0.5, 0.509, 0.635, 0.982};
     const long tiles = (p.n + kTileM - 1) / kTileM;
     const int max_split = (allow_scratch && std::getenv("TSR_TILE_NO_KSPLIT") == nullptr) ? 4 : 1;
     double best = 0.0;
     int pick = widest;
-    for (int mode = widest; mode >= 1; --mode) {
+    for (int mode = widest; mode >= (widest >= 2 ? 1 : widest); --mode) {
       const long per = static_cast<long>(kMaxTokens) << mode;
       const long ctas = tiles * ((p.m + per - 1) / per);
       for (int sp = 1; sp <= max_split; ++sp) {
