@@ -967,7 +967,8 @@ def gpu_arm(args):
 
             # ---- the step with its elementwise neighbours, folded into the projection launches
             # and as launches of their own (outside the metric: it is quoted on the projections)
-            with_elementwise, full_forward, prefill = None, None, None
+            with_elementwise, full_forward, prefill, verify = None, None, None, None
+            step_bytes_n1 = workload.total_weight_bytes(0, 1)
             if deferred == 1 and not args.only and not args.no_elementwise:
                 full, keep_full = record_with_elementwise()
 
@@ -1007,38 +1008,46 @@ def gpu_arm(args):
                                     "kernels_per_token": (k1 - k0) // args.steps, "ms_per_token": ms / args.steps,
                                     "tok_s": args.steps / (ms * 1e-3)}
                     del forward, keep_forward, emit, keep_mixers
-                    # a prefill chunk: every projection of the model over 512 tokens at once (the ids ProjectBatch
-                    # picks for that batch: the tcgen05 tiles), activations and outputs resident
-                    chunk = 512
-                    pre_act = {name: backend.upload(synth.activations(chunk, ln, seed=6, index=i))
-                               for i, (name, ln) in enumerate(act_len.items())}
-                    pre_out = {}
-                    for p_, n_, _, _ in weights:
-                        pre_out[p_.name] = max(pre_out.get(p_.name, 0), n_)
-                    pre_out = {name: backend.AllocateBuffer(chunk * n_ * 4) for name, n_ in pre_out.items()}
-                    pre_batch = LaunchBatch()
-                    pre_proj = Projector(Recorder(backend, pre_batch))
-                    flops = 0.0
-                    for p_, n_, k_, w_ in weights:
-                        pre_proj.ProjectBatch(p_.dtype, pre_act[p_.act], w_, pre_out[p_.name], chunk, n_, k_)
-                        flops += 2.0 * chunk * n_ * k_
-
-                    def run_prefill():
-                        backend.LaunchMany(pre_batch)
-                        backend.Flush()
-
-                    for _ in range(2):
-                        run_prefill()
-                    backend.Synchronize()
-                    pre_steps = max(3, args.steps // 4)
-                    ms = timed(run_prefill, pre_steps)
+                    # batches: every projection of the model over 16 tokens (a speculative-verify step) and over 512
+                    # (a prefill chunk) at once, through the ids ProjectBatch picks for the batch; activations and
+                    # outputs resident
                     peaks_now, _ = measured_peaks()
-                    tf = flops * pre_steps / (ms * 1e-3) / 1e12
-                    prefill = {"chunk_tokens": chunk, "ms_per_chunk": ms / pre_steps, "tok_s": chunk * pre_steps / (ms * 1e-3),
-                               "tflops": tf, "tensor_frac": tf / peaks_now.get("bf16_tflops_sustained", peaks_now.get("bf16_tflops", 1590.0)),
-                               "tensor_peak": "bf16_tflops_sustained (a seconds-long loop)" if "bf16_tflops_sustained" in peaks_now else "bf16_tflops"}
-                    for b_ in list(pre_act.values()) + list(pre_out.values()):
-                        b_.release()
+                    tensor_peak = peaks_now.get("bf16_tflops_sustained", peaks_now.get("bf16_tflops", 1590.0))
+                    for chunk in (16, 512):
+                        pre_act = {name: backend.upload(synth.activations(chunk, ln, seed=6, index=i))
+                                   for i, (name, ln) in enumerate(act_len.items())}
+                        pre_out = {}
+                        for p_, n_, _, _ in weights:
+                            pre_out[p_.name] = max(pre_out.get(p_.name, 0), n_)
+                        pre_out = {name: backend.AllocateBuffer(chunk * n_ * 4) for name, n_ in pre_out.items()}
+                        pre_batch = LaunchBatch()
+                        pre_proj = Projector(Recorder(backend, pre_batch))
+                        flops = 0.0
+                        for p_, n_, k_, w_ in weights:
+                            pre_proj.ProjectBatch(p_.dtype, pre_act[p_.act], w_, pre_out[p_.name], chunk, n_, k_)
+                            flops += 2.0 * chunk * n_ * k_
+
+                        def run_batched():
+                            backend.LaunchMany(pre_batch)
+                            backend.Flush()
+
+                        for _ in range(3):
+                            run_batched()
+                        backend.Synchronize()
+                        pre_steps = max(3, args.steps // 4)
+                        ms = timed(run_batched, pre_steps)
+                        tf = flops * pre_steps / (ms * 1e-3) / 1e12
+                        row = {"tokens": chunk, "ms": ms / pre_steps, "tok_s": chunk * pre_steps / (ms * 1e-3), "tflops": tf}
+                        if chunk >= 128:
+                            row["tensor_frac"] = tf / tensor_peak
+                            row["tensor_peak"] = "bf16_tflops_sustained (a seconds-long loop)" if "bf16_tflops_sustained" in peaks_now else "bf16_tflops"
+                            prefill = row
+                        else:
+                            row["hbm_gbs"] = step_bytes_n1 / (ms * 1e-3 / pre_steps) / 1e9
+                            verify = row
+                        del pre_batch, pre_proj
+                        for b_ in list(pre_act.values()) + list(pre_out.values()):
+                            b_.release()
 
     value = args.steps / (ms_total * 1e-3)
     e2e_value = args.steps / (ms_e2e * 1e-3)
@@ -1084,6 +1093,8 @@ def gpu_arm(args):
         line["with_elementwise"] = with_elementwise
     if full_forward is not None:
         line["full_forward"] = full_forward
+    if verify is not None:
+        line["verify"] = verify
     if prefill is not None:
         line["prefill"] = prefill
     if parity is not None:

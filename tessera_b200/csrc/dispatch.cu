@@ -55,10 +55,28 @@ int staged_in_chunks(uint64_t m, uint64_t n, Launch launch, uint64_t always_up_t
   // eight rows per pass; up to eight rows as two passes of four where eight rows of a long k do not fit the
   // kernel's shared memory (k = 17408: the digits of eight activation rows alone are 296 KB)
   for (uint64_t per : {kStagedRows, kStagedRows / 2}) {
-    if (per < kStagedRows && m > kStagedRows) break;  // larger batches of a long k: the tile cuts k among its CTAs
+    if (per < kStagedRows && m > kStagedRows) break;  // larger batches: the tile (it cuts k among its CTAs)
     int rc = kOk;
     for (uint64_t i0 = 0; i0 < m && rc == kOk; i0 += per) rc = launch(i0, m - i0 < per ? m - i0 : per);
     if (rc != kUnsupportedFeature) return rc;  // kUnsupportedFeature can only come from the first pass
+  }
+  return kUnsupportedFeature;
+}
+
+// One pass of up to eight rows over a k too long for the staged kernel's shared memory in one piece: k is cut
+// into `parts` equal block ranges, each range's sums go to a region of a scratch buffer (the kernel's caller
+// split, as gemm_*_vec with a split writes them) and gemm_vec_reduce adds the regions.
+template <typename Staged>
+int staged_pass_cut(uint64_t rows, uint64_t n, uint64_t k, float* c, cudaStream_t st, Staged staged) {
+  const uint64_t nb = k / 256;
+  for (uint64_t parts = 2; parts <= 8; ++parts) {
+    if (nb % parts != 0) continue;
+    float* part = reinterpret_cast<float*>(stream_scratch(st, parts * rows * n * 4, 3));
+    if (part == nullptr) return kUnsupportedFeature;
+    const int rc = staged(part, parts);
+    if (rc == kUnsupportedFeature) continue;
+    if (rc != kOk) return rc;
+    return tsr_gemm_vec_reduce(part, c, rows * n, parts, st);
   }
   return kUnsupportedFeature;
 }
@@ -71,7 +89,13 @@ int gemm_q4k_dispatch(const float* a, const void* w, float* c, uint64_t m, uint6
   // more than four rows: passes of eight (or four) rows; up to eight rows that is one pass wherever it fits
   const int rc = (m > kStagedRows / 2 && split == 1)
                      ? staged_in_chunks(m, n, [&](uint64_t i0, uint64_t rows) {
-                         return staged_gemm_q4k(a + i0 * k, w, c + i0 * n, rows, n, k, 1, st);
+                         int r = staged_gemm_q4k(a + i0 * k, w, c + i0 * n, rows, n, k, 1, st);
+                         // (larger batches of such a k are faster on the tile, which cuts k among its CTAs: 55 against 69 us at m = 16)
+                         if (r == kUnsupportedFeature && rows > kStagedRows / 2 && m <= kStagedRows && allow_scratch)
+                           r = staged_pass_cut(rows, n, k, c + i0 * n, st, [&](float* part, uint64_t parts) {
+                             return staged_gemm_q4k(a + i0 * k, w, part, rows, n, k, parts, st);
+                           });
+                         return r;
                        }, kStagedRows)
                      : staged_gemm_q4k(a, w, c, m, n, k, split, st);
   if (rc != kUnsupportedFeature) return rc;
@@ -104,7 +128,12 @@ int tsr_gemm_q6k(const float* a, const void* w, float* c, uint64_t m, uint64_t n
   const cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int rc = (m > kStagedRows / 2 && split == 1)
                      ? staged_in_chunks(m, n, [&](uint64_t i0, uint64_t rows) {
-                         return staged_gemm_q6k(a + i0 * k, w, c + i0 * n, rows, n, k, 1, st);
+                         int r = staged_gemm_q6k(a + i0 * k, w, c + i0 * n, rows, n, k, 1, st);
+                         if (r == kUnsupportedFeature && rows > kStagedRows / 2)
+                           r = staged_pass_cut(rows, n, k, c + i0 * n, st, [&](float* part, uint64_t parts) {
+                             return staged_gemm_q6k(a + i0 * k, w, part, rows, n, k, parts, st);
+                           });
+                         return r;
                        }, kQ6KStagedRows)
                      : staged_gemm_q6k(a, w, c, m, n, k, split, st);
   if (rc != kUnsupportedFeature) return rc;
