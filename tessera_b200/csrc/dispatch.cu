@@ -1066,7 +1066,8 @@ bool as_projection(const std::vector<PendingLaunch>& q, size_t i, Projection* ou
   if (op.nbuf != 3 || (op.nsc != 3 && op.nsc != 4)) return false;
   const bool with_tp = name_ends(name, "_allreduce");
   const uint64_t m = op.sc[0], n = op.sc[1], k = op.sc[2], split = op.nsc == 4 ? op.sc[3] : 1;
-  if (m > 8) return false;
+  // nine to sixteen rows (a verify step): two passes of the merged launch, see issue_queue
+  if (m > 2 * kStagedRows || (m > kStagedRows && with_tp)) return false;
   *out = Projection{fmt, static_cast<const float*>(op.buf[0]),
                     GroupTarget{op.buf[1], static_cast<float*>(const_cast<void*>(op.buf[2])), n}, m, k, 1, with_tp};
   if (split == 1) return true;
@@ -1100,7 +1101,7 @@ bool as_prologue(const tsr_context* ctx, const std::vector<PendingLaunch>& q, si
   if (!ctx->fold_elementwise || !fuse_elementwise() || i + 1 >= q.size()) return false;
   const PendingLaunch& op = q[i];
   Projection next;
-  if (!as_projection(q, i + 1, &next)) return false;
+  if (!as_projection(q, i + 1, &next) || next.m > kStagedRows) return false;
   if (is_named(op, "silu_mul")) {
     const size_t bytes = op.sc[0] * 4;
     if (next.a != op.buf[2] || next.m * next.k != op.sc[0]) return false;
@@ -1338,15 +1339,28 @@ int issue_queue(tsr_context* ctx, const std::vector<PendingLaunch>& q) {
       t[count++] = next.t;
       end += next.ops;
     }
-    if (count == 1) {
+    if (count == 1 && first.m <= kStagedRows) {
       Projection only = first;
       only.t = t[0];
       if (as_epilogue_add(ctx, q, end, only, has_pro ? pro_in : first.a, a_bytes, has_pro ? &pro : nullptr, &t[0])) ++end;
     }
     // with a prologue the launch reads the prologue's input; the projections' A is its output
     const float* act = has_pro ? pro_in : first.a;
-    int rc = fused_group(ctx, first.fmt, act, t, count, first.m, first.k, first.with_tp, ctx->stream,
-                         has_pro ? &pro : nullptr);
+    int rc = kOk;
+    if (first.m <= kStagedRows) {
+      rc = fused_group(ctx, first.fmt, act, t, count, first.m, first.k, first.with_tp, ctx->stream, has_pro ? &pro : nullptr);
+    } else {
+      // nine to sixteen rows: the merged launch twice, eight rows and the rest
+      for (uint64_t i0 = 0; i0 < first.m && rc == kOk; i0 += kStagedRows) {
+        GroupTarget part[kMaxGroup];
+        for (int j = 0; j < count; ++j) {
+          part[j] = t[j];
+          part[j].c = t[j].c + i0 * t[j].n;
+        }
+        const uint64_t rows = first.m - i0 < kStagedRows ? first.m - i0 : kStagedRows;
+        rc = fused_group(ctx, first.fmt, act + i0 * first.k, part, count, rows, first.k, false, ctx->stream, nullptr);
+      }
+    }
     if (rc == kUnsupportedFeature) {
       for (size_t j = i; j < end; ++j)
         if (int r = issue_one(ctx, q[j])) return r;

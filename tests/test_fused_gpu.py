@@ -149,6 +149,41 @@ def test_deferred_queue_merges_and_replays_as_a_graph(backend, oracle):
         backend.SetDeferred(0)
 
 
+@pytest.mark.parametrize("m", [11, 16])
+def test_deferred_queue_merges_verify_batches_as_two_passes(backend, oracle, m):
+    """Nine to sixteen rows (a speculative-verify step): projections that share their activations leave the
+    queue as the merged launch run twice, eight rows and the rest; a single projection over a long k (which
+    one staged pass cannot hold in shared memory) the same way with k cut inside the launch."""
+    proj = Projector(backend)
+    k, ns = 5120, [1024, 768, 48]
+    a = synth.activations(m, k, seed=190)
+    ab = backend.upload(a)
+    ws = [synth.q4k_weights(n, k, seed=192 + i) for i, n in enumerate(ns)]
+    wbs = [backend.upload(w) for w in ws]
+    k2, n2 = 17408, 264
+    a2 = synth.activations(m, k2, seed=191)
+    w2 = synth.q6k_weights(n2, k2, seed=199)
+    a2b, w2b = backend.upload(a2), backend.upload(w2)
+    outs = [backend.AllocateBuffer(m * n * 4) for n in ns + [n2]]
+    refs = [oracle.gemm_q4k(a, w, m, n, k) for w, n in zip(ws, ns)] + [oracle.gemm_q6k(a2, w2, m, n2, k2)]
+    backend.Synchronize()
+    backend.SetDeferred(1)
+    try:
+        for rep in range(3):
+            _, dev0, _ = backend.LaunchStats()
+            for wb, out, n in zip(wbs, outs, ns):
+                proj.ProjectBatch(Q4K, ab, wb, out, m, n, k)
+            proj.ProjectBatch(Q6K, a2b, w2b, outs[3], m, n2, k2)
+            backend.Synchronize()
+            _, dev1, _ = backend.LaunchStats()
+            assert dev1 - dev0 == 4, dev1 - dev0   # two passes for the three that share a, two for the long one
+            for out, n, r in zip(outs, ns + [n2], refs):
+                y = backend.download(out, np.float32, m * n).reshape(m, n)
+                assert rel_err(y, r) < 2e-4 and per_element_ok(y, r)
+    finally:
+        backend.SetDeferred(0)
+
+
 def test_deferred_launch_still_checks_its_arguments_at_once(backend):
     backend.SetDeferred(1)
     try:
